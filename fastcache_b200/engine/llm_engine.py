@@ -1,0 +1,509 @@
+"""Serving engine: request intake, the step loop and the compression policies.
+
+Parity
+  * text engine and `generate()`       nanovllm/engine/llm_engine.py:12-82
+  * multimodal engine with compression "kv-cache pipeline"/nanovllm/engine/
+    llava_engine.py:52-620 — constructor kwargs (:61-86), `add_request`,
+    `step(apply_compression) -> (outputs, num_tokens)` with num_tokens > 0 for
+    prefill tokens and < 0 for minus the decode batch size, dual-batch choice,
+    per-prefill controller decision, sync / async / decode-overlap
+    compression, `_free_compressed_blocks`
+  * lazy policy (compress when the pool is nearly full)
+    nanovllm_fastapi_server.py:98-145
+
+One engine class serves text and image requests.  Host decisions never depend
+on `event.query()` or timing, only on step counts and queue state, so the
+replicated schedulers of tensor-parallel ranks stay in lockstep; the ordering
+"compression finished before its tail blocks are reused" is enforced on the
+device (`main_stream.wait_event`) before the blocks return to the free list.
+"""
+from __future__ import annotations
+
+import atexit
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence as Seq, Tuple, Union
+
+import torch
+
+from ..config import Config, ModelConfig, text_config_of
+from ..parallel import tp as tpmod
+from ..sampling_params import SamplingParams
+from .model_runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import CompressionState, Sequence, SequenceStatus
+
+
+@dataclass
+class PendingCompression:
+    """A compression launched on a side stream (or in layer chunks)."""
+    seq: Sequence
+    event: Any = None
+    start_event: Any = None
+    tokens: int = 0
+    next_layer: int = 0           # decode pipeline: first layer not yet launched
+    rows: int = 0                 # rows that were compressed
+    new_len: int = 0
+    reported: bool = False
+
+
+@dataclass
+class StepStats:
+    steps: int = 0
+    prefill_steps: int = 0
+    decode_steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    compressions: int = 0
+    compressed_rows_in: int = 0
+    compressed_rows_out: int = 0
+    blocks_freed: int = 0
+    lazy_triggers: int = 0
+    preemptions: int = 0
+    history: List[dict] = field(default_factory=list)
+
+
+class LLMEngine:
+    def __init__(self, model: Union[str, Any] = "", compressor_path: Optional[str] = None,
+                 compression_factor: int = 5, enable_compression: bool = False,
+                 async_compression: bool = False, compression_backend: str = "mlp",
+                 kvpress_method: str = "streaming_llm", compression_pipeline: str = "auto",
+                 compression_streams: int = 2, greenctx_enabled: bool = False,
+                 greenctx_compress_ratio: float = 0.25, greenctx_main_ratio: float = 0.75,
+                 greenctx_main_stream: bool = False, decode_layers_per_step: int = 4,
+                 auto_tune: bool = False, auto_tune_interval: int = 4, auto_dual_batch: bool = True,
+                 auto_dual_interval: int = 4, auto_min_seq_len: int = 256, auto_min_output_len: int = 64,
+                 auto_min_speedup: float = 1.05, auto_force_compress: bool = False,
+                 compressor: Any = None, tokenizer: Any = None, **kwargs):
+        hf_config = kwargs.pop("hf_config", None)
+        if not isinstance(model, str):          # a config object / dict instead of a path: random init
+            hf_config, model = model, ""
+        if isinstance(hf_config, dict):
+            hf_config = ModelConfig(**hf_config)
+        config = Config.from_kwargs(model, **kwargs)
+        if hf_config is not None:
+            config.hf_config = hf_config
+            if not model:
+                config.extra["random_init"] = True
+        elif model:
+            config.hf_config = ModelConfig.from_pretrained(model)
+        else:
+            raise ValueError("give a model directory or an hf_config")
+        tc = text_config_of(config.hf_config)
+        config.max_model_len = min(config.max_model_len, getattr(tc, "max_position_embeddings", 1 << 30))
+        if config.tensor_parallel_size > 1 and not tpmod.is_tp_initialized():
+            tpmod.init_tensor_parallel(config.tensor_parallel_size)
+        self.config = config
+        Sequence.block_size = config.kvcache_block_size
+
+        self.tokenizer = tokenizer
+        self.processor = None
+        if tokenizer is None and model:
+            self._load_tokenizer(model)
+        if config.eos < 0:
+            eos = getattr(self.tokenizer, "eos_token_id", None)
+            if eos is None:
+                eos = getattr(tc, "eos_token_id", -1)
+                if isinstance(eos, (list, tuple)):
+                    eos = eos[0]
+            config.eos = -1 if eos is None else int(eos)
+
+        # a compression mode given through Config wins over the bool pair
+        if config.compression_mode != "none":
+            enable_compression = True
+            async_compression = config.compression_mode == "async"
+        elif enable_compression:
+            config.compression_mode = "async" if async_compression else "eager"
+        self.model_runner = ModelRunner(
+            config, compressor_path=compressor_path, compression_factor=compression_factor,
+            enable_compression=enable_compression, async_compression=async_compression,
+            compression_backend=compression_backend, kvpress_method=kvpress_method,
+            compression_pipeline=compression_pipeline, compression_streams=compression_streams,
+            greenctx_enabled=greenctx_enabled, greenctx_compress_ratio=greenctx_compress_ratio,
+            greenctx_main_ratio=greenctx_main_ratio, greenctx_main_stream=greenctx_main_stream,
+            decode_layers_per_step=decode_layers_per_step, compressor=compressor,
+            min_seq_len=int(config.extra.get("min_seq_len", 2)),
+            kvpress_params=config.extra.get("kvpress_params"))
+        self.scheduler = Scheduler(config)
+        self.scheduler.on_release = self._on_release
+
+        r = self.model_runner
+        self.enable_compression = enable_compression and r.compression_pipeline != "none"
+        self.async_compression = async_compression
+        self.compression_factor = r.compression_factor
+        self.compression_backend = compression_backend
+        self.kvpress_method = kvpress_method
+        self.compression_pipeline = r.compression_pipeline
+        self.compression_mode = config.compression_mode if self.enable_compression else "none"
+        self.image_token_len = r.image_token_len
+        self.image_token_id = r.image_token_id
+        self.auto_tune = auto_tune
+        self.auto_tune_interval = max(1, auto_tune_interval)
+        self.auto_dual_batch = auto_dual_batch
+        self.auto_dual_interval = max(1, auto_dual_interval)
+        self._auto_controller = None
+        if auto_tune and self.enable_compression:
+            from .auto_compress_controller import AutoCompressionController
+            self._auto_controller = AutoCompressionController(
+                compression_backend=compression_backend, kvpress_method=kvpress_method,
+                compression_factor=self.compression_factor, num_layers=r.num_hidden_layers,
+                num_kv_heads=r.num_key_value_heads, head_dim=r.head_dim,
+                greenctx_enabled=r.greenctx_enabled, decision_interval=self.auto_tune_interval,
+                min_seq_len=auto_min_seq_len, min_output_len=auto_min_output_len,
+                min_speedup=auto_min_speedup, force_compress=auto_force_compress,
+                dual_batch_enabled=auto_dual_batch, dual_batch_interval=self.auto_dual_interval)
+        self._pending: Dict[int, PendingCompression] = {}
+        self._pending_compression_events = self._pending     # name used by the reference's benches
+        self.stats = StepStats()
+        self._timing: Optional[dict] = None
+        atexit.register(self.exit)
+
+    # ------------------------------------------------------------------ set-up
+    def _load_tokenizer(self, model: str) -> None:
+        try:
+            from transformers import AutoTokenizer
+            self.tokenizer = AutoTokenizer.from_pretrained(model, use_fast=True, trust_remote_code=False)
+        except Exception:
+            self.tokenizer = None
+        try:
+            from transformers import AutoProcessor
+            self.processor = AutoProcessor.from_pretrained(model, trust_remote_code=False)
+        except Exception:
+            self.processor = None
+
+    def exit(self) -> None:
+        r = getattr(self, "model_runner", None)
+        if r is not None:
+            r.exit()
+
+    # ---------------------------------------------------------------- requests
+    def preprocess_image(self, image: Any) -> Tuple[torch.Tensor, Any]:
+        """PIL image / array / tensor -> (pixel tensor on the model device, metadata)."""
+        return self.model_runner.model.preprocess_image(image, self.model_runner.device,
+                                                        self.model_runner.dtype, self.processor)
+
+    def add_request(self, prompt: Union[str, List[int]], sampling_params: Optional[SamplingParams] = None,
+                    image: Any = None) -> Sequence:
+        sp = sampling_params or SamplingParams()
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("no tokenizer is loaded: pass token ids")
+            prompt = self.tokenizer.encode(prompt)
+        prompt = list(prompt)
+        n_img, img_pos, pixels, meta = 0, -1, None, None
+        if image is not None:
+            if not self.model_runner.is_multimodal:
+                raise ValueError("this model takes no images")
+            pixels, meta = self.preprocess_image(image)
+            n_img = self.model_runner.model.num_image_rows(meta)
+            tok = self.image_token_id
+            if tok in prompt:
+                img_pos = prompt.index(tok)
+            else:                                   # no placeholder given: put the image first
+                prompt = [tok] + prompt
+                img_pos = 0
+        seq = Sequence(prompt, sp, num_image_tokens=n_img, image_token_pos=img_pos)
+        seq.pixel_values, seq.image_meta = pixels, meta
+        if seq.prompt_rows + 1 > self.config.max_model_len:
+            raise ValueError(f"prompt of {seq.prompt_rows} rows exceeds max_model_len {self.config.max_model_len}")
+        self.scheduler.add(seq)
+        return seq
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    # -------------------------------------------------------------- compression
+    def _on_release(self, seq: Sequence) -> None:
+        """A request is about to lose its blocks: order any running compression first."""
+        p = self._pending.pop(seq.seq_id, None)
+        if p is not None and p.event is not None and self.model_runner.main_stream is not None:
+            self.model_runner.main_stream.wait_event(p.event)
+        self.model_runner.release(seq)
+
+    def _privatize(self, seq: Sequence) -> None:
+        bm = self.scheduler.block_manager
+        for i in bm.private_copy_needed(seq):
+            if i >= seq.kv_num_blocks:
+                continue
+            old, new = bm.make_private(seq, i)
+            self.model_runner.copy_block(old, new)
+
+    def _free_compressed_blocks(self, seq: Sequence, new_len: Optional[int] = None) -> int:
+        """Set the compressed length and give the tail blocks back to the pool."""
+        if new_len is not None:
+            seq.kv_cache_len = new_len + int(seq._pending_row)
+        freed = self.scheduler.block_manager.free_blocks_after_compression(seq, seq.kv_num_blocks)
+        self.stats.blocks_freed += freed
+        return freed
+
+    def _eligible(self, seq: Sequence) -> bool:
+        return (seq.compression_state is CompressionState.NONE and not seq.is_finished
+                and seq.rows_in_pool >= max(2 * self.compression_factor, 4))
+
+    def _compress_now(self, seqs: List[Sequence]) -> None:
+        """Synchronous (main-stream) compression of `seqs`, in chunks of the compress cap."""
+        r = self.model_runner
+        cap = self.scheduler.compress_cap
+        seqs = [s for s in seqs if self._eligible(s)]
+        for i in range(0, len(seqs), cap):
+            chunk = seqs[i:i + cap]
+            for s in chunk:
+                self._privatize(s)
+            rows = [s.rows_in_pool for s in chunk]
+            saved = [s._kv_cache_len for s in chunk]
+            for s, n in zip(chunk, rows):
+                s._kv_cache_len = n
+            try:
+                new = r.compress_kv_cache_batch(chunk, stream=r.main_stream)
+            except Exception:
+                for s, v in zip(chunk, saved):
+                    s._kv_cache_len = v
+                raise
+            for s, n_in, n_out in zip(chunk, rows, new):
+                s.compression_state = CompressionState.COMPLETED
+                self._free_compressed_blocks(s, n_out)
+                self.stats.compressions += 1
+                self.stats.compressed_rows_in += n_in
+                self.stats.compressed_rows_out += n_out
+
+    def _launch_async(self, seqs: List[Sequence]) -> None:
+        """Whole-request compression on a side stream; finalised before the request decodes."""
+        r = self.model_runner
+        seqs = [s for s in seqs if self._eligible(s)]
+        if not seqs:
+            return
+        if r.main_stream is None:                 # no streams on this device: degrade to sync
+            self._compress_now(seqs)
+            return
+        for s in seqs:
+            self._privatize(s)
+        stream = r.next_compress_stream()
+        ready = torch.cuda.Event()
+        ready.record(r.main_stream)
+        stream.wait_event(ready)
+        rows = [s.rows_in_pool for s in seqs]
+        for s, n in zip(seqs, rows):
+            s._kv_cache_len = n
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        new = r.compress_kv_cache_batch(seqs, stream=stream)
+        end.record(stream)
+        for s, n_in, n_out in zip(seqs, rows, new):
+            s.compression_state = CompressionState.IN_PROGRESS
+            s.kv_cache_len = n_out + int(s._pending_row)
+            self._pending[s.seq_id] = PendingCompression(s, end, start, n_in, rows=n_in, new_len=n_out)
+            self.stats.compressions += 1
+            self.stats.compressed_rows_in += n_in
+            self.stats.compressed_rows_out += n_out
+
+    def _start_chunked(self, seqs: List[Sequence]) -> None:
+        """Decode pipeline: compress a few layers per engine step beside decode."""
+        for s in seqs:
+            if not self._eligible(s):
+                continue
+            self._privatize(s)
+            s.compression_state = CompressionState.IN_PROGRESS
+            s.hold = True
+            self._pending[s.seq_id] = PendingCompression(s, None, None, s.rows_in_pool, 0, s.rows_in_pool, 0)
+
+    def _advance_chunked(self) -> None:
+        r = self.model_runner
+        todo = [p for p in self._pending.values() if p.seq.hold]
+        if not todo:
+            return
+        L = r.num_hidden_layers
+        step = max(1, r.decode_layers_per_step)
+        stream = r.next_compress_stream()
+        if stream is not None:
+            ready = torch.cuda.Event()
+            ready.record(r.main_stream)
+            stream.wait_event(ready)
+        groups: Dict[int, List[PendingCompression]] = {}
+        for p in todo:
+            groups.setdefault(p.next_layer, []).append(p)
+        for first, ps in groups.items():
+            last = min(L, first + step)
+            seqs = [p.seq for p in ps]
+            saved = [s._kv_cache_len for s in seqs]
+            for p in ps:
+                p.seq._kv_cache_len = p.rows
+            new = r.compress_kv_cache_batch(seqs, first, last, stream=stream)
+            for p, s, v, n in zip(ps, seqs, saved, new):
+                s._kv_cache_len = v
+                p.next_layer = last
+                p.new_len = n
+                if last >= L:
+                    ev = None
+                    if stream is not None:
+                        ev = torch.cuda.Event()
+                        ev.record(stream)
+                    p.event = ev
+                    s.hold = False
+                    s.kv_cache_len = n + int(s._pending_row)
+                    self.stats.compressions += 1
+                    self.stats.compressed_rows_in += p.rows
+                    self.stats.compressed_rows_out += n
+
+    def _finalize_pending(self, seqs: Seq[Sequence]) -> None:
+        """Before `seqs` read their KV: wait (on the device) for their compression, free tails."""
+        r = self.model_runner
+        for s in seqs:
+            p = self._pending.get(s.seq_id)
+            if p is None or s.hold:
+                continue
+            if p.event is not None and r.main_stream is not None:
+                r.main_stream.wait_event(p.event)
+            del self._pending[s.seq_id]
+            s.compression_state = CompressionState.COMPLETED
+            self._free_compressed_blocks(s)
+
+    def _lazy_check(self) -> None:
+        sch = self.scheduler
+        if not sch.lazy_compress_due():
+            return
+        cands = [s for s in sch.lazy_candidates() if self._eligible(s)]
+        if not cands:
+            return
+        self.stats.lazy_triggers += 1
+        self._compress_now(cands)
+
+    # ----------------------------------------------------------------------- step
+    def step(self, apply_compression: Optional[bool] = None) -> Tuple[List[Tuple[int, List[int]]], int]:
+        sch, r = self.scheduler, self.model_runner
+        compress = self.enable_compression if apply_compression is None else \
+            (apply_compression and self.enable_compression)
+        mode = self.compression_mode
+        ctl = self._auto_controller if compress else None
+        if compress and mode == "lazy":
+            self._lazy_check()
+        if compress:
+            self._advance_chunked()
+        prefer_decode = False
+        if ctl is not None and self.auto_dual_batch:
+            prefer_decode = ctl.decide_batch_type(waiting=len(sch.waiting), running=len(sch.running),
+                                                  pending_compressions=len(self._pending)) == "decode"
+        seqs, is_prefill = sch.schedule(prefer_decode=prefer_decode)
+        self.stats.preemptions = sch.num_preemptions
+        if not seqs:
+            if self._pending:
+                return [], 0
+            raise RuntimeError("nothing to schedule")
+        pipeline, use_async = self.compression_pipeline, self.async_compression
+        if is_prefill and ctl is not None:
+            d = ctl.decide(batch_size=len(seqs), seq_len=max(s.prompt_rows for s in seqs),
+                           expected_output_len=max(1, sum(s.max_tokens for s in seqs) // len(seqs)),
+                           pending_compressions=len(self._pending))
+            pipeline, use_async = d.pipeline, d.async_compress
+            r.update_streams(d.greenctx_enabled, d.sm_compress_ratio, d.sm_main_ratio, d.compression_streams)
+            r.decode_layers_per_step = d.decode_layers_per_step
+        if not is_prefill:
+            self._finalize_pending(seqs)
+        timing = self._begin_timing(ctl)
+        tokens = r.run(seqs, is_prefill)
+        self._end_timing(ctl, timing, is_prefill, seqs)
+        now = time.perf_counter()
+        if is_prefill:
+            n_tok = sum(s.logical_len - s.num_cached_tokens for s in seqs)
+            for s in seqs:
+                if s.first_token_time is None:
+                    s.first_token_time = now
+            if compress and mode in ("eager", "async") and pipeline != "none":
+                if pipeline == "decode":
+                    self._start_chunked(list(seqs))
+                elif use_async or mode == "async":
+                    self._launch_async(list(seqs))
+                else:
+                    self._compress_now(list(seqs))
+        else:
+            n_tok = -len(seqs)
+        finished = sch.postprocess(seqs, tokens)
+        for s in finished:
+            s.finish_time = now
+        st = self.stats
+        st.steps += 1
+        if is_prefill:
+            st.prefill_steps += 1
+            st.prefill_tokens += n_tok
+        else:
+            st.decode_steps += 1
+            st.decode_tokens += len(seqs)
+        outputs = [(s.seq_id, s.completion_token_ids) for s in finished]
+        self._last_finished = finished
+        return outputs, n_tok
+
+    # ---------------------------------------------------------- controller timing
+    def _begin_timing(self, ctl):
+        if ctl is None or self.model_runner.main_stream is None:
+            return None
+        if self.stats.steps % self.auto_tune_interval:
+            return None
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(self.model_runner.main_stream)
+        return a, b
+
+    def _end_timing(self, ctl, timing, is_prefill: bool, seqs) -> None:
+        if timing is None:
+            return
+        a, b = timing
+        b.record(self.model_runner.main_stream)
+        b.synchronize()
+        ms = a.elapsed_time(b)
+        if is_prefill:
+            ctl.update_prefill(ms, sum(s.prompt_rows for s in seqs))
+        else:
+            ctl.update_decode(ms, len(seqs))
+        for p in self._pending.values():
+            if not p.reported and p.start_event is not None and p.event is not None and p.event.query():
+                # feeds an EWMA only; scheduling never branches on it
+                ctl.update_compress(p.start_event.elapsed_time(p.event), p.tokens)
+                p.reported = True
+
+    # ------------------------------------------------------------------- generate
+    def generate(self, prompts: List[Union[str, List[int]]],
+                 sampling_params: Union[SamplingParams, List[SamplingParams], None] = None,
+                 images: Optional[List[Any]] = None, use_tqdm: bool = False,
+                 apply_compression: Optional[bool] = None) -> List[dict]:
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        if not isinstance(sampling_params, list):
+            sampling_params = [sampling_params] * len(prompts)
+        images = images or [None] * len(prompts)
+        order = []
+        for p, sp, im in zip(prompts, sampling_params, images):
+            order.append(self.add_request(p, sp, im).seq_id)
+        bar = None
+        if use_tqdm:
+            try:
+                from tqdm.auto import tqdm
+                bar = tqdm(total=len(prompts), desc="Generating", dynamic_ncols=True)
+            except Exception:
+                bar = None
+        results: Dict[int, List[int]] = {}
+        prefill_tps = decode_tps = 0.0
+        while not self.is_finished():
+            t = time.perf_counter()
+            out, n = self.step(apply_compression)
+            dt = max(time.perf_counter() - t, 1e-9)
+            if n > 0:
+                prefill_tps = n / dt
+            elif n < 0:
+                decode_tps = -n / dt
+            for sid, toks in out:
+                results[sid] = toks
+                if bar is not None:
+                    bar.update(1)
+            if bar is not None:
+                bar.set_postfix({"Prefill": f"{int(prefill_tps)}tok/s", "Decode": f"{int(decode_tps)}tok/s"})
+        if bar is not None:
+            bar.close()
+        outs = []
+        for sid in order:
+            toks = results[sid]
+            text = self.tokenizer.decode(toks) if self.tokenizer is not None else ""
+            outs.append({"text": text, "token_ids": toks})
+        return outs
+
+
+# names of the reference's engine classes
+LlavaLLMEngine = LLMEngine

@@ -1,0 +1,522 @@
+"""Model runner: owns the model, the paged KV pool, step metadata, CUDA graphs
+and the compression entry points.
+
+Parity
+  * text runner     nanovllm/engine/model_runner.py:12-199 (pool sizing and
+    binding :32-45, prefill/decode metadata :56-112, graph capture :155-199)
+  * multimodal / compression runner  "kv-cache pipeline"/nanovllm/engine/
+    llava_model_runner.py:208-1415 (model-type detection, compressor loading,
+    image-expanded prefill metadata, compress batch, async compression on side
+    streams, decode-overlap chunks, stream rebuilds, graph capture)
+
+One class serves every model family here.  Differences by design: block
+tables always cover image-expanded rows; compression and eviction run in the
+pool (see fastcache_b200.compress.inpool); under tensor parallelism every rank
+samples the same token from gathered logits with a shared seed instead of
+rank 0 broadcasting it; on a CPU device the "graph" path is the same
+static-buffer, padded-batch replay code with eager execution in place of
+`CUDAGraph.replay()`, which keeps that path testable without a GPU.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Dict, List, Optional, Sequence as Seq, Tuple
+
+import numpy as np
+import torch
+
+from ..compress.ccm import PackedCCMWeights, load_compressor
+from ..compress.inpool import ccm_compress_in_pool, evict_in_pool
+from ..compress.scorers import NEEDS_QUERIES, n_kept_for, ratio_from_factor
+from ..config import Config, ModelConfig, text_config_of
+from ..layers.sampler import Sampler
+from ..models.registry import build_model, detect_model_type
+from ..parallel import tp as tpmod
+from ..utils.context import reset_context, set_context
+from ..utils.loader import init_random_weights, load_model
+from ..utils.memory import get_gpu_memory
+from .sequence import CompressionState, Sequence
+
+
+def _resolve_device(config: Config) -> torch.device:
+    if config.device != "auto":
+        return torch.device(config.device)
+    if torch.cuda.is_available():
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
+
+
+def _resolve_dtype(config: Config, device: torch.device) -> torch.dtype:
+    if config.dtype == "auto":
+        return torch.bfloat16 if device.type == "cuda" else torch.float32
+    return {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16,
+            "float16": torch.float16, "fp32": torch.float32, "float32": torch.float32}[config.dtype]
+
+
+class ModelRunner:
+    def __init__(self, config: Config, compressor_path: Optional[str] = None, compression_factor: int = 5,
+                 enable_compression: bool = False, async_compression: bool = False,
+                 compression_backend: str = "mlp", kvpress_method: str = "streaming_llm",
+                 compression_pipeline: str = "auto", compression_streams: int = 2,
+                 greenctx_enabled: bool = False, greenctx_compress_ratio: float = 0.25,
+                 greenctx_main_ratio: float = 0.75, greenctx_main_stream: bool = False,
+                 decode_layers_per_step: int = 4, compressor: Any = None, min_seq_len: int = 2,
+                 kvpress_params: Optional[dict] = None):
+        self.config = config
+        self.device = _resolve_device(config)
+        self.dtype = _resolve_dtype(config, self.device)
+        self.block_size = config.kvcache_block_size
+        self.enforce_eager = config.enforce_eager
+        self.tp_size = tpmod.get_tp_size()
+        self.tp_rank = tpmod.get_tp_rank()
+        hf = config.hf_config
+        if hf is None:
+            hf = ModelConfig.from_pretrained(config.model)
+            config.hf_config = hf
+        self.hf_config = hf
+        self.text_config = text_config_of(hf)
+        self.model_type = detect_model_type(hf)
+        self.is_multimodal = self.model_type in ("llava", "minicpm")
+
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(self.dtype)
+        try:
+            with torch.device(self.device):
+                self.model = build_model(hf)
+        finally:
+            torch.set_default_dtype(prev)
+        self.model.eval()
+        self._load_weights()
+
+        tc = self.text_config
+        self.num_hidden_layers = tc.num_hidden_layers
+        heads = tc.num_attention_heads
+        kvh = getattr(tc, "num_key_value_heads", None) or heads
+        self.head_dim = getattr(tc, "head_dim", None) or tc.hidden_size // heads
+        self.total_kv_heads = kvh
+        self.num_key_value_heads = max(1, kvh // self.tp_size)     # per rank
+        self.num_heads_local = heads // self.tp_size
+        self.image_token_len = int(getattr(self.model, "image_token_len", 0))
+        self.image_token_id = getattr(self.model, "image_token_id", None)
+
+        self.sampler = Sampler(config.seed)
+        self.allocate_kv_cache()
+
+        # ------------------------------------------------------ compression
+        self.enable_compression = enable_compression
+        self.async_compression = async_compression
+        self.compression_backend = compression_backend
+        self.kvpress_method = kvpress_method
+        self.kvpress_params = dict(kvpress_params or {})
+        self.compression_factor = compression_factor
+        self.min_seq_len = min_seq_len
+        self.decode_layers_per_step = decode_layers_per_step
+        self.compressor = None
+        self.packed_compressor: Optional[PackedCCMWeights] = None
+        self._compressed_lens: Dict[int, int] = {}
+        self._window_q: Dict[int, Dict[int, torch.Tensor]] = {}
+        if enable_compression:
+            self._load_compressor(compressor_path, compressor)
+        if not enable_compression or (compression_backend == "mlp" and self.packed_compressor is None):
+            self.compression_pipeline = "none"
+        elif compression_pipeline == "auto":
+            # merge compression is GEMM work that hides under memory-bound decode;
+            # eviction is cheap and goes with prefill
+            self.compression_pipeline = "decode" if compression_backend == "mlp" else "prefill"
+        else:
+            self.compression_pipeline = compression_pipeline
+        self.obs_window = int(self.kvpress_params.get("window", 64)) \
+            if (enable_compression and compression_backend == "kvpress" and kvpress_method in NEEDS_QUERIES) else 0
+
+        # ---------------------------------------------------------- streams
+        self.greenctx_enabled = False
+        self._greenctx_info: Dict[str, Any] = {}
+        self.main_stream = None
+        self.compress_streams: List[Any] = []
+        self._rr = 0
+        if self.device.type == "cuda":
+            from ..utils.streams import build_streams
+            pool = build_streams(self.device, n_compress=max(1, compression_streams),
+                                 use_greenctx=greenctx_enabled, compress_ratio=greenctx_compress_ratio,
+                                 main_on_greenctx=greenctx_main_stream)
+            self.main_stream = pool.main
+            self.compress_streams = pool.compress
+            self.greenctx_enabled = pool.greenctx
+            self._greenctx_info = pool.info
+            self._stream_pool = pool
+
+        # ------------------------------------------------------------ graphs
+        self.graphs: Dict[int, Any] = {}
+        self.graph_bs: List[int] = []
+        self.graph_vars: Dict[str, torch.Tensor] = {}
+        self.graph_pool = None
+        if not self.enforce_eager:
+            self.capture_cudagraph()
+
+    # ------------------------------------------------------------------ setup
+    def _load_weights(self) -> None:
+        cfg = self.config
+        random_init = bool(cfg.extra.get("random_init", False)) or not cfg.model
+        if random_init:
+            shapes = self.model.hf_weight_shapes(self.hf_config)
+            init_random_weights(self.model, shapes, seed=cfg.seed, std=float(cfg.extra.get("init_std", 0.02)),
+                                device=str(self.device) if self.device.type == "cuda" else "cpu")
+        else:
+            load_model(self.model, cfg.model)
+
+    def _load_compressor(self, path: Optional[str], module: Any) -> None:
+        if self.compression_backend != "mlp":
+            return
+        try:
+            if module is None:
+                if path is None:
+                    raise FileNotFoundError("compression_backend='mlp' needs compressor_path or a module")
+                module = load_compressor(path, None, min_seq_len=self.min_seq_len,
+                                         nhead=self.total_kv_heads)
+            if module.n_layer != self.num_hidden_layers or module.head_dim != self.head_dim:
+                raise ValueError(f"compressor is for {module.n_layer} layers x head_dim {module.head_dim}; "
+                                 f"model has {self.num_hidden_layers} x {self.head_dim}")
+            self.compressor = module
+            self.compression_factor = module.compression_factor
+            self.packed_compressor = module.pack(self.dtype, self.device)
+        except Exception as exc:
+            # same recovery as the reference: a compressor that cannot be loaded
+            # turns compression off instead of failing the engine
+            # ("kv-cache pipeline"/nanovllm/engine/llava_model_runner.py:555-565)
+            print(f"[fastcache_b200] compressor unavailable ({exc}); compression disabled")
+            self.compressor = None
+            self.packed_compressor = None
+
+    def allocate_kv_cache(self) -> None:
+        cfg = self.config
+        L, H, D, bs = self.num_hidden_layers, self.num_key_value_heads, self.head_dim, self.block_size
+        block_bytes = 2 * L * bs * H * D * torch.empty((), dtype=self.dtype).element_size()
+        if cfg.num_kvcache_blocks <= 0:
+            if self.device.type == "cuda":
+                total, used, free = get_gpu_memory(self.device.index)
+                budget = int(total * cfg.gpu_memory_utilization) - used
+                cfg.num_kvcache_blocks = max(1, budget // block_bytes)
+            else:
+                need = cfg.max_num_seqs * -(-cfg.max_model_len // bs)
+                cfg.num_kvcache_blocks = max(1, min(need, (1 << 30) // block_bytes))
+        self.num_blocks = cfg.num_kvcache_blocks
+        self.kv_cache = torch.zeros(L, 2, self.num_blocks, bs, H, D, dtype=self.dtype, device=self.device)
+        i = 0
+        for module in self.model.modules():
+            if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
+                module.k_cache = self.kv_cache[i, 0]
+                module.v_cache = self.kv_cache[i, 1]
+                i += 1
+        if i != L:
+            raise RuntimeError(f"bound {i} attention layers, expected {L}")
+
+    # --------------------------------------------------------------- metadata
+    def _to_dev(self, arr: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+        t = torch.from_numpy(arr).to(dtype)
+        if self.device.type == "cuda":
+            return t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    def _block_table_array(self, seqs: Seq[Sequence], width: Optional[int] = None) -> np.ndarray:
+        width = width or max(len(s.block_table) for s in seqs)
+        bt = np.full((len(seqs), width), -1, dtype=np.int32)
+        for i, s in enumerate(seqs):
+            bt[i, : len(s.block_table)] = s.block_table
+        return bt
+
+    def prepare_prefill(self, seqs: Seq[Sequence]):
+        bs = self.block_size
+        ids: List[np.ndarray] = []
+        pos: List[np.ndarray] = []
+        slots: List[np.ndarray] = []
+        cu_q = [0]
+        kv_lens = []
+        image_rows: List[Tuple[int, int, int]] = []      # (seq index, first flat row, count)
+        max_q = max_k = 0
+        for si, s in enumerate(seqs):
+            toks = np.asarray(s.token_ids, dtype=np.int64)
+            if s.has_image:
+                p = s.image_token_pos
+                toks = np.concatenate([toks[:p], np.full(s.num_image_tokens, toks[p], dtype=np.int64),
+                                       toks[p + 1:]])
+            n = toks.shape[0]
+            start = s.num_cached_tokens
+            rows = np.arange(start, n, dtype=np.int64)
+            if s.has_image:
+                image_rows.append((si, cu_q[-1] + s.image_token_pos - start, s.num_image_tokens))
+            ids.append(toks[start:])
+            pos.append(rows)
+            table = np.asarray(s.block_table, dtype=np.int64)
+            slots.append(table[rows // bs] * bs + rows % bs)
+            cu_q.append(cu_q[-1] + n - start)
+            kv_lens.append(n)
+            max_q = max(max_q, n - start)
+            max_k = max(max_k, n)
+        input_ids = self._to_dev(np.concatenate(ids), torch.int64)
+        positions = self._to_dev(np.concatenate(pos), torch.int64)
+        slot_mapping = self._to_dev(np.concatenate(slots), torch.int32)
+        cu = self._to_dev(np.asarray(cu_q, dtype=np.int32), torch.int32)
+        kvl = self._to_dev(np.asarray(kv_lens, dtype=np.int32), torch.int32)
+        block_tables = self._to_dev(self._block_table_array(seqs), torch.int32)
+        window = None
+        if self.obs_window > 0:
+            idx = []
+            for i in range(len(seqs)):
+                q_len = cu_q[i + 1] - cu_q[i]
+                w = min(self.obs_window, q_len)
+                idx.append(np.arange(cu_q[i + 1] - w, cu_q[i + 1], dtype=np.int64))
+            window = {"indices": self._to_dev(np.concatenate(idx), torch.int64), "q": {},
+                      "counts": [len(x) for x in idx]}
+        set_context(True, cu, cu, max_q, max_k, slot_mapping, kvl, block_tables, window_q=window,
+                    obs_window=self.obs_window)
+        return input_ids, positions, image_rows
+
+    def prepare_decode(self, seqs: Seq[Sequence]):
+        bs = self.block_size
+        n = len(seqs)
+        ids = np.empty(n, dtype=np.int64)
+        pos = np.empty(n, dtype=np.int64)
+        slots = np.empty(n, dtype=np.int32)
+        lens = np.empty(n, dtype=np.int32)
+        mode = self.config.position_mode
+        for i, s in enumerate(seqs):
+            ids[i] = s.last_token
+            pos[i] = s.next_position(mode)
+            kv = s.kv_cache_len
+            lens[i] = kv
+            slots[i] = s.block_table[(kv - 1) // bs] * bs + (kv - 1) % bs
+        return ids, pos, slots, lens, self._block_table_array(seqs)
+
+    # ------------------------------------------------------------------ forward
+    def _forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
+                 seqs: Optional[Seq[Sequence]] = None, image_rows=None) -> torch.Tensor:
+        if self.is_multimodal:
+            pixel = None
+            if image_rows:
+                pixel = [(seqs[si].pixel_values, seqs[si].image_meta, row, cnt) for si, row, cnt in image_rows]
+            hidden = self.model(input_ids, positions, images=pixel)
+        else:
+            hidden = self.model(input_ids, positions)
+        return self.model.compute_logits(hidden)
+
+    @torch.inference_mode()
+    def run_prefill(self, seqs: Seq[Sequence]) -> torch.Tensor:
+        input_ids, positions, image_rows = self.prepare_prefill(seqs)
+        from ..utils.context import get_context
+        ctx = get_context()
+        logits = self._forward(input_ids, positions, seqs, image_rows)
+        if ctx.window_q is not None:
+            counts = ctx.window_q["counts"]
+            offs = np.concatenate([[0], np.cumsum(counts)])
+            for i, s in enumerate(seqs):
+                self._window_q[s.seq_id] = {l: q[offs[i]:offs[i + 1]] for l, q in ctx.window_q["q"].items()}
+        return logits
+
+    def _graph_bucket(self, n: int) -> Optional[int]:
+        for b in self.graph_bs:
+            if b >= n:
+                return b
+        return None
+
+    @torch.inference_mode()
+    def run_decode(self, seqs: Seq[Sequence]) -> torch.Tensor:
+        ids, pos, slots, lens, bt = self.prepare_decode(seqs)
+        n = len(seqs)
+        bucket = None if self.enforce_eager else self._graph_bucket(n)
+        if bucket is None or bt.shape[1] > self.graph_vars["block_tables"].shape[1]:
+            set_context(False, slot_mapping=self._to_dev(slots, torch.int32),
+                        context_lens=self._to_dev(lens, torch.int32),
+                        block_tables=self._to_dev(bt, torch.int32),
+                        attn_workspace=getattr(self, "attn_workspace", None))
+            return self._forward(self._to_dev(ids, torch.int64), self._to_dev(pos, torch.int64))
+        gv = self.graph_vars
+        h = self._staging
+        h["input_ids"][:n] = torch.from_numpy(ids)
+        h["input_ids"][n:bucket] = 0
+        h["positions"][:n] = torch.from_numpy(pos)
+        h["positions"][n:bucket] = 0
+        h["slot_mapping"][:n] = torch.from_numpy(slots)
+        h["slot_mapping"][n:bucket] = -1
+        h["context_lens"][:n] = torch.from_numpy(lens)
+        h["context_lens"][n:bucket] = 0
+        h["block_tables"][:bucket].fill_(0)
+        h["block_tables"][:n, : bt.shape[1]] = torch.from_numpy(np.maximum(bt, 0))
+        for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
+            gv[k][:bucket].copy_(h[k][:bucket], non_blocking=True)
+        gv["block_tables"][:bucket].copy_(h["block_tables"][:bucket], non_blocking=True)
+        self._replay(bucket)
+        return gv["logits"][:n]
+
+    def _replay(self, bucket: int) -> None:
+        g = self.graphs[bucket]
+        if g is None:                       # CPU: same static buffers, eager execution
+            self._decode_on_static(bucket)
+        else:
+            g.replay()
+
+    def _decode_on_static(self, bucket: int) -> None:
+        gv = self.graph_vars
+        set_context(False, slot_mapping=gv["slot_mapping"][:bucket], context_lens=gv["context_lens"][:bucket],
+                    block_tables=gv["block_tables"][:bucket],
+                    attn_workspace=getattr(self, "attn_workspace", None))
+        gv["logits"][:bucket] = self._forward(gv["input_ids"][:bucket], gv["positions"][:bucket])
+
+    @torch.inference_mode()
+    def capture_cudagraph(self) -> None:
+        cfg = self.config
+        max_bs = min(cfg.max_num_seqs, cfg.decode_batch_size or cfg.max_num_seqs, 512)
+        max_blocks = -(-cfg.max_model_len // self.block_size) + 1
+        dev = self.device
+        vocab = self.text_config.vocab_size
+        self.graph_vars = {
+            "input_ids": torch.zeros(max_bs, dtype=torch.int64, device=dev),
+            "positions": torch.zeros(max_bs, dtype=torch.int64, device=dev),
+            "slot_mapping": torch.full((max_bs,), -1, dtype=torch.int32, device=dev),
+            "context_lens": torch.zeros(max_bs, dtype=torch.int32, device=dev),
+            "block_tables": torch.zeros(max_bs, max_blocks, dtype=torch.int32, device=dev),
+            "logits": torch.zeros(max_bs, vocab, dtype=self.dtype, device=dev),
+        }
+        pin = dev.type == "cuda"
+        self._staging = {k: torch.zeros(v.shape, dtype=v.dtype, pin_memory=pin)
+                         for k, v in self.graph_vars.items() if k != "logits"}
+        buckets = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
+        if max_bs not in buckets:
+            buckets.append(max_bs)
+        self.graph_bs = sorted(set(buckets))
+        if dev.type != "cuda":
+            self.graphs = {b: None for b in self.graph_bs}
+            return
+        stream = self.main_stream or torch.cuda.current_stream()
+        with torch.cuda.stream(stream):
+            for b in reversed(self.graph_bs):
+                self._decode_on_static(b)            # warm-up (allocations, lazy init)
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self.graph_pool, stream=stream):
+                    self._decode_on_static(b)
+                if self.graph_pool is None:
+                    self.graph_pool = g.pool()
+                self.graphs[b] = g
+        stream.synchronize()
+        reset_context()
+
+    # --------------------------------------------------------------------- run
+    def _temperatures(self, seqs: Seq[Sequence]) -> torch.Tensor:
+        return self._to_dev(np.asarray([s.temperature for s in seqs], dtype=np.float32), torch.float32)
+
+    def run(self, seqs: Seq[Sequence], is_prefill: bool, **_ignored) -> List[int]:
+        """One model step for a batch; returns the sampled token per request."""
+        cm = torch.cuda.stream(self.main_stream) if self.main_stream is not None else _Null()
+        with cm:
+            logits = self.run_prefill(seqs) if is_prefill else self.run_decode(seqs)
+            tokens = self.sampler(logits, self._temperatures(seqs))
+            out = tokens.tolist()
+        reset_context()
+        return out
+
+    # ------------------------------------------------------------- compression
+    def compressed_len_for(self, seq: Sequence) -> int:
+        n = seq.kv_cache_len
+        if self.compression_backend == "mlp":
+            img = self._image_rows_of(seq)
+            if self.packed_compressor.single_segment:
+                img = 0
+            from ..compress.ccm import ccm_output_len
+            return ccm_output_len(n, img, self.compression_factor, self.min_seq_len)
+        return n_kept_for(n, ratio_from_factor(self.compression_factor))
+
+    @staticmethod
+    def _image_rows_of(seq: Sequence) -> int:
+        return seq.image_token_pos + seq.num_image_tokens if seq.has_image else 0
+
+    @torch.inference_mode()
+    def compress_kv_cache_batch(self, seqs: Seq[Sequence], layer_start: int = 0,
+                                layer_end: Optional[int] = None, stream: Any = None) -> List[int]:
+        """Compress the pool rows of `seqs` in place; returns the new row counts.
+
+        Does not touch scheduler state: the engine updates `seq.kv_cache_len`
+        and frees the tail blocks once the work is ordered before their reuse.
+        """
+        if not seqs:
+            return []
+        tables = [s.block_table for s in seqs]
+        lens = [s.kv_cache_len for s in seqs]
+        cm = torch.cuda.stream(stream) if stream is not None else _Null()
+        with cm:
+            if self.compression_backend == "mlp":
+                if self.packed_compressor is None:
+                    raise RuntimeError("no compressor loaded")
+                imgs = [self._image_rows_of(s) for s in seqs]
+                new = ccm_compress_in_pool(self.kv_cache, tables, lens, imgs, self.packed_compressor,
+                                           layer_start, layer_end)
+            else:
+                ratio = ratio_from_factor(self.compression_factor)
+                kept = [n_kept_for(n, ratio) for n in lens]
+                wq = None
+                if self.kvpress_method in NEEDS_QUERIES:
+                    wq = [self._window_q.get(s.seq_id) for s in seqs]
+                new = evict_in_pool(self.kv_cache, tables, lens, self.kvpress_method, kept, wq,
+                                    self.kvpress_params)
+        full = (layer_start == 0 and (layer_end is None or layer_end >= self.num_hidden_layers))
+        for s, n in zip(seqs, new):
+            if full or (layer_end is not None and layer_end >= self.num_hidden_layers):
+                self._compressed_lens[s.seq_id] = n
+                self._window_q.pop(s.seq_id, None)
+        return new
+
+    def get_compressed_block_count(self, seq_id: int) -> int:
+        n = self._compressed_lens.get(seq_id)
+        return 0 if n is None else -(-n // self.block_size)
+
+    def copy_block(self, src: int, dst: int) -> None:
+        self.kv_cache[:, :, dst].copy_(self.kv_cache[:, :, src])
+
+    def release(self, seq: Sequence) -> None:
+        self._compressed_lens.pop(seq.seq_id, None)
+        self._window_q.pop(seq.seq_id, None)
+
+    def next_compress_stream(self):
+        if not self.compress_streams:
+            return None
+        s = self.compress_streams[self._rr % len(self.compress_streams)]
+        self._rr += 1
+        return s
+
+    def update_streams(self, use_greenctx: bool, sm_compress_ratio: float, sm_main_ratio: float = 0.0,
+                       num_streams: Optional[int] = None) -> None:
+        """Rebuild the compression streams for a new SM split (controller decision)."""
+        if self.device.type != "cuda":
+            return
+        from ..utils.streams import build_streams
+        info = self._greenctx_info
+        same = (use_greenctx == self.greenctx_enabled and
+                abs(info.get("compress_ratio", -1.0) - sm_compress_ratio) < 1e-3 and
+                (num_streams is None or num_streams == len(self.compress_streams)))
+        if same:
+            return
+        torch.cuda.synchronize(self.device)
+        pool = build_streams(self.device, n_compress=num_streams or max(1, len(self.compress_streams)),
+                             use_greenctx=use_greenctx, compress_ratio=sm_compress_ratio,
+                             main_on_greenctx=False, reuse_main=self.main_stream)
+        self.compress_streams = pool.compress
+        self.greenctx_enabled = pool.greenctx
+        self._greenctx_info = pool.info
+        self._stream_pool = pool
+
+    def exit(self) -> None:
+        self.graphs.clear()
+        self.graph_pool = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+# name used by the reference's multimodal engine
+LlavaModelRunner = ModelRunner

@@ -1,0 +1,194 @@
+"""Three-queue scheduler: prefill, compress, decode.
+
+Parity
+  * text scheduler with prefill-first batching, token / sequence caps,
+    decode-time preemption and the `prefer_decode` flip used for dual-batch
+    alternation: "kv-cache pipeline"/nanovllm/engine/scheduler.py:9-95
+  * multimodal rule (an image request is prefetched alone):
+    "kv-cache pipeline"/nanovllm/engine/llava_scheduler.py:65-86 — kept as an
+    option (`one_image_per_prefill`), off by default because this build's
+    vision tower takes a batch of images
+  * per-stage batch caps [prefill, compress, decode] of the HF harness
+    (scripts/llava_testcon2.6.py:2095-2100, configs/experiments.yaml:38)
+  * lazy trigger "compress every uncompressed running request when the pool is
+    nearly full" (nanovllm_fastapi_server.py:98-145)
+
+The compress queue is explicit here: a request that finished prefill and is
+eligible for compression is parked in `compress_queue` until the engine asks
+for a compression batch (`schedule_compress`).  It can decode meanwhile — the
+runner orders the pool accesses — so the queue is a work list, not a state
+that blocks the request.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Callable, Deque, List, Optional, Tuple
+
+from ..config import Config
+from .block_manager import BlockManager
+from .sequence import CompressionState, Sequence, SequenceStatus
+
+
+class Scheduler:
+    def __init__(self, config: Config):
+        self.max_num_seqs = config.max_num_seqs
+        self.max_num_batched_tokens = config.max_num_batched_tokens
+        self.eos = config.eos
+        self.prefill_cap = config.prefill_batch_size or config.max_num_seqs
+        self.compress_cap = config.compress_batch_size or config.max_num_seqs
+        self.decode_cap = config.decode_batch_size or config.max_num_seqs
+        self.lazy_threshold = config.lazy_occupancy_threshold
+        self.one_image_per_prefill = bool(config.extra.get("one_image_per_prefill", False))
+        self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size,
+                                          prefix_caching=config.prefix_caching)
+        self.waiting: Deque[Sequence] = deque()
+        self.running: Deque[Sequence] = deque()
+        self.compress_queue: Deque[Sequence] = deque()
+        self.num_preemptions = 0
+        # called with a sequence that loses its blocks (lets the runner drop
+        # per-request device state)
+        self.on_release: Optional[Callable[[Sequence], None]] = None
+
+    # ------------------------------------------------------------------ queues
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def add(self, seq: Sequence) -> None:
+        self.waiting.append(seq)
+
+    # ----------------------------------------------------------------- prefill
+    def _schedule_prefill(self) -> List[Sequence]:
+        picked: List[Sequence] = []
+        tokens = 0
+        while self.waiting and len(picked) < self.prefill_cap \
+                and len(self.running) + len(picked) < self.max_num_seqs:
+            seq = self.waiting[0]
+            if self.one_image_per_prefill and seq.has_image and picked:
+                break
+            cost = seq.prompt_rows + seq.num_completion_tokens - seq.num_cached_tokens
+            if tokens + cost > self.max_num_batched_tokens and picked:
+                break
+            if tokens + cost > self.max_num_batched_tokens or not self.block_manager.can_allocate(seq):
+                break
+            self.block_manager.allocate(seq)
+            tokens += seq.logical_len - seq.num_cached_tokens
+            seq.status = SequenceStatus.RUNNING
+            self.waiting.popleft()
+            picked.append(seq)
+            if self.one_image_per_prefill and seq.has_image:
+                break
+        self.running.extend(picked)
+        return picked
+
+    # ------------------------------------------------------------------ decode
+    def _schedule_decode(self) -> List[Sequence]:
+        picked: List[Sequence] = []
+        skipped: List[Sequence] = []
+        while self.running and len(picked) < self.decode_cap:
+            seq = self.running.popleft()
+            if seq.hold:
+                skipped.append(seq)
+                continue
+            while not self.block_manager.can_append(seq):
+                if self.running:
+                    self.preempt(self.running.pop())
+                else:
+                    self.preempt(seq)
+                    break
+            else:
+                self.block_manager.may_append(seq)
+                picked.append(seq)
+        # keep arrival order: visited requests go back to the front
+        visited = sorted(picked + skipped, key=lambda s: s.seq_id)
+        self.running.extendleft(reversed(visited))
+        return picked
+
+    def schedule(self, prefer_decode: bool = False) -> Tuple[List[Sequence], bool]:
+        """Pick the next batch.  Returns (sequences, is_prefill)."""
+        if prefer_decode and self.running:
+            seqs = self._schedule_decode()
+            if seqs:
+                return seqs, False
+        seqs = self._schedule_prefill()
+        if seqs:
+            return seqs, True
+        seqs = self._schedule_decode()
+        if not seqs and (self.waiting or self.running) and not any(s.hold for s in self.running):
+            head = self.waiting[0] if self.waiting else self.running[0]
+            raise RuntimeError(
+                f"request {head.seq_id} needs {head.num_blocks} blocks but the pool has "
+                f"{self.block_manager.num_blocks}; raise num_kvcache_blocks or shorten the request")
+        return seqs, False
+
+    def preempt(self, seq: Sequence) -> None:
+        """Take a running request's blocks away; it is prefetched again later."""
+        self.num_preemptions += 1
+        seq.status = SequenceStatus.WAITING
+        self.block_manager.deallocate(seq)
+        if self.on_release is not None:
+            self.on_release(seq)
+        seq.reset_for_recompute()
+        try:
+            self.compress_queue.remove(seq)
+        except ValueError:
+            pass
+        self.waiting.appendleft(seq)
+
+    # ---------------------------------------------------------------- compress
+    def enqueue_compress(self, seqs: List[Sequence]) -> None:
+        for seq in seqs:
+            if seq.compression_state is CompressionState.NONE and not seq.is_finished:
+                seq.compression_state = CompressionState.PENDING
+                self.compress_queue.append(seq)
+
+    def schedule_compress(self, limit: Optional[int] = None) -> List[Sequence]:
+        cap = self.compress_cap if limit is None else min(limit, self.compress_cap)
+        picked: List[Sequence] = []
+        while self.compress_queue and len(picked) < cap:
+            seq = self.compress_queue.popleft()
+            if seq.is_finished or seq.compression_state is not CompressionState.PENDING:
+                continue
+            picked.append(seq)
+        return picked
+
+    def lazy_compress_due(self) -> bool:
+        return self.block_manager.occupancy > self.lazy_threshold
+
+    def lazy_candidates(self) -> List[Sequence]:
+        """Uncompressed running requests, largest KV first."""
+        cands = [s for s in self.running
+                 if s.compression_state is CompressionState.NONE and not s.is_finished]
+        cands.sort(key=lambda s: -s.kv_cache_len)
+        return cands
+
+    # ------------------------------------------------------------- postprocess
+    def postprocess(self, seqs: List[Sequence], token_ids: List[int]) -> List[Sequence]:
+        """Append sampled tokens; retire finished requests.  Returns the finished ones."""
+        done: List[Sequence] = []
+        for seq, token_id in zip(seqs, token_ids):
+            seq.append_token(int(token_id))
+            hit_eos = (not seq.ignore_eos) and token_id == self.eos
+            if hit_eos or seq.num_completion_tokens >= seq.max_tokens:
+                self.finish(seq)
+                done.append(seq)
+        return done
+
+    def finish(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.FINISHED
+        self.block_manager.deallocate(seq)
+        if self.on_release is not None:
+            self.on_release(seq)
+        try:
+            self.running.remove(seq)
+        except ValueError:
+            pass
+        try:
+            self.compress_queue.remove(seq)
+        except ValueError:
+            pass
+
+
+# the reference exposes a second class for multimodal requests
+class LlavaScheduler(Scheduler):
+    def __init__(self, config: Config):
+        super().__init__(config)

@@ -1,0 +1,104 @@
+"""Op entry points.
+
+Each function runs the hand-written sm_100a kernel when its tensors live on a
+CUDA device and the PyTorch statement in `reference.py` otherwise.  There is
+no backend registry: the device of the data decides, and a CUDA tensor without
+the compiled extension is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+from .loader import ext, ext_available  # noqa: F401
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def rms_norm(x, weight, eps):
+    if _cuda(x):
+        return ext().rms_norm(x, weight, float(eps))
+    return ref.rms_norm(x, weight, eps)
+
+
+def add_rms_norm(x, residual, weight, eps) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns (normed, new_residual).  On CUDA `residual` is updated in place."""
+    if _cuda(x):
+        y = ext().add_rms_norm(x, residual, weight, float(eps))
+        return y, residual
+    return ref.add_rms_norm(x, residual, weight, eps)
+
+
+def layer_norm(x, weight, bias, eps):
+    if _cuda(x):
+        return ext().layer_norm(x, weight, bias, float(eps))
+    return ref.layer_norm(x, weight, bias, eps)
+
+
+def silu_and_mul(x):
+    if _cuda(x):
+        return ext().silu_and_mul(x)
+    return ref.silu_and_mul(x)
+
+
+def linear(x, weight, bias=None, act: str = "none", out: Optional[torch.Tensor] = None):
+    """y = act(x @ weight.T + bias).  weight is [N, K] as in nn.Linear.
+
+    act "swiglu" expects weight rows interleaved per 64-column group by
+    `interleave_gate_up` and returns N/2 columns.
+    """
+    if _cuda(x):
+        from .gemm import gemm
+        return gemm(x, weight, bias, act, out)
+    y = ref.linear(x, weight, bias, act)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                      q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping):
+    if _cuda(qkv):
+        return ext().rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                                       q_norm_weight, k_norm_weight, float(eps), k_cache, v_cache,
+                                       slot_mapping)
+    return ref.rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                                 q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping)
+
+
+def prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
+                      max_q_len: int = 0):
+    if _cuda(q):
+        return ext().prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens,
+                                       float(scale), int(max_q_len))
+    return ref.prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale)
+
+
+def decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale, workspace=None):
+    if _cuda(q):
+        from .attention import decode_attention as _dec
+        return _dec(q, k_cache, v_cache, block_tables, context_lens, scale, workspace)
+    return ref.decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
+
+
+def dense_attention(q, k, v, scale, key_mask=None):
+    if _cuda(q):
+        return ext().dense_attention(q, k, v, float(scale), key_mask)
+    return ref.dense_attention(q, k, v, scale, key_mask)
+
+
+def embedding(ids, weight, vocab_start: int = 0):
+    if _cuda(weight):
+        return ext().embedding(ids, weight, int(vocab_start))
+    return ref.embedding(ids, weight, vocab_start)
+
+
+def sample(logits, temperatures, noise=None, seed: int = 0):
+    if _cuda(logits) and noise is None:
+        return ext().sample(logits, temperatures, int(seed))
+    return ref.sample(logits, temperatures, noise)
