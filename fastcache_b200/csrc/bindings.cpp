@@ -1,0 +1,296 @@
+// Python bindings (torch extension `fastcache_b200._C`).  Tensors are checked here
+// (device, dtype, contiguity, alignment) so the kernels can assume their layout.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm.h"
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+struct DeviceWorkspace {
+  Tensor gemm_scratch, gemm_counters, status, attn_o, attn_lse;
+};
+std::unordered_map<int, DeviceWorkspace> g_ws;
+std::unordered_map<uint64_t, int> g_stream_sms;
+std::mutex g_mu;
+
+constexpr int64_t ATTN_WS_FLOATS = 4 << 20;   // 16 MiB of split-KV partial outputs
+constexpr int64_t ATTN_LSE_FLOATS = 1 << 18;
+
+DeviceWorkspace& workspace(int dev) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_ws.find(dev);
+  if (it != g_ws.end()) return it->second;
+  auto f32 = torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, dev);
+  auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, dev);
+  DeviceWorkspace w;
+  w.gemm_scratch = torch::empty({int64_t(fc::gemm_scratch_bytes() / 4)}, f32);
+  w.gemm_counters = torch::zeros({int64_t(fc::gemm_counter_bytes() / 4)}, i32);
+  w.status = torch::zeros({4}, i32);
+  w.attn_o = torch::empty({ATTN_WS_FLOATS}, f32);
+  w.attn_lse = torch::empty({ATTN_LSE_FLOATS}, f32);
+  return g_ws.emplace(dev, std::move(w)).first->second;
+}
+
+uint32_t* status_ptr(int dev) { return reinterpret_cast<uint32_t*>(workspace(dev).status.data_ptr<int>()); }
+
+void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bf16 (got ", t.scalar_type(), ")");
+}
+
+int sm_limit_for(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_stream_sms.find(reinterpret_cast<uint64_t>(s));
+  return it == g_stream_sms.end() ? 0 : it->second;
+}
+
+// y = act(x @ w.T + bias)
+Tensor gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t act,
+            const c10::optional<Tensor>& out_opt) {
+  check_bf16(x, "x");
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2, "gemm expects 2-D operands");
+  TORCH_CHECK(x.size(1) == w.size(1), "inner dimensions differ: ", x.size(1), " vs ", w.size(1));
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1, "operands must be row-major (unit inner stride)");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(K % 8 == 0, "K must be a multiple of 8 (16-byte rows for TMA)");
+  TORCH_CHECK(x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "row pitches must be multiples of 8 elements");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = out_opt.has_value() ? *out_opt : torch::empty({M, N}, x.options());
+  check_bf16(out, "out");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "bad out tensor");
+  const void* bptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be a contiguous [N] vector");
+    bptr = bias->data_ptr();
+  }
+  if (M == 0) return out;
+  auto& ws = workspace(x.get_device());
+  fc::GemmWorkspace gw;
+  gw.scratch = ws.gemm_scratch.data_ptr<float>();
+  gw.counters = ws.gemm_counters.data_ptr<int>();
+  gw.status = reinterpret_cast<uint32_t*>(ws.status.data_ptr<int>());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  fc::gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, int(M), int(N), int(K), x.stride(0), w.stride(0),
+                out.stride(0), int(act), gw, sm_limit_for(stream), stream);
+  return out;
+}
+
+Tensor rms_norm(const Tensor& x, const Tensor& w, double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "rms_norm expects contiguous tensors");
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && H <= 8192 && w.numel() == H, "hidden size must be a multiple of 8 and <= 8192");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  fc::launch_rms_norm(x.data_ptr(), nullptr, w.data_ptr(), y.data_ptr(), x.numel() / H, int(H), float(eps),
+                      at::cuda::getCurrentCUDAStream());
+  return y;
+}
+
+Tensor add_rms_norm(const Tensor& x, Tensor& residual, const Tensor& w, double eps) {
+  check_bf16(x, "x");
+  check_bf16(residual, "residual");
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.is_contiguous() && residual.is_contiguous() && w.is_contiguous(), "expects contiguous tensors");
+  TORCH_CHECK(x.sizes() == residual.sizes(), "x and residual differ in shape");
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && H <= 8192 && w.numel() == H, "hidden size must be a multiple of 8 and <= 8192");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  fc::launch_rms_norm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), y.data_ptr(), x.numel() / H, int(H),
+                      float(eps), at::cuda::getCurrentCUDAStream());
+  return y;
+}
+
+Tensor layer_norm(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "weight");
+  check_bf16(b, "bias");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous() && b.is_contiguous(), "expects contiguous tensors");
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && H <= 8192 && w.numel() == H && b.numel() == H, "bad hidden size");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  fc::launch_layer_norm(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), x.numel() / H, int(H), float(eps),
+                        at::cuda::getCurrentCUDAStream());
+  return y;
+}
+
+Tensor silu_and_mul(const Tensor& x) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && x.size(-1) % 16 == 0, "expects contiguous input with last dim % 16 == 0");
+  const int64_t I = x.size(-1) / 2;
+  auto sizes = x.sizes().vec();
+  sizes.back() = I;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty(sizes, x.options());
+  fc::launch_silu_and_mul(x.data_ptr(), y.data_ptr(), x.numel() / (2 * I), int(I), at::cuda::getCurrentCUDAStream());
+  return y;
+}
+
+Tensor embedding(const Tensor& ids, const Tensor& weight, int64_t vocab_start) {
+  check_bf16(weight, "weight");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids must be int64 CUDA");
+  TORCH_CHECK(weight.is_contiguous() && weight.size(1) % 8 == 0, "bad embedding table");
+  c10::cuda::CUDAGuard guard(weight.device());
+  Tensor out = torch::empty({ids.numel(), weight.size(1)}, weight.options());
+  fc::launch_embedding(ids.data_ptr(), weight.data_ptr(), out.data_ptr(), int(ids.numel()), int(weight.size(1)),
+                       int(weight.size(0)), int(vocab_start), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+Tensor rope_qknorm_store(const Tensor& qkv, const Tensor& positions, const Tensor& cos_sin, int64_t Hq, int64_t Hkv,
+                         int64_t D, const c10::optional<Tensor>& q_w, const c10::optional<Tensor>& k_w, double eps,
+                         const c10::optional<Tensor>& k_cache, const c10::optional<Tensor>& v_cache,
+                         const c10::optional<Tensor>& slots) {
+  check_bf16(qkv, "qkv");
+  TORCH_CHECK(qkv.is_contiguous() && qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D, "bad qkv shape");
+  TORCH_CHECK(positions.scalar_type() == torch::kInt64 && positions.is_contiguous() && positions.is_cuda(),
+              "positions must be int64 CUDA");
+  TORCH_CHECK(cos_sin.scalar_type() == torch::kFloat32 && cos_sin.is_contiguous() && cos_sin.size(1) == D &&
+                  cos_sin.is_cuda(), "cos_sin must be fp32 [max_pos, D] on the device");
+  TORCH_CHECK(D % 8 == 0 && D <= 256, "head_dim must be a multiple of 8 and <= 256");
+  const int64_t T = qkv.size(0);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor q_out = torch::empty({T, Hq, D}, qkv.options());
+  const void *qw = nullptr, *kw = nullptr, *sl = nullptr;
+  void *kc = nullptr, *vc = nullptr;
+  int64_t num_slots = 0;
+  if (q_w.has_value() && q_w->defined()) { check_bf16(*q_w, "q_norm"); qw = q_w->data_ptr(); }
+  if (k_w.has_value() && k_w->defined()) { check_bf16(*k_w, "k_norm"); kw = k_w->data_ptr(); }
+  if (k_cache.has_value() && k_cache->defined() && slots.has_value() && slots->defined()) {
+    check_bf16(*k_cache, "k_cache");
+    check_bf16(*v_cache, "v_cache");
+    TORCH_CHECK(k_cache->is_contiguous() && v_cache->is_contiguous(), "cache slices must be contiguous");
+    TORCH_CHECK(k_cache->size(-1) == D && k_cache->size(-2) == Hkv, "cache layout must be [blocks, block, Hkv, D]");
+    TORCH_CHECK(slots->scalar_type() == torch::kInt32 && slots->numel() == T && slots->is_cuda(),
+                "slot_mapping must be int32 [T]");
+    kc = k_cache->data_ptr();
+    vc = v_cache->data_ptr();
+    sl = slots->data_ptr();
+    num_slots = k_cache->size(0) * k_cache->size(1);
+  }
+  fc::launch_rope_qknorm_store(qkv.data_ptr(), positions.data_ptr(), cos_sin.data_ptr(), qw, kw, q_out.data_ptr(),
+                               kc, vc, sl, int(T), int(Hq), int(Hkv), int(D), float(eps), num_slots,
+                               status_ptr(qkv.get_device()), at::cuda::getCurrentCUDAStream());
+  return q_out;
+}
+
+void check_cache(const Tensor& kc, const Tensor& vc, int64_t D) {
+  check_bf16(kc, "k_cache");
+  check_bf16(vc, "v_cache");
+  TORCH_CHECK(kc.dim() == 4 && kc.is_contiguous() && vc.is_contiguous() && kc.size(3) == D,
+              "cache layout must be contiguous [blocks, block, Hkv, D]");
+}
+
+Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_tables,
+                         const Tensor& cu_q, const Tensor& kv_lens, double scale, int64_t max_q_len) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous(), "q must be contiguous [T, Hq, D]");
+  const int64_t Hq = q.size(1), D = q.size(2);
+  check_cache(kc, vc, D);
+  TORCH_CHECK(block_tables.scalar_type() == torch::kInt32 && block_tables.dim() == 2 && block_tables.is_contiguous(),
+              "block_tables must be int32 [B, max_blocks]");
+  TORCH_CHECK(cu_q.scalar_type() == torch::kInt32 && kv_lens.scalar_type() == torch::kInt32, "lengths must be int32");
+  const int64_t B = kv_lens.numel();
+  TORCH_CHECK(cu_q.numel() == B + 1 && block_tables.size(0) >= B, "inconsistent batch metadata");
+  if (max_q_len <= 0) max_q_len = q.size(0);
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty_like(q);
+  fc::launch_prefill_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
+                               cu_q.data_ptr<int>(), kv_lens.data_ptr<int>(), out.data_ptr(), int(B), int(max_q_len),
+                               int(Hq), int(kc.size(2)), int(D), int(kc.size(1)), int(block_tables.size(1)),
+                               int(kc.size(0)), float(scale), status_ptr(q.get_device()),
+                               at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+// splits <= 0: choose from the batch shape and `max_ctx`
+Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_tables,
+                        const Tensor& context_lens, double scale, int64_t splits, int64_t max_ctx) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous(), "q must be contiguous [B, Hq, D]");
+  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2);
+  check_cache(kc, vc, D);
+  const int64_t Hkv = kc.size(2);
+  TORCH_CHECK(block_tables.scalar_type() == torch::kInt32 && block_tables.dim() == 2 && block_tables.is_contiguous() &&
+                  block_tables.size(0) >= B, "block_tables must be int32 [B, max_blocks]");
+  TORCH_CHECK(context_lens.scalar_type() == torch::kInt32 && context_lens.numel() >= B, "context_lens must be int32 [B]");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto& ws = workspace(q.get_device());
+  if (max_ctx <= 0) max_ctx = block_tables.size(1) * kc.size(1);
+  if (splits <= 0) splits = fc::decode_attn_pick_splits(int(B), int(Hkv), int(max_ctx), fc::gemm_num_sms());
+  while (splits > 1 && (B * Hq * splits * D > ATTN_WS_FLOATS || B * Hq * splits > ATTN_LSE_FLOATS)) --splits;
+  Tensor out = torch::empty_like(q);
+  fc::launch_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
+                              context_lens.data_ptr<int>(), out.data_ptr(), ws.attn_o.data_ptr<float>(),
+                              ws.attn_lse.data_ptr<float>(), int(B), int(Hq), int(Hkv), int(D), int(kc.size(1)),
+                              int(block_tables.size(1)), int(kc.size(0)), int(splits), float(scale),
+                              status_ptr(q.get_device()), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+Tensor sample(const Tensor& logits, const Tensor& temps, int64_t seed) {
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [B, V] with unit inner stride");
+  TORCH_CHECK(temps.is_cuda() && temps.scalar_type() == torch::kFloat32 && temps.numel() == logits.size(0),
+              "temperatures must be fp32 [B] on the device");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty({logits.size(0)}, logits.options().dtype(torch::kInt64));
+  fc::launch_sample(logits.data_ptr(), temps.data_ptr(), out.data_ptr(), int(logits.size(0)), int(logits.size(1)),
+                    logits.stride(0), uint32_t(seed), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+// Reads and clears the device status word (synchronises the current stream).
+int64_t read_status(int64_t device) {
+  auto& ws = workspace(int(device));
+  int64_t v = ws.status[0].item<int>();
+  if (v != 0) ws.status.zero_();
+  return v;
+}
+
+void register_stream_sms(int64_t stream_ptr, int64_t sms) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (sms <= 0) g_stream_sms.erase(uint64_t(stream_ptr));
+  else g_stream_sms[uint64_t(stream_ptr)] = int(sms);
+}
+
+}  // namespace
+
+void register_greenctx(pybind11::module_& m);
+void register_compress(pybind11::module_& m);
+void register_comm(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "y = act(x @ w.T + bias) on tcgen05", py::arg("x"), py::arg("w"), py::arg("bias") = py::none(),
+        py::arg("act") = 0, py::arg("out") = py::none());
+  m.def("rms_norm", &rms_norm);
+  m.def("add_rms_norm", &add_rms_norm);
+  m.def("layer_norm", &layer_norm);
+  m.def("silu_and_mul", &silu_and_mul);
+  m.def("embedding", &embedding);
+  m.def("rope_qknorm_store", &rope_qknorm_store);
+  m.def("prefill_attention", &prefill_attention);
+  m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,
+        py::arg("max_ctx") = 0);
+  m.def("sample", &sample);
+  m.def("read_status", &read_status);
+  m.def("register_stream_sms", &register_stream_sms);
+  m.def("num_sms", []() { return fc::gemm_num_sms(); });
+  register_greenctx(m);
+  register_compress(m);
+  register_comm(m);
+}

@@ -1,0 +1,372 @@
+// Bandwidth-bound ops: RMSNorm / add+RMSNorm / LayerNorm, SwiGLU gate, embedding
+// gather, fused q/k-norm + rotary + paged KV store, and the sampler.  All bf16
+// in/out with fp32 math; rows are held in registers between the statistics pass
+// and the scaling pass so each element is read once.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <algorithm>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace fc {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_CHUNKS = 4;   // 16-byte chunks per thread: rows up to 256 * 4 * 8 = 8192 elements
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]);
+  u.y = pack_bf16(f[2], f[3]);
+  u.z = pack_bf16(f[4], f[5]);
+  u.w = pack_bf16(f[6], f[7]);
+  return u;
+}
+
+// y = rms_norm(x [+ residual]) * w ; if residual != nullptr it is updated in place with x + residual.
+// One block per row; H % 8 == 0, H <= 8192.  x may be fp32 partial sums? no: bf16 only.
+template <bool ADD>
+__global__ void __launch_bounds__(NORM_THREADS)
+rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
+                bf16* __restrict__ y, int H, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int chunks = H >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  uint4* rr = ADD ? reinterpret_cast<uint4*>(residual + row * H) : nullptr;
+  float v[NORM_MAX_CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int idx = threadIdx.x + c * NORM_THREADS;
+    if (idx < chunks) {
+      unpack8(xr[idx], v[c]);
+      if (ADD) {
+        float r[8];
+        unpack8(rr[idx], r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += r[i];
+        const uint4 s = pack8(v[c]);
+        rr[idx] = s;
+        unpack8(s, v[c]);            // normalise the bf16-rounded sum, like the PyTorch statement
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float inv = rsqrtf(tot / float(H) + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int idx = threadIdx.x + c * NORM_THREADS;
+    if (idx < chunks) {
+      float g[8], o[8];
+      unpack8(wr[idx], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = __bfloat162float(__float2bfloat16(v[c][i] * inv)) * g[i];
+      yr[idx] = pack8(o);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NORM_THREADS)
+layer_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                  bf16* __restrict__ y, int H, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int chunks = H >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  float v[NORM_MAX_CHUNKS][8];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int idx = threadIdx.x + c * NORM_THREADS;
+    if (idx < chunks) {
+      unpack8(xr[idx], v[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[c][i];
+    }
+  }
+  const float mean = block_sum(s, red) / float(H);
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int idx = threadIdx.x + c * NORM_THREADS;
+    if (idx < chunks) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = v[c][i] - mean;
+        ss += d * d;
+      }
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / float(H) + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const uint4* br = reinterpret_cast<const uint4*>(b);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int idx = threadIdx.x + c * NORM_THREADS;
+    if (idx < chunks) {
+      float g[8], bb[8], o[8];
+      unpack8(wr[idx], g);
+      unpack8(br[idx], bb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mean) * inv * g[i] + bb[i];
+      yr[idx] = pack8(o);
+    }
+  }
+}
+
+// y[t, i] = silu(x[t, i]) * x[t, I + i]
+__global__ void silu_and_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long T, int I) {
+  const int chunks = I >> 3;
+  const long long total = T * chunks;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / chunks;
+    const int c = int(idx - t * chunks);
+    const uint4* row = reinterpret_cast<const uint4*>(x + t * 2 * I);
+    float g[8], u[8], o[8];
+    unpack8(row[c], g);
+    unpack8(row[chunks + c], u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+    reinterpret_cast<uint4*>(y + t * I)[c] = pack8(o);
+  }
+}
+
+// out[t, :] = (vocab_start <= ids[t] < vocab_start + V) ? weight[ids[t] - vocab_start, :] : 0
+__global__ void embedding_kernel(const long long* __restrict__ ids, const bf16* __restrict__ weight,
+                                 bf16* __restrict__ out, int T, int H, int V, int vocab_start) {
+  const int t = blockIdx.x;
+  const long long id = ids[t] - vocab_start;
+  const int chunks = H >> 3;
+  uint4* o = reinterpret_cast<uint4*>(out + (long long)t * H);
+  if (id < 0 || id >= V) {
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) o[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(weight + id * H);
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) o[c] = src[c];
+}
+
+// One warp per (token, head).  Heads [0, Hq) are queries (normed, rotated, written to q_out),
+// [Hq, Hq+Hkv) keys (normed, rotated, stored in the pool), the rest values (stored).
+__global__ void __launch_bounds__(128)
+rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restrict__ positions,
+                         const float* __restrict__ cos_sin, const bf16* __restrict__ q_w,
+                         const bf16* __restrict__ k_w, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                         bf16* __restrict__ v_cache, const int* __restrict__ slots, int T, int Hq, int Hkv,
+                         int D, float eps, long long num_slots, uint32_t* status) {
+  const int heads = Hq + 2 * Hkv;
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)T * heads) return;
+  const int t = int(wid / heads);
+  const int h = int(wid - (long long)t * heads);
+  const bf16* src = qkv + (long long)t * heads * D + (long long)h * D;
+  const int half = D >> 1;
+  long long slot = -1;
+  if (h >= Hq && slots != nullptr) {
+    slot = slots[t];
+    if (slot >= num_slots) {
+      report(status, ST_BAD_INDEX);
+      slot = -1;
+    }
+  }
+  if (h >= Hq + Hkv) {            // value head: plain copy into the pool
+    if (slot < 0) return;
+    bf16* dst = v_cache + (slot * Hkv + (h - Hq - Hkv)) * D;
+    for (int i = lane; i < (D >> 3); i += 32)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    return;
+  }
+  const bool is_q = h < Hq;
+  const bf16* nw = is_q ? q_w : k_w;
+  if (!is_q && slot < 0 && slots != nullptr) return;
+  // pairs (p, p + half), p = lane, lane + 32, ...   (D <= 256)
+  float lo[4], hi[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p = lane + 32 * j;
+    if (p < half) {
+      lo[j] = __bfloat162float(src[p]);
+      hi[j] = __bfloat162float(src[p + half]);
+      ss += lo[j] * lo[j] + hi[j] * hi[j];
+    }
+  }
+  if (nw != nullptr) {
+    const float inv = rsqrtf(warp_sum(ss) / float(D) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = lane + 32 * j;
+      if (p < half) {
+        lo[j] = __bfloat162float(__float2bfloat16(lo[j] * inv)) * __bfloat162float(nw[p]);
+        hi[j] = __bfloat162float(__float2bfloat16(hi[j] * inv)) * __bfloat162float(nw[p + half]);
+        // the PyTorch statement rounds the normed head to bf16 before the rotation
+        lo[j] = __bfloat162float(__float2bfloat16(lo[j]));
+        hi[j] = __bfloat162float(__float2bfloat16(hi[j]));
+      }
+    }
+  }
+  const float* cs = cos_sin + positions[t] * D;
+  bf16* dst = is_q ? (q_out + ((long long)t * Hq + h) * D) : (k_cache + (slot * Hkv + (h - Hq)) * D);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p = lane + 32 * j;
+    if (p < half) {
+      const float c = cs[p], s = cs[p + half];
+      dst[p] = __float2bfloat16(lo[j] * c - hi[j] * s);
+      dst[p + half] = __float2bfloat16(hi[j] * c + lo[j] * s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------- sampler
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352dU;
+  x ^= x >> 15;
+  x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+
+// token[b] = argmax_j logits[b, j] / T_b + Gumbel_j   (plain argmax when T_b == 0).
+// argmax(softmax(l / T) / E) with E ~ Exp(1) is the same draw: log p_j - log E_j.
+__global__ void __launch_bounds__(1024)
+sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, long long* __restrict__ out,
+              int V, long long ld, uint32_t seed) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  const int b = blockIdx.x;
+  const float T = temps[b];
+  const bf16* row = logits + (long long)b * ld;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    float v = __bfloat162float(row[j]);
+    if (T > 0.f) {
+      const uint32_t r = mix32(mix32(seed ^ (uint32_t(b) * 0x9E3779B9u)) + uint32_t(j));
+      const float u = (float(r >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
+      v = v / T - __logf(-__logf(u));
+    }
+    if (v > best || (v == best && j < best_i)) {
+      best = v;
+      best_i = j;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    s_val[warp] = best;
+    s_idx[warp] = best_i;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    best = (lane < (blockDim.x >> 5)) ? s_val[lane] : -INFINITY;
+    best_i = (lane < (blockDim.x >> 5)) ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (lane == 0) out[b] = best_i;
+  }
+}
+
+// ================================================================= launchers
+void launch_rms_norm(const void* x, void* residual, const void* w, void* y, long long T, int H, float eps,
+                     cudaStream_t s) {
+  if (T == 0) return;
+  if (residual != nullptr)
+    rms_norm_kernel<true><<<(unsigned)T, NORM_THREADS, 0, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w,
+                                                               (bf16*)y, H, eps);
+  else
+    rms_norm_kernel<false><<<(unsigned)T, NORM_THREADS, 0, s>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y,
+                                                                H, eps);
+}
+
+void launch_layer_norm(const void* x, const void* w, const void* b, void* y, long long T, int H, float eps,
+                       cudaStream_t s) {
+  if (T == 0) return;
+  layer_norm_kernel<<<(unsigned)T, NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y,
+                                                         H, eps);
+}
+
+void launch_silu_and_mul(const void* x, void* y, long long T, int I, cudaStream_t s) {
+  if (T == 0) return;
+  const long long total = T * (I >> 3);
+  const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  silu_and_mul_kernel<<<blocks, 256, 0, s>>>((const bf16*)x, (bf16*)y, T, I);
+}
+
+void launch_embedding(const void* ids, const void* weight, void* out, int T, int H, int V, int vocab_start,
+                      cudaStream_t s) {
+  if (T == 0) return;
+  embedding_kernel<<<T, 128, 0, s>>>((const long long*)ids, (const bf16*)weight, (bf16*)out, T, H, V, vocab_start);
+}
+
+void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
+                              const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
+                              int Hq, int Hkv, int D, float eps, long long num_slots, uint32_t* status,
+                              cudaStream_t s) {
+  if (T == 0) return;
+  const long long warps = (long long)T * (Hq + 2 * Hkv);
+  const long long blocks = (warps + 3) / 4;
+  rope_qknorm_store_kernel<<<(unsigned)blocks, 128, 0, s>>>(
+      (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, D, eps, num_slots, status);
+}
+
+void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
+                   cudaStream_t s) {
+  if (B == 0) return;
+  sample_kernel<<<B, 1024, 0, s>>>((const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed);
+}
+
+}  // namespace fc

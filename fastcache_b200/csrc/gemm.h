@@ -1,0 +1,35 @@
+// Host interface of the tcgen05 GEMM (gemm.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fc {
+
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_TANH = 3, ACT_QUICK_GELU = 4, ACT_SILU = 5 };
+
+// Split-K needs scratch for fp32 partial tiles and one arrival counter per output
+// tile (zero before the first launch; the kernel leaves them zero).
+constexpr int GEMM_SCRATCH_TILES = 192;     // (tile, split) partials that fit the scratch
+constexpr int GEMM_MAX_TILES_SPLIT = 4096;  // counters
+
+struct GemmWorkspace {
+  float* scratch = nullptr;
+  int* counters = nullptr;
+  uint32_t* status = nullptr;
+};
+
+size_t gemm_scratch_bytes();
+size_t gemm_counter_bytes();
+int gemm_num_sms();
+
+CUtensorMap make_tmap_bf16_2d(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                              uint32_t box_cols);
+
+// c[M, N] = act(x[M, K] @ w[N, K]^T + bias[N]); bf16 in/out, fp32 accumulate.
+// ldx / ldw / ldc are row pitches in elements.  sm_limit > 0 caps the persistent grid
+// (used when the launching stream belongs to a green context with fewer SMs).
+void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
+               long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit, cudaStream_t stream);
+
+}  // namespace fc

@@ -1,0 +1,33 @@
+// Launchers of the non-GEMM kernels (elementwise.cu, attn_*.cu, compress.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fc {
+
+constexpr int DECODE_MAX_SPLITS = 32;
+
+void launch_rms_norm(const void* x, void* residual, const void* w, void* y, long long T, int H, float eps,
+                     cudaStream_t s);
+void launch_layer_norm(const void* x, const void* w, const void* b, void* y, long long T, int H, float eps,
+                       cudaStream_t s);
+void launch_silu_and_mul(const void* x, void* y, long long T, int I, cudaStream_t s);
+void launch_embedding(const void* ids, const void* weight, void* out, int T, int H, int V, int vocab_start,
+                      cudaStream_t s);
+void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
+                              const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
+                              int Hq, int Hkv, int D, float eps, long long num_slots, uint32_t* status,
+                              cudaStream_t s);
+void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
+                   cudaStream_t s);
+
+int decode_attn_pick_splits(int B, int Hkv, int max_ctx, int num_sms);
+void launch_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                             const int* context_lens, void* out, float* part_o, float* part_lse, int B, int Hq,
+                             int Hkv, int D, int block_size, int max_blocks, int num_blocks, int splits,
+                             float scale, uint32_t* status, cudaStream_t stream);
+void launch_prefill_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                              const int* cu_seqlens_q, const int* kv_lens, void* out, int num_seqs, int max_q_len,
+                              int Hq, int Hkv, int D, int block_size, int max_blocks, int num_blocks, float scale,
+                              uint32_t* status, cudaStream_t stream);
+}  // namespace fc

@@ -160,7 +160,8 @@ class ModelRunner:
         if random_init:
             shapes = self.model.hf_weight_shapes(self.hf_config)
             init_random_weights(self.model, shapes, seed=cfg.seed, std=float(cfg.extra.get("init_std", 0.02)),
-                                device=str(self.device) if self.device.type == "cuda" else "cpu")
+                                device=cfg.extra.get("init_device") or
+                                (str(self.device) if self.device.type == "cuda" else "cpu"))
         else:
             load_model(self.model, cfg.model)
 

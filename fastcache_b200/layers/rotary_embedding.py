@@ -61,7 +61,7 @@ _ROPE_CACHE: dict = {}
 def get_rope(head_size: int, rotary_dim: int, max_position: int, base: float,
              rope_scaling: Optional[dict] = None) -> RotaryEmbedding:
     key = (head_size, rotary_dim, max_position, float(base),
-           tuple(sorted(rope_scaling.items())) if rope_scaling else None)
+           tuple(sorted(rope_scaling.items())) if rope_scaling else None, str(torch.get_default_device()))
     if key not in _ROPE_CACHE:
         _ROPE_CACHE[key] = RotaryEmbedding(head_size, rotary_dim, max_position, base, rope_scaling)
     return _ROPE_CACHE[key]

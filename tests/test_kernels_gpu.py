@@ -1,0 +1,154 @@
+"""sm_100a kernels against the fp32 PyTorch statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from fastcache_b200 import ops
+from fastcache_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def _check_status():
+    assert ops.ext().read_status(torch.cuda.current_device()) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (1000, 768, 320), (4096, 6144, 4096),
+                                   (300, 1376, 4096), (257, 128, 8200)])
+def test_gemm_large_m(M, N, K):
+    x, w = _rand(M, K, seed=1), _rand(N, K, scale=0.05, seed=2)
+    y = ops.linear(x, w)
+    want = x.float() @ w.float().T
+    torch.cuda.synchronize()
+    _check_status()
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (7, 6144, 4096), (33, 4096, 12288), (90, 1024, 512),
+                                   (128, 4096, 4096), (200, 512, 4096), (256, 24576, 4096), (128, 1000, 136)])
+def test_gemm_small_m_swapped_splitk(M, N, K):
+    x, w = _rand(M, K, seed=3), _rand(N, K, scale=0.05, seed=4)
+    b = _rand(N, seed=5)
+    y = ops.linear(x, w, b)
+    want = x.float() @ w.float().T + b.float()
+    torch.cuda.synchronize()
+    _check_status()
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+    y2 = ops.linear(x, w, b)           # counters must have been left at zero
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", "gelu_tanh", "quick_gelu", "swiglu"])
+def test_gemm_activation_bias(act):
+    x, w, b = _rand(300, 256, seed=6), _rand(512, 256, scale=0.1, seed=7), _rand(512, seed=8)
+    y = ops.linear(x, w, b, act)
+    want = ref.linear(x.float(), w.float(), b.float(), act)
+    assert (y.float() - want).abs().max().item() < 5e-2
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (37, 4096), (128, 5120), (5, 3584), (3, 1152)])
+def test_rms_and_layer_norm(T, H):
+    x, r, w, b = _rand(T, H, seed=1), _rand(T, H, seed=2), _rand(H, seed=3), _rand(H, seed=4)
+    y = ops.rms_norm(x, w, 1e-6)
+    assert (y.float() - ref.rms_norm(x, w, 1e-6).float()).abs().max().item() < 3e-2
+    r2 = r.clone()
+    y2, r_out = ops.add_rms_norm(x, r2, w, 1e-6)
+    wy, wr = ref.add_rms_norm(x, r, w, 1e-6)
+    assert torch.equal(r_out, wr)
+    assert (y2.float() - wy.float()).abs().max().item() < 3e-2
+    y3 = ops.layer_norm(x, w, b, 1e-5)
+    assert (y3.float() - ref.layer_norm(x.float(), w.float(), b.float(), 1e-5)).abs().max().item() < 5e-2
+
+
+def test_silu_embedding_sample():
+    x = _rand(77, 2 * 1376, seed=1)
+    assert (ops.silu_and_mul(x).float() - ref.silu_and_mul(x.float())).abs().max().item() < 2e-2
+    w = _rand(1000, 256, seed=2)
+    ids = torch.randint(0, 1200, (50,), device=DEV)
+    assert torch.equal(ops.embedding(ids, w, 100), ref.embedding(ids, w, 100))
+    logits = _rand(9, 5000, seed=3)
+    t0 = torch.zeros(9, device=DEV)
+    assert torch.equal(ops.sample(logits, t0), logits.float().argmax(-1))
+    t1 = torch.full((9,), 0.8, device=DEV)
+    s1, s2 = ops.sample(logits, t1, seed=5), ops.sample(logits, t1, seed=5)
+    assert torch.equal(s1, s2) and int(s1.max()) < 5000
+    # a peaked distribution must be sampled at its peak
+    peaked = logits.clone()
+    peaked[:, 123] = 200.0
+    assert torch.all(ops.sample(peaked, t1, seed=9) == 123)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,qk", [(128, 8, 2, True), (64, 4, 2, False), (128, 4, 4, False)])
+def test_rope_qknorm_store(D, Hq, Hkv, qk):
+    T, nb, bs = 45, 8, 16
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=1)
+    pos = torch.randint(0, 500, (T,), device=DEV)
+    cs = ref.build_cos_sin_cache(D, 512, 10000.0, DEV)
+    qw = _rand(D, seed=2) if qk else None
+    kw = _rand(D, seed=3) if qk else None
+    slots = torch.randperm(nb * bs, device=DEV)[:T].int()
+    slots[3] = -1
+    kc, vc = (torch.zeros(nb, bs, Hkv, D, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = ops.rope_qknorm_store(qkv, pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc, vc, slots)
+    q2 = ref.rope_qknorm_store(qkv, pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc2, vc2, slots)
+    _check_status()
+    assert (q.float() - q2.float()).abs().max().item() < 6e-2
+    assert (kc.float() - kc2.float()).abs().max().item() < 6e-2
+    assert torch.equal(vc, vc2)
+
+
+def _paged(B, lens, Hkv, D, bs, seed=0):
+    nb_per = [-(-n // bs) for n in lens]
+    nb = sum(nb_per) + 3
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed)).tolist()
+    kc, vc = _rand(nb, bs, Hkv, D, seed=seed + 1), _rand(nb, bs, Hkv, D, seed=seed + 2)
+    bt = torch.zeros(B, max(nb_per), dtype=torch.int32)
+    k = 0
+    for i, n in enumerate(nb_per):
+        bt[i, :n] = torch.tensor(perm[k:k + n], dtype=torch.int32)
+        k += n
+    return kc, vc, bt.to(DEV)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,bs,lens", [
+    (128, 32, 8, 16, [1, 17, 64, 65, 300]), (128, 8, 8, 256, [1000, 5]), (64, 4, 2, 16, [33, 129]),
+    (128, 28, 4, 64, [2049]), (128, 8, 1, 32, [4000, 77, 640])])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_decode_attention(D, Hq, Hkv, bs, lens, splits):
+    B = len(lens)
+    kc, vc, bt = _paged(B, lens, Hkv, D, bs)
+    q = _rand(B, Hq, D, seed=9)
+    cl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = D ** -0.5
+    o = ops.decode_attention(q, kc, vc, bt, cl, scale, {"splits": splits})
+    want = ref.decode_attention(q.float(), kc.float(), vc.float(), bt, cl, scale)
+    _check_status()
+    assert (o.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,bs,qlens,kvlens", [
+    (128, 8, 2, 16, [5, 64, 130], [5, 64, 130]), (128, 4, 4, 256, [300], [300]),
+    (64, 4, 2, 16, [128, 128], [128, 128]), (128, 8, 2, 32, [10, 100], [74, 228]),
+    (128, 32, 8, 64, [1000], [1000])])
+def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens):
+    B = len(qlens)
+    kc, vc, bt = _paged(B, kvlens, Hkv, D, bs, seed=4)
+    T = sum(qlens)
+    q = _rand(T, Hq, D, seed=11)
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    kl = torch.tensor(kvlens, dtype=torch.int32, device=DEV)
+    scale = D ** -0.5
+    o = ops.prefill_attention(q, kc, vc, bt, cu, kl, scale, max(qlens))
+    want = ref.prefill_attention(q.float(), kc.float(), vc.float(), bt, cu, kl, scale)
+    _check_status()
+    assert (o.float() - want).abs().max().item() < 2e-2
