@@ -290,6 +290,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &read_status);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
+  m.def("status_tensor", [](int64_t device) { return workspace(int(device)).status; });
   register_greenctx(m);
   register_compress(m);
   register_comm(m);

@@ -1,2 +1,58 @@
-#include <pybind11/pybind11.h>
-void register_compress(pybind11::module_& m) {}
+// Bindings of the in-pool compression kernels (evict.cu, ccm.cu).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels.h"
+
+namespace {
+using torch::Tensor;
+
+void check_pool(const Tensor& pool) {
+  TORCH_CHECK(pool.is_cuda() && pool.scalar_type() == torch::kBFloat16 && pool.dim() == 6 && pool.is_contiguous() &&
+                  pool.size(1) == 2, "pool must be contiguous bf16 [L, 2, blocks, block, Hkv, D]");
+}
+void check_i32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be int32 CUDA");
+}
+
+// scores [n_seq, L, Hkv, s_stride] fp32; mode 0: -||k|| per head, mode 1: +mean_heads ||k||
+Tensor knorm_scores(const Tensor& pool, const Tensor& block_tables, const Tensor& kv_lens, int64_t max_len,
+                    int64_t mode, Tensor status) {
+  check_pool(pool);
+  check_i32(block_tables, "block_tables");
+  check_i32(kv_lens, "kv_lens");
+  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(4);
+  const int64_t stride = (max_len + 3) / 4 * 4;
+  c10::cuda::CUDAGuard guard(pool.device());
+  Tensor scores = torch::empty({n, L, Hkv, stride}, pool.options().dtype(torch::kFloat32));
+  fc::launch_knorm_scores(pool.data_ptr(), block_tables.data_ptr<int>(), kv_lens.data_ptr<int>(),
+                          scores.data_ptr<float>(), int(n), int(L), int(pool.size(2)), int(pool.size(3)), int(Hkv),
+                          int(pool.size(5)), int(block_tables.size(1)), int(max_len), int(stride), int(mode),
+                          reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
+  return scores;
+}
+
+void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_tables, const Tensor& kv_lens,
+                    const Tensor& n_kepts, Tensor status) {
+  check_pool(pool);
+  check_i32(block_tables, "block_tables");
+  check_i32(kv_lens, "kv_lens");
+  check_i32(n_kepts, "n_kepts");
+  TORCH_CHECK(scores.is_cuda() && scores.scalar_type() == torch::kFloat32 && scores.dim() == 4 &&
+                  scores.is_contiguous(), "scores must be contiguous fp32 [n_seq, L, Hkv, stride]");
+  TORCH_CHECK(scores.size(0) == kv_lens.numel() && scores.size(1) == pool.size(0) && scores.size(2) == pool.size(4),
+              "scores do not match the pool / batch");
+  c10::cuda::CUDAGuard guard(pool.device());
+  fc::launch_select_compact(pool.data_ptr(), scores.data_ptr<float>(), block_tables.data_ptr<int>(),
+                            kv_lens.data_ptr<int>(), n_kepts.data_ptr<int>(), int(kv_lens.numel()),
+                            int(pool.size(0)), int(pool.size(2)), int(pool.size(3)), int(pool.size(4)),
+                            int(pool.size(5)), int(block_tables.size(1)), int(scores.size(3)),
+                            reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
+}
+}  // namespace
+
+void register_compress(pybind11::module_& m) {
+  m.def("knorm_scores", &knorm_scores);
+  m.def("select_compact", &select_compact);
+}

@@ -1,0 +1,253 @@
+// KV eviction in the paged pool: key-norm scoring, per-head top-k selection and
+// stable in-place compaction.
+//
+// Pool layout [L, 2, num_blocks, block_size, Hkv, D] bf16.  Scores are fp32
+// [n_seq, L, Hkv, s_stride], higher = keep (+inf = always keep).
+//
+// select_compact: one CTA per (kv head, layer, request).  The scores of the
+// request are turned into order-preserving 32-bit keys in shared memory, the
+// k-th largest key is found with a 4-pass radix select, and the kept rows
+// (ties resolved toward later rows) are moved to the front of the request's rows
+// in ascending order.  A destination index never exceeds its source index, and
+// each 128-row chunk is read completely into registers before it is written, so
+// the compaction is safe in place.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace fc {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t float_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// scores[seq, layer, h, tok] = sign * ||K[tok, h, :]||      (mode 0: per head)
+//                            = mean_h ||K[tok, h, :]||       (mode 1: shared by heads, largest kept)
+__global__ void __launch_bounds__(256)
+knorm_score_kernel(const bf16* __restrict__ pool, const int* __restrict__ block_tables,
+                   const int* __restrict__ kv_lens, float* __restrict__ scores, int L, int num_blocks,
+                   int block_size, int Hkv, int D, int max_blocks, int s_stride, int mode, uint32_t* status) {
+  const int seq = blockIdx.z, layer = blockIdx.y;
+  const int len = kv_lens[seq];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * 8 + warp;
+  if (tok >= len) return;
+  const int blk = block_tables[(long long)seq * max_blocks + tok / block_size];
+  if (blk < 0 || blk >= num_blocks) {
+    report(status, ST_BAD_INDEX);
+    return;
+  }
+  const long long kbase = ((long long)layer * 2 + 0) * num_blocks;
+  const bf16* row = pool + (((kbase + blk) * block_size + tok % block_size) * Hkv) * D;
+  float* out = scores + (((long long)seq * L + layer) * Hkv) * s_stride + tok;
+  float mean = 0.f;
+  for (int h = 0; h < Hkv; ++h) {
+    float ss = 0.f;
+    for (int i = lane; i < D / 2; i += 32) {
+      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(row + h * D)[i]);
+      ss += v.x * v.x + v.y * v.y;
+    }
+    const float n = sqrtf(warp_sum(ss));
+    if (mode == 0) {
+      if (lane == 0) out[(long long)h * s_stride] = -n;
+    } else {
+      mean += n;
+    }
+  }
+  if (mode == 1 && lane == 0) {
+    mean /= float(Hkv);
+    for (int h = 0; h < Hkv; ++h) out[(long long)h * s_stride] = mean;
+  }
+}
+
+constexpr int SC_THREADS = 256;
+constexpr int SC_CHUNK = 128;
+
+template <int D>
+__global__ void __launch_bounds__(SC_THREADS)
+select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
+                      const int* __restrict__ block_tables, const int* __restrict__ kv_lens,
+                      const int* __restrict__ n_kepts, int L, int num_blocks, int block_size, int Hkv,
+                      int max_blocks, int s_stride, uint32_t* status) {
+  extern __shared__ uint32_t sm[];
+  const int h = blockIdx.x, layer = blockIdx.y, seq = blockIdx.z;
+  const int S = kv_lens[seq];
+  int k = n_kepts[seq];
+  if (k >= S || S <= 0) return;
+  if (k < 1) k = 1;
+  uint32_t* keys = sm;                       // [S]
+  uint32_t* hist = sm + s_stride;            // [256]
+  int* s_misc = reinterpret_cast<int*>(hist + 256);   // [8]: bin, above, ...
+  int* dstpos = s_misc + 8;                  // [SC_CHUNK]
+  int* wsum = dstpos + SC_CHUNK;             // [2][8] warp partials
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const float* sc = scores + (((long long)seq * L + layer) * Hkv + h) * s_stride;
+  for (int i = tid; i < S; i += SC_THREADS) keys[i] = float_key(sc[i]);
+  __syncthreads();
+
+  // ---- radix select: the k-th largest key
+  uint32_t prefix = 0, mask = 0;
+  int remaining = k;                         // rank still to find inside the current prefix class
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    hist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < S; i += SC_THREADS) {
+      const uint32_t key = keys[i];
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int acc = 0, bin = 255;
+      for (; bin > 0; --bin) {
+        if (acc + int(hist[bin]) >= remaining) break;
+        acc += int(hist[bin]);
+      }
+      s_misc[0] = bin;
+      s_misc[1] = acc;
+    }
+    __syncthreads();
+    prefix |= uint32_t(s_misc[0]) << shift;
+    mask |= 0xFFu << shift;
+    remaining -= s_misc[1];
+    __syncthreads();
+  }
+  const uint32_t thr = prefix;               // keep key > thr, plus the last `remaining` rows with key == thr
+  const int need_eq = remaining;
+
+  // total number of ties
+  int eq_local = 0;
+  for (int i = tid; i < S; i += SC_THREADS) eq_local += (keys[i] == thr);
+  eq_local = int(warp_sum(float(eq_local)) + 0.5f);
+  if (lane == 0) wsum[warp] = eq_local;
+  __syncthreads();
+  int eq_total = 0;
+  for (int w = 0; w < SC_THREADS / 32; ++w) eq_total += wsum[w];
+  __syncthreads();
+
+  const long long kbase = ((long long)layer * 2 + 0) * num_blocks;
+  const long long vbase = ((long long)layer * 2 + 1) * num_blocks;
+  const int* bt = block_tables + (long long)seq * max_blocks;
+  auto row_ptr = [&](long long base, int tok) -> bf16* {
+    const int blk = bt[tok / block_size];
+    if (blk < 0 || blk >= num_blocks) {
+      report(status, ST_BAD_INDEX);
+      return nullptr;
+    }
+    return pool + (((base + blk) * block_size + tok % block_size) * Hkv + h) * D;
+  };
+
+  int out_base = 0;        // rows already written
+  int eq_seen = 0;         // ties already passed
+  constexpr int PIECES = D / 8;              // 16-byte pieces per row (K or V)
+  constexpr int PER_THREAD = (SC_CHUNK * 2 * PIECES) / SC_THREADS;
+  for (int c0 = 0; c0 < S; c0 += SC_CHUNK) {
+    // flags and positions for this chunk (threads 0..127 own one row each)
+    int keep = 0, iseq = 0;
+    const int tok = c0 + tid;
+    if (tid < SC_CHUNK && tok < S) {
+      const uint32_t key = keys[tok];
+      iseq = (key == thr);
+      keep = (key > thr);
+    }
+    // exclusive scans of `iseq` and (later) `keep` over the first 128 threads
+    int x = iseq;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) wsum[warp] = x;
+    __syncthreads();
+    int eq_before = eq_seen + x - iseq;
+    for (int w = 0; w < warp; ++w) eq_before += wsum[w];
+    int eq_chunk = 0;
+    for (int w = 0; w < SC_THREADS / 32; ++w) eq_chunk += wsum[w];
+    __syncthreads();
+    // a tie is kept when it is among the last `need_eq` ties of the request
+    if (iseq && (eq_total - eq_before) <= need_eq) keep = 1;
+    x = keep;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) wsum[8 + warp] = x;
+    __syncthreads();
+    int pos = out_base + x - keep;
+    for (int w = 0; w < warp; ++w) pos += wsum[8 + w];
+    int kept_chunk = 0;
+    for (int w = 0; w < SC_THREADS / 32; ++w) kept_chunk += wsum[8 + w];
+    if (tid < SC_CHUNK) dstpos[tid] = keep ? pos : -1;
+    __syncthreads();
+
+    // move rows: read the whole chunk, then write it
+    uint4 regs[PER_THREAD];
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+      const int piece = tid + j * SC_THREADS;
+      const int r = piece / (2 * PIECES), part = piece % (2 * PIECES);
+      regs[j] = make_uint4(0, 0, 0, 0);
+      if (dstpos[r] >= 0 && dstpos[r] != c0 + r) {
+        const bf16* src = row_ptr(part < PIECES ? kbase : vbase, c0 + r);
+        if (src != nullptr) regs[j] = reinterpret_cast<const uint4*>(src)[part % PIECES];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+      const int piece = tid + j * SC_THREADS;
+      const int r = piece / (2 * PIECES), part = piece % (2 * PIECES);
+      if (dstpos[r] >= 0 && dstpos[r] != c0 + r) {
+        bf16* dst = row_ptr(part < PIECES ? kbase : vbase, dstpos[r]);
+        if (dst != nullptr) reinterpret_cast<uint4*>(dst)[part % PIECES] = regs[j];
+      }
+    }
+    out_base += kept_chunk;
+    eq_seen += eq_chunk;
+    __syncthreads();
+  }
+}
+
+void launch_knorm_scores(const void* pool, const int* block_tables, const int* kv_lens, float* scores, int n_seq,
+                         int L, int num_blocks, int block_size, int Hkv, int D, int max_blocks, int max_len,
+                         int s_stride, int mode, uint32_t* status, cudaStream_t stream) {
+  if (n_seq == 0 || max_len == 0) return;
+  dim3 grid((max_len + 7) / 8, L, n_seq);
+  knorm_score_kernel<<<grid, 256, 0, stream>>>((const bf16*)pool, block_tables, kv_lens, scores, L, num_blocks,
+                                               block_size, Hkv, D, max_blocks, s_stride, mode, status);
+}
+
+void launch_select_compact(void* pool, const float* scores, const int* block_tables, const int* kv_lens,
+                           const int* n_kepts, int n_seq, int L, int num_blocks, int block_size, int Hkv, int D,
+                           int max_blocks, int s_stride, uint32_t* status, cudaStream_t stream) {
+  if (n_seq == 0) return;
+  dim3 grid(Hkv, L, n_seq);
+  const int smem = (s_stride + 256 + 8 + SC_CHUNK + 16) * 4;
+  if (smem > 220 * 1024) throw std::runtime_error("select_compact: request too long for one CTA's shared memory");
+  auto launch = [&](auto kern) {
+    static int configured = 0;
+    if (smem > configured) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      configured = smem;
+    }
+    kern<<<grid, SC_THREADS, smem, stream>>>((bf16*)pool, scores, block_tables, kv_lens, n_kepts, L, num_blocks,
+                                             block_size, Hkv, max_blocks, s_stride, status);
+  };
+  if (D == 128) launch(select_compact_kernel<128>);
+  else if (D == 64) launch(select_compact_kernel<64>);
+  else throw std::runtime_error("select_compact: head_dim must be 64 or 128");
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("select_compact launch: ") + cudaGetErrorString(e));
+}
+
+}  // namespace fc

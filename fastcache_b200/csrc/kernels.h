@@ -31,3 +31,12 @@ void launch_prefill_attention(const void* q, const void* k_cache, const void* v_
                               int Hq, int Hkv, int D, int block_size, int max_blocks, int num_blocks, float scale,
                               uint32_t* status, cudaStream_t stream);
 }  // namespace fc
+
+namespace fc {
+void launch_knorm_scores(const void* pool, const int* block_tables, const int* kv_lens, float* scores, int n_seq,
+                         int L, int num_blocks, int block_size, int Hkv, int D, int max_blocks, int max_len,
+                         int s_stride, int mode, uint32_t* status, cudaStream_t stream);
+void launch_select_compact(void* pool, const float* scores, const int* block_tables, const int* kv_lens,
+                           const int* n_kepts, int n_seq, int L, int num_blocks, int block_size, int Hkv, int D,
+                           int max_blocks, int s_stride, uint32_t* status, cudaStream_t stream);
+}  // namespace fc
