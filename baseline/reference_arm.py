@@ -1,0 +1,146 @@
+"""Runs the reference engine (installed unmodified under baseline/_ref) on the
+benchmark workload through its own public API: `LlavaLLM(...)`, `add_request`,
+`step(apply_compression=True)`.  Nothing of fastcache_b200 is imported here.
+
+The reference can only load weights from a HuggingFace directory, so a seeded
+random-init checkpoint (safetensors + config.json + a minimal tokenizer) is
+written to a scratch directory first.  Two packages the reference imports are
+absent from this environment (`xxhash`, `kvpress`); baseline/shims provides
+stand-ins that only satisfy the imports (see their docstrings).
+"""
+import json
+import os
+import sys
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _write_checkpoint(path, hf, seed=0):
+    import torch
+    from safetensors.torch import save_file
+    if os.path.exists(os.path.join(path, "DONE")):
+        return
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump(hf, fh, indent=1)
+    h, L = hf["hidden_size"], hf["num_hidden_layers"]
+    heads, kvh, d = hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"]
+    inter, vocab = hf["intermediate_size"], hf["vocab_size"]
+    g = torch.Generator(device="cuda").manual_seed(seed)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16).cpu()
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16)
+
+    index = {}
+    def save(tensors, name):
+        save_file(tensors, os.path.join(path, name))
+        for k in tensors:
+            index[k] = name
+
+    save({"model.embed_tokens.weight": rnd(vocab, h), "model.norm.weight": ones(h),
+          "lm_head.weight": rnd(vocab, h)}, "model-embed.safetensors")
+    for i in range(L):
+        p = f"model.layers.{i}."
+        save({p + "self_attn.q_proj.weight": rnd(heads * d, h), p + "self_attn.k_proj.weight": rnd(kvh * d, h),
+              p + "self_attn.v_proj.weight": rnd(kvh * d, h), p + "self_attn.o_proj.weight": rnd(h, heads * d),
+              p + "self_attn.q_norm.weight": ones(d), p + "self_attn.k_norm.weight": ones(d),
+              p + "mlp.gate_proj.weight": rnd(inter, h), p + "mlp.up_proj.weight": rnd(inter, h),
+              p + "mlp.down_proj.weight": rnd(h, inter), p + "input_layernorm.weight": ones(h),
+              p + "post_attention_layernorm.weight": ones(h)}, f"model-layer{i:03d}.safetensors")
+    # minimal tokenizer: the engine only needs eos_token_id and encode() for string prompts
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    vocab_map = {"<unk>": 0, "<eos>": 1, "hello": 2}
+    tok = Tokenizer(models.WordLevel(vocab_map, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(os.path.join(path, "tokenizer.json"))
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as fh:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<eos>", "unk_token": "<unk>"}, fh)
+    with open(os.path.join(path, "special_tokens_map.json"), "w") as fh:
+        json.dump({"eos_token": "<eos>", "unk_token": "<unk>"}, fh)
+    open(os.path.join(path, "DONE"), "w").close()
+
+
+def run(args, workload, ClockSampler, prompts_for, percentile):
+    import torch
+    hf, n_req, p_len, o_len = workload
+    n_req = args.requests or n_req
+    sys.path.insert(0, os.path.join(HERE, "shims"))
+    sys.path.insert(0, os.path.join(HERE, "_ref"))
+    torch.cuda.set_device(0)
+    ckpt = os.path.join(os.environ.get("FC_REF_CKPT_DIR", "/tmp"), f"fc_ref_{args.config}")
+    _write_checkpoint(ckpt, dict(hf))
+
+    from nanovllm.engine.llava_engine import LlavaLLM          # the reference's engine
+    from nanovllm.sampling_params import SamplingParams
+
+    compress = not args.no_compression
+    method = "knorm" if args.method in ("knorm", "knorm_ref") else args.method
+    llm = LlavaLLM(ckpt, enable_compression=compress, compression_backend="kvpress", kvpress_method=method,
+                   compression_factor=2, async_compression=False, max_model_len=p_len + o_len + 256,
+                   max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768, kvcache_block_size=256,
+                   gpu_memory_utilization=args.mem_util, enforce_eager=False)
+    sp = SamplingParams(temperature=0.6, max_tokens=o_len, ignore_eos=True)
+    wsp = SamplingParams(temperature=0.6, max_tokens=max(2, args.warmup), ignore_eos=True)
+    done = 0
+    while done < args.warmup:
+        for p in prompts_for(2, 512, hf["vocab_size"], 7):
+            llm.add_request(p, wsp)
+        while not llm.is_finished():
+            llm.step(apply_compression=compress)
+            done += 1
+
+    prompts = prompts_for(n_req, p_len, hf["vocab_size"], 1)
+    for p in prompts:
+        llm.add_request(p, sp)
+    sampler = ClockSampler(0)
+    torch.cuda.synchronize()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    t0 = time.perf_counter()
+    steps = out_tokens = 0
+    ttft = []
+    limit = args.steps if args.steps > 0 else 1 << 30
+    wave = 1
+    while steps < limit:
+        if llm.is_finished():
+            if args.steps <= 0:
+                break
+            wave += 1
+            for p in prompts_for(n_req, p_len, hf["vocab_size"], wave):
+                llm.add_request(p, sp)
+        _, n = llm.step(apply_compression=compress)
+        steps += 1
+        if n > 0:                                   # a prefill step: each request in it got its first token
+            now = time.perf_counter() - t0
+            batch = sum(1 for s in llm.scheduler.running if s.num_completion_tokens == 1)
+            ttft.extend([now] * batch)
+            out_tokens += batch
+        else:
+            out_tokens += -n
+    ev1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    clocks = sampler.stop()
+    ms = max(ev0.elapsed_time(ev1), (t1 - t0) * 1e3)
+    value = out_tokens / (ms / 1e3)
+    return {
+        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / max(1, steps), 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights",
+        "config": {"model": "Qwen3-8B shape", "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
+                   "parallelism": "tp1", "compression": f"{method} keep 50% (reference engine-native variant)"
+                   if compress else "none", "cuda_graph_decode": True, "kv_block": 256,
+                   "l2": "working set per step far exceeds L2; no flush needed"},
+        "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
+        "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
+        "output_tokens": out_tokens,
+        "e2e": {"value": round(value, 2), "unit": "tok/s", "ms_total": round(ms, 2),
+                "note": "the reference exposes no device-only timer; its single number is end to end"},
+        "clocks": clocks, "impl": "reference", "shims": ["xxhash", "kvpress"],
+    }

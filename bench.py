@@ -1,0 +1,294 @@
+"""Headline benchmark: output tokens/s (and p50 TTFT) of the serving engine.
+
+    python bench.py --gpus N --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Config (the reference's text benchmark shape): Qwen3-8B architecture, bf16,
+random-init weights, synthetic token ids; 128 concurrent requests of 4096
+prompt tokens and 512 output tokens each; KV eviction by key norm (default) or
+SnapKV (--method snapkv, window 64, pooling kernel 5) keeping 50 % of the prompt
+rows; CUDA-graph decode; tensor parallel over the N GPUs.
+
+A "step" is one engine step (one prefill batch or one decode batch including the
+compression that follows a prefill).  W warm-up steps run on a separate small
+wave of requests.  Then exactly K steps of the job are timed between a barrier +
+synchronize on both sides (default K = every step of the job).  Two numbers come
+out of the same run:
+  value      output tokens / device time, where device time is the sum of CUDA
+             event intervals around the model and compression kernels of each
+             step (max over ranks)
+  e2e.value  output tokens / elapsed time of the whole step loop through the
+             public `LLM.step()` API, including scheduling, the per-step copy of
+             the step's inputs from pinned host memory and the read-back of the
+             sampled tokens (max over ranks)
+`--impl reference` runs the reference engine installed under baseline/_ref on the
+same workload through its own API.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960,
+                tie_word_embeddings=False, eos_token_id=151645, torch_dtype="bfloat16", hidden_act="silu",
+                attention_bias=False, bos_token_id=151643)
+
+WORKLOADS = {
+    # name: (hf config, requests, prompt tokens, output tokens)
+    "qwen3-8b": (QWEN3_8B, 128, 4096, 512),
+    # shrunken variant for quick functional checks; never reported as the headline
+    "qwen3-8b-small": (dict(QWEN3_8B, num_hidden_layers=4), 16, 1024, 32),
+}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = int(vis.split(",")[self.index]) if vis else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                     "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                     "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                     "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = get(h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+                self._stop_evt.wait(self.period)
+        except Exception as exc:                       # NVML missing: report that instead of numbers
+            self.reasons.add(f"nvml_unavailable:{type(exc).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world <= 1:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def prompts_for(n, length, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(1000, vocab - 1000, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def percentile(xs, q):
+    xs = sorted(xs)
+    if not xs:
+        return None
+    i = min(len(xs) - 1, max(0, int(round(q * (len(xs) - 1)))))
+    return xs[i]
+
+
+# ----------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        if args.gpus == 1 and world == 1:
+            pass
+        else:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    from fastcache_b200 import LLM, SamplingParams, ops
+    from fastcache_b200.engine.model_runner import DeviceTimer
+    from fastcache_b200.parallel import tp as tpmod
+    if world > 1:
+        tpmod.init_tensor_parallel(world, rank)
+    hf, n_req, p_len, o_len = WORKLOADS[args.config]
+    n_req = args.requests or n_req
+    method = args.method
+    kv_params = {"window": 64, "kernel_size": 5} if method == "snapkv" else {}
+    llm = LLM(dict(hf), tensor_parallel_size=world, device=f"cuda:{local_rank}", kvcache_block_size=256,
+              max_model_len=p_len + o_len + 256, max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768,
+              gpu_memory_utilization=args.mem_util, enable_compression=not args.no_compression,
+              compression_backend="kvpress", kvpress_method=method, compression_factor=2,
+              compression_pipeline="prefill", kvpress_params=kv_params, seed=0, prefix_caching=False)
+    runner = llm.model_runner
+    sp = SamplingParams(temperature=0.0, max_tokens=o_len, ignore_eos=True)
+
+    # ---- warm-up wave (untimed): one prefill step then decode steps
+    wsp = SamplingParams(temperature=0.0, max_tokens=max(2, args.warmup), ignore_eos=True)
+    for p in prompts_for(2, 512, hf["vocab_size"], 7):
+        llm.add_request(p, wsp)
+    done = 0
+    while not llm.is_finished():
+        llm.step()
+        done += 1
+    while done < args.warmup:                     # W larger than the wave: repeat it
+        for p in prompts_for(2, 512, hf["vocab_size"], 7):
+            llm.add_request(p, wsp)
+        while not llm.is_finished():
+            llm.step()
+            done += 1
+
+    # ---- the job
+    prompts = prompts_for(n_req, p_len, hf["vocab_size"], 1)
+    seqs = [llm.add_request(p, sp) for p in prompts]
+    t_arrival = time.perf_counter()
+    for s in seqs:
+        s.arrival_time = t_arrival
+    runner.timer = DeviceTimer(runner.main_stream)
+    runner.io["h2d_bytes"] = runner.io["d2h_bytes"] = 0
+    ops.COUNTERS["launches"] = 0
+    out_tokens_before = sum(s.num_completion_tokens for s in seqs)
+    sampler = ClockSampler(local_rank)
+    barrier(world)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(runner.main_stream)
+    t0 = time.perf_counter()
+    steps = 0
+    limit = args.steps if args.steps > 0 else 1 << 30
+    wave = 1
+    while steps < limit:
+        if llm.is_finished():
+            if args.steps <= 0:
+                break
+            wave += 1                                # K exceeds the job: keep serving identical waves
+            more = [llm.add_request(p, sp) for p in prompts_for(n_req, p_len, hf["vocab_size"], wave)]
+            seqs.extend(more)
+        llm.step()
+        steps += 1
+    ev1.record(runner.main_stream)
+    barrier(world)
+    t1 = time.perf_counter()
+    clocks = sampler.stop()
+    e2e_ms = max(ev0.elapsed_time(ev1), 0.0)
+    wall_ms = (t1 - t0) * 1e3
+    dev_ms = runner.timer.total_ms()
+    runner.timer = None
+    out_tokens = sum(s.num_completion_tokens for s in seqs) - out_tokens_before
+    ttft = [s.first_token_time - s.arrival_time for s in seqs if s.first_token_time is not None]
+    status = ops.ext().read_status(local_rank)
+
+    dev_ms = max_over_ranks(dev_ms, world)
+    e2e_ms = max_over_ranks(max(e2e_ms, wall_ms), world)
+    if rank == 0:
+        base = None
+        value = out_tokens / (dev_ms / 1e3)
+        line = {
+            "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / max(1, steps), 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": base, "dtype": "bf16",
+            "data": "synthetic token ids, random-init weights",
+            "config": {"model": "Qwen3-8B shape (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)",
+                       "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
+                       "parallelism": f"tp{world}", "compression": f"{method} keep 50%" if not args.no_compression else "none",
+                       "cuda_graph_decode": True, "kv_block": 256,
+                       "l2": "working set per step (weights 16 GB + KV) far exceeds the 126 MB L2; no flush needed",
+                       "step": "one engine step (prefill batch incl. its compression, or decode batch)",
+                       "prefill_steps": llm.stats.prefill_steps, "decode_steps": llm.stats.decode_steps},
+            "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
+            "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
+            "output_tokens": out_tokens,
+            "e2e": {"value": round(out_tokens / (e2e_ms / 1e3), 2), "unit": "tok/s",
+                    "ms_total": round(e2e_ms, 2),
+                    "h2d_bytes_per_step": int(runner.io["h2d_bytes"] / max(1, steps)),
+                    "d2h_bytes_per_step": int(runner.io["d2h_bytes"] / max(1, steps))},
+            "gpu_launches": int(ops.COUNTERS["launches"]),
+            "clocks": clocks, "device_status": int(status), "impl": "fastcache_b200",
+        }
+        print(json.dumps(line), flush=True)
+    llm.exit()
+    if world > 1:
+        tpmod.cleanup_tensor_parallel()
+
+
+# ------------------------------------------------------------------ reference
+def unavailable(why: str):
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    sys.exit(0)
+
+
+def run_reference(args):
+    rank, local_rank, world = dist_env()
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "nanovllm", "engine")):
+        if rank == 0:
+            unavailable("reference is not installed under baseline/_ref (see DESIGN.md, reference install)")
+        sys.exit(0)
+    if world > 1:
+        if rank == 0:
+            unavailable("reference hard-codes tp_size = 1 in its Qwen3 attention (nanovllm/models/qwen3.py:36): "
+                        "it cannot run this model tensor-parallel")
+        sys.exit(0)
+    from baseline.reference_arm import run as ref_run
+    try:
+        line = ref_run(args, WORKLOADS[args.config], ClockSampler, prompts_for, percentile)
+    except SystemExit:
+        raise
+    except Exception as exc:                       # import/runtime failure of the reference itself
+        unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=0, help="engine steps to time (0 = the whole job)")
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="qwen3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--method", default="knorm", choices=["knorm", "snapkv", "knorm_ref", "streaming_llm"])
+    ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--no-compression", action="store_true")
+    ap.add_argument("--mem-util", type=float, default=0.85)
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

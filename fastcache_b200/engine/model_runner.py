@@ -53,6 +53,32 @@ def _resolve_dtype(config: Config, device: torch.device) -> torch.dtype:
             "float16": torch.float16, "fp32": torch.float32, "float32": torch.float32}[config.dtype]
 
 
+class DeviceTimer:
+    """Collects CUDA-event pairs around device work; `total_ms()` synchronises and sums them."""
+
+    def __init__(self, stream=None):
+        self.stream = stream
+        self.pairs: List[Tuple[Any, Any]] = []
+        self._open = None
+
+    def start(self, stream=None) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream or self.stream)
+        self._open = ev
+
+    def stop(self, stream=None) -> None:
+        if self._open is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream or self.stream)
+        self.pairs.append((self._open, ev))
+        self._open = None
+
+    def total_ms(self) -> float:
+        torch.cuda.synchronize()
+        return float(sum(a.elapsed_time(b) for a, b in self.pairs))
+
+
 class ModelRunner:
     def __init__(self, config: Config, compressor_path: Optional[str] = None, compression_factor: int = 5,
                  enable_compression: bool = False, async_compression: bool = False,
@@ -100,6 +126,9 @@ class ModelRunner:
         self.image_token_id = getattr(self.model, "image_token_id", None)
 
         self.sampler = Sampler(config.seed)
+        self.io = {"h2d_bytes": 0, "d2h_bytes": 0}      # host<->device traffic of the step loop
+        self.timer: Optional[DeviceTimer] = None        # set by benchmarks to time device work only
+        self.graph_launches: Dict[int, int] = {}
         self.allocate_kv_cache()
 
         # ------------------------------------------------------ compression
@@ -215,6 +244,7 @@ class ModelRunner:
     def _to_dev(self, arr: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
         t = torch.from_numpy(arr).to(dtype)
         if self.device.type == "cuda":
+            self.io["h2d_bytes"] += t.numel() * t.element_size()
             return t.pin_memory().to(self.device, non_blocking=True)
         return t
 
@@ -305,6 +335,8 @@ class ModelRunner:
         input_ids, positions, image_rows = self.prepare_prefill(seqs)
         from ..utils.context import get_context
         ctx = get_context()
+        if self.timer is not None:
+            self.timer.start(self.main_stream)
         logits = self._forward(input_ids, positions, seqs, image_rows)
         if ctx.window_q is not None:
             counts = ctx.window_q["counts"]
@@ -329,7 +361,10 @@ class ModelRunner:
                         context_lens=self._to_dev(lens, torch.int32),
                         block_tables=self._to_dev(bt, torch.int32),
                         attn_workspace=getattr(self, "attn_workspace", None))
-            return self._forward(self._to_dev(ids, torch.int64), self._to_dev(pos, torch.int64))
+            ids_d, pos_d = self._to_dev(ids, torch.int64), self._to_dev(pos, torch.int64)
+            if self.timer is not None:
+                self.timer.start(self.main_stream)
+            return self._forward(ids_d, pos_d)
         gv = self.graph_vars
         h = self._staging
         h["input_ids"][:n] = torch.from_numpy(ids)
@@ -342,9 +377,12 @@ class ModelRunner:
         h["context_lens"][n:bucket] = 0
         h["block_tables"][:bucket].fill_(0)
         h["block_tables"][:n, : bt.shape[1]] = torch.from_numpy(np.maximum(bt, 0))
-        for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
+        for k in ("input_ids", "positions", "slot_mapping", "context_lens", "block_tables"):
             gv[k][:bucket].copy_(h[k][:bucket], non_blocking=True)
-        gv["block_tables"][:bucket].copy_(h["block_tables"][:bucket], non_blocking=True)
+            if self.device.type == "cuda":
+                self.io["h2d_bytes"] += h[k][:bucket].numel() * h[k].element_size()
+        if self.timer is not None:
+            self.timer.start(self.main_stream)
         self._replay(bucket)
         return gv["logits"][:n]
 
@@ -354,6 +392,8 @@ class ModelRunner:
             self._decode_on_static(bucket)
         else:
             g.replay()
+            from .. import ops
+            ops.COUNTERS["launches"] += self.graph_launches.get(bucket, 0)
 
     def _decode_on_static(self, bucket: int) -> None:
         gv = self.graph_vars
@@ -393,8 +433,11 @@ class ModelRunner:
                 self._decode_on_static(b)            # warm-up (allocations, lazy init)
                 stream.synchronize()
                 g = torch.cuda.CUDAGraph()
+                from .. import ops
+                before = ops.COUNTERS["launches"]
                 with torch.cuda.graph(g, pool=self.graph_pool, stream=stream):
                     self._decode_on_static(b)
+                self.graph_launches[b] = ops.COUNTERS["launches"] - before
                 if self.graph_pool is None:
                     self.graph_pool = g.pool()
                 self.graphs[b] = g
@@ -410,8 +453,12 @@ class ModelRunner:
         cm = torch.cuda.stream(self.main_stream) if self.main_stream is not None else _Null()
         with cm:
             logits = self.run_prefill(seqs) if is_prefill else self.run_decode(seqs)
-            tokens = self.sampler(logits, self._temperatures(seqs))
+            temps = self._temperatures(seqs)
+            tokens = self.sampler(logits, temps)
+            if self.timer is not None:
+                self.timer.stop(self.main_stream)
             out = tokens.tolist()
+            self.io["d2h_bytes"] += 8 * len(out)
         reset_context()
         return out
 
@@ -443,6 +490,9 @@ class ModelRunner:
         tables = [s.block_table for s in seqs]
         lens = [s.kv_cache_len for s in seqs]
         cm = torch.cuda.stream(stream) if stream is not None else _Null()
+        timed = self.timer is not None and (stream is None or stream is self.main_stream)
+        if timed:
+            self.timer.start(stream)
         with cm:
             if self.compression_backend == "mlp":
                 if self.packed_compressor is None:
@@ -458,6 +508,8 @@ class ModelRunner:
                     wq = [self._window_q.get(s.seq_id) for s in seqs]
                 new = evict_in_pool(self.kv_cache, tables, lens, self.kvpress_method, kept, wq,
                                     self.kvpress_params)
+        if timed:
+            self.timer.stop(stream)
         full = (layer_start == 0 and (layer_end is None or layer_end >= self.num_hidden_layers))
         for s, n in zip(seqs, new):
             if full or (layer_end is not None and layer_end >= self.num_hidden_layers):

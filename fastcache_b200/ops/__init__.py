@@ -4,6 +4,9 @@ Each function runs the hand-written sm_100a kernel when its tensors live on a
 CUDA device and the PyTorch statement in `reference.py` otherwise.  There is
 no backend registry: the device of the data decides, and a CUDA tensor without
 the compiled extension is an error, never a silent fallback.
+
+`COUNTERS["launches"]` counts kernels of this package launched from Python
+(the model runner adds the kernels inside CUDA graphs per replay).
 """
 from __future__ import annotations
 
@@ -14,45 +17,48 @@ import torch
 from . import reference as ref
 from .loader import ext, ext_available  # noqa: F401
 
+COUNTERS = {"launches": 0}
 
-def _cuda(t: torch.Tensor) -> bool:
-    return t.is_cuda
+
+def _n(k: int = 1) -> None:
+    COUNTERS["launches"] += k
 
 
 def rms_norm(x, weight, eps):
-    if _cuda(x):
+    if x.is_cuda:
+        _n()
         return ext().rms_norm(x, weight, float(eps))
     return ref.rms_norm(x, weight, eps)
 
 
 def add_rms_norm(x, residual, weight, eps) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns (normed, new_residual).  On CUDA `residual` is updated in place."""
-    if _cuda(x):
+    if x.is_cuda:
+        _n()
         y = ext().add_rms_norm(x, residual, weight, float(eps))
         return y, residual
     return ref.add_rms_norm(x, residual, weight, eps)
 
 
 def layer_norm(x, weight, bias, eps):
-    if _cuda(x):
-        return ext().layer_norm(x, weight, bias, float(eps))
+    if x.is_cuda:
+        _n()
+        return ext().layer_norm(x.contiguous(), weight, bias, float(eps))
     return ref.layer_norm(x, weight, bias, eps)
 
 
 def silu_and_mul(x):
-    if _cuda(x):
+    if x.is_cuda:
+        _n()
         return ext().silu_and_mul(x)
     return ref.silu_and_mul(x)
 
 
 def linear(x, weight, bias=None, act: str = "none", out: Optional[torch.Tensor] = None):
-    """y = act(x @ weight.T + bias).  weight is [N, K] as in nn.Linear.
-
-    act "swiglu" expects weight rows interleaved per 64-column group by
-    `interleave_gate_up` and returns N/2 columns.
-    """
-    if _cuda(x):
+    """y = act(x @ weight.T + bias).  weight is [N, K] as in nn.Linear."""
+    if x.is_cuda:
         from .gemm import gemm
+        _n(2 if act == "swiglu" else 1)
         return gemm(x, weight, bias, act, out)
     y = ref.linear(x, weight, bias, act)
     if out is not None:
@@ -63,7 +69,8 @@ def linear(x, weight, bias=None, act: str = "none", out: Optional[torch.Tensor] 
 
 def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
                       q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping):
-    if _cuda(qkv):
+    if qkv.is_cuda:
+        _n()
         return ext().rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
                                        q_norm_weight, k_norm_weight, float(eps), k_cache, v_cache,
                                        slot_mapping)
@@ -73,32 +80,37 @@ def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_d
 
 def prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
                       max_q_len: int = 0):
-    if _cuda(q):
+    if q.is_cuda:
+        _n()
         return ext().prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens,
                                        float(scale), int(max_q_len))
     return ref.prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale)
 
 
 def decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale, workspace=None):
-    if _cuda(q):
+    if q.is_cuda:
         from .attention import decode_attention as _dec
+        _n()
         return _dec(q, k_cache, v_cache, block_tables, context_lens, scale, workspace)
     return ref.decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
 
 
 def dense_attention(q, k, v, scale, key_mask=None):
-    if _cuda(q):
-        return ext().dense_attention(q, k, v, float(scale), key_mask)
+    if q.is_cuda:
+        _n()
+        return ext().dense_attention(q.contiguous(), k.contiguous(), v.contiguous(), float(scale), key_mask)
     return ref.dense_attention(q, k, v, scale, key_mask)
 
 
 def embedding(ids, weight, vocab_start: int = 0):
-    if _cuda(weight):
+    if weight.is_cuda:
+        _n()
         return ext().embedding(ids, weight, int(vocab_start))
     return ref.embedding(ids, weight, vocab_start)
 
 
 def sample(logits, temperatures, noise=None, seed: int = 0):
-    if _cuda(logits) and noise is None:
-        return ext().sample(logits, temperatures, int(seed))
+    if logits.is_cuda and noise is None:
+        _n()
+        return ext().sample(logits, temperatures, int(seed) & 0x7FFFFFFF)
     return ref.sample(logits, temperatures, noise)
