@@ -267,6 +267,8 @@ def run_reference(args):
     except SystemExit:
         raise
     except Exception as exc:                       # import/runtime failure of the reference itself
+        import traceback
+        traceback.print_exc()
         unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
     print(json.dumps(line), flush=True)
 

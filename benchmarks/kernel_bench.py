@@ -73,8 +73,8 @@ def bench_decode_attn(rows):
         D = 128
         nb_per = -(-ctx // bs)
         nb = B * nb_per
-        kc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
-        vc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        kc = torch.randn(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
         bt = torch.randperm(nb, device="cuda").int().view(B, nb_per)
         cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
         q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
@@ -92,8 +92,8 @@ def bench_prefill_attn(rows):
         D, bs = 128, 256
         nb_per = -(-S // bs)
         nb = nseq * nb_per
-        kc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
-        vc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        kc = torch.randn(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
         bt = torch.arange(nb, device="cuda").int().view(nseq, nb_per)
         q = torch.randn(nseq * S, Hq, D, device="cuda", dtype=torch.bfloat16)
         cu = (torch.arange(nseq + 1, device="cuda") * S).int()

@@ -8,7 +8,8 @@ eviction read rows through the block table and write the shorter result into
 the *leading rows of the same blocks*, so the tail blocks can be freed; no
 intermediate per-request tensors exist on the GPU path.
 
-Pool layout: `[L, 2, num_blocks, block_size, Hkv, D]` (index 1: 0 = K, 1 = V).
+Pool layout: `[L, 2, num_blocks, Hkv, block_size, D]` (index 1: 0 = K, 1 = V); inside a block
+the rows of one head are contiguous.
 
 In-place safety: every output row index is <= the index of each input row it
 depends on.  The CUDA kernels give each (request, head, layer, K|V) to one
@@ -27,17 +28,15 @@ from .scorers import NEEDS_QUERIES, SHARED_INDICES, score_keys, select_keep
 
 def _rows(pool_lkv: torch.Tensor, block_ids: torch.Tensor, n: int) -> torch.Tensor:
     """[n, Hkv, D] rows of one (layer, K|V) slice of the pool."""
-    nb = -(-n // pool_lkv.shape[1])
-    return pool_lkv[block_ids[:nb]].reshape(-1, pool_lkv.shape[2], pool_lkv.shape[3])[:n]
+    nb = -(-n // pool_lkv.shape[2])
+    return pool_lkv[block_ids[:nb]].permute(0, 2, 1, 3).reshape(-1, pool_lkv.shape[1], pool_lkv.shape[3])[:n]
 
 
 def _write_rows(pool_lkv: torch.Tensor, block_ids: torch.Tensor, rows: torch.Tensor) -> None:
     n = rows.shape[0]
-    bs = pool_lkv.shape[1]
-    nb = -(-n // bs)
-    flat = pool_lkv.view(-1, pool_lkv.shape[2], pool_lkv.shape[3])
-    idx = (block_ids[:nb, None] * bs + torch.arange(bs, device=rows.device)[None, :]).reshape(-1)[:n]
-    flat[idx] = rows.to(flat.dtype)
+    bs = pool_lkv.shape[2]
+    r = torch.arange(n, device=rows.device)
+    pool_lkv[block_ids[r // bs], :, r % bs] = rows.to(pool_lkv.dtype)
 
 
 # ----------------------------------------------------------------- CCM merge

@@ -1,8 +1,12 @@
 // Paged decode attention: one query row per request over its (possibly compressed) K/V in the pool.
 //
 // Grid (request, kv head, kv split).  A CTA streams 64-row K and V tiles of its
-// kv head through a 3-stage cp.async ring (16-byte copies, XOR-swizzled rows,
-// zero fill past the context), gathering rows through the block table.  The G =
+// kv head through a 3-stage ring filled by TMA (cp.async.bulk.tensor 2-D boxes with
+// the 128-byte swizzle, completion on an mbarrier): the pool is head-major inside a
+// block, so the rows of one head are a dense [rows, D] matrix and one elected thread
+// moves a whole tile with a handful of instructions.  Boxes never straddle a pool
+// block (box rows = min(64, block_size)); boxes wholly past the context are skipped
+// and rows past it are masked.  The G =
 // Hq / Hkv query heads that share the kv head form the 16-row A operand of
 // mma.sync.m16n8k16 (rows >= G are zero); each of the 4 warps owns 16 of the 64
 // rows of a tile and keeps its own running (max, sum, O[16 x D]).  The warps are
@@ -21,6 +25,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "gemm.h"
 #include "kernels.h"
 #include "mma.cuh"
 #include "ptx.cuh"
@@ -33,18 +38,33 @@ constexpr int DEC_TILE = 64;      // kv rows per stage
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_THREADS = 128;
 
+// byte offset of 16-byte chunk `chunk` of row `row` inside a TMA-swizzled tile:
+// sub-tiles of [64 rows x 128 bytes], chunk index XOR (row mod 8) inside the 128-byte row
+__device__ __forceinline__ uint32_t tswz(int row, int chunk) {
+  return uint32_t((chunk >> 3) * (DEC_TILE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS)
-decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                   const int* __restrict__ block_tables, const int* __restrict__ context_lens,
+decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const bf16* __restrict__ q, int box_rows, const int* __restrict__ block_tables, const int* __restrict__ context_lens,
                    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_lse, int Hq,
                    int Hkv, int block_size, int max_blocks, int num_blocks, int splits, float scale_log2,
                    uint32_t* status) {
   constexpr int CH = D / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
-  // stage s: K tile at s * 2 * TILE_BYTES, V tile right after
+  // stage s: K tile at s * 2 * TILE_BYTES, V tile right after; a tile is D/64 sub-tiles of [64 rows x 128 B]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + DEC_STAGES * 2 * TILE_BYTES);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(&full_bar[s], 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  __syncthreads();
 
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
@@ -73,28 +93,32 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
     }
   }
 
+  // one thread: TMA boxes of tile `tile` into `stage`
   auto load_tile = [&](int tile, int stage) {
-    const uint32_t sk = s_base + stage * 2 * TILE_BYTES;
-    const uint32_t sv = sk + TILE_BYTES;
+    uint8_t* sk = smem + stage * 2 * TILE_BYTES;
+    uint8_t* sv = sk + TILE_BYTES;
     const int row0 = tile * DEC_TILE;
-#pragma unroll
-    for (int i = 0; i < (DEC_TILE * CH) / DEC_THREADS; ++i) {
-      const int c = threadIdx.x + i * DEC_THREADS;
-      const int r = c / CH, ch = c % CH;
-      const int tok = row0 + r;
-      bool valid = tok < ctx;
-      long long off = 0;
-      if (valid) {
-        const int blk = bt[tok / block_size];
-        if (blk < 0 || blk >= num_blocks) {
-          report(status, ST_BAD_INDEX);
-          valid = false;
-        } else {
-          off = (((long long)blk * block_size + tok % block_size) * Hkv + hk) * D + ch * 8;
-        }
+    const int pieces = DEC_TILE / box_rows;
+    constexpr int SUBS = D / 64;
+    uint32_t bytes = 0;
+    for (int pc = 0; pc < pieces; ++pc)
+      if (row0 + pc * box_rows < ctx) bytes += uint32_t(2 * SUBS * box_rows * 128);
+    mbar_expect_tx(&full_bar[stage], bytes);
+    for (int pc = 0; pc < pieces; ++pc) {
+      const int tok = row0 + pc * box_rows;
+      if (tok >= ctx) break;
+      int blk = bt[tok / block_size];
+      if (blk < 0 || blk >= num_blocks) {
+        report(status, ST_BAD_INDEX);
+        blk = 0;                          // keep the byte count consistent; the rows are garbage either way
       }
-      cp_async16(sk + swz<D>(r, ch), k_cache + off, valid);
-      cp_async16(sv + swz<D>(r, ch), v_cache + off, valid);
+      const int grow = (blk * Hkv + hk) * block_size + tok % block_size;
+#pragma unroll
+      for (int sub = 0; sub < SUBS; ++sub) {
+        const int soff = sub * (DEC_TILE * 128) + pc * box_rows * 128;
+        tma_load_2d(sk + soff, &tm_k, &full_bar[stage], sub * 64, grow);
+        tma_load_2d(sv + soff, &tm_v, &full_bar[stage], sub * 64, grow);
+      }
     }
   };
 
@@ -103,21 +127,27 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-#pragma unroll
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(tile0 + s, s);
-    cp_async_commit();
-  }
-
-  for (int it = 0; it < n_tiles; ++it) {
-    cp_async_wait<DEC_STAGES - 2>();
-    __syncthreads();
-    {   // prefetch tile it + STAGES - 1 into the stage that was consumed in the previous iteration
-      const int nxt = it + DEC_STAGES - 1;
-      if (nxt < n_tiles) load_tile(tile0 + nxt, nxt % DEC_STAGES);
-      cp_async_commit();
+  if (n_tiles <= DEC_STAGES) {
+    // Boxes past the context are never loaded.  In a short run their shared memory has not been
+    // written at all, and 0 * (uninitialised V) could be NaN, so clear the V tiles once.
+    for (int s = 0; s < n_tiles; ++s) {
+      uint4* v = reinterpret_cast<uint4*>(smem + s * 2 * TILE_BYTES + TILE_BYTES);
+      for (int i = threadIdx.x; i < TILE_BYTES / 16; i += DEC_THREADS) v[i] = make_uint4(0, 0, 0, 0);
     }
+    fence_proxy_async();
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s)
+      if (s < n_tiles) load_tile(tile0 + s, s);
+  }
+  bool alive = true;
+  for (int it = 0; it < n_tiles; ++it) {
     const int stage = it % DEC_STAGES;
+    if (!mbar_wait(&full_bar[stage], (it / DEC_STAGES) & 1, status, ST_TIMEOUT_FULL)) {
+      alive = false;
+      break;
+    }
     const uint32_t sk = s_base + stage * 2 * TILE_BYTES;
     const uint32_t sv = sk + TILE_BYTES;
     const int wrow = warp * 16;                         // this warp's 16 rows of the tile
@@ -133,7 +163,7 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
       const int r = wrow + (mat >> 1) * 8 + (lane & 7);
       const int ch = kk * 2 + (mat & 1);
       uint32_t b0, b1, b2, b3;
-      ldsm_x4(sk + swz<D>(r, ch), b0, b1, b2, b3);
+      ldsm_x4(sk + tswz(r, ch), b0, b1, b2, b3);
       mma_bf16(sc[0], qa[kk], b0, b1);
       mma_bf16(sc[1], qa[kk], b2, b3);
     }
@@ -198,13 +228,14 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
       const int r = wrow + (mat & 1) * 8 + (lane & 7);
       const int ch = jp * 2 + (mat >> 1);
       uint32_t b0, b1, b2, b3;
-      ldsm_x4_t(sv + swz<D>(r, ch), b0, b1, b2, b3);
+      ldsm_x4_t(sv + tswz(r, ch), b0, b1, b2, b3);
       mma_bf16(o[2 * jp], pa, b0, b1);
       mma_bf16(o[2 * jp + 1], pa, b2, b3);
     }
+    __syncthreads();                       // every warp is done with this stage
+    if (threadIdx.x == 0 && it + DEC_STAGES < n_tiles) load_tile(tile0 + it + DEC_STAGES, stage);
   }
-  cp_async_wait<0>();
-  __syncthreads();
+  if (__syncthreads_or(!alive)) return;    // a TMA never landed: status is set, nothing is written
 
   // ---- merge the four warps (each saw a different quarter of every tile)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -295,18 +326,24 @@ void launch_decode_attention(const void* q, const void* k_cache, const void* v_c
   if (Hq % Hkv != 0 || Hq / Hkv > 16) throw std::runtime_error("decode attention: group size must divide and be <= 16");
   if (splits > 1 && (part_o == nullptr || part_lse == nullptr))
     throw std::runtime_error("decode attention: split-KV needs scratch");
+  int box_rows = DEC_TILE;
+  while (box_rows > block_size || block_size % box_rows != 0) box_rows >>= 1;
+  if (box_rows < 8) throw std::runtime_error("decode attention: block_size must be a multiple of 8");
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(B, Hkv, splits);
-  const int smem = DEC_STAGES * 2 * DEC_TILE * D * 2;
+  const int smem = DEC_STAGES * 2 * DEC_TILE * D * 2 + 64 + 1024;
+  const uint64_t rows = (uint64_t)num_blocks * Hkv * block_size;
+  const CUtensorMap tk = make_tmap_bf16_2d(k_cache, rows, D, D, box_rows, 64);
+  const CUtensorMap tv = make_tmap_bf16_2d(v_cache, rows, D, D, box_rows, 64);
   auto launch = [&](auto kern) {
     static bool configured = false;
     if (!configured) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       configured = true;
     }
-    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                              block_tables, context_lens, (bf16*)out, part_o, part_lse, Hq, Hkv,
-                                              block_size, max_blocks, num_blocks, splits, scale_log2, status);
+    kern<<<grid, DEC_THREADS, smem, stream>>>(tk, tv, (const bf16*)q, box_rows, block_tables, context_lens,
+                                              (bf16*)out, part_o, part_lse, Hq, Hkv, block_size, max_blocks,
+                                              num_blocks, splits, scale_log2, status);
   };
   if (D == 128) launch(decode_attn_kernel<128>);
   else if (D == 64) launch(decode_attn_kernel<64>);

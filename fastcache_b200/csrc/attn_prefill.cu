@@ -82,7 +82,7 @@ prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
           report(status, ST_BAD_INDEX);
           valid = false;
         } else {
-          off = (((long long)blk * block_size + tok % block_size) * Hkv + hk) * D + ch * 8;
+          off = (((long long)blk * Hkv + hk) * block_size + tok % block_size) * D + ch * 8;
         }
       }
       cp_async16(sk + swz<D>(r, ch), k_cache + off, valid);

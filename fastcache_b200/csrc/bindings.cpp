@@ -166,23 +166,25 @@ Tensor rope_qknorm_store(const Tensor& qkv, const Tensor& positions, const Tenso
   Tensor q_out = torch::empty({T, Hq, D}, qkv.options());
   const void *qw = nullptr, *kw = nullptr, *sl = nullptr;
   void *kc = nullptr, *vc = nullptr;
-  int64_t num_slots = 0;
+  int64_t num_slots = 0, block_size = 1;
   if (q_w.has_value() && q_w->defined()) { check_bf16(*q_w, "q_norm"); qw = q_w->data_ptr(); }
   if (k_w.has_value() && k_w->defined()) { check_bf16(*k_w, "k_norm"); kw = k_w->data_ptr(); }
   if (k_cache.has_value() && k_cache->defined() && slots.has_value() && slots->defined()) {
     check_bf16(*k_cache, "k_cache");
     check_bf16(*v_cache, "v_cache");
     TORCH_CHECK(k_cache->is_contiguous() && v_cache->is_contiguous(), "cache slices must be contiguous");
-    TORCH_CHECK(k_cache->size(-1) == D && k_cache->size(-2) == Hkv, "cache layout must be [blocks, block, Hkv, D]");
+    TORCH_CHECK(k_cache->dim() == 4 && k_cache->size(3) == D && k_cache->size(1) == Hkv,
+                "cache layout must be [blocks, Hkv, block, D]");
     TORCH_CHECK(slots->scalar_type() == torch::kInt32 && slots->numel() == T && slots->is_cuda(),
                 "slot_mapping must be int32 [T]");
     kc = k_cache->data_ptr();
     vc = v_cache->data_ptr();
     sl = slots->data_ptr();
-    num_slots = k_cache->size(0) * k_cache->size(1);
+    num_slots = k_cache->size(0) * k_cache->size(2);
+    block_size = k_cache->size(2);
   }
   fc::launch_rope_qknorm_store(qkv.data_ptr(), positions.data_ptr(), cos_sin.data_ptr(), qw, kw, q_out.data_ptr(),
-                               kc, vc, sl, int(T), int(Hq), int(Hkv), int(D), float(eps), num_slots,
+                               kc, vc, sl, int(T), int(Hq), int(Hkv), int(D), float(eps), num_slots, int(block_size),
                                status_ptr(qkv.get_device()), at::cuda::getCurrentCUDAStream());
   return q_out;
 }
@@ -191,7 +193,7 @@ void check_cache(const Tensor& kc, const Tensor& vc, int64_t D) {
   check_bf16(kc, "k_cache");
   check_bf16(vc, "v_cache");
   TORCH_CHECK(kc.dim() == 4 && kc.is_contiguous() && vc.is_contiguous() && kc.size(3) == D,
-              "cache layout must be contiguous [blocks, block, Hkv, D]");
+              "cache layout must be contiguous [blocks, Hkv, block, D]");
 }
 
 Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_tables,
@@ -210,7 +212,7 @@ Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, co
   Tensor out = torch::empty_like(q);
   fc::launch_prefill_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
                                cu_q.data_ptr<int>(), kv_lens.data_ptr<int>(), out.data_ptr(), int(B), int(max_q_len),
-                               int(Hq), int(kc.size(2)), int(D), int(kc.size(1)), int(block_tables.size(1)),
+                               int(Hq), int(kc.size(1)), int(D), int(kc.size(2)), int(block_tables.size(1)),
                                int(kc.size(0)), float(scale), status_ptr(q.get_device()),
                                at::cuda::getCurrentCUDAStream());
   return out;
@@ -223,19 +225,19 @@ Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, con
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous(), "q must be contiguous [B, Hq, D]");
   const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2);
   check_cache(kc, vc, D);
-  const int64_t Hkv = kc.size(2);
+  const int64_t Hkv = kc.size(1);
   TORCH_CHECK(block_tables.scalar_type() == torch::kInt32 && block_tables.dim() == 2 && block_tables.is_contiguous() &&
                   block_tables.size(0) >= B, "block_tables must be int32 [B, max_blocks]");
   TORCH_CHECK(context_lens.scalar_type() == torch::kInt32 && context_lens.numel() >= B, "context_lens must be int32 [B]");
   c10::cuda::CUDAGuard guard(q.device());
   auto& ws = workspace(q.get_device());
-  if (max_ctx <= 0) max_ctx = block_tables.size(1) * kc.size(1);
+  if (max_ctx <= 0) max_ctx = block_tables.size(1) * kc.size(2);
   if (splits <= 0) splits = fc::decode_attn_pick_splits(int(B), int(Hkv), int(max_ctx), fc::gemm_num_sms());
   while (splits > 1 && (B * Hq * splits * D > ATTN_WS_FLOATS || B * Hq * splits > ATTN_LSE_FLOATS)) --splits;
   Tensor out = torch::empty_like(q);
   fc::launch_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
                               context_lens.data_ptr<int>(), out.data_ptr(), ws.attn_o.data_ptr<float>(),
-                              ws.attn_lse.data_ptr<float>(), int(B), int(Hq), int(Hkv), int(D), int(kc.size(1)),
+                              ws.attn_lse.data_ptr<float>(), int(B), int(Hq), int(Hkv), int(D), int(kc.size(2)),
                               int(block_tables.size(1)), int(kc.size(0)), int(splits), float(scale),
                               status_ptr(q.get_device()), at::cuda::getCurrentCUDAStream());
   return out;

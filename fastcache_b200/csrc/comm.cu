@@ -1,0 +1,197 @@
+// Tensor-parallel communication fused with the residual add and RMSNorm.
+//
+// allreduce_add_rmsnorm (decode-size inputs, "one shot"): every rank holds a bf16
+// partial [T, H] in a symmetric buffer (the row-parallel GEMM wrote it there).
+// One kernel, one CTA per token row:
+//   1. flag exchange with the same CTA on every peer ("my partial is complete");
+//      the stores are st.release.sys to the peers' signal pads, the wait is a
+//      bounded ld.acquire.sys spin that reports ST_TIMEOUT_PEER instead of hanging
+//   2. sum of the row over all ranks, read either with plain peer loads in rank
+//      order (bit-identical on every rank) or with one multimem.ld_reduce per
+//      16 bytes through the NVSwitch multicast address
+//   3. + residual (updated in place), RMSNorm, normalised row written locally
+// The buffers are used in alternation (two per rank) and the per-CTA epoch lives
+// in device memory, so the kernel can be replayed from a CUDA graph: a rank can
+// only overwrite a buffer after it has passed the next flag exchange, which every
+// peer joins only after it finished reading that buffer.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "comm.h"
+#include "ptx.cuh"
+
+namespace fc {
+
+using bf16 = __nv_bfloat16;
+
+#ifndef FC_PEER_SPIN_LIMIT
+#define FC_PEER_SPIN_LIMIT (1u << 24)      // about a second of polling before giving up
+#endif
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// sum over all ranks bound to the multicast object, 8 bf16 at a time, fp32 accumulation in the switch
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]);
+  u.y = pack_bf16(f[2], f[3]);
+  u.z = pack_bf16(f[4], f[5]);
+  u.w = pack_bf16(f[6], f[7]);
+  return u;
+}
+
+// Exchange "arrived" flags between CTA `slot` of all ranks.  Returns false on timeout.
+__device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, uint32_t epoch, uint32_t* status) {
+  const int tid = threadIdx.x;
+  __shared__ int s_ok;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < peers.world) {
+    st_release_sys(peers.flags[tid] + (size_t)slot * COMM_MAX_WORLD + peers.rank, epoch);
+    const uint32_t* mine = peers.flags[peers.rank] + (size_t)slot * COMM_MAX_WORLD + tid;
+    bool got = false;
+    for (uint32_t i = 0; i < FC_PEER_SPIN_LIMIT; ++i) {
+      // epochs only grow; a peer that is already one exchange ahead is fine
+      if (int32_t(ld_acquire_sys(mine) - epoch) >= 0) {
+        got = true;
+        break;
+      }
+      __nanosleep(20);
+    }
+    if (!got) {
+      report(status, ST_TIMEOUT_PEER);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+constexpr int AR_THREADS = 256;
+constexpr int AR_MAX_CHUNKS = 4;      // H <= 256 * 4 * 8 = 8192
+
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(AR_THREADS)
+allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ mc_in, bf16* __restrict__ residual,
+                             const bf16* __restrict__ weight, bf16* __restrict__ out, int T, int H, float eps,
+                             uint32_t* __restrict__ epochs, uint32_t* status) {
+  __shared__ float red[32];
+  __shared__ uint32_t s_epoch;
+  const int slot = blockIdx.x;
+  if (threadIdx.x == 0) s_epoch = epochs[slot] + 1;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const bool ok = peer_barrier(peers, slot, epoch, status);
+  if (threadIdx.x == 0) epochs[slot] = epoch;
+  if (!ok) return;                       // the host reads the status word and raises
+
+  const int chunks = H >> 3;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const size_t base = (size_t)row * H;
+    float v[AR_MAX_CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < AR_MAX_CHUNKS; ++c) {
+      const int idx = threadIdx.x + c * AR_THREADS;
+      if (idx < chunks) {
+        const size_t off = base + (size_t)idx * 8;
+        float acc[8];
+        if (MULTIMEM) {
+          unpack8f(multimem_ld_reduce_bf16x8(mc_in + off), acc);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          for (int p = 0; p < peers.world; ++p) {
+            float f[8];
+            unpack8f(ld_peer_16(peers.data[buf][p] + off), f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          }
+        }
+        float r[8];
+        unpack8f(*reinterpret_cast<const uint4*>(residual + off), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += r[i];
+        const uint4 s = pack8f(acc);
+        *reinterpret_cast<uint4*>(residual + off) = s;
+        unpack8f(s, v[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < AR_THREADS / 32; ++w) tot += red[w];
+    __syncthreads();
+    const float inv = rsqrtf(tot / float(H) + eps);
+#pragma unroll
+    for (int c = 0; c < AR_MAX_CHUNKS; ++c) {
+      const int idx = threadIdx.x + c * AR_THREADS;
+      if (idx < chunks) {
+        float g[8], o[8];
+        unpack8f(*reinterpret_cast<const uint4*>(weight + (size_t)idx * 8), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __bfloat162float(__float2bfloat16(v[c][i] * inv)) * g[i];
+        *reinterpret_cast<uint4*>(out + base + (size_t)idx * 8) = pack8f(o);
+      }
+    }
+  }
+}
+
+void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* mc_in, void* residual,
+                                  const void* weight, void* out, int T, int H, float eps, uint32_t* epochs,
+                                  uint32_t* status, bool use_multimem, cudaStream_t stream) {
+  if (T == 0) return;
+  if (H % 8 != 0 || H > AR_THREADS * AR_MAX_CHUNKS * 8) throw std::runtime_error("allreduce: unsupported hidden size");
+  // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
+  const int grid = T < COMM_MAX_SLOTS ? T : COMM_MAX_SLOTS;
+  if (use_multimem && mc_in != nullptr)
+    allreduce_add_rmsnorm_kernel<true><<<grid, AR_THREADS, 0, stream>>>(
+        peers, buf, (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+  else
+    allreduce_add_rmsnorm_kernel<false><<<grid, AR_THREADS, 0, stream>>>(
+        peers, buf, nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("allreduce launch: ") + cudaGetErrorString(e));
+}
+
+}  // namespace fc

@@ -10,7 +10,7 @@ using torch::Tensor;
 
 void check_pool(const Tensor& pool) {
   TORCH_CHECK(pool.is_cuda() && pool.scalar_type() == torch::kBFloat16 && pool.dim() == 6 && pool.is_contiguous() &&
-                  pool.size(1) == 2, "pool must be contiguous bf16 [L, 2, blocks, block, Hkv, D]");
+                  pool.size(1) == 2, "pool must be contiguous bf16 [L, 2, blocks, Hkv, block, D]");
 }
 void check_i32(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be int32 CUDA");
@@ -22,12 +22,12 @@ Tensor knorm_scores(const Tensor& pool, const Tensor& block_tables, const Tensor
   check_pool(pool);
   check_i32(block_tables, "block_tables");
   check_i32(kv_lens, "kv_lens");
-  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(4);
+  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(3);
   const int64_t stride = (max_len + 3) / 4 * 4;
   c10::cuda::CUDAGuard guard(pool.device());
   Tensor scores = torch::empty({n, L, Hkv, stride}, pool.options().dtype(torch::kFloat32));
   fc::launch_knorm_scores(pool.data_ptr(), block_tables.data_ptr<int>(), kv_lens.data_ptr<int>(),
-                          scores.data_ptr<float>(), int(n), int(L), int(pool.size(2)), int(pool.size(3)), int(Hkv),
+                          scores.data_ptr<float>(), int(n), int(L), int(pool.size(2)), int(pool.size(4)), int(Hkv),
                           int(pool.size(5)), int(block_tables.size(1)), int(max_len), int(stride), int(mode),
                           reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
   return scores;
@@ -41,12 +41,12 @@ void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_table
   check_i32(n_kepts, "n_kepts");
   TORCH_CHECK(scores.is_cuda() && scores.scalar_type() == torch::kFloat32 && scores.dim() == 4 &&
                   scores.is_contiguous(), "scores must be contiguous fp32 [n_seq, L, Hkv, stride]");
-  TORCH_CHECK(scores.size(0) == kv_lens.numel() && scores.size(1) == pool.size(0) && scores.size(2) == pool.size(4),
+  TORCH_CHECK(scores.size(0) == kv_lens.numel() && scores.size(1) == pool.size(0) && scores.size(2) == pool.size(3),
               "scores do not match the pool / batch");
   c10::cuda::CUDAGuard guard(pool.device());
   fc::launch_select_compact(pool.data_ptr(), scores.data_ptr<float>(), block_tables.data_ptr<int>(),
                             kv_lens.data_ptr<int>(), n_kepts.data_ptr<int>(), int(kv_lens.numel()),
-                            int(pool.size(0)), int(pool.size(2)), int(pool.size(3)), int(pool.size(4)),
+                            int(pool.size(0)), int(pool.size(2)), int(pool.size(4)), int(pool.size(3)),
                             int(pool.size(5)), int(block_tables.size(1)), int(scores.size(3)),
                             reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
 }

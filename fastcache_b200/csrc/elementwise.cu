@@ -188,7 +188,7 @@ rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restri
                          const float* __restrict__ cos_sin, const bf16* __restrict__ q_w,
                          const bf16* __restrict__ k_w, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
                          bf16* __restrict__ v_cache, const int* __restrict__ slots, int T, int Hq, int Hkv,
-                         int D, float eps, long long num_slots, uint32_t* status) {
+                         int D, float eps, long long num_slots, int block_size, uint32_t* status) {
   const int heads = Hq + 2 * Hkv;
   const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -207,7 +207,7 @@ rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restri
   }
   if (h >= Hq + Hkv) {            // value head: plain copy into the pool
     if (slot < 0) return;
-    bf16* dst = v_cache + (slot * Hkv + (h - Hq - Hkv)) * D;
+    bf16* dst = v_cache + (((slot / block_size) * Hkv + (h - Hq - Hkv)) * block_size + slot % block_size) * D;
     for (int i = lane; i < (D >> 3); i += 32)
       reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
     return;
@@ -242,7 +242,7 @@ rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restri
     }
   }
   const float* cs = cos_sin + positions[t] * D;
-  bf16* dst = is_q ? (q_out + ((long long)t * Hq + h) * D) : (k_cache + (slot * Hkv + (h - Hq)) * D);
+  bf16* dst = is_q ? (q_out + ((long long)t * Hq + h) * D) : (k_cache + (((slot / block_size) * Hkv + (h - Hq)) * block_size + slot % block_size) * D);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int p = lane + 32 * j;
@@ -353,14 +353,15 @@ void launch_embedding(const void* ids, const void* weight, void* out, int T, int
 
 void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
                               const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
-                              int Hq, int Hkv, int D, float eps, long long num_slots, uint32_t* status,
-                              cudaStream_t s) {
+                              int Hq, int Hkv, int D, float eps, long long num_slots, int block_size,
+                              uint32_t* status, cudaStream_t s) {
   if (T == 0) return;
   const long long warps = (long long)T * (Hq + 2 * Hkv);
   const long long blocks = (warps + 3) / 4;
   rope_qknorm_store_kernel<<<(unsigned)blocks, 128, 0, s>>>(
       (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,
-      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, D, eps, num_slots, status);
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, D, eps, num_slots, block_size,
+      status);
 }
 
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,

@@ -1,7 +1,7 @@
 // KV eviction in the paged pool: key-norm scoring, per-head top-k selection and
 // stable in-place compaction.
 //
-// Pool layout [L, 2, num_blocks, block_size, Hkv, D] bf16.  Scores are fp32
+// Pool layout [L, 2, num_blocks, Hkv, block_size, D] bf16 (rows of one head contiguous in a block).  Scores are fp32
 // [n_seq, L, Hkv, s_stride], higher = keep (+inf = always keep).
 //
 // select_compact: one CTA per (kv head, layer, request).  The scores of the
@@ -47,13 +47,13 @@ knorm_score_kernel(const bf16* __restrict__ pool, const int* __restrict__ block_
     return;
   }
   const long long kbase = ((long long)layer * 2 + 0) * num_blocks;
-  const bf16* row = pool + (((kbase + blk) * block_size + tok % block_size) * Hkv) * D;
+  const bf16* row = pool + ((kbase + blk) * Hkv * block_size + tok % block_size) * D;
   float* out = scores + (((long long)seq * L + layer) * Hkv) * s_stride + tok;
   float mean = 0.f;
   for (int h = 0; h < Hkv; ++h) {
     float ss = 0.f;
     for (int i = lane; i < D / 2; i += 32) {
-      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(row + h * D)[i]);
+      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(row + (long long)h * block_size * D)[i]);
       ss += v.x * v.x + v.y * v.y;
     }
     const float n = sqrtf(warp_sum(ss));
@@ -143,7 +143,7 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
       report(status, ST_BAD_INDEX);
       return nullptr;
     }
-    return pool + (((base + blk) * block_size + tok % block_size) * Hkv + h) * D;
+    return pool + (((base + blk) * Hkv + h) * block_size + tok % block_size) * D;
   };
 
   int out_base = 0;        // rows already written

@@ -470,42 +470,8 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
     }
     return;
   }
-  // swapped: weights are the 128-row operand, the token batch is the N operand
-  p.M = N;            // rows of the MMA = output features
-  p.N = M;            // columns of the MMA = tokens
-  p.ldc_i = 1;
-  p.ldc_j = ldc;
-  p.bias_on_i = 1;
-  p.num_m = (N + BM - 1) / BM;
-  p.num_n = 1;
-  p.group_m = 16;
-  const int tiles = p.num_m;
-  int splits = 1;
-  if (ws.scratch != nullptr && ws.counters != nullptr && tiles < sms) {
-    splits = std::min(std::min(sms / tiles, num_kb / 4), 16);
-    if (splits < 1) splits = 1;
-    if (tiles > GEMM_MAX_TILES_SPLIT || (long long)tiles * splits > GEMM_SCRATCH_TILES) splits = 1;
-  }
-  int kb_per = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kb_per - 1) / kb_per;      // no empty split
-  p.splits = splits;
-  p.kb_per_split = kb_per;
-  p.total_work = tiles * splits;
-  CUtensorMap ta = make_tmap_bf16_2d(w, N, K, ldw, BM, BK);
-  const int grid = std::min(p.total_work, sms);
-  if (M <= 32) {
-    CUtensorMap tb = make_tmap_bf16_2d(x, M, K, ldx, 32, BK);
-    launch_one<32, 8, true>(ta, tb, p, grid, stream);
-  } else if (M <= 64) {
-    CUtensorMap tb = make_tmap_bf16_2d(x, M, K, ldx, 64, BK);
-    launch_one<64, 8, true>(ta, tb, p, grid, stream);
-  } else if (M <= 128) {
-    CUtensorMap tb = make_tmap_bf16_2d(x, M, K, ldx, 128, BK);
-    launch_one<128, 6, true>(ta, tb, p, grid, stream);
-  } else {
-    CUtensorMap tb = make_tmap_bf16_2d(x, M, K, ldx, 256, BK);
-    launch_one<256, 4, true>(ta, tb, p, grid, stream);
-  }
+  // decode-size batch: weight-streaming kernel (gemm_skinny.cu)
+  gemm_skinny_bf16(x, w, c, bias, M, N, K, ldx, ldw, ldc, act, ws, sm_limit, 0, true, stream);
 }
 
 }  // namespace fc

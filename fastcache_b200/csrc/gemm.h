@@ -10,7 +10,7 @@ enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_TANH = 3, AC
 
 // Split-K needs scratch for fp32 partial tiles and one arrival counter per output
 // tile (zero before the first launch; the kernel leaves them zero).
-constexpr int GEMM_SCRATCH_TILES = 192;     // (tile, split) partials that fit the scratch
+constexpr int GEMM_SCRATCH_TILES = 512;     // (tile, split) partials that fit the scratch
 constexpr int GEMM_MAX_TILES_SPLIT = 4096;  // counters
 
 struct GemmWorkspace {
@@ -31,5 +31,11 @@ CUtensorMap make_tmap_bf16_2d(const void* base, uint64_t rows, uint64_t cols, ui
 // (used when the launching stream belongs to a green context with fewer SMs).
 void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit, cudaStream_t stream);
+
+// Decode-size batches (M <= 256).  Returns the number of K splits used; when that is > 1 and
+// `finalize` is false, ws.scratch holds fp32 partial sums [splits, M, N] for the caller to reduce.
+int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
+                     long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
+                     int splits_request, bool finalize, cudaStream_t stream);
 
 }  // namespace fc

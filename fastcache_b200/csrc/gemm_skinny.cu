@@ -1,0 +1,339 @@
+// Weight-streaming GEMM for decode-size batches (M <= 256 tokens): y[M, N] = x[M, K] @ W[N, K]^T.
+//
+// At these sizes the op is bound by reading W from HBM once.  The weight matrix is
+// therefore the 128-row tcgen05 operand ("swapped" form) and the token batch is the
+// N operand, so one CTA covers *all* tokens for its rows of W and W is never read
+// twice.  A CTA owns 256 rows of W (two M = 128 MMAs that share one x tile in shared
+// memory, which halves the re-reads of x from L2) and a slice of K:
+//
+//   grid = (N / 256 tiles) x (K splits), chosen so the CTA count is close to a
+//   multiple of the SM count
+//   warp 0: TMA producer (W tile 256 x 64 and x tile BN x 64 per stage, 128-byte swizzle)
+//   warp 1: tcgen05.mma issuer, accumulators in TMEM (2 x BN fp32 columns)
+//   warps 2-5: epilogue, tcgen05.ld -> transposed store
+//
+// With one split the epilogue writes bf16 (bias and activation applied).  With
+// several it writes fp32 partial sums [split, M, N] to scratch; the partials are
+// summed by the consumer (add + RMSNorm, see elementwise.cu) or by the small
+// finalize kernel below.  No inter-CTA synchronisation is needed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+#include "gemm.h"
+#include "ptx.cuh"
+
+namespace fc {
+
+constexpr int SK_BM = 256;       // rows of W per CTA
+constexpr int SK_BK = 64;
+constexpr int SK_THREADS = 192;
+
+struct SkinnyParams {
+  int Nw;                 // rows of W (output features)
+  int Mtok;               // tokens
+  int K;
+  __nv_bfloat16* out;     // [Mtok, ldc] bf16 (splits == 1)
+  long long ldc;
+  float* partial;         // [splits, Mtok, Nw] fp32 (splits > 1)
+  const __nv_bfloat16* bias;
+  int act;
+  int splits;
+  int kb_per_split;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ float sk_act(float v, int act) {
+  switch (act) {
+    case ACT_RELU: return fmaxf(v, 0.f);
+    case ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    case ACT_GELU_TANH: {
+      float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+      return 0.5f * v * (1.f + tanhf(u));
+    }
+    case ACT_QUICK_GELU: return v / (1.f + __expf(-1.702f * v));
+    case ACT_SILU: return v / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+
+template <int BN, int STAGES>
+struct SkinnySmem {
+  static constexpr int A_BYTES = SK_BM * SK_BK * 2;
+  static constexpr int B_BYTES = BN * SK_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
+                   const SkinnyParams p) {
+  using L = SkinnySmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int num_kb = (p.K + SK_BK - 1) / SK_BK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(num_kb, kb0 + p.kb_per_split);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *s_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_w);
+    tma_prefetch_desc(&tma_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (*s_abort || !mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) {
+          *s_abort = 1;
+          ok = false;
+          break;
+        }
+        uint8_t* sa = smem + stage * L::STAGE_BYTES;
+        uint8_t* sb = sa + L::A_BYTES;
+        mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+        tma_load_2d(sa, &tma_w, &full_bar[stage], kb * SK_BK, tile * SK_BM);
+        tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[stage], kb * SK_BK, tile * SK_BM + 128);
+        tma_load_2d(sb, &tma_x, &full_bar[stage], kb * SK_BK, 0);
+        ++issued;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        int s = stage;
+        uint32_t ph = phase;
+        for (int n = 0; n < min(issued, STAGES); ++n) {
+          if (--s < 0) {
+            s = STAGES - 1;
+            ph ^= 1;
+          }
+          mbar_wait(&full_bar[s], ph, nullptr, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (*s_abort || !mbar_wait(&full_bar[stage], phase, p.status, ST_TIMEOUT_FULL)) {
+          *s_abort = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+        const uint64_t da0 = make_sdesc_sw128(sa);
+        const uint64_t da1 = make_sdesc_sw128(sa + L::A_BYTES / 2);
+        const uint64_t db = make_sdesc_sw128(sa + L::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < SK_BK / 16; ++k) {
+          const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+          tc_mma_f16(tmem_base, da0 + uint64_t(2 * k), db + uint64_t(2 * k), idesc, accum);
+          tc_mma_f16(tmem_base + BN, da1 + uint64_t(2 * k), db + uint64_t(2 * k), idesc, accum);
+        }
+        tc_commit(&empty_bar[stage]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;
+    if (!*s_abort && mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int mt = 0; mt < 2; ++mt) {
+        const int n = tile * SK_BM + mt * 128 + row;          // output feature of this thread
+        const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(mt * BN);
+        const float bi = (p.bias != nullptr && n < p.Nw && p.splits == 1) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + uint32_t(c * 32), r);
+          tmem_ld_wait();
+          if (n < p.Nw) {
+            if (p.splits == 1) {
+#pragma unroll
+              for (int t = 0; t < 32; ++t) {
+                const int tok = c * 32 + t;
+                if (tok < p.Mtok)
+                  p.out[(long long)tok * p.ldc + n] = __float2bfloat16(sk_act(__uint_as_float(r[t]) + bi, p.act));
+              }
+            } else {
+              float* dst = p.partial + ((long long)split * p.Mtok) * p.Nw + n;
+#pragma unroll
+              for (int t = 0; t < 32; ++t) {
+                const int tok = c * 32 + t;
+                if (tok < p.Mtok) dst[(long long)tok * p.Nw] = __uint_as_float(r[t]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[m, n] = act(sum_s partial[s, m, n] + bias[n])
+__global__ void skinny_finalize_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias,
+                                       __nv_bfloat16* __restrict__ out, int M, int N, long long ldc, int splits,
+                                       int act) {
+  const long long total = (long long)M * (N / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int m = int(i / (N / 4)), n = int(i % (N / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + ((long long)s * M + m) * N + n);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    if (bias != nullptr) {
+      acc.x += __bfloat162float(bias[n]);
+      acc.y += __bfloat162float(bias[n + 1]);
+      acc.z += __bfloat162float(bias[n + 2]);
+      acc.w += __bfloat162float(bias[n + 3]);
+    }
+    __nv_bfloat16* o = out + (long long)m * ldc + n;
+    o[0] = __float2bfloat16(sk_act(acc.x, act));
+    o[1] = __float2bfloat16(sk_act(acc.y, act));
+    o[2] = __float2bfloat16(sk_act(acc.z, act));
+    o[3] = __float2bfloat16(sk_act(acc.w, act));
+  }
+}
+
+template <int BN, int STAGES>
+static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, int tiles,
+                          cudaStream_t stream) {
+  using L = SkinnySmem<BN, STAGES>;
+  auto kern = gemm_skinny_kernel<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<dim3(tiles, p.splits), SK_THREADS, L::TOTAL, stream>>>(tw, tx, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("skinny gemm launch: ") + cudaGetErrorString(e));
+}
+
+// Number of K splits for `tiles` row tiles on `sms` SMs: fill the machine to a whole
+// number of waves while keeping at least 4 K blocks per CTA.
+int skinny_pick_splits(int tiles, int num_kb, int sms, int M, int N, size_t scratch_floats) {
+  int best = 1;
+  double best_cost = 1e30;
+  const int max_s = std::max(1, std::min(num_kb / 4, 32));
+  for (int s = 1; s <= max_s; ++s) {
+    if (s > 1 && (size_t)s * M * N > scratch_floats) break;
+    const int ctas = tiles * s;
+    const int waves = (ctas + sms - 1) / sms;
+    const int kb = (num_kb + s - 1) / s;
+    // time ~ waves * (kb + fixed overhead per CTA) ; partial traffic adds a little per split
+    const double cost = waves * (kb + 6.0) + 0.15 * s;
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+// Returns the number of splits used.  splits_request: 0 = choose; when the result is > 1 and
+// `finalize` is false the caller consumes ws.scratch as fp32 [splits, M, N] itself.
+int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
+                     long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
+                     int splits_request, bool finalize, cudaStream_t stream) {
+  const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
+  const int tiles = (N + SK_BM - 1) / SK_BM;
+  const int num_kb = (K + SK_BK - 1) / SK_BK;
+  const size_t scratch_floats = ws.scratch != nullptr ? gemm_scratch_bytes() / 4 : 0;
+  int splits = splits_request > 0 ? splits_request : skinny_pick_splits(tiles, num_kb, sms, M, N, scratch_floats);
+  if (N % 4 != 0) splits = 1;
+  if (splits > 1 && (size_t)splits * M * N > scratch_floats) splits = 1;
+  int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;
+  SkinnyParams p{};
+  p.Nw = N;
+  p.Mtok = M;
+  p.K = K;
+  p.out = reinterpret_cast<__nv_bfloat16*>(c);
+  p.ldc = ldc;
+  p.partial = ws.scratch;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.act = act;
+  p.splits = splits;
+  p.kb_per_split = kb_per;
+  p.status = ws.status;
+  CUtensorMap tw = make_tmap_bf16_2d(w, N, K, ldw, 128, SK_BK);
+  if (M <= 32) {
+    CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 32, SK_BK);
+    launch_skinny<32, 6>(tw, tx, p, tiles, stream);
+  } else if (M <= 64) {
+    CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 64, SK_BK);
+    launch_skinny<64, 5>(tw, tx, p, tiles, stream);
+  } else if (M <= 128) {
+    CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 128, SK_BK);
+    launch_skinny<128, 4>(tw, tx, p, tiles, stream);
+  } else {
+    CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 256, SK_BK);
+    launch_skinny<256, 3>(tw, tx, p, tiles, stream);
+  }
+  if (splits > 1 && finalize) {
+    const long long total = (long long)M * (N / 4);
+    const int blocks = (int)std::min<long long>((total + 255) / 256, 2048);
+    skinny_finalize_kernel<<<blocks, 256, 0, stream>>>(ws.scratch, p.bias, p.out, M, N, ldc, splits, act);
+  }
+  return splits;
+}
+
+}  // namespace fc

@@ -16,8 +16,8 @@ void launch_embedding(const void* ids, const void* weight, void* out, int T, int
                       cudaStream_t s);
 void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
                               const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
-                              int Hq, int Hkv, int D, float eps, long long num_slots, uint32_t* status,
-                              cudaStream_t s);
+                              int Hq, int Hkv, int D, float eps, long long num_slots, int block_size,
+                              uint32_t* status, cudaStream_t s);
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
                    cudaStream_t s);
 

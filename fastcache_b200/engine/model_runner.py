@@ -125,6 +125,11 @@ class ModelRunner:
         self.image_token_len = int(getattr(self.model, "image_token_len", 0))
         self.image_token_id = getattr(self.model, "image_token_id", None)
 
+        self.fused_comm = None
+        if self.tp_size > 1 and self.device.type == "cuda" and not config.extra.get("disable_fused_comm", False):
+            from ..parallel import symm
+            self.fused_comm = symm.enable(int(config.extra.get("fused_comm_tokens", 512)), tc.hidden_size,
+                                          self.device)
         self.sampler = Sampler(config.seed)
         self.io = {"h2d_bytes": 0, "d2h_bytes": 0}      # host<->device traffic of the step loop
         self.timer: Optional[DeviceTimer] = None        # set by benchmarks to time device work only
@@ -230,7 +235,7 @@ class ModelRunner:
                 need = cfg.max_num_seqs * -(-cfg.max_model_len // bs)
                 cfg.num_kvcache_blocks = max(1, min(need, (1 << 30) // block_bytes))
         self.num_blocks = cfg.num_kvcache_blocks
-        self.kv_cache = torch.zeros(L, 2, self.num_blocks, bs, H, D, dtype=self.dtype, device=self.device)
+        self.kv_cache = torch.zeros(L, 2, self.num_blocks, H, bs, D, dtype=self.dtype, device=self.device)
         i = 0
         for module in self.model.modules():
             if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
@@ -321,6 +326,8 @@ class ModelRunner:
     # ------------------------------------------------------------------ forward
     def _forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
                  seqs: Optional[Seq[Sequence]] = None, image_rows=None) -> torch.Tensor:
+        if self.fused_comm is not None:
+            self.fused_comm.begin_forward()
         if self.is_multimodal:
             pixel = None
             if image_rows:

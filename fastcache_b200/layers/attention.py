@@ -27,7 +27,7 @@ class Attention(nn.Module):
         self.num_kv_heads = num_kv_heads
         self.layer_idx = layer_idx
         # bound by the model runner to this layer's slice of the pool:
-        # [num_blocks, block_size, num_kv_heads, head_dim]
+        # [num_blocks, num_kv_heads, block_size, head_dim]
         self.k_cache: Optional[torch.Tensor] = None
         self.v_cache: Optional[torch.Tensor] = None
 

@@ -10,7 +10,7 @@ from .loader import ext
 
 
 def _batch_meta(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: Sequence[int]):
-    bs = pool.shape[3]
+    bs = pool.shape[4]
     need = [-(-n // bs) for n in kv_lens]
     width = max(1, max(need))
     bt = np.zeros((len(kv_lens), width), dtype=np.int32)
@@ -26,7 +26,7 @@ def _torch_scores(pool, block_tables, kv_lens, method, window_q, params, stride)
     """Scores for the methods without a dedicated kernel: the PyTorch statement, on the device."""
     from ..compress.inpool import _rows
     from ..compress.scorers import NEEDS_QUERIES, score_keys
-    L, _, _, _, H, D = pool.shape
+    L, _, _, H, _, D = pool.shape
     out = torch.full((len(kv_lens), L, H, stride), float("-inf"), dtype=torch.float32, device=pool.device)
     for i, (bt, n) in enumerate(zip(block_tables, kv_lens)):
         blocks = torch.as_tensor(list(bt), dtype=torch.long, device=pool.device)
@@ -63,11 +63,11 @@ def evict_cuda(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: S
         p = dict(params)
         if method == "uniform":
             p.pop("n_kept", None)
-            scores = torch.full((len(kv_lens), pool.shape[0], pool.shape[4], stride), float("-inf"),
+            scores = torch.full((len(kv_lens), pool.shape[0], pool.shape[3], stride), float("-inf"),
                                 dtype=torch.float32, device=dev)
             from ..compress.scorers import uniform
             for i, (n, k) in enumerate(zip(kv_lens, kept)):
-                dummy = torch.empty(pool.shape[4], n, 1, device=dev)
+                dummy = torch.empty(pool.shape[3], n, 1, device=dev)
                 scores[i, :, :, :n] = uniform(dummy, n_kept=k)[None]
         else:
             scores = _torch_scores(pool, block_tables, kv_lens, method, window_q, p, stride)

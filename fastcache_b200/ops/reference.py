@@ -90,8 +90,9 @@ def rope_qknorm_store(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch
     the paged pool.  Returns rotated q [T, Hq, D].
 
     qkv: [T, (Hq + 2 Hkv) * D] packed q | k | v
-    k_cache / v_cache: [num_blocks, block_size, Hkv, D]; slot = block * block_size + offset,
-    negative slots are skipped.
+    k_cache / v_cache: [num_blocks, Hkv, block_size, D] (head-major inside a block, so the
+    rows of one head are contiguous); slot = block * block_size + offset, negative slots
+    are skipped.
     """
     T = qkv.shape[0]
     qd, kd = num_q_heads * head_dim, num_kv_heads * head_dim
@@ -109,19 +110,20 @@ def rope_qknorm_store(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch
     if k_cache is not None and slot_mapping is not None:
         valid = slot_mapping >= 0
         slots = slot_mapping[valid].long()
-        kc = k_cache.view(-1, num_kv_heads, head_dim)
-        vc = v_cache.view(-1, num_kv_heads, head_dim)
-        kc[slots] = k[valid].to(kc.dtype)
-        vc[slots] = v[valid].to(vc.dtype)
+        bs = k_cache.shape[2]
+        blk, off = slots // bs, slots % bs
+        k_cache[blk, :, off] = k[valid].to(k_cache.dtype)
+        v_cache[blk, :, off] = v[valid].to(v_cache.dtype)
     return q.contiguous()
 
 
 # -------------------------------------------------------------- attention
 def gather_paged(cache: torch.Tensor, block_table: torch.Tensor, length: int) -> torch.Tensor:
     """Rows [0, length) of one request from the pool: [length, Hkv, D]."""
-    block_size = cache.shape[1]
+    block_size = cache.shape[2]
     nb = -(-length // block_size)
-    rows = cache[block_table[:nb].long()].reshape(nb * block_size, cache.shape[2], cache.shape[3])
+    rows = cache[block_table[:nb].long()].permute(0, 2, 1, 3).reshape(nb * block_size, cache.shape[1],
+                                                                       cache.shape[3])
     return rows[:length]
 
 

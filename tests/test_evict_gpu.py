@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 def _pool(L=3, nb=40, bs=16, H=2, D=128, seed=0):
     g = torch.Generator().manual_seed(seed)
-    return torch.randn(L, 2, nb, bs, H, D, generator=g).to(torch.bfloat16).cuda()
+    return torch.randn(L, 2, nb, H, bs, D, generator=g).to(torch.bfloat16).cuda()
 
 
 @pytest.mark.parametrize("method", ["knorm", "knorm_ref", "streaming_llm", "random"])
@@ -26,10 +26,10 @@ def test_evict_matches_reference(method, D):
     out = evict_in_pool(got, tables, lens, method, kept, None, {})
     torch.cuda.synchronize()
     assert out == kept
-    bs = pool.shape[3]
+    bs = pool.shape[4]
     for bt, k in zip(tables, kept):
         nb = -(-k // bs)
         idx = torch.tensor(bt[:nb], device="cuda")
-        a = got[:, :, idx].reshape(pool.shape[0], 2, -1, pool.shape[4], D)[:, :, :k]
-        b = want[:, :, idx].reshape(pool.shape[0], 2, -1, pool.shape[4], D)[:, :, :k]
+        a = got[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(pool.shape[0], 2, -1, pool.shape[3], D)[:, :, :k]
+        b = want[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(pool.shape[0], 2, -1, pool.shape[3], D)[:, :, :k]
         assert torch.equal(a, b)

@@ -97,7 +97,7 @@ def test_rope_qknorm_store(D, Hq, Hkv, qk):
     kw = _rand(D, seed=3) if qk else None
     slots = torch.randperm(nb * bs, device=DEV)[:T].int()
     slots[3] = -1
-    kc, vc = (torch.zeros(nb, bs, Hkv, D, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    kc, vc = (torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV) for _ in range(2))
     kc2, vc2 = kc.clone(), vc.clone()
     q = ops.rope_qknorm_store(qkv, pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc, vc, slots)
     q2 = ref.rope_qknorm_store(qkv, pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc2, vc2, slots)
@@ -111,7 +111,7 @@ def _paged(B, lens, Hkv, D, bs, seed=0):
     nb_per = [-(-n // bs) for n in lens]
     nb = sum(nb_per) + 3
     perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed)).tolist()
-    kc, vc = _rand(nb, bs, Hkv, D, seed=seed + 1), _rand(nb, bs, Hkv, D, seed=seed + 2)
+    kc, vc = _rand(nb, Hkv, bs, D, seed=seed + 1), _rand(nb, Hkv, bs, D, seed=seed + 2)
     bt = torch.zeros(B, max(nb_per), dtype=torch.int32)
     k = 0
     for i, n in enumerate(nb_per):

@@ -1,0 +1,82 @@
+"""Worker for the tensor-parallel tests: launched with torch.distributed.run (any world size,
+including 1) on CPU (gloo) or CUDA (nccl).  Writes its results as JSON on rank 0."""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from fastcache_b200 import LLM, SamplingParams  # noqa: E402
+from fastcache_b200.parallel import tp as tpmod  # noqa: E402
+from helpers import tiny_qwen3_config  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--kv-heads", type=int, default=2)
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    res = {}
+    if world > 1:
+        tpmod.init_tensor_parallel(world, rank, backend="nccl" if a.device == "cuda" else "gloo", timeout_s=120)
+    device = f"cuda:{local}" if a.device == "cuda" else "cpu"
+
+    if a.device == "cuda" and world > 1:
+        # fused all-reduce + residual + RMSNorm against the library all-reduce
+        from fastcache_b200 import ops
+        from fastcache_b200.ops import reference as ref
+        from fastcache_b200.parallel import symm
+        torch.cuda.set_device(local)
+        comm = symm.enable(512, 1024, torch.device(device))
+        g = torch.Generator(device="cpu").manual_seed(100 + rank)
+        errs = []
+        for it, T in enumerate([1, 7, 128, 300]):
+            part = (torch.randn(T, 1024, generator=g) * 0.5).to(torch.bfloat16).to(device)
+            gres = torch.Generator(device="cpu").manual_seed(7 + it)
+            resid = torch.randn(T, 1024, generator=gres).to(torch.bfloat16).to(device)
+            w = torch.ones(1024, dtype=torch.bfloat16, device=device)
+            total = part.float().clone()
+            torch.distributed.all_reduce(total)
+            want_n, want_r = ref.add_rms_norm(total.to(torch.bfloat16), resid.clone(), w, 1e-6)
+            for mm in ([False, True] if comm.use_multimem or os.environ.get("FC_MULTIMEM") == "1" else [False]):
+                buf = it % 2
+                comm.bufs[buf][:T].copy_(part)
+                r2 = resid.clone()
+                y = ops.ext().allreduce_add_rmsnorm(buf, r2, w, 1e-6, mm, comm.status)
+                torch.cuda.synchronize()
+                errs.append(float((y.float() - want_n.float()).abs().max()))
+                errs.append(float((r2.float() - want_r.float()).abs().max()))
+                torch.distributed.barrier()
+        res["allreduce_max_err"] = max(errs)
+        res["status"] = int(ops.ext().read_status(local))
+
+    cfg = tiny_qwen3_config(hidden_size=512, num_attention_heads=8, num_key_value_heads=a.kv_heads, head_dim=64,
+                            intermediate_size=1024, vocab_size=2000)
+    llm = LLM(cfg, device=device, dtype="bf16" if a.device == "cuda" else "fp32", tensor_parallel_size=world,
+              kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=256, max_num_seqs=8,
+              enforce_eager=False, init_device="cpu")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (9, 40, 77, 120)]
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    res["tokens"] = [o["token_ids"] for o in out]
+    llm.exit()
+    if rank == 0:
+        with open(a.out, "w") as fh:
+            json.dump(res, fh)
+    if world > 1:
+        if a.device == "cuda":
+            from fastcache_b200.parallel import symm
+            symm.disable()
+        tpmod.cleanup_tensor_parallel()
+
+
+if __name__ == "__main__":
+    main()
