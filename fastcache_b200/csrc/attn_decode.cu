@@ -336,11 +336,8 @@ void launch_decode_attention(const void* q, const void* k_cache, const void* v_c
   const CUtensorMap tk = make_tmap_bf16_2d(k_cache, rows, D, D, box_rows, 64);
   const CUtensorMap tv = make_tmap_bf16_2d(v_cache, rows, D, D, box_rows, 64);
   auto launch = [&](auto kern) {
-    static bool configured = false;
-    if (!configured) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      configured = true;
-    }
+    // set on every launch: both head-dim instantiations share this lambda's function-pointer type
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     kern<<<grid, DEC_THREADS, smem, stream>>>(tk, tv, (const bf16*)q, box_rows, block_tables, context_lens,
                                               (bf16*)out, part_o, part_lse, Hq, Hkv, block_size, max_blocks,
                                               num_blocks, splits, scale_log2, status);

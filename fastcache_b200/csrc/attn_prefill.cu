@@ -232,11 +232,8 @@ void launch_prefill_attention(const void* q, const void* k_cache, const void* v_
   dim3 grid((max_q_len + PF_BM - 1) / PF_BM, Hq, num_seqs);
   const int smem = PF_BM * D * 2 + 2 * 2 * PF_BN * D * 2;
   auto launch = [&](auto kern) {
-    static bool configured = false;
-    if (!configured) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      configured = true;
-    }
+    // set on every launch: both head-dim instantiations share this lambda's function-pointer type
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     kern<<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_tables, cu_seqlens_q, kv_lens, (bf16*)out, Hq, Hkv, block_size,
                                              max_blocks, num_blocks, scale_log2, status);

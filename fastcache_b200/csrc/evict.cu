@@ -235,11 +235,7 @@ void launch_select_compact(void* pool, const float* scores, const int* block_tab
   const int smem = (s_stride + 256 + 8 + SC_CHUNK + 16) * 4;
   if (smem > 220 * 1024) throw std::runtime_error("select_compact: request too long for one CTA's shared memory");
   auto launch = [&](auto kern) {
-    static int configured = 0;
-    if (smem > configured) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      configured = smem;
-    }
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     kern<<<grid, SC_THREADS, smem, stream>>>((bf16*)pool, scores, block_tables, kv_lens, n_kepts, L, num_blocks,
                                              block_size, Hkv, max_blocks, s_stride, status);
   };
