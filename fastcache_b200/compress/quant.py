@@ -1,0 +1,99 @@
+"""KV quantisers: per-row INT8 (symmetric / asymmetric), group-wise INT4 (packed two per
+byte), FP8 casts and NF4 (nearest entry of the 16-value NormalFloat table).
+
+Parity: nanovllm/autocompress/methods.py:636-757, nanovllm/autocompress/kernels.py:388-422,
+utils_ccm/utils_compress.py:51-70, :144-154 (SimpleKVQuantizer / ImprovedKVQuantizer fake-quant).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict
+
+import torch
+
+NF4_TABLE = torch.tensor([-1.0, -0.6961928, -0.52507305, -0.39491749, -0.28444138, -0.18477343, -0.09105004, 0.0,
+                          0.0795803, 0.1609302, 0.2461123, 0.33791524, 0.44070983, 0.562617, 0.72295684, 1.0])
+
+
+def _groups(x: torch.Tensor, g: int):
+    n = x.shape[-1]
+    if n % g:
+        g = n
+    return x.reshape(*x.shape[:-1], n // g, g), g
+
+
+def quantize(x: torch.Tensor, mode: str = "int8", group_size: int = 128) -> Dict[str, Any]:
+    xf = x.float()
+    meta: Dict[str, Any] = {"mode": mode, "shape": tuple(x.shape), "dtype": x.dtype}
+    if mode == "int8":
+        scale = xf.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / 127.0
+        meta.update(q=torch.round(xf / scale).clamp(-127, 127).to(torch.int8), scale=scale)
+    elif mode == "int8_asym":
+        lo, hi = xf.amin(dim=-1, keepdim=True), xf.amax(dim=-1, keepdim=True)
+        scale = ((hi - lo) / 255.0).clamp_min(1e-8)
+        meta.update(q=torch.round((xf - lo) / scale).clamp(0, 255).to(torch.uint8), scale=scale, zero=lo)
+    elif mode in ("int4", "nf4"):
+        xg, g = _groups(xf, group_size)
+        absmax = xg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
+        if mode == "int4":
+            q = (torch.round(xg / absmax * 7.0).clamp(-8, 7) + 8).to(torch.uint8)
+        else:
+            table = NF4_TABLE.to(xg.device)
+            q = (xg / absmax).unsqueeze(-1).sub(table).abs().argmin(dim=-1).to(torch.uint8)
+        q = q.reshape(*q.shape[:-2], -1)
+        if q.shape[-1] % 2:
+            q = torch.cat([q, torch.zeros_like(q[..., :1])], dim=-1)
+        meta.update(q=(q[..., 0::2] | (q[..., 1::2] << 4)), scale=absmax, group=g)
+    elif mode in ("fp8_e4m3", "fp8_e5m2"):
+        dt = torch.float8_e4m3fn if mode == "fp8_e4m3" else torch.float8_e5m2
+        amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
+        scale = amax / (448.0 if mode == "fp8_e4m3" else 57344.0)
+        meta.update(q=(xf / scale).to(dt), scale=scale)
+    else:
+        raise ValueError(mode)
+    return meta
+
+
+def dequantize(p: Dict[str, Any]) -> torch.Tensor:
+    mode = p["mode"]
+    if mode == "int8":
+        y = p["q"].float() * p["scale"]
+    elif mode == "int8_asym":
+        y = p["q"].float() * p["scale"] + p["zero"]
+    elif mode in ("int4", "nf4"):
+        q = p["q"]
+        lo, hi = (q & 0xF), (q >> 4)
+        u = torch.stack([lo, hi], dim=-1).reshape(*q.shape[:-1], -1)
+        n = p["shape"][-1]
+        u = u[..., :n]
+        g = p["group"]
+        ug = u.reshape(*u.shape[:-1], n // g, g)
+        if mode == "int4":
+            y = (ug.float() - 8.0) / 7.0 * p["scale"]
+        else:
+            y = NF4_TABLE.to(q.device)[ug.long()] * p["scale"]
+        y = y.reshape(p["shape"])
+    elif mode in ("fp8_e4m3", "fp8_e5m2"):
+        y = p["q"].float() * p["scale"]
+    else:
+        raise ValueError(mode)
+    return y.reshape(p["shape"]).to(p["dtype"])
+
+
+def fake_quantize(x: torch.Tensor, nbits: int = 4, group_size: int = 128) -> torch.Tensor:
+    """Quantise and immediately restore (the HF harness' SimpleKVQuantizer behaviour)."""
+    mode = {8: "int8", 4: "int4"}.get(nbits)
+    if mode is None:
+        raise ValueError("nbits must be 4 or 8")
+    return dequantize(quantize(x, mode, group_size))
+
+
+class SimpleKVQuantizer:
+    def __init__(self, nbits: int = 4, group_size: int = 128):
+        self.nbits, self.group_size = nbits, group_size
+
+    def __call__(self, kv_cache):
+        return [(fake_quantize(k, self.nbits, self.group_size), fake_quantize(v, self.nbits, self.group_size))
+                for k, v in kv_cache]
+
+
+ImprovedKVQuantizer = SimpleKVQuantizer
