@@ -243,6 +243,39 @@ Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, con
   return out;
 }
 
+// q [B, Sq, H, D], k / v [B, Sk, H, D]; any strides with a contiguous last dim; key_mask [B, Sk] bool
+Tensor dense_attention(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
+                       const c10::optional<Tensor>& key_mask) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "dense attention expects [B, S, H, D] tensors");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1, "last dim must be contiguous");
+  const int64_t B = q.size(0), Sq = q.size(1), H = q.size(2), D = q.size(3), Sk = k.size(1);
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(2) == H && v.size(2) == H && k.size(3) == D &&
+                  v.size(3) == D && v.size(1) == Sk, "q / k / v shapes do not agree");
+  for (const Tensor* t : {&q, &k, &v}) {
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0 && t->stride(0) % 8 == 0 &&
+                    t->stride(1) % 8 == 0 && t->stride(2) % 8 == 0, "operands must be 16-byte aligned per row");
+  }
+  const uint8_t* mask = nullptr;
+  Tensor mask_c;
+  if (key_mask.has_value() && key_mask->defined()) {
+    TORCH_CHECK(key_mask->scalar_type() == torch::kBool && key_mask->dim() == 2 && key_mask->size(0) == B &&
+                    key_mask->size(1) == Sk && key_mask->is_cuda(), "key_mask must be bool [B, Sk] on the device");
+    mask_c = key_mask->contiguous();
+    mask = reinterpret_cast<const uint8_t*>(mask_c.data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({B, Sq, H, D}, q.options());
+  const long long qs[3] = {q.stride(0), q.stride(1), q.stride(2)};
+  const long long ks[3] = {k.stride(0), k.stride(1), k.stride(2)};
+  const long long vs[3] = {v.stride(0), v.stride(1), v.stride(2)};
+  fc::launch_dense_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), mask, int(B), int(Sq),
+                             int(Sk), int(H), int(D), qs, ks, vs, float(scale), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
 Tensor sample(const Tensor& logits, const Tensor& temps, int64_t seed) {
   check_bf16(logits, "logits");
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [B, V] with unit inner stride");
@@ -289,6 +322,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,
         py::arg("max_ctx") = 0);
   m.def("sample", &sample);
+  m.def("dense_attention", &dense_attention);
   m.def("read_status", &read_status);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });

@@ -50,9 +50,39 @@ void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_table
                             int(pool.size(5)), int(block_tables.size(1)), int(scores.size(3)),
                             reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
 }
+// In-place CCM merge of `kv_lens.numel()` requests for pool layers [layer_start, layer_end).
+// Weights are the packed [Lw, 4, ...] tensors; weight_layer_start is the index of pool layer
+// `layer_start` inside them.
+void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens, const Tensor& image_lens,
+                  const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, const Tensor& w3,
+                  const Tensor& b3, int64_t layer_start, int64_t layer_end, int64_t weight_layer_start,
+                  int64_t factor, int64_t min_seq_len, bool single_segment, Tensor status) {
+  check_pool(pool);
+  check_i32(block_tables, "block_tables");
+  check_i32(kv_lens, "kv_lens");
+  check_i32(image_lens, "image_lens");
+  const int64_t D = pool.size(5);
+  for (const Tensor* t : {&w1, &b1, &w2, &b2, &w3, &b3})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kBFloat16 && t->is_contiguous(),
+                "compressor weights must be contiguous bf16 CUDA tensors");
+  TORCH_CHECK(w1.dim() == 4 && w1.size(1) == 4 && w1.size(2) == D && w1.size(3) == D * factor,
+              "w1 must be [L, 4, D, D * factor]");
+  TORCH_CHECK(w2.sizes() == w3.sizes() && w2.size(2) == D && w2.size(3) == D, "w2 / w3 must be [L, 4, D, D]");
+  TORCH_CHECK(layer_start >= 0 && layer_end <= pool.size(0) && weight_layer_start >= 0 &&
+                  weight_layer_start + (layer_end - layer_start) <= w1.size(0), "layer range out of bounds");
+  c10::cuda::CUDAGuard guard(pool.device());
+  fc::launch_ccm_fused(pool.data_ptr(), block_tables.data_ptr<int>(), kv_lens.data_ptr<int>(),
+                       image_lens.data_ptr<int>(), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), b1.data_ptr(),
+                       b2.data_ptr(), b3.data_ptr(), int(kv_lens.numel()), int(w1.size(0)), int(layer_start),
+                       int(layer_end), int(weight_layer_start), int(pool.size(2)), int(pool.size(3)),
+                       int(pool.size(4)), int(D), int(block_tables.size(1)), int(factor), int(min_seq_len),
+                       single_segment ? 1 : 0, reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
+                       at::cuda::getCurrentCUDAStream());
+}
 }  // namespace
 
 void register_compress(pybind11::module_& m) {
   m.def("knorm_scores", &knorm_scores);
   m.def("select_compact", &select_compact);
+  m.def("ccm_compress", &ccm_compress);
 }

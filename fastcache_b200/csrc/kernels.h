@@ -40,3 +40,18 @@ void launch_select_compact(void* pool, const float* scores, const int* block_tab
                            const int* n_kepts, int n_seq, int L, int num_blocks, int block_size, int Hkv, int D,
                            int max_blocks, int s_stride, uint32_t* status, cudaStream_t stream);
 }  // namespace fc
+
+namespace fc {
+void launch_dense_attention(const void* q, const void* k, const void* v, void* out, const uint8_t* key_mask,
+                            int B, int Sq, int Sk, int H, int D, const long long* q_strides,
+                            const long long* k_strides, const long long* v_strides, float scale,
+                            cudaStream_t stream);
+}  // namespace fc
+
+namespace fc {
+void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, const int* image_lens,
+                      const void* w1, const void* w2, const void* w3, const void* b1, const void* b2,
+                      const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
+                      int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
+                      int factor, int min_seq_len, int single_segment, uint32_t* status, cudaStream_t stream);
+}  // namespace fc

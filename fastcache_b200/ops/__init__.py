@@ -98,7 +98,7 @@ def decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale, wor
 def dense_attention(q, k, v, scale, key_mask=None):
     if q.is_cuda:
         _n()
-        return ext().dense_attention(q.contiguous(), k.contiguous(), v.contiguous(), float(scale), key_mask)
+        return ext().dense_attention(q, k, v, float(scale), key_mask)
     return ref.dense_attention(q, k, v, scale, key_mask)
 
 

@@ -152,3 +152,17 @@ def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens):
     want = ref.prefill_attention(q.float(), kc.float(), vc.float(), bt, cu, kl, scale)
     _check_status()
     assert (o.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,D,masked", [(2, 577, 577, 16, 64, False), (3, 1024, 1024, 16, 72, True),
+                                                (2, 64, 700, 28, 128, True), (1, 10, 10, 4, 64, False)])
+def test_dense_attention(B, Sq, Sk, H, D, masked):
+    qkv = _rand(B, max(Sq, Sk), 3, H, D, seed=21)
+    q, k, v = qkv[:, :Sq, 0], qkv[:, :Sk, 1], qkv[:, :Sk, 2]          # strided views, as the towers pass them
+    mask = None
+    if masked:
+        lens = torch.randint(Sk // 2, Sk + 1, (B,))
+        mask = (torch.arange(Sk)[None, :] < lens[:, None]).to(DEV)
+    o = ops.dense_attention(q, k, v, D ** -0.5, mask)
+    want = ref.dense_attention(q.float(), k.float(), v.float(), D ** -0.5, mask)
+    assert (o.float() - want).abs().max().item() < 2e-2
