@@ -162,6 +162,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
       int it = 0;
       uint32_t h_phase = 0, free_phase = 0;
+      uint32_t a_uses[CCM_STAGES] = {0, 0, 0};
       bool ok = true;
       for (int tile = 0; tile < total_tiles && ok; ++tile) {
         // the previous tile's last epilogue must have drained accumulator 0
@@ -184,7 +185,12 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
             const int stage = it % CCM_STAGES;
             const uint32_t ph = (it / CCM_STAGES) & 1;
             ok = mbar_wait(&w_full[stage], ph, p.status, ST_TIMEOUT_FULL);
-            if (ok && g == 0) ok = mbar_wait(&a_full[stage], ph, p.status, ST_TIMEOUT_FULL);
+            if (ok && g == 0) {
+              // a_full[stage] completes a phase only when the stage carries a gathered operand,
+              // so its parity is counted per stage, not derived from the ring position
+              ok = mbar_wait(&a_full[stage], a_uses[stage] & 1u, p.status, ST_TIMEOUT_FULL);
+              ++a_uses[stage];
+            }
             if (!ok) break;
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * 2 * CCM_KB_BYTES);
@@ -269,7 +275,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
           fence_proxy_async();
           mbar_arrive(&a_full[stage]);
         }
-        it += 4;                                      // the W2 / W3 stages carry no gathered operand
+        it += 4;     // the W2 / W3 stages carry no gathered operand (the MMA warp counts a_full uses per stage)
         if (!ok) break;
         // ---- epilogues 1 and 2: bias + ReLU, activation tile to shared memory for the next GEMM
         for (int g = 0; g < 2 && ok; ++g) {

@@ -86,6 +86,7 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, u
     st_release_sys(peers.flags[tid] + (size_t)slot * COMM_MAX_WORLD + peers.rank, epoch);
     const uint32_t* mine = peers.flags[peers.rank] + (size_t)slot * COMM_MAX_WORLD + tid;
     bool got = false;
+    const uint64_t t0 = global_timer_ns();
     for (uint32_t i = 0; i < FC_PEER_SPIN_LIMIT; ++i) {
       // epochs only grow; a peer that is already one exchange ahead is fine
       if (int32_t(ld_acquire_sys(mine) - epoch) >= 0) {
@@ -93,6 +94,8 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, u
         break;
       }
       __nanosleep(20);
+      // ranks are launched by different host processes: allow seconds of skew, not more
+      if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
     }
     if (!got) {
       report(status, ST_TIMEOUT_PEER);
@@ -192,6 +195,30 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
         peers, buf, nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("allreduce launch: ") + cudaGetErrorString(e));
+}
+
+}  // namespace fc
+
+namespace fc {
+
+__global__ void wait_gathered_kernel(const uint32_t* flags, int world, uint32_t epoch, uint32_t* status) {
+  if (threadIdx.x < world) {
+    const uint64_t t0 = global_timer_ns();
+    bool got = false;
+    for (uint32_t i = 0;; ++i) {
+      if (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) >= 0) {
+        got = true;
+        break;
+      }
+      __nanosleep(40);
+      if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
+    }
+    if (!got) report(status, ST_TIMEOUT_PEER);
+  }
+}
+
+void wait_gathered(const TpBuffers& b, uint32_t epoch, uint32_t* status, cudaStream_t stream) {
+  wait_gathered_kernel<<<1, 32, 0, stream>>>(b.gathered_flags[b.rank], b.world, epoch, status);
 }
 
 }  // namespace fc

@@ -22,3 +22,36 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
                                   uint32_t* status, bool use_multimem, cudaStream_t stream);
 
 }  // namespace fc
+
+namespace fc {
+
+// Symmetric buffers of the prefill-size fused GEMM + collective kernels (gemm_tp.cu).
+struct TpBuffers {
+  int world = 1;
+  int rank = 0;
+  __nv_bfloat16* stage[COMM_MAX_WORLD] = {};        // per rank: [world][chunk_rows_max][hidden] partial sums by source
+  __nv_bfloat16* xg[COMM_MAX_WORLD] = {};           // per rank: gathered normalised activations [max_tokens][hidden]
+  uint32_t* rs_flags[COMM_MAX_WORLD] = {};          // per rank: [world] "source s delivered its partials"
+  uint32_t* gathered_flags[COMM_MAX_WORLD] = {};    // per rank: [world] "owner o's rows have landed here"
+  int* owner_done = nullptr;                        // local [world + 1] counters, zero between calls
+};
+
+// Row-parallel GEMM + reduce-scatter + residual add + RMSNorm + send half of the all-gather.
+// x [M, K] and w [N, K] are this rank's shards; `residual` holds the rows owned by this rank
+// ([min(M - rank * chunk_rows, chunk_rows), N]) and is updated in place.  The normalised rows of all
+// ranks arrive in xg (rows [0, M)) on every rank; consume them with gemm_after_gather or after
+// wait_gathered.
+void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                      const TpBuffers& b, void* residual, const void* norm_w, float eps, int chunk_rows,
+                      uint32_t epoch, uint32_t* status, int sm_limit, cudaStream_t stream);
+
+// Column-parallel GEMM over the gathered activations: c [M, N] = xg[:M] @ w[N, K]^T.  Tiles of a
+// chunk are loaded only after its owner's "gathered" flag for `epoch` has been observed.
+void gemm_after_gather(const void* xg_local, const void* w, void* c, int M, int N, int K, long long ldw,
+                       long long ldc, const TpBuffers& b, int chunk_rows, uint32_t epoch, uint32_t* status,
+                       int sm_limit, cudaStream_t stream);
+
+// Blocks the stream (one tiny kernel, bounded wait) until every owner's rows of `epoch` have landed.
+void wait_gathered(const TpBuffers& b, uint32_t epoch, uint32_t* status, cudaStream_t stream);
+
+}  // namespace fc

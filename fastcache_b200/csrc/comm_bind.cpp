@@ -62,10 +62,99 @@ Tensor allreduce_add_rmsnorm(int64_t buf, Tensor residual, const Tensor& weight,
                                    at::cuda::getCurrentCUDAStream());
   return out;
 }
+// ------------------------------------------------------------ prefill-size fused GEMM + collective
+struct TpState {
+  bool ready = false;
+  fc::TpBuffers b;
+  Tensor owner_done;
+  int64_t stage_rows = 0, xg_rows = 0, hidden = 0;
+};
+TpState g_tp;
+
+void tp_init(int64_t rank, int64_t world, const std::vector<int64_t>& stage, const std::vector<int64_t>& xg,
+             const std::vector<int64_t>& flags, int64_t stage_rows, int64_t xg_rows, int64_t hidden,
+             int64_t device) {
+  TORCH_CHECK(world >= 2 && world <= fc::COMM_MAX_WORLD, "world size must be in [2, ", fc::COMM_MAX_WORLD, "]");
+  TORCH_CHECK((int64_t)stage.size() == world && (int64_t)xg.size() == world && (int64_t)flags.size() == world,
+              "need one pointer per rank");
+  g_tp.b.world = int(world);
+  g_tp.b.rank = int(rank);
+  for (int i = 0; i < world; ++i) {
+    g_tp.b.stage[i] = reinterpret_cast<__nv_bfloat16*>(stage[i]);
+    g_tp.b.xg[i] = reinterpret_cast<__nv_bfloat16*>(xg[i]);
+    g_tp.b.rs_flags[i] = reinterpret_cast<uint32_t*>(flags[i]);
+    g_tp.b.gathered_flags[i] = reinterpret_cast<uint32_t*>(flags[i]) + fc::COMM_MAX_WORLD;
+  }
+  g_tp.owner_done = torch::zeros({fc::COMM_MAX_WORLD + 1},
+                                 torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, int(device)));
+  g_tp.b.owner_done = g_tp.owner_done.data_ptr<int>();
+  g_tp.stage_rows = stage_rows;      // rows per source slot of the staging buffer
+  g_tp.xg_rows = xg_rows;
+  g_tp.hidden = hidden;
+  g_tp.ready = true;
+}
+
+void check_gemm_operand(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 &&
+                  t.stride(0) % 8 == 0 && t.size(1) % 8 == 0, name, " must be a row-major bf16 matrix with K % 8 == 0");
+}
+
+// Partial products of x @ w.T are reduce-scattered, added to `residual` (the rows this rank owns,
+// updated in place) and normalised; the normalised rows of every rank land in xg on every rank.
+void gemm_rs_add_norm(const Tensor& x, const Tensor& w, Tensor residual, const Tensor& norm_w, double eps,
+                      int64_t chunk_rows, int64_t epoch, Tensor status, int64_t sm_limit) {
+  TORCH_CHECK(g_tp.ready, "tp_init was not called");
+  check_gemm_operand(x, "x");
+  check_gemm_operand(w, "weight");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && N == g_tp.hidden, "weight shape does not match the staging buffers");
+  TORCH_CHECK(chunk_rows % 128 == 0 && chunk_rows <= g_tp.stage_rows && M <= g_tp.xg_rows &&
+                  chunk_rows * g_tp.b.world >= M, "chunk_rows / token count exceed the staging buffers");
+  const int64_t own = std::max<int64_t>(0, std::min<int64_t>(M - g_tp.b.rank * chunk_rows, chunk_rows));
+  TORCH_CHECK(residual.scalar_type() == torch::kBFloat16 && residual.is_contiguous() && residual.dim() == 2 &&
+                  residual.size(0) == own && residual.size(1) == N, "residual must hold the ", own,
+              " rows owned by this rank");
+  TORCH_CHECK(norm_w.scalar_type() == torch::kBFloat16 && norm_w.is_contiguous() && norm_w.numel() == N,
+              "bad norm weight");
+  c10::cuda::CUDAGuard guard(x.device());
+  fc::gemm_rs_add_norm(x.data_ptr(), w.data_ptr(), int(M), int(N), int(K), x.stride(0), w.stride(0), g_tp.b,
+                       residual.data_ptr(), norm_w.data_ptr(), float(eps), int(chunk_rows), uint32_t(epoch),
+                       reinterpret_cast<uint32_t*>(status.data_ptr<int>()), int(sm_limit),
+                       at::cuda::getCurrentCUDAStream());
+}
+
+// y = xg[:M] @ w.T where xg is this rank's gathered-activation buffer (passed as a tensor view).
+Tensor gemm_after_gather(const Tensor& xg_view, const Tensor& w, int64_t chunk_rows, int64_t epoch, Tensor status,
+                         int64_t sm_limit) {
+  TORCH_CHECK(g_tp.ready, "tp_init was not called");
+  check_gemm_operand(xg_view, "xg");
+  check_gemm_operand(w, "weight");
+  TORCH_CHECK(xg_view.is_contiguous() && xg_view.data_ptr() == g_tp.b.xg[g_tp.b.rank],
+              "xg must be the gathered-activation buffer of this rank");
+  const int64_t M = xg_view.size(0), K = xg_view.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "inner dimensions differ");
+  c10::cuda::CUDAGuard guard(w.device());
+  Tensor out = torch::empty({M, N}, w.options());
+  fc::gemm_after_gather(xg_view.data_ptr(), w.data_ptr(), out.data_ptr(), int(M), int(N), int(K), w.stride(0),
+                        out.stride(0), g_tp.b, int(chunk_rows), uint32_t(epoch),
+                        reinterpret_cast<uint32_t*>(status.data_ptr<int>()), int(sm_limit),
+                        at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+void wait_gathered(int64_t epoch, Tensor status) {
+  TORCH_CHECK(g_tp.ready, "tp_init was not called");
+  fc::wait_gathered(g_tp.b, uint32_t(epoch), reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
+                    at::cuda::getCurrentCUDAStream());
+}
 }  // namespace
 
 void register_comm(pybind11::module_& m) {
   m.def("comm_init", &comm_init);
   m.def("comm_shutdown", &comm_shutdown);
   m.def("allreduce_add_rmsnorm", &allreduce_add_rmsnorm);
+  m.def("tp_init", &tp_init);
+  m.def("gemm_rs_add_norm", &gemm_rs_add_norm);
+  m.def("gemm_after_gather", &gemm_after_gather);
+  m.def("wait_gathered", &wait_gathered);
 }

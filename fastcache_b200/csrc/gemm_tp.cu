@@ -1,0 +1,471 @@
+// Tensor-parallel GEMMs fused with their collective (prefill sizes), over symmetric memory.
+//
+// Token rows are split into `tp` contiguous chunks of `chunk_rows` (a multiple of 128); rank r owns
+// chunk r: it holds the residual stream of those rows and is the one that normalises them.
+//
+// MODE_RS  (row-parallel projection: o_proj, down_proj)
+//   y_partial[T, H] = x[T, K/tp] @ W[H, K/tp]^T on every rank.  The tcgen05 main loop is the one of
+//   gemm.cu (TMA -> smem ring -> tcgen05.mma -> TMEM); the epilogue stores each 128-row tile of the
+//   partial sums straight into the OWNER's staging buffer (slot = source rank) with peer stores, remote
+//   owners first so the NVLink traffic overlaps the rest of the GEMM.  When a rank has written all
+//   tiles of an owner it raises that owner's flag (release, system scope).  After its own tiles every
+//   CTA turns to the rows this rank owns: it waits (bounded) for the flags of all source ranks, sums
+//   the tp partials, adds the residual (updated in place), applies RMSNorm and stores the normalised
+//   rows into the gathered activation buffer of EVERY rank; the last CTA raises the "gathered" flag on
+//   every rank.  That is reduce-scatter + residual add + RMSNorm + the send half of the all-gather in
+//   the GEMM kernel.
+//
+// MODE_AG  (column-parallel projection that follows: qkv_proj, gate_up_proj)
+//   A is the gathered activation buffer in local memory.  The TMA producer waits (bounded) for the
+//   "gathered" flag of a chunk's owner before it loads the first tile of that chunk and starts with
+//   its own chunk, so the GEMM runs while later chunks are still arriving.
+//
+// No TMA touches peer memory and no load is multicast; remote data always lands in the consumer's own
+// memory through ordinary stores first.  Every wait is bounded and reports through the status word.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+#include "comm.h"
+#include "gemm.h"
+#include "ptx.cuh"
+
+namespace fc {
+
+constexpr int TP_BM = 128;
+constexpr int TP_BK = 64;
+constexpr int TP_BN = 256;
+constexpr int TP_STAGES = 4;
+constexpr int TP_THREADS = 192;
+constexpr int MODE_RS = 1;
+constexpr int MODE_AG = 2;
+
+struct TpGemmParams {
+  int M, N, K;                 // tokens, output features, reduction length (local)
+  int num_m, num_n, group_m;
+  int total_tiles;
+  int tp, rank, chunk_rows, blocks_per_chunk, rot;
+  uint32_t epoch;
+  uint32_t* status;
+  // MODE_AG: plain output
+  __nv_bfloat16* C;
+  long long ldc;
+  const uint32_t* gathered_flags;             // local [tp]: raised by each owner when its rows have landed
+  // MODE_RS
+  __nv_bfloat16* stage_peer[COMM_MAX_WORLD];  // staging buffer of every rank: [tp][chunk_rows][N]
+  uint32_t* rs_flag_peer[COMM_MAX_WORLD];     // [tp] words on every rank: "source s has delivered"
+  const __nv_bfloat16* stage_local;           // this rank's staging buffer
+  const uint32_t* rs_flags_local;
+  int* owner_done;                            // local [tp + 1] counters (last = CTAs done with phase 2)
+  __nv_bfloat16* residual;                    // [rows owned, N], updated in place
+  const __nv_bfloat16* norm_w;
+  float eps;
+  __nv_bfloat16* xg_peer[COMM_MAX_WORLD];     // gathered activation buffer of every rank: [>= M, N]
+  uint32_t* gathered_flag_peer[COMM_MAX_WORLD];
+};
+
+__device__ __forceinline__ void tp_st_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// bounded wait for a flag to reach `epoch` (epochs only grow)
+__device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status) {
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (int32_t(tp_ld_acquire(flag) - epoch) >= 0) return true;
+    __nanosleep(40);
+    if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
+  }
+  report(status, ST_TIMEOUT_PEER);
+  return false;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(TP_THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const TpGemmParams p) {
+  constexpr int A_BYTES = TP_BM * TP_BK * 2, B_BYTES = TP_BN * TP_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + TP_STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + TP_STAGES;
+  uint64_t* acc_full = empty_bar + TP_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* s_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);   // [0] abort, [1] scratch
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TP_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    s_flag[0] = 0;
+    s_flag[1] = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (p.K + TP_BK - 1) / TP_BK;
+
+  // tile -> (m_blk, n_blk): grouped raster, then the m-block order is rotated by `rot` blocks so that
+  // MODE_RS starts with the chunk of rank + 1 (own chunk last) and MODE_AG with its own chunk
+  auto decode_tile = [&](int tile, int& m_blk, int& n_blk) {
+    const int padded = p.tp * p.blocks_per_chunk;            // >= num_m; blocks >= num_m are skipped
+    const int per_group = p.group_m * p.num_n;
+    const int g = tile / per_group;
+    const int first_m = g * p.group_m;
+    const int gm = min(padded - first_m, p.group_m);
+    const int local = tile - g * per_group;
+    const int m_lin = first_m + local % gm;
+    n_blk = local / gm;
+    m_blk = (m_lin + p.rot) % padded;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t seen = 0;                                   // owners whose "gathered" flag was observed
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.total_tiles && ok; w += gridDim.x) {
+        int m_blk, n_blk;
+        decode_tile(w, m_blk, n_blk);
+        if (m_blk >= p.num_m) continue;                    // padding block of the rotated order
+        if (MODE == MODE_AG) {
+          const int owner = m_blk / p.blocks_per_chunk;
+          if (owner != p.rank && !(seen & (1u << owner))) {
+            if (!tp_wait_flag(p.gathered_flags + owner, p.epoch, p.status)) {
+              s_flag[0] = 1;
+              break;
+            }
+            seen |= 1u << owner;
+            asm volatile("fence.proxy.async.global;" ::: "memory");   // peer stores -> TMA reads
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (s_flag[0] || !mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) {
+            s_flag[0] = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tma_a, &full_bar[stage], kb * TP_BK, m_blk * TP_BM);
+          tma_load_2d(sa + A_BYTES, &tma_b, &full_bar[stage], kb * TP_BK, n_blk * TP_BN);
+          if (++stage == TP_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TP_BM, TP_BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.total_tiles && ok; w += gridDim.x) {
+        int m_blk, n_blk;
+        decode_tile(w, m_blk, n_blk);
+        if (m_blk >= p.num_m) continue;
+        if (s_flag[0] || !mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, ST_TIMEOUT_ACC_EMPTY)) {
+          s_flag[0] = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * TP_BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (s_flag[0] || !mbar_wait(&full_bar[stage], phase, p.status, ST_TIMEOUT_FULL)) {
+            s_flag[0] = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t da = make_sdesc_sw128(sa), db = make_sdesc_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TP_BK / 16; ++k)
+            tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty_bar[stage]);
+          if (++stage == TP_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;
+    const int ep_tid = (warp - 2) * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < p.total_tiles; w += gridDim.x) {
+      int m_blk, n_blk;
+      decode_tile(w, m_blk, n_blk);
+      if (m_blk >= p.num_m) continue;
+      if (s_flag[0] || !mbar_wait(&acc_full[acc], acc_phase, p.status, ST_TIMEOUT_ACC_FULL)) {
+        s_flag[0] = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * TP_BN);
+      const int gi = m_blk * TP_BM + row;                 // token row
+      const int owner = m_blk / p.blocks_per_chunk;
+      __nv_bfloat16* dst_row;
+      if (MODE == MODE_RS)
+        dst_row = p.stage_peer[owner] + ((long long)p.rank * p.chunk_rows + (gi - owner * p.chunk_rows)) * p.N;
+      else
+        dst_row = p.C + (long long)gi * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < TP_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + uint32_t(c * 32), r);
+        tmem_ld_wait();
+        if (c == TP_BN / 32 - 1) {
+          tc_fence_before();
+          mbar_arrive(&acc_empty[acc]);
+        }
+        const int jb = n_blk * TP_BN + c * 32;
+        if (gi < p.M) {
+          if (jb + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+              u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+              u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+              u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst_row + jb + q * 8) = u;
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 32; ++t)
+              if (jb + t < p.N) dst_row[jb + t] = __float2bfloat16(__uint_as_float(r[t]));
+          }
+        }
+      }
+      if (MODE == MODE_RS) {
+        // this tile is delivered: count it, and raise the owner's flag after the last one
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_tid == 0) {
+          const int first = owner * p.blocks_per_chunk;
+          const int nblk = max(0, min(p.num_m - first, p.blocks_per_chunk));
+          const int old = atomicAdd(&p.owner_done[owner], 1);
+          if (old + 1 == nblk * p.num_n) tp_st_release(p.rs_flag_peer[owner] + p.rank, p.epoch);
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (MODE != MODE_RS) return;
+
+  // ------------------------------------------------------------------ phase 2: rows owned by this rank
+  const int row0 = p.rank * p.chunk_rows;
+  const int my_rows = max(0, min(p.M - row0, p.chunk_rows));
+  if (my_rows > 0 && !s_flag[0]) {
+    if (threadIdx.x < p.tp) {
+      if (!tp_wait_flag(p.rs_flags_local + threadIdx.x, p.epoch, p.status)) s_flag[0] = 1;
+    }
+    __syncthreads();
+    if (!s_flag[0]) {
+      __shared__ float red[TP_THREADS / 32];
+      const int chunks = p.N >> 3;                         // 16-byte pieces per row
+      constexpr int MAXC = 6;                              // 192 threads * 6 * 8 = 9216 columns
+      for (int r = blockIdx.x; r < my_rows; r += gridDim.x) {
+        float v[MAXC][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+          const int idx = threadIdx.x + c * TP_THREADS;
+          if (idx < chunks) {
+            float acc8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc8[i] = 0.f;
+            for (int s = 0; s < p.tp; ++s) {
+              const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
+                  p.stage_local + ((long long)s * p.chunk_rows + r) * p.N + idx * 8));
+              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h2[i]);
+                acc8[2 * i] += f.x;
+                acc8[2 * i + 1] += f.y;
+              }
+            }
+            uint4* rp = reinterpret_cast<uint4*>(p.residual + (long long)r * p.N + idx * 8);
+            const uint4 ru = *rp;
+            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&ru);
+            uint4 su;
+            uint32_t* sw = reinterpret_cast<uint32_t*>(&su);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(rh[i]);
+              sw[i] = pack_bf16(acc8[2 * i] + f.x, acc8[2 * i + 1] + f.y);
+            }
+            *rp = su;
+            const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(sh[i]);
+              v[c][2 * i] = f.x;
+              v[c][2 * i + 1] = f.y;
+              ss += f.x * f.x + f.y * f.y;
+            }
+          }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < TP_THREADS / 32; ++wq) tot += red[wq];
+        __syncthreads();
+        const float inv = rsqrtf(tot / float(p.N) + p.eps);
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+          const int idx = threadIdx.x + c * TP_THREADS;
+          if (idx < chunks) {
+            const uint4 gu = *reinterpret_cast<const uint4*>(p.norm_w + idx * 8);
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
+            uint4 ou;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&ou);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 g2 = __bfloat1622float2(gh[i]);
+              const float a = __bfloat162float(__float2bfloat16(v[c][2 * i] * inv)) * g2.x;
+              const float b = __bfloat162float(__float2bfloat16(v[c][2 * i + 1] * inv)) * g2.y;
+              ow[i] = pack_bf16(a, b);
+            }
+            const long long off = (long long)(row0 + r) * p.N + idx * 8;
+            for (int d = 0; d < p.tp; ++d) *reinterpret_cast<uint4*>(p.xg_peer[d] + off) = ou;
+          }
+        }
+      }
+    }
+  }
+  // the last CTA to get here publishes "rows of this rank are gathered" everywhere and resets the counters
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&p.owner_done[p.tp], 1);
+    if (old == int(gridDim.x) - 1) {
+      for (int o = 0; o <= p.tp; ++o) p.owner_done[o] = 0;
+      __threadfence_system();
+      for (int d = 0; d < p.tp; ++d) tp_st_release(p.gathered_flag_peer[d] + p.rank, p.epoch);
+    }
+  }
+}
+
+static int tp_smem_bytes() { return TP_STAGES * (TP_BM * TP_BK * 2 + TP_BN * TP_BK * 2) + 256 + 1024; }
+
+static void fill_common(TpGemmParams& p, int M, int N, int K, int tp, int rank, int chunk_rows, uint32_t epoch,
+                        uint32_t* status, bool own_first) {
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_n = (N + TP_BN - 1) / TP_BN;
+  p.tp = tp;
+  p.rank = rank;
+  p.chunk_rows = chunk_rows;
+  p.blocks_per_chunk = chunk_rows / TP_BM;
+  p.num_m = (M + TP_BM - 1) / TP_BM;
+  p.group_m = std::min(16, p.blocks_per_chunk);
+  // the rotated order runs over tp * blocks_per_chunk m-blocks; blocks >= num_m are skipped by every role
+  p.total_tiles = tp * p.blocks_per_chunk * p.num_n;
+  p.rot = ((own_first ? rank : rank + 1) % tp) * p.blocks_per_chunk;
+  p.epoch = epoch;
+  p.status = status;
+}
+
+void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                      const TpBuffers& b, void* residual, const void* norm_w, float eps, int chunk_rows,
+                      uint32_t epoch, uint32_t* status, int sm_limit, cudaStream_t stream) {
+  if (M <= 0) return;
+  if (chunk_rows % TP_BM != 0 || N % 8 != 0 || N > TP_THREADS * 6 * 8)
+    throw std::runtime_error("gemm_rs_add_norm: chunk_rows must be a multiple of 128 and N <= 9216, N % 8 == 0");
+  TpGemmParams p{};
+  fill_common(p, M, N, K, b.world, b.rank, chunk_rows, epoch, status, false);
+  // the grouped raster must see `padded` m-blocks
+  const int padded_m = p.tp * p.blocks_per_chunk;
+  const int real_num_m = p.num_m;
+  for (int i = 0; i < b.world; ++i) {
+    p.stage_peer[i] = b.stage[i];
+    p.rs_flag_peer[i] = b.rs_flags[i];
+    p.xg_peer[i] = b.xg[i];
+    p.gathered_flag_peer[i] = b.gathered_flags[i];
+  }
+  p.stage_local = b.stage[b.rank];
+  p.rs_flags_local = b.rs_flags[b.rank];
+  p.owner_done = b.owner_done;
+  p.residual = reinterpret_cast<__nv_bfloat16*>(residual);
+  p.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
+  p.eps = eps;
+  (void)padded_m;
+  (void)real_num_m;
+  const CUtensorMap ta = make_tmap_bf16_2d(x, M, K, ldx, TP_BM, TP_BK);
+  const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
+  const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
+  auto kern = gemm_tp_kernel<MODE_RS>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+  // every CTA takes part in the flag exchange of phase 2: the grid must be fully resident
+  kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("gemm_rs_add_norm launch: ") + cudaGetErrorString(e));
+}
+
+void gemm_after_gather(const void* xg_local, const void* w, void* c, int M, int N, int K, long long ldw,
+                       long long ldc, const TpBuffers& b, int chunk_rows, uint32_t epoch, uint32_t* status,
+                       int sm_limit, cudaStream_t stream) {
+  if (M <= 0) return;
+  TpGemmParams p{};
+  fill_common(p, M, N, K, b.world, b.rank, chunk_rows, epoch, status, true);
+  p.C = reinterpret_cast<__nv_bfloat16*>(c);
+  p.ldc = ldc;
+  p.gathered_flags = b.gathered_flags[b.rank];
+  const CUtensorMap ta = make_tmap_bf16_2d(xg_local, M, K, K, TP_BM, TP_BK);
+  const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
+  const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
+  auto kern = gemm_tp_kernel<MODE_AG>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+  kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("gemm_after_gather launch: ") + cudaGetErrorString(e));
+}
+
+}  // namespace fc

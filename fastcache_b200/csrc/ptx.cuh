@@ -23,7 +23,7 @@ enum : uint32_t {
 };
 
 #ifndef FC_SPIN_LIMIT
-#define FC_SPIN_LIMIT (1u << 26)
+#define FC_SPIN_LIMIT (1u << 22)   // a few seconds of polling at most, then the kernel unwinds
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -62,10 +62,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false after FC_SPIN_LIMIT unsuccessful polls.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  One try_wait may itself block for a hardware-defined interval, so the bound is
+// on elapsed time (FC_WAIT_LIMIT_NS, about a second) as well as on the number of polls.
+// Returns false when the bound is reached; the caller unwinds.
+#ifndef FC_WAIT_LIMIT_NS
+#define FC_WAIT_LIMIT_NS 1500000000ull
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 0; i < FC_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && global_timer_ns() - t0 > FC_WAIT_LIMIT_NS) break;
   }
   report(status, code);
   return false;

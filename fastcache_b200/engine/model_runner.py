@@ -128,8 +128,9 @@ class ModelRunner:
         self.fused_comm = None
         if self.tp_size > 1 and self.device.type == "cuda" and not config.extra.get("disable_fused_comm", False):
             from ..parallel import symm
+            big = 0 if config.extra.get("disable_fused_prefill", False) else config.max_num_batched_tokens
             self.fused_comm = symm.enable(int(config.extra.get("fused_comm_tokens", 512)), tc.hidden_size,
-                                          self.device)
+                                          self.device, max_tokens=big)
         self.sampler = Sampler(config.seed)
         self.io = {"h2d_bytes": 0, "d2h_bytes": 0}      # host<->device traffic of the step loop
         self.timer: Optional[DeviceTimer] = None        # set by benchmarks to time device work only

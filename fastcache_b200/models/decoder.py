@@ -27,7 +27,7 @@ from ..layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from ..layers.layernorm import RMSNorm
 from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
 from ..layers.rotary_embedding import get_rope
-from ..parallel.fused import row_linear_reduce_add_norm
+from ..parallel.fused import get_fused_comm, row_linear_reduce_add_norm
 
 
 class DecoderAttention(nn.Module):
@@ -112,6 +112,9 @@ class DecoderModel(nn.Module):
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1].input_layernorm.weight if i + 1 < n else self.norm.weight
             normed, residual = layer(positions, normed, residual, nxt)
+        comm = get_fused_comm()
+        if comm is not None:
+            normed = comm.finish_forward(normed)
         return normed
 
 

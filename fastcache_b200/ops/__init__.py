@@ -57,6 +57,13 @@ def silu_and_mul(x):
 def linear(x, weight, bias=None, act: str = "none", out: Optional[torch.Tensor] = None):
     """y = act(x @ weight.T + bias).  weight is [N, K] as in nn.Linear."""
     if x.is_cuda:
+        from ..parallel.fused import get_fused_comm
+        comm = get_fused_comm()
+        if comm is not None and getattr(comm, "_gather", None) is not None and out is None:
+            # x may be the gathered activation buffer that is still filling up over NVLink
+            y = comm.gathered_linear(x, weight, bias, act)
+            if y is not None:
+                return y
         from .gemm import gemm
         _n(2 if act == "swiglu" else 1)
         return gemm(x, weight, bias, act, out)

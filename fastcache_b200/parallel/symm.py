@@ -1,15 +1,21 @@
-"""Symmetric-memory staging buffers and the fused communication path.
+"""Symmetric-memory staging buffers and the fused communication paths.
 
-Each rank allocates two activation staging buffers and a small flag array in
-symmetric memory (`torch.distributed._symmetric_memory`: CUDA VMM allocations
-whose peer mappings and NVSwitch multicast address are exchanged over the
-process group once).  The kernels in csrc/comm.cu then read and write peers'
-buffers directly over NVLink; NCCL is left with bootstrap, small control
-messages and the library baseline.
+Each rank allocates its buffers in symmetric memory (`torch.distributed._symmetric_memory`:
+CUDA VMM allocations whose peer mappings and NVSwitch multicast address are exchanged over the
+process group once).  The kernels in csrc/comm.cu and csrc/gemm_tp.cu then read and write the
+peers' buffers directly over NVLink; NCCL is left with bootstrap, small control messages and the
+library baseline.
 
-`FusedComm.row_linear_reduce_add_norm` is what the decoder layers call for
-"row-parallel GEMM -> sum over ranks -> + residual -> RMSNorm" when the tensors
-are on a CUDA device and tensor parallelism is on.
+`FusedComm.row_linear_reduce_add_norm` is what the decoder layers call for "row-parallel GEMM ->
+sum over ranks -> + residual -> RMSNorm":
+
+  * decode-size inputs (T <= one_shot_max_tokens): the GEMM writes its partial sums into a
+    symmetric buffer and ONE kernel does flag exchange + all-reduce (peer loads or
+    multimem.ld_reduce) + residual add + RMSNorm; the residual stream stays replicated.
+  * prefill-size inputs: ONE kernel does GEMM + reduce-scatter (peer stores from the epilogue) +
+    residual add + RMSNorm on the owned rows + the send half of the all-gather; the residual
+    stream is sharded by token rows between layers.  The next column-parallel GEMM
+    (`gathered_linear`) waits per chunk for the rows to land and runs while later chunks arrive.
 """
 from __future__ import annotations
 
@@ -29,22 +35,23 @@ MAX_WORLD = 8
 
 
 class FusedComm:
-    def __init__(self, max_tokens: int, hidden: int, device: torch.device, use_multimem: Optional[bool] = None,
-                 one_shot_max_tokens: int = 512):
+    def __init__(self, one_shot_tokens: int, hidden: int, device: torch.device, max_tokens: int = 0,
+                 use_multimem: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
         if not tpmod.is_tp_initialized():
             raise RuntimeError("tensor parallelism is not initialised")
         self.world, self.rank = tpmod.get_tp_size(), tpmod.get_tp_rank()
         if self.world > MAX_WORLD:
             raise ValueError(f"fused communication supports up to {MAX_WORLD} ranks")
-        self.device = device
-        self.hidden = hidden
-        self.max_tokens = max_tokens
-        self.one_shot_max_tokens = min(one_shot_max_tokens, max_tokens)
+        self.device, self.hidden = device, hidden
+        self.one_shot_max_tokens = one_shot_tokens
         group = tpmod.get_tp_group()
         name = group.group_name
-        self._symm = symm_mem
-        self.bufs = [symm_mem.empty((max_tokens, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        bf16 = torch.bfloat16
+
+        # ---- one-shot all-reduce + add + norm (decode)
+        self.bufs = [symm_mem.empty((one_shot_tokens, hidden), dtype=bf16, device=device) for _ in range(2)]
         self.flags = symm_mem.empty((MAX_SLOTS * MAX_WORLD,), dtype=torch.int32, device=device)
         self.flags.zero_()
         self.handles = [symm_mem.rendezvous(b, name) for b in self.bufs]
@@ -53,36 +60,95 @@ class FusedComm:
         if use_multimem is None:
             use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
         self.use_multimem = bool(use_multimem and all(mc))
-        index = device.index if device.index is not None else torch.cuda.current_device()
         ext().comm_init(self.rank, self.world, [int(p) for p in self.handles[0].buffer_ptrs],
                         [int(p) for p in self.handles[1].buffer_ptrs],
                         [int(p) for p in self.flag_handle.buffer_ptrs], mc[0], mc[1], index)
         self.status = ext().status_tensor(index)
         self.cur = 0
+
+        # ---- GEMM + reduce-scatter + add + norm / all-gather + GEMM (prefill)
+        self.max_tokens = 0
+        self.epoch = 0
+        self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
+        if max_tokens > one_shot_tokens:
+            per_rank = -(-max_tokens // self.world)
+            self.chunk_max = -(-per_rank // 128) * 128
+            self.max_tokens = max_tokens
+            self.stage = symm_mem.empty((self.world * self.chunk_max, hidden), dtype=bf16, device=device)
+            self.xg = symm_mem.empty((self.chunk_max * self.world, hidden), dtype=bf16, device=device)
+            self.tp_flags = symm_mem.empty((2 * MAX_WORLD,), dtype=torch.int32, device=device)
+            self.tp_flags.zero_()
+            hs, hx, hf = (symm_mem.rendezvous(t, name) for t in (self.stage, self.xg, self.tp_flags))
+            self._tp_handles = (hs, hx, hf)
+            ext().tp_init(self.rank, self.world, [int(p) for p in hs.buffer_ptrs], [int(p) for p in hx.buffer_ptrs],
+                          [int(p) for p in hf.buffer_ptrs], self.chunk_max, self.chunk_max * self.world, hidden, index)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
+    # ------------------------------------------------------------------ forward hooks
     def begin_forward(self) -> None:
-        """Every forward pass starts on staging buffer 0 and makes an even number of calls,
+        """Every forward pass starts on staging buffer 0 and makes an even number of one-shot calls,
         so consecutive passes (eager or replayed from a graph) keep alternating buffers."""
         self.cur = 0
+        self._gather = None
 
+    def finish_forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        """The last normalised activations may still be arriving: order the stream after them."""
+        if self._gather is not None and hidden.data_ptr() == self.xg.data_ptr():
+            ext().wait_gathered(self._gather[0], self.status)
+            ops._n()
+            self._gather = None
+        return hidden
+
+    def chunk_rows_for(self, T: int) -> int:
+        return -(-(-(-T // self.world)) // 128) * 128
+
+    # --------------------------------------------------------------------- the fused unit
     def row_linear_reduce_add_norm(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                                    residual: torch.Tensor, norm_weight: torch.Tensor, eps: float
                                    ) -> Tuple[torch.Tensor, torch.Tensor]:
         T = x.shape[0]
-        if T > self.one_shot_max_tokens:
-            return self._large(x, weight, bias, residual, norm_weight, eps)
-        buf = self.cur
-        self.cur ^= 1
-        staging = self.bufs[buf][:T]
-        ops.linear(x, weight, bias, out=staging)           # partial sums land in symmetric memory
+        if T <= self.one_shot_max_tokens:
+            buf = self.cur
+            self.cur ^= 1
+            staging = self.bufs[buf][:T]
+            ops.linear(x, weight, bias, out=staging)           # partial sums land in symmetric memory
+            ops._n()
+            y = ext().allreduce_add_rmsnorm(buf, residual, norm_weight, float(eps), self.use_multimem, self.status)
+            return y, residual
+        if bias is not None or T > self.max_tokens or weight.shape[0] != self.hidden:
+            return self._library(x, weight, bias, residual, norm_weight, eps)
+        chunk = self.chunk_rows_for(T)
+        lo = min(T, self.rank * chunk)
+        hi = min(T, lo + chunk)
+        if residual.shape[0] == T and not getattr(residual, "_fc_shard", False):
+            # first call of the pass: keep only the rows this rank owns (the residual stream is
+            # sharded by token rows until the end of the pass)
+            residual = residual[lo:hi].contiguous()
+            residual._fc_shard = True
+        self.epoch += 1
         ops._n()
-        y = ext().allreduce_add_rmsnorm(buf, residual, norm_weight, float(eps), self.use_multimem, self.status)
-        return y, residual
+        ext().gemm_rs_add_norm(x, weight, residual, norm_weight, float(eps), chunk, self.epoch, self.status, 0)
+        self._gather = (self.epoch, chunk, T)
+        return self.xg[:T], residual
 
-    def _large(self, x, weight, bias, residual, norm_weight, eps):
-        # prefill-size inputs: library all-reduce until the GEMM + reduce-scatter kernel takes over
+    def gathered_linear(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                        act: str = "none") -> Optional[torch.Tensor]:
+        """Column-parallel GEMM whose input is the gathered buffer that is still filling up.
+        Returns None when the caller should run the plain GEMM: `x` is another tensor, or the
+        projection has a bias / activation, in which case the stream is first ordered after the
+        arrival of all rows."""
+        g = self._gather
+        if g is None or x.data_ptr() != self.xg.data_ptr():
+            return None
+        ops._n()
+        if bias is not None or act != "none" or x.shape[0] != g[2] or not x.is_contiguous():
+            ext().wait_gathered(g[0], self.status)
+            self._gather = None
+            return None
+        return ext().gemm_after_gather(x, weight, g[1], g[0], self.status, 0)
+
+    def _library(self, x, weight, bias, residual, norm_weight, eps):
         y = ops.linear(x, weight, bias)
         tpmod.tp_all_reduce(y)
         return ops.add_rms_norm(y, residual, norm_weight, eps)
@@ -91,8 +157,8 @@ class FusedComm:
         ext().comm_shutdown()
 
 
-def enable(max_tokens: int, hidden: int, device: torch.device, **kw) -> FusedComm:
-    comm = FusedComm(max_tokens, hidden, device, **kw)
+def enable(one_shot_tokens: int, hidden: int, device: torch.device, **kw) -> FusedComm:
+    comm = FusedComm(one_shot_tokens, hidden, device, **kw)
     fused_mod.set_fused_comm(comm)
     return comm
 

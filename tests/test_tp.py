@@ -38,6 +38,11 @@ def test_tp2_gpu_fused_comm(tmp_path):
     two = _run(2, "cuda", str(tmp_path / "b.json"), 29632)
     assert two["status"] == 0
     assert two["allreduce_max_err"] < 6e-2
+    assert two["fused_prefill_max_err"] < 8e-2
+    # same engine with the one-shot limit lowered so that prefill takes the GEMM + reduce-scatter path
+    big = _run(2, "cuda", str(tmp_path / "c.json"), 29633, ["--one-shot-tokens", "64"])
+    assert big["status"] == 0
+    assert sum(a[0] == b[0] for a, b in zip(one["tokens"], big["tokens"])) >= len(one["tokens"]) - 1, (one, big)
     # bf16 summation order differs between 1 and 2 ranks: the first tokens (pure prefill) agree
     same = sum(a[0] == b[0] for a, b in zip(one["tokens"], two["tokens"]))
     assert same >= len(one["tokens"]) - 1, (one, two)

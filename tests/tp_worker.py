@@ -20,6 +20,7 @@ def main():
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--out", required=True)
     ap.add_argument("--kv-heads", type=int, default=2)
+    ap.add_argument("--one-shot-tokens", type=int, default=512)
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
@@ -35,7 +36,33 @@ def main():
         from fastcache_b200.ops import reference as ref
         from fastcache_b200.parallel import symm
         torch.cuda.set_device(local)
-        comm = symm.enable(512, 1024, torch.device(device))
+        comm = symm.enable(512, 1024, torch.device(device), max_tokens=4096)
+        # GEMM + reduce-scatter + add + norm, then all-gather + GEMM, against the library all-reduce
+        fused_errs = []
+        for it, T in enumerate([600, 1000, 4096, 777]):
+            gx = torch.Generator(device="cpu").manual_seed(1000 + 10 * it + rank)
+            x = (torch.randn(T, 256, generator=gx) * 0.5).to(torch.bfloat16).to(device)
+            wr = (torch.randn(1024, 256, generator=gx) * 0.05).to(torch.bfloat16).to(device)
+            gs = torch.Generator(device="cpu").manual_seed(2000 + it)
+            resid = torch.randn(T, 1024, generator=gs).to(torch.bfloat16).to(device)
+            nw = (1.0 + 0.1 * torch.randn(1024, generator=gs)).to(torch.bfloat16).to(device)
+            wc = (torch.randn(768, 1024, generator=gs) * 0.05).to(torch.bfloat16).to(device)
+            total = x.float() @ wr.float().T
+            torch.distributed.all_reduce(total)
+            want_n, want_r = ref.add_rms_norm(total.to(torch.bfloat16), resid.clone(), nw, 1e-6)
+            want_y = want_n.float() @ wc.float().T
+            comm.begin_forward()
+            normed, shard = comm.row_linear_reduce_add_norm(x, wr, None, resid.clone(), nw, 1e-6)
+            y = ops.linear(normed, wc)                      # all-gather + GEMM path
+            normed = comm.finish_forward(normed)
+            torch.cuda.synchronize()
+            chunk = comm.chunk_rows_for(T)
+            lo, hi = min(T, rank * chunk), min(T, rank * chunk + chunk)
+            fused_errs.append(float((normed.float() - want_n.float()).abs().max()))
+            fused_errs.append(float((shard.float() - want_r[lo:hi].float()).abs().max()) if hi > lo else 0.0)
+            fused_errs.append(float((y.float() - want_y).abs().max()) / max(1.0, float(want_y.abs().max())))
+            torch.distributed.barrier()
+        res["fused_prefill_max_err"] = max(fused_errs)
         g = torch.Generator(device="cpu").manual_seed(100 + rank)
         errs = []
         for it, T in enumerate([1, 7, 128, 300]):
@@ -62,7 +89,7 @@ def main():
                             intermediate_size=1024, vocab_size=2000)
     llm = LLM(cfg, device=device, dtype="bf16" if a.device == "cuda" else "fp32", tensor_parallel_size=world,
               kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=256, max_num_seqs=8,
-              enforce_eager=False, init_device="cpu")
+              enforce_eager=False, init_device="cpu", fused_comm_tokens=a.one_shot_tokens)
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (9, 40, 77, 120)]
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
