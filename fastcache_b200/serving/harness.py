@@ -1,0 +1,475 @@
+"""Concurrent serving harness: arrival process, three-stage batching, per-request timing.
+
+Parity with the reference's HuggingFace-based harness:
+  * request structs and life cycle            utils_ccm/utils_requests.py:7-127
+  * TimestampManager (9 stage timestamps -> queue / process times, TTFT = prefill finish -
+    prefill queueing start, TPOT = decode time / generated length, latency, normalised
+    latency)                                   utils_ccm/utils_schedule_v11.py:27-193
+  * GPUMonitor (sampling thread, CSV)          utils_ccm/utils_schedule_v11.py:196-310
+  * DynamicScheduler (prefill and decode priority queues; shorter first with ageing toward
+    max_wait_time; prefill goes first but waits for a full batch or max_wait_time; decode batch =
+    longest prefix whose cumulative size fits the decode cap)
+                                               utils_ccm/utils_schedule_v11.py:431-803
+  * KVCachePool (request id -> per-layer (K, V), store / get / release / merge_and_pop / pop)
+                                               utils_ccm/utils_kvcachePool.py:22-394
+  * ImprovedConcurrentTester, PerformanceMonitor, TestResult (collector + dispatcher threads,
+    p50 / p90 / p99, throughput)               scripts/llava_testcon2.6.py:100-222, :385-1695
+The reference drives HuggingFace `generate`; here the tester drives this package's engine, whose
+scheduler already has the prefill / compress / decode queues with their batch caps, so the
+harness supplies the arrival process, the per-stage batching rule for the caps, timing and
+reporting.
+"""
+from __future__ import annotations
+
+import heapq
+import math
+import random
+import threading
+import time
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+# ------------------------------------------------------------------------ requests
+class RequestStatus(Enum):
+    PENDING = "pending"
+    PREFILLING = "prefilling"
+    COMPRESSING = "compressing"
+    DECODING = "decoding"
+    COMPLETED = "completed"
+    FAILED = "failed"
+
+
+@dataclass
+class RequestMetrics:
+    arrival: float = 0.0
+    prefill_start: float = 0.0
+    prefill_end: float = 0.0
+    compress_start: float = 0.0
+    compress_end: float = 0.0
+    decode_start: float = 0.0
+    decode_end: float = 0.0
+    generated: int = 0
+
+    @property
+    def ttft(self) -> float:
+        return self.prefill_end - self.arrival
+
+    @property
+    def tpot(self) -> float:
+        return (self.decode_end - self.decode_start) / max(1, self.generated)
+
+    @property
+    def latency(self) -> float:
+        return self.decode_end - self.arrival
+
+
+@dataclass
+class Request:
+    request_id: int
+    prompt: Any
+    max_tokens: int = 64
+    image: Any = None
+    status: RequestStatus = RequestStatus.PENDING
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
+    output: List[int] = field(default_factory=list)
+    error: Optional[str] = None
+
+    @property
+    def input_len(self) -> int:
+        return len(self.prompt) if not isinstance(self.prompt, str) else len(self.prompt.split())
+
+    def fail(self, why: str) -> None:
+        self.status, self.error = RequestStatus.FAILED, why
+
+
+@dataclass(order=True)
+class PrioritizedRequest:
+    priority: float
+    seq: int
+    request: Any = field(compare=False)
+
+
+PriorityRequest = PrioritizedRequest
+
+
+# ---------------------------------------------------------------------- timestamps
+class TimestampManager:
+    STAGES = ("arrival", "prefill_queueing_start", "prefill_start", "prefill_finish", "compress_queueing_start",
+              "compress_start", "compress_finish", "decoding_queueing_start", "decoding_start", "decoding_finish")
+
+    def __init__(self) -> None:
+        self._t: Dict[int, Dict[str, float]] = {}
+        self._lock = threading.Lock()
+
+    def record(self, request_id: int, stage: str, t: Optional[float] = None) -> None:
+        with self._lock:
+            self._t.setdefault(request_id, {})[stage] = time.perf_counter() if t is None else t
+
+    def get(self, request_id: int) -> Dict[str, float]:
+        with self._lock:
+            return dict(self._t.get(request_id, {}))
+
+    def analyze(self, request_id: int, generated_len: int = 1) -> Dict[str, float]:
+        t = self.get(request_id)
+        g = lambda k, d=0.0: t.get(k, d)  # noqa: E731
+        out = {
+            "prefill_queue": g("prefill_start") - g("prefill_queueing_start", g("arrival")),
+            "prefill_process": g("prefill_finish") - g("prefill_start"),
+            "compress_queue": g("compress_start") - g("compress_queueing_start", g("prefill_finish")),
+            "compress_process": g("compress_finish") - g("compress_start"),
+            "decoding_queue": g("decoding_start") - g("decoding_queueing_start", g("prefill_finish")),
+            "decoding_process": g("decoding_finish") - g("decoding_start"),
+            "ttft": g("prefill_finish") - g("prefill_queueing_start", g("arrival")),
+            "latency": g("decoding_finish") - g("arrival"),
+        }
+        out["tpot"] = out["decoding_process"] / max(1, generated_len)
+        out["normalized_latency"] = out["latency"] / max(1, generated_len)
+        return out
+
+
+# --------------------------------------------------------------------- GPU monitor
+class GPUMonitor(threading.Thread):
+    """Samples utilisation and memory every `period` seconds, tagged with the current stage."""
+
+    def __init__(self, device_index: int = 0, period: float = 0.05):
+        super().__init__(daemon=True)
+        self.device_index, self.period = device_index, period
+        self.stage = "idle"
+        self.samples: List[Dict[str, Any]] = []
+        self._halt = threading.Event()
+
+    def run(self) -> None:
+        nv = handle = None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self.device_index)
+        except Exception:
+            nv = None
+        t0 = time.perf_counter()
+        while not self._halt.is_set():
+            row: Dict[str, Any] = {"t": time.perf_counter() - t0, "stage": self.stage}
+            if nv is not None:
+                try:
+                    u = nv.nvmlDeviceGetUtilizationRates(handle)
+                    m = nv.nvmlDeviceGetMemoryInfo(handle)
+                    row.update(gpu_util=u.gpu, mem_util=u.memory, mem_used_gb=m.used / 2 ** 30)
+                except Exception:
+                    pass
+            if torch.cuda.is_available():
+                row["torch_allocated_gb"] = torch.cuda.memory_allocated() / 2 ** 30
+            self.samples.append(row)
+            self._halt.wait(self.period)
+
+    def stop(self) -> List[Dict[str, Any]]:
+        self._halt.set()
+        self.join(timeout=2)
+        return self.samples
+
+    def to_csv(self, path: str) -> None:
+        import csv
+        keys = sorted({k for r in self.samples for k in r})
+        with open(path, "w", newline="") as fh:
+            w = csv.DictWriter(fh, fieldnames=keys)
+            w.writeheader()
+            w.writerows(self.samples)
+
+
+# -------------------------------------------------------------------- KV cache pool
+class KVCachePool:
+    """Request id -> list of per-layer (K, V) in HF layout [1, H, S, D] (lock protected)."""
+
+    def __init__(self, max_entries: int = 0) -> None:
+        self._pool: Dict[int, List[Tuple[torch.Tensor, torch.Tensor]]] = {}
+        self._lock = threading.Lock()
+        self.max_entries = max_entries
+        self.stores = self.releases = 0
+
+    def store_kvcache(self, request_ids: Sequence[int], kv_cache: Sequence[Tuple[torch.Tensor, torch.Tensor]],
+                      lengths: Optional[Sequence[int]] = None) -> None:
+        """Splits a batch along dim 0 (optionally trimming left padding to `lengths`)."""
+        with self._lock:
+            for b, rid in enumerate(request_ids):
+                entry = []
+                for k, v in kv_cache:
+                    kb, vb = k[b:b + 1], v[b:b + 1]
+                    if lengths is not None:
+                        kb, vb = kb[:, :, -lengths[b]:], vb[:, :, -lengths[b]:]
+                    entry.append((kb.contiguous(), vb.contiguous()))
+                self._pool[rid] = entry
+                self.stores += 1
+
+    def get(self, request_id: int):
+        with self._lock:
+            return self._pool.get(request_id)
+
+    def pop_kvcache(self, request_id: int):
+        with self._lock:
+            return self._pool.pop(request_id, None)
+
+    def release(self, request_id: int) -> bool:
+        with self._lock:
+            self.releases += 1
+            return self._pool.pop(request_id, None) is not None
+
+    def clear(self) -> None:
+        with self._lock:
+            self._pool.clear()
+
+    def merge_and_pop(self, request_ids: Sequence[int]):
+        """Concatenate the entries of `request_ids` along the batch dim (left-padding to the longest)."""
+        entries = [self.pop_kvcache(r) for r in request_ids]
+        entries = [e for e in entries if e is not None]
+        if not entries:
+            return None, []
+        lens = [e[0][0].shape[2] for e in entries]
+        S = max(lens)
+        merged = []
+        for layer in range(len(entries[0])):
+            ks, vs = [], []
+            for e, n in zip(entries, lens):
+                k, v = e[layer]
+                if n < S:
+                    pad = (0, 0, S - n, 0)
+                    k, v = torch.nn.functional.pad(k, pad), torch.nn.functional.pad(v, pad)
+                ks.append(k)
+                vs.append(v)
+            merged.append((torch.cat(ks, 0), torch.cat(vs, 0)))
+        return merged, lens
+
+    def get_stats(self) -> Dict[str, Any]:
+        with self._lock:
+            byts = sum(k.numel() * k.element_size() + v.numel() * v.element_size()
+                       for e in self._pool.values() for k, v in e)
+            return {"entries": len(self._pool), "bytes": byts, "stores": self.stores, "releases": self.releases}
+
+
+# ----------------------------------------------------------------- dynamic scheduler
+class DynamicScheduler:
+    """Two priority queues with the reference's selection rule.
+
+    priority = size * (1 - aged share): shorter requests first, and a request that has waited
+    `max_wait_time` gets the top priority.  `select_batch` returns ("prefill" | "decoding", batch):
+    prefill wins whenever a prefill is queued, but is held until `max_batch_size` requests are
+    queued or `max_wait_time` has passed since the last prefill; a decode batch is the longest prefix
+    (in priority order) whose cumulative request sizes stay within `std_batch_threshold_decoding`.
+    """
+
+    def __init__(self, max_batch_size: int = 15, std_batch_threshold_decoding: int = 90,
+                 max_wait_time: float = 0.5, compress_batch_size: int = 45):
+        self.max_batch_size = max_batch_size
+        self.std_batch_threshold_decoding = std_batch_threshold_decoding
+        self.compress_batch_size = compress_batch_size
+        self.max_wait_time = max_wait_time
+        self._prefill: List[PrioritizedRequest] = []
+        self._decode: List[PrioritizedRequest] = []
+        self._n = 0
+        self._last_prefill = time.perf_counter()
+        self._lock = threading.Lock()
+        # kept for interface parity: the reference carries PID gains but leaves the batch size fixed
+        self.kp, self.ki, self.kd = 0.5, 0.1, 0.05
+
+    def _priority(self, size: float, arrival: float) -> float:
+        waited = time.perf_counter() - arrival
+        return size * max(0.0, 1.0 - waited / max(self.max_wait_time, 1e-6))
+
+    def add_prefill(self, request: Any, size: int, arrival: Optional[float] = None) -> None:
+        with self._lock:
+            self._n += 1
+            heapq.heappush(self._prefill, PrioritizedRequest(self._priority(size, arrival or time.perf_counter()),
+                                                             self._n, (request, size, arrival or time.perf_counter())))
+
+    def add_decoding(self, request: Any, size: int = 1, arrival: Optional[float] = None) -> None:
+        with self._lock:
+            self._n += 1
+            heapq.heappush(self._decode, PrioritizedRequest(self._priority(size, arrival or time.perf_counter()),
+                                                            self._n, (request, size, arrival or time.perf_counter())))
+
+    def qsize(self) -> Tuple[int, int]:
+        with self._lock:
+            return len(self._prefill), len(self._decode)
+
+    def _reprioritise(self, heap: List[PrioritizedRequest]) -> None:
+        items = [PrioritizedRequest(self._priority(p.request[1], p.request[2]), p.seq, p.request) for p in heap]
+        heap[:] = items
+        heapq.heapify(heap)
+
+    def select_batch(self, now: Optional[float] = None) -> Tuple[Optional[str], List[Any]]:
+        now = time.perf_counter() if now is None else now
+        with self._lock:
+            if self._prefill:
+                full = len(self._prefill) >= self.max_batch_size
+                waited = now - self._last_prefill >= self.max_wait_time
+                if full or waited:
+                    self._reprioritise(self._prefill)
+                    n = min(self.max_batch_size, len(self._prefill))
+                    batch = [heapq.heappop(self._prefill).request[0] for _ in range(n)]
+                    self._last_prefill = now
+                    return "prefill", batch
+                if not self._decode:
+                    return None, []
+            if self._decode:
+                self._reprioritise(self._decode)
+                batch, used = [], 0
+                while self._decode:
+                    size = self._decode[0].request[1]
+                    if batch and used + size > self.std_batch_threshold_decoding:
+                        break
+                    batch.append(heapq.heappop(self._decode).request[0])
+                    used += size
+                return "decoding", batch
+        return None, []
+
+
+# ---------------------------------------------------------------------- monitoring
+@dataclass
+class TestResult:
+    num_requests: int = 0
+    completed: int = 0
+    failed: int = 0
+    wall_s: float = 0.0
+    output_tokens: int = 0
+    throughput_tok_s: float = 0.0
+    request_rate: float = 0.0
+    ttft: Dict[str, float] = field(default_factory=dict)
+    tpot: Dict[str, float] = field(default_factory=dict)
+    latency: Dict[str, float] = field(default_factory=dict)
+    compression: Dict[str, Any] = field(default_factory=dict)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self.__dict__)
+
+
+class PerformanceMonitor:
+    @staticmethod
+    def percentiles(xs: Sequence[float]) -> Dict[str, float]:
+        if not xs:
+            return {}
+        s = sorted(xs)
+        pick = lambda q: s[min(len(s) - 1, max(0, int(round(q * (len(s) - 1)))))]  # noqa: E731
+        return {"mean": sum(s) / len(s), "p50": pick(0.5), "p90": pick(0.9), "p99": pick(0.99), "max": s[-1]}
+
+    def summarise(self, requests: Sequence[Request], wall_s: float, rate: float, stats: Any = None) -> TestResult:
+        done = [r for r in requests if r.status is RequestStatus.COMPLETED]
+        toks = sum(len(r.output) for r in done)
+        res = TestResult(len(requests), len(done), sum(r.status is RequestStatus.FAILED for r in requests), wall_s,
+                         toks, toks / max(wall_s, 1e-9), rate,
+                         self.percentiles([r.metrics.ttft for r in done]),
+                         self.percentiles([r.metrics.tpot for r in done]),
+                         self.percentiles([r.metrics.latency for r in done]))
+        if stats is not None:
+            res.compression = {"compressions": stats.compressions, "rows_in": stats.compressed_rows_in,
+                               "rows_out": stats.compressed_rows_out, "blocks_freed": stats.blocks_freed,
+                               "lazy_triggers": stats.lazy_triggers, "preemptions": stats.preemptions}
+        return res
+
+
+# ---------------------------------------------------------------------------- tester
+class ConcurrentTester:
+    """Open-loop load test of an engine: arrivals at `req_per_sec` (Poisson by default, fixed
+    spacing like the reference with poisson=False), engine steps in the calling thread.
+
+    `batching = [prefill, compress, decode]` sets the per-stage batch caps of the engine's scheduler
+    (default [15, 45, 90]; `ccm_intensity_rule(decode)` gives the MiniCPM harness' rule
+    compress = decode // 3, prefill = compress // 3).
+    """
+
+    def __init__(self, llm: Any, batching: Sequence[int] = (15, 45, 90), req_per_sec: float = 10.0,
+                 poisson: bool = True, seed: int = 0, monitor_gpu: bool = False):
+        self.llm = llm
+        self.rate, self.poisson = req_per_sec, poisson
+        self.rng = random.Random(seed)
+        sch = llm.scheduler
+        sch.prefill_cap, sch.compress_cap, sch.decode_cap = (int(b) for b in batching)
+        self.timestamps = TimestampManager()
+        self.monitor = GPUMonitor() if monitor_gpu else None
+        self.perf = PerformanceMonitor()
+
+    @staticmethod
+    def ccm_intensity_rule(decode: int = 135) -> List[int]:
+        compress = decode // 3
+        return [compress // 3, compress, decode]
+
+    def arrival_times(self, n: int) -> List[float]:
+        t, out = 0.0, []
+        for _ in range(n):
+            out.append(t)
+            t += self.rng.expovariate(self.rate) if self.poisson else 1.0 / self.rate
+        return out
+
+    def run(self, prompts: Sequence[Any], max_tokens: int = 128, images: Optional[Sequence[Any]] = None,
+            temperature: float = 0.0, time_scale: float = 1.0,
+            on_step: Optional[Callable[[int], None]] = None) -> TestResult:
+        from ..sampling_params import SamplingParams
+        llm = self.llm
+        reqs = [Request(i, p, max_tokens, images[i] if images else None) for i, p in enumerate(prompts)]
+        arrivals = [a * time_scale for a in self.arrival_times(len(reqs))]
+        if self.monitor is not None:
+            self.monitor.start()
+        seq_of: Dict[int, Request] = {}
+        nxt, steps = 0, 0
+        t0 = time.perf_counter()
+        while nxt < len(reqs) or not llm.is_finished():
+            now = time.perf_counter() - t0
+            while nxt < len(reqs) and arrivals[nxt] <= now:
+                r = reqs[nxt]
+                r.metrics.arrival = t0 + arrivals[nxt]
+                self.timestamps.record(r.request_id, "arrival", r.metrics.arrival)
+                try:
+                    seq = llm.add_request(r.prompt, SamplingParams(temperature=temperature, max_tokens=r.max_tokens,
+                                                                   ignore_eos=True), r.image)
+                    seq.arrival_time = r.metrics.arrival
+                    seq_of[seq.seq_id] = r
+                    r.status = RequestStatus.PREFILLING
+                    r._seq = seq
+                except Exception as exc:
+                    r.fail(str(exc))
+                nxt += 1
+            if llm.is_finished():
+                if nxt < len(reqs):
+                    time.sleep(max(0.0, min(0.01, arrivals[nxt] - now)))
+                continue
+            if self.monitor is not None:
+                self.monitor.stage = f"step{steps}"
+            outputs, _ = llm.step()
+            steps += 1
+            t = time.perf_counter()
+            for sid, toks in outputs:
+                r = seq_of.pop(sid, None)
+                if r is None:
+                    continue
+                s = r._seq
+                r.output = list(toks)
+                r.metrics.prefill_end = s.first_token_time or t
+                r.metrics.decode_start = r.metrics.prefill_end
+                r.metrics.decode_end = t
+                r.metrics.generated = len(toks)
+                r.status = RequestStatus.COMPLETED
+                self.timestamps.record(r.request_id, "prefill_finish", r.metrics.prefill_end)
+                self.timestamps.record(r.request_id, "decoding_finish", t)
+            if on_step is not None:
+                on_step(steps)
+        wall = time.perf_counter() - t0
+        if self.monitor is not None:
+            self.monitor.stop()
+        return self.perf.summarise(reqs, wall, self.rate, getattr(llm, "stats", None))
+
+
+# names used by the reference's scripts
+ImprovedConcurrentTester = ConcurrentTester
+
+
+class ServiceMiddleware:
+    """Thin front for the tester: keeps the engine, the tester settings and the last result."""
+
+    def __init__(self, llm: Any, **tester_kwargs: Any):
+        self.llm, self.kw = llm, tester_kwargs
+        self.last: Optional[TestResult] = None
+
+    def run_concurrent_test(self, prompts: Sequence[Any], **run_kwargs: Any) -> TestResult:
+        self.last = ConcurrentTester(self.llm, **self.kw).run(prompts, **run_kwargs)
+        return self.last

@@ -1,0 +1,61 @@
+"""Serving harness pieces on the CPU engine."""
+import time
+
+import torch
+
+from fastcache_b200 import LLM
+from fastcache_b200.serving.harness import (ConcurrentTester, DynamicScheduler, KVCachePool, PerformanceMonitor,
+                                            Request, RequestStatus, TimestampManager)
+from helpers import tiny_llama_config
+
+
+def test_dynamic_scheduler_prefill_priority_and_decode_budget():
+    s = DynamicScheduler(max_batch_size=3, std_batch_threshold_decoding=10, max_wait_time=0.05)
+    for i, n in enumerate([50, 10, 30]):
+        s.add_prefill(f"p{i}", n)
+    kind, batch = s.select_batch()
+    assert kind == "prefill" and batch[0] == "p1" and len(batch) == 3      # shortest first, full batch
+    s.add_prefill("late", 5)
+    for i, n in enumerate([4, 4, 4, 4]):
+        s.add_decoding(f"d{i}", n)
+    kind, batch = s.select_batch()                                          # prefill not full, not waited long
+    assert kind == "decoding" and len(batch) == 2                           # 4 + 4 <= 10 < 12
+    time.sleep(0.06)
+    kind, batch = s.select_batch()
+    assert kind == "prefill" and batch == ["late"]                          # waited max_wait_time
+
+
+def test_kv_pool_and_timestamps():
+    pool = KVCachePool()
+    kv = [(torch.randn(2, 2, 6, 4), torch.randn(2, 2, 6, 4))]
+    pool.store_kvcache([7, 8], kv, lengths=[6, 4])
+    assert pool.get(8)[0][0].shape == (1, 2, 4, 4) and pool.get_stats()["entries"] == 2
+    merged, lens = pool.merge_and_pop([7, 8])
+    assert merged[0][0].shape == (2, 2, 6, 4) and lens == [6, 4] and pool.get_stats()["entries"] == 0
+    assert torch.equal(merged[0][0][1, :, 2:], kv[0][0][1, :, 2:])
+    t = TimestampManager()
+    for i, st in enumerate(["arrival", "prefill_queueing_start", "prefill_start", "prefill_finish",
+                            "decoding_start", "decoding_finish"]):
+        t.record(1, st, float(i))
+    a = t.analyze(1, generated_len=4)
+    assert a["ttft"] == 2.0 and a["tpot"] == 0.25 and a["latency"] == 5.0
+    p = PerformanceMonitor.percentiles([1.0, 2.0, 3.0, 4.0, 100.0])
+    assert p["p50"] == 3.0 and p["max"] == 100.0
+    r = Request(0, [1, 2, 3])
+    r.fail("boom")
+    assert r.status is RequestStatus.FAILED and r.input_len == 3
+
+
+def test_concurrent_tester_poisson_arrivals_with_compression():
+    llm = LLM(tiny_llama_config(), device="cpu", kvcache_block_size=16, num_kvcache_blocks=256, max_model_len=256,
+              enforce_eager=True, enable_compression=True, compression_backend="kvpress", kvpress_method="knorm",
+              compression_factor=2, compression_pipeline="prefill")
+    tester = ConcurrentTester(llm, batching=[3, 9, 18], req_per_sec=200.0, seed=1)
+    assert ConcurrentTester.ccm_intensity_rule(135) == [15, 45, 135]
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 1000, (40,), generator=g).tolist() for _ in range(12)]
+    res = tester.run(prompts, max_tokens=6)
+    assert res.completed == 12 and res.output_tokens == 72 and res.failed == 0
+    assert res.ttft["p50"] > 0 and res.latency["p99"] >= res.ttft["p99"]
+    assert res.compression["compressions"] == 12 and res.compression["blocks_freed"] > 0
+    assert llm.stats.prefill_steps >= 4                     # prefill cap 3 -> at least 4 prefill batches
