@@ -85,6 +85,87 @@ Tensor gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias,
   return out;
 }
 
+// Launches the GEMM of x @ w.T.  Decode-size inputs may leave fp32 partial sums in the workspace
+// instead of a finished result: returns the number of K splits (1 = `out` holds the result).
+static int gemm_maybe_partial(const Tensor& x, const Tensor& w, Tensor& out, DeviceWorkspace& ws,
+                              cudaStream_t stream) {
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  fc::GemmWorkspace gw;
+  gw.scratch = ws.gemm_scratch.data_ptr<float>();
+  gw.counters = ws.gemm_counters.data_ptr<int>();
+  gw.status = reinterpret_cast<uint32_t*>(ws.status.data_ptr<int>());
+  if (M <= 256) {
+    return fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, int(M), int(N), int(K),
+                                x.stride(0), w.stride(0), out.stride(0), 0, gw, sm_limit_for(stream), 0, false,
+                                stream);
+  }
+  fc::gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, int(M), int(N), int(K), x.stride(0),
+                w.stride(0), out.stride(0), 0, gw, sm_limit_for(stream), stream);
+  return 1;
+}
+
+static void check_linear_pair(const Tensor& x, const Tensor& w) {
+  check_bf16(x, "x");
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1 &&
+                  x.size(1) % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0,
+              "operands must be row-major bf16 matrices with K % 8 == 0");
+}
+
+// residual += x @ w.T (+ bias); returns RMSNorm(residual) * norm_w.  One GEMM launch and one
+// norm launch: split-K partial sums are reduced by the norm kernel.
+Tensor linear_add_rms_norm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, Tensor& residual,
+                           const Tensor& norm_w, double eps) {
+  check_linear_pair(x, w);
+  check_bf16(residual, "residual");
+  check_bf16(norm_w, "norm weight");
+  const int64_t M = x.size(0), N = w.size(0);
+  TORCH_CHECK(residual.is_contiguous() && residual.dim() == 2 && residual.size(0) == M && residual.size(1) == N,
+              "residual must be contiguous [M, N]");
+  TORCH_CHECK(N % 8 == 0 && N <= 8192 && norm_w.numel() == N && norm_w.is_contiguous(), "bad hidden size");
+  const void* bptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be a contiguous [N] vector");
+    bptr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  auto& ws = workspace(x.get_device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  Tensor y = torch::empty({M, N}, x.options());
+  if (M == 0) return y;
+  Tensor tmp = torch::empty({M, N}, x.options());
+  const int splits = gemm_maybe_partial(x, w, tmp, ws, stream);
+  if (splits > 1) {
+    fc::launch_add_rms_norm_partials(ws.gemm_scratch.data_ptr<float>(), splits, M * N, bptr, residual.data_ptr(),
+                                     norm_w.data_ptr(), y.data_ptr(), M, int(N), float(eps), stream);
+  } else {
+    if (bptr != nullptr) tmp.add_(*bias);
+    fc::launch_rms_norm(tmp.data_ptr(), residual.data_ptr(), norm_w.data_ptr(), y.data_ptr(), M, int(N), float(eps),
+                        stream);
+  }
+  return y;
+}
+
+// silu(x @ wg.T) * (x @ wu.T) with w = [wg; wu] stacked on dim 0 ([2 I, K]).
+Tensor linear_silu_mul(const Tensor& x, const Tensor& w) {
+  check_linear_pair(x, w);
+  const int64_t M = x.size(0), N = w.size(0), I = N / 2;
+  TORCH_CHECK(N % 16 == 0, "gate|up width must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto& ws = workspace(x.get_device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  Tensor out = torch::empty({M, I}, x.options());
+  if (M == 0) return out;
+  Tensor tmp = torch::empty({M, N}, x.options());
+  const int splits = gemm_maybe_partial(x, w, tmp, ws, stream);
+  if (splits > 1)
+    fc::launch_silu_mul_partials(ws.gemm_scratch.data_ptr<float>(), splits, M * N, out.data_ptr(), M, int(I), stream);
+  else
+    fc::launch_silu_and_mul(tmp.data_ptr(), out.data_ptr(), M, int(I), stream);
+  return out;
+}
+
 Tensor rms_norm(const Tensor& x, const Tensor& w, double eps) {
   check_bf16(x, "x");
   check_bf16(w, "weight");
@@ -311,6 +392,8 @@ void register_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "y = act(x @ w.T + bias) on tcgen05", py::arg("x"), py::arg("w"), py::arg("bias") = py::none(),
         py::arg("act") = 0, py::arg("out") = py::none());
+  m.def("linear_add_rms_norm", &linear_add_rms_norm);
+  m.def("linear_silu_mul", &linear_silu_mul);
   m.def("rms_norm", &rms_norm);
   m.def("add_rms_norm", &add_rms_norm);
   m.def("layer_norm", &layer_norm);

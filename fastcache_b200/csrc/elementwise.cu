@@ -215,6 +215,29 @@ rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restri
   const bool is_q = h < Hq;
   const bf16* nw = is_q ? q_w : k_w;
   if (!is_q && slot < 0 && slots != nullptr) return;
+  if (D == 128) {
+    // fast path: each lane owns the pairs (2l, 2l+1) of the low half and their partners in the high half
+    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(src);
+    float2 a = __bfloat1622float2(s2[lane]), b = __bfloat1622float2(s2[32 + lane]);
+    if (nw != nullptr) {
+      const float inv = rsqrtf(warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y) / 128.f + eps);
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(nw);
+      const float2 wa = __bfloat1622float2(w2[lane]), wb = __bfloat1622float2(w2[32 + lane]);
+      auto rn = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
+      a.x = rn(rn(a.x * inv) * wa.x);
+      a.y = rn(rn(a.y * inv) * wa.y);
+      b.x = rn(rn(b.x * inv) * wb.x);
+      b.y = rn(rn(b.y * inv) * wb.y);
+    }
+    const float2* cs2 = reinterpret_cast<const float2*>(cos_sin + positions[t] * 128);
+    const float2 c = cs2[lane], s = cs2[32 + lane];
+    __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(
+        is_q ? (q_out + ((long long)t * Hq + h) * 128)
+             : (k_cache + (((slot / block_size) * Hkv + (h - Hq)) * block_size + slot % block_size) * 128));
+    d2[lane] = __floats2bfloat162_rn(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
+    d2[32 + lane] = __floats2bfloat162_rn(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+    return;
+  }
   // pairs (p, p + half), p = lane, lane + 32, ...   (D <= 256)
   float lo[4], hi[4];
   float ss = 0.f;
@@ -276,10 +299,10 @@ sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, 
   const bf16* row = logits + (long long)b * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    float v = __bfloat162float(row[j]);
+  const uint32_t row_seed = mix32(seed ^ (uint32_t(b) * 0x9E3779B9u));
+  auto consider = [&](float v, int j) {
     if (T > 0.f) {
-      const uint32_t r = mix32(mix32(seed ^ (uint32_t(b) * 0x9E3779B9u)) + uint32_t(j));
+      const uint32_t r = mix32(row_seed + uint32_t(j));
       const float u = (float(r >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
       v = v / T - __logf(-__logf(u));
     }
@@ -287,7 +310,20 @@ sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, 
       best = v;
       best_i = j;
     }
+  };
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+  const int v8 = vec ? (V >> 3) : 0;
+  for (int c = threadIdx.x; c < v8; c += blockDim.x) {           // 16-byte loads: 8 logits at a time
+    const uint4 u = reinterpret_cast<const uint4*>(row)[c];
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      consider(f.x, c * 8 + 2 * i);
+      consider(f.y, c * 8 + 2 * i + 1);
+    }
   }
+  for (int j = v8 * 8 + threadIdx.x; j < V; j += blockDim.x) consider(__bfloat162float(row[j]), j);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);

@@ -54,4 +54,11 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
                       const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
                       int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
                       int factor, int min_seq_len, int single_segment, uint32_t* status, cudaStream_t stream);
+
+// consumers of split-K partial sums [splits, T, N] fp32 (partials.cu)
+void launch_add_rms_norm_partials(const float* partial, int splits, long long split_stride, const void* bias,
+                                  void* residual, const void* w, void* y, long long T, int H, float eps,
+                                  cudaStream_t s);
+void launch_silu_mul_partials(const float* partial, int splits, long long split_stride, void* out, long long T,
+                              int I, cudaStream_t s);
 }  // namespace fc

@@ -71,6 +71,9 @@ class DecoderMLP(nn.Module):
         self.act_fn = SiluAndMul()
 
     def forward(self, normed: torch.Tensor) -> torch.Tensor:
+        if normed.is_cuda and normed.shape[0] <= 256 and self.gate_up_proj.bias is None:
+            # decode sizes: the SwiGLU kernel also reduces the GEMM's split-K partial sums
+            return ops.linear_silu_mul(normed, self.gate_up_proj.weight)
         return self.act_fn(self.gate_up_proj(normed))
 
 

@@ -74,6 +74,24 @@ def linear(x, weight, bias=None, act: str = "none", out: Optional[torch.Tensor] 
     return y
 
 
+def linear_add_rms_norm(x, weight, bias, residual, norm_weight, eps) -> Tuple[torch.Tensor, torch.Tensor]:
+    """residual += x @ weight.T (+ bias); returns (RMSNorm(residual), residual).  On CUDA the split-K
+    partial sums of a decode-size GEMM are reduced inside the norm kernel (two launches in all)."""
+    if x.is_cuda:
+        _n(2)
+        y = ext().linear_add_rms_norm(x, weight, bias, residual, norm_weight, float(eps))
+        return y, residual
+    return ref.add_rms_norm(ref.linear(x, weight, bias), residual, norm_weight, eps)
+
+
+def linear_silu_mul(x, weight):
+    """silu(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu]."""
+    if x.is_cuda:
+        _n(2)
+        return ext().linear_silu_mul(x, weight)
+    return ref.silu_and_mul(ref.linear(x, weight))
+
+
 def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
                       q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping):
     if qkv.is_cuda:

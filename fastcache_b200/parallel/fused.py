@@ -43,6 +43,8 @@ def row_linear_reduce_add_norm(x: torch.Tensor, weight: torch.Tensor, bias: Opti
         bias = None
     if tp > 1 and x.is_cuda and _FUSED_COMM is not None:
         return _FUSED_COMM.row_linear_reduce_add_norm(x, weight, bias, residual, norm_weight, eps)
+    if tp == 1 and x.is_cuda:
+        return ops.linear_add_rms_norm(x, weight, bias, residual, norm_weight, eps)
     y = ops.linear(x, weight, bias)
     if tp > 1:
         tpmod.tp_all_reduce(y)
