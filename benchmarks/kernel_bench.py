@@ -98,12 +98,13 @@ def bench_prefill_attn(rows):
         q = torch.randn(nseq * S, Hq, D, device="cuda", dtype=torch.bfloat16)
         cu = (torch.arange(nseq + 1, device="cuda") * S).int()
         kl = torch.full((nseq,), S, dtype=torch.int32, device="cuda")
-        ms = timeit(lambda: ops.prefill_attention(q, kc, vc, bt, cu, kl, D ** -0.5, S), iters=5)
         flops = 4.0 * nseq * Hq * D * S * S / 2
-        rows.append({"kernel": "prefill_attn", "seqs": nseq, "S": S, "Hq": Hq, "Hkv": Hkv, "ms": round(ms, 3),
-                     "tflops": round(flops / ms / 1e9, 1), "frac_of_bf16_peak": round(flops / ms / 1e9 / tf, 3),
-                     "peaks": src})
-        print(rows[-1], flush=True)
+        for impl, name in ((1, "mma.sync"), (2, "tcgen05")):
+            ms = timeit(lambda: ops.prefill_attention(q, kc, vc, bt, cu, kl, D ** -0.5, S, impl), iters=5)
+            rows.append({"kernel": "prefill_attn", "impl": name, "seqs": nseq, "S": S, "Hq": Hq, "Hkv": Hkv,
+                         "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
+                         "frac_of_bf16_peak": round(flops / ms / 1e9 / tf, 3), "peaks": src})
+            print(rows[-1], flush=True)
 
 
 def bench_norm(rows):

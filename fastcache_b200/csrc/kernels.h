@@ -30,6 +30,12 @@ void launch_prefill_attention(const void* q, const void* k_cache, const void* v_
                               const int* cu_seqlens_q, const int* kv_lens, void* out, int num_seqs, int max_q_len,
                               int Hq, int Hkv, int D, int block_size, int max_blocks, int num_blocks, float scale,
                               uint32_t* status, cudaStream_t stream);
+// tcgen05 version (head_dim 128, block_size a multiple of 8)
+bool prefill_attention_tc_supported(int D, int block_size);
+void launch_prefill_attention_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                                 const int* cu_seqlens_q, const int* kv_lens, void* out, long long total_q,
+                                 int num_seqs, int max_q_len, int Hq, int Hkv, int block_size, int max_blocks,
+                                 int num_blocks, float scale, uint32_t* status, cudaStream_t stream);
 }  // namespace fc
 
 namespace fc {

@@ -139,8 +139,12 @@ def test_decode_attention(D, Hq, Hkv, bs, lens, splits):
 @pytest.mark.parametrize("D,Hq,Hkv,bs,qlens,kvlens", [
     (128, 8, 2, 16, [5, 64, 130], [5, 64, 130]), (128, 4, 4, 256, [300], [300]),
     (64, 4, 2, 16, [128, 128], [128, 128]), (128, 8, 2, 32, [10, 100], [74, 228]),
-    (128, 32, 8, 64, [1000], [1000])])
-def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens):
+    (128, 32, 8, 64, [1000], [1000]), (128, 4, 2, 8, [257, 3], [300, 131]),
+    (128, 16, 8, 256, [2048, 700], [2048, 1212])])
+@pytest.mark.parametrize("impl", [1, 2])
+def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens, impl):
+    if impl == 2 and D != 128:
+        pytest.skip("the tcgen05 kernel is head_dim 128 only")
     B = len(qlens)
     kc, vc, bt = _paged(B, kvlens, Hkv, D, bs, seed=4)
     T = sum(qlens)
@@ -148,7 +152,7 @@ def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens):
     cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
     kl = torch.tensor(kvlens, dtype=torch.int32, device=DEV)
     scale = D ** -0.5
-    o = ops.prefill_attention(q, kc, vc, bt, cu, kl, scale, max(qlens))
+    o = ops.prefill_attention(q, kc, vc, bt, cu, kl, scale, max(qlens), impl)
     want = ref.prefill_attention(q.float(), kc.float(), vc.float(), bt, cu, kl, scale)
     _check_status()
     assert (o.float() - want).abs().max().item() < 2e-2
