@@ -45,12 +45,15 @@ def _write_checkpoint(path, hf, seed=0):
           "lm_head.weight": rnd(vocab, h)}, "model-embed.safetensors")
     for i in range(L):
         p = f"model.layers.{i}."
-        save({p + "self_attn.q_proj.weight": rnd(heads * d, h), p + "self_attn.k_proj.weight": rnd(kvh * d, h),
-              p + "self_attn.v_proj.weight": rnd(kvh * d, h), p + "self_attn.o_proj.weight": rnd(h, heads * d),
-              p + "self_attn.q_norm.weight": ones(d), p + "self_attn.k_norm.weight": ones(d),
-              p + "mlp.gate_proj.weight": rnd(inter, h), p + "mlp.up_proj.weight": rnd(inter, h),
-              p + "mlp.down_proj.weight": rnd(h, inter), p + "input_layernorm.weight": ones(h),
-              p + "post_attention_layernorm.weight": ones(h)}, f"model-layer{i:03d}.safetensors")
+        layer = {p + "self_attn.q_proj.weight": rnd(heads * d, h), p + "self_attn.k_proj.weight": rnd(kvh * d, h),
+                 p + "self_attn.v_proj.weight": rnd(kvh * d, h), p + "self_attn.o_proj.weight": rnd(h, heads * d),
+                 p + "mlp.gate_proj.weight": rnd(inter, h), p + "mlp.up_proj.weight": rnd(inter, h),
+                 p + "mlp.down_proj.weight": rnd(h, inter), p + "input_layernorm.weight": ones(h),
+                 p + "post_attention_layernorm.weight": ones(h)}
+        if hf.get("model_type") == "qwen3":
+            layer[p + "self_attn.q_norm.weight"] = ones(d)
+            layer[p + "self_attn.k_norm.weight"] = ones(d)
+        save(layer, f"model-layer{i:03d}.safetensors")
     # minimal tokenizer: the engine only needs eos_token_id and encode() for string prompts
     from tokenizers import Tokenizer, models, pre_tokenizers
     vocab_map = {"<unk>": 0, "<eos>": 1, "hello": 2}
@@ -64,7 +67,39 @@ def _write_checkpoint(path, hf, seed=0):
     open(os.path.join(path, "DONE"), "w").close()
 
 
-def run(args, workload, ClockSampler, prompts_for, percentile):
+
+
+def _transformers_4x_config_view():
+    """The reference was written against transformers 4.x, where a config without rope scaling has
+    `rope_scaling = None` and a top-level `rope_theta`.  transformers 5.x folds both into a
+    `rope_parameters` dict, which the reference's `get_rope` (nanovllm/layers/rotary_embedding.py:63-73,
+    an lru_cache over its arguments plus `assert rope_scaling is None`) cannot take.  This wraps
+    `AutoConfig.from_pretrained` so that the object the reference receives reads as it did under 4.x.
+    Nothing of the reference is changed."""
+    import transformers
+    orig = transformers.AutoConfig.from_pretrained
+
+    def from_pretrained(path, *a, **kw):
+        cfg = orig(path, *a, **kw)
+        try:
+            with open(os.path.join(str(path), "config.json")) as fh:
+                raw = json.load(fh)
+        except OSError:
+            raw = {}
+        targets = [cfg] + ([cfg.text_config] if getattr(cfg, "text_config", None) is not None else [])
+        for c, r in zip(targets, [raw, raw.get("text_config", raw)]):
+            params = getattr(c, "rope_parameters", None) or {}
+            if params.get("rope_type", "default") == "default":
+                theta = r.get("rope_theta", params.get("rope_theta"))
+                c.rope_scaling = None
+                if theta is not None:
+                    c.rope_theta = float(theta)
+        return cfg
+
+    transformers.AutoConfig.from_pretrained = staticmethod(from_pretrained)
+
+
+def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
     import torch
     hf, n_req, p_len, o_len = workload
     n_req = args.requests or n_req
@@ -73,6 +108,7 @@ def run(args, workload, ClockSampler, prompts_for, percentile):
     torch.cuda.set_device(0)
     ckpt = os.path.join(os.environ.get("FC_REF_CKPT_DIR", "/tmp"), f"fc_ref_{args.config}")
     _write_checkpoint(ckpt, dict(hf))
+    _transformers_4x_config_view()
 
     from nanovllm.engine.llava_engine import LlavaLLM          # the reference's engine
     from nanovllm.sampling_params import SamplingParams
@@ -84,44 +120,35 @@ def run(args, workload, ClockSampler, prompts_for, percentile):
                    max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768, kvcache_block_size=256,
                    gpu_memory_utilization=args.mem_util, enforce_eager=False)
     sp = SamplingParams(temperature=0.6, max_tokens=o_len, ignore_eos=True)
-    wsp = SamplingParams(temperature=0.6, max_tokens=max(2, args.warmup), ignore_eos=True)
-    done = 0
-    while done < args.warmup:
-        for p in prompts_for(2, 512, hf["vocab_size"], 7):
+    wsp = SamplingParams(temperature=0.6, max_tokens=4, ignore_eos=True)
+    for w in range(args.warmup):                    # the same reduced waves as the other arm
+        for p in prompts_for(min(8, n_req), p_len, hf["vocab_size"], 1000 + w):
             llm.add_request(p, wsp)
         while not llm.is_finished():
             llm.step(apply_compression=compress)
-            done += 1
 
-    prompts = prompts_for(n_req, p_len, hf["vocab_size"], 1)
-    for p in prompts:
-        llm.add_request(p, sp)
     sampler = ClockSampler(0)
     torch.cuda.synchronize()
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     t0 = time.perf_counter()
-    steps = out_tokens = 0
+    engine_steps = out_tokens = 0
     ttft = []
-    limit = args.steps if args.steps > 0 else 1 << 30
-    wave = 1
-    while steps < limit:
-        if llm.is_finished():
-            if args.steps <= 0:
-                break
-            wave += 1
-            for p in prompts_for(n_req, p_len, hf["vocab_size"], wave):
-                llm.add_request(p, sp)
-        _, n = llm.step(apply_compression=compress)
-        steps += 1
-        if n > 0:                                   # a prefill step: each request in it got its first token
-            now = time.perf_counter() - t0
-            batch = sum(1 for s in llm.scheduler.running if s.num_completion_tokens == 1)
-            ttft.extend([now] * batch)
-            out_tokens += batch
-        else:
-            out_tokens += -n
+    for job in range(args.steps):
+        for p in prompts_for(n_req, p_len, hf["vocab_size"], 1 + job):
+            llm.add_request(p, sp)
+        t_arrival = time.perf_counter()
+        while not llm.is_finished():
+            _, n = llm.step(apply_compression=compress)
+            engine_steps += 1
+            if n > 0:                               # a prefill step: each request in it got its first token
+                now = time.perf_counter() - t_arrival
+                batch = sum(1 for s in llm.scheduler.running if s.num_completion_tokens == 1)
+                ttft.extend([now] * batch)
+                out_tokens += batch
+            else:
+                out_tokens += -n
     ev1.record()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
@@ -129,18 +156,22 @@ def run(args, workload, ClockSampler, prompts_for, percentile):
     ms = max(ev0.elapsed_time(ev1), (t1 - t0) * 1e3)
     value = out_tokens / (ms / 1e3)
     return {
-        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": round(ms / max(1, steps), 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights",
-        "config": {"model": "Qwen3-8B shape", "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
+        "config": {"model": model_label, "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
                    "parallelism": "tp1", "compression": f"{method} keep 50% (reference engine-native variant)"
                    if compress else "none", "cuda_graph_decode": True, "kv_block": 256,
-                   "l2": "working set per step far exceeds L2; no flush needed"},
+                   "l2": "working set per step far exceeds L2; no flush needed",
+                   "step": "one whole job (all requests submitted at once, served to completion)",
+                   "warmup_step": "wave of 8 prompts of the same length, 4 output tokens",
+                   "engine_steps": engine_steps},
         "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
         "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
         "output_tokens": out_tokens,
         "e2e": {"value": round(value, 2), "unit": "tok/s", "ms_total": round(ms, 2),
                 "note": "the reference exposes no device-only timer; its single number is end to end"},
-        "clocks": clocks, "impl": "reference", "shims": ["xxhash", "kvpress"],
+        "clocks": clocks, "impl": "reference",
+        "shims": ["xxhash", "kvpress", "transformers 4.x view of the config's rope fields"],
     }

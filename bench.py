@@ -10,11 +10,13 @@ prompt tokens and 512 output tokens each; KV eviction by key norm (default) or
 SnapKV (--method snapkv, window 64, pooling kernel 5) keeping 50 % of the prompt
 rows; CUDA-graph decode; tensor parallel over the N GPUs.
 
-A "step" is one engine step (one prefill batch or one decode batch including the
-compression that follows a prefill).  W warm-up steps run on a separate small
-wave of requests.  Then exactly K steps of the job are timed between a barrier +
-synchronize on both sides (default K = every step of the job).  Two numbers come
-out of the same run:
+A "step" is one complete serving job: all requests of the workload submitted at
+once and served to their last output token (the unit the reference's benchmark
+times; output tokens/s and TTFT are only defined over a whole job).  W warm-up
+steps are reduced waves (8 prompts of the job's prompt length, 4 output tokens)
+that run every kernel at the job's prefill batch shape.  Then exactly K jobs are
+timed between a barrier + synchronize on both sides (default K = 1).  Two numbers
+come out of the same run:
   value      output tokens / device time, where device time is the sum of CUDA
              event intervals around the model and compression kernels of each
              step (max over ranks)
@@ -42,11 +44,26 @@ QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_s
                 tie_word_embeddings=False, eos_token_id=151645, torch_dtype="bfloat16", hidden_act="silu",
                 attention_bias=False, bos_token_id=151643)
 
+LLAMA2_7B = dict(model_type="llama", architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=32, head_dim=128, intermediate_size=11008,
+                 vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=4096,
+                 tie_word_embeddings=False, eos_token_id=2, bos_token_id=1, torch_dtype="bfloat16",
+                 hidden_act="silu", attention_bias=False)
+
 WORKLOADS = {
     # name: (hf config, requests, prompt tokens, output tokens)
     "qwen3-8b": (QWEN3_8B, 128, 4096, 512),
-    # shrunken variant for quick functional checks; never reported as the headline
+    # the language model of the LLaVA-1.5-7B config, text only (MHA: 4x the KV bytes per token of Qwen3-8B)
+    "llama2-7b": (LLAMA2_7B, 64, 2048, 256),
+    # shrunken variants for quick functional checks; never reported as the headline
     "qwen3-8b-small": (dict(QWEN3_8B, num_hidden_layers=4), 16, 1024, 32),
+    "llama2-7b-small": (dict(LLAMA2_7B, num_hidden_layers=4), 16, 1024, 32),
+}
+MODEL_LABEL = {
+    "qwen3-8b": "Qwen3-8B shape (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)",
+    "llama2-7b": "Llama-2-7B shape (32L, h4096, 32 MHA heads, d128, ffn11008, vocab32000)",
+    "qwen3-8b-small": "Qwen3-8B shape cut to 4 layers (functional check only)",
+    "llama2-7b-small": "Llama-2-7B shape cut to 4 layers (functional check only)",
 }
 
 
@@ -155,49 +172,37 @@ def run_ours(args):
     runner = llm.model_runner
     sp = SamplingParams(temperature=0.0, max_tokens=o_len, ignore_eos=True)
 
-    # ---- warm-up wave (untimed): one prefill step then decode steps
-    wsp = SamplingParams(temperature=0.0, max_tokens=max(2, args.warmup), ignore_eos=True)
-    for p in prompts_for(2, 512, hf["vocab_size"], 7):
-        llm.add_request(p, wsp)
-    done = 0
-    while not llm.is_finished():
-        llm.step()
-        done += 1
-    while done < args.warmup:                     # W larger than the wave: repeat it
-        for p in prompts_for(2, 512, hf["vocab_size"], 7):
+    # ---- warm-up (untimed): W reduced waves that run every kernel of the job at its full
+    # prefill batch shape (8 prompts of the job's length), compression and graph decode included
+    wsp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    for w in range(args.warmup):
+        for p in prompts_for(min(8, n_req), p_len, hf["vocab_size"], 1000 + w):
             llm.add_request(p, wsp)
         while not llm.is_finished():
             llm.step()
-            done += 1
 
-    # ---- the job
-    prompts = prompts_for(n_req, p_len, hf["vocab_size"], 1)
-    seqs = [llm.add_request(p, sp) for p in prompts]
-    t_arrival = time.perf_counter()
-    for s in seqs:
-        s.arrival_time = t_arrival
+    # ---- K timed jobs
     runner.timer = DeviceTimer(runner.main_stream)
     runner.io["h2d_bytes"] = runner.io["d2h_bytes"] = 0
     ops.COUNTERS["launches"] = 0
-    out_tokens_before = sum(s.num_completion_tokens for s in seqs)
     sampler = ClockSampler(local_rank)
+    seqs = []
+    engine_steps = 0
     barrier(world)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(runner.main_stream)
     t0 = time.perf_counter()
-    steps = 0
-    limit = args.steps if args.steps > 0 else 1 << 30
-    wave = 1
-    while steps < limit:
-        if llm.is_finished():
-            if args.steps <= 0:
-                break
-            wave += 1                                # K exceeds the job: keep serving identical waves
-            more = [llm.add_request(p, sp) for p in prompts_for(n_req, p_len, hf["vocab_size"], wave)]
-            seqs.extend(more)
-        llm.step()
-        steps += 1
+    for job in range(args.steps):
+        batch = [llm.add_request(p, sp) for p in prompts_for(n_req, p_len, hf["vocab_size"], 1 + job)]
+        t_arrival = time.perf_counter()
+        for s in batch:
+            s.arrival_time = t_arrival
+        seqs.extend(batch)
+        while not llm.is_finished():
+            llm.step()
+            engine_steps += 1
+    steps = args.steps
     ev1.record(runner.main_stream)
     barrier(world)
     t1 = time.perf_counter()
@@ -206,7 +211,7 @@ def run_ours(args):
     wall_ms = (t1 - t0) * 1e3
     dev_ms = runner.timer.total_ms()
     runner.timer = None
-    out_tokens = sum(s.num_completion_tokens for s in seqs) - out_tokens_before
+    out_tokens = sum(s.num_completion_tokens for s in seqs)
     ttft = [s.first_token_time - s.arrival_time for s in seqs if s.first_token_time is not None]
     status = ops.ext().read_status(local_rank)
 
@@ -220,13 +225,14 @@ def run_ours(args):
             "steps": steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / max(1, steps), 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": base, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights",
-            "config": {"model": "Qwen3-8B shape (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)",
+            "config": {"model": MODEL_LABEL[args.config],
                        "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
                        "parallelism": f"tp{world}", "compression": f"{method} keep 50%" if not args.no_compression else "none",
                        "cuda_graph_decode": True, "kv_block": 256,
                        "l2": "working set per step (weights 16 GB + KV) far exceeds the 126 MB L2; no flush needed",
-                       "step": "one engine step (prefill batch incl. its compression, or decode batch)",
-                       "prefill_steps": llm.stats.prefill_steps, "decode_steps": llm.stats.decode_steps},
+                       "step": "one whole job (all requests submitted at once, served to completion)",
+                       "warmup_step": "wave of 8 prompts of the same length, 4 output tokens",
+                       "engine_steps": engine_steps, "prefill_steps": llm.stats.prefill_steps, "decode_steps": llm.stats.decode_steps},
             "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
             "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
             "output_tokens": out_tokens,
@@ -258,12 +264,13 @@ def run_reference(args):
         sys.exit(0)
     if world > 1:
         if rank == 0:
-            unavailable("reference hard-codes tp_size = 1 in its Qwen3 attention (nanovllm/models/qwen3.py:36): "
-                        "it cannot run this model tensor-parallel")
+            unavailable("the reference's LlavaLLM engine runs one process on one GPU (its Qwen3 attention "
+                        "hard-codes tp_size = 1, nanovllm/models/qwen3.py:36): no tensor-parallel run of this job")
         sys.exit(0)
     from baseline.reference_arm import run as ref_run
     try:
-        line = ref_run(args, WORKLOADS[args.config], ClockSampler, prompts_for, percentile)
+        line = ref_run(args, WORKLOADS[args.config], MODEL_LABEL[args.config], ClockSampler, prompts_for,
+                       percentile)
     except SystemExit:
         raise
     except Exception as exc:                       # import/runtime failure of the reference itself
@@ -276,8 +283,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=0, help="engine steps to time (0 = the whole job)")
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=1, help="whole jobs to time")
+    ap.add_argument("--warmup", type=int, default=3, help="reduced warm-up waves (at least 3)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--method", default="knorm", choices=["knorm", "snapkv", "knorm_ref", "streaming_llm"])
@@ -286,6 +293,7 @@ def main():
     ap.add_argument("--mem-util", type=float, default=0.85)
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    args.steps = max(1, args.steps)
     if args.impl == "reference":
         run_reference(args)
     else:

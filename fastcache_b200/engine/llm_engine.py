@@ -60,6 +60,9 @@ class StepStats:
     blocks_freed: int = 0
     lazy_triggers: int = 0
     preemptions: int = 0
+    compress_failures: int = 0
+    aborted: int = 0
+    recoveries: int = 0
     history: List[dict] = field(default_factory=list)
 
 
@@ -212,6 +215,46 @@ class LLMEngine:
     def is_finished(self) -> bool:
         return self.scheduler.is_finished()
 
+    # ------------------------------------------------------- failures and recovery
+    compression_error_policy = "skip"        # or "raise"
+    last_compress_error: Optional[BaseException] = None
+
+    def abort_request(self, seq_id: int) -> bool:
+        """Cancel one request (waiting, running or mid-compression).  True if it was live."""
+        sch = self.scheduler
+        for seq in list(sch.waiting) + list(sch.running):
+            if seq.seq_id == seq_id:
+                ok = sch.abort(seq)       # running: `finish` orders any compression in flight first
+                self._pending.pop(seq_id, None)
+                self.stats.aborted += int(ok)
+                return ok
+        return False
+
+    def recover(self) -> int:
+        """Abort the step in flight after a failure (a device wait that ran out, a dead peer, a
+        watchdog deadline): drop outstanding compressions, take every running request's blocks back
+        and queue it for prefill again.  Finished requests and their outputs are untouched.  Returns
+        the number of requests that will be recomputed."""
+        r = self.model_runner
+        if r.main_stream is not None:
+            for p in self._pending.values():
+                if p.event is not None:
+                    r.main_stream.wait_event(p.event)
+        self._pending.clear()
+        n = self.scheduler.requeue_running()
+        self.stats.recoveries += 1
+        self.scheduler.block_manager.check_invariants()
+        return n
+
+    def check_device_status(self) -> None:
+        """Raise if a kernel of this package reported a wait that ran out or a bad index since the
+        last call (the kernels return instead of hanging and leave a code in a status word)."""
+        r = self.model_runner
+        code = r.read_device_status() if hasattr(r, "read_device_status") else 0
+        if code:
+            from ..utils.watchdog import DeviceWaitTimeout
+            raise DeviceWaitTimeout(code)
+
     # -------------------------------------------------------------- compression
     def _on_release(self, seq: Sequence) -> None:
         """A request is about to lose its blocks: order any running compression first."""
@@ -255,10 +298,18 @@ class LLMEngine:
                 s._kv_cache_len = n
             try:
                 new = r.compress_kv_cache_batch(chunk, stream=r.main_stream)
-            except Exception:
+            except Exception as exc:
                 for s, v in zip(chunk, saved):
                     s._kv_cache_len = v
-                raise
+                if self.compression_error_policy == "raise":
+                    raise
+                # the reference's rule (nanovllm/engine/llava_model_runner.py:150-153): a failed
+                # compression leaves the request uncompressed and serving continues
+                self.stats.compress_failures += 1
+                self.last_compress_error = exc
+                for s in chunk:
+                    s.compression_state = CompressionState.FAILED
+                continue
             for s, n_in, n_out in zip(chunk, rows, new):
                 s.compression_state = CompressionState.COMPLETED
                 self._free_compressed_blocks(s, n_out)

@@ -532,6 +532,15 @@ class ModelRunner:
     def copy_block(self, src: int, dst: int) -> None:
         self.kv_cache[:, :, dst].copy_(self.kv_cache[:, :, src])
 
+    def read_device_status(self) -> int:
+        """Status word the kernels write when a bounded wait runs out or an index is out of range
+        (0 = clean).  Reading it synchronises with the device and clears it."""
+        dev = torch.device(self.device)
+        if dev.type != "cuda":
+            return 0
+        from .. import ops
+        return int(ops.ext().read_status(dev.index if dev.index is not None else torch.cuda.current_device()))
+
     def release(self, seq: Sequence) -> None:
         self._compressed_lens.pop(seq.seq_id, None)
         self._window_q.pop(seq.seq_id, None)

@@ -134,6 +134,36 @@ class Scheduler:
             pass
         self.waiting.appendleft(seq)
 
+    def abort(self, seq: Sequence) -> bool:
+        """Cancel a request wherever it is queued; its blocks return to the pool.  False if it had
+        already finished."""
+        if seq.is_finished:
+            return False
+        was_running = seq in self.running
+        try:
+            self.waiting.remove(seq)
+        except ValueError:
+            pass
+        if was_running:
+            self.finish(seq)
+        else:
+            seq.status = SequenceStatus.FINISHED
+            try:
+                self.compress_queue.remove(seq)
+            except ValueError:
+                pass
+        return True
+
+    def requeue_running(self) -> int:
+        """Recovery after an aborted step: every running request gives its blocks back and is
+        prefilled again from its tokens so far (arrival order kept).  Returns how many moved."""
+        moved = sorted(self.running, key=lambda s: s.seq_id, reverse=True)
+        self.running.clear()
+        for seq in moved:
+            seq.hold = False
+            self.preempt(seq)
+        return len(moved)
+
     # ---------------------------------------------------------------- compress
     def enqueue_compress(self, seqs: List[Sequence]) -> None:
         for seq in seqs:

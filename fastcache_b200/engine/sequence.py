@@ -32,6 +32,7 @@ class CompressionState(Enum):
     PENDING = auto()      # chosen for compression, not launched
     IN_PROGRESS = auto()  # launched on a side stream, event outstanding
     COMPLETED = auto()
+    FAILED = auto()       # the compressor raised; the request keeps its full KV and is not retried
 
 
 class Sequence:

@@ -1,0 +1,255 @@
+"""Failure detection and recovery, injected on the host only (no GPU is faulted, trapped or hung).
+
+Failures made here: a compressor that raises, a request cancelled mid-flight, an aborted step,
+a step that overruns its deadline, a rank that stops beating, a rank that leaves, and a
+collective whose peer never joins (gloo ranks with a short process-group timeout).
+"""
+import multiprocessing as mp
+import os
+import time
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from fastcache_b200 import LLM, SamplingParams
+from fastcache_b200.compress import KVCacheLinearDecoupleCompressor
+from fastcache_b200.engine.sequence import CompressionState
+from fastcache_b200.utils.watchdog import (DeviceWaitTimeout, RankFailure, RankHeartbeat, StepDeadlineExceeded,
+                                           StepWatchdog)
+from helpers import random_compressor, tiny_llama_config
+
+
+def _prompts(n=4, length=96, vocab=1024, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(3, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _engine(compress=True, **kw):
+    comp = random_compressor(KVCacheLinearDecoupleCompressor, 2, 64, 4) if compress else None
+    return LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=512,
+               device="cpu", enforce_eager=True, enable_compression=compress, compressor=comp,
+               compression_backend="mlp", **{"compression_pipeline": "prefill", **kw})
+
+
+# ------------------------------------------------------------------ compressor failure
+def test_compressor_exception_leaves_requests_uncompressed_and_serving():
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = _engine(compress=False).generate(_prompts(), sp)
+    llm = _engine(compress=True)
+    calls = {"n": 0}
+
+    def boom(*a, **k):
+        calls["n"] += 1
+        raise RuntimeError("injected compressor failure")
+
+    llm.model_runner.compress_kv_cache_batch = boom
+    got = llm.generate(_prompts(), sp)
+    assert calls["n"] >= 1 and llm.stats.compress_failures >= 1
+    assert isinstance(llm.last_compress_error, RuntimeError)
+    # nothing was compressed, so the tokens are those of the uncompressed engine
+    assert [o["token_ids"] for o in got] == [o["token_ids"] for o in want]
+    llm.scheduler.block_manager.check_invariants()
+    assert llm.scheduler.block_manager.num_free_blocks == llm.scheduler.block_manager.num_blocks
+
+
+def test_compressor_exception_policy_raise():
+    llm = _engine(compress=True)
+    llm.compression_error_policy = "raise"
+    llm.model_runner.compress_kv_cache_batch = lambda *a, **k: (_ for _ in ()).throw(ValueError("injected"))
+    for p in _prompts(2):
+        llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    with pytest.raises(ValueError):
+        llm.step()
+    # the lengths the failed call had overwritten are restored
+    assert all(s.compression_state is CompressionState.NONE for s in llm.scheduler.running)
+
+
+# ------------------------------------------------------------------------- cancellation
+def test_abort_running_and_waiting_requests_returns_blocks():
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    llm = _engine(compress=True, max_num_seqs=2)
+    seqs = [llm.add_request(p, sp) for p in _prompts(4)]
+    llm.step()                                         # two requests prefilled, two still waiting
+    running = list(llm.scheduler.running)
+    waiting = list(llm.scheduler.waiting)
+    assert len(running) == 2 and len(waiting) == 2
+    assert llm.abort_request(running[0].seq_id)
+    assert llm.abort_request(waiting[0].seq_id)
+    assert not llm.abort_request(running[0].seq_id)    # already gone
+    assert not llm.abort_request(10 ** 9)
+    while not llm.is_finished():
+        llm.step()
+    done = [s for s in seqs if s.num_completion_tokens == 16]
+    assert len(done) == 2 and llm.stats.aborted == 2
+    bm = llm.scheduler.block_manager
+    bm.check_invariants()
+    assert bm.num_free_blocks == bm.num_blocks
+
+
+# ---------------------------------------------------------------------------- recovery
+def test_recover_requeues_running_requests_and_output_is_unchanged():
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    want = _engine(compress=False).generate(_prompts(), sp)
+    llm = _engine(compress=False)
+    seqs = [llm.add_request(p, sp) for p in _prompts()]
+    for _ in range(5):
+        llm.step()
+    assert llm.recover() == 4                          # the step "in flight" is abandoned
+    bm = llm.scheduler.block_manager
+    assert bm.num_free_blocks == bm.num_blocks and not llm.scheduler.running
+    while not llm.is_finished():
+        llm.step()
+    # recompute replays prompt + tokens so far, so greedy outputs are those of an undisturbed run
+    assert [s.completion_token_ids for s in seqs] == [o["token_ids"] for o in want]
+    assert llm.stats.recoveries == 1
+
+
+def test_recover_with_compression_pending():
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = _engine(compress=True, compression_pipeline="decode")
+    seqs = [llm.add_request(p, sp) for p in _prompts(3)]
+    llm.step()
+    llm.step()
+    llm.recover()
+    assert not llm._pending
+    assert all(s.compression_state is CompressionState.NONE and not s.hold for s in seqs)
+    while not llm.is_finished():
+        llm.step()
+    assert all(s.num_completion_tokens == 6 for s in seqs)
+    llm.scheduler.block_manager.check_invariants()
+
+
+def test_pool_exhaustion_is_reported_not_hung():
+    llm = LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=4, max_model_len=512,
+              device="cpu", enforce_eager=True)
+    llm.add_request(_prompts(1, length=200)[0], SamplingParams(max_tokens=4))
+    with pytest.raises(RuntimeError, match="blocks"):
+        llm.step()
+
+
+def test_device_status_code_becomes_exception():
+    llm = _engine(compress=False)
+    llm.check_device_status()                          # CPU runner: always clean
+    llm.model_runner.read_device_status = lambda: 5    # what a peer wait that ran out would leave
+    with pytest.raises(DeviceWaitTimeout) as e:
+        llm.check_device_status()
+    assert e.value.code == 5 and "another GPU" in str(e.value)
+
+
+# ---------------------------------------------------------------------------- watchdog
+def test_step_watchdog_fires_once_and_raises():
+    fired = []
+    wd = StepWatchdog(0.05, on_expire=lambda label, t: fired.append((label, t)))
+    with wd.step("fast"):
+        pass
+    with pytest.raises(StepDeadlineExceeded):
+        with wd.step("slow"):
+            time.sleep(0.25)
+    with wd.step("fast again"):
+        pass
+    wd.close()
+    assert [f[0] for f in fired] == ["slow"] and fired[0][1] >= 0.05
+
+
+def test_watchdog_triggers_engine_recovery():
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    llm = _engine(compress=False)
+    seqs = [llm.add_request(p, sp) for p in _prompts(2)]
+    llm.step()
+    wd = StepWatchdog(0.05)
+    real_run = llm.model_runner.run
+
+    def stuck_once(batch, is_prefill):
+        time.sleep(0.2)                                # a step that overruns (host side only)
+        llm.model_runner.run = real_run
+        return real_run(batch, is_prefill)
+
+    llm.model_runner.run = stuck_once
+    with pytest.raises(StepDeadlineExceeded):
+        with wd.step("decode"):
+            llm.step()
+    llm.recover()
+    while not llm.is_finished():
+        with wd.step("step"):
+            llm.step()
+    wd.close()
+    assert all(s.num_completion_tokens == 4 for s in seqs)
+
+
+# --------------------------------------------------------------------------- heartbeat
+def test_heartbeat_detects_silent_and_departed_ranks():
+    store = dist.HashStore()
+    hbs = [RankHeartbeat(store, r, 3, period_s=0.02, timeout_s=0.2) for r in range(3)]
+    time.sleep(0.1)
+    assert hbs[0].dead_ranks() == []
+    hbs[2].pause()                                     # rank 2 hangs: process alive, no progress
+    deadline = time.monotonic() + 3.0
+    while time.monotonic() < deadline and hbs[0].dead_ranks() != [2]:
+        time.sleep(0.05)
+    assert hbs[0].dead_ranks() == [2]
+    hbs[1].dead_ranks()                                # first look only records the counter
+    time.sleep(0.3)
+    with pytest.raises(RankFailure) as e:
+        hbs[1].check()
+    assert e.value.ranks == [2]
+    hbs[2].resume()
+    time.sleep(0.1)
+    assert hbs[0].dead_ranks() == []
+    hbs[1].leave()                                     # an orderly exit is seen at once
+    assert hbs[0].dead_ranks() == [1]
+    for h in hbs:
+        h.close()
+
+
+def _rank_main(rank, world, port, q):
+    """gloo ranks: rank 1 leaves between steps; rank 0 learns of it from the heartbeat before its
+    next collective, and a collective entered anyway ends with an error after the short timeout."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20),
+                          wait_for_workers=True)
+    dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world,
+                            timeout=timedelta(seconds=2))
+    hb = RankHeartbeat(dist.PrefixStore("hb", store), rank, world, period_s=0.05, timeout_s=0.5)
+    x = torch.ones(4) * (rank + 1)
+    dist.all_reduce(x)                                  # step 1: everyone present
+    ok_first = bool(torch.allclose(x, torch.full((4,), 3.0)))
+    if rank == 1:
+        hb.leave()                                      # leaves between steps, nothing in flight
+        hb.close()
+        q.put(("left", rank, ok_first))
+        time.sleep(4.0)                                 # keep the store's peer socket open meanwhile
+        return
+    deadline = time.monotonic() + 5.0
+    dead = []
+    while time.monotonic() < deadline and not dead:
+        dead = hb.dead_ranks()
+        time.sleep(0.05)
+    err = None
+    t0 = time.monotonic()
+    try:                                                # what would happen without the heartbeat
+        dist.all_reduce(torch.ones(4))
+    except Exception as exc:                            # the short timeout turns a hang into an error
+        err = type(exc).__name__
+    q.put(("survivor", dead, ok_first, err, time.monotonic() - t0))
+    hb.close()
+
+
+def test_dead_rank_is_detected_by_gloo_survivor():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msgs = [q.get(timeout=60) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.kill()                                    # exact child, never a pattern
+    left = [m for m in msgs if m[0] == "left"][0]
+    surv = [m for m in msgs if m[0] == "survivor"][0]
+    assert left[2] and surv[2]                          # the collective before the failure was correct
+    assert surv[1] == [1]                               # learnt on the host, before any launch
+    assert surv[3] is not None and surv[4] < 15.0       # the orphaned collective errored, it did not hang
