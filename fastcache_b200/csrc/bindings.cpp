@@ -64,9 +64,11 @@ Tensor gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias,
   TORCH_CHECK(K % 8 == 0, "K must be a multiple of 8 (16-byte rows for TMA)");
   TORCH_CHECK(x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "row pitches must be multiples of 8 elements");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor out = out_opt.has_value() ? *out_opt : torch::empty({M, N}, x.options());
+  const int64_t N_out = (act == fc::ACT_SWIGLU) ? N / 2 : N;      // fused SwiGLU halves the width
+  TORCH_CHECK(act != fc::ACT_SWIGLU || (M > 256 && N % 256 == 0), "fused SwiGLU GEMM needs M > 256 and N % 256 == 0");
+  Tensor out = out_opt.has_value() ? *out_opt : torch::empty({M, N_out}, x.options());
   check_bf16(out, "out");
-  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "bad out tensor");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N_out && out.stride(1) == 1, "bad out tensor");
   const void* bptr = nullptr;
   if (bias.has_value() && bias->defined()) {
     check_bf16(*bias, "bias");

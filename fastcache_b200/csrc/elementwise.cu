@@ -277,6 +277,86 @@ rope_qknorm_store_kernel(const bf16* __restrict__ qkv, const long long* __restri
   }
 }
 
+// head_dim 128: eight lanes per (token, head), each lane owns 8 consecutive elements of the low
+// half and their rotation partners in the high half (two 16-byte loads, two 16-byte stores).
+__global__ void __launch_bounds__(256)
+rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __restrict__ positions,
+                              const float* __restrict__ cos_sin, const bf16* __restrict__ q_w,
+                              const bf16* __restrict__ k_w, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                              bf16* __restrict__ v_cache, const int* __restrict__ slots, int T, int Hq, int Hkv,
+                              float eps, long long num_slots, int block_size, uint32_t* status) {
+  const int heads = Hq + 2 * Hkv;
+  const long long gid = (blockIdx.x * 256ll + threadIdx.x) >> 3;
+  const int j = threadIdx.x & 7;
+  const bool active = gid < (long long)T * heads;
+  const long long g = active ? gid : 0;
+  const int t = int(g / heads);
+  const int h = int(g - (long long)t * heads);
+  const uint4* src = reinterpret_cast<const uint4*>(qkv + ((long long)t * heads + h) * 128);
+  const uint4 ulo = src[j], uhi = src[8 + j];
+  long long slot = -1;
+  if (h >= Hq && slots != nullptr) {
+    slot = slots[t];
+    if (slot >= num_slots) {
+      report(status, ST_BAD_INDEX);
+      slot = -1;
+    }
+  }
+  float lo[8], hi[8];
+  unpack8(ulo, lo);
+  unpack8(uhi, hi);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+  // every lane of the warp takes part (the 8-lane groups of a warp may sit on different heads)
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  if (!active) return;
+  if (h >= Hq + Hkv) {            // value head: plain copy into the pool
+    if (slot < 0) return;
+    uint4* dst = reinterpret_cast<uint4*>(
+        v_cache + (((slot / block_size) * Hkv + (h - Hq - Hkv)) * block_size + slot % block_size) * 128);
+    dst[j] = ulo;
+    dst[8 + j] = uhi;
+    return;
+  }
+  const bool is_q = h < Hq;
+  if (!is_q && slot < 0) return;
+  const bf16* nw = is_q ? q_w : k_w;
+  if (nw != nullptr) {
+    const float inv = rsqrtf(ss / 128.f + eps);
+    float wl[8], wh[8];
+    unpack8(reinterpret_cast<const uint4*>(nw)[j], wl);
+    unpack8(reinterpret_cast<const uint4*>(nw)[8 + j], wh);
+    auto rn = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo[i] = rn(rn(lo[i] * inv) * wl[i]);
+      hi[i] = rn(rn(hi[i] * inv) * wh[i]);
+    }
+  }
+  const float4* cs = reinterpret_cast<const float4*>(cos_sin + positions[t] * 128);
+  const float4 c0 = cs[2 * j], c1 = cs[2 * j + 1], s0 = cs[16 + 2 * j], s1 = cs[16 + 2 * j + 1];
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  uint4 olo, ohi;
+  uint32_t* pl = reinterpret_cast<uint32_t*>(&olo);
+  uint32_t* ph = reinterpret_cast<uint32_t*>(&ohi);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    pl[i] = pack_bf16(lo[2 * i] * c[2 * i] - hi[2 * i] * s[2 * i],
+                      lo[2 * i + 1] * c[2 * i + 1] - hi[2 * i + 1] * s[2 * i + 1]);
+    ph[i] = pack_bf16(hi[2 * i] * c[2 * i] + lo[2 * i] * s[2 * i],
+                      hi[2 * i + 1] * c[2 * i + 1] + lo[2 * i + 1] * s[2 * i + 1]);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(
+      is_q ? (q_out + ((long long)t * Hq + h) * 128)
+           : (k_cache + (((slot / block_size) * Hkv + (h - Hq)) * block_size + slot % block_size) * 128));
+  dst[j] = olo;
+  dst[8 + j] = ohi;
+}
+
 // ------------------------------------------------------------------- sampler
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16;
@@ -393,6 +473,13 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
                               uint32_t* status, cudaStream_t s) {
   if (T == 0) return;
   const long long warps = (long long)T * (Hq + 2 * Hkv);
+  if (D == 128 && slots != nullptr) {
+    rope_qknorm_store_d128_kernel<<<(unsigned)((warps + 31) / 32), 256, 0, s>>>(
+        (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,
+        (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, eps, num_slots, block_size,
+        status);
+    return;
+  }
   const long long blocks = (warps + 3) / 4;
   rope_qknorm_store_kernel<<<(unsigned)blocks, 128, 0, s>>>(
       (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,

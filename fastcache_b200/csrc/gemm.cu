@@ -57,6 +57,7 @@ struct GemmParams {
   uint32_t* status;
   int num_m, num_n, group_m;
   int total_work;
+  int up_row0;            // SWIGLU: row of W where the `up` half starts (= output width)
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -82,7 +83,7 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // + barriers + alignment slack
 };
 
-template <int BN, int STAGES, bool TRANS_OUT>
+template <int BN, int STAGES, bool TRANS_OUT, bool SWIGLU = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmParams p) {
@@ -161,7 +162,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, m_blk * BM);
-          tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, n_blk * BN);
+          if constexpr (SWIGLU) {
+            // B tile = 128 rows of the gate half + the matching 128 rows of the up half
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, n_blk * (BN / 2));
+            tma_load_2d(sb + L::B_BYTES / 2, &tma_b, &full_bar[stage], kb * BK, p.up_row0 + n_blk * (BN / 2));
+          } else {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, n_blk * BN);
+          }
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -292,7 +299,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       };
 
-      if (p.splits == 1) {
+      if constexpr (SWIGLU) {
+        // accumulator columns [0, BN/2) = gate, [BN/2, BN) = up; out[:, n_blk * BN/2 + j] = silu(gate_j) * up_j
+        const int jo = n_blk * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_addr + uint32_t(c * 32), rg);
+          tmem_ld_32x32(t_addr + uint32_t(BN / 2 + c * 32), ru);
+          tmem_ld_wait();
+          if (c == BN / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(&acc_empty[acc]);
+          }
+          if (gi < p.M) {
+            __nv_bfloat16* dst = p.C + (long long)gi * p.ldc_i + jo + c * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t u[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int t = q * 8 + e * 2;
+                const float g0 = __uint_as_float(rg[t]), g1 = __uint_as_float(rg[t + 1]);
+                const float a = g0 / (1.f + __expf(-g0)) * __uint_as_float(ru[t]);
+                const float b = g1 / (1.f + __expf(-g1)) * __uint_as_float(ru[t + 1]);
+                u[e] = pack_bf16(a, b);
+              }
+              *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(u[0], u[1], u[2], u[3]);
+            }
+          }
+        }
+      } else if (p.splits == 1) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -396,11 +433,11 @@ CUtensorMap make_tmap_bf16_2d(const void* base, uint64_t rows, uint64_t cols, ui
   return m;
 }
 
-template <int BN, int STAGES, bool TRANS>
+template <int BN, int STAGES, bool TRANS, bool SWIGLU = false>
 static void launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                        cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, STAGES, TRANS>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, TRANS, SWIGLU>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -455,6 +492,21 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
     p.num_m = (M + BM - 1) / BM;
     p.group_m = 16;
     CUtensorMap ta = make_tmap_bf16_2d(x, M, K, ldx, BM, BK);
+    if (act == ACT_SWIGLU) {
+      // w = [gate; up] stacked ([N, K], N = 2 x width); c is [M, N / 2]
+      constexpr int BN = 256;
+      const int width = N / 2;
+      if (N % 256 != 0 || ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(c) & 15) != 0 || bias != nullptr)
+        throw std::runtime_error("fused SwiGLU GEMM needs N % 256 == 0, a 16-byte aligned output and no bias");
+      p.N = width;
+      p.act = ACT_NONE;
+      p.up_row0 = width;
+      p.num_n = width / (BN / 2);
+      p.total_work = p.num_m * p.num_n;
+      CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, BN / 2, BK);
+      launch_one<BN, 4, false, true>(ta, tb, p, std::min(p.total_work, sms), stream);
+      return;
+    }
     if (N >= 256 || N % 256 == 0) {
       constexpr int BN = 256;
       p.num_n = (N + BN - 1) / BN;
@@ -470,6 +522,7 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
     }
     return;
   }
+  if (act == ACT_SWIGLU) throw std::runtime_error("fused SwiGLU GEMM is for M > 256; use linear_silu_mul below that");
   // decode-size batch: weight-streaming kernel (gemm_skinny.cu)
   gemm_skinny_bf16(x, w, c, bias, M, N, K, ldx, ldw, ldc, act, ws, sm_limit, 0, true, stream);
 }

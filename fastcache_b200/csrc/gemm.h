@@ -6,7 +6,8 @@
 
 namespace fc {
 
-enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_TANH = 3, ACT_QUICK_GELU = 4, ACT_SILU = 5 };
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_TANH = 3, ACT_QUICK_GELU = 4, ACT_SILU = 5,
+                 ACT_SWIGLU = 6 };   // w = [gate; up]: out[M, N/2] = silu(x gate^T) * (x up^T), M > 256 only
 
 // Split-K needs scratch for fp32 partial tiles and one arrival counter per output
 // tile (zero before the first launch; the kernel leaves them zero).

@@ -18,8 +18,11 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = N
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
     if act == "swiglu":
-        y = ext().gemm(x2, weight, bias, 0, None)
-        y = ext().silu_and_mul(y)
+        if x2.shape[0] > 256 and weight.shape[0] % 256 == 0 and bias is None:
+            y = ext().gemm(x2, weight, None, 6, None)        # SwiGLU applied in the GEMM epilogue
+        else:
+            y = ext().gemm(x2, weight, bias, 0, None)
+            y = ext().silu_and_mul(y)
     else:
         y = ext().gemm(x2, weight, bias, _ACT[act], out.reshape(-1, weight.shape[0]) if out is not None else None)
     return y.reshape(*lead, y.shape[-1])

@@ -38,3 +38,15 @@ def test_linear_silu_mul(M, I, K):
     want = ref.silu_and_mul(ref.linear(x.float(), w.float()).to(torch.bfloat16).float())
     torch.cuda.synchronize()
     assert ((y.float() - want).abs() / (want.abs() + 1.0)).max().item() < 3e-2
+
+
+@pytest.mark.parametrize("M,I,K", [(1000, 1024, 512), (4096, 12288, 4096), (257, 128, 64), (640, 2432, 1152)])
+def test_gemm_swiglu_epilogue(M, I, K):
+    """Prefill-size gate/up projection with SwiGLU applied in the GEMM epilogue."""
+    x, w = _rand(M, K, seed=8), _rand(2 * I, K, scale=0.05, seed=9)
+    y = ops.linear(x, w, None, act="swiglu")
+    assert y.shape == (M, I)
+    want = ref.silu_and_mul(ref.linear(x.float(), w.float()))
+    torch.cuda.synchronize()
+    assert ops.ext().read_status(0) == 0
+    assert ((y.float() - want).abs() / (want.abs() + 1.0)).max().item() < 3e-2
