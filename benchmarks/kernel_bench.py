@@ -99,7 +99,7 @@ def bench_prefill_attn(rows):
         cu = (torch.arange(nseq + 1, device="cuda") * S).int()
         kl = torch.full((nseq,), S, dtype=torch.int32, device="cuda")
         flops = 4.0 * nseq * Hq * D * S * S / 2
-        for impl, name in ((1, "mma.sync"), (2, "tcgen05")):
+        for impl, name in ((1, "mma.sync"), (2, "tcgen05"), (3, "tcgen05 2-tile")):
             ms = timeit(lambda: ops.prefill_attention(q, kc, vc, bt, cu, kl, D ** -0.5, S, impl), iters=5)
             rows.append({"kernel": "prefill_attn", "impl": name, "seqs": nseq, "S": S, "Hq": Hq, "Hkv": Hkv,
                          "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),

@@ -282,7 +282,8 @@ void check_cache(const Tensor& kc, const Tensor& vc, int64_t D) {
 Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_tables,
                          const Tensor& cu_q, const Tensor& kv_lens, double scale, int64_t max_q_len,
                          int64_t impl) {
-  // impl: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel
+  // impl: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel (one query tile per CTA),
+  // 3 = tcgen05 kernel with two query tiles per CTA (what 0 picks for head_dim 128)
   check_bf16(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous(), "q must be contiguous [T, Hq, D]");
   const int64_t Hq = q.size(1), D = q.size(2);
@@ -296,7 +297,15 @@ Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, co
   c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty_like(q);
   const bool tc_ok = fc::prefill_attention_tc_supported(int(D), int(kc.size(2)));
-  TORCH_CHECK(impl != 2 || tc_ok, "tcgen05 prefill attention needs head_dim 128 and block_size % 8 == 0");
+  TORCH_CHECK((impl != 2 && impl != 3) || tc_ok, "tcgen05 prefill attention needs head_dim 128 and block_size % 8 == 0");
+  if (impl == 3 || (impl == 0 && tc_ok && max_q_len > 64)) {
+    fc::launch_prefill_attention_tc2(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
+                                     cu_q.data_ptr<int>(), kv_lens.data_ptr<int>(), out.data_ptr(), q.size(0), int(B),
+                                     int(max_q_len), int(Hq), int(kc.size(1)), int(kc.size(2)),
+                                     int(block_tables.size(1)), int(kc.size(0)), float(scale),
+                                     status_ptr(q.get_device()), at::cuda::getCurrentCUDAStream());
+    return out;
+  }
   if (impl == 2 || (impl == 0 && tc_ok && max_q_len > 64)) {
     fc::launch_prefill_attention_tc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(),
                                     cu_q.data_ptr<int>(), kv_lens.data_ptr<int>(), out.data_ptr(), q.size(0), int(B),

@@ -36,6 +36,11 @@ void launch_prefill_attention_tc(const void* q, const void* k_cache, const void*
                                  const int* cu_seqlens_q, const int* kv_lens, void* out, long long total_q,
                                  int num_seqs, int max_q_len, int Hq, int Hkv, int block_size, int max_blocks,
                                  int num_blocks, float scale, uint32_t* status, cudaStream_t stream);
+// two query tiles per CTA in ping-pong, P and O in tensor memory (same limits)
+void launch_prefill_attention_tc2(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                                  const int* cu_seqlens_q, const int* kv_lens, void* out, long long total_q,
+                                  int num_seqs, int max_q_len, int Hq, int Hkv, int block_size, int max_blocks,
+                                  int num_blocks, float scale, uint32_t* status, cudaStream_t stream);
 }  // namespace fc
 
 namespace fc {

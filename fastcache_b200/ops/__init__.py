@@ -105,8 +105,9 @@ def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_d
 
 def prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
                       max_q_len: int = 0, impl: int = 0):
-    """Causal attention of new tokens over the paged cache.  `impl`: 0 picks the kernel (tcgen05 for
-    head_dim 128 and more than 64 query rows), 1 forces the mma.sync kernel, 2 the tcgen05 kernel."""
+    """Causal attention of new tokens over the paged cache.  `impl`: 0 picks the kernel (the two-tile
+    tcgen05 kernel for head_dim 128 and more than 64 query rows), 1 forces the mma.sync kernel, 2 the
+    one-tile tcgen05 kernel, 3 the two-tile tcgen05 kernel."""
     if q.is_cuda:
         _n()
         return ext().prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens,

@@ -141,9 +141,9 @@ def test_decode_attention(D, Hq, Hkv, bs, lens, splits):
     (64, 4, 2, 16, [128, 128], [128, 128]), (128, 8, 2, 32, [10, 100], [74, 228]),
     (128, 32, 8, 64, [1000], [1000]), (128, 4, 2, 8, [257, 3], [300, 131]),
     (128, 16, 8, 256, [2048, 700], [2048, 1212])])
-@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("impl", [1, 2, 3])
 def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens, impl):
-    if impl == 2 and D != 128:
+    if impl >= 2 and D != 128:
         pytest.skip("the tcgen05 kernel is head_dim 128 only")
     B = len(qlens)
     kc, vc, bt = _paged(B, kvlens, Hkv, D, bs, seed=4)
