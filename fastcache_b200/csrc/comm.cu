@@ -140,11 +140,19 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-          for (int p = 0; p < peers.world; ++p) {
-            float f[8];
-            unpack8f(ld_peer_16(peers.data[buf][p] + off), f);
+          // all peers' pieces are requested before the first is used (one NVLink round trip, not `world`)
+          uint4 raw[COMM_MAX_WORLD];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          for (int p = 0; p < COMM_MAX_WORLD; ++p)
+            if (p < peers.world) raw[p] = ld_peer_16(peers.data[buf][p] + off);
+#pragma unroll
+          for (int p = 0; p < COMM_MAX_WORLD; ++p) {
+            if (p < peers.world) {
+              float f[8];
+              unpack8f(raw[p], f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] += f[i];
+            }
           }
         }
         float r[8];

@@ -88,6 +88,106 @@ __device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoc
   return false;
 }
 
+// Phase 2 of MODE_RS for the rows this rank owns.  One warp per row, U 16-byte pieces per lane in
+// flight: pass 1 sums the tp partial rows and the residual (written back), pass 2 re-reads the new
+// residual (the lane's own lines), scales it and stores the row into every rank's gathered buffer as
+// full 512-byte warp stores.
+template <int TPMAX, int U>
+__device__ __forceinline__ void tp_reduce_rows(const TpGemmParams& p, int row0, int my_rows, int warp, int lane) {
+  const int chunks = p.N >> 3;                         // 16-byte pieces per row
+  constexpr int WARPS = TP_THREADS / 32;
+  for (int r = blockIdx.x * WARPS + warp; r < my_rows; r += gridDim.x * WARPS) {
+    __nv_bfloat16* res_row = p.residual + (long long)r * p.N;
+    float ss = 0.f;
+    for (int i0 = lane; i0 < chunks; i0 += 32 * U) {
+      uint4 part[U][TPMAX];
+      uint4 ru[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+#pragma unroll
+          for (int s = 0; s < TPMAX; ++s)
+            if (s < p.tp)
+              part[u][s] = __ldcg(reinterpret_cast<const uint4*>(
+                  p.stage_local + ((long long)s * p.chunk_rows + r) * p.N + idx * 8));
+          ru[u] = *reinterpret_cast<const uint4*>(res_row + idx * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          float acc8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc8[i] = 0.f;
+#pragma unroll
+          for (int s = 0; s < TPMAX; ++s) {
+            if (s < p.tp) {
+              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&part[u][s]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h2[i]);
+                acc8[2 * i] += f.x;
+                acc8[2 * i + 1] += f.y;
+              }
+            }
+          }
+          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&ru[u]);
+          uint4 su;
+          uint32_t* sw = reinterpret_cast<uint32_t*>(&su);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(rh[i]);
+            sw[i] = pack_bf16(acc8[2 * i] + f.x, acc8[2 * i + 1] + f.y);
+          }
+          *reinterpret_cast<uint4*>(res_row + idx * 8) = su;
+          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(sh[i]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+    }
+    const float inv = rsqrtf(warp_sum(ss) / float(p.N) + p.eps);
+    const long long off_row = (long long)(row0 + r) * p.N;
+    for (int i0 = lane; i0 < chunks; i0 += 32 * U) {
+      uint4 su[U], gu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          su[u] = *reinterpret_cast<const uint4*>(res_row + idx * 8);
+          gu[u] = *reinterpret_cast<const uint4*>(p.norm_w + idx * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su[u]);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu[u]);
+          uint4 ou;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&ou);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(sh[i]);
+            const float2 g2 = __bfloat1622float2(gh[i]);
+            const float a = __bfloat162float(__float2bfloat16(f.x * inv)) * g2.x;
+            const float b = __bfloat162float(__float2bfloat16(f.y * inv)) * g2.y;
+            ow[i] = pack_bf16(a, b);
+          }
+#pragma unroll
+          for (int d = 0; d < TPMAX; ++d)
+            if (d < p.tp) *reinterpret_cast<uint4*>(p.xg_peer[d] + off_row + idx * 8) = ou;
+        }
+      }
+    }
+  }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -101,6 +201,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* s_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);   // [0] abort, [1] scratch
+  // per epilogue warp: 32 rows x 64 columns of bf16 output on their way from "one row per lane" to
+  // "eight lanes per 128-byte row piece" (row pitch 144 bytes keeps both phases free of bank conflicts)
+  uint8_t* out_stage = smem + TP_STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -222,7 +325,6 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   } else {
     const int lane_group = warp & 3;
-    const int row = lane_group * 32 + lane;
     const int ep_tid = (warp - 2) * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -236,50 +338,64 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * TP_BN);
-      const int gi = m_blk * TP_BM + row;                 // token row
       const int owner = m_blk / p.blocks_per_chunk;
-      __nv_bfloat16* dst_row;
-      if (MODE == MODE_RS)
-        dst_row = p.stage_peer[owner] + ((long long)p.rank * p.chunk_rows + (gi - owner * p.chunk_rows)) * p.N;
-      else
-        dst_row = p.C + (long long)gi * p.ldc;
+      const int gi0 = m_blk * TP_BM + lane_group * 32;    // first token row of this warp's 32 rows
+      // row `gi0 + rr` of the output lives at dst0 + rr * ld
+      __nv_bfloat16* dst0;
+      long long ld;
+      if (MODE == MODE_RS) {
+        ld = p.N;
+        dst0 = p.stage_peer[owner] + ((long long)p.rank * p.chunk_rows + (gi0 - owner * p.chunk_rows)) * p.N;
+      } else {
+        ld = p.ldc;
+        dst0 = p.C + (long long)gi0 * p.ldc;
+      }
+      uint8_t* stg = out_stage + (warp - 2) * (32 * 144);
 #pragma unroll 1
-      for (int c = 0; c < TP_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + uint32_t(c * 32), r);
-        tmem_ld_wait();
-        if (c == TP_BN / 32 - 1) {
-          tc_fence_before();
-          mbar_arrive(&acc_empty[acc]);
-        }
-        const int jb = n_blk * TP_BN + c * 32;
-        if (gi < p.M) {
-          if (jb + 32 <= p.N) {
+      for (int c2 = 0; c2 < TP_BN / 64; ++c2) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
-              u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
-              u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
-              u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst_row + jb + q * 8) = u;
-            }
-          } else {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + uint32_t(c2 * 64 + half * 32), r);
+          tmem_ld_wait();
+          if (c2 == TP_BN / 64 - 1 && half == 1) {
+            tc_fence_before();
+            mbar_arrive(&acc_empty[acc]);
+          }
 #pragma unroll
-            for (int t = 0; t < 32; ++t)
-              if (jb + t < p.N) dst_row[jb + t] = __float2bfloat16(__uint_as_float(r[t]));
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+            *reinterpret_cast<uint4*>(stg + lane * 144 + half * 64 + q * 16) = u;
           }
         }
+        __syncwarp();
+        // eight lanes write one 128-byte piece of a row: full lines towards HBM or NVLink
+        const int jb = n_blk * TP_BN + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = (lane >> 3) + 4 * i;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 144 + (lane & 7) * 16);
+          if (gi0 + rr < p.M && jb < p.N) *reinterpret_cast<uint4*>(dst0 + (long long)rr * ld + jb) = v;
+        }
+        __syncwarp();
       }
       if (MODE == MODE_RS) {
-        // this tile is delivered: count it, and raise the owner's flag after the last one
-        __threadfence_system();
+        // this tile is delivered: one thread makes the CTA's stores visible system-wide and counts the
+        // tile; the owner's flag goes up after the last one
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ep_tid == 0) {
+          __threadfence_system();
           const int first = owner * p.blocks_per_chunk;
           const int nblk = max(0, min(p.num_m - first, p.blocks_per_chunk));
           const int old = atomicAdd(&p.owner_done[owner], 1);
-          if (old + 1 == nblk * p.num_n) tp_st_release(p.rs_flag_peer[owner] + p.rank, p.epoch);
+          if (old + 1 == nblk * p.num_n) {
+            __threadfence_system();
+            tp_st_release(p.rs_flag_peer[owner] + p.rank, p.epoch);
+          }
         }
       }
       acc ^= 1;
@@ -304,79 +420,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
     __syncthreads();
     if (!s_flag[0]) {
-      __shared__ float red[TP_THREADS / 32];
-      const int chunks = p.N >> 3;                         // 16-byte pieces per row
-      constexpr int MAXC = 6;                              // 192 threads * 6 * 8 = 9216 columns
-      for (int r = blockIdx.x; r < my_rows; r += gridDim.x) {
-        float v[MAXC][8];
-        float ss = 0.f;
-#pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-          const int idx = threadIdx.x + c * TP_THREADS;
-          if (idx < chunks) {
-            float acc8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc8[i] = 0.f;
-            for (int s = 0; s < p.tp; ++s) {
-              const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
-                  p.stage_local + ((long long)s * p.chunk_rows + r) * p.N + idx * 8));
-              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(h2[i]);
-                acc8[2 * i] += f.x;
-                acc8[2 * i + 1] += f.y;
-              }
-            }
-            uint4* rp = reinterpret_cast<uint4*>(p.residual + (long long)r * p.N + idx * 8);
-            const uint4 ru = *rp;
-            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&ru);
-            uint4 su;
-            uint32_t* sw = reinterpret_cast<uint32_t*>(&su);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(rh[i]);
-              sw[i] = pack_bf16(acc8[2 * i] + f.x, acc8[2 * i + 1] + f.y);
-            }
-            *rp = su;
-            const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(sh[i]);
-              v[c][2 * i] = f.x;
-              v[c][2 * i + 1] = f.y;
-              ss += f.x * f.x + f.y * f.y;
-            }
-          }
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-#pragma unroll
-        for (int wq = 0; wq < TP_THREADS / 32; ++wq) tot += red[wq];
-        __syncthreads();
-        const float inv = rsqrtf(tot / float(p.N) + p.eps);
-#pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-          const int idx = threadIdx.x + c * TP_THREADS;
-          if (idx < chunks) {
-            const uint4 gu = *reinterpret_cast<const uint4*>(p.norm_w + idx * 8);
-            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
-            uint4 ou;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&ou);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 g2 = __bfloat1622float2(gh[i]);
-              const float a = __bfloat162float(__float2bfloat16(v[c][2 * i] * inv)) * g2.x;
-              const float b = __bfloat162float(__float2bfloat16(v[c][2 * i + 1] * inv)) * g2.y;
-              ow[i] = pack_bf16(a, b);
-            }
-            const long long off = (long long)(row0 + r) * p.N + idx * 8;
-            for (int d = 0; d < p.tp; ++d) *reinterpret_cast<uint4*>(p.xg_peer[d] + off) = ou;
-          }
-        }
-      }
+      if (p.tp <= 2) tp_reduce_rows<2, 8>(p, row0, my_rows, warp, lane);
+      else if (p.tp <= 4) tp_reduce_rows<4, 4>(p, row0, my_rows, warp, lane);
+      else tp_reduce_rows<8, 2>(p, row0, my_rows, warp, lane);
     }
   }
   // the last CTA to get here publishes "rows of this rank are gathered" everywhere and resets the counters
@@ -392,7 +438,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 }
 
-static int tp_smem_bytes() { return TP_STAGES * (TP_BM * TP_BK * 2 + TP_BN * TP_BK * 2) + 256 + 1024; }
+static int tp_smem_bytes() {
+  // operand ring + barriers + output staging (4 epilogue warps x 32 rows x 144 bytes) + alignment slack
+  return TP_STAGES * (TP_BM * TP_BK * 2 + TP_BN * TP_BK * 2) + 256 + 4 * 32 * 144 + 1024;
+}
 
 static void fill_common(TpGemmParams& p, int M, int N, int K, int tp, int rank, int chunk_rows, uint32_t epoch,
                         uint32_t* status, bool own_first) {
