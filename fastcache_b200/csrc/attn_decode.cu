@@ -27,6 +27,7 @@
 
 #include "gemm.h"
 #include "kernels.h"
+#include "launch.h"
 #include "mma.cuh"
 #include "ptx.cuh"
 
@@ -58,6 +59,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const uint32_t s_base = smem_u32(smem);
   // stage s: K tile at s * 2 * TILE_BYTES, V tile right after; a tile is D/64 sub-tiles of [64 rows x 128 B]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + DEC_STAGES * 2 * TILE_BYTES);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < DEC_STAGES; ++s) mbar_init(&full_bar[s], 1);
     fence_barrier_init();
@@ -65,6 +67,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     tma_prefetch_desc(&tm_v);
   }
   __syncthreads();
+  pdl_wait();                                // q and the new K/V rows come from the kernels before this one
+  // the rows were written with ordinary stores and are read by TMA: order the two proxies
+  asm volatile("fence.proxy.async.global;" ::: "memory");
 
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
@@ -291,6 +296,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 // out[b, h, :] = sum_s w_s * part_o[b, h, s, :],  w_s = 2^(lse_s - max) / sum
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                     bf16* __restrict__ out, int splits, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long bh = blockIdx.x;
   const float* lse = part_lse + bh * splits;
   float mx = -INFINITY;
@@ -338,14 +345,16 @@ void launch_decode_attention(const void* q, const void* k_cache, const void* v_c
   auto launch = [&](auto kern) {
     // set on every launch: both head-dim instantiations share this lambda's function-pointer type
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    kern<<<grid, DEC_THREADS, smem, stream>>>(tk, tv, (const bf16*)q, box_rows, block_tables, context_lens,
-                                              (bf16*)out, part_o, part_lse, Hq, Hkv, block_size, max_blocks,
-                                              num_blocks, splits, scale_log2, status);
+    launch_pdl(PDL_DECODE_ATTN, kern, grid, dim3(DEC_THREADS), smem, stream, tk, tv, (const bf16*)q, box_rows, block_tables,
+               context_lens, (bf16*)out, part_o, part_lse, Hq, Hkv, block_size, max_blocks, num_blocks, splits,
+               scale_log2, status);
   };
   if (D == 128) launch(decode_attn_kernel<128>);
   else if (D == 64) launch(decode_attn_kernel<64>);
   else throw std::runtime_error("decode attention: head_dim must be 64 or 128");
-  if (splits > 1) decode_merge_kernel<<<B * Hq, 128, 0, stream>>>(part_o, part_lse, (bf16*)out, splits, D);
+  if (splits > 1)
+    launch_pdl(PDL_DECODE_MERGE, decode_merge_kernel, dim3(B * Hq), dim3(128), 0, stream, (const float*)part_o, (const float*)part_lse,
+               (bf16*)out, splits, D);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("decode attention launch: ") + cudaGetErrorString(e));
 }

@@ -22,6 +22,7 @@
 #include <string>
 
 #include "comm.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace fc {
@@ -116,6 +117,8 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
                              uint32_t* __restrict__ epochs, uint32_t* status) {
   __shared__ float red[32];
   __shared__ uint32_t s_epoch;
+  pdl_launch_dependents();
+  pdl_wait();                            // the GEMM that filled the staging buffer, the previous epoch counters
   const int slot = blockIdx.x;
   if (threadIdx.x == 0) s_epoch = epochs[slot] + 1;
   __syncthreads();
@@ -195,13 +198,14 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
   if (H % 8 != 0 || H > AR_THREADS * AR_MAX_CHUNKS * 8) throw std::runtime_error("allreduce: unsupported hidden size");
   // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
   const int grid = T < COMM_MAX_SLOTS ? T : COMM_MAX_SLOTS;
+  cudaError_t e;
   if (use_multimem && mc_in != nullptr)
-    allreduce_add_rmsnorm_kernel<true><<<grid, AR_THREADS, 0, stream>>>(
-        peers, buf, (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<true>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
+                   (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
   else
-    allreduce_add_rmsnorm_kernel<false><<<grid, AR_THREADS, 0, stream>>>(
-        peers, buf, nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
-  cudaError_t e = cudaGetLastError();
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<false>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
+                   (const bf16*)nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("allreduce launch: ") + cudaGetErrorString(e));
 }
 

@@ -8,6 +8,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace fc {
@@ -58,6 +59,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
                 bf16* __restrict__ y, int H, float eps) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   const int chunks = H >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
@@ -169,6 +172,8 @@ __global__ void silu_and_mul_kernel(const bf16* __restrict__ x, bf16* __restrict
 // out[t, :] = (vocab_start <= ids[t] < vocab_start + V) ? weight[ids[t] - vocab_start, :] : 0
 __global__ void embedding_kernel(const long long* __restrict__ ids, const bf16* __restrict__ weight,
                                  bf16* __restrict__ out, int T, int H, int V, int vocab_start) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long id = ids[t] - vocab_start;
   const int chunks = H >> 3;
@@ -285,6 +290,8 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
                               const bf16* __restrict__ k_w, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
                               bf16* __restrict__ v_cache, const int* __restrict__ slots, int T, int Hq, int Hkv,
                               float eps, long long num_slots, int block_size, uint32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int heads = Hq + 2 * Hkv;
   const long long gid = (blockIdx.x * 256ll + threadIdx.x) >> 3;
   const int j = threadIdx.x & 7;
@@ -374,6 +381,8 @@ sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, 
               int V, long long ld, uint32_t seed) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   const float T = temps[b];
   const bf16* row = logits + (long long)b * ld;
@@ -440,11 +449,11 @@ void launch_rms_norm(const void* x, void* residual, const void* w, void* y, long
                      cudaStream_t s) {
   if (T == 0) return;
   if (residual != nullptr)
-    rms_norm_kernel<true><<<(unsigned)T, NORM_THREADS, 0, s>>>((const bf16*)x, (bf16*)residual, (const bf16*)w,
-                                                               (bf16*)y, H, eps);
+    launch_pdl(PDL_NORM, rms_norm_kernel<true>, dim3((unsigned)T), dim3(NORM_THREADS), 0, s, (const bf16*)x, (bf16*)residual,
+               (const bf16*)w, (bf16*)y, H, eps);
   else
-    rms_norm_kernel<false><<<(unsigned)T, NORM_THREADS, 0, s>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y,
-                                                                H, eps);
+    launch_pdl(PDL_NORM, rms_norm_kernel<false>, dim3((unsigned)T), dim3(NORM_THREADS), 0, s, (const bf16*)x, (bf16*)nullptr,
+               (const bf16*)w, (bf16*)y, H, eps);
 }
 
 void launch_layer_norm(const void* x, const void* w, const void* b, void* y, long long T, int H, float eps,
@@ -464,7 +473,8 @@ void launch_silu_and_mul(const void* x, void* y, long long T, int I, cudaStream_
 void launch_embedding(const void* ids, const void* weight, void* out, int T, int H, int V, int vocab_start,
                       cudaStream_t s) {
   if (T == 0) return;
-  embedding_kernel<<<T, 128, 0, s>>>((const long long*)ids, (const bf16*)weight, (bf16*)out, T, H, V, vocab_start);
+  launch_pdl(PDL_EMBEDDING, embedding_kernel, dim3(T), dim3(128), 0, s, (const long long*)ids, (const bf16*)weight, (bf16*)out, T, H,
+             V, vocab_start);
 }
 
 void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
@@ -474,10 +484,10 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
   if (T == 0) return;
   const long long warps = (long long)T * (Hq + 2 * Hkv);
   if (D == 128 && slots != nullptr) {
-    rope_qknorm_store_d128_kernel<<<(unsigned)((warps + 31) / 32), 256, 0, s>>>(
-        (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,
-        (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, eps, num_slots, block_size,
-        status);
+    launch_pdl(PDL_ROPE, rope_qknorm_store_d128_kernel, dim3((unsigned)((warps + 31) / 32)), dim3(256), 0, s,
+               (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w,
+               (const bf16*)k_w, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, eps,
+               num_slots, block_size, status);
     return;
   }
   const long long blocks = (warps + 3) / 4;
@@ -490,7 +500,8 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
                    cudaStream_t s) {
   if (B == 0) return;
-  sample_kernel<<<B, 1024, 0, s>>>((const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed);
+  launch_pdl(PDL_SAMPLE, sample_kernel, dim3(B), dim3(1024), 0, s, (const bf16*)logits, (const float*)temps, (long long*)out, V,
+             ld, seed);
 }
 
 }  // namespace fc

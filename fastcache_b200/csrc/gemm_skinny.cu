@@ -25,6 +25,7 @@
 #include <string>
 
 #include "gemm.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace fc {
@@ -83,6 +84,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   const int tile = blockIdx.x, split = blockIdx.y;
@@ -109,6 +111,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                              // x, the scratch and the output belong to earlier kernels until here
+  asm volatile("fence.proxy.async.global;" ::: "memory");   // x: ordinary stores before, TMA reads now
 
   if (warp == 0) {
     if (lane == 0) {
@@ -225,6 +229,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 __global__ void skinny_finalize_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias,
                                        __nv_bfloat16* __restrict__ out, int M, int N, long long ldc, int splits,
                                        int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)M * (N / 4);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -262,8 +268,8 @@ static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Sk
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<dim3(tiles, p.splits), SK_THREADS, L::TOTAL, stream>>>(tw, tx, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(PDL_SKINNY_GEMM, kern, dim3(tiles, p.splits), dim3(SK_THREADS), L::TOTAL, stream, tw, tx, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("skinny gemm launch: ") + cudaGetErrorString(e));
 }
 
@@ -331,7 +337,8 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   if (splits > 1 && finalize) {
     const long long total = (long long)M * (N / 4);
     const int blocks = (int)std::min<long long>((total + 255) / 256, 2048);
-    skinny_finalize_kernel<<<blocks, 256, 0, stream>>>(ws.scratch, p.bias, p.out, M, N, ldc, splits, act);
+    launch_pdl(PDL_FINALIZE, skinny_finalize_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)ws.scratch, p.bias, p.out, M,
+               N, ldc, splits, act);
   }
   return splits;
 }

@@ -10,6 +10,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace fc {
@@ -24,6 +25,8 @@ add_rms_norm_partials_kernel(const float* __restrict__ partial, int splits, long
                              const bf16* __restrict__ bias, bf16* __restrict__ residual,
                              const bf16* __restrict__ w, bf16* __restrict__ y, int H, float eps) {
   __shared__ float red[PN_THREADS / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   const int chunks = H >> 3;
   float v[PN_MAX_CHUNKS][8];
@@ -100,6 +103,8 @@ add_rms_norm_partials_kernel(const float* __restrict__ partial, int splits, long
 // out[t, i] = silu(g) * u with g = sum_s partial[s, t, i], u = sum_s partial[s, t, I + i]
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partial, int splits, long long split_stride,
                                          bf16* __restrict__ out, long long T, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int quads = I >> 2;
   const long long total = T * quads;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -130,8 +135,8 @@ void launch_add_rms_norm_partials(const float* partial, int splits, long long sp
                                   void* residual, const void* w, void* y, long long T, int H, float eps,
                                   cudaStream_t s) {
   if (T == 0) return;
-  add_rms_norm_partials_kernel<<<(unsigned)T, PN_THREADS, 0, s>>>(partial, splits, split_stride, (const bf16*)bias,
-                                                                  (bf16*)residual, (const bf16*)w, (bf16*)y, H, eps);
+  launch_pdl(PDL_PARTIALS, add_rms_norm_partials_kernel, dim3((unsigned)T), dim3(PN_THREADS), 0, s, partial, splits, split_stride,
+             (const bf16*)bias, (bf16*)residual, (const bf16*)w, (bf16*)y, H, eps);
 }
 
 void launch_silu_mul_partials(const float* partial, int splits, long long split_stride, void* out, long long T,
@@ -139,7 +144,7 @@ void launch_silu_mul_partials(const float* partial, int splits, long long split_
   if (T == 0) return;
   const long long total = T * (I >> 2);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 8);
-  silu_mul_partials_kernel<<<blocks, 256, 0, s>>>(partial, splits, split_stride, (bf16*)out, T, I);
+  launch_pdl(PDL_PARTIALS, silu_mul_partials_kernel, dim3(blocks), dim3(256), 0, s, partial, splits, split_stride, (bf16*)out, T, I);
 }
 
 }  // namespace fc

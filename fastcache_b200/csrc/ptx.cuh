@@ -207,6 +207,17 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with `launch_pdl` (launch.h) may start while its predecessor in the stream is
+// still running.  `pdl_launch_dependents()` at the top lets the successor's CTAs be scheduled early;
+// `pdl_wait()` returns once the predecessor grid has completed and its writes are visible.  Only work
+// that touches no global memory (barrier init, TMEM allocation, descriptor prefetch) may come before
+// `pdl_wait()`.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ misc
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
