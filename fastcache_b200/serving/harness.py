@@ -403,7 +403,10 @@ class ConcurrentTester:
 
     def run(self, prompts: Sequence[Any], max_tokens: int = 128, images: Optional[Sequence[Any]] = None,
             temperature: float = 0.0, time_scale: float = 1.0,
-            on_step: Optional[Callable[[int], None]] = None) -> TestResult:
+            on_step: Optional[Callable[[int], None]] = None,
+            agree: Optional[Callable[[int], int]] = None) -> TestResult:
+        """`agree(n)`: under tensor parallelism every rank must admit the same requests before the same
+        step; each rank passes the number of arrivals it sees as due and gets back rank 0's number."""
         from ..sampling_params import SamplingParams
         llm = self.llm
         reqs = [Request(i, p, max_tokens, images[i] if images else None) for i, p in enumerate(prompts)]
@@ -415,7 +418,12 @@ class ConcurrentTester:
         t0 = time.perf_counter()
         while nxt < len(reqs) or not llm.is_finished():
             now = time.perf_counter() - t0
-            while nxt < len(reqs) and arrivals[nxt] <= now:
+            due = nxt
+            while due < len(reqs) and arrivals[due] <= now:
+                due += 1
+            if agree is not None:
+                due = max(nxt, min(len(reqs), int(agree(due))))
+            while nxt < due:
                 r = reqs[nxt]
                 r.metrics.arrival = t0 + arrivals[nxt]
                 self.timestamps.record(r.request_id, "arrival", r.metrics.arrival)
