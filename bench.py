@@ -50,9 +50,18 @@ LLAMA2_7B = dict(model_type="llama", architectures=["LlamaForCausalLM"], hidden_
                  tie_word_embeddings=False, eos_token_id=2, bos_token_id=1, torch_dtype="bfloat16",
                  hidden_act="silu", attention_bias=False)
 
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600)
+
+# Long prompts under memory pressure: lazy CCM merge (ratio 4) fires when the paged pool passes 90 %
+LAZY_CCM = dict(mode="lazy", threshold=0.9, factor=4, compressor="KVCacheLinearCompressor")
+
 WORKLOADS = {
-    # name: (hf config, requests, prompt tokens, output tokens)
+    # name: (hf config, requests, prompt tokens, output tokens[, compression override])
     "qwen3-8b": (QWEN3_8B, 128, 4096, 512),
+    # 8 GPUs: 256 x 32768-token prompts do not fit the pool uncompressed (262 KB of KV per token)
+    "qwen3-32b": (QWEN3_32B, 256, 32768, 256, LAZY_CCM),
+    "qwen3-32b-small": (dict(QWEN3_32B, num_hidden_layers=4), 24, 32768, 32, LAZY_CCM),
     # the language model of the LLaVA-1.5-7B config, text only (MHA: 4x the KV bytes per token of Qwen3-8B)
     "llama2-7b": (LLAMA2_7B, 64, 2048, 256),
     # shrunken variants for quick functional checks; never reported as the headline
@@ -63,6 +72,8 @@ MODEL_LABEL = {
     "qwen3-8b": "Qwen3-8B shape (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)",
     "llama2-7b": "Llama-2-7B shape (32L, h4096, 32 MHA heads, d128, ffn11008, vocab32000)",
     "qwen3-8b-small": "Qwen3-8B shape cut to 4 layers (functional check only)",
+    "qwen3-32b": "Qwen3-32B shape (64L, h5120, 64q/8kv, d128, ffn25600, vocab151936)",
+    "qwen3-32b-small": "Qwen3-32B shape cut to 4 layers (functional check only)",
     "llama2-7b-small": "Llama-2-7B shape cut to 4 layers (functional check only)",
 }
 
@@ -160,15 +171,35 @@ def run_ours(args):
     from fastcache_b200.parallel import tp as tpmod
     if world > 1:
         tpmod.init_tensor_parallel(world, rank)
-    hf, n_req, p_len, o_len = WORKLOADS[args.config]
+    hf, n_req, p_len, o_len = WORKLOADS[args.config][:4]
+    override = WORKLOADS[args.config][4] if len(WORKLOADS[args.config]) > 4 else None
     n_req = args.requests or n_req
     method = args.method
     kv_params = {"window": 64, "kernel_size": 5} if method == "snapkv" else {}
+    if override is None:
+        comp_kw = dict(enable_compression=not args.no_compression, compression_backend="kvpress",
+                       kvpress_method=method, compression_factor=2, compression_pipeline="prefill",
+                       kvpress_params=kv_params)
+        comp_label = f"{method} keep 50%"
+    else:
+        from fastcache_b200 import compress as compress_mod
+        head_dim = hf.get("head_dim") or hf["hidden_size"] // hf["num_attention_heads"]
+        torch.manual_seed(0)
+        comp = getattr(compress_mod, override["compressor"])(None, override["factor"], 2,
+                                                             n_layer=hf["num_hidden_layers"], nhead=2,
+                                                             head_dim=head_dim)
+        for prm in comp.parameters():
+            torch.nn.init.normal_(prm, std=0.02)
+        comp_kw = dict(compression_mode=override["mode"], lazy_occupancy_threshold=override["threshold"],
+                       compression_backend="mlp", compressor=comp.eval(), compression_factor=override["factor"],
+                       compression_pipeline="prefill")
+        if args.no_compression:
+            comp_kw = dict(enable_compression=False)
+        comp_label = f"{override['mode']} CCM merge ratio {override['factor']} above {override['threshold']:.0%} pool occupancy"
     llm = LLM(dict(hf), tensor_parallel_size=world, device=f"cuda:{local_rank}", kvcache_block_size=256,
               max_model_len=p_len + o_len + 256, max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768,
-              gpu_memory_utilization=args.mem_util, enable_compression=not args.no_compression,
-              compression_backend="kvpress", kvpress_method=method, compression_factor=2,
-              compression_pipeline="prefill", kvpress_params=kv_params, seed=0, prefix_caching=False)
+              gpu_memory_utilization=args.mem_util, seed=0, prefix_caching=False,
+              **({"num_kvcache_blocks": args.kv_blocks} if args.kv_blocks > 0 else {}), **comp_kw)
     runner = llm.model_runner
     sp = SamplingParams(temperature=0.0, max_tokens=o_len, ignore_eos=True)
 
@@ -227,7 +258,9 @@ def run_ours(args):
             "data": "synthetic token ids, random-init weights",
             "config": {"model": MODEL_LABEL[args.config],
                        "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
-                       "parallelism": f"tp{world}", "compression": f"{method} keep 50%" if not args.no_compression else "none",
+                       "parallelism": f"tp{world}", "compression": comp_label if not args.no_compression else "none",
+                       "compressions": llm.stats.compressions, "lazy_triggers": llm.stats.lazy_triggers,
+                       "preemptions": llm.stats.preemptions, "blocks_freed": llm.stats.blocks_freed,
                        "cuda_graph_decode": True, "kv_block": 256,
                        "l2": "working set per step (weights 16 GB + KV) far exceeds the 126 MB L2; no flush needed",
                        "step": "one whole job (all requests submitted at once, served to completion)",
@@ -459,6 +492,7 @@ def main():
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--no-compression", action="store_true")
     ap.add_argument("--mem-util", type=float, default=0.85)
+    ap.add_argument("--kv-blocks", type=int, default=0, help="size of the paged pool in blocks (0 = from free memory)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.steps = max(1, args.steps)
