@@ -38,3 +38,46 @@ def test_gpu_first_tokens_match_cpu_oracle():
     cpu = _run("cpu", True, "fp32")
     agree = sum(g[0] == c[0] for g, c in zip(gpu, cpu))
     assert agree >= len(gpu) - 1, (gpu, cpu)
+
+
+def _llava_cfg():
+    from fastcache_b200 import ModelConfig
+    text = dict(model_type="llama", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=4, intermediate_size=512, vocab_size=600, rms_norm_eps=1e-5,
+                max_position_embeddings=1024, rope_theta=10000.0)
+    vis = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=4,
+               image_size=56, patch_size=14)
+    return ModelConfig(model_type="llava", architectures=["LlavaForConditionalGeneration"], text_config=text,
+                       vision_config=vis, image_token_index=500)
+
+
+def _minicpm_cfg():
+    from fastcache_b200 import ModelConfig
+    return ModelConfig(model_type="minicpmv", architectures=["MiniCPMV"], hidden_size=256, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, intermediate_size=512, vocab_size=600,
+                       rms_norm_eps=1e-6, max_position_embeddings=2048, rope_theta=1e6, query_num=4,
+                       max_slice_nums=9, scale_resolution=56, image_token_id=501,
+                       vision_config=dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                          num_attention_heads=4, image_size=140, patch_size=14))
+
+
+@pytest.mark.parametrize("make_cfg,img_tok", [(_llava_cfg, 500), (_minicpm_cfg, 501)])
+def test_multimodal_request_on_gpu_matches_cpu_first_token(make_cfg, img_tok):
+    """Vision tower (dense attention kernel, GEMMs), projector / resampler and the language model on
+    the GPU against the fp32 CPU path of the same seeded model: same image rows, same first token."""
+    g = torch.Generator().manual_seed(5)
+    img = torch.rand(3, 90, 70, generator=g)
+    prompt = [5, 6, img_tok, 7, 8, 9, 10]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs, rows = {}, {}
+    for dev, dtype in (("cuda", "auto"), ("cpu", "fp32")):
+        llm = LLM(make_cfg(), device=dev, dtype=dtype, kvcache_block_size=16, num_kvcache_blocks=128,
+                  max_model_len=512, enforce_eager=True, init_device="cpu")
+        seq = llm.add_request(prompt, sp, image=img)
+        rows[dev] = seq.prompt_rows
+        while not llm.is_finished():
+            llm.step()
+        outs[dev] = list(seq.completion_token_ids)
+        llm.exit()
+    assert rows["cuda"] == rows["cpu"] and len(outs["cuda"]) == 6
+    assert outs["cuda"][0] == outs["cpu"][0], (outs["cuda"], outs["cpu"])
