@@ -272,6 +272,43 @@ Tensor rope_qknorm_store(const Tensor& qkv, const Tensor& positions, const Tenso
   return q_out;
 }
 
+// qkv = x @ w.T, then q/k RMSNorm + rotary + paged K/V store (head_dim 128).  Decode-size GEMMs leave split-K
+// partial sums that the rope kernel reduces itself: two launches instead of three.
+Tensor linear_rope_qknorm_store(const Tensor& x, const Tensor& w, const Tensor& positions, const Tensor& cos_sin,
+                                int64_t Hq, int64_t Hkv, int64_t D, const c10::optional<Tensor>& q_w,
+                                const c10::optional<Tensor>& k_w, double eps, const Tensor& k_cache,
+                                const Tensor& v_cache, const Tensor& slots) {
+  check_linear_pair(x, w);
+  const int64_t T = x.size(0), N = w.size(0);
+  TORCH_CHECK(D == 128 && N == (Hq + 2 * Hkv) * D, "fused qkv + rope needs head_dim 128 and N = (Hq + 2 Hkv) * 128");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto& ws = workspace(x.get_device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  Tensor qkv = torch::empty({T, N}, x.options());
+  if (T == 0) return torch::empty({0, Hq, D}, x.options());
+  const int splits = gemm_maybe_partial(x, w, qkv, ws, stream);
+  if (splits <= 1) return rope_qknorm_store(qkv, positions, cos_sin, Hq, Hkv, D, q_w, k_w, eps, k_cache, v_cache, slots);
+  TORCH_CHECK(positions.scalar_type() == torch::kInt64 && positions.is_contiguous() && positions.is_cuda(),
+              "positions must be int64 CUDA");
+  TORCH_CHECK(cos_sin.scalar_type() == torch::kFloat32 && cos_sin.is_contiguous() && cos_sin.size(1) == D &&
+                  cos_sin.is_cuda(), "cos_sin must be fp32 [max_pos, D] on the device");
+  check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(3) == D &&
+                  k_cache.size(1) == Hkv, "cache layout must be contiguous [blocks, Hkv, block, D]");
+  TORCH_CHECK(slots.scalar_type() == torch::kInt32 && slots.numel() == T && slots.is_cuda(),
+              "slot_mapping must be int32 [T]");
+  const void *qw = nullptr, *kw = nullptr;
+  if (q_w.has_value() && q_w->defined()) { check_bf16(*q_w, "q_norm"); qw = q_w->data_ptr(); }
+  if (k_w.has_value() && k_w->defined()) { check_bf16(*k_w, "k_norm"); kw = k_w->data_ptr(); }
+  Tensor q_out = torch::empty({T, Hq, D}, x.options());
+  fc::launch_rope_qknorm_store(nullptr, positions.data_ptr(), cos_sin.data_ptr(), qw, kw, q_out.data_ptr(),
+                               k_cache.data_ptr(), v_cache.data_ptr(), slots.data_ptr(), int(T), int(Hq), int(Hkv),
+                               int(D), float(eps), k_cache.size(0) * k_cache.size(2), int(k_cache.size(2)),
+                               status_ptr(x.get_device()), stream, ws.gemm_scratch.data_ptr<float>(), splits, T * N);
+  return q_out;
+}
+
 void check_cache(const Tensor& kc, const Tensor& vc, int64_t D) {
   check_bf16(kc, "k_cache");
   check_bf16(vc, "v_cache");
@@ -423,6 +460,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_and_mul", &silu_and_mul);
   m.def("embedding", &embedding);
   m.def("rope_qknorm_store", &rope_qknorm_store);
+  m.def("linear_rope_qknorm_store", &linear_rope_qknorm_store);
   m.def("prefill_attention", &prefill_attention);
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,

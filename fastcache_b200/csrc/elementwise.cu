@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <algorithm>
+#include <stdexcept>
 
 #include "kernels.h"
 #include "launch.h"
@@ -289,7 +290,8 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
                               const float* __restrict__ cos_sin, const bf16* __restrict__ q_w,
                               const bf16* __restrict__ k_w, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
                               bf16* __restrict__ v_cache, const int* __restrict__ slots, int T, int Hq, int Hkv,
-                              float eps, long long num_slots, int block_size, uint32_t* status) {
+                              float eps, long long num_slots, int block_size, uint32_t* status,
+                              const float* __restrict__ partial, int splits, long long split_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int heads = Hq + 2 * Hkv;
@@ -299,8 +301,29 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
   const long long g = active ? gid : 0;
   const int t = int(g / heads);
   const int h = int(g - (long long)t * heads);
-  const uint4* src = reinterpret_cast<const uint4*>(qkv + ((long long)t * heads + h) * 128);
-  const uint4 ulo = src[j], uhi = src[8 + j];
+  uint4 ulo, uhi;
+  if (partial != nullptr) {
+    // qkv is still the split-K partial sums of its GEMM ([splits, T, heads * 128] fp32): reduce them here and
+    // round to bf16 as the GEMM epilogue would have
+    const float* p0 = partial + ((long long)t * heads + h) * 128 + 8 * j;
+    float a[8], b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = b[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float4* ps = reinterpret_cast<const float4*>(p0 + s * split_stride);
+      const float4 l0 = __ldcg(ps), l1 = __ldcg(ps + 1), h0 = __ldcg(ps + 16), h1 = __ldcg(ps + 17);
+      a[0] += l0.x; a[1] += l0.y; a[2] += l0.z; a[3] += l0.w;
+      a[4] += l1.x; a[5] += l1.y; a[6] += l1.z; a[7] += l1.w;
+      b[0] += h0.x; b[1] += h0.y; b[2] += h0.z; b[3] += h0.w;
+      b[4] += h1.x; b[5] += h1.y; b[6] += h1.z; b[7] += h1.w;
+    }
+    ulo = pack8(a);
+    uhi = pack8(b);
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(qkv + ((long long)t * heads + h) * 128);
+    ulo = src[j];
+    uhi = src[8 + j];
+  }
   long long slot = -1;
   if (h >= Hq && slots != nullptr) {
     slot = slots[t];
@@ -480,16 +503,18 @@ void launch_embedding(const void* ids, const void* weight, void* out, int T, int
 void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
                               const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
                               int Hq, int Hkv, int D, float eps, long long num_slots, int block_size,
-                              uint32_t* status, cudaStream_t s) {
+                              uint32_t* status, cudaStream_t s, const float* partial, int splits,
+                              long long split_stride) {
   if (T == 0) return;
   const long long warps = (long long)T * (Hq + 2 * Hkv);
   if (D == 128 && slots != nullptr) {
     launch_pdl(PDL_ROPE, rope_qknorm_store_d128_kernel, dim3((unsigned)((warps + 31) / 32)), dim3(256), 0, s,
                (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w,
                (const bf16*)k_w, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, T, Hq, Hkv, eps,
-               num_slots, block_size, status);
+               num_slots, block_size, status, partial, splits, split_stride);
     return;
   }
+  if (partial != nullptr) throw std::runtime_error("rope from split-K partial sums needs head_dim 128 and a slot map");
   const long long blocks = (warps + 3) / 4;
   rope_qknorm_store_kernel<<<(unsigned)blocks, 128, 0, s>>>(
       (const bf16*)qkv, (const long long*)positions, (const float*)cos_sin, (const bf16*)q_w, (const bf16*)k_w,

@@ -17,7 +17,9 @@ void launch_embedding(const void* ids, const void* weight, void* out, int T, int
 void launch_rope_qknorm_store(const void* qkv, const void* positions, const void* cos_sin, const void* q_w,
                               const void* k_w, void* q_out, void* k_cache, void* v_cache, const void* slots, int T,
                               int Hq, int Hkv, int D, float eps, long long num_slots, int block_size,
-                              uint32_t* status, cudaStream_t s);
+                              uint32_t* status, cudaStream_t s, const float* partial = nullptr, int splits = 0,
+                              long long split_stride = 0);   // partial != nullptr (head_dim 128 only): qkv is still
+                                                             // fp32 split-K partial sums [splits, T, heads * D]
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
                    cudaStream_t s);
 

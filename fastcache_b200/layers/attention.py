@@ -33,13 +33,20 @@ class Attention(nn.Module):
 
     def forward(self, qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
                 q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
-                eps: float = 1e-6) -> torch.Tensor:
+                eps: float = 1e-6, fused_qkv=None) -> torch.Tensor:
+        """`fused_qkv = (x, qkv_weight)` instead of `qkv`: the projection runs here, fused with the
+        rope / norm / store kernel."""
         ctx = get_context()
         if self.k_cache is None:
             raise RuntimeError("attention layer used before the KV pool was bound")
-        q = ops.rope_qknorm_store(qkv, positions, cos_sin, self.num_heads, self.num_kv_heads, self.head_dim,
-                                  q_norm_weight, k_norm_weight, eps, self.k_cache, self.v_cache,
-                                  ctx.slot_mapping)
+        if fused_qkv is not None:
+            q = ops.linear_rope_qknorm_store(fused_qkv[0], fused_qkv[1], positions, cos_sin, self.num_heads,
+                                             self.num_kv_heads, self.head_dim, q_norm_weight, k_norm_weight, eps,
+                                             self.k_cache, self.v_cache, ctx.slot_mapping)
+        else:
+            q = ops.rope_qknorm_store(qkv, positions, cos_sin, self.num_heads, self.num_kv_heads, self.head_dim,
+                                      q_norm_weight, k_norm_weight, eps, self.k_cache, self.v_cache,
+                                      ctx.slot_mapping)
         if ctx.is_prefill:
             if ctx.window_q is not None:
                 ctx.window_q["q"][self.layer_idx] = q.index_select(0, ctx.window_q["indices"])

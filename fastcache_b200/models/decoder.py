@@ -55,11 +55,14 @@ class DecoderAttention(nn.Module):
 
     def forward(self, positions: torch.Tensor, normed: torch.Tensor) -> torch.Tensor:
         """Returns this rank's partial attention output rows (before o_proj)."""
-        qkv = self.qkv_proj(normed)
         cs = self.rotary_emb.cos_sin_cache
-        return self.attn(qkv, positions, cs,
-                         self.q_norm.weight if self.q_norm is not None else None,
-                         self.k_norm.weight if self.k_norm is not None else None, self.eps)
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        if (normed.is_cuda and normed.shape[0] <= 256 and self.head_dim == 128 and self.qkv_proj.bias is None
+                and getattr(get_fused_comm(), "_gather", None) is None):
+            # decode sizes: the rope / q-k norm / KV store kernel reduces the GEMM's split-K partial sums
+            return self.attn(None, positions, cs, qw, kw, self.eps, fused_qkv=(normed, self.qkv_proj.weight))
+        return self.attn(self.qkv_proj(normed), positions, cs, qw, kw, self.eps)
 
 
 class DecoderMLP(nn.Module):

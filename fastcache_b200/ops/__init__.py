@@ -103,6 +103,19 @@ def rope_qknorm_store(qkv, positions, cos_sin, num_q_heads, num_kv_heads, head_d
                                  q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping)
 
 
+def linear_rope_qknorm_store(x, weight, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                             q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping):
+    """`rope_qknorm_store(x @ weight.T, ...)`.  On CUDA with head_dim 128 the rope kernel also reduces the
+    split-K partial sums of a decode-size GEMM (two launches in all)."""
+    if x.is_cuda and head_dim == 128 and slot_mapping is not None:
+        _n(2)
+        return ext().linear_rope_qknorm_store(x, weight, positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                                              q_norm_weight, k_norm_weight, float(eps), k_cache, v_cache,
+                                              slot_mapping)
+    return rope_qknorm_store(linear(x, weight), positions, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                             q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping)
+
+
 def prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
                       max_q_len: int = 0, impl: int = 0):
     """Causal attention of new tokens over the paged cache.  `impl`: 0 picks the kernel (the two-tile

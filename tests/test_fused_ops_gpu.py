@@ -50,3 +50,22 @@ def test_gemm_swiglu_epilogue(M, I, K):
     torch.cuda.synchronize()
     assert ops.ext().read_status(0) == 0
     assert ((y.float() - want).abs() / (want.abs() + 1.0)).max().item() < 3e-2
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,qk", [(128, 32, 8, True), (5, 8, 2, False), (256, 16, 16, True)])
+def test_linear_rope_qknorm_store_matches_unfused(T, Hq, Hkv, qk):
+    """qkv projection fused with rope / q-k norm / paged store: same bits as GEMM followed by the rope op."""
+    D, K, nb, bs = 128, 1024, 40, 16
+    x, w = _rand(T, K, seed=11), _rand((Hq + 2 * Hkv) * D, K, scale=0.05, seed=12)
+    pos = torch.randint(0, 500, (T,), device="cuda")
+    cs = ref.build_cos_sin_cache(D, 512, 10000.0, "cuda")
+    qw = _rand(D, seed=13) if qk else None
+    kw = _rand(D, seed=14) if qk else None
+    slots = torch.randperm(nb * bs, device="cuda")[:T].int()
+    kc, vc = (torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = ops.linear_rope_qknorm_store(x, w, pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc, vc, slots)
+    q2 = ops.rope_qknorm_store(ops.linear(x, w), pos, cs, Hq, Hkv, D, qw, kw, 1e-6, kc2, vc2, slots)
+    torch.cuda.synchronize()
+    assert ops.ext().read_status(0) == 0
+    assert torch.equal(q, q2) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
