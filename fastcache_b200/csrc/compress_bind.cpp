@@ -33,6 +33,29 @@ Tensor knorm_scores(const Tensor& pool, const Tensor& block_tables, const Tensor
   return scores;
 }
 
+// SnapKV scores [n_seq, L, Hkv, stride] from the observation-window queries qw [n_seq, L, w, Hq, D]
+Tensor snapkv_scores(const Tensor& pool, const Tensor& block_tables, const Tensor& kv_lens, int64_t max_len,
+                     const Tensor& qw, int64_t kernel_size, double scale, Tensor status) {
+  check_pool(pool);
+  check_i32(block_tables, "block_tables");
+  check_i32(kv_lens, "kv_lens");
+  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(3), D = pool.size(5);
+  TORCH_CHECK(qw.is_cuda() && qw.scalar_type() == torch::kBFloat16 && qw.is_contiguous() && qw.dim() == 5 &&
+                  qw.size(0) == n && qw.size(1) == L && qw.size(4) == D,
+              "window queries must be contiguous bf16 [n_seq, L, w, Hq, D]");
+  const int64_t w = qw.size(2), Hq = qw.size(3);
+  const int64_t stride = (max_len + 3) / 4 * 4;
+  c10::cuda::CUDAGuard guard(pool.device());
+  Tensor votes = torch::empty({n, L, Hkv, stride}, pool.options().dtype(torch::kFloat32));
+  Tensor scores = torch::empty({n, L, Hkv, stride}, pool.options().dtype(torch::kFloat32));
+  fc::launch_snapkv_scores(pool.data_ptr(), qw.data_ptr(), block_tables.data_ptr<int>(), kv_lens.data_ptr<int>(),
+                           votes.data_ptr<float>(), scores.data_ptr<float>(), int(n), int(L), int(pool.size(2)),
+                           int(Hkv), int(Hq), int(pool.size(4)), int(D), int(block_tables.size(1)), int(stride),
+                           int(w), int(kernel_size), float(scale),
+                           reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
+  return scores;
+}
+
 void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_tables, const Tensor& kv_lens,
                     const Tensor& n_kepts, Tensor status) {
   check_pool(pool);
@@ -84,5 +107,6 @@ void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens
 void register_compress(pybind11::module_& m) {
   m.def("knorm_scores", &knorm_scores);
   m.def("select_compact", &select_compact);
+  m.def("snapkv_scores", &snapkv_scores);
   m.def("ccm_compress", &ccm_compress);
 }

@@ -49,6 +49,10 @@ namespace fc {
 void launch_knorm_scores(const void* pool, const int* block_tables, const int* kv_lens, float* scores, int n_seq,
                          int L, int num_blocks, int block_size, int Hkv, int D, int max_blocks, int max_len,
                          int s_stride, int mode, uint32_t* status, cudaStream_t stream);
+void launch_snapkv_scores(const void* pool, const void* qw, const int* block_tables, const int* kv_lens, float* votes,
+                          float* scores, int n_seq, int L, int num_blocks, int Hkv, int Hq, int block_size, int D,
+                          int max_blocks, int stride, int w, int kernel_size, float scale, uint32_t* status,
+                          cudaStream_t stream);
 void launch_select_compact(void* pool, const float* scores, const int* block_tables, const int* kv_lens,
                            const int* n_kepts, int n_seq, int L, int num_blocks, int block_size, int Hkv, int D,
                            int max_blocks, int s_stride, uint32_t* status, cudaStream_t stream);

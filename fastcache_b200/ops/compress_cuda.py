@@ -53,12 +53,14 @@ def evict_cuda(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: S
     kept_d = torch.tensor(kept, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
     status = e.status_tensor(dev.index if dev.index is not None else torch.cuda.current_device())
     max_len = int(max(kv_lens))
+    scores = None
     if method in ("knorm", "knorm_ref"):
         scores = e.knorm_scores(pool, bt_d, lens_d, max_len, 1 if method == "knorm_ref" else 0, status)
-    elif method == "snapkv" and hasattr(e, "snapkv_scores") and window_q is not None:
+    elif method == "snapkv" and window_q is not None and all(wq is not None for wq in window_q) \
+            and min(kv_lens) > int(params.get("window", 64)):
         from .snapkv import snapkv_scores_cuda
         scores = snapkv_scores_cuda(pool, bt_d, lens_d, max_len, window_q, params, status)
-    else:
+    if scores is None:
         stride = (max_len + 3) // 4 * 4
         p = dict(params)
         if method == "uniform":

@@ -33,3 +33,46 @@ def test_evict_matches_reference(method, D):
         a = got[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(pool.shape[0], 2, -1, pool.shape[3], D)[:, :, :k]
         b = want[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(pool.shape[0], 2, -1, pool.shape[3], D)[:, :, :k]
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("D,Hq,H,w", [(128, 8, 2, 64), (64, 4, 4, 32), (128, 4, 1, 64)])
+def test_snapkv_scores_kernel_matches_torch_statement(D, Hq, H, w):
+    from fastcache_b200.compress.inpool import _rows
+    from fastcache_b200.compress.scorers import snapkv
+    from fastcache_b200.ops import ext
+    from fastcache_b200.ops.compress_cuda import _batch_meta
+    from fastcache_b200.ops.snapkv import snapkv_scores_cuda
+    L = 2
+    pool = _pool(L=L, nb=40, bs=16, H=H, D=D, seed=3)
+    tables = [[3, 7, 1, 9, 12, 30, 31, 33, 34, 35, 36, 37, 38], [5, 6, 20, 21, 22, 23, 24, 25, 26, 2, 4]]
+    lens = [200, 170]
+    g = torch.Generator().manual_seed(9)
+    window_q = [{l: torch.randn(w, Hq, D, generator=g).to(torch.bfloat16).cuda() for l in range(L)} for _ in lens]
+    bt_d, lens_d = _batch_meta(pool, tables, lens)
+    status = ext().status_tensor(0)
+    got = snapkv_scores_cuda(pool, bt_d, lens_d, max(lens), window_q, {"window": w, "kernel_size": 5}, status)
+    torch.cuda.synchronize()
+    assert got is not None and ext().read_status(0) == 0
+    for i, (bt, n) in enumerate(zip(tables, lens)):
+        blocks = torch.as_tensor(bt, dtype=torch.long, device="cuda")
+        for l in range(L):
+            k = _rows(pool[l, 0], blocks, n).permute(1, 0, 2)
+            want = snapkv(k, None, window_q[i][l].permute(1, 0, 2), window=w, kernel_size=5)     # [H, n]
+            a, b = got[i, l, :, :n - w], want[:, :n - w]
+            assert (a - b).abs().max().item() < 2e-3 * b.abs().max().item() + 1e-6
+            assert torch.all(got[i, l, :, n - w:n] > 1e37) and torch.all(torch.isinf(got[i, l, :, n:]))
+
+
+def test_snapkv_eviction_in_pool_keeps_window_and_top_votes():
+    pool = _pool(L=2, nb=40, bs=16, H=2, D=128, seed=5)
+    tables, lens, kept = [[3, 7, 1, 9, 12, 30, 31, 33, 34, 35, 36, 37, 38]], [200], [100]
+    g = torch.Generator().manual_seed(2)
+    wq = [{l: torch.randn(64, 8, 128, generator=g).to(torch.bfloat16).cuda() for l in range(2)}]
+    before = pool.clone()
+    out = evict_in_pool(pool, tables, lens, "snapkv", kept, wq, {"window": 64, "kernel_size": 5})
+    torch.cuda.synchronize()
+    assert out == kept
+    # the last 64 rows of the request (the window) end up as the last 64 kept rows, in order
+    idx = torch.tensor(tables[0], device="cuda")
+    flat = lambda p: p[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(2, 2, -1, 2, 128)   # noqa: E731
+    assert torch.equal(flat(pool)[:, :, 36:100], flat(before)[:, :, 136:200])
