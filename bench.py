@@ -455,7 +455,7 @@ def run_reference(args):
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "nanovllm", "engine")):
         if rank == 0:
-            unavailable("reference is not installed under baseline/_ref (see DESIGN.md, reference install)")
+            unavailable("reference is not installed under baseline/_ref")
         sys.exit(0)
     if args.config in SERVING:
         if rank == 0:
