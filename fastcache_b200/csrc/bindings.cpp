@@ -106,6 +106,21 @@ static int gemm_maybe_partial(const Tensor& x, const Tensor& w, Tensor& out, Dev
   return 1;
 }
 
+static void check_linear_pair(const Tensor& x, const Tensor& w);
+
+// x @ w.T for a consumer that can reduce split-K partial sums itself: returns the number of K splits.  1: `out`
+// holds the bf16 result; > 1: the workspace (`gemm_scratch`) holds fp32 partial sums [splits, M, N] and `out` is
+// untouched.
+int64_t gemm_partial(const Tensor& x, const Tensor& w, Tensor out) {
+  check_linear_pair(x, w);
+  check_bf16(out, "out");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == w.size(0) && out.stride(1) == 1,
+              "bad out tensor");
+  if (x.size(0) == 0) return 1;
+  c10::cuda::CUDAGuard guard(x.device());
+  return gemm_maybe_partial(x, w, out, workspace(x.get_device()), at::cuda::getCurrentCUDAStream());
+}
+
 static void check_linear_pair(const Tensor& x, const Tensor& w) {
   check_bf16(x, "x");
   check_bf16(w, "weight");
@@ -461,6 +476,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding);
   m.def("rope_qknorm_store", &rope_qknorm_store);
   m.def("linear_rope_qknorm_store", &linear_rope_qknorm_store);
+  m.def("gemm_partial", &gemm_partial);
+  m.def("gemm_scratch", [](int64_t device) { return workspace(int(device)).gemm_scratch; });
   m.def("prefill_attention", &prefill_attention);
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,

@@ -114,11 +114,40 @@ template <bool MULTIMEM>
 __global__ void __launch_bounds__(AR_THREADS)
 allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ mc_in, bf16* __restrict__ residual,
                              const bf16* __restrict__ weight, bf16* __restrict__ out, int T, int H, float eps,
-                             uint32_t* __restrict__ epochs, uint32_t* status) {
+                             uint32_t* __restrict__ epochs, uint32_t* status, const float* __restrict__ partial,
+                             int splits, long long split_stride, const bf16* __restrict__ bias) {
   __shared__ float red[32];
   __shared__ uint32_t s_epoch;
   pdl_launch_dependents();
   pdl_wait();                            // the GEMM that filled the staging buffer, the previous epoch counters
+  if (partial != nullptr) {
+    // the GEMM left split-K partial sums [splits, T, H] in local scratch: finish this CTA's rows into this
+    // rank's staging buffer first (what the GEMM's finalize kernel would have done), then join the exchange
+    bf16* mine = peers.data[buf][peers.rank];
+    const int chunks0 = H >> 3;
+    for (int row = blockIdx.x; row < T; row += gridDim.x) {
+      for (int idx = threadIdx.x; idx < chunks0; idx += AR_THREADS) {
+        const size_t off = (size_t)row * H + (size_t)idx * 8;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int s = 0; s < splits; ++s) {
+          const float4* ps = reinterpret_cast<const float4*>(partial + (size_t)s * split_stride + off);
+          const float4 a = __ldcg(ps), b = __ldcg(ps + 1);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+          acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+        if (bias != nullptr) {
+          float bb[8];
+          unpack8f(*reinterpret_cast<const uint4*>(bias + (size_t)idx * 8), bb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += bb[i];
+        }
+        *reinterpret_cast<uint4*>(mine + off) = pack8f(acc);
+      }
+    }
+    __syncthreads();
+  }
   const int slot = blockIdx.x;
   if (threadIdx.x == 0) s_epoch = epochs[slot] + 1;
   __syncthreads();
@@ -193,7 +222,8 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
 
 void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* mc_in, void* residual,
                                   const void* weight, void* out, int T, int H, float eps, uint32_t* epochs,
-                                  uint32_t* status, bool use_multimem, cudaStream_t stream) {
+                                  uint32_t* status, bool use_multimem, cudaStream_t stream, const float* partial,
+                                  int splits, long long split_stride, const void* bias) {
   if (T == 0) return;
   if (H % 8 != 0 || H > AR_THREADS * AR_MAX_CHUNKS * 8) throw std::runtime_error("allreduce: unsupported hidden size");
   // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
@@ -201,10 +231,12 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
   cudaError_t e;
   if (use_multimem && mc_in != nullptr)
     e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<true>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
-                   (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+                   (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
+                   partial, splits, split_stride, (const bf16*)bias);
   else
     e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<false>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
-                   (const bf16*)nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status);
+                   (const bf16*)nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
+                   partial, splits, split_stride, (const bf16*)bias);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("allreduce launch: ") + cudaGetErrorString(e));
 }

@@ -19,7 +19,11 @@ struct CommPeers {
 
 void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* mc_in, void* residual,
                                   const void* weight, void* out, int T, int H, float eps, uint32_t* epochs,
-                                  uint32_t* status, bool use_multimem, cudaStream_t stream);
+                                  uint32_t* status, bool use_multimem, cudaStream_t stream,
+                                  const float* partial = nullptr, int splits = 0, long long split_stride = 0,
+                                  const void* bias = nullptr);
+// `partial` != nullptr: this rank's contribution is still fp32 split-K partial sums [splits, T, H] (plus an optional
+// bias); each CTA finishes its rows into the staging buffer before it joins the exchange.
 
 }  // namespace fc
 

@@ -45,7 +45,8 @@ void comm_shutdown() {
 // The partial sums of this rank are rows [0, T) of staging buffer `buf`.  Returns the normalised
 // rows; `residual` is updated in place.
 Tensor allreduce_add_rmsnorm(int64_t buf, Tensor residual, const Tensor& weight, double eps, bool use_multimem,
-                             Tensor status) {
+                             Tensor status, const c10::optional<Tensor>& partial, int64_t splits,
+                             const c10::optional<Tensor>& bias) {
   TORCH_CHECK(g_comm.ready, "comm_init was not called");
   TORCH_CHECK(residual.is_cuda() && residual.scalar_type() == torch::kBFloat16 && residual.is_contiguous() &&
                   residual.dim() == 2, "residual must be contiguous bf16 [T, H]");
@@ -55,11 +56,23 @@ Tensor allreduce_add_rmsnorm(int64_t buf, Tensor residual, const Tensor& weight,
   c10::cuda::CUDAGuard guard(residual.device());
   Tensor out = torch::empty_like(residual);
   const void* mc = (use_multimem && g_comm.mc[buf] != 0) ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
+  const float* part = nullptr;
+  const void* bptr = nullptr;
+  if (partial.has_value() && partial->defined() && splits > 1) {
+    TORCH_CHECK(partial->is_cuda() && partial->scalar_type() == torch::kFloat32 && partial->is_contiguous() &&
+                    partial->numel() >= splits * residual.numel(), "partial sums must be fp32 [splits, T, H]");
+    part = partial->data_ptr<float>();
+    if (bias.has_value() && bias->defined()) {
+      TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 && bias->is_contiguous() && bias->numel() == residual.size(1),
+                  "bias must be a contiguous bf16 [H] vector");
+      bptr = bias->data_ptr();
+    }
+  }
   fc::launch_allreduce_add_rmsnorm(g_comm.peers, int(buf), mc, residual.data_ptr(), weight.data_ptr(), out.data_ptr(),
                                    int(residual.size(0)), int(residual.size(1)), float(eps),
                                    reinterpret_cast<uint32_t*>(g_comm.epochs.data_ptr<int>()),
                                    reinterpret_cast<uint32_t*>(status.data_ptr<int>()), mc != nullptr,
-                                   at::cuda::getCurrentCUDAStream());
+                                   at::cuda::getCurrentCUDAStream(), part, int(splits), residual.numel(), bptr);
   return out;
 }
 // ------------------------------------------------------------ prefill-size fused GEMM + collective
@@ -152,7 +165,10 @@ void wait_gathered(int64_t epoch, Tensor status) {
 void register_comm(pybind11::module_& m) {
   m.def("comm_init", &comm_init);
   m.def("comm_shutdown", &comm_shutdown);
-  m.def("allreduce_add_rmsnorm", &allreduce_add_rmsnorm);
+  m.def("allreduce_add_rmsnorm", &allreduce_add_rmsnorm, pybind11::arg("buf"), pybind11::arg("residual"),
+        pybind11::arg("weight"), pybind11::arg("eps"), pybind11::arg("use_multimem"), pybind11::arg("status"),
+        pybind11::arg("partial") = pybind11::none(), pybind11::arg("splits") = 0,
+        pybind11::arg("bias") = pybind11::none());
   m.def("tp_init", &tp_init);
   m.def("gemm_rs_add_norm", &gemm_rs_add_norm);
   m.def("gemm_after_gather", &gemm_after_gather);

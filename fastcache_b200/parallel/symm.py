@@ -64,6 +64,7 @@ class FusedComm:
                         [int(p) for p in self.handles[1].buffer_ptrs],
                         [int(p) for p in self.flag_handle.buffer_ptrs], mc[0], mc[1], index)
         self.status = ext().status_tensor(index)
+        self._scratch = ext().gemm_scratch(index)
         self.cur = 0
 
         # ---- GEMM + reduce-scatter + add + norm / all-gather + GEMM (prefill)
@@ -112,9 +113,15 @@ class FusedComm:
             buf = self.cur
             self.cur ^= 1
             staging = self.bufs[buf][:T]
-            ops.linear(x, weight, bias, out=staging)           # partial sums land in symmetric memory
-            ops._n()
-            y = ext().allreduce_add_rmsnorm(buf, residual, norm_weight, float(eps), self.use_multimem, self.status)
+            x2 = x if x.stride(-1) == 1 else x.contiguous()
+            ops._n(2)
+            # split-K partial sums of the GEMM are finished into the staging buffer by the reduce kernel itself
+            splits = ext().gemm_partial(x2, weight, staging)
+            if splits == 1 and bias is not None:
+                staging.add_(bias)
+            y = ext().allreduce_add_rmsnorm(buf, residual, norm_weight, float(eps), self.use_multimem, self.status,
+                                            self._scratch if splits > 1 else None, splits,
+                                            bias if splits > 1 else None)
             return y, residual
         if bias is not None or T > self.max_tokens or weight.shape[0] != self.hidden:
             return self._library(x, weight, bias, residual, norm_weight, eps)
