@@ -111,8 +111,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();                              // x, the scratch and the output belong to earlier kernels until here
-  asm volatile("fence.proxy.async.global;" ::: "memory");   // x: ordinary stores before, TMA reads now
+  const bool is_producer = (warp == 0 && lane == 0);
+  if (!is_producer) {
+    pdl_wait();                            // x, the scratch and the output belong to earlier kernels until here
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -120,7 +122,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      // The weights never change during serving: their first tiles are requested while the previous kernel
+      // of the stream is still draining (programmatic dependent launch); only the activations wait for it.
+      const int npre = min(STAGES, kb1 - kb0);
+      for (int s = 0; s < npre; ++s) {
+        uint8_t* sa = smem + s * L::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        tma_load_2d(sa, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * SK_BM);
+        tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * SK_BM + 128);
+      }
+      pdl_wait();
+      asm volatile("fence.proxy.async.global;" ::: "memory");   // x: ordinary stores before, TMA reads now
+      for (int s = 0; s < npre; ++s)
+        tma_load_2d(smem + s * L::STAGE_BYTES + L::A_BYTES, &tma_x, &full_bar[s], (kb0 + s) * SK_BK, 0);
+      issued = npre;
+      stage = npre == STAGES ? 0 : npre;
+      phase = npre == STAGES ? 1u : 0u;
+      for (int kb = kb0 + npre; kb < kb1; ++kb) {
         if (*s_abort || !mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) {
           *s_abort = 1;
           ok = false;
