@@ -111,7 +111,7 @@ def expected_attention(keys, values=None, queries=None, n_sink: int = 4, **kw):
     Hkv, S, D = keys.shape
     Hq = queries.shape[0]
     g = Hq // Hkv
-    q = queries.float().view(Hkv, g * queries.shape[1], D)
+    q = queries.float().reshape(Hkv, g * queries.shape[1], D)
     mu = q.mean(dim=1)                                             # [Hkv, D]
     qc = q - mu[:, None, :]
     cov = torch.matmul(qc.transpose(1, 2), qc) / max(1, q.shape[1] - 1)   # [Hkv, D, D]

@@ -56,6 +56,43 @@ Tensor snapkv_scores(const Tensor& pool, const Tensor& block_tables, const Tenso
   return scores;
 }
 
+// ExpectedAttention scores (log domain) from the window queries qw [n_seq, L, w, Hq, D]
+Tensor expected_attention_scores(const Tensor& pool, const Tensor& block_tables, const Tensor& kv_lens,
+                                 int64_t max_len, const Tensor& qw, int64_t n_sink, Tensor status) {
+  check_pool(pool);
+  check_i32(block_tables, "block_tables");
+  check_i32(kv_lens, "kv_lens");
+  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(3), D = pool.size(5);
+  TORCH_CHECK(qw.is_cuda() && qw.scalar_type() == torch::kBFloat16 && qw.is_contiguous() && qw.dim() == 5 &&
+                  qw.size(0) == n && qw.size(1) == L && qw.size(4) == D,
+              "window queries must be contiguous bf16 [n_seq, L, w, Hq, D]");
+  const int64_t stride = (max_len + 3) / 4 * 4;
+  c10::cuda::CUDAGuard guard(pool.device());
+  auto f32 = pool.options().dtype(torch::kFloat32);
+  Tensor stats = torch::empty({n, L, Hkv, D + D * D}, f32);
+  Tensor scores = torch::empty({n, L, Hkv, stride}, f32);
+  fc::launch_expected_attention_scores(pool.data_ptr(), qw.data_ptr(), block_tables.data_ptr<int>(),
+                                       kv_lens.data_ptr<int>(), stats.data_ptr<float>(), scores.data_ptr<float>(),
+                                       int(n), int(L), int(pool.size(2)), int(Hkv), int(qw.size(3)), int(pool.size(4)),
+                                       int(D), int(block_tables.size(1)), int(stride), int(qw.size(2)), int(n_sink),
+                                       reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
+                                       at::cuda::getCurrentCUDAStream());
+  return scores;
+}
+
+// StreamingLLM scores: position, sinks always kept
+Tensor position_scores(const Tensor& pool, const Tensor& kv_lens, int64_t max_len, int64_t n_sink) {
+  check_pool(pool);
+  check_i32(kv_lens, "kv_lens");
+  const int64_t n = kv_lens.numel(), L = pool.size(0), Hkv = pool.size(3);
+  const int64_t stride = (max_len + 3) / 4 * 4;
+  c10::cuda::CUDAGuard guard(pool.device());
+  Tensor scores = torch::empty({n, L, Hkv, stride}, pool.options().dtype(torch::kFloat32));
+  fc::launch_position_scores(scores.data_ptr<float>(), kv_lens.data_ptr<int>(), int(n), int(L * Hkv), int(stride),
+                             int(n_sink), at::cuda::getCurrentCUDAStream());
+  return scores;
+}
+
 void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_tables, const Tensor& kv_lens,
                     const Tensor& n_kepts, Tensor status) {
   check_pool(pool);
@@ -108,5 +145,7 @@ void register_compress(pybind11::module_& m) {
   m.def("knorm_scores", &knorm_scores);
   m.def("select_compact", &select_compact);
   m.def("snapkv_scores", &snapkv_scores);
+  m.def("expected_attention_scores", &expected_attention_scores);
+  m.def("position_scores", &position_scores);
   m.def("ccm_compress", &ccm_compress);
 }

@@ -53,6 +53,12 @@ void launch_snapkv_scores(const void* pool, const void* qw, const int* block_tab
                           float* scores, int n_seq, int L, int num_blocks, int Hkv, int Hq, int block_size, int D,
                           int max_blocks, int stride, int w, int kernel_size, float scale, uint32_t* status,
                           cudaStream_t stream);
+void launch_expected_attention_scores(const void* pool, const void* qw, const int* block_tables, const int* kv_lens,
+                                      float* stats, float* scores, int n_seq, int L, int num_blocks, int Hkv, int Hq,
+                                      int block_size, int D, int max_blocks, int stride, int w, int n_sink,
+                                      uint32_t* status, cudaStream_t stream);
+void launch_position_scores(float* scores, const int* kv_lens, int n_seq, int units_per_seq, int stride, int n_sink,
+                            cudaStream_t stream);
 void launch_select_compact(void* pool, const float* scores, const int* block_tables, const int* kv_lens,
                            const int* n_kepts, int n_seq, int L, int num_blocks, int block_size, int Hkv, int D,
                            int max_blocks, int s_stride, uint32_t* status, cudaStream_t stream);

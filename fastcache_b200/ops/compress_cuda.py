@@ -60,6 +60,13 @@ def evict_cuda(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: S
             and min(kv_lens) > int(params.get("window", 64)):
         from .snapkv import snapkv_scores_cuda
         scores = snapkv_scores_cuda(pool, bt_d, lens_d, max_len, window_q, params, status)
+    elif method == "expected_attention" and window_q is not None and all(wq is not None for wq in window_q):
+        from .snapkv import stack_window_queries
+        qw = stack_window_queries(window_q, pool.shape[0])
+        if qw is not None and pool.shape[5] in (64, 128):
+            scores = e.expected_attention_scores(pool, bt_d, lens_d, max_len, qw, int(params.get("n_sink", 4)), status)
+    elif method == "streaming_llm":
+        scores = e.position_scores(pool, lens_d, max_len, int(params.get("n_sink", 4)))
     if scores is None:
         stride = (max_len + 3) // 4 * 4
         p = dict(params)

@@ -76,3 +76,33 @@ def test_snapkv_eviction_in_pool_keeps_window_and_top_votes():
     idx = torch.tensor(tables[0], device="cuda")
     flat = lambda p: p[:, :, idx].permute(0, 1, 2, 4, 3, 5).reshape(2, 2, -1, 2, 128)   # noqa: E731
     assert torch.equal(flat(pool)[:, :, 36:100], flat(before)[:, :, 136:200])
+
+
+@pytest.mark.parametrize("D,Hq,H,w", [(128, 8, 2, 64), (64, 4, 4, 32)])
+def test_expected_attention_scores_kernel_matches_torch_statement(D, Hq, H, w):
+    from fastcache_b200.compress.inpool import _rows
+    from fastcache_b200.compress.scorers import expected_attention
+    from fastcache_b200.ops import ext
+    from fastcache_b200.ops.compress_cuda import _batch_meta
+    from fastcache_b200.ops.snapkv import stack_window_queries
+    L = 2
+    pool = (_pool(L=L, nb=40, bs=16, H=H, D=D, seed=7).float() * 0.5).to(torch.bfloat16)
+    tables = [[3, 7, 1, 9, 12, 30, 31, 33, 34, 35, 36, 37, 38], [5, 6, 20, 21, 22, 23, 24, 25, 26, 2, 4]]
+    lens = [200, 170]
+    g = torch.Generator().manual_seed(4)
+    window_q = [{l: (torch.randn(w, Hq, D, generator=g) * 0.5).to(torch.bfloat16).cuda() for l in range(L)}
+                for _ in lens]
+    bt_d, lens_d = _batch_meta(pool, tables, lens)
+    status = ext().status_tensor(0)
+    got = ext().expected_attention_scores(pool, bt_d, lens_d, max(lens), stack_window_queries(window_q, L), 4, status)
+    torch.cuda.synchronize()
+    assert ext().read_status(0) == 0
+    for i, (bt, n) in enumerate(zip(tables, lens)):
+        blocks = torch.as_tensor(bt, dtype=torch.long, device="cuda")
+        for l in range(L):
+            k = _rows(pool[l, 0], blocks, n).permute(1, 0, 2)
+            v = _rows(pool[l, 1], blocks, n).permute(1, 0, 2)
+            want = expected_attention(k, v, window_q[i][l].permute(1, 0, 2), n_sink=4)        # [H, n]
+            diff = got[i, l, :, 4:n] - torch.log(want[:, 4:n])
+            assert (diff - diff.mean(dim=1, keepdim=True)).abs().max().item() < 2e-2          # same up to a constant
+            assert torch.all(got[i, l, :, :4] > 1e37) and torch.all(torch.isinf(got[i, l, :, n:]))
