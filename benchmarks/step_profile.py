@@ -27,8 +27,15 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=128)
     ap.add_argument("--context", type=int, default=2304)
     ap.add_argument("--graphs", action="store_true", help="decode through CUDA graphs (one launch per step)")
+    ap.add_argument("--shard", type=int, default=1,
+                    help="run the per-rank shapes of a tensor-parallel shard of this degree (heads, KV heads and "
+                         "ffn width divided; no communication)")
     args = ap.parse_args()
     hf = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    if args.shard > 1:
+        hf.update(num_attention_heads=hf["num_attention_heads"] // args.shard,
+                  num_key_value_heads=max(1, hf["num_key_value_heads"] // args.shard),
+                  intermediate_size=hf["intermediate_size"] // args.shard)
     blocks = args.decode_batch * (-(-(args.context + 16) // 256)) + 8 * 17 + 8
     llm = LLM(hf, device="cuda:0", kvcache_block_size=256, max_model_len=8192, max_num_seqs=args.decode_batch + 32,
               max_num_batched_tokens=32768, num_kvcache_blocks=blocks, enforce_eager=not args.graphs,

@@ -131,6 +131,7 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
         for (int s = 0; s < splits; ++s) {
           const float4* ps = reinterpret_cast<const float4*>(partial + (size_t)s * split_stride + off);
           const float4 a = __ldcg(ps), b = __ldcg(ps + 1);

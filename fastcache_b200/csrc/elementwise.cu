@@ -309,6 +309,7 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
     float a[8], b[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) a[i] = b[i] = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
       const float4* ps = reinterpret_cast<const float4*>(p0 + s * split_stride);
       const float4 l0 = __ldcg(ps), l1 = __ldcg(ps + 1), h0 = __ldcg(ps + 16), h1 = __ldcg(ps + 17);

@@ -254,6 +254,7 @@ __global__ void skinny_finalize_kernel(const float* __restrict__ partial, const 
        i += (long long)gridDim.x * blockDim.x) {
     const int m = int(i / (N / 4)), n = int(i % (N / 4)) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(partial + ((long long)s * M + m) * N + n);
       acc.x += v.x;
@@ -303,7 +304,8 @@ int skinny_pick_splits(int tiles, int num_kb, int sms, int M, int N, size_t scra
     const int waves = (ctas + sms - 1) / sms;
     const int kb = (num_kb + s - 1) / s;
     // time ~ waves * (kb + fixed overhead per CTA) ; partial traffic adds a little per split
-    const double cost = waves * (kb + 6.0) + 0.15 * s;
+    // (every extra split is another fp32 copy of the output for the consumer to read back)
+    const double cost = waves * (kb + 6.0) + 0.5 * s;
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best = s;

@@ -39,7 +39,8 @@ add_rms_norm_partials_kernel(const float* __restrict__ partial, int splits, long
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
       const float* p0 = partial + row * H + idx * 8;
-      for (int s = 0; s < splits; ++s) {
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) {          // loads of four splits in flight, summed in split order
         const float4 a = __ldcg(reinterpret_cast<const float4*>(p0 + s * split_stride));
         const float4 b = __ldcg(reinterpret_cast<const float4*>(p0 + s * split_stride) + 1);
         acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
@@ -113,6 +114,7 @@ __global__ void silu_mul_partials_kernel(const float* __restrict__ partial, int 
     const int c = int(idx - t * quads) * 4;
     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
     const float* base = partial + t * 2 * I + c;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
       const float4 a = __ldcg(reinterpret_cast<const float4*>(base + s * split_stride));
       const float4 b = __ldcg(reinterpret_cast<const float4*>(base + s * split_stride + I));
