@@ -53,7 +53,8 @@ void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long lo
 // chunk are loaded only after its owner's "gathered" flag for `epoch` has been observed.
 void gemm_after_gather(const void* xg_local, const void* w, void* c, int M, int N, int K, long long ldw,
                        long long ldc, const TpBuffers& b, int chunk_rows, uint32_t epoch, uint32_t* status,
-                       int sm_limit, cudaStream_t stream);
+                       int sm_limit, cudaStream_t stream, bool swiglu = false);
+// swiglu: w = [gate; up] stacked on dim 0; c [M, N / 2] = silu(xg gate^T) * (xg up^T), applied in the epilogue.
 
 // Blocks the stream (one tiny kernel, bounded wait) until every owner's rows of `epoch` have landed.
 void wait_gathered(const TpBuffers& b, uint32_t epoch, uint32_t* status, cudaStream_t stream);

@@ -138,7 +138,7 @@ void gemm_rs_add_norm(const Tensor& x, const Tensor& w, Tensor residual, const T
 
 // y = xg[:M] @ w.T where xg is this rank's gathered-activation buffer (passed as a tensor view).
 Tensor gemm_after_gather(const Tensor& xg_view, const Tensor& w, int64_t chunk_rows, int64_t epoch, Tensor status,
-                         int64_t sm_limit) {
+                         int64_t sm_limit, bool swiglu) {
   TORCH_CHECK(g_tp.ready, "tp_init was not called");
   check_gemm_operand(xg_view, "xg");
   check_gemm_operand(w, "weight");
@@ -147,11 +147,12 @@ Tensor gemm_after_gather(const Tensor& xg_view, const Tensor& w, int64_t chunk_r
   const int64_t M = xg_view.size(0), K = xg_view.size(1), N = w.size(0);
   TORCH_CHECK(w.size(1) == K, "inner dimensions differ");
   c10::cuda::CUDAGuard guard(w.device());
-  Tensor out = torch::empty({M, N}, w.options());
+  TORCH_CHECK(!swiglu || N % 256 == 0, "fused SwiGLU needs N % 256 == 0");
+  Tensor out = torch::empty({M, swiglu ? N / 2 : N}, w.options());
   fc::gemm_after_gather(xg_view.data_ptr(), w.data_ptr(), out.data_ptr(), int(M), int(N), int(K), w.stride(0),
                         out.stride(0), g_tp.b, int(chunk_rows), uint32_t(epoch),
                         reinterpret_cast<uint32_t*>(status.data_ptr<int>()), int(sm_limit),
-                        at::cuda::getCurrentCUDAStream());
+                        at::cuda::getCurrentCUDAStream(), swiglu);
   return out;
 }
 
@@ -171,6 +172,8 @@ void register_comm(pybind11::module_& m) {
         pybind11::arg("bias") = pybind11::none());
   m.def("tp_init", &tp_init);
   m.def("gemm_rs_add_norm", &gemm_rs_add_norm);
-  m.def("gemm_after_gather", &gemm_after_gather);
+  m.def("gemm_after_gather", &gemm_after_gather, pybind11::arg("xg"), pybind11::arg("weight"),
+        pybind11::arg("chunk_rows"), pybind11::arg("epoch"), pybind11::arg("status"), pybind11::arg("sm_limit"),
+        pybind11::arg("swiglu") = false);
   m.def("wait_gathered", &wait_gathered);
 }

@@ -43,6 +43,7 @@ constexpr int TP_STAGES = 4;
 constexpr int TP_THREADS = 192;
 constexpr int MODE_RS = 1;
 constexpr int MODE_AG = 2;
+constexpr int MODE_AG_SWIGLU = 3;   // MODE_AG on w = [gate; up] with silu(gate) * up applied in the epilogue
 
 struct TpGemmParams {
   int M, N, K;                 // tokens, output features, reduction length (local)
@@ -51,6 +52,7 @@ struct TpGemmParams {
   int tp, rank, chunk_rows, blocks_per_chunk, rot;
   uint32_t epoch;
   uint32_t* status;
+  int up_row0;                 // MODE_AG_SWIGLU: first row of the up half of w (= output width)
   // MODE_AG: plain output
   __nv_bfloat16* C;
   long long ldc;
@@ -255,7 +257,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         int m_blk, n_blk;
         decode_tile(w, m_blk, n_blk);
         if (m_blk >= p.num_m) continue;                    // padding block of the rotated order
-        if (MODE == MODE_AG) {
+        if (MODE != MODE_RS) {
           const int owner = m_blk / p.blocks_per_chunk;
           if (owner != p.rank && !(seen & (1u << owner))) {
             if (!tp_wait_flag(p.gathered_flags + owner, p.epoch, p.status)) {
@@ -275,7 +277,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           uint8_t* sa = smem + stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           tma_load_2d(sa, &tma_a, &full_bar[stage], kb * TP_BK, m_blk * TP_BM);
-          tma_load_2d(sa + A_BYTES, &tma_b, &full_bar[stage], kb * TP_BK, n_blk * TP_BN);
+          if (MODE == MODE_AG_SWIGLU) {
+            // B tile = 128 rows of this rank's gate weights + the matching 128 rows of its up weights
+            tma_load_2d(sa + A_BYTES, &tma_b, &full_bar[stage], kb * TP_BK, n_blk * (TP_BN / 2));
+            tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tma_b, &full_bar[stage], kb * TP_BK,
+                        p.up_row0 + n_blk * (TP_BN / 2));
+          } else {
+            tma_load_2d(sa + A_BYTES, &tma_b, &full_bar[stage], kb * TP_BK, n_blk * TP_BN);
+          }
           if (++stage == TP_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -351,14 +360,27 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         dst0 = p.C + (long long)gi0 * p.ldc;
       }
       uint8_t* stg = out_stage + (warp - 2) * (32 * 144);
+      // SwiGLU: accumulator columns [0, 128) = gate, [128, 256) = up, 128 output columns per tile
+      constexpr int OUT_COLS = (MODE == MODE_AG_SWIGLU) ? TP_BN / 2 : TP_BN;
 #pragma unroll 1
-      for (int c2 = 0; c2 < TP_BN / 64; ++c2) {
+      for (int c2 = 0; c2 < OUT_COLS / 64; ++c2) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t r[32];
           tmem_ld_32x32(t_addr + uint32_t(c2 * 64 + half * 32), r);
-          tmem_ld_wait();
-          if (c2 == TP_BN / 64 - 1 && half == 1) {
+          if (MODE == MODE_AG_SWIGLU) {
+            uint32_t ru[32];
+            tmem_ld_32x32(t_addr + uint32_t(TP_BN / 2 + c2 * 64 + half * 32), ru);
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+              const float g = __uint_as_float(r[t]);
+              r[t] = __float_as_uint(g / (1.f + __expf(-g)) * __uint_as_float(ru[t]));
+            }
+          } else {
+            tmem_ld_wait();
+          }
+          if (c2 == OUT_COLS / 64 - 1 && half == 1) {
             tc_fence_before();
             mbar_arrive(&acc_empty[acc]);
           }
@@ -374,7 +396,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
         __syncwarp();
         // eight lanes write one 128-byte piece of a row: full lines towards HBM or NVLink
-        const int jb = n_blk * TP_BN + c2 * 64 + (lane & 7) * 8;
+        const int jb = n_blk * OUT_COLS + c2 * 64 + (lane & 7) * 8;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int rr = (lane >> 3) + 4 * i;
@@ -500,7 +522,7 @@ void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long lo
 
 void gemm_after_gather(const void* xg_local, const void* w, void* c, int M, int N, int K, long long ldw,
                        long long ldc, const TpBuffers& b, int chunk_rows, uint32_t epoch, uint32_t* status,
-                       int sm_limit, cudaStream_t stream) {
+                       int sm_limit, cudaStream_t stream, bool swiglu) {
   if (M <= 0) return;
   TpGemmParams p{};
   fill_common(p, M, N, K, b.world, b.rank, chunk_rows, epoch, status, true);
@@ -508,8 +530,25 @@ void gemm_after_gather(const void* xg_local, const void* w, void* c, int M, int 
   p.ldc = ldc;
   p.gathered_flags = b.gathered_flags[b.rank];
   const CUtensorMap ta = make_tmap_bf16_2d(xg_local, M, K, K, TP_BM, TP_BK);
-  const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
+  if (swiglu) {
+    // w = [gate; up] ([N, K], N = 2 x width); c is [M, N / 2]
+    if (N % 256 != 0 || ldc % 8 != 0) throw std::runtime_error("gemm_after_gather: SwiGLU needs N % 256 == 0");
+    const int width = N / 2;
+    p.N = width;
+    p.up_row0 = width;
+    p.num_n = width / (TP_BN / 2);
+    p.total_tiles = p.tp * p.blocks_per_chunk * p.num_n;
+    const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN / 2, TP_BK);
+    auto kern = gemm_tp_kernel<MODE_AG_SWIGLU>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+    kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);
+    cudaError_t e2 = cudaGetLastError();
+    if (e2 != cudaSuccess)
+      throw std::runtime_error(std::string("gemm_after_gather (SwiGLU) launch: ") + cudaGetErrorString(e2));
+    return;
+  }
+  const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
   auto kern = gemm_tp_kernel<MODE_AG>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
   kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);

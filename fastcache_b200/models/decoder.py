@@ -77,8 +77,9 @@ class DecoderMLP(nn.Module):
         if normed.is_cuda and normed.shape[0] <= 256 and self.gate_up_proj.bias is None:
             # decode sizes: the SwiGLU kernel also reduces the GEMM's split-K partial sums
             return ops.linear_silu_mul(normed, self.gate_up_proj.weight)
-        if normed.is_cuda and self.gate_up_proj.bias is None and get_fused_comm() is None:
-            # prefill sizes on one GPU: SwiGLU runs in the GEMM epilogue (gate and up rows share a tile)
+        if normed.is_cuda and self.gate_up_proj.bias is None:
+            # prefill sizes: SwiGLU runs in the GEMM epilogue (gate and up rows share a tile), also in the
+            # tensor-parallel GEMM that consumes the gathered activations
             return ops.linear(normed, self.gate_up_proj.weight, None, act="swiglu")
         return self.act_fn(self.gate_up_proj(normed))
 

@@ -149,11 +149,12 @@ class FusedComm:
         if g is None or x.data_ptr() != self.xg.data_ptr():
             return None
         ops._n()
-        if bias is not None or act != "none" or x.shape[0] != g[2] or not x.is_contiguous():
+        swiglu = act == "swiglu" and weight.shape[0] % 256 == 0
+        if bias is not None or (act != "none" and not swiglu) or x.shape[0] != g[2] or not x.is_contiguous():
             ext().wait_gathered(g[0], self.status)
             self._gather = None
             return None
-        return ext().gemm_after_gather(x, weight, g[1], g[0], self.status, 0)
+        return ext().gemm_after_gather(x, weight, g[1], g[0], self.status, 0, swiglu)
 
     def _library(self, x, weight, bias, residual, norm_weight, eps):
         y = ops.linear(x, weight, bias)
