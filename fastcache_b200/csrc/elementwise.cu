@@ -54,7 +54,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // y = rms_norm(x [+ residual]) * w ; if residual != nullptr it is updated in place with x + residual.
-// One block per row; H % 8 == 0, H <= 8192.  x may be fp32 partial sums? no: bf16 only.
+// One block per row; H % 8 == 0, H <= 8192; x is bf16 (fp32 split-K partial sums go through partials.cu).
 template <bool ADD>
 __global__ void __launch_bounds__(NORM_THREADS)
 rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,

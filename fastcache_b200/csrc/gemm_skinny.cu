@@ -14,8 +14,9 @@
 //
 // With one split the epilogue writes bf16 (bias and activation applied).  With
 // several it writes fp32 partial sums [split, M, N] to scratch; the partials are
-// summed by the consumer (add + RMSNorm, see elementwise.cu) or by the small
-// finalize kernel below.  No inter-CTA synchronisation is needed.
+// summed by the kernel that consumes the result (add + RMSNorm and SwiGLU in
+// partials.cu, rope + KV store in elementwise.cu, the one-shot all-reduce in comm.cu)
+// or by the small finalize kernel below.  No inter-CTA synchronisation is needed.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
