@@ -63,20 +63,23 @@ __device__ __forceinline__ float sk_act(float v, int act) {
   }
 }
 
-template <int BN, int STAGES>
+// ROWS = rows of W per CTA: 256 (two MMAs share the x tile) or 128 (twice the CTAs, for matrices with so few
+// rows that 256-row tiles would leave most SMs without work, e.g. the per-rank shards under tensor parallelism)
+template <int BN, int STAGES, int ROWS = SK_BM>
 struct SkinnySmem {
-  static constexpr int A_BYTES = SK_BM * SK_BK * 2;
+  static constexpr int A_BYTES = ROWS * SK_BK * 2;
   static constexpr int B_BYTES = BN * SK_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int ROWS>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                    const SkinnyParams p) {
-  using L = SkinnySmem<BN, STAGES>;
+  using L = SkinnySmem<BN, STAGES, ROWS>;
+  constexpr int MT = ROWS / 128;            // 128-row MMAs per K step
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -87,7 +90,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  constexpr uint32_t TMEM_COLS = (MT * BN <= 32) ? 32 : (MT * BN <= 64) ? 64 : (MT * BN <= 128) ? 128
+                                 : (MT * BN <= 256) ? 256 : 512;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int num_kb = (p.K + SK_BK - 1) / SK_BK;
   const int kb0 = split * p.kb_per_split;
@@ -129,8 +133,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       for (int s = 0; s < npre; ++s) {
         uint8_t* sa = smem + s * L::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-        tma_load_2d(sa, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * SK_BM);
-        tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * SK_BM + 128);
+        tma_load_2d(sa, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * ROWS);
+        if constexpr (MT == 2)
+          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * ROWS + 128);
       }
       pdl_wait();
       asm volatile("fence.proxy.async.global;" ::: "memory");   // x: ordinary stores before, TMA reads now
@@ -148,8 +153,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         uint8_t* sa = smem + stage * L::STAGE_BYTES;
         uint8_t* sb = sa + L::A_BYTES;
         mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-        tma_load_2d(sa, &tma_w, &full_bar[stage], kb * SK_BK, tile * SK_BM);
-        tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[stage], kb * SK_BK, tile * SK_BM + 128);
+        tma_load_2d(sa, &tma_w, &full_bar[stage], kb * SK_BK, tile * ROWS);
+        if constexpr (MT == 2)
+          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[stage], kb * SK_BK, tile * ROWS + 128);
         tma_load_2d(sb, &tma_x, &full_bar[stage], kb * SK_BK, 0);
         ++issued;
         if (++stage == STAGES) {
@@ -190,7 +196,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         for (int k = 0; k < SK_BK / 16; ++k) {
           const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
           tc_mma_f16(tmem_base, da0 + uint64_t(2 * k), db + uint64_t(2 * k), idesc, accum);
-          tc_mma_f16(tmem_base + BN, da1 + uint64_t(2 * k), db + uint64_t(2 * k), idesc, accum);
+          if constexpr (MT == 2)
+            tc_mma_f16(tmem_base + BN, da1 + uint64_t(2 * k), db + uint64_t(2 * k), idesc, accum);
         }
         tc_commit(&empty_bar[stage]);
         if (++stage == STAGES) {
@@ -206,8 +213,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     if (!*s_abort && mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int mt = 0; mt < 2; ++mt) {
-        const int n = tile * SK_BM + mt * 128 + row;          // output feature of this thread
+      for (int mt = 0; mt < MT; ++mt) {
+        const int n = tile * ROWS + mt * 128 + row;           // output feature of this thread
         const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(mt * BN);
         const float bi = (p.bias != nullptr && n < p.Nw && p.splits == 1) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
@@ -277,11 +284,11 @@ __global__ void skinny_finalize_kernel(const float* __restrict__ partial, const 
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int ROWS>
 static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, int tiles,
                           cudaStream_t stream) {
-  using L = SkinnySmem<BN, STAGES>;
-  auto kern = gemm_skinny_kernel<BN, STAGES>;
+  using L = SkinnySmem<BN, STAGES, ROWS>;
+  auto kern = gemm_skinny_kernel<BN, STAGES, ROWS>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -321,8 +328,12 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
                      long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
                      int splits_request, bool finalize, cudaStream_t stream) {
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
-  const int tiles = (N + SK_BM - 1) / SK_BM;
   const int num_kb = (K + SK_BK - 1) / SK_BK;
+  // 128-row tiles when 256-row tiles would cover less than half of the SMs: the same SM count is then reached
+  // with half the K splits, i.e. half the partial-sum traffic
+  const bool small_rows = (N + SK_BM - 1) / SK_BM <= sms / 2;
+  const int rows = small_rows ? 128 : SK_BM;
+  const int tiles = (N + rows - 1) / rows;
   const size_t scratch_floats = ws.scratch != nullptr ? gemm_scratch_bytes() / 4 : 0;
   int splits = splits_request > 0 ? splits_request : skinny_pick_splits(tiles, num_kb, sms, M, N, scratch_floats);
   if (N % 4 != 0) splits = 1;
@@ -344,16 +355,20 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   CUtensorMap tw = make_tmap_bf16_2d(w, N, K, ldw, 128, SK_BK);
   if (M <= 32) {
     CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 32, SK_BK);
-    launch_skinny<32, 6>(tw, tx, p, tiles, stream);
+    if (small_rows) launch_skinny<32, 8, 128>(tw, tx, p, tiles, stream);
+    else launch_skinny<32, 6, 256>(tw, tx, p, tiles, stream);
   } else if (M <= 64) {
     CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 64, SK_BK);
-    launch_skinny<64, 5>(tw, tx, p, tiles, stream);
+    if (small_rows) launch_skinny<64, 7, 128>(tw, tx, p, tiles, stream);
+    else launch_skinny<64, 5, 256>(tw, tx, p, tiles, stream);
   } else if (M <= 128) {
     CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 128, SK_BK);
-    launch_skinny<128, 4>(tw, tx, p, tiles, stream);
+    if (small_rows) launch_skinny<128, 6, 128>(tw, tx, p, tiles, stream);
+    else launch_skinny<128, 4, 256>(tw, tx, p, tiles, stream);
   } else {
     CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 256, SK_BK);
-    launch_skinny<256, 3>(tw, tx, p, tiles, stream);
+    if (small_rows) launch_skinny<256, 4, 128>(tw, tx, p, tiles, stream);
+    else launch_skinny<256, 3, 256>(tw, tx, p, tiles, stream);
   }
   if (splits > 1 && finalize) {
     const long long total = (long long)M * (N / 4);
