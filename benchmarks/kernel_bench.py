@@ -1,6 +1,7 @@
 """Device-timed micro-benchmarks of the hot kernels against the measured roofline.
 
-Usage:  python benchmarks/kernel_bench.py [--what gemm,decode_gemm,decode_attn,prefill_attn,norm] [--json out.json]
+Usage:  python benchmarks/kernel_bench.py [--what gemm,decode_gemm,decode_attn,prefill_attn,norm,elementwise,
+                                            dense_attn,vit_gemm,ccm,evict] [--small] [--json out.json]
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, an L2 flush
 (write of a 256 MB buffer) before every timed iteration, median of the samples.
 Peaks come from MEASURED_PEAKS.json at the repository root when present
@@ -120,10 +121,140 @@ def bench_norm(rows):
         print(rows[-1], flush=True)
 
 
+def _bw_row(rows, name, ms, byts, extra):
+    hbm, _, src = peaks()
+    rows.append(dict({"kernel": name}, **extra, ms=round(ms, 4), gbs=round(byts / ms / 1e6, 1),
+                     frac_of_hbm=round(byts / ms / 1e6 / hbm, 3), peaks=src))
+    print(rows[-1], flush=True)
+
+
+def bench_elementwise(rows):
+    """Rope + q/k norm + paged store, standalone SwiGLU, embedding gather, sampler (prefill and decode sizes)."""
+    from fastcache_b200.ops import reference as ref
+    Hq, Hkv, D, bs = 32, 8, 128, 256
+    cs = ref.build_cos_sin_cache(D, 8192, 1e6, "cuda")
+    qw = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    for T in (32768, 128):
+        nb = -(-T // bs) + 1
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        pos = torch.arange(T, device="cuda") % 8192
+        slots = torch.randperm(nb * bs, device="cuda")[:T].int()
+        kc, vc = (torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+        ms = timeit(lambda: ops.rope_qknorm_store(qkv, pos, cs, Hq, Hkv, D, qw, qw, 1e-6, kc, vc, slots))
+        byts = 2.0 * T * D * ((Hq + 2 * Hkv) + Hq + 2 * Hkv)
+        _bw_row(rows, "rope_qknorm_store", ms, byts, {"T": T, "Hq": Hq, "Hkv": Hkv})
+    for T, inter in ((32768, 12288), (128, 12288)):
+        x = torch.randn(T, 2 * inter, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: ops.silu_and_mul(x))
+        _bw_row(rows, "silu_and_mul", ms, 2.0 * T * inter * 3, {"T": T, "I": inter})
+    emb = torch.randn(151936, 4096, device="cuda", dtype=torch.bfloat16)
+    for T in (32768, 128):
+        ids = torch.randint(0, 151936, (T,), device="cuda")
+        ms = timeit(lambda: ops.embedding(ids, emb))
+        _bw_row(rows, "embedding", ms, 2.0 * T * 4096 * 2, {"T": T, "H": 4096})
+    del emb
+    logits = torch.randn(128, 151936, device="cuda", dtype=torch.bfloat16)
+    temps = torch.full((128,), 0.6, device="cuda")
+    ms = timeit(lambda: ops.sample(logits, temps, seed=1))
+    _bw_row(rows, "sample", ms, 2.0 * logits.numel(), {"B": 128, "V": 151936})
+
+
+def bench_dense_attn(rows):
+    """Vision-tower attention (CLIP 577 x 16 x 64, SigLIP 1024 x 16 x 72) beside torch's fused attention."""
+    _, tf, src = peaks()
+    for B, S, H, D in [(16, 577, 16, 64), (8, 1024, 16, 72)]:
+        qkv = torch.randn(B, S, 3, H, D, device="cuda", dtype=torch.bfloat16)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        ms = timeit(lambda: ops.dense_attention(q, k, v, D ** -0.5, None))
+        qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))
+        ms_lib = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt))
+        flops = 4.0 * B * H * S * S * D
+        rows.append({"kernel": "dense_attn", "B": B, "S": S, "H": H, "D": D, "ms": round(ms, 4),
+                     "torch_sdpa_ms": round(ms_lib, 4), "tflops": round(flops / ms / 1e9, 1),
+                     "frac_of_bf16_peak": round(flops / ms / 1e9 / tf, 3), "peaks": src})
+        print(rows[-1], flush=True)
+
+
+def bench_vit_gemm(rows):
+    """Vision-tower GEMMs with bias and the activation in the epilogue (16 images of 577 tokens, CLIP ViT-L)."""
+    hbm, tf, src = peaks()
+    M = 16 * 577
+    for N, K, act in [(3072, 1024, "none"), (1024, 1024, "none"), (4096, 1024, "quick_gelu"), (1024, 4096, "none"),
+                      (4096, 4096, "gelu")]:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: ops.linear(x, w, b, act=act))
+        ms_lib = timeit(lambda: torch.nn.functional.linear(x, w, b))
+        flops = 2.0 * M * N * K
+        byts = 2.0 * (M * K + N * K + M * N)
+        t_roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
+        rows.append({"kernel": "gemm_vit", "M": M, "N": N, "K": K, "act": act, "ms": round(ms, 4),
+                     "cublas_no_act_ms": round(ms_lib, 4), "tflops": round(flops / ms / 1e9, 1),
+                     "frac_of_roofline": round(t_roof / ms, 3), "peaks": src})
+        print(rows[-1], flush=True)
+
+
+def _tables(nreq, nb_per):
+    perm = torch.randperm(nreq * nb_per).view(nreq, nb_per)
+    return [perm[i].tolist() for i in range(nreq)]
+
+
+def bench_ccm(rows, small=False):
+    """Fused CCM merge (gather -> 3 GEMMs -> in-place scatter), LLaVA-1.5-7B shape: 32 layers, 32 KV heads,
+    15 requests of 576 image + 64 text rows, factor 4; beside the PyTorch statement of the same operation."""
+    from fastcache_b200.compress import KVCacheLinearDecoupleCompressor
+    from fastcache_b200.compress.inpool import ccm_compress_in_pool, ccm_compress_reference
+    hbm, tf, src = peaks()
+    L, H, D, bs, f, nreq, n, img = 32, 32, 128, 256, 4, (4 if small else 15), 640, 576
+    nb_per = -(-n // bs)
+    m = KVCacheLinearDecoupleCompressor(None, f, 1, n_layer=L, nhead=H, head_dim=D).eval()
+    w = m.pack(torch.bfloat16, "cuda")
+    pool = torch.randn(L, 2, nreq * nb_per, H, bs, D, device="cuda", dtype=torch.bfloat16)
+    tables, lens, imgs = _tables(nreq, nb_per), [n] * nreq, [img] * nreq
+    new = ccm_compress_in_pool(pool, tables, lens, imgs, w)
+    ms = timeit(lambda: ccm_compress_in_pool(pool, tables, lens, imgs, w), iters=5)
+
+    def torch_statement():
+        for bt in tables:
+            ccm_compress_reference(pool, bt, n, img, w)
+    ms_ref = float("nan") if small else timeit(torch_statement, iters=2, warmup=1)
+    rows_in, rows_out = nreq * n, sum(new)
+    byts = 2.0 * L * 2 * H * D * (rows_in + rows_out)
+    flops = 2.0 * L * 2 * H * (rows_in // f) * (D * f * D + 2 * D * D)
+    t_roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
+    rows.append({"kernel": "ccm_merge", "layers": L, "kv_heads": H, "requests": nreq, "rows": n, "factor": f,
+                 "ms": round(ms, 4), "torch_statement_ms": round(ms_ref, 3), "gbs": round(byts / ms / 1e6, 1),
+                 "tflops": round(flops / ms / 1e9, 1), "frac_of_roofline": round(t_roof / ms, 3), "peaks": src})
+    print(rows[-1], flush=True)
+
+
+def bench_evict(rows, small=False):
+    """Scoring + top-k + in-pool compaction, Qwen3-8B shape: 36 layers, 8 KV heads, 8 requests of 4096 rows, keep
+    half.  Algorithmic bytes: K read once for the scores, kept K and V rows read and written once."""
+    from fastcache_b200.compress.inpool import evict_in_pool
+    L, H, Hq, D, bs, nreq, n, w = 36, 8, 32, 128, 256, (2 if small else 8), 4096, 64
+    nb_per = n // bs
+    pool = torch.randn(L, 2, nreq * nb_per, H, bs, D, device="cuda", dtype=torch.bfloat16)
+    tables, lens, kept = _tables(nreq, nb_per), [n] * nreq, [n // 2] * nreq
+    wq = [{l: torch.randn(w, Hq, D, device="cuda", dtype=torch.bfloat16) for l in range(L)} for _ in range(nreq)]
+    for method, params in (("knorm", {}), ("streaming_llm", {"n_sink": 4}),
+                           ("snapkv", {"window": w, "kernel_size": 5}), ("expected_attention", {"n_sink": 4})):
+        use_q = wq if method in ("snapkv", "expected_attention") else None
+        ms = timeit(lambda: evict_in_pool(pool, tables, lens, method, kept, use_q, params), iters=5)
+        k_bytes = 2.0 * L * H * D * nreq * n
+        byts = (k_bytes if method != "streaming_llm" else 0.0) + 2 * k_bytes      # kept K, V: half read + half written
+        if method == "expected_attention":
+            byts += k_bytes                                                         # the score needs the value norms
+        _bw_row(rows, "evict_" + method, ms, byts, {"layers": L, "kv_heads": H, "requests": nreq, "rows": n,
+                                                    "kept": n // 2})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,decode_gemm,decode_attn,prefill_attn,norm")
     ap.add_argument("--json", default="")
+    ap.add_argument("--small", action="store_true", help="capture-sized cases (about 1.5 GB on the device)")
     a = ap.parse_args()
     rows = []
     what = a.what.split(",")
@@ -139,6 +270,16 @@ def main():
         bench_prefill_attn(rows)
     if "norm" in what:
         bench_norm(rows)
+    if "elementwise" in what:
+        bench_elementwise(rows)
+    if "dense_attn" in what:
+        bench_dense_attn(rows)
+    if "vit_gemm" in what:
+        bench_vit_gemm(rows)
+    if "ccm" in what:
+        bench_ccm(rows, a.small)
+    if "evict" in what:
+        bench_evict(rows, a.small)
     if a.json:
         os.makedirs(os.path.dirname(os.path.abspath(a.json)), exist_ok=True)
         json.dump(rows, open(a.json, "w"), indent=1)

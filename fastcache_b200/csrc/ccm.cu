@@ -1,23 +1,28 @@
 // Fused CCM merge compressor operating in the paged KV pool (head_dim 128).
 //
-// For one (request, kv head, layer, K|V) a CTA walks the request's rows in ascending
-// order, segment by segment (image rows first, then text rows, each with its own MLP
-// bank): f consecutive rows of the head are concatenated (they are adjacent in the
+// For one (request, group of G kv heads, layer, K|V) a CTA walks the request's rows in
+// ascending order, segment by segment (image rows first, then text rows, each with its own
+// MLP bank): f consecutive rows of a head are concatenated (they are adjacent in the
 // head-major pool, so the "concatenation" is only an addressing rule), pushed through
 //        y = W3 relu(W2 relu(W1 z + b1) + b2) + b3
 // and written to the leading rows of the same request; the (rows mod f) remainder of a
-// segment is moved unchanged.  A tile is 128 output rows:
+// segment is moved unchanged.  A tile is 128 output rows: 128 / G consecutive output rows of
+// each of the G heads (the MLP weights are shared by all heads, so short segments still fill
+// the 128-row tensor-core tile; the host picks G from the segment lengths).
 //
 //   warps 2-5 (128 workers)  gather the A operand k-block by k-block with cp.async into the
-//                            128-byte-swizzled layout tcgen05 expects, run the epilogues
-//                            (tcgen05.ld, bias, ReLU, bf16) and scatter the result rows
+//                            128-byte-swizzled layout tcgen05 expects (up to three k-blocks
+//                            in flight), run the epilogues (tcgen05.ld, bias, ReLU, bf16) and
+//                            scatter the result rows
 //   warp 0                   streams W1 / W2 / W3 k-blocks with TMA into the same stage ring
 //   warp 1                   issues tcgen05.mma: GEMM1 over f*2 k-blocks (A gathered), GEMM2 and
-//                            GEMM3 with the activation tile (written to shared memory by the
-//                            epilogue) as the A operand; accumulators live in TMEM
+//                            GEMM3 with the activation tile as the A operand; the epilogue writes
+//                            that tile into the A halves of the two stages whose W halves carry
+//                            the matching W2 / W3 k-blocks (those halves are idle then), so the
+//                            CTA needs 96 KiB and two CTAs share an SM; accumulators live in TMEM
 // The intermediates never leave the SM.  In-place safety: an output row index never
-// exceeds the index of any input row it depends on, tiles are processed in ascending
-// order by one CTA, and a tile is read completely (GEMM1 is done) before it is written.
+// exceeds the index of any input row of the same head it depends on, tiles are processed in
+// ascending order by one CTA, and a tile is read completely (GEMM1 is done) before it is written.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -52,6 +57,8 @@ struct CcmParams {
   int weight_layer_start;     // index of that layer in the packed weights
   int factor, min_seq_len;
   int single_segment;
+  int heads_per_cta;          // G: 1, 2, 4 or 8 heads share a tile
+  int rj_shift;               // log2(128 / G): output rows of one head per tile
   uint32_t* status;
 };
 
@@ -61,14 +68,13 @@ __device__ __forceinline__ int ccm_seg_out(int n, int f, int min_len) {
   return s < min_len ? n : s + n % f;
 }
 
-__global__ void __launch_bounds__(CCM_THREADS, 1)
+__global__ void __launch_bounds__(CCM_THREADS, 2)
 ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
                  const __grid_constant__ CUtensorMap tm_w3, const CcmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // stage s: A sub-tile at s * 2 * KB, W sub-tile right after; then the activation tile H (2 sub-tiles)
-  uint8_t* s_h = smem + CCM_STAGES * 2 * CCM_KB_BYTES;
-  uint64_t* a_full = reinterpret_cast<uint64_t*>(s_h + 2 * CCM_KB_BYTES);
+  // stage s: A sub-tile at s * 2 * KB, W sub-tile right after
+  uint64_t* a_full = reinterpret_cast<uint64_t*>(smem + CCM_STAGES * 2 * CCM_KB_BYTES);
   uint64_t* w_full = a_full + CCM_STAGES;
   uint64_t* empty = w_full + CCM_STAGES;
   uint64_t* acc_full = empty + CCM_STAGES;      // [1]
@@ -78,7 +84,8 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.x, seq = blockIdx.z;
+  const int G = p.heads_per_cta, rj_shift = p.rj_shift, RJ = 1 << rj_shift;
+  const int h0 = blockIdx.x * G, seq = blockIdx.z;
   const int layer_off = blockIdx.y >> 1, kv = blockIdx.y & 1;
   const int layer = p.layer_start + layer_off, wlayer = p.weight_layer_start + layer_off;
   const int f = p.factor;
@@ -119,19 +126,19 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
   int seg_tiles[2];
   for (int s = 0; s < 2; ++s) {
     const int sp = seg_len[s] / f;
-    seg_tiles[s] = (seg_len[s] > 0 && sp >= p.min_seq_len) ? (sp + CCM_TILE - 1) / CCM_TILE : 0;
+    seg_tiles[s] = (seg_len[s] > 0 && sp >= p.min_seq_len) ? (sp + RJ - 1) >> rj_shift : 0;
   }
   const int total_tiles = seg_tiles[0] + seg_tiles[1];
 
   const int* bt = p.block_tables + (long long)seq * p.max_blocks;
   const long long plane = (((long long)layer * 2 + kv) * p.num_blocks);
-  auto row_ptr = [&](int tok) -> bf16* {
+  auto row_ptr = [&](int hh, int tok) -> bf16* {
     int blk = bt[tok / p.block_size];
     if (blk < 0 || blk >= p.num_blocks) {
       report(p.status, ST_BAD_INDEX);
       return nullptr;
     }
-    return p.pool + (((plane + blk) * p.Hkv + h) * p.block_size + tok % p.block_size) * CCM_D;
+    return p.pool + (((plane + blk) * p.Hkv + hh) * p.block_size + tok % p.block_size) * CCM_D;
   };
 
   if (warp == 0) {
@@ -193,8 +200,10 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
             }
             if (!ok) break;
             tc_fence_after();
+            // the A half of the stage holds the gathered rows (GEMM1) or the activation sub-tile that the
+            // epilogue wrote for this k-block (GEMM2, GEMM3)
             const uint32_t sa = smem_u32(smem + stage * 2 * CCM_KB_BYTES);
-            const uint64_t da = make_sdesc_sw128(g == 0 ? sa : smem_u32(s_h + i * CCM_KB_BYTES));
+            const uint64_t da = make_sdesc_sw128(sa);
             const uint64_t db = make_sdesc_sw128(sa + CCM_KB_BYTES);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
@@ -223,20 +232,22 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
       if (seg_tiles[seg] == 0) {
         // too short to compress: move the rows unchanged (at most a few rows; out0 <= in0)
         if (out0 != in0) {
-          for (int base = 0; base < n; base += 8) {
-            const int r = base + wt / 16, piece = wt % 16;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            const bool live = r < n;
-            if (live) {
-              const bf16* src = row_ptr(in0 + r);
-              if (src != nullptr) v = reinterpret_cast<const uint4*>(src)[piece];
+          for (int hl = 0; hl < G; ++hl) {
+            for (int base = 0; base < n; base += 8) {
+              const int r = base + wt / 16, piece = wt % 16;
+              uint4 v = make_uint4(0, 0, 0, 0);
+              const bool live = r < n;
+              if (live) {
+                const bf16* src = row_ptr(h0 + hl, in0 + r);
+                if (src != nullptr) v = reinterpret_cast<const uint4*>(src)[piece];
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (live) {
+                bf16* dst = row_ptr(h0 + hl, out0 + r);
+                if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (live) {
-              bf16* dst = row_ptr(out0 + r);
-              if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
           }
         }
         continue;
@@ -246,8 +257,9 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
       const bf16* b2 = p.b2 + ((long long)wlayer * 4 + bank) * CCM_D;
       const bf16* b3 = p.b3 + ((long long)wlayer * 4 + bank) * CCM_D;
       for (int t = 0; t < seg_tiles[seg] && ok; ++t, ++tile) {
-        const int j0 = t * CCM_TILE;
-        // ---- gather the A operand of GEMM1, one [128 x 64] k-block per stage
+        const int j0 = t << rj_shift;
+        // ---- gather the A operand of GEMM1, one [128 x 64] k-block per stage; the copies of up to three
+        //      k-blocks are in flight, a stage is handed to the MMA warp when its own group has landed
         for (int i = 0; i < nk1 && ok; ++i, ++it) {
           const int stage = it % CCM_STAGES;
           if (*s_abort || !mbar_wait(&empty[stage], ((it / CCM_STAGES) & 1) ^ 1, p.status, ST_TIMEOUT_EMPTY)) {
@@ -258,25 +270,33 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
           const int tok_in_group = i / (CCM_D / 64), half = i % (CCM_D / 64);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const int c = wt + q * 128;              // 1024 chunks of 16 bytes: (row r, chunk ch)
+            const int c = wt + q * 128;              // 1024 chunks of 16 bytes: (tile row r, chunk ch)
             const int r = c >> 3, ch = c & 7;
-            const int j = j0 + r;
+            const int j = j0 + (r & (RJ - 1));       // tile row r = head (r >> rj_shift), output row j of that head
             const bf16* src = p.pool;
             bool live = j < sp;
             if (live) {
-              const bf16* rp = row_ptr(in0 + j * f + tok_in_group);
+              const bf16* rp = row_ptr(h0 + (r >> rj_shift), in0 + j * f + tok_in_group);
               if (rp == nullptr) live = false;
               else src = rp + half * 64 + ch * 8;
             }
             cp_async16(sa + r * 128 + ((ch ^ (r & 7)) << 4), src, live);
           }
           cp_async_commit();
-          cp_async_wait<0>();
-          fence_proxy_async();
-          mbar_arrive(&a_full[stage]);
+          if (i >= 2) {
+            cp_async_wait<2>();
+            fence_proxy_async();
+            mbar_arrive(&a_full[(it - 2) % CCM_STAGES]);
+          }
         }
-        it += 4;     // the W2 / W3 stages carry no gathered operand (the MMA warp counts a_full uses per stage)
+        cp_async_wait<0>();
         if (!ok) break;
+        // the last two k-blocks (GEMM1 always has at least two)
+        fence_proxy_async();
+        mbar_arrive(&a_full[(it - 2) % CCM_STAGES]);
+        mbar_arrive(&a_full[(it - 1) % CCM_STAGES]);
+        const int it_h = it;     // ring position of the first W2 k-block: its stage takes the first activation sub-tile
+        it += 4;     // the W2 / W3 stages carry no gathered operand (the MMA warp counts a_full uses per stage)
         // ---- epilogues 1 and 2: bias + ReLU, activation tile to shared memory for the next GEMM
         for (int g = 0; g < 2 && ok; ++g) {
           if (!mbar_wait(acc_full, acc_phase, p.status, ST_TIMEOUT_ACC_FULL)) {
@@ -287,24 +307,30 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
           tc_fence_after();
           const bf16* bias = g == 0 ? b1 : b2;
           const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + (g == 1 ? 128u : 0u);
+          // activation sub-tile i (columns 64 i .. 64 i + 63) goes to the A half of the stage whose W half
+          // carries k-block i of the next GEMM; every earlier use of those halves is complete (acc_full)
+          uint8_t* const h_dst0 = smem + ((it_h + 2 * g) % CCM_STAGES) * 2 * CCM_KB_BYTES;
+          uint8_t* const h_dst1 = smem + ((it_h + 2 * g + 1) % CCM_STAGES) * 2 * CCM_KB_BYTES;
 #pragma unroll 1
           for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t rr[32];
             tmem_ld_32x32(t_addr + uint32_t(c4 * 32), rr);
             tmem_ld_wait();
+            uint8_t* const h_row = (c4 < 2 ? h_dst0 : h_dst1) + row * 128;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(bias + c4 * 32 + q * 8);
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
               uint32_t u[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int col = c4 * 32 + q * 8 + e * 2;
-                const float a = fmaxf(__uint_as_float(rr[q * 8 + e * 2]) + __bfloat162float(bias[col]), 0.f);
-                const float b = fmaxf(__uint_as_float(rr[q * 8 + e * 2 + 1]) + __bfloat162float(bias[col + 1]), 0.f);
+                // a bf16 is the upper half of the fp32 with the same value
+                const float a = fmaxf(__uint_as_float(rr[q * 8 + e * 2]) + __uint_as_float(bw[e] << 16), 0.f);
+                const float b = fmaxf(__uint_as_float(rr[q * 8 + e * 2 + 1]) + __uint_as_float(bw[e] & 0xffff0000u), 0.f);
                 u[e] = pack_bf16(a, b);
               }
-              const int chunk = c4 * 4 + q;            // 16-byte chunk of the 256-byte activation row
-              uint8_t* dst = s_h + (chunk >> 3) * CCM_KB_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-              *reinterpret_cast<uint4*>(dst) = make_uint4(u[0], u[1], u[2], u[3]);
+              const int chunk = (c4 & 1) * 4 + q;      // 16-byte chunk of the 128-byte sub-tile row
+              *reinterpret_cast<uint4*>(h_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(u[0], u[1], u[2], u[3]);
             }
           }
           tc_fence_before();
@@ -320,8 +346,8 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
         acc_phase ^= 1;
         tc_fence_after();
         {
-          const int j = j0 + row;
-          bf16* dst = (j < sp) ? row_ptr(out0 + j) : nullptr;
+          const int j = j0 + (row & (RJ - 1));
+          bf16* dst = (j < sp) ? row_ptr(h0 + (row >> rj_shift), out0 + j) : nullptr;
           const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16);
 #pragma unroll 1
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -331,12 +357,13 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
             if (dst != nullptr) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(b3 + c4 * 32 + q * 8);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
                 uint32_t u[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  const int col = c4 * 32 + q * 8 + e * 2;
-                  u[e] = pack_bf16(__uint_as_float(rr[q * 8 + e * 2]) + __bfloat162float(b3[col]),
-                                   __uint_as_float(rr[q * 8 + e * 2 + 1]) + __bfloat162float(b3[col + 1]));
+                  u[e] = pack_bf16(__uint_as_float(rr[q * 8 + e * 2]) + __uint_as_float(bw[e] << 16),
+                                   __uint_as_float(rr[q * 8 + e * 2 + 1]) + __uint_as_float(bw[e] & 0xffff0000u));
                 }
                 reinterpret_cast<uint4*>(dst)[c4 * 4 + q] = make_uint4(u[0], u[1], u[2], u[3]);
               }
@@ -350,18 +377,20 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
       // ---- remainder rows of the segment move behind the compressed rows (fewer than f rows)
       const int rem = n - sp * f;
       if (rem > 0) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int r = wt / 16, piece = wt % 16;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        const bool live = r < rem;
-        if (live) {
-          const bf16* src = row_ptr(in0 + sp * f + r);
-          if (src != nullptr) v = reinterpret_cast<const uint4*>(src)[piece];
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (live) {
-          bf16* dst = row_ptr(out0 + sp + r);
-          if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
+        for (int hl = 0; hl < G; ++hl) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int r = wt / 16, piece = wt % 16;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          const bool live = r < rem;
+          if (live) {
+            const bf16* src = row_ptr(h0 + hl, in0 + sp * f + r);
+            if (src != nullptr) v = reinterpret_cast<const uint4*>(src)[piece];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (live) {
+            bf16* dst = row_ptr(h0 + hl, out0 + sp + r);
+            if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
+          }
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -382,8 +411,14 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
                       const void* w1, const void* w2, const void* w3, const void* b1, const void* b2,
                       const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
                       int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
-                      int factor, int min_seq_len, int single_segment, uint32_t* status, cudaStream_t stream) {
+                      int factor, int min_seq_len, int single_segment, int heads_per_cta, uint32_t* status,
+                      cudaStream_t stream) {
   if (n_seq == 0 || layer_end <= layer_start) return;
+  int G = heads_per_cta <= 0 ? 1 : heads_per_cta;
+  if ((G != 1 && G != 2 && G != 4 && G != 8) || Hkv % G != 0)
+    throw std::runtime_error("fused CCM kernel: heads per CTA must be 1, 2, 4 or 8 and divide the KV heads");
+  int rj_shift = 7;
+  for (int g = G; g > 1; g >>= 1) --rj_shift;
   if (D != CCM_D) throw std::runtime_error("fused CCM kernel: head_dim must be 128");
   if (factor < 1 || factor > 8) throw std::runtime_error("fused CCM kernel: factor must be in [1, 8]");
   if (factor > 8) throw std::runtime_error("remainder move handles fewer than 8 rows");
@@ -404,14 +439,16 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
   p.factor = factor;
   p.min_seq_len = min_seq_len;
   p.single_segment = single_segment;
+  p.heads_per_cta = G;
+  p.rj_shift = rj_shift;
   p.status = status;
   const uint64_t wrows = (uint64_t)n_weight_layers * 4 * D;
   const CUtensorMap t1 = make_tmap_bf16_2d(w1, wrows, (uint64_t)D * factor, (uint64_t)D * factor, 128, 64);
   const CUtensorMap t2 = make_tmap_bf16_2d(w2, wrows, D, D, 128, 64);
   const CUtensorMap t3 = make_tmap_bf16_2d(w3, wrows, D, D, 128, 64);
-  const int smem = CCM_STAGES * 2 * CCM_KB_BYTES + 2 * CCM_KB_BYTES + 256 + 1024;
+  const int smem = CCM_STAGES * 2 * CCM_KB_BYTES + 256 + 1024;
   cudaFuncSetAttribute(ccm_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  dim3 grid(Hkv, (layer_end - layer_start) * 2, n_seq);
+  dim3 grid(Hkv / G, (layer_end - layer_start) * 2, n_seq);
   ccm_fused_kernel<<<grid, CCM_THREADS, smem, stream>>>(t1, t2, t3, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("fused CCM launch: ") + cudaGetErrorString(e));

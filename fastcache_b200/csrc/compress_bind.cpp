@@ -116,7 +116,7 @@ void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_table
 void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens, const Tensor& image_lens,
                   const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, const Tensor& w3,
                   const Tensor& b3, int64_t layer_start, int64_t layer_end, int64_t weight_layer_start,
-                  int64_t factor, int64_t min_seq_len, bool single_segment, Tensor status) {
+                  int64_t factor, int64_t min_seq_len, bool single_segment, Tensor status, int64_t heads_per_cta) {
   check_pool(pool);
   check_i32(block_tables, "block_tables");
   check_i32(kv_lens, "kv_lens");
@@ -136,7 +136,7 @@ void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens
                        b2.data_ptr(), b3.data_ptr(), int(kv_lens.numel()), int(w1.size(0)), int(layer_start),
                        int(layer_end), int(weight_layer_start), int(pool.size(2)), int(pool.size(3)),
                        int(pool.size(4)), int(D), int(block_tables.size(1)), int(factor), int(min_seq_len),
-                       single_segment ? 1 : 0, reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
+                       single_segment ? 1 : 0, int(heads_per_cta), reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
                        at::cuda::getCurrentCUDAStream());
 }
 }  // namespace
@@ -147,5 +147,10 @@ void register_compress(pybind11::module_& m) {
   m.def("snapkv_scores", &snapkv_scores);
   m.def("expected_attention_scores", &expected_attention_scores);
   m.def("position_scores", &position_scores);
-  m.def("ccm_compress", &ccm_compress);
+  namespace py = pybind11;
+  m.def("ccm_compress", &ccm_compress, py::arg("pool"), py::arg("block_tables"), py::arg("kv_lens"),
+        py::arg("image_lens"), py::arg("w1"), py::arg("b1"), py::arg("w2"), py::arg("b2"), py::arg("w3"),
+        py::arg("b3"), py::arg("layer_start"), py::arg("layer_end"), py::arg("weight_layer_start"),
+        py::arg("factor"), py::arg("min_seq_len"), py::arg("single_segment"), py::arg("status"),
+        py::arg("heads_per_cta") = 1);
 }

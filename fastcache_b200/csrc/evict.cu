@@ -32,40 +32,66 @@ __device__ __forceinline__ uint32_t float_key(float f) {
 
 // scores[seq, layer, h, tok] = sign * ||K[tok, h, :]||      (mode 0: per head)
 //                            = mean_h ||K[tok, h, :]||       (mode 1: shared by heads, largest kept)
+constexpr int KN_ROWS = 32;
+
 __global__ void __launch_bounds__(256)
 knorm_score_kernel(const bf16* __restrict__ pool, const int* __restrict__ block_tables,
                    const int* __restrict__ kv_lens, float* __restrict__ scores, int L, int num_blocks,
                    int block_size, int Hkv, int D, int max_blocks, int s_stride, int mode, uint32_t* status) {
+  // One CTA: 32 consecutive rows of every head.  Sixteen lanes read one 16-byte piece each of a row (rows of one
+  // head are adjacent in a block, so consecutive lane groups read consecutive memory); the norms pass through
+  // shared memory so that the scores are written 32 consecutive floats at a time.  Hkv <= 32 (checked on the host).
+  __shared__ float sn[KN_ROWS][33];
   const int seq = blockIdx.z, layer = blockIdx.y;
   const int len = kv_lens[seq];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tok = blockIdx.x * 8 + warp;
-  if (tok >= len) return;
-  const int blk = block_tables[(long long)seq * max_blocks + tok / block_size];
-  if (blk < 0 || blk >= num_blocks) {
-    report(status, ST_BAD_INDEX);
-    return;
-  }
+  const int tok0 = blockIdx.x * KN_ROWS;
+  if (tok0 >= len) return;
+  const int sub = threadIdx.x & 15, grp = threadIdx.x >> 4;
   const long long kbase = ((long long)layer * 2 + 0) * num_blocks;
-  const bf16* row = pool + ((kbase + blk) * Hkv * block_size + tok % block_size) * D;
-  float* out = scores + (((long long)seq * L + layer) * Hkv) * s_stride + tok;
-  float mean = 0.f;
-  for (int h = 0; h < Hkv; ++h) {
+  const int* bt = block_tables + (long long)seq * max_blocks;
+  const int rows = KN_ROWS * Hkv;
+#pragma unroll 4
+  for (int r = grp; r < rows; r += 16) {
+    const int h = r / KN_ROWS, tl = r % KN_ROWS;
+    const int tok = tok0 + tl;
     float ss = 0.f;
-    for (int i = lane; i < D / 2; i += 32) {
-      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(row + (long long)h * block_size * D)[i]);
-      ss += v.x * v.x + v.y * v.y;
+    if (tok < len) {
+      const int blk = bt[tok / block_size];
+      if (blk < 0 || blk >= num_blocks) {
+        report(status, ST_BAD_INDEX);
+      } else {
+        const uint4* row = reinterpret_cast<const uint4*>(
+            pool + (((kbase + blk) * Hkv + h) * block_size + tok % block_size) * D);
+        for (int i = sub; i < D / 8; i += 16) {
+          const uint4 v = row[i];
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {        // a bf16 is the upper half of the fp32 with the same value
+            const float a = __uint_as_float(w[e] << 16), b = __uint_as_float(w[e] & 0xffff0000u);
+            ss += a * a + b * b;
+          }
+        }
+      }
     }
-    const float n = sqrtf(warp_sum(ss));
-    if (mode == 0) {
-      if (lane == 0) out[(long long)h * s_stride] = -n;
-    } else {
-      mean += n;
-    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (sub == 0) sn[tl][h] = sqrtf(ss);
   }
-  if (mode == 1 && lane == 0) {
-    mean /= float(Hkv);
-    for (int h = 0; h < Hkv; ++h) out[(long long)h * s_stride] = mean;
+  __syncthreads();
+  float* out = scores + (((long long)seq * L + layer) * Hkv) * s_stride;
+  for (int idx = threadIdx.x; idx < rows; idx += 256) {
+    const int h = idx / KN_ROWS, tl = idx % KN_ROWS;
+    const int tok = tok0 + tl;
+    if (tok >= len) continue;
+    float v;
+    if (mode == 0) {
+      v = -sn[tl][h];
+    } else {
+      float m = 0.f;
+      for (int hh = 0; hh < Hkv; ++hh) m += sn[tl][hh];
+      v = m / float(Hkv);
+    }
+    out[(long long)h * s_stride + tok] = v;
   }
 }
 
@@ -222,7 +248,8 @@ void launch_knorm_scores(const void* pool, const int* block_tables, const int* k
                          int L, int num_blocks, int block_size, int Hkv, int D, int max_blocks, int max_len,
                          int s_stride, int mode, uint32_t* status, cudaStream_t stream) {
   if (n_seq == 0 || max_len == 0) return;
-  dim3 grid((max_len + 7) / 8, L, n_seq);
+  if (Hkv > 32 || D % 8 != 0) throw std::runtime_error("knorm scores: at most 32 KV heads, head_dim a multiple of 8");
+  dim3 grid((max_len + KN_ROWS - 1) / KN_ROWS, L, n_seq);
   knorm_score_kernel<<<grid, 256, 0, stream>>>((const bf16*)pool, block_tables, kv_lens, scores, L, num_blocks,
                                                block_size, Hkv, D, max_blocks, s_stride, mode, status);
 }

@@ -65,12 +65,41 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case ACT_RELU: return fmaxf(v, 0.f);
     case ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
     case ACT_GELU_TANH: {
-      float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-      return 0.5f * v * (1.f + tanhf(u));
+      float u = 0.7978845608028654f * (v + 0.044715f * v * v * v), th;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+      return 0.5f * v * (1.f + th);
     }
-    case ACT_QUICK_GELU: return v / (1.f + __expf(-1.702f * v));
-    case ACT_SILU: return v / (1.f + __expf(-v));
+    case ACT_QUICK_GELU: return __fdividef(v, 1.f + __expf(-1.702f * v));
+    case ACT_SILU: return __fdividef(v, 1.f + __expf(-v));
     default: return v;
+  }
+}
+
+// The activation of 32 values with the (uniform) selector tested once, not per element.
+__device__ __forceinline__ void apply_act_chunk(float (&v)[32], int act) {
+  switch (act) {
+    case ACT_NONE: break;
+    case ACT_RELU:
+#pragma unroll
+      for (int t = 0; t < 32; ++t) v[t] = apply_act(v[t], ACT_RELU);
+      break;
+    case ACT_GELU:
+#pragma unroll
+      for (int t = 0; t < 32; ++t) v[t] = apply_act(v[t], ACT_GELU);
+      break;
+    case ACT_GELU_TANH:
+#pragma unroll
+      for (int t = 0; t < 32; ++t) v[t] = apply_act(v[t], ACT_GELU_TANH);
+      break;
+    case ACT_QUICK_GELU:
+#pragma unroll
+      for (int t = 0; t < 32; ++t) v[t] = apply_act(v[t], ACT_QUICK_GELU);
+      break;
+    case ACT_SILU:
+#pragma unroll
+      for (int t = 0; t < 32; ++t) v[t] = apply_act(v[t], ACT_SILU);
+      break;
+    default: break;
   }
 }
 
@@ -262,19 +291,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           __nv_bfloat16* dst = p.C + (long long)gi * p.ldc_i + jb;
           const bool vec_ok = (jb + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
           if (vec_ok) {
+            if (p.bias != nullptr) {
+              if (p.bias_on_i) {
+#pragma unroll
+                for (int t = 0; t < 32; ++t) v[t] += bi;
+              } else if ((reinterpret_cast<uintptr_t>(p.bias + jb) & 15) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + jb + q * 8);
+                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {      // a bf16 is the upper half of the fp32 with the same value
+                    v[q * 8 + e * 2] += __uint_as_float(bw[e] << 16);
+                    v[q * 8 + e * 2 + 1] += __uint_as_float(bw[e] & 0xffff0000u);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int t = 0; t < 32; ++t) v[t] += __bfloat162float(p.bias[jb + t]);
+              }
+            }
+            apply_act_chunk(v, p.act);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint32_t u[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int t = q * 8 + e * 2;
-                float a = v[t] + bi, b = v[t + 1] + bi;
-                if (p.bias != nullptr && !p.bias_on_i) {
-                  a += __bfloat162float(p.bias[jb + t]);
-                  b += __bfloat162float(p.bias[jb + t + 1]);
-                }
-                u[e] = pack_bf16(apply_act(a, p.act), apply_act(b, p.act));
-              }
+              for (int e = 0; e < 4; ++e) u[e] = pack_bf16(v[q * 8 + e * 2], v[q * 8 + e * 2 + 1]);
               *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(u[0], u[1], u[2], u[3]);
             }
           } else {

@@ -76,7 +76,8 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
                       const void* w1, const void* w2, const void* w3, const void* b1, const void* b2,
                       const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
                       int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
-                      int factor, int min_seq_len, int single_segment, uint32_t* status, cudaStream_t stream);
+                      int factor, int min_seq_len, int single_segment, int heads_per_cta, uint32_t* status,
+                      cudaStream_t stream);
 
 // consumers of split-K partial sums [splits, T, N] fp32 (partials.cu)
 void launch_add_rms_norm_partials(const float* partial, int splits, long long split_stride, const void* bias,

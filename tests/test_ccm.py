@@ -108,3 +108,40 @@ def test_fused_kernel_layer_chunks_equal_whole():
     ccm_compress_in_pool(b, tables, lens, imgs, w, 0, 1)
     ccm_compress_in_pool(b, tables, lens, imgs, w, 1, 4)
     assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("G", [1, 2, 4, 8])
+def test_fused_kernel_head_groups(G):
+    """A tile holds 128 / G output rows of G heads: every grouping gives the rows of the PyTorch statement."""
+    from fastcache_b200.ops.compress_cuda import _batch_meta
+    from fastcache_b200.ops.loader import ext
+    L, H, D, bs, f = 2, 8, 128, 64, 4
+    m = random_compressor(KVCacheLinearDecoupleCompressor, L, D, f)
+    w = m.pack(torch.bfloat16, "cuda")
+    pool = _pool(L, 24, H, bs, D, torch.bfloat16, "cuda")
+    tables = [[3, 7, 1, 9, 12, 20, 21, 22, 23, 2, 11], [5, 6, 14, 15], [8]]
+    lens, imgs = [650, 203, 9], [577, 0, 4]
+    want = pool.clone()
+    new = [ccm_compress_reference(want, bt, n, i, w) for bt, n, i in zip(tables, lens, imgs)]
+    bt_d, lens_d = _batch_meta(pool, tables, lens)
+    img_d = torch.tensor(imgs, dtype=torch.int32, device="cuda")
+    e = ext()
+    e.ccm_compress(pool, bt_d, lens_d, img_d, w.w1, w.b1, w.w2, w.b2, w.w3, w.b3, 0, L, 0, f, int(w.min_seq_len),
+                   bool(w.single_segment), e.status_tensor(0), G)
+    torch.cuda.synchronize()
+    assert e.read_status(0) == 0
+    for bt, n in zip(tables, new):
+        blocks = torch.tensor(bt, device="cuda")
+        for l in range(L):
+            for kv in (0, 1):
+                a = _rows(pool[l, kv], blocks, n).float()
+                b = _rows(want[l, kv], blocks, n).float()
+                assert (a - b).abs().max().item() < 3e-2 * max(1.0, b.abs().max().item())
+
+
+def test_heads_per_tile_minimises_tiles():
+    from fastcache_b200.ops.ccm_cuda import heads_per_tile
+    assert heads_per_tile(32, [640] * 15, [576] * 15, 4, 1, False) == 8      # 144 + 16 output rows per head
+    assert heads_per_tile(8, [4096] * 8, [0] * 8, 2, 1, False) == 1          # long segments fill tiles by themselves
+    assert heads_per_tile(3, [640], [576], 4, 1, False) == 1                 # 3 heads: no other group divides them
