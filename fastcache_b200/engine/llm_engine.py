@@ -29,6 +29,7 @@ import torch
 from ..config import Config, ModelConfig, text_config_of
 from ..parallel import tp as tpmod
 from ..sampling_params import SamplingParams
+from ..utils.tracing import StepTrace, nvtx_range
 from .model_runner import ModelRunner
 from .scheduler import Scheduler
 from .sequence import CompressionState, Sequence, SequenceStatus
@@ -158,6 +159,7 @@ class LLMEngine:
         self._pending: Dict[int, PendingCompression] = {}
         self._pending_compression_events = self._pending     # name used by the reference's benches
         self.stats = StepStats()
+        self.trace: Optional[StepTrace] = None
         self._timing: Optional[dict] = None
         atexit.register(self.exit)
 
@@ -246,6 +248,12 @@ class LLMEngine:
         self.scheduler.block_manager.check_invariants()
         return n
 
+    def enable_trace(self, capacity: int = 4096, device_timing: bool = True) -> StepTrace:
+        """Starts a per-step trace (kind, batch, tokens, pool state, host and device time per step); returns it.
+        `llm.trace.dump(path)` writes a chrome://tracing file, `llm.trace.summary()` the totals per phase."""
+        self.trace = StepTrace(capacity, device_timing)
+        return self.trace
+
     def check_device_status(self) -> None:
         """Raise if a kernel of this package reported a wait that ran out or a bad index since the
         last call (the kernels return instead of hanging and leave a code in a status word)."""
@@ -297,7 +305,8 @@ class LLMEngine:
             for s, n in zip(chunk, rows):
                 s._kv_cache_len = n
             try:
-                new = r.compress_kv_cache_batch(chunk, stream=r.main_stream)
+                with nvtx_range("compress"):
+                    new = r.compress_kv_cache_batch(chunk, stream=r.main_stream)
             except Exception as exc:
                 for s, v in zip(chunk, saved):
                     s._kv_cache_len = v
@@ -338,7 +347,8 @@ class LLMEngine:
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
         start.record(stream)
-        new = r.compress_kv_cache_batch(seqs, stream=stream)
+        with nvtx_range("compress"):
+            new = r.compress_kv_cache_batch(seqs, stream=stream)
         end.record(stream)
         for s, n_in, n_out in zip(seqs, rows, new):
             s.compression_state = CompressionState.IN_PROGRESS
@@ -379,7 +389,8 @@ class LLMEngine:
             saved = [s._kv_cache_len for s in seqs]
             for p in ps:
                 p.seq._kv_cache_len = p.rows
-            new = r.compress_kv_cache_batch(seqs, first, last, stream=stream)
+            with nvtx_range("compress_chunk"):
+                new = r.compress_kv_cache_batch(seqs, first, last, stream=stream)
             for p, s, v, n in zip(ps, seqs, saved, new):
                 s._kv_cache_len = v
                 p.next_layer = last
@@ -451,7 +462,16 @@ class LLMEngine:
         if not is_prefill:
             self._finalize_pending(seqs)
         timing = self._begin_timing(ctl)
-        tokens = r.run(seqs, is_prefill)
+        rec = None
+        if self.trace is not None:
+            bm = sch.block_manager
+            rec = self.trace.begin(self.stats.steps, "prefill" if is_prefill else "decode", len(seqs),
+                                   sum(s.logical_len - s.num_cached_tokens for s in seqs) if is_prefill else len(seqs),
+                                   len(bm.free_block_ids), len(bm.blocks), self.stats.compressions, r.main_stream)
+        with nvtx_range("prefill" if is_prefill else "decode"):
+            tokens = r.run(seqs, is_prefill)
+        if rec is not None:
+            self.trace.end(rec, r.main_stream)
         self._end_timing(ctl, timing, is_prefill, seqs)
         now = time.perf_counter()
         if is_prefill:

@@ -58,3 +58,25 @@ def test_uncompressed_matches_dense_forward():
     out = llm.generate(prompts, sp)
     out2 = _engine(False, False).generate(prompts, sp)
     assert [x["token_ids"] for x in out] == [x["token_ids"] for x in out2]
+
+
+def test_step_trace_records_every_step_and_exports_chrome_trace(tmp_path):
+    import json
+    from fastcache_b200.utils import tracing
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    llm = _engine(True, True)
+    trace = llm.enable_trace(capacity=64)
+    with tracing.nvtx_range("no-op without a GPU"):
+        llm.generate(_prompts(), sp)
+    kinds = [r.kind for r in trace.records]
+    assert kinds[0] == "prefill" and kinds.count("decode") == 3 and len(kinds) == llm.stats.steps
+    first = trace.records[0]
+    assert first.num_seqs == 4 and first.tokens == 4 * 128 and first.total_blocks == 256
+    assert trace.records[1].compressions == 4 and trace.records[1].free_blocks == 256 - 4 * 3
+    s = trace.summary()
+    assert s["prefill"]["tokens"] == 512 and s["decode"]["steps"] == 3 and s["decode"]["device_ms"] is None
+    path = tmp_path / "trace.json"
+    trace.dump(str(path))
+    blob = json.loads(path.read_text())
+    assert sum(e["ph"] == "X" for e in blob["traceEvents"]) == len(kinds)
+    assert not tracing.nvtx_enabled() or torch.cuda.is_available()
