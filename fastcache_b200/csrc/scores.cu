@@ -68,20 +68,25 @@ ea_stats_kernel(const bf16* __restrict__ qw, float* __restrict__ stats, int L, i
 }
 
 // ------------------------------------------------------------------ scores
-// grid (key tiles of KEYS_PER_CTA, Hkv, n_seq * L), 256 threads: one warp walks its keys, each lane owns
-// D / 32 rows of Sigma (kept in shared memory) and the matching elements of the key.
-constexpr int EA_KEYS_PER_CTA = 256;
+// grid (key tiles of EA_KEYS_PER_CTA, Hkv, n_seq * L), 256 threads.  Sigma stays in shared memory (rows padded to
+// D + 4 floats: 16-byte aligned and conflict-free for 128-bit reads).  A warp takes EA_KB keys at a time: lane l owns
+// rows l, l + 32, ... of Sigma and accumulates (Sigma k)_row for the EA_KB keys at once, so every 128-bit piece of a
+// Sigma row read from shared memory feeds 4 * EA_KB multiply-adds (one key at a time, two shared-memory reads per
+// multiply-add bound the kernel).
+constexpr int EA_KEYS_PER_CTA = 512;
+constexpr int EA_KB = 8;
 
 template <int D>
 __global__ void __launch_bounds__(256)
 ea_scores_kernel(const bf16* __restrict__ pool, const float* __restrict__ stats, const int* __restrict__ block_tables,
                  const int* __restrict__ kv_lens, float* __restrict__ scores, int L, int num_blocks, int Hkv,
                  int block_size, int max_blocks, int stride, int n_sink, uint32_t* status) {
-  constexpr int PER = D / 32;                                // key elements per lane
+  constexpr int PER = D / 32;                                // Sigma rows (and key elements) per lane
+  constexpr int CP = D + 4;                                  // padded row of Sigma, floats
   extern __shared__ __align__(16) uint8_t smem[];
-  float* s_cov = reinterpret_cast<float*>(smem);             // [D][D + 1] (padded rows: no bank conflicts)
-  float* s_mu = s_cov + D * (D + 1);
-  float* s_k = s_mu + D;                                     // [8 warps][D]
+  float* s_cov = reinterpret_cast<float*>(smem);             // [D][CP]
+  float* s_mu = s_cov + D * CP;
+  float* s_k = s_mu + D;                                     // [8 warps][EA_KB][D]
   const int hk = blockIdx.y, unit_sl = blockIdx.z;
   const int seq = unit_sl / L, layer = unit_sl % L;
   const int S = kv_lens[seq];
@@ -90,7 +95,7 @@ ea_scores_kernel(const bf16* __restrict__ pool, const float* __restrict__ stats,
   if (c_begin >= stride) return;
   const float* st = stats + (((long long)seq * L + layer) * Hkv + hk) * (D + D * D);
   if (c_begin < S) {
-    for (int i = threadIdx.x; i < D * D; i += blockDim.x) s_cov[(i / D) * (D + 1) + (i % D)] = st[D + i];
+    for (int i = threadIdx.x; i < D * D; i += blockDim.x) s_cov[(i / D) * CP + (i % D)] = st[D + i];
     for (int i = threadIdx.x; i < D; i += blockDim.x) s_mu[i] = st[i];
   }
   __syncthreads();
@@ -99,48 +104,75 @@ ea_scores_kernel(const bf16* __restrict__ pool, const float* __restrict__ stats,
   const bf16* kbase = pool + ((long long)layer * 2) * num_blocks * Hkv * block_size * D;
   const bf16* vbase = kbase + (long long)num_blocks * Hkv * block_size * D;
   const float inv_sqrt_d = rsqrtf(float(D)), inv_2d = 0.5f / float(D);
-  float* myk = s_k + warp * D;
-  for (int c = c_begin + warp; c < min(c_begin + EA_KEYS_PER_CTA, stride); c += 8) {
-    float result;
-    if (c >= S) {
-      result = -INFINITY;
-    } else if (c < n_sink) {
-      result = SC_POS;
-    } else {
-      int blk = bt[c / block_size];
-      if (blk < 0 || blk >= num_blocks) {
-        report(status, ST_BAD_INDEX);
-        blk = 0;
+  float* myk = s_k + warp * EA_KB * D;
+  const int c_end = min(c_begin + EA_KEYS_PER_CTA, stride);
+  for (int c0 = c_begin + warp * EA_KB; c0 < c_end; c0 += 8 * EA_KB) {
+    // ---- the keys of this group into shared memory (zeros for rows that get a fixed score)
+    float vss[EA_KB], lin[EA_KB];
+#pragma unroll
+    for (int kb = 0; kb < EA_KB; ++kb) {
+      const int c = c0 + kb;
+      vss[kb] = lin[kb] = 0.f;
+      const bool live = c < S && c >= n_sink;
+      long long off = 0;
+      if (live) {
+        int blk = bt[c / block_size];
+        if (blk < 0 || blk >= num_blocks) {
+          report(status, ST_BAD_INDEX);
+          blk = 0;
+        }
+        off = (((long long)blk * Hkv + hk) * block_size + c % block_size) * D;
       }
-      const long long off = (((long long)blk * Hkv + hk) * block_size + c % block_size) * D;
-      float kreg[PER], vss = 0.f, lin = 0.f;
 #pragma unroll
       for (int e = 0; e < PER; ++e) {
         const int d = lane + 32 * e;
-        kreg[e] = __bfloat162float(kbase[off + d]);
-        const float v = __bfloat162float(vbase[off + d]);
-        vss += v * v;
-        lin += kreg[e] * s_mu[d];
-        myk[d] = kreg[e];
+        float kv = 0.f;
+        if (live) {
+          kv = __bfloat162float(kbase[off + d]);
+          const float v = __bfloat162float(vbase[off + d]);
+          vss[kb] += v * v;
+          lin[kb] += kv * s_mu[d];
+        }
+        myk[kb * D + d] = kv;
       }
-      __syncwarp();
-      // quad = sum_i k_i * (Sigma k)_i ; lane owns rows i = lane + 32 e
+    }
+    __syncwarp();
+    // ---- acc[e][kb] = (Sigma k_kb)_(lane + 32 e)
+    float acc[PER][EA_KB];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+#pragma unroll
+      for (int kb = 0; kb < EA_KB; ++kb) acc[e][kb] = 0.f;
+    }
+#pragma unroll 2
+    for (int d = 0; d < D; d += 4) {
+      float4 r[PER];
+#pragma unroll
+      for (int e = 0; e < PER; ++e) r[e] = *reinterpret_cast<const float4*>(s_cov + (lane + 32 * e) * CP + d);
+#pragma unroll
+      for (int kb = 0; kb < EA_KB; ++kb) {
+        const float4 kk = *reinterpret_cast<const float4*>(myk + kb * D + d);
+#pragma unroll
+        for (int e = 0; e < PER; ++e)
+          acc[e][kb] += r[e].x * kk.x + r[e].y * kk.y + r[e].z * kk.z + r[e].w * kk.w;
+      }
+    }
+    // ---- quad = k^T Sigma k, then the score of every key of the group
+#pragma unroll
+    for (int kb = 0; kb < EA_KB; ++kb) {
+      const int c = c0 + kb;
       float quad = 0.f;
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const float* row = s_cov + (lane + 32 * e) * (D + 1);
-        float y = 0.f;
-#pragma unroll 8
-        for (int d = 0; d < D; ++d) y += row[d] * myk[d];
-        quad += kreg[e] * y;
-      }
-      __syncwarp();
-      vss = warp_sum(vss);
-      lin = warp_sum(lin);
+      for (int e = 0; e < PER; ++e) quad += myk[kb * D + lane + 32 * e] * acc[e][kb];
       quad = warp_sum(quad);
-      result = lin * inv_sqrt_d + quad * inv_2d + 0.5f * __logf(fmaxf(vss, 1e-30f));
+      const float vs = warp_sum(vss[kb]), ln = warp_sum(lin[kb]);
+      float result;
+      if (c >= S) result = -INFINITY;
+      else if (c < n_sink) result = SC_POS;
+      else result = ln * inv_sqrt_d + quad * inv_2d + 0.5f * __logf(fmaxf(vs, 1e-30f));
+      if (lane == 0 && c < c_end) out[c] = result;
     }
-    if (lane == 0) out[c] = result;
+    __syncwarp();
   }
 }
 
@@ -163,7 +195,7 @@ void launch_expected_attention_scores(const void* pool, const void* qw, const in
   const int rows = (Hq / Hkv) * w;
   if (Hq % Hkv != 0 || rows < 2) throw std::runtime_error("expected attention: bad head grouping or window");
   const int smem1 = (rows * D + D) * 4;
-  const int smem2 = (D * (D + 1) + D + 8 * D) * 4;
+  const int smem2 = (D * (D + 4) + D + 8 * EA_KB * D) * 4;
   if (smem1 > 220 * 1024) throw std::runtime_error("expected attention: (Hq / Hkv) * window * head_dim is too large");
   dim3 g1(Hkv, L, n_seq);
   dim3 g2((stride + EA_KEYS_PER_CTA - 1) / EA_KEYS_PER_CTA, Hkv, n_seq * L);
