@@ -302,7 +302,7 @@ static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Sk
 
 // Number of K splits for `tiles` row tiles on `sms` SMs: fill the machine to a whole
 // number of waves while keeping at least 4 K blocks per CTA.
-int skinny_pick_splits(int tiles, int num_kb, int sms, int M, int N, size_t scratch_floats) {
+int skinny_pick_splits(int tiles, int tile_rows, int num_kb, int sms, int M, int N, size_t scratch_floats) {
   int best = 1;
   double best_cost = 1e30;
   const int max_s = std::max(1, std::min(num_kb / 4, 32));
@@ -311,9 +311,16 @@ int skinny_pick_splits(int tiles, int num_kb, int sms, int M, int N, size_t scra
     const int ctas = tiles * s;
     const int waves = (ctas + sms - 1) / sms;
     const int kb = (num_kb + s - 1) / s;
-    // time ~ waves * (kb + fixed overhead per CTA) ; partial traffic adds a little per split
-    // (every extra split is another fp32 copy of the output for the consumer to read back)
-    const double cost = waves * (kb + 6.0) + 0.5 * s;
+    // time ~ waves * (kb + fixed overhead per CTA), in units of one k-block step of a full wave; partial traffic
+    // adds a little per split while the fp32 partial sums stay in L2 (every extra split is another copy of the
+    // output for the consumer to read back), and their full write + read-back once they no longer fit (the LM
+    // head: 128 x 151936 x 4 bytes per split), counted against the weight bytes a wave moves per step
+    double cost = waves * (kb + 6.0) + 0.5 * s;
+    if (s > 1) {
+      const double partial_bytes = 4.0 * s * M * N, l2_resident = 48.0 * 1024 * 1024;
+      if (partial_bytes > l2_resident)
+        cost += 2.0 * (partial_bytes - l2_resident) / (double(sms) * tile_rows * SK_BK * 2.0);
+    }
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best = s;
@@ -335,7 +342,7 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   const int rows = small_rows ? 128 : SK_BM;
   const int tiles = (N + rows - 1) / rows;
   const size_t scratch_floats = ws.scratch != nullptr ? gemm_scratch_bytes() / 4 : 0;
-  int splits = splits_request > 0 ? splits_request : skinny_pick_splits(tiles, num_kb, sms, M, N, scratch_floats);
+  int splits = splits_request > 0 ? splits_request : skinny_pick_splits(tiles, rows, num_kb, sms, M, N, scratch_floats);
   if (N % 4 != 0) splits = 1;
   if (splits > 1 && (size_t)splits * M * N > scratch_floats) splits = 1;
   int kb_per = (num_kb + splits - 1) / splits;
