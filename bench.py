@@ -120,6 +120,26 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.samples)}
 
 
+_RESULT_OUT = None
+
+
+def claim_stdout() -> None:
+    """Keeps the process's standard output for the one result line.  Libraries write to file descriptor 1 as well
+    (NCCL prints "NCCL version ..." there when a communicator is created): from here on descriptor 1 is stderr,
+    and `emit` writes the JSON line to the original standard output."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -276,7 +296,7 @@ def run_ours(args):
             "gpu_launches": int(ops.COUNTERS["launches"]),
             "clocks": clocks, "device_status": int(status), "impl": "fastcache_b200",
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     llm.exit()
     if world > 1:
         tpmod.cleanup_tensor_parallel()
@@ -438,7 +458,7 @@ def run_serving(args):
             "gpu_launches": int(ops.COUNTERS["launches"]), "clocks": clocks, "device_status": int(status),
             "impl": "fastcache_b200",
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     llm.exit()
     if world > 1:
         tpmod.cleanup_tensor_parallel()
@@ -446,7 +466,7 @@ def run_serving(args):
 
 # ------------------------------------------------------------------ reference
 def unavailable(why: str):
-    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    emit({"impl": "reference", "unavailable": why})
     sys.exit(0)
 
 
@@ -478,7 +498,7 @@ def run_reference(args):
         import traceback
         traceback.print_exc()
         unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
@@ -496,6 +516,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.steps = max(1, args.steps)
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     elif args.config in SERVING:
