@@ -307,6 +307,22 @@ def load_compressor(path_or_state: Any, src_config: Any = None, compression_fact
     return m
 
 
+def load_minicpm_compressor(compressor_path: str, hf_config: Any, compression_factor: int = 5,
+                            device: Any = None, dtype: Optional[torch.dtype] = None) -> "MiniCPMKVCompressor":
+    """The full (tk / tv / ik / iv + attention) MiniCPM compressor with its `.pth` loaded strictly.
+
+    Same job as "kv-cache pipeline"/nanovllm/kernels/minicpm_compressor.py:195-229; the device is the
+    caller's choice here (the reference always moves to the current CUDA device), and a missing file
+    is an error instead of a compressor with random weights."""
+    if not os.path.exists(compressor_path):
+        raise FileNotFoundError(f"compressor checkpoint not found: {compressor_path}")
+    m = load_compressor(compressor_path, src_config=hf_config, compression_factor=compression_factor,
+                        min_seq_len=2, kind="minicpm")
+    if device is not None or dtype is not None:
+        m = m.to(device=device, dtype=dtype)
+    return m.eval()
+
+
 def save_compressor(module: _CCMBase, path: str, epoch: int = 0, optimizer: Any = None, scheduler: Any = None,
                     loss: float = 0.0) -> None:
     """Write the training-script checkpoint layout (scripts/finetune_llava.py:29-47)."""

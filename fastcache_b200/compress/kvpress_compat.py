@@ -175,6 +175,37 @@ def exec_compression_methods(kv_cache: KV, name: str, compression_ratio: float =
     return out, press.totalTime
 
 
+def get_underlying_model(model: Any) -> Any:
+    """The transformer stack (the object that owns `.layers`) inside a wrapper model.
+
+    Looks through the attribute names the supported families use (LLaVA: `language_model`,
+    MiniCPM: `llm`, plus `llava_model`, `llama_model`, `decoder`) and then through `.model` /
+    `.transformer` nesting (reference: utils_ccm/utils_compress.py:351-411).  Raises if nothing with
+    layers is found, where the reference goes on with None."""
+    seen = set()
+
+    def descend(m: Any, depth: int = 0) -> Any:
+        if m is None or id(m) in seen or depth > 4:
+            return None
+        seen.add(id(m))
+        if hasattr(m, "layers"):
+            return m
+        for inner in ("model", "transformer", "decoder"):
+            got = descend(getattr(m, inner, None), depth + 1)
+            if got is not None:
+                return got
+        return None
+
+    for attr in ("language_model", "llava_model", "llama_model", "decoder", "llm"):
+        got = descend(getattr(model, attr, None))
+        if got is not None:
+            return got
+    got = descend(model)
+    if got is None:
+        raise AttributeError(f"no transformer stack with `.layers` found in {type(model).__name__}")
+    return got
+
+
 class TimeTik:
     """Named timers (reference: utils_ccm/utils_compress.py:414-475)."""
 

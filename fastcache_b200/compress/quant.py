@@ -97,3 +97,41 @@ class SimpleKVQuantizer:
 
 
 ImprovedKVQuantizer = SimpleKVQuantizer
+
+
+class QuantizedCacheWrapper:
+    """`with QuantizedCacheWrapper(nbits)(model) as m:` switches a HuggingFace model's generation
+    cache to its quantised implementation for the block and restores the config afterwards
+    (reference: utils_ccm/utils_compress.py:166-197).  `backend` is the HF cache backend name; the
+    reference fixes it to "quanto"."""
+
+    def __init__(self, nbits: int = 4, backend: str = "quanto"):
+        self.nbits, self.backend = nbits, backend
+
+    def __call__(self, model):
+        return self.QuantizedContext(model, self.nbits, self.backend)
+
+    class QuantizedContext:
+        _UNSET = object()
+
+        def __init__(self, model, nbits: int, backend: str = "quanto"):
+            self.model, self.nbits, self.backend = model, nbits, backend
+            self._saved = {}
+
+        def __enter__(self):
+            cfg = self.model.config
+            for name in ("cache_implementation", "cache_config"):
+                self._saved[name] = getattr(cfg, name, self._UNSET)
+            cfg.cache_implementation = "quantized"
+            cfg.cache_config = {"backend": self.backend, "nbits": self.nbits}
+            return self.model
+
+        def __exit__(self, exc_type, exc, tb):
+            cfg = self.model.config
+            for name, old in self._saved.items():
+                if old is self._UNSET:
+                    if hasattr(cfg, name):
+                        delattr(cfg, name)
+                else:
+                    setattr(cfg, name, old)
+            return False

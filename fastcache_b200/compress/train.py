@@ -21,7 +21,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .ccm import _CCMBase, save_compressor
+from .ccm import (KVCacheHybridCompressor, KVCacheLinearDecoupleCompressor, _CCMBase, load_compressor,
+                  save_compressor)
 
 
 class KVCacheCompressionLoss(nn.Module):
@@ -140,7 +141,7 @@ def finetune_compressor(compressor: _CCMBase,
             if cfg.grad_clip:
                 nn.utils.clip_grad_norm_(compressor.parameters(), cfg.grad_clip)
             opt.step()
-            tot, n = tot + float(loss), n + 1
+            tot, n = tot + float(loss.detach()), n + 1
         compressor.eval()
         vtot = vacc = vn = 0.0
         with torch.no_grad():
@@ -163,3 +164,146 @@ def _compress_with_grad(compressor: _CCMBase, kv, it_len):
     """`forward` of the modules is wrapped in no_grad for inference; training calls the layer path."""
     img = 0 if not hasattr(compressor, "compress_ik") else int(it_len[0])
     return [compressor.compress_layer_kv(k, v, l, img) for l, (k, v) in enumerate(kv)]
+
+
+# --------------------------------------------------------------------------- named recipes
+def hf_forward_with_kv(model: Any, prefix_len_of: Callable[[Any], int]) -> Callable:
+    """`forward_with_kv` for a HuggingFace-style causal LM (`model(input_ids=..., past_key_values=...,
+    output_hidden_states=True, use_cache=True)`).  A batch is a dict with `input_ids` [B, T] (and
+    whatever else the model takes); the first `prefix_len_of(batch)` tokens are the prefix whose KV
+    is compressed, the rest is the continuation that is scored."""
+
+    def as_pairs(past) -> List[Tuple[torch.Tensor, torch.Tensor]]:
+        if hasattr(past, "to_legacy_cache"):
+            past = past.to_legacy_cache()
+        return [(k, v) for k, v in past]
+
+    def fwd(batch: Dict[str, Any], kv: Optional[List[Tuple[torch.Tensor, torch.Tensor]]]):
+        ids = batch["input_ids"]
+        n = int(prefix_len_of(batch))
+        extra = {k: v for k, v in batch.items() if k not in ("input_ids", "labels", "it_len")}
+        if kv is None:
+            out = model(input_ids=ids[:, :n], use_cache=True, output_hidden_states=True, **extra)
+            return out.logits, tuple(out.hidden_states), as_pairs(out.past_key_values)
+        past = tuple((k, v) for k, v in kv)
+        out = model(input_ids=ids[:, n:], past_key_values=past, use_cache=True, output_hidden_states=True)
+        return out.logits, tuple(out.hidden_states), as_pairs(out.past_key_values)
+
+    return fwd
+
+
+def _split(samples: Sequence[Any], train_ratio: float) -> Tuple[List[Any], List[Any]]:
+    cut = max(1, min(len(samples) - 1, int(len(samples) * train_ratio))) if len(samples) > 1 else len(samples)
+    return list(samples[:cut]), list(samples[cut:]) or list(samples[:cut])
+
+
+def _recipe(cls, model: Any, samples: Sequence[Any], model_config: Any, forward_with_kv: Optional[Callable],
+            prefix_len_of: Callable[[Any], int], it_len_of: Callable[[Any], Sequence[int]],
+            compressor_load_path: str, compressor_save_name: str, out_dir: str, num_epochs: int,
+            learning_rate: float, compression_ratio: int, train_ratio: float, is_continue: bool,
+            strategy: str) -> Tuple[_CCMBase, Dict[str, Any]]:
+    cfg_obj = model_config if model_config is not None else getattr(model, "config", None)
+    if compressor_load_path:
+        comp = load_compressor(compressor_load_path, src_config=cfg_obj, compression_factor=compression_ratio,
+                               min_seq_len=2, kind="hybrid" if cls is KVCacheHybridCompressor else "decouple")
+    else:
+        comp = cls(cfg_obj, compression_ratio, 2)
+    first = next(iter(model.parameters()), None) if hasattr(model, "parameters") else None
+    if first is not None:
+        comp = comp.to(first.device)
+    fwd = forward_with_kv or hf_forward_with_kv(model, prefix_len_of)
+    train, val = _split(samples, train_ratio)
+    cfg = FinetuneConfig(lr=learning_rate, epochs=num_epochs, compression_factor=compression_ratio,
+                         out_dir=out_dir, name=compressor_save_name, is_continue=is_continue)
+    return comp, finetune_compressor(comp, fwd, train, val, cfg, it_len_of, KVCacheCompressionLoss(strategy))
+
+
+def finetune_llava(model: Any, samples: Sequence[Any], model_config: Any = None,
+                   forward_with_kv: Optional[Callable] = None,
+                   prefix_len_of: Callable[[Any], int] = lambda b: int(b["it_len"][0]) + int(b["it_len"][1]),
+                   it_len_of: Callable[[Any], Sequence[int]] = lambda b: b["it_len"],
+                   compressor_load_path: str = "", compressor_save_name: str = "finetune_mlp_llava",
+                   out_dir: str = "ckpt", num_epochs: int = 40, learning_rate: float = 5e-4,
+                   compression_ratio: int = 5, train_ratio: float = 0.8, is_continue: bool = False,
+                   strategy: str = "logit") -> Tuple[_CCMBase, Dict[str, Any]]:
+    """The LLaVA recipe (scripts/finetune_llava.py:509-791): image / text decoupled compressor,
+    Adam 5e-4, plateau scheduler, factor 5, 40 epochs, 80 / 20 split, `last_` / `best_` files."""
+    return _recipe(KVCacheLinearDecoupleCompressor, model, samples, model_config, forward_with_kv, prefix_len_of,
+                   it_len_of, compressor_load_path, compressor_save_name, out_dir, num_epochs, learning_rate,
+                   compression_ratio, train_ratio, is_continue, strategy)
+
+
+def finetune_com_minicpm(model: Any, samples: Sequence[Any], model_config: Any = None,
+                         forward_with_kv: Optional[Callable] = None,
+                         prefix_len_of: Callable[[Any], int] = lambda b: int(b["it_len"][0]) + int(b["it_len"][1]),
+                         it_len_of: Callable[[Any], Sequence[int]] = lambda b: (0, int(sum(b["it_len"]))),
+                         compressor_load_path: str = "", compressor_save_name: str = "finetune_mlp_minicpm",
+                         out_dir: str = "ckpt", num_epochs: int = 40, learning_rate: float = 5e-4,
+                         compression_ratio: int = 5, train_ratio: float = 0.8, is_continue: bool = False,
+                         strategy: str = "logit") -> Tuple[_CCMBase, Dict[str, Any]]:
+    """The MiniCPM recipe (scripts/finetune_minicpm.py:863-1195, defaults :1408-1445): the hybrid
+    compressor (text banks only; the whole prefix counts as text), otherwise as for LLaVA."""
+    return _recipe(KVCacheHybridCompressor, model, samples, model_config, forward_with_kv, prefix_len_of,
+                   it_len_of, compressor_load_path, compressor_save_name, out_dir, num_epochs, learning_rate,
+                   compression_ratio, train_ratio, is_continue, strategy)
+
+
+def main(argv: Optional[Sequence[str]] = None) -> Dict[str, Any]:
+    """`python -m fastcache_b200.compress.train --model-path DIR --data FILE.json ...` fine-tunes a
+    compressor for a HuggingFace checkpoint.  Samples come from the dataset loaders of
+    `fastcache_b200.serving.datasets`; this entry distils on the text of each conversation (question and
+    reference answers), the first half as the prefix whose KV is compressed."""
+    import argparse
+    import random
+
+    ap = argparse.ArgumentParser(description="fine-tune a CCM merge compressor by distillation")
+    ap.add_argument("--model-path", required=True)
+    ap.add_argument("--data", required=True, help="llava_v1_5_mix665k-style JSON")
+    ap.add_argument("--images", default="", help="folder the JSON's image paths are relative to")
+    ap.add_argument("--datasets-type", default="image", choices=["text", "image"])
+    ap.add_argument("--model-mode", default="minicpm", choices=["llava", "minicpm"])
+    ap.add_argument("--num-samples", type=int, default=320)
+    ap.add_argument("--max-input-len", type=int, default=512)
+    ap.add_argument("--epochs", type=int, default=40)
+    ap.add_argument("--lr", type=float, default=5e-4)
+    ap.add_argument("--compression-ratio", type=int, default=5)
+    ap.add_argument("--train-ratio", type=float, default=0.8)
+    ap.add_argument("--compressor-load-path", default="")
+    ap.add_argument("--compressor-save-name", default="")
+    ap.add_argument("--out-dir", default="ckpt")
+    ap.add_argument("--continue", dest="is_continue", action="store_true")
+    ap.add_argument("--seed", type=int, default=48)
+    a = ap.parse_args(argv)
+
+    from transformers import AutoModelForCausalLM, AutoTokenizer
+    from ..serving.datasets import load_image_data
+
+    random.seed(a.seed)
+    torch.manual_seed(a.seed)
+    tok = AutoTokenizer.from_pretrained(a.model_path, trust_remote_code=True)
+    model = AutoModelForCausalLM.from_pretrained(a.model_path, trust_remote_code=True,
+                                                 torch_dtype=torch.bfloat16).eval()
+    if torch.cuda.is_available():
+        model = model.cuda()
+    for p_ in model.parameters():
+        p_.requires_grad_(False)
+    dev = next(model.parameters()).device
+    samples = []
+    for rec in load_image_data(a.data, a.images, a.num_samples, seed=a.seed):
+        ids = tok(rec.prompt + " " + " ".join(rec.answers), return_tensors="pt", truncation=True,
+                  max_length=a.max_input_len)["input_ids"].to(dev)
+        if ids.shape[1] < 4 * a.compression_ratio:
+            continue
+        half = ids.shape[1] // 2
+        samples.append({"input_ids": ids, "it_len": (0, half)})
+    fn = finetune_llava if a.model_mode == "llava" else finetune_com_minicpm
+    name = a.compressor_save_name or f"finetune_mlp_{a.model_mode}"
+    _, result = fn(model, samples, compressor_load_path=a.compressor_load_path, compressor_save_name=name,
+                   out_dir=a.out_dir, num_epochs=a.epochs, learning_rate=a.lr,
+                   compression_ratio=a.compression_ratio, train_ratio=a.train_ratio, is_continue=a.is_continue)
+    print({k: result[k] for k in ("best_val", "last", "best")})
+    return result
+
+
+if __name__ == "__main__":
+    main()

@@ -32,6 +32,7 @@ from ..sampling_params import SamplingParams
 from ..utils.tracing import StepTrace, nvtx_range
 from .model_runner import ModelRunner
 from .scheduler import Scheduler
+from .async_compression import AsyncCompressionManager
 from .sequence import CompressionState, Sequence, SequenceStatus
 
 
@@ -158,6 +159,8 @@ class LLMEngine:
                 dual_batch_enabled=auto_dual_batch, dual_batch_interval=self.auto_dual_interval)
         self._pending: Dict[int, PendingCompression] = {}
         self._pending_compression_events = self._pending     # name used by the reference's benches
+        self.async_manager = AsyncCompressionManager(self)
+        self.model_runner._async_manager = self.async_manager   # where the reference keeps it
         self.stats = StepStats()
         self.trace: Optional[StepTrace] = None
         self._timing: Optional[dict] = None

@@ -35,6 +35,7 @@ from ..parallel import tp as tpmod
 from ..utils.context import reset_context, set_context
 from ..utils.loader import init_random_weights, load_model
 from ..utils.memory import get_gpu_memory
+from .async_compression import AsyncCompressionManager  # noqa: F401  (the reference exports it from here)
 from .sequence import CompressionState, Sequence
 
 

@@ -64,6 +64,29 @@ class LlavaForConditionalGeneration(nn.Module):
     def encode_images(self, pixels: torch.Tensor) -> torch.Tensor:
         return self.multi_modal_projector(self.vision_tower(pixels))
 
+    get_image_features = encode_images
+
+    def merge_input_ids_with_image_features(self, input_ids: torch.Tensor, image_features: torch.Tensor,
+                                            positions: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Flat (1-D) token ids with ONE image placeholder -> embeddings and positions with the
+        placeholder replaced by the image's rows (nanovllm/models/llava.py:491-551).
+
+        The engine does not call this: its runner expands the placeholder when it builds the step's
+        rows, so the features are written into an embedding buffer of the final length.  It is
+        kept for callers that drive the model directly."""
+        embeds = self.language_model.get_input_embeddings(input_ids)
+        if image_features.dim() == 3:
+            image_features = image_features[0]
+        where = (input_ids == self.image_token_id).nonzero(as_tuple=True)[0]
+        if where.numel() == 0:
+            return embeds, positions
+        i, n = int(where[0]), image_features.shape[0]
+        merged = torch.cat([embeds[:i], image_features.to(embeds.dtype), embeds[i + 1:]], 0)
+        pos = torch.cat([positions[:i],
+                         torch.arange(i, i + n, dtype=positions.dtype, device=positions.device),
+                         positions[i + 1:] + (n - 1)])
+        return merged, pos
+
     # -------------------------------------------------------------- forward
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
                 images: Optional[List[Tuple[torch.Tensor, Any, int, int]]] = None) -> torch.Tensor:

@@ -157,6 +157,43 @@ class MiniCPMForConditionalGeneration(nn.Module):
             mask[idx, : h * w] = True
         return feats, mask
 
+    def get_vllm_embedding(self, data: Dict[str, Any]) -> Tuple[torch.Tensor, List[torch.Tensor]]:
+        """Batched entry of the HuggingFace-style harness (nanovllm/models/minicpm.py:342-432).
+
+        `data`: `input_ids` [B, T]; `pixel_values`: per sample a list of [3, H, W] slices;
+        `tgt_sizes`: per sample a [slices, 2] tensor of patch grids; `image_bound`: per sample a
+        [n, 2] tensor of [start, end) spans of placeholder tokens.  Returns the input embeddings
+        with each span overwritten by that slice's `query_num` rows, and the per-sample vision
+        features.  The reference borrows the vision modules from the HF remote-code model; these
+        are the native tower and resampler."""
+        ids = data["input_ids"]
+        if ids.dim() == 1:
+            ids = ids[None]
+        embeds = self.llm.get_input_embeddings(ids.reshape(-1)).reshape(*ids.shape, -1).clone()
+        p = self.vision_config.patch_size
+        bounds = data.get("image_bound") or [None] * ids.shape[0]
+        vision: List[torch.Tensor] = []
+        for b, slices in enumerate(data.get("pixel_values") or []):
+            if slices is None or len(slices) == 0:
+                vision.append(embeds.new_zeros(0, embeds.shape[-1]))
+                continue
+            tgt = torch.as_tensor(data["tgt_sizes"][b], dtype=torch.long).reshape(-1, 2)
+            Hm, Wm = int(tgt[:, 0].max()) * p, int(tgt[:, 1].max()) * p
+            batch = embeds.new_zeros(len(slices), 3, Hm, Wm)
+            for i, sl in enumerate(slices):
+                h, w = int(tgt[i, 0]) * p, int(tgt[i, 1]) * p
+                batch[i, :, :h, :w] = sl.reshape(3, h, w).to(batch.dtype)
+            feats = self.encode_images(batch, {"tgt_sizes": tgt.to(embeds.device)})
+            feats = feats.reshape(len(slices), self.query_num, -1)
+            vision.append(feats)
+            span = bounds[b]
+            if span is None:
+                continue
+            for i, (lo, hi) in enumerate(torch.as_tensor(span).reshape(-1, 2).tolist()):
+                if i < feats.shape[0]:
+                    embeds[b, lo:hi] = feats[i, : hi - lo].to(embeds.dtype)
+        return embeds, vision
+
     # -------------------------------------------------------------- forward
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
                 images: Optional[List[Tuple[torch.Tensor, Any, int, int]]] = None) -> torch.Tensor:

@@ -32,6 +32,9 @@ _ALIASES = {
     "nanovllm.kernels.batched_compress": "fastcache_b200.compress.batched",
     "nanovllm.kernels.kvpress_compressor": "fastcache_b200.compress.kvpress_compat",
     "nanovllm.kernels.minicpm_compressor": "fastcache_b200.compress.ccm",
+    "nanovllm.kernels.fused_compress": "fastcache_b200.compress.batched",
+    "nanovllm.kernels.zero_overhead_compress": "fastcache_b200.compress.batched",
+    "nanovllm.autocompress.kernels": "fastcache_b200.autocompress.kernels",
 }
 
 

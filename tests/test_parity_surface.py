@@ -1,0 +1,141 @@
+"""Names that scripts written against the reference import or call: the async-compression manager,
+the MiniCPM compressor loader, the quantised-cache context, the model unwrapping helper, the
+multimodal merge helpers and the import paths of the helper package."""
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from fastcache_b200 import LLM, SamplingParams
+from fastcache_b200.compress import (KVCacheLinearDecoupleCompressor, MiniCPMKVCompressor, load_minicpm_compressor,
+                                     save_compressor)
+from fastcache_b200.compress.kvpress_compat import get_underlying_model
+from fastcache_b200.compress.quant import QuantizedCacheWrapper
+from fastcache_b200.engine.async_compression import AsyncCompressionManager
+from fastcache_b200.engine.sequence import CompressionState
+from helpers import random_compressor, tiny_llama_config
+from test_vision_cpu import _llava_cfg, _minicpm_cfg
+
+
+def _engine():
+    comp = random_compressor(KVCacheLinearDecoupleCompressor, 2, 64, 4)
+    return LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=512, device="cpu",
+               enforce_eager=True, enable_compression=True, compressor=comp, compression_backend="mlp",
+               compression_pipeline="prefill")
+
+
+def test_async_manager_views_engine_state():
+    llm = _engine()
+    mgr = llm.async_manager
+    assert isinstance(mgr, AsyncCompressionManager) and llm.model_runner._async_manager is mgr
+    from nanovllm.engine.llava_model_runner import AsyncCompressionManager as Aliased
+    assert Aliased is AsyncCompressionManager
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    g = torch.Generator().manual_seed(0)
+    seqs = [llm.add_request(torch.randint(3, 1000, (64,), generator=g).tolist(), sp) for _ in range(2)]
+    assert mgr.get_state(seqs[0].seq_id) is CompressionState.NONE
+    llm.step(apply_compression=False)                       # prefill only
+    assert all(not s.is_compressed and mgr.get_effective_kv_len(s) == 65 for s in seqs)
+    launched = mgr.start_async_compression(seqs)
+    assert launched == [s.seq_id for s in seqs]
+    # no side stream on the CPU: the launch degrades to the synchronous path and is complete at once
+    assert all(mgr.is_compression_complete(s.seq_id) for s in seqs)
+    assert mgr.wait_all_compressions(100.0) and mgr.wait_for_compression(seqs[0].seq_id, 10.0)
+    assert all(mgr.get_state(s.seq_id) is CompressionState.COMPLETED for s in seqs)
+    assert all(mgr.get_effective_kv_len(s) == 16 + 1 for s in seqs)
+    assert mgr.start_async_compression(seqs) == []          # not eligible twice
+    llm.scheduler.block_manager.check_invariants(seqs)
+    while not llm.is_finished():
+        llm.step()
+    mgr.cleanup_seq(seqs[0].seq_id)
+    assert mgr.get_state(seqs[0].seq_id) is CompressionState.NONE
+
+
+def test_load_minicpm_compressor_strict(tmp_path):
+    cfg = SimpleNamespace(num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, hidden_size=32,
+                          head_dim=8)
+    src = MiniCPMKVCompressor(cfg, 5, 2)
+    for p in src.parameters():
+        torch.nn.init.normal_(p, std=0.1)
+    path = os.path.join(tmp_path, "minicpm_mlp.pth")
+    save_compressor(src, path)
+    got = load_minicpm_compressor(path, cfg, compression_factor=5)
+    assert isinstance(got, MiniCPMKVCompressor) and not got.training and got.min_seq_len == 2
+    for (n1, a), (n2, b) in zip(src.state_dict().items(), got.state_dict().items()):
+        assert n1 == n2 and torch.equal(a, b)
+    with pytest.raises(FileNotFoundError):
+        load_minicpm_compressor(os.path.join(tmp_path, "absent.pth"), cfg)
+    with pytest.raises(ValueError):
+        load_minicpm_compressor(path, cfg, compression_factor=4)
+
+
+def test_quantized_cache_context_restores_config():
+    model = SimpleNamespace(config=SimpleNamespace())
+    with QuantizedCacheWrapper(nbits=4)(model) as m:
+        assert m is model and m.config.cache_implementation == "quantized"
+        assert m.config.cache_config == {"backend": "quanto", "nbits": 4}
+    assert not hasattr(model.config, "cache_implementation") and not hasattr(model.config, "cache_config")
+    model.config.cache_implementation = "static"
+    with QuantizedCacheWrapper(2)(model):
+        pass
+    assert model.config.cache_implementation == "static"
+
+
+def test_get_underlying_model_shapes():
+    stack = SimpleNamespace(layers=[1, 2])
+    assert get_underlying_model(SimpleNamespace(language_model=stack)) is stack
+    assert get_underlying_model(SimpleNamespace(language_model=SimpleNamespace(model=stack))) is stack
+    assert get_underlying_model(SimpleNamespace(llm=SimpleNamespace(model=stack))) is stack
+    assert get_underlying_model(SimpleNamespace(model=stack)) is stack
+    with pytest.raises(AttributeError):
+        get_underlying_model(SimpleNamespace(foo=1))
+
+
+def test_llava_merge_helper_positions():
+    llm = LLM(_llava_cfg(), device="cpu", kvcache_block_size=16, num_kvcache_blocks=32, max_model_len=128,
+              enforce_eager=True)
+    model = llm.model_runner.model
+    ids = torch.tensor([5, 6, 500, 7, 8])
+    pos = torch.arange(5)
+    feats = model.get_image_features(torch.rand(1, 3, 56, 56))
+    assert feats.shape[:2] == (1, 16)
+    emb, p2 = model.merge_input_ids_with_image_features(ids, feats, pos)
+    assert emb.shape[0] == 5 + 15 and p2.tolist() == list(range(20))
+    assert torch.equal(emb[2:18], feats[0].to(emb.dtype))
+    text = model.language_model.get_input_embeddings(ids)
+    assert torch.equal(emb[:2], text[:2]) and torch.equal(emb[18:], text[3:])
+    e0, p0 = model.merge_input_ids_with_image_features(torch.tensor([5, 6]), feats, torch.arange(2))
+    assert e0.shape[0] == 2 and p0.tolist() == [0, 1]
+
+
+def test_minicpm_get_vllm_embedding_scatter():
+    llm = LLM(_minicpm_cfg(), device="cpu", kvcache_block_size=16, num_kvcache_blocks=32, max_model_len=256,
+              enforce_eager=True)
+    model = llm.model_runner.model
+    q = model.query_num
+    ids = torch.full((2, 16), 7)
+    slices = [torch.rand(3, 28, 42), torch.rand(3, 42, 28)]
+    data = {"input_ids": ids, "pixel_values": [slices, []],
+            "tgt_sizes": [torch.tensor([[2, 3], [3, 2]]), torch.zeros(0, 2)],
+            "image_bound": [torch.tensor([[1, 1 + q], [8, 8 + q]]), torch.zeros(0, 2)]}
+    emb, vis = model.get_vllm_embedding(data)
+    assert emb.shape[:2] == (2, 16) and vis[0].shape[:2] == (2, q) and vis[1].shape[0] == 0
+    text = model.llm.get_input_embeddings(ids.reshape(-1)).reshape(2, 16, -1)
+    assert torch.equal(emb[1], text[1]) and torch.equal(emb[0, 0], text[0, 0])
+    assert torch.equal(emb[0, 1:1 + q], vis[0][0].to(emb.dtype)) and torch.equal(emb[0, 8:8 + q], vis[0][1].to(emb.dtype))
+
+
+def test_reference_import_paths_resolve():
+    import fastcache_paths
+    from utils_ccm.module_ccm_v11 import (KVCacheCompressionLoss, KVCacheHybridCompressor,  # noqa: F401
+                                          KVCacheLinearDecoupleCompressor as K1)
+    from utils_ccm.utils_compress import press_select, exec_compression_methods, TimeTik  # noqa: F401
+    from utils_ccm.utils_kvcachePool import KVCachePool  # noqa: F401
+    from utils_ccm.utils_schedule_v11 import DynamicScheduler, TimestampManager, GPUMonitor  # noqa: F401
+    from utils_ccm.utils_requests import Request, RequestStatus  # noqa: F401
+    from utils_ccm.utils_profiler import LLaVAIntensityAnalyzer  # noqa: F401
+    from nanovllm.kernels.zero_overhead_compress import ZeroOverheadCompressEngine  # noqa: F401
+    from nanovllm.kernels.fused_compress import FusedCompressor  # noqa: F401
+    assert K1 is KVCacheLinearDecoupleCompressor
+    assert hasattr(fastcache_paths, "REPO_ROOT") and callable(fastcache_paths.ensure_sys_paths)

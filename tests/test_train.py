@@ -53,3 +53,33 @@ def test_finetune_improves_and_checkpoints(tmp_path):
     cfg2 = FinetuneConfig(lr=5e-3, epochs=7, out_dir=str(tmp_path), name="toy", is_continue=True)
     more = finetune_compressor(again, fwd, train, val, cfg2, it_len_of=lambda b: (4, 8))
     assert [r["epoch"] for r in more["history"]] == [6]
+
+
+def test_named_recipes_pick_the_compressor_family(tmp_path):
+    from types import SimpleNamespace
+    from fastcache_b200.compress import KVCacheHybridCompressor
+    from fastcache_b200.compress.train import finetune_com_minicpm, finetune_llava
+
+    torch.manual_seed(0)
+    fwd = _toy()
+    cfg = SimpleNamespace(num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2, hidden_size=16,
+                          head_dim=8)
+    mk = lambda s: [(torch.randn(2, 2, 12, 8, generator=torch.Generator().manual_seed(s + l)),
+                     torch.randn(2, 2, 12, 8, generator=torch.Generator().manual_seed(50 + s + l)))
+                    for l in range(2)]
+    samples = [mk(s) for s in range(5)]
+    comp, out = finetune_com_minicpm(SimpleNamespace(config=cfg), samples, forward_with_kv=fwd,
+                                     it_len_of=lambda b: (0, 12), out_dir=str(tmp_path), num_epochs=2,
+                                     compression_ratio=2, compressor_save_name="mini")
+    assert isinstance(comp, KVCacheHybridCompressor) and not hasattr(comp, "compress_ik")
+    assert len(out["history"]) == 2 and os.path.basename(out["best"]) == "best_mini.pth"
+    comp2, out2 = finetune_llava(SimpleNamespace(config=cfg), samples, forward_with_kv=fwd,
+                                 it_len_of=lambda b: (4, 8), out_dir=str(tmp_path), num_epochs=1,
+                                 compression_ratio=2, compressor_save_name="lv")
+    assert isinstance(comp2, KVCacheLinearDecoupleCompressor) and len(out2["history"]) == 1
+    # resume from the saved file through the load path of the recipe
+    comp3, _ = finetune_llava(SimpleNamespace(config=cfg), samples, forward_with_kv=fwd,
+                              it_len_of=lambda b: (4, 8), out_dir=str(tmp_path), num_epochs=1,
+                              compression_ratio=2, compressor_save_name="lv2",
+                              compressor_load_path=out2["last"])
+    assert comp3.compression_factor == 2

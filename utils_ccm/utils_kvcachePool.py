@@ -1,0 +1,2 @@
+"""`utils_ccm.utils_kvcachePool` of the reference."""
+from fastcache_b200.serving.harness import KVCachePool  # noqa: F401
