@@ -93,9 +93,28 @@ class KVPressCompressor:
         self.calls += 1
         return out
 
+    def forward(self, kv_cache: KV, it_len: Optional[Sequence[int]] = None, **kwargs: Any) -> KV:
+        """Same call under the name the batched compressors use (kvpress_compressor.py:253-289)."""
+        if len(kv_cache) == 0:
+            return kv_cache
+        return self(kv_cache, it_len or (0, 0), kwargs.get("queries"))
+
+    def get_compressed_length(self, original_length: int) -> int:
+        return n_kept_for(original_length, self.compression_ratio)
+
+    @property
+    def compression_factor(self) -> float:
+        return 1.0 / (1.0 - self.compression_ratio)
+
     def get_stats(self) -> Dict[str, Any]:
         return {"method": self.method_name, "compression_ratio": self.compression_ratio, "calls": self.calls,
                 "total_time_ms": self.total_time_ms}
+
+
+def create_kvpress_compressor(method: str = "streaming_llm", compression_factor: float = 5, config: Any = None,
+                              **kwargs: Any) -> KVPressCompressor:
+    """Factor f keeps 1 / f of the rows (kvpress_compressor.py:310-336)."""
+    return KVPressCompressor(method, 1.0 - 1.0 / compression_factor, config, **kwargs)
 
 
 class _DeviceTimer:

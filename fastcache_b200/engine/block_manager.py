@@ -256,3 +256,7 @@ class BlockManager:
                     raise AssertionError(f"block {b}: {n} holders, ref_count {self.blocks[b].ref_count}")
             if set(refs) != self.used_block_ids:
                 raise AssertionError("used set differs from the union of live block tables")
+
+
+# module-level name used by the reference (nanovllm/engine/block_manager.py:9-14)
+compute_hash = BlockManager.compute_hash

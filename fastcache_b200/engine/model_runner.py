@@ -574,6 +574,107 @@ class ModelRunner:
         self._greenctx_info = pool.info
         self._stream_pool = pool
 
+    # ------------------------------------------------- reference runner surface
+    # Method names of the reference's multimodal runner ("kv-cache pipeline"/nanovllm/engine/
+    # llava_model_runner.py:621-629, :756-790, :879-891, :998-1005, :1140-1352).  The policies they
+    # drive (side-stream and layer-chunked compression) live in the engine here, because they
+    # change scheduler and block-manager state; the runner methods forward to the engine that
+    # owns this runner.
+    def _owner(self):
+        mgr = getattr(self, "_async_manager", None)
+        if mgr is None:
+            raise RuntimeError("this runner is not attached to an engine")
+        return mgr.engine
+
+    def preare_block_tables(self, seqs: Seq[Sequence]) -> torch.Tensor:      # (sic) the reference's spelling
+        return self._to_dev(self._block_table_array(seqs), torch.int32)
+
+    prepare_block_tables = preare_block_tables
+
+    def prepare_sample(self, seqs: Seq[Sequence]) -> torch.Tensor:
+        return self._temperatures(seqs)
+
+    @torch.inference_mode()
+    def run_model(self, input_ids: torch.Tensor, positions: torch.Tensor, is_prefill: bool,
+                  pixel_values: Any = None) -> torch.Tensor:
+        """Eager forward to logits on metadata already set by `prepare_prefill` / `prepare_decode`.
+        `pixel_values`: the `images` list the multimodal models take ((pixels, meta, row, count))."""
+        if self.fused_comm is not None:
+            self.fused_comm.begin_forward()
+        if self.is_multimodal:
+            hidden = self.model(input_ids, positions, images=pixel_values)
+        else:
+            hidden = self.model(input_ids, positions)
+        return self.model.compute_logits(hidden)
+
+    def get_blocks_to_free(self, seq_id: int) -> List[int]:
+        """Tail blocks a compressed request no longer needs (empty once the engine has freed them)."""
+        keep = self.get_compressed_block_count(seq_id)
+        if keep <= 0:
+            return []
+        for s in self._owner().scheduler.running:
+            if s.seq_id == seq_id:
+                return list(s.block_table[max(keep, s.kv_num_blocks):])
+        return []
+
+    def reset_graph_vars(self) -> None:
+        for name, t in getattr(self, "graph_vars", {}).items():
+            if name == "slot_mapping":
+                t.fill_(-1)
+            elif name != "logits":
+                t.zero_()
+
+    def start_background_compression(self, seqs: Seq[Sequence], compress_stream: Any = None):
+        """Whole-request compression on a compression stream; returns (start_event, end_event) of the
+        launch, or None when nothing was eligible or the device has no streams."""
+        eng = self._owner()
+        before = set(eng._pending)
+        if compress_stream is not None and compress_stream in self.compress_streams:
+            self._rr = self.compress_streams.index(compress_stream)
+        eng._launch_async(list(seqs))
+        new = [p for sid, p in eng._pending.items() if sid not in before]
+        return (new[0].start_event, new[0].event) if new else None
+
+    def update_decode_overlap_engine(self, layers_per_step: int) -> bool:
+        """Layers compressed per engine step in the decode pipeline.  Refused (False) while chunked
+        compressions are in flight, as in the reference."""
+        layers_per_step = max(1, int(layers_per_step))
+        if layers_per_step == self.decode_layers_per_step:
+            return True
+        mgr = getattr(self, "_async_manager", None)
+        if mgr is not None and any(p.seq.hold for p in mgr.engine._pending.values()):
+            return False
+        if self.compression_backend == "mlp" and self.packed_compressor is None:
+            return False
+        self.decode_layers_per_step = layers_per_step
+        return True
+
+    def get_next_compress_stream(self):
+        return self.next_compress_stream()
+
+    def start_decode_overlap_compression(self, seqs: Seq[Sequence]) -> None:
+        self._owner()._start_chunked(list(seqs))
+
+    def step_decode_overlap_compression(self, seqs: Seq[Sequence]) -> List[Sequence]:
+        """Launch the next layer chunk of every held request; returns those of `seqs` whose last
+        chunk has now been launched (their blocks are freed when they next decode)."""
+        eng = self._owner()
+        held = {s.seq_id for s in seqs if s.hold}
+        eng._advance_chunked()
+        return [s for s in seqs if s.seq_id in held and not s.hold]
+
+    @staticmethod
+    def wait_compression(event: Any) -> None:
+        if event is not None:
+            event.synchronize()
+
+    def clear_compressed_lens(self, seq_ids: Optional[Seq[int]] = None) -> None:
+        if seq_ids is None:
+            self._compressed_lens.clear()
+        else:
+            for sid in seq_ids:
+                self._compressed_lens.pop(sid, None)
+
     def exit(self) -> None:
         self.graphs.clear()
         self.graph_pool = None

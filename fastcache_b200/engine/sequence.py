@@ -144,6 +144,11 @@ class Sequence:
         """Blocks needed for the rows really held in the pool."""
         return -(-self.kv_cache_len // self.block_size)
 
+    def last_block(self) -> List[int]:
+        """Token ids of the last (possibly partial) block, counted over the token ids like `block(i)`."""
+        n = -(-len(self.token_ids) // self.block_size)
+        return self.token_ids[max(0, n - 1) * self.block_size:]
+
     @property
     def last_block_num_tokens(self) -> int:
         return self.kv_cache_len - (self.kv_num_blocks - 1) * self.block_size

@@ -67,6 +67,13 @@ def is_tp_initialized() -> bool:
     return _TP_SIZE > 1
 
 
+def get_tp_device() -> torch.device:
+    """The device this rank computes on (reference nanovllm/utils/tp.py:102-104)."""
+    if torch.cuda.is_available():
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
+
+
 def get_tp_size() -> int:
     return _TP_SIZE
 

@@ -53,6 +53,27 @@ class RequestMetrics:
     decode_start: float = 0.0
     decode_end: float = 0.0
     generated: int = 0
+    # life-cycle stamps of the reference's request struct (utils_ccm/utils_requests.py:17-46)
+    create_time: float = 0.0
+    queue_time: float = 0.0
+    start_time: float = 0.0
+    complete_time: float = 0.0
+
+    @property
+    def wait_time(self) -> float:
+        return self.start_time - self.queue_time if self.start_time > 0 else 0.0
+
+    @property
+    def prefill_time(self) -> float:
+        return self.prefill_end - self.prefill_start if self.prefill_end > 0 else 0.0
+
+    @property
+    def decode_time(self) -> float:
+        return self.decode_end - self.decode_start if self.decode_end > 0 else 0.0
+
+    @property
+    def total_time(self) -> float:
+        return self.complete_time - self.create_time if self.complete_time > 0 else 0.0
 
     @property
     def ttft(self) -> float:
@@ -82,8 +103,49 @@ class Request:
     def input_len(self) -> int:
         return len(self.prompt) if not isinstance(self.prompt, str) else len(self.prompt.split())
 
-    def fail(self, why: str) -> None:
-        self.status, self.error = RequestStatus.FAILED, why
+    def fail(self, why: Any) -> None:
+        self.status, self.error = RequestStatus.FAILED, str(why)
+        self.metrics.complete_time = time.time()
+
+    # life-cycle transitions (utils_ccm/utils_requests.py:64-100)
+    def __post_init__(self) -> None:
+        self.batch_id: Optional[int] = None
+        self.result: Any = None
+        if not self.metrics.create_time:
+            self.metrics.create_time = time.time()
+
+    def enter_queue(self) -> None:
+        self.status = RequestStatus.PENDING
+        self.metrics.queue_time = time.time()
+
+    def start_processing(self) -> None:
+        self.metrics.start_time = time.time()
+
+    def start_prefill(self) -> None:
+        self.status = RequestStatus.PREFILLING
+        self.metrics.prefill_start = time.time()
+
+    def end_prefill(self) -> None:
+        self.metrics.prefill_end = time.time()
+
+    def start_decode(self) -> None:
+        self.status = RequestStatus.DECODING
+        self.metrics.decode_start = time.time()
+
+    def end_decode(self) -> None:
+        self.metrics.decode_end = time.time()
+
+    def complete(self, result: Any = None) -> None:
+        self.status, self.result = RequestStatus.COMPLETED, result
+        self.metrics.complete_time = time.time()
+
+    def to_dict(self) -> dict:
+        m = self.metrics
+        return {"request_id": self.request_id, "batch_id": self.batch_id, "status": self.status.value,
+                "metrics": {"create_time": m.create_time, "queue_time": m.queue_time, "start_time": m.start_time,
+                            "wait_time": m.wait_time, "prefill_time": m.prefill_time,
+                            "decode_time": m.decode_time, "total_time": m.total_time},
+                "error": self.error}
 
 
 @dataclass(order=True)
@@ -130,6 +192,58 @@ class TimestampManager:
         out["normalized_latency"] = out["latency"] / max(1, generated_len)
         return out
 
+    # list-of-ids interface of the reference (utils_ccm/utils_schedule_v11.py:35-193); its stage
+    # names `compress_queueing`, `decoding_queueing`, `decode_start` map to the names above
+    _STAGE_ALIASES = {"compress_queueing": "compress_queueing_start", "decoding_queueing": "decoding_queueing_start",
+                      "decode_start": "decoding_start"}
+
+    def create_request(self, request_id_list: Sequence[Any]) -> None:
+        with self._lock:
+            for rid in request_id_list:
+                self._t.setdefault(rid, {})
+
+    def record_timestamp(self, request_id_list: Sequence[Any], stage: str, timestamps: float) -> None:
+        stage = self._STAGE_ALIASES.get(stage, stage)
+        with self._lock:
+            for rid in request_id_list:
+                if rid in self._t:
+                    self._t[rid][stage] = timestamps
+
+    get_timestamps = get
+
+    def remove_request(self, request_id: Any) -> None:
+        with self._lock:
+            self._t.pop(request_id, None)
+
+    def calculate_stage_durations(self) -> Dict[str, List[float]]:
+        """Per-stage lists over the requests that reached `decoding_finish`."""
+        with self._lock:
+            ids = [rid for rid, t in self._t.items() if "decoding_finish" in t]
+        keys = ("prefill_queue", "prefill_process", "compress_queue", "compress_process", "decoding_queue",
+                "decoding_process", "ttft", "tpot", "latency", "normalized_latency")
+        out: Dict[str, List[float]] = {k: [] for k in keys}
+        out["generated_lens"] = []
+        for rid in ids:
+            n = int(self.get(rid).get("generated_lens") or 1)
+            a = self.analyze(rid, n)
+            for k in keys:
+                out[k].append(a[k])
+            out["generated_lens"].append(n)
+        return out
+
+    @staticmethod
+    def calculate_average_times(durations: Dict[str, List[float]]) -> Dict[str, float]:
+        return {k: (round(sum(v) / len(v), 3) if v else 0) for k, v in durations.items()}
+
+    @staticmethod
+    def calculate_generated_lens(durations: Dict[str, List[float]]) -> int:
+        return int(sum(durations.get("generated_lens", [])))
+
+    def analyze_timestamps(self) -> Tuple[Dict[str, Any], Dict[str, List[float]]]:
+        d = self.calculate_stage_durations()
+        return {"average_times": self.calculate_average_times(d),
+                "total_generated_lens": self.calculate_generated_lens(d)}, d
+
 
 # --------------------------------------------------------------------- GPU monitor
 class GPUMonitor(threading.Thread):
@@ -170,6 +284,39 @@ class GPUMonitor(threading.Thread):
         self.join(timeout=2)
         return self.samples
 
+    # names of the reference's monitor (utils_ccm/utils_schedule_v11.py:242-306)
+    def start_monitoring(self) -> None:
+        if not self.is_alive() and not self._halt.is_set():
+            self.samples.clear()
+            self.start()
+
+    def stop_monitoring(self) -> None:
+        if self.is_alive():
+            self.stop()
+
+    def set_batch_size(self, batch_size: int) -> None:
+        self.batch_size = int(batch_size)
+
+    def accum_state_round(self, state_name: str) -> None:
+        """Count one more round of `state_name` (prefill / compress / decoding) and tag samples with it."""
+        rounds = self.__dict__.setdefault("state_round", {})
+        rounds[state_name] = rounds.get(state_name, 0) + 1
+        self.stage = f"{state_name} {rounds[state_name]}"
+
+    def get_state_round_info(self) -> str:
+        return self.stage if " " in self.stage else "ready -1"
+
+    def check_gpu_stats(self) -> Dict[str, Any]:
+        """The latest sample (empty before the first one)."""
+        return dict(self.samples[-1]) if self.samples else {}
+
+    def get_stats(self) -> Dict[str, List[Any]]:
+        keys = sorted({k for r in self.samples for k in r})
+        return {k: [r.get(k) for r in self.samples] for k in keys}
+
+    def save_stats(self, filename: str) -> None:
+        self.to_csv(filename)
+
     def to_csv(self, path: str) -> None:
         import csv
         keys = sorted({k for r in self.samples for k in r})
@@ -180,6 +327,15 @@ class GPUMonitor(threading.Thread):
 
 
 # -------------------------------------------------------------------- KV cache pool
+@dataclass
+class KVCacheItem:
+    """One request's stored cache with its bookkeeping (utils_ccm/utils_kvcachePool.py:23-30)."""
+    request_id: Any
+    kv_cache: List[Tuple[torch.Tensor, torch.Tensor]]
+    seq_len: int = 0
+    created: float = field(default_factory=time.time)
+
+
 class KVCachePool:
     """Request id -> list of per-layer (K, V) in HF layout [1, H, S, D] (lock protected)."""
 
@@ -207,6 +363,16 @@ class KVCachePool:
         with self._lock:
             return self._pool.get(request_id)
 
+    def get_kvcache(self, request_ids):
+        """One id -> its entry (or None); a list of ids -> list of entries."""
+        if isinstance(request_ids, (list, tuple)):
+            return [self.get(r) for r in request_ids]
+        return self.get(request_ids)
+
+    def release_kvcache(self, request_ids) -> bool:
+        ids = request_ids if isinstance(request_ids, (list, tuple)) else [request_ids]
+        return all([self.release(r) for r in ids])
+
     def pop_kvcache(self, request_id: int):
         with self._lock:
             return self._pool.pop(request_id, None)
@@ -219,6 +385,8 @@ class KVCachePool:
     def clear(self) -> None:
         with self._lock:
             self._pool.clear()
+
+    clear_kvcache = clear
 
     def merge_and_pop(self, request_ids: Sequence[int]):
         """Concatenate the entries of `request_ids` along the batch dim (left-padding to the longest)."""
@@ -293,6 +461,57 @@ class DynamicScheduler:
         with self._lock:
             return len(self._prefill), len(self._decode)
 
+    # interface of the reference's scheduler (utils_ccm/utils_schedule_v11.py:532-803)
+    def add_request(self, request: Any, request_type: str) -> None:
+        """`request.batch` carries the tensors: prefill requests are sized by their prompt length,
+        decoding requests by `batch["request_size"]` (how many sequences the group holds)."""
+        batch = getattr(request, "batch", None) or {}
+        if request_type == "prefill":
+            ids = batch.get("input_ids")
+            self.add_prefill(request, int(ids.shape[1]) if ids is not None else 1)
+        else:
+            self.add_decoding(request, int(batch.get("request_size", 1)))
+
+    def update_priorities(self) -> None:
+        with self._lock:
+            self._reprioritise(self._prefill)
+            self._reprioritise(self._decode)
+
+    @staticmethod
+    def binary_search_last_le(lst: Sequence[float], x: float) -> int:
+        """Index of the last element <= x in an ascending list, -1 if none."""
+        import bisect
+        return bisect.bisect_right(lst, x) - 1
+
+    def adaptive_batch_size(self, queue_type: str, current_performance: float = 0.0, gpu_stats: Any = None) -> int:
+        """Batch cap for the queue.  The reference computes a PID correction and then discards it
+        (`new_size = current_size`); the caps are fixed here as well, and the decode cap counts how many
+        queued groups fit the decoding threshold."""
+        if queue_type == "prefill":
+            return self.max_batch_size
+        with self._lock:
+            sizes = sorted(p.request[1] for p in self._decode)
+        total, n = 0, 0
+        for sz in sizes:
+            if n and total + sz > self.std_batch_threshold_decoding:
+                break
+            total, n = total + sz, n + 1
+        return max(1, n)
+
+    def update_performance(self, metrics: Dict[str, Any]) -> None:
+        win = self.__dict__.setdefault("perf_window", [])
+        win.append(metrics["batch_size"])
+        del win[:-100]
+
+    def get_current_performance(self) -> float:
+        win = self.__dict__.get("perf_window") or []
+        recent = win[-10:]
+        return sum(recent) / len(recent) if recent else 0
+
+    def get_queue_status(self) -> Dict[str, Any]:
+        p, d = self.qsize()
+        return {"prefill_count": p, "decoding_count": d, "current_mode": self.__dict__.get("current_mode", "prefill")}
+
     def _reprioritise(self, heap: List[PrioritizedRequest]) -> None:
         items = [PrioritizedRequest(self._priority(p.request[1], p.request[2]), p.seq, p.request) for p in heap]
         heap[:] = items
@@ -309,6 +528,7 @@ class DynamicScheduler:
                     n = min(self.max_batch_size, len(self._prefill))
                     batch = [heapq.heappop(self._prefill).request[0] for _ in range(n)]
                     self._last_prefill = now
+                    self.current_mode = "prefill"
                     return "prefill", batch
                 if not self._decode:
                     return None, []
@@ -321,6 +541,7 @@ class DynamicScheduler:
                         break
                     batch.append(heapq.heappop(self._decode).request[0])
                     used += size
+                self.current_mode = "decoding"
                 return "decoding", batch
         return None, []
 

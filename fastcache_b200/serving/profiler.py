@@ -112,3 +112,209 @@ class LLaVAIntensityAnalyzer:
             ctx = rows // factor
         out["decode_per_token"] = self.llm.decode(1, ctx + out_tokens // 2)
         return out
+
+
+# ----------------------------------------------------------- tensor-driven interface
+# The reference's analyzers are built from a HuggingFace config and take the step's tensors
+# (utils_ccm/utils_profiler.py:8-160, :294-428, :520-908).  The classes below give that interface on top
+# of the shape-driven cost model above; "theoretical_time" uses the peak passed in (the reference
+# hard-codes the A100's 312 TFLOP/s).
+@dataclass
+class ComputeStats:
+    flops: float = 0
+    memory_read: float = 0
+    memory_write: float = 0
+    batch_size: int = 1
+    seq_length: int = 0
+
+    def __add__(self, other: "ComputeStats") -> "ComputeStats":
+        return ComputeStats(self.flops + other.flops, self.memory_read + other.memory_read,
+                            self.memory_write + other.memory_write, max(self.batch_size, other.batch_size),
+                            max(self.seq_length, other.seq_length))
+
+    @property
+    def total_memory(self) -> float:
+        return self.memory_read + self.memory_write
+
+    @property
+    def compute_intensity(self) -> float:
+        return self.flops / self.total_memory if self.total_memory > 0 else 0
+
+    @property
+    def per_sample_flops(self) -> float:
+        return self.flops / self.batch_size if self.batch_size > 0 else self.flops
+
+    @property
+    def per_sample_memory(self) -> float:
+        return self.total_memory / self.batch_size if self.batch_size > 0 else self.total_memory
+
+    def report(self, phase: str, peak_tflops: float) -> Dict:
+        return {"phase": phase, "batch_size": self.batch_size, "seq_length": self.seq_length, "flops": self.flops,
+                "memory_read": self.memory_read, "memory_write": self.memory_write,
+                "total_memory": self.total_memory, "compute_intensity": self.compute_intensity,
+                "theoretical_time": self.flops / (peak_tflops * 1e12)}
+
+
+def format_number(number: float, base: int = 1024) -> str:
+    units = ["", "K", "M", "G", "T", "P"]
+    i = 0
+    while number >= base and i < len(units) - 1:
+        number, i = number / base, i + 1
+    return f"{number:.2f}{units[i]}"
+
+
+_DTYPE_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "float8_e4m3fn": 1, "int8": 1}
+
+
+class LLMConfigWrapper:
+    """Flat view of a (possibly nested multimodal) HuggingFace config with the fields the cost
+    model needs; unknown attributes fall through to the wrapped config."""
+
+    def __init__(self, config):
+        self.original_config = config
+        text = getattr(config, "text_config", None) or getattr(config, "llm_config", None) or config
+        if isinstance(text, dict):
+            from types import SimpleNamespace
+            text = SimpleNamespace(**text)
+        self.hidden_size = text.hidden_size
+        self.num_attention_heads = text.num_attention_heads
+        self.num_hidden_layers = text.num_hidden_layers
+        self.vocab_size = text.vocab_size
+        self.intermediate_size = getattr(text, "intermediate_size", 4 * text.hidden_size)
+        self.model_type = getattr(text, "model_type", "llama")
+        self.num_key_value_heads = getattr(text, "num_key_value_heads", None) or text.num_attention_heads
+        self.head_dim = getattr(text, "head_dim", None) or text.hidden_size // text.num_attention_heads
+        self.rope_theta = getattr(text, "rope_theta", 10000.0)
+        self.max_position_embeddings = getattr(text, "max_position_embeddings", None)
+        dt = getattr(config, "torch_dtype", None) or getattr(text, "torch_dtype", None) or getattr(config, "dtype", None)
+        self.dtype_size = _DTYPE_BYTES.get(str(dt).replace("torch.", ""), 2)
+
+    @classmethod
+    def from_pretrained(cls, model_name_or_path: str):
+        from ..config import ModelConfig
+        return cls(ModelConfig.from_pretrained(model_name_or_path))
+
+    def __getattr__(self, name: str):
+        return getattr(self.__dict__["original_config"], name)
+
+
+LLMConfig = LLMConfigWrapper
+
+
+class LLaVAConfigWrapper(LLMConfigWrapper):
+    def __init__(self, config):
+        super().__init__(config)
+        vis = getattr(config, "vision_config", None)
+        get = (lambda k, d: vis.get(k, d)) if isinstance(vis, dict) else (lambda k, d: getattr(vis, k, d))
+        self.vision_config = {"hidden_size": get("hidden_size", 1024), "num_hidden_layers": get("num_hidden_layers", 24),
+                              "num_attention_heads": get("num_attention_heads", 16),
+                              "intermediate_size": get("intermediate_size", 4096),
+                              "image_size": get("image_size", 336), "patch_size": get("patch_size", 14)}
+        self.mm_hidden_size = self.hidden_size
+
+
+def _as_wrapper(config, cls=LLMConfigWrapper):
+    if isinstance(config, LLMConfigWrapper):
+        return config
+    if isinstance(config, str):
+        return cls.from_pretrained(config)
+    return cls(config)
+
+
+def _stats(cost: PhaseCost, batch: int, seq: int, write_bytes: float) -> ComputeStats:
+    w = min(write_bytes, cost.bytes)
+    return ComputeStats(cost.flops, cost.bytes - w, w, batch, seq)
+
+
+def _llm_analyze_prefill(self, input_ids, position_ids=None, attention_mask=None) -> Dict:
+    B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
+    c = self.prefill(B, S)
+    out = B * S * (self.kv_bytes_per_token() + self.h * self.b) + B * self.vocab * self.b
+    return _stats(c, B, S, out).report("prefill", self.peak_tflops)
+
+
+def _llm_analyze_decode(self, input_ids, past_key_values, position_ids=None, attention_mask=None, **_) -> Dict:
+    B = 1 if input_ids.dim() == 1 else input_ids.shape[0]
+    ctx = int(past_key_values[0][0].shape[2]) if past_key_values else 0
+    c = self.decode(B, ctx)
+    return _stats(c, B, ctx + 1, B * (self.kv_bytes_per_token() + self.vocab * self.b)).report("decode", self.peak_tflops)
+
+
+def _llm_from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
+    """Build the analyzer from a HuggingFace config, a model directory or a config wrapper."""
+    w = _as_wrapper(config)
+    a = cls(w.hidden_size, w.num_hidden_layers, w.num_attention_heads, w.num_key_value_heads, w.head_dim,
+            w.intermediate_size, w.vocab_size, w.dtype_size, tp)
+    a.config = w
+    a.peak_tflops = peak_tflops
+    return a
+
+
+LLMIntensityAnalyzer.peak_tflops = 1590.0
+LLMIntensityAnalyzer.from_config = classmethod(_llm_from_config)
+LLMIntensityAnalyzer.analyze_prefill = _llm_analyze_prefill
+LLMIntensityAnalyzer.analyze_decode = _llm_analyze_decode
+
+
+def _vision_analyze(self, batch_size: int = 1) -> ComputeStats:
+    c = self.encode(batch_size)
+    return _stats(c, batch_size, self.n, batch_size * self.n * self.h * self.b)
+
+
+VisionEncoderAnalyzer.analyze_vision_encoding = _vision_analyze
+
+
+def _llava_from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
+    w = _as_wrapper(config, LLaVAConfigWrapper)
+    v = w.vision_config
+    n = (v["image_size"] // v["patch_size"]) ** 2 + 1
+    a = cls(LLMIntensityAnalyzer.from_config(w, peak_tflops, tp),
+            VisionEncoderAnalyzer(v["hidden_size"], v["num_hidden_layers"], v["num_attention_heads"],
+                                  v["intermediate_size"], n, v["patch_size"], w.dtype_size), w.hidden_size)
+    a.config = w
+    return a
+
+
+def _llava_analyze_multimodal_prefill(self, input_ids, pixel_values=None, **_) -> Dict:
+    B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
+    total, rows = ComputeStats(batch_size=B), S
+    if pixel_values is not None:
+        n_img = len(pixel_values)
+        total = total + self.vision.analyze_vision_encoding(n_img)
+        p = self.projection(n_img)
+        total = total + _stats(p, n_img, self.vision.n - 1, n_img * (self.vision.n - 1) * self.proj * 2.0)
+        rows = S + self.vision.n - 2           # the placeholder token becomes n - 1 feature rows
+    c = self.llm.prefill(B, rows)
+    total = total + _stats(c, B, rows, B * rows * self.llm.kv_bytes_per_token())
+    return total.report("multimodal_prefill", self.llm.peak_tflops)
+
+
+def _llava_analyze_decode(self, input_ids, past_key_values, **kw) -> Dict:
+    return self.llm.analyze_decode(input_ids, past_key_values, **kw)
+
+
+def _llava_analyze_kv_cache_compression(self, kv_cache, image_len: int, text_len: int,
+                                        compression_factor: int = 2) -> Dict:
+    """Cost of the merge MLPs over a cache given as per-layer (K, V) of shape [B, H, S, D]: each
+    segment of at least `compression_factor` rows is merged, K and V each through a
+    (D f -> D -> D -> D) MLP shared by all heads."""
+    B, H, _, D = kv_cache[0][0].shape
+    b = kv_cache[0][0].element_size()
+    f = compression_factor
+    weights = (D * f * D + 2 * D * D + 3 * D) * b
+    total = ComputeStats(batch_size=B, seq_length=image_len + text_len)
+    for _layer in kv_cache:
+        for seg in (image_len, text_len):
+            if seg < f:
+                continue
+            rows = B * H * (seg // f)
+            one = ComputeStats(2.0 * rows * (D * f * D + 2 * D * D), rows * D * f * b + weights, rows * D * b, B,
+                               image_len + text_len)
+            total = total + one + one           # K and V
+    return total.report("kv_cache_compression", self.llm.peak_tflops)
+
+
+LLaVAIntensityAnalyzer.from_config = classmethod(_llava_from_config)
+LLaVAIntensityAnalyzer.analyze_multimodal_prefill = _llava_analyze_multimodal_prefill
+LLaVAIntensityAnalyzer.analyze_decode = _llava_analyze_decode
+LLaVAIntensityAnalyzer.analyze_kv_cache_compression = _llava_analyze_kv_cache_compression

@@ -99,6 +99,14 @@ class LazyCompressionEngine:
     def step(self):
         return self.llm.step()
 
+    def add_request(self, prompt: Any, sampling_params: Any = None, image: Any = None):
+        if image is None:
+            return self.llm.add_request(prompt, sampling_params)
+        return self.llm.add_request(prompt, sampling_params, image=image)
+
+    def is_finished(self) -> bool:
+        return self.llm.is_finished()
+
     def get_stats(self) -> Dict[str, Any]:
         st, bm = self.llm.stats, self.llm.scheduler.block_manager
         return {"compression_count": st.compressions, "lazy_triggers": st.lazy_triggers,

@@ -16,11 +16,37 @@ import torch
 
 
 @dataclass
+class GreenCtxInfo:
+    """Whether green contexts could be set up, and why not (reference streams.py:12-14)."""
+    available: bool
+    reason: Optional[str] = None
+
+
+@dataclass
 class StreamPool:
     main: Any
     compress: List[Any]
     greenctx: bool = False
     info: Dict[str, Any] = field(default_factory=dict)
+    _next: int = 0
+
+    @property
+    def streams(self) -> List[Any]:
+        return list(self.compress)
+
+    def next_stream(self) -> Any:
+        """Compression streams in round-robin order; the current stream when there is none."""
+        if not self.compress:
+            return torch.cuda.current_stream() if torch.cuda.is_available() else None
+        s = self.compress[self._next % len(self.compress)]
+        self._next = (self._next + 1) % len(self.compress)
+        return s
+
+    @property
+    def greenctx_info(self) -> GreenCtxInfo:
+        if self.greenctx:
+            return GreenCtxInfo(True)
+        return GreenCtxInfo(False, str(self.info.get("fallback", "not requested")))
 
 
 def try_create_greenctx_streams(device: torch.device, compress_ratio: float, n_compress: int = 1

@@ -139,3 +139,90 @@ def test_reference_import_paths_resolve():
     from nanovllm.kernels.fused_compress import FusedCompressor  # noqa: F401
     assert K1 is KVCacheLinearDecoupleCompressor
     assert hasattr(fastcache_paths, "REPO_ROOT") and callable(fastcache_paths.ensure_sys_paths)
+
+
+def test_runner_surface_drives_chunked_compression():
+    comp = random_compressor(KVCacheLinearDecoupleCompressor, 2, 64, 4)
+    llm = LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=512, device="cpu",
+              enforce_eager=True, enable_compression=True, compressor=comp, compression_backend="mlp",
+              compression_pipeline="decode", decode_layers_per_step=1)
+    r = llm.model_runner
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    g = torch.Generator().manual_seed(3)
+    seqs = [llm.add_request(torch.randint(3, 1000, (64,), generator=g).tolist(), sp) for _ in range(2)]
+    llm.step(apply_compression=False)
+    assert r.preare_block_tables(seqs).shape == (2, 4) and r.prepare_sample(seqs).tolist() == [0.0, 0.0]
+    assert r.get_compressed_block_count(seqs[0].seq_id) == 0 and r.get_blocks_to_free(seqs[0].seq_id) == []
+    r.start_decode_overlap_compression(seqs)
+    assert all(s.hold for s in seqs) and not r.update_decode_overlap_engine(2)     # refused while in flight
+    assert r.step_decode_overlap_compression(seqs) == []                           # layer 0 of 2
+    done = r.step_decode_overlap_compression(seqs)
+    assert done == seqs and all(not s.hold and s.kv_cache_len == 17 for s in seqs)
+    llm.async_manager.finalize(seqs)
+    assert all(len(s.block_table) == 2 for s in seqs)
+    llm.scheduler.block_manager.check_invariants(seqs)
+    assert r.update_decode_overlap_engine(2) and r.decode_layers_per_step == 2
+    r.clear_compressed_lens([seqs[0].seq_id])
+    assert r.get_compressed_block_count(seqs[0].seq_id) == 0 and r.get_compressed_block_count(seqs[1].seq_id) == 1
+    while not llm.is_finished():
+        llm.step()
+    # run_model: logits from metadata prepared by the caller
+    seq = llm.add_request([5, 6, 7, 8], sp)
+    llm.scheduler.schedule()
+    ids, pos, _ = r.prepare_prefill([seq])
+    assert r.run_model(ids, pos, True).shape[-1] == 1024
+
+
+def test_harness_reference_method_names():
+    import fastcache_b200.serving.harness as h
+    from fastcache_b200.compress.kvpress_compat import create_kvpress_compressor
+    from fastcache_b200.engine.block_manager import BlockManager, compute_hash
+    from fastcache_b200.utils.streams import StreamPool
+
+    r = h.Request(1, [1, 2, 3])
+    for step in (r.enter_queue, r.start_processing, r.start_prefill, r.end_prefill, r.start_decode, r.end_decode):
+        step()
+    r.complete("ok")
+    d = r.to_dict()
+    assert d["status"] == "completed" and d["metrics"]["total_time"] >= 0 and r.result == "ok"
+    t = h.TimestampManager()
+    t.create_request(["a", "b"])
+    for i, st in enumerate(["prefill_queueing_start", "prefill_start", "prefill_finish", "compress_queueing",
+                            "compress_start", "compress_finish", "decoding_queueing", "decode_start",
+                            "decoding_finish"]):
+        t.record_timestamp(["a"], st, float(i))
+    t.record_timestamp(["a"], "generated_lens", 4)
+    summary, durations = t.analyze_timestamps()
+    assert summary["total_generated_lens"] == 4 and summary["average_times"]["ttft"] == 2.0
+    assert durations["tpot"] == [0.25] and t.get_timestamps("b") == {}
+    t.remove_request("a")
+    assert t.analyze_timestamps()[0]["total_generated_lens"] == 0
+    pool = h.KVCachePool()
+    kv = [(torch.zeros(2, 1, 3, 4), torch.zeros(2, 1, 3, 4))]
+    pool.store_kvcache([7, 8], kv)
+    assert pool.get_kvcache(7)[0][0].shape == (1, 1, 3, 4) and len(pool.get_kvcache([7, 8])) == 2
+    assert pool.release_kvcache([7]) and not pool.release_kvcache(7)
+    pool.clear_kvcache()
+    assert pool.get_stats()["entries"] == 0
+    sch = h.DynamicScheduler(max_batch_size=2, std_batch_threshold_decoding=5, max_wait_time=0.0)
+    from types import SimpleNamespace as NS
+    sch.add_request(NS(batch={"input_ids": torch.zeros(1, 9)}), "prefill")
+    sch.add_request(NS(batch={"request_size": 3}), "decoding")
+    sch.add_request(NS(batch={"request_size": 3}), "decoding")
+    assert sch.get_queue_status()["prefill_count"] == 1 and sch.adaptive_batch_size("decoding") == 1
+    assert sch.binary_search_last_le([1, 2, 5], 3) == 1 and sch.binary_search_last_le([4], 3) == -1
+    sch.update_performance({"batch_size": 4})
+    assert sch.get_current_performance() == 4
+    kind, batch = sch.select_batch()
+    assert kind == "prefill" and sch.get_queue_status()["current_mode"] == "prefill"
+    mon = h.GPUMonitor(period=0.01)
+    mon.accum_state_round("prefill")
+    mon.accum_state_round("prefill")
+    assert mon.get_state_round_info() == "prefill 2" and mon.check_gpu_stats() == {}
+    c = create_kvpress_compressor("knorm", 4)
+    assert abs(c.compression_factor - 4) < 1e-9 and c.get_compressed_length(100) == 25
+    out = c.forward([(torch.randn(1, 2, 16, 8), torch.randn(1, 2, 16, 8))])
+    assert out[0][0].shape == (1, 2, 4, 8)
+    assert compute_hash([1, 2, 3], 5) == BlockManager.compute_hash([1, 2, 3], 5)
+    sp_ = StreamPool(None, [])
+    assert sp_.streams == [] and not sp_.greenctx_info.available
