@@ -22,6 +22,10 @@ class CalibrationData:
     decode_scale: float = 1.0
     compress_scale: Dict[str, float] = field(default_factory=dict)
     samples: int = 0
+    # raw measurements, keyed "batch,seq_len" and "method,seq_len,batch" (the keys of the
+    # reference's JSON file, cost_model.py:45-84); the cost model prefers an exact hit over its formula
+    decode_measurements: Dict[str, float] = field(default_factory=dict)
+    compress_measurements: Dict[str, float] = field(default_factory=dict)
 
     def save(self, path: str) -> None:
         with open(path, "w") as fh:
@@ -30,7 +34,15 @@ class CalibrationData:
     @classmethod
     def load(cls, path: str) -> "CalibrationData":
         with open(path) as fh:
-            return cls(**json.load(fh))
+            blob = json.load(fh)
+        known = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in blob.items() if k in known})
+
+    def add_decode_measurement(self, batch_size: int, seq_len: int, latency_ms: float) -> None:
+        self.decode_measurements[f"{batch_size},{seq_len}"] = float(latency_ms)
+
+    def add_compress_measurement(self, method: str, seq_len: int, batch_size: int, latency_ms: float) -> None:
+        self.compress_measurements[f"{method},{seq_len},{batch_size}"] = float(latency_ms)
 
     def update_decode(self, predicted_ms: float, measured_ms: float, alpha: float = 0.2) -> None:
         if predicted_ms > 0:
@@ -53,11 +65,17 @@ class CostModel:
         s = w.seq_len if seq_len is None else seq_len
         if w.avg_decode_latency_ms is not None and seq_len is None:
             return w.avg_decode_latency_ms
+        hit = self.cal.decode_measurements.get(f"{w.batch_size},{s}")
+        if hit is not None:
+            return hit
         return self.cal.decode_scale * self.hw.estimate_decode_latency_ms(
             w.batch_size, s, w.num_layers, w.num_kv_heads, w.head_dim, w.hidden_size)
 
     def compress_latency_ms(self, p: CompressMethodProfile, w: WorkloadContext) -> float:
         """All layers, K and V, whole batch."""
+        hit = self.cal.compress_measurements.get(f"{p.name},{w.seq_len},{w.batch_size}")
+        if hit is not None:
+            return hit
         rows = float(w.batch_size) * w.seq_len * w.num_kv_heads
         units = rows * w.num_layers * 2
         t_mem = units * max(p.bytes_per_row, 2.0 * w.head_dim) / max(self.hw.memory_bandwidth_gbps * 1e9, 1.0)
@@ -70,6 +88,37 @@ class CostModel:
             t = t_mem + t_cmp
         launch = 0.01 * (1 if p.compute_type is not ComputeType.MIXED else 3)
         return self.cal.compress_scale.get(p.name, 1.0) * (t * 1e3 + launch)
+
+    # names of the reference's model (cost_model.py:172-300)
+    def estimate_decode_latency(self, workload: WorkloadContext, compressed: bool = False,
+                                compression_ratio: float = 1.0) -> float:
+        s = workload.seq_len
+        if compressed and compression_ratio > 1.0:
+            s = max(1, int(s / compression_ratio))
+        return self.decode_latency_ms(workload, s)
+
+    def estimate_compress_latency(self, method: str, workload: WorkloadContext) -> float:
+        return self.compress_latency_ms(get_profile(method), workload)
+
+    def estimate_total_time(self, workload: WorkloadContext, method: Optional[str] = None,
+                            async_mode: bool = False) -> Tuple[float, Dict[str, float]]:
+        """(total ms, breakdown).  Asynchronous compression hides the share of its time that the
+        method's profile says can run beside decode."""
+        n = int(workload.avg_output_len or workload.expected_output_len)
+        if method is None:
+            t = self.total_time_ms(None, workload)
+            return t, {"compress_ms": 0.0, "decode_ms": t, "output_tokens": n, "overlap": 0.0}
+        p = get_profile(method)
+        overlap = 0.0
+        if async_mode:
+            mem_bound = self.hw.is_decode_memory_bound(workload.batch_size, workload.seq_len, workload.num_layers,
+                                                       workload.num_kv_heads, workload.head_dim,
+                                                       workload.hidden_size)
+            overlap = 0.8 * p.decode_compatibility if p.can_overlap_with_decode(mem_bound) else 0.0
+        t_c = self.compress_latency_ms(p, workload)
+        total = self.total_time_ms(p, workload, overlap)
+        return total, {"compress_ms": t_c, "exposed_compress_ms": (1.0 - overlap) * t_c,
+                       "decode_ms": total - (1.0 - overlap) * t_c, "output_tokens": n, "overlap": overlap}
 
     # -------------------------------------------------------------- totals
     def total_time_ms(self, p: Optional[CompressMethodProfile], w: WorkloadContext, overlap: float = 0.0

@@ -49,6 +49,12 @@ class AsyncCompressionHandle:
     def is_done(self) -> bool:
         return self._started and (self._event is None or self._event.query())
 
+    is_ready = is_done
+
+    def get_result(self) -> Any:
+        """The result if the work has finished, else None (never blocks)."""
+        return self._result if self.is_done() else None
+
     def wait(self) -> Any:
         if not self._started:
             self.start()
@@ -90,6 +96,47 @@ class AutoCompressManager:
         sm = get_stream_manager()
         return AsyncCompressionHandle(lambda: self.method.compress(kv_cache, **ctx), sm.compress).start()
 
+    # argument-style interface of the reference (integration.py:93-210)
+    def get_plan(self, batch_size: int, seq_len: int, expected_output_len: int = 100, num_layers: int = 32,
+                 num_kv_heads: int = 8, head_dim: int = 128) -> ExecutionPlan:
+        return self.plan(WorkloadContext(batch_size=batch_size, seq_len=seq_len,
+                                         expected_output_len=expected_output_len, num_layers=num_layers,
+                                         num_kv_heads=num_kv_heads, head_dim=head_dim))
+
+    def should_compress(self, batch_size: int, seq_len: int, expected_output_len: int = 100) -> bool:
+        plan = self.get_plan(batch_size, seq_len, expected_output_len)
+        return plan.should_compress and plan.estimated_speedup >= self.config.min_speedup
+
+    def execute_sync(self, kv_cache, compressor: Any = None, **kwargs):
+        """Run `compressor` (default: this manager's method) on the current stream."""
+        fn = compressor if compressor is not None else self.method.compress
+        self.stats["compressed"] += 1
+        return fn(kv_cache, **kwargs)
+
+    def execute_async(self, kv_cache, compressor: Any = None, chunk_size: int = 4,
+                      callback: Optional[Callable[[Any], None]] = None, **kwargs) -> AsyncCompressionHandle:
+        """Queue the compression on the compression stream; `callback(result)` runs on the host once
+        the work is queued (the device-side completion is what `wait()` joins).  `chunk_size` is taken
+        for callers that pass it: layer chunking belongs to the engine's decode pipeline."""
+        fn = compressor if compressor is not None else self.method.compress
+
+        def work():
+            out = fn(kv_cache, **kwargs)
+            if callback is not None:
+                callback(out)
+            return out
+
+        self.stats["compressed"] += 1
+        return AsyncCompressionHandle(work, get_stream_manager().compress).start()
+
+    def get_statistics(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = dict(self.stats)
+        out["method"] = self.config.method
+        if self.last_plan is not None:
+            out["last_speedup"] = self.last_plan.estimated_speedup
+            out["last_timing"] = self.last_plan.timing.name
+        return out
+
 
 class AdaptiveCompressionWrapper:
     """Wraps a compressor callable: compresses only when the plan predicts a gain."""
@@ -105,6 +152,20 @@ class AdaptiveCompressionWrapper:
                             num_kv_heads=k0.shape[1], head_dim=k0.shape[3], **self.defaults)
         out, _ = self.manager.maybe_compress(kv_cache, w, it_len=it_len, **kw)
         return out
+
+    def compress(self, kv_cache, batch_size: Optional[int] = None, seq_len: Optional[int] = None,
+                 expected_output_len: int = 100, **kwargs):
+        """Same decision with the workload stated by the caller (sizes default to the cache's)."""
+        k0 = kv_cache[0][0]
+        w = WorkloadContext(batch_size=batch_size or k0.shape[0], seq_len=seq_len or k0.shape[2],
+                            expected_output_len=expected_output_len, num_layers=len(kv_cache),
+                            num_kv_heads=k0.shape[1], head_dim=k0.shape[3],
+                            **{k: v for k, v in self.defaults.items() if k != "expected_output_len"})
+        out, _ = self.manager.maybe_compress(kv_cache, w, **kwargs)
+        return out
+
+    def get_last_plan(self) -> Optional[ExecutionPlan]:
+        return self.manager.last_plan
 
 
 class _Callable(CompressionMethod):

@@ -50,6 +50,21 @@ class TileLangKernelGenerator:
     def get_quantize_kernels(self) -> Tuple[Callable, Callable]:
         return quant.quantize, quant.dequantize
 
+    # `generate_*` names of the reference (kernels.py:99-422): nothing is generated at run time here,
+    # each returns the same ahead-of-time kernel as the `get_*` accessor
+    def generate_mlp_compress_kernel(self, *shape_hints, **kw) -> Callable:
+        return self.get_mlp_kernel()
+
+    def generate_sparse_gather_kernel(self, *shape_hints, **kw) -> Callable:
+        return self.get_sparse_gather_kernel()
+
+    def generate_quantize_kernel(self, bits: int = 8, group_size: int = 128, **kw) -> Callable:
+        mode = {8: "int8", 4: "int4"}[bits]
+        return lambda x: quant.quantize(x, mode, group_size)
+
+    def generate_dequantize_kernel(self, bits: int = 8, **kw) -> Callable:
+        return quant.dequantize
+
 
 _GEN = None
 

@@ -39,6 +39,25 @@ class CompressionMethod(ABC):
     def output_len(self, seq_len: int) -> int:
         return self.profile.get_output_seq_len(seq_len) if self.profile is not None else seq_len
 
+    def get_optimal_timing(self, workload: Any, hw_profile: Any) -> "ExecutionTiming":
+        """When to run relative to prefill and decode (reference methods.py:80-110): methods that
+        need attention scores run inside prefill when they are cheap (under 1 ms), otherwise after
+        it; the others overlap with decode when decode is memory-bound and the profile allows it."""
+        from .cost_model import CostModel
+        from .execution import ExecutionTiming
+        p = self.profile
+        if p is None:
+            return ExecutionTiming.AFTER_PREFILL
+        if p.requires_attention:
+            cheap = CostModel(hw_profile).compress_latency_ms(p, workload) < 1.0
+            return ExecutionTiming.INLINE_PREFILL if cheap else ExecutionTiming.AFTER_PREFILL
+        mem_bound = hw_profile.is_decode_memory_bound(workload.batch_size, workload.seq_len, workload.num_layers,
+                                                      workload.num_kv_heads, workload.head_dim,
+                                                      workload.hidden_size)
+        if p.can_overlap_with_decode(mem_bound) and p.decode_compatibility >= 0.5:
+            return ExecutionTiming.ASYNC_DECODE
+        return ExecutionTiming.AFTER_PREFILL
+
 
 class MLPCompressionMethod(CompressionMethod):
     """CCM merge: a trained compressor module folds f rows into one."""
@@ -54,6 +73,20 @@ class MLPCompressionMethod(CompressionMethod):
         if self.compressor is None:
             raise RuntimeError("MLPCompressionMethod needs a compressor module")
         return self.compressor(kv_cache, it_len=list(it_len))
+
+    def get_optimal_timing(self, workload: Any, hw_profile: Any) -> "ExecutionTiming":
+        """Small batches compress right after prefill (the merge GEMMs are too small to be worth a
+        second stream); from batch 4 with memory-bound decode, or batch 8, overlap with decode
+        (reference methods.py:200-230)."""
+        from .execution import ExecutionTiming
+        if workload.batch_size < 4:
+            return ExecutionTiming.AFTER_PREFILL
+        mem_bound = hw_profile.is_decode_memory_bound(workload.batch_size, workload.seq_len, workload.num_layers,
+                                                      workload.num_kv_heads, workload.head_dim,
+                                                      workload.hidden_size)
+        if mem_bound or workload.batch_size >= 8:
+            return ExecutionTiming.ASYNC_DECODE
+        return ExecutionTiming.AFTER_PREFILL
 
 
 class KVPressMethod(CompressionMethod):
@@ -129,6 +162,12 @@ class QuantizationMethod(CompressionMethod):
     def decompress(self, packed) -> KV:
         return [(self.dequantize(k), self.dequantize(v)) for k, v in packed]
 
+    def get_optimal_timing(self, workload: Any, hw_profile: Any) -> "ExecutionTiming":
+        """Quantisation streams the cache once: after prefill for short prompts, layer by layer
+        beside decode for long ones (reference methods.py:759-790)."""
+        from .execution import ExecutionTiming
+        return ExecutionTiming.AFTER_PREFILL if workload.seq_len < 1024 else ExecutionTiming.ASYNC_DECODE
+
 
 class MethodRegistry:
     _factories: Dict[str, Any] = {}
@@ -152,6 +191,10 @@ class MethodRegistry:
         if name in ("int8_quant", "int4_quant"):
             return QuantizationMethod(name.split("_")[0], **kw)
         raise KeyError(f"unknown compression method {name!r}")
+
+    @classmethod
+    def list_methods(cls) -> List[str]:
+        return cls.names()
 
     @classmethod
     def names(cls) -> List[str]:

@@ -88,3 +88,78 @@ def test_controller_dual_batch_choice():
     picks = [c.decide_batch_type(waiting=10, running=10) for _ in range(16)]
     assert "decode" in picks and "prefill" in picks
     assert c.decide_batch_type(waiting=100, running=10) == "prefill"
+
+
+def test_reference_named_planning_surface(tmp_path):
+    """Factories, step-wise executor, measurement-keyed calibration, timing rules and the
+    argument-style manager calls that scripts written against the reference use."""
+    import torch
+    from fastcache_b200.autocompress import (AutoCompressManager, CompressionConfig, WorkloadContext,
+                                             AdaptiveCompressionWrapper)
+    from fastcache_b200.autocompress.context import get_hardware_profile
+    from fastcache_b200.autocompress.cost_model import CalibrationData, CostModel
+    from fastcache_b200.autocompress.execution import (ChunkingConfig, ExecutionPlan, ExecutionTiming,
+                                                       PipelineExecutor, StepType, StreamManager)
+    from fastcache_b200.autocompress.kernels import TileLangKernelGenerator
+    from fastcache_b200.autocompress.methods import MethodRegistry, get_method
+
+    plan = ExecutionPlan.create_async_plan("mlp", 3.0, 1.2, chunk_size=8, num_layers=36)
+    assert plan.chunking.num_chunks == 5 and plan.is_valid() and "5 x 8 layers" in plan.summary()
+    assert [s.type for s in plan.to_schedule()].count(StepType.COMPRESS_CHUNK) == 5
+    assert ExecutionPlan.create_sync_plan("mlp", 1.0, 0.9).is_valid() is False
+    assert ExecutionPlan.create_inline_plan("snapkv", 0.5, 1.1).timing is ExecutionTiming.INLINE_PREFILL
+    none = ExecutionPlan.create_no_compress_plan()
+    assert not none.should_compress and [s.type for s in none.steps] == [StepType.PREFILL, StepType.DECODE]
+    assert ChunkingConfig.create(30, 4).num_chunks == 8 and ChunkingConfig.create(30, 4).chunk_size == 4
+    seen = []
+    ex = PipelineExecutor()
+    ex.register_callback(StepType.COMPRESS_CHUNK, lambda st: seen.append(st.chunk))
+    ex.register_callback(StepType.FREE_BLOCKS, lambda st: 1 / 0)
+    ex.set_plan(plan)
+    assert ex.execute_all() is False and seen == [0, 1, 2, 3, 4]
+    st = ex.get_statistics()
+    assert st["total_steps"] == len(plan.steps) and len(st["warnings"]) == 1
+    sm = StreamManager()
+    sm.initialize()
+    assert sm.get_main_stream() is sm.main and sm.get_compress_stream() is sm.compress
+    sm.synchronize_compress_to_main()
+
+    hw = get_hardware_profile("B200")
+    cal = CalibrationData(gpu_name="B200")
+    cal.add_decode_measurement(8, 1024, 7.5)
+    cal.add_compress_measurement("mlp", 1024, 8, 2.25)
+    path = str(tmp_path / "cal.json")
+    cal.save(path)
+    cm = CostModel(hw, CalibrationData.load(path))
+    w = WorkloadContext(batch_size=8, seq_len=1024, expected_output_len=128)
+    assert cm.estimate_decode_latency(w) == 7.5 and cm.estimate_compress_latency("mlp", w) == 2.25
+    assert cm.estimate_decode_latency(w, compressed=True, compression_ratio=4.0) < 7.5
+    total, parts = cm.estimate_total_time(w, "mlp", async_mode=True)
+    base, _ = cm.estimate_total_time(w)
+    assert parts["compress_ms"] == 2.25 and 0.0 <= parts["overlap"] <= 1.0 and total < base
+
+    small = WorkloadContext(batch_size=2, seq_len=2048)
+    big = WorkloadContext(batch_size=16, seq_len=2048)
+    assert get_method("mlp").get_optimal_timing(small, hw) is ExecutionTiming.AFTER_PREFILL
+    assert get_method("mlp").get_optimal_timing(big, hw) is ExecutionTiming.ASYNC_DECODE
+    assert get_method("snapkv").get_optimal_timing(big, hw) in (ExecutionTiming.INLINE_PREFILL,
+                                                                ExecutionTiming.AFTER_PREFILL)
+    assert get_method("quant_int8").get_optimal_timing(small, hw) is ExecutionTiming.ASYNC_DECODE
+    assert "mlp" in MethodRegistry.list_methods()
+
+    mgr = AutoCompressManager(CompressionConfig(method="knorm", compression_ratio=0.5), hardware=hw)
+    plan2 = mgr.get_plan(16, 4096, 512)
+    assert isinstance(mgr.should_compress(16, 4096, 512), bool) and plan2 is not None
+    kv = [(torch.randn(1, 2, 32, 8), torch.randn(1, 2, 32, 8))]
+    assert mgr.execute_sync(kv)[0][0].shape[2] == 16
+    got = []
+    h = mgr.execute_async(kv, callback=got.append)
+    assert h.is_ready() and h.get_result()[0][0].shape[2] == 16 and len(got) == 1
+    assert mgr.get_statistics()["compressed"] == 2
+    wrap = AdaptiveCompressionWrapper(lambda kv_, it_len=(0, 0): kv_)
+    assert wrap.compress(kv, expected_output_len=4) is not None and wrap.get_last_plan() is not None
+    gen = TileLangKernelGenerator()
+    q = gen.generate_quantize_kernel(8)(torch.randn(4, 128))
+    assert torch.allclose(gen.generate_dequantize_kernel(8)(q), gen.generate_dequantize_kernel()(q))
+    assert gen.generate_sparse_gather_kernel()(torch.arange(6.).reshape(3, 2), torch.tensor([2, 0])).tolist() == \
+        [[4.0, 5.0], [0.0, 1.0]]
