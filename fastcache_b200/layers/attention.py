@@ -56,3 +56,20 @@ class Attention(nn.Module):
             o = ops.decode_attention(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens,
                                      self.scale, ctx.attn_workspace)
         return o.reshape(-1, self.num_heads * self.head_dim)
+
+
+def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  slot_mapping: torch.Tensor) -> None:
+    """Scatter new K / V rows `[T, Hkv, D]` into the paged pool `[blocks, Hkv, block, D]` by slot
+    (slot = block * block_size + offset; negative slots are skipped).
+
+    The reference launches a Triton kernel for this (nanovllm/layers/attention.py:10-39).  The
+    engine here never stores on its own: the rows are written by the fused rope / q-k-norm / store
+    kernel.  This function is the stand-alone form for callers that fill a pool themselves (tests,
+    cache import); it is index arithmetic plus two indexed copies on whatever device the pool is on."""
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    bs = k_cache.shape[2]
+    blk, off = slots // bs, slots % bs
+    k_cache[blk, :, off] = key[valid].to(k_cache.dtype)
+    v_cache[blk, :, off] = value[valid].to(v_cache.dtype)

@@ -21,6 +21,13 @@ class RMSNorm(nn.Module):
             return ops.rms_norm(x, self.weight, self.eps)
         return ops.add_rms_norm(x, residual, self.weight, self.eps)
 
+    # the two halves of `forward` under the reference's names (nanovllm/layers/layernorm.py:17-41)
+    def rms_forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rms_norm(x, self.weight, self.eps)
+
+    def add_rms_forward(self, x: torch.Tensor, residual: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        return ops.add_rms_norm(x, residual, self.weight, self.eps)
+
 
 class LayerNorm(nn.Module):
     def __init__(self, hidden_size: int, eps: float = 1e-5):

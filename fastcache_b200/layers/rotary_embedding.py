@@ -55,6 +55,12 @@ class RotaryEmbedding(nn.Module):
         return q, k
 
 
+def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half (neox) rotation of `x [..., D]` by `cos`, `sin` `[..., D / 2]`, computed in fp32
+    (nanovllm/layers/rotary_embedding.py:7-17)."""
+    return ref._rotate(x.float(), cos.float(), sin.float()).to(x.dtype)
+
+
 _ROPE_CACHE: dict = {}
 
 

@@ -16,7 +16,7 @@ import torch
 from torch import nn
 
 from ..config import ModelConfig
-from .llama import LlamaForCausalLM
+from .llama import LlamaAttention, LlamaDecoderLayer, LlamaForCausalLM, LlamaMLP, LlamaModel  # noqa: F401
 from .vision import (CLIP_MEAN, CLIP_STD, CLIPVisionTower, LlavaProjector, clip_vision_shapes, resize_normalize,
                      to_chw_float)
 
@@ -115,3 +115,46 @@ class LlavaForConditionalGeneration(nn.Module):
         for k, shp in LlamaForCausalLM.hf_weight_shapes(cfg.text_config).items():
             s["language_model." + k] = shp
         return s
+
+
+# ------------------------------------------------------------ reference names
+# Classes of the reference's module (nanovllm/models/llava.py:28-199) -> the vision classes here.
+from . import vision as _v  # noqa: E402
+
+CLIPVisionEmbeddings = _v._CLIPEmbeddings
+CLIPAttention = _v.VisionAttention
+CLIPMLP = _v.VisionMLP
+CLIPEncoderLayer = _v.VisionLayer
+CLIPEncoder = _v._Encoder
+CLIPVisionTransformer = _v._CLIPVisionModel
+CLIPVisionModel = CLIPVisionTower
+LlavaMultiModalProjector = LlavaProjector
+
+
+class LlavaConfig:
+    """Flat view of a LLaVA HuggingFace config (nanovllm/models/llava.py:410-437)."""
+
+    def __init__(self, hf_config):
+        text, vis = hf_config.text_config, _vision_cfg(hf_config)
+        self.text_config, self.vision_config = text, vis
+        self.vocab_size = text.vocab_size
+        self.hidden_size = text.hidden_size
+        self.num_hidden_layers = text.num_hidden_layers
+        self.num_attention_heads = text.num_attention_heads
+        self.num_key_value_heads = getattr(text, "num_key_value_heads", None) or text.num_attention_heads
+        self.intermediate_size = text.intermediate_size
+        self.rms_norm_eps = getattr(text, "rms_norm_eps", 1e-6)
+        self.max_position_embeddings = getattr(text, "max_position_embeddings", 4096)
+        self.rope_theta = getattr(text, "rope_theta", 10000.0)
+        self.head_dim = getattr(text, "head_dim", None) or self.hidden_size // self.num_attention_heads
+        self.vision_hidden_size = vis.hidden_size
+        self.image_size, self.patch_size = vis.image_size, vis.patch_size
+        self.num_channels = getattr(vis, "num_channels", 3)
+        self.image_token_len = (self.image_size // self.patch_size) ** 2
+
+
+def get_llava_weight_mapping() -> Dict[str, str]:
+    """Checkpoint prefix -> module prefix for both HuggingFace layouts of LLaVA-1.5.  (The reference
+    returns a partial identity table, nanovllm/models/llava.py:595-611; the loader here works from
+    prefixes and `packed_modules_mapping`.)"""
+    return dict(LlavaForConditionalGeneration.checkpoint_prefix_map)

@@ -16,7 +16,7 @@ import torch
 from torch import nn
 
 from ..config import ModelConfig
-from .qwen3 import Qwen2ForCausalLM
+from .qwen3 import Qwen2Attention, Qwen2DecoderLayer, Qwen2ForCausalLM, Qwen2MLP, Qwen2Model  # noqa: F401
 from .vision import (SIGLIP_MEAN, SIGLIP_STD, Resampler, SiglipVisionTower, resampler_shapes, resize_normalize,
                      siglip_vision_shapes, to_chw_float)
 
@@ -157,6 +157,19 @@ class MiniCPMForConditionalGeneration(nn.Module):
             mask[idx, : h * w] = True
         return feats, mask
 
+    def load_vision_modules(self, hf_model: Any) -> None:
+        """Copy the vision tower and resampler weights out of a loaded HuggingFace MiniCPM-V model.
+        The reference adopts the HF modules themselves (nanovllm/models/minicpm.py:329-340); here the
+        native modules keep running and only take the tensors, so the sm_100a kernels stay in use."""
+        for name in ("vpm", "resampler"):
+            src = getattr(hf_model, name).state_dict()
+            dst = getattr(self, name)
+            own = dst.state_dict()
+            take = {k: v.to(own[k].dtype).reshape(own[k].shape) for k, v in src.items()
+                    if k in own and v.numel() == own[k].numel()}
+            dst.load_state_dict(take, strict=False)
+        self.finalize_weights()
+
     def get_vllm_embedding(self, data: Dict[str, Any]) -> Tuple[torch.Tensor, List[torch.Tensor]]:
         """Batched entry of the HuggingFace-style harness (nanovllm/models/minicpm.py:342-432).
 
@@ -221,3 +234,33 @@ class MiniCPMForConditionalGeneration(nn.Module):
         for k, shp in Qwen2ForCausalLM.hf_weight_shapes(t).items():
             s["llm." + k] = shp
         return s
+
+
+class MiniCPMConfig:
+    """Flat view of a MiniCPM-V HuggingFace config (nanovllm/models/minicpm.py:237-271)."""
+
+    def __init__(self, hf_config):
+        text = _llm_cfg(hf_config)
+        self.vocab_size = text.vocab_size
+        self.hidden_size = text.hidden_size
+        self.num_hidden_layers = text.num_hidden_layers
+        self.num_attention_heads = text.num_attention_heads
+        self.num_key_value_heads = getattr(text, "num_key_value_heads", None) or text.num_attention_heads
+        self.intermediate_size = text.intermediate_size
+        self.rms_norm_eps = getattr(text, "rms_norm_eps", 1e-6)
+        self.max_position_embeddings = getattr(text, "max_position_embeddings", 32768)
+        self.rope_theta = getattr(text, "rope_theta", 1000000.0)
+        self.head_dim = getattr(text, "head_dim", None) or self.hidden_size // self.num_attention_heads
+        self.hidden_act = getattr(text, "hidden_act", "silu")
+        self.vision_config = _vision_cfg(hf_config)
+        self.vision_hidden_size = self.vision_config.hidden_size
+        self.image_size = getattr(self.vision_config, "image_size", 980)
+        self.patch_size = getattr(self.vision_config, "patch_size", 14)
+        self.query_num = int(getattr(hf_config, "query_num", 64))
+        self.image_token_len = self.query_num
+
+
+def get_minicpm_weight_mapping() -> Dict[str, str]:
+    """Checkpoint prefix -> module of this model: `llm.*` native language model, `vpm.*` SigLIP tower,
+    `resampler.*` perceiver resampler (nanovllm/models/minicpm.py:280-303, :473-483)."""
+    return {"llm.": "llm.", "vpm.": "vpm.", "resampler.": "resampler."}
