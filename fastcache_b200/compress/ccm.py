@@ -90,12 +90,14 @@ class _CCMBase(nn.Module):
     # ----------------------------------------------------------------- math
     def compress_segment(self, x: torch.Tensor, layer_idx: int, bank: str) -> torch.Tensor:
         """x: [B, H, S, D] -> [B, H, S_c, D] with the rule in the module docstring."""
+        return self._merge(x, getattr(self, f"compress_{bank}")[layer_idx])
+
+    def _merge(self, x: torch.Tensor, mlp: nn.Module) -> torch.Tensor:
         B, H, S, D = x.shape
         f = self.compression_factor
         s = S // f
         if S == 0 or s < self.min_seq_len:
             return x
-        mlp = getattr(self, f"compress_{bank}")[layer_idx]
         w = next(mlp.parameters())
         z = x[:, :, : s * f, :].reshape(B, H, s, D * f)
         y = mlp(z.to(w.dtype)).to(x.dtype)
@@ -105,6 +107,15 @@ class _CCMBase(nn.Module):
 
     def _bank_for(self, segment: str, which: str) -> str:
         raise NotImplementedError
+
+    def compress_layer(self, layer_cache: Tuple[torch.Tensor, torch.Tensor], layer_idx: int,
+                       compressor_k: nn.ModuleList, compressor_v: nn.ModuleList
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One segment of one layer through an explicit pair of banks, e.g.
+        `m.compress_layer((k, v), l, m.compress_tk, m.compress_tv)` (utils_ccm/module_ccm_v11.py:666-694).
+        `forward` and `compress_layer_kv` pick the banks from the image / text split themselves."""
+        k, v = layer_cache
+        return self._merge(k, compressor_k[layer_idx]), self._merge(v, compressor_v[layer_idx])
 
     def compress_layer_kv(self, k: torch.Tensor, v: torch.Tensor, layer_idx: int, image_len: int):
         outs = []

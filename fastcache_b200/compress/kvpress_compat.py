@@ -149,6 +149,31 @@ class ScorerPressWithTime:
         self.totalTime += (self._impl.total_time_ms - before) / 1e3
         return out
 
+    def reset_timeCheck(self) -> None:
+        self.totalTime = 0.0
+
+    def forward_hook(self, module: Any, input: Any, kwargs: dict, output: Any):
+        """Forward hook of a HuggingFace attention layer (`register_forward_hook(..., with_kwargs=True)`):
+        once prefill has filled the layer's cache, compress that layer in place and time it on the
+        device (the reference's hook accumulates host time without a synchronize,
+        utils_ccm/utils_compress.py:209-268).  Decode steps (one query row) pass through."""
+        hidden = kwargs.get("hidden_states", input[0] if input else None)
+        cache = kwargs.get("past_key_value", kwargs.get("past_key_values"))
+        if hidden is None or cache is None or hidden.shape[1] <= 1:
+            return output
+        li = int(getattr(module, "layer_idx", 0))
+        layers = getattr(cache, "layers", None)
+        if layers is not None:
+            k, v = layers[li].keys, layers[li].values
+        else:
+            k, v = cache.key_cache[li], cache.value_cache[li]
+        (ck, cv), = self([(k, v)])
+        if layers is not None:
+            layers[li].keys, layers[li].values = ck, cv
+        else:
+            cache.key_cache[li], cache.value_cache[li] = ck, cv
+        return output
+
 
 class StreamingLLMPressWithTime(ScorerPressWithTime):
     method = "streaming_llm"
@@ -226,16 +251,70 @@ def get_underlying_model(model: Any) -> Any:
 
 
 class TimeTik:
-    """Named timers (reference: utils_ccm/utils_compress.py:414-475)."""
+    """Named accumulating timers plus per-token decode latencies (utils_ccm/utils_compress.py:414-475).
+
+    `timeTik(name)` / `timeTok(name)` bracket a region: its time adds to `timeTable[name]` and its
+    count to `timeTimesTable[name]`.  With `pos_tik_check` set, `timeTikPos()` stamps the moment a
+    token was produced and `timeTokPos(next_id)` records the time since the stamp `src_id`."""
 
     def __init__(self) -> None:
-        self._t: Dict[str, float] = {}
-        self.totals: Dict[str, float] = {}
+        self.timeTable: Dict[str, float] = {}
+        self.timeTimesTable: Dict[str, int] = {}
+        self.startTimeTable: Dict[str, float] = {}
+        self.pos_tik_check = 0
+        self.pos_reset()
 
-    def tik(self, name: str) -> None:
-        self._t[name] = time.perf_counter()
+    @property
+    def totals(self) -> Dict[str, float]:
+        return self.timeTable
 
-    def tok(self, name: str) -> float:
-        dt = time.perf_counter() - self._t.pop(name)
-        self.totals[name] = self.totals.get(name, 0.0) + dt
+    def timeTik(self, token_name: str = "") -> None:
+        self.timeTable.setdefault(token_name, 0.0)
+        self.timeTimesTable.setdefault(token_name, 0)
+        self.startTimeTable[token_name] = time.perf_counter()
+
+    def timeTok(self, token_name: str = "") -> float:
+        dt = time.perf_counter() - self.startTimeTable[token_name]
+        self.timeTable[token_name] += dt
+        self.timeTimesTable[token_name] += 1
         return dt
+
+    tik, tok = timeTik, timeTok
+
+    def timeTikPos(self) -> None:
+        if self.pos_tik_check:
+            self.generated_id_time.append(time.perf_counter())
+
+    def timeTokPos(self, next_id: int) -> None:
+        if self.pos_tik_check:
+            self.generated_pos_latency.append(time.perf_counter() - self.generated_id_time[self.src_id])
+            self.src_id = next_id
+
+    def get_token_time(self) -> List[float]:
+        return self.generated_pos_latency
+
+    def reset(self) -> None:
+        for name in self.timeTable:
+            self.timeTable[name], self.timeTimesTable[name] = 0.0, 0
+
+    def report(self) -> str:
+        return "\n".join(f"{n}: {self.timeTable[n]:.4f}. {self.timeTimesTable[n]}" for n in self.timeTable)
+
+    def show(self) -> None:
+        print(self.report())
+
+    def show_and_reset(self) -> None:
+        self.show()
+        self.reset()
+
+    def pos_reset(self) -> None:
+        self.generated_pos_latency: List[float] = []
+        self.generated_id_time: List[float] = []
+        self.src_id = 0
+
+    def show_posTik(self) -> None:
+        print("generated_pos_latency", self.generated_pos_latency)
+
+    def show_posTik_and_reset(self) -> None:
+        self.show_posTik()
+        self.pos_reset()

@@ -88,15 +88,80 @@ def fake_quantize(x: torch.Tensor, nbits: int = 4, group_size: int = 128) -> tor
 
 
 class SimpleKVQuantizer:
+    """Quantise-and-restore of a whole cache (utils_ccm/utils_compress.py:118-164).  Called with a
+    cache it returns the restored cache; `totalTime` accumulates seconds like the timed presses."""
+
     def __init__(self, nbits: int = 4, group_size: int = 128):
         self.nbits, self.group_size = nbits, group_size
+        self.totalTime = 0.0
+
+    def reset_timeCheck(self) -> None:
+        self.totalTime = 0.0
+
+    def quantize_cache(self, past_key_values):
+        import time
+        t0 = time.perf_counter()
+        out = tuple((fake_quantize(k, self.nbits, self.group_size), fake_quantize(v, self.nbits, self.group_size))
+                    for k, v in past_key_values)
+        if out and out[0][0].is_cuda:
+            torch.cuda.synchronize(out[0][0].device)
+        self.totalTime += time.perf_counter() - t0
+        return out
 
     def __call__(self, kv_cache):
-        return [(fake_quantize(k, self.nbits, self.group_size), fake_quantize(v, self.nbits, self.group_size))
-                for k, v in kv_cache]
+        return list(self.quantize_cache(kv_cache))
 
 
-ImprovedKVQuantizer = SimpleKVQuantizer
+class ImprovedKVQuantizer(SimpleKVQuantizer):
+    """Per-row absmax variant that keeps its scales (utils_ccm/utils_compress.py:27-116):
+    `quantize_cache` returns integer codes and remembers one scale per row and tensor,
+    `dequantize_cache` restores the values from them."""
+
+    def __init__(self, nbits: int = 4):
+        super().__init__(nbits)
+        self.cache: Dict[str, Dict[str, torch.Tensor]] = {}
+
+    def _codes(self, x: torch.Tensor, key: str) -> torch.Tensor:
+        qmax = 2 ** (self.nbits - 1) - 1
+        max_val = x.abs().amax(dim=-1, keepdim=True)
+        scale = (max_val / qmax).clamp_min(torch.finfo(torch.float32).tiny)
+        self.cache[key] = {"scale": scale, "max_val": max_val}
+        return torch.round(x / scale).clamp(-qmax - 1, qmax).to(torch.int8)
+
+    def quantize_cache(self, past_key_values):
+        return tuple((self._codes(k, f"k_{i}"), self._codes(v, f"v_{i}"))
+                     for i, (k, v) in enumerate(past_key_values))
+
+    def dequantize_cache(self, quantized_cache):
+        out = []
+        for i, (k, v) in enumerate(quantized_cache):
+            sk, sv = self.cache[f"k_{i}"]["scale"], self.cache[f"v_{i}"]["scale"]
+            out.append((k.to(sk.dtype) * sk, v.to(sv.dtype) * sv))
+        return tuple(out)
+
+    def __call__(self, kv_cache):
+        return list(self.dequantize_cache(self.quantize_cache(kv_cache)))
+
+
+class BaseCompressionMethod:
+    """`with method(model) as m:` frame that the harness wraps around generation
+    (utils_ccm/utils_compress.py:96-116): the base does nothing to the model."""
+
+    def __init__(self, compression_ratio: float = 0.5):
+        self.compression_ratio = compression_ratio
+
+    def __call__(self, model):
+        return self.CompressionContext(model, self.compression_ratio)
+
+    class CompressionContext:
+        def __init__(self, model, compression_ratio: float):
+            self.model, self.compression_ratio = model, compression_ratio
+
+        def __enter__(self):
+            return self.model
+
+        def __exit__(self, exc_type, exc, tb):
+            return False
 
 
 class QuantizedCacheWrapper:

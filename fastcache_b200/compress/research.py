@@ -275,3 +275,40 @@ class CrossModelKVCompressor(nn.Module):
 
 class CrossModelRealKVCompressor(CrossModelKVCompressor):
     heads_merge = True
+
+
+# ----------------------------------------------------------------- small helpers
+class PositionalEncoding(nn.Module):
+    """Additive sinusoidal positions for `[S, B, d_model]` inputs (utils_ccm/module_ccm_v11.py:333-345)."""
+
+    def __init__(self, d_model: int, max_len: int = 5000):
+        super().__init__()
+        pos = torch.arange(max_len, dtype=torch.float32)[:, None]
+        div = torch.exp(torch.arange(0, d_model, 2, dtype=torch.float32) * (-math.log(10000.0) / d_model))
+        pe = torch.zeros(max_len, d_model)
+        pe[:, 0::2] = torch.sin(pos * div)
+        pe[:, 1::2] = torch.cos(pos * div)[:, : d_model // 2]
+        self.register_buffer("pe", pe[:, None, :])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return x + self.pe[: x.size(0)]
+
+
+def logits_to_onehot(logits: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """One-hot of the arg-max along `dim` (utils_ccm/module_ccm_v11.py:2050-2053)."""
+    return F.one_hot(logits.argmax(dim=dim), num_classes=logits.size(dim))
+
+
+def count_true_segments_with_zeros(bool_tensor: torch.Tensor) -> List[int]:
+    """Lengths of the pieces a 1-D mask falls into when cut after every False: each piece is a run
+    of True values plus the False that ends it; the last piece has no closing False
+    (utils_ccm/module_ccm_v11.py:2055-2064).  [T, T, F, T] -> [3, 1]; all True -> [len]."""
+    flags = bool_tensor.bool().tolist()
+    out, run = [], 0
+    for f in flags:
+        run += 1
+        if not f:
+            out.append(run)
+            run = 0
+    out.append(run)
+    return out

@@ -13,6 +13,7 @@ The loop here is model-agnostic: the caller supplies `forward_with_kv(batch, kv 
 """
 from __future__ import annotations
 
+import math
 import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
@@ -79,6 +80,143 @@ class KVCacheCompressionLoss(nn.Module):
     def accuracy(student_logits: torch.Tensor, teacher_logits: torch.Tensor) -> float:
         """Share of positions where the compressed-KV prediction equals the original-KV prediction."""
         return float((student_logits.argmax(-1) == teacher_logits.argmax(-1)).float().mean())
+
+
+    # ------------------------------------------------ probability-space interface
+    # The reference's loss takes probability distributions and mixes its terms with
+    # (alpha, beta, 1 - alpha - beta) (utils_ccm/module_ccm_v11.py:1281-1867).  The methods below give
+    # that interface; `alpha`, `beta`, `epsilon`, `p_threshold` and the position weights are
+    # attributes with the reference's defaults.
+    alpha, beta, epsilon, p_threshold = 1.0, 1.0, 1e-8, 0.9
+    high_weight_count, low_weight, high_weight = 30, 1.0, 3.0
+
+    def _mix(self, target: torch.Tensor, mid: torch.Tensor, out: torch.Tensor,
+             weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+        eps = self.epsilon
+        ce_rows = -(target * torch.log(out + eps)).sum(-1)
+        ce = (ce_rows * weights).mean() if weights is not None else ce_rows.mean()
+        m = 0.5 * (mid + out)
+        js = 0.5 * ((mid * torch.log(mid / (m + eps) + eps)).sum(-1) +
+                    (out * torch.log(out / (m + eps) + eps)).sum(-1)).mean()
+        l1 = (mid - out).abs().sum(-1).mean()
+        return self.alpha * ce + self.beta * js + (1.0 - self.alpha - self.beta) * l1
+
+    def _targets(self, mid_probs: torch.Tensor) -> torch.Tensor:
+        if self.strategy == "logit":
+            return mid_probs
+        return F.one_hot(mid_probs.argmax(-1), mid_probs.shape[-1]).to(mid_probs.dtype)
+
+    def prob_loss(self, mid_probs: torch.Tensor, output_probs: torch.Tensor) -> torch.Tensor:
+        """CE + JS + L1 between the original-KV distribution `mid_probs` and the compressed-KV
+        distribution `output_probs`; the CE target is the distribution itself (strategy "logit") or
+        its arg-max (the label strategies)."""
+        return self._mix(self._targets(mid_probs), mid_probs, output_probs)
+
+    def loss_weight(self, mid_probs: torch.Tensor, output_probs: torch.Tensor) -> torch.Tensor:
+        """`prob_loss` with the first `high_weight_count` positions of each sequence weighted
+        `high_weight` : `low_weight` in the CE term (label strategies)."""
+        if self.strategy == "logit":
+            return self.prob_loss(mid_probs, output_probs)
+        w = torch.full(output_probs.shape[:-1], self.low_weight, device=output_probs.device)
+        w[:, : self.high_weight_count] = self.high_weight
+        return self._mix(self._targets(mid_probs), mid_probs, output_probs, w)
+
+    def loss_gen(self, mid_probs: torch.Tensor, output_probs: torch.Tensor, gen_output_probs: torch.Tensor
+                 ) -> torch.Tensor:
+        """Teacher-forced loss plus the same loss on the free-running generation (cut to the shorter)."""
+        n = min(mid_probs.shape[1], gen_output_probs.shape[1])
+        return 0.5 * (self.prob_loss(mid_probs, output_probs) +
+                      self.prob_loss(mid_probs[:, :n], gen_output_probs[:, :n]))
+
+    @staticmethod
+    def indices_to_mask(indices: torch.Tensor, hidden_dim: int, mask: Optional[torch.Tensor] = None
+                        ) -> torch.Tensor:
+        """[B, S] indices -> bool [B, S, hidden_dim] with mask[b, s, indices[b, s]] set (added to `mask`)."""
+        if mask is None:
+            mask = torch.zeros(*indices.shape, hidden_dim, dtype=torch.bool, device=indices.device)
+        return mask.scatter_(-1, indices.long().unsqueeze(-1), True)
+
+    def get_top_p_mask(self, probs: torch.Tensor) -> torch.Tensor:
+        """Per position, the smallest set of most likely tokens whose mass reaches `p_threshold`."""
+        sp, si = torch.sort(probs, dim=-1, descending=True)
+        keep = torch.cumsum(sp, dim=-1) <= self.p_threshold
+        crossing = keep.sum(-1).clamp_max(probs.shape[-1] - 1)        # the token that crosses the threshold
+        keep = self.indices_to_mask(crossing, probs.shape[-1], keep)
+        return torch.zeros_like(probs, dtype=torch.bool).scatter_(-1, si, keep)
+
+    def forward_attn(self, original_twice_outputs_logits: torch.Tensor, compress_output_logits: torch.Tensor,
+                     pos_len: Sequence[int], orig_hidden_states: Sequence[torch.Tensor],
+                     compress_hidden_states: Sequence[torch.Tensor], attention_mask: Any = None) -> torch.Tensor:
+        """Half output-distribution loss with top-p soft labels over the first `pos_len[0] + pos_len[1]`
+        positions, half per-layer hidden-state loss (MSE + cosine distance of the softmaxed states,
+        the embedding layer skipped).  Both inputs are probability distributions despite their names."""
+        n = int(pos_len[0]) + int(pos_len[1])
+        base, comp = original_twice_outputs_logits, compress_output_logits
+        head = base[:, :n] * self.get_top_p_mask(base[:, :n]).to(base.dtype)
+        labels = head / (head.sum(-1, keepdim=True) + self.epsilon)
+        eps = self.epsilon
+        ce = -(labels * torch.log(comp[:, :n] + eps)).sum(-1).mean()
+        m = 0.5 * (base + comp)
+        js = 0.5 * ((base * torch.log(base / (m + eps) + eps)).sum(-1) +
+                    (comp * torch.log(comp / (m + eps) + eps)).sum(-1)).mean()
+        l1 = (base - comp).abs().sum(-1).mean()
+        layer = base.new_zeros(())
+        for i, (o, c) in enumerate(zip(orig_hidden_states, compress_hidden_states)):
+            if i == 0:
+                continue
+            po, pc = torch.softmax(o.float(), -1), torch.softmax(c.float(), -1)
+            layer = layer + F.mse_loss(c.float(), o.float()) + \
+                (1.0 - F.cosine_similarity(pc.flatten(0, -2), po.flatten(0, -2), dim=-1).mean())
+        out = self.alpha * ce + self.beta * js + (1.0 - self.alpha - self.beta) * l1
+        return 0.5 * out + 0.5 * (layer / 2)
+
+    @staticmethod
+    def cvt_hidden_states(hidden_states: Sequence[Sequence[torch.Tensor]]) -> Tuple[torch.Tensor, ...]:
+        """`generate()`'s per-step tuples (step -> layer -> [B, 1, H]) to per-layer [B, steps, H]."""
+        n_layers = len(hidden_states[0])
+        return tuple(torch.cat([step[l][:, -1:, :] for step in hidden_states], dim=1) for l in range(n_layers))
+
+    @staticmethod
+    def compute_attention_patterns(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                   attention_mask: Optional[torch.Tensor] = None
+                                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """softmax(Q K^T / sqrt(d)) (+ additive mask) and its product with V."""
+        w = query @ key.transpose(-1, -2) / math.sqrt(query.shape[-1])
+        if attention_mask is not None:
+            w = w + attention_mask
+        w = torch.softmax(w.float(), dim=-1).to(value.dtype)
+        return w, w @ value
+
+    @staticmethod
+    def calc_metrics(mid_probs: torch.Tensor, output_probs: torch.Tensor):
+        a, b = mid_probs.argmax(-1), output_probs.argmax(-1)
+        return (a == b).float().mean(), a, b
+
+    def calc_metrics2(self, mid_probs, output_probs, gen_output_probs):
+        """Agreement of the teacher-forced and of the free-running predictions with the original ones."""
+        a, b = mid_probs.argmax(-1), output_probs.argmax(-1)
+        n = min(mid_probs.shape[1], gen_output_probs.shape[1])
+        g = gen_output_probs[:, :n].argmax(-1)
+        return (a == b).float().mean(), (a[:, :n] == g).float().mean(), a, b, g
+
+    def calc_metrics3(self, mid_probs, output_probs):
+        """Accuracy, mean length of a matching run, perplexity of the compressed model on the labels."""
+        from .research import count_true_segments_with_zeros
+        a, b = mid_probs.argmax(-1), output_probs.argmax(-1)
+        runs = count_true_segments_with_zeros((a == b).reshape(-1))
+        labels = F.one_hot(a, mid_probs.shape[-1]).to(output_probs.dtype)
+        ce = -(labels * torch.log(output_probs + self.epsilon)).sum(-1).mean()
+        return (a == b).float().mean(), float(sum(runs)) / len(runs), torch.exp(ce), a, b
+
+    def calc_metrics4(self, mid_probs, output_probs, dmodel_probs):
+        """As `calc_metrics3` for two candidate models and for "either of them is right"."""
+        from .research import count_true_segments_with_zeros
+        a = mid_probs.argmax(-1)
+        e1, e2 = a == output_probs.argmax(-1), a == dmodel_probs.argmax(-1)
+        e3 = e1 | e2
+        run = lambda e: (lambda r: float(sum(r)) / (len(r) + 1e-5))(count_true_segments_with_zeros(e.reshape(-1)))  # noqa: E731
+        return (e1.float().mean().item(), e2.float().mean().item(), e3.float().mean().item(),
+                run(e1), run(e2), run(e3))
 
 
 @dataclass

@@ -83,3 +83,67 @@ def test_named_recipes_pick_the_compressor_family(tmp_path):
                               compression_ratio=2, compressor_save_name="lv2",
                               compressor_load_path=out2["last"])
     assert comp3.compression_factor == 2
+
+
+def test_probability_space_loss_interface():
+    from fastcache_b200.compress.research import count_true_segments_with_zeros, logits_to_onehot
+
+    torch.manual_seed(0)
+    loss = KVCacheCompressionLoss("logit")
+    loss.alpha, loss.beta = 0.4, 0.4
+    a = torch.softmax(torch.randn(2, 6, 10), -1)
+    b = torch.softmax(torch.randn(2, 6, 10), -1)
+    assert loss.prob_loss(a, a) < loss.prob_loss(a, b)
+    # top-p mask: smallest prefix of the sorted tokens whose mass reaches the threshold
+    m = loss.get_top_p_mask(a)
+    kept = (a * m).sum(-1)
+    assert bool((kept >= loss.p_threshold - 1e-6).all())
+    smallest = torch.where(m, a, torch.ones_like(a)).min(-1).values
+    assert bool((kept - smallest < loss.p_threshold).all())               # dropping the last one falls short
+    assert loss.indices_to_mask(torch.tensor([[1, 0]]), 3).tolist() == [[[False, True, False], [True, False, False]]]
+    hs = [torch.randn(2, 6, 8) for _ in range(3)]
+    same = loss.forward_attn(a, a, (2, 3, 0), hs, hs)
+    diff = loss.forward_attn(a, b, (2, 3, 0), hs, [h + 0.5 * torch.randn_like(h) for h in hs])
+    assert same < diff
+    steps = [[torch.full((2, 1, 4), float(t * 10 + l)) for l in range(3)] for t in range(5)]
+    per_layer = loss.cvt_hidden_states(steps)
+    assert len(per_layer) == 3 and per_layer[1].shape == (2, 5, 4) and per_layer[1][0, :, 0].tolist() == [1, 11, 21, 31, 41]
+    acc, ta, tb = loss.calc_metrics(a, a)
+    assert acc == 1.0 and torch.equal(ta, tb)
+    acc3, run3, ppl, _, _ = loss.calc_metrics3(a, a)
+    assert acc3 == 1.0 and run3 == 12.0 and ppl > 1.0
+    assert loss.calc_metrics4(a, b, a)[1:3] == (1.0, 1.0)
+    assert len(loss.calc_metrics2(a, b, b[:, :4])) == 5 and loss.loss_gen(a, b, b[:, :4]) > 0
+    assert KVCacheCompressionLoss("label").loss_weight(a, b) > KVCacheCompressionLoss("label").prob_loss(a, b)
+    w, o = loss.compute_attention_patterns(torch.randn(1, 2, 4, 8), torch.randn(1, 2, 4, 8), torch.randn(1, 2, 4, 8))
+    assert torch.allclose(w.sum(-1), torch.ones(1, 2, 4)) and o.shape == (1, 2, 4, 8)
+    assert count_true_segments_with_zeros(torch.tensor([True, True, False, True])) == [3, 1]
+    assert count_true_segments_with_zeros(torch.tensor([False, True, True, False])) == [1, 3, 0]
+    assert logits_to_onehot(torch.tensor([[0.1, 0.9]])).tolist() == [[0, 1]]
+
+
+def test_training_datasets_encode_turns():
+    from fastcache_b200.compress.train_data import CustomDataset, CustomImageTextDataset
+
+    class Tok:
+        def __call__(self, text, **kw):
+            n = min(len(text.split()), kw.get("max_length", 512))
+            if kw.get("padding") == "max_length":
+                n = kw["max_length"]
+            return {"input_ids": torch.arange(n)[None], "attention_mask": torch.ones(1, n, dtype=torch.long)}
+
+    ds = CustomDataset(["a b c", "d e"], Tok(), max_length=4)
+    assert len(ds) == 2 and ds[0]["input_ids"].tolist() == [0, 1, 2] and "draft_input_ids" not in ds[0]
+    ds.new_tokenizer(Tok())
+    assert ds[1]["draft_input_ids"].shape == (4,)
+
+    class Proc:
+        def __call__(self, images=None, text=None, **kw):
+            n = kw.get("max_length", 3) if kw.get("padding") == "max_length" else 3
+            return {"input_ids": torch.zeros(1, n, dtype=torch.long), "attention_mask": torch.ones(1, n, dtype=torch.long),
+                    "pixel_values": torch.zeros(1, 3, 4, 4)}
+
+    conv = [([("describe", "img0"), ("more", "img1"), ("text only", None)], [1, 1, 0])]
+    items = CustomImageTextDataset(conv, Proc(), max_length=8)[0]
+    assert len(items) == 2 and items[0]["input_ids"].shape == (8,) and items[0]["pixel_values"].shape == (3, 4, 4)
+    assert CustomImageTextDataset(conv, Proc(), 8, launch_padding_flag=False)[0][0]["input_ids"].shape == (3,)

@@ -5,5 +5,5 @@ from fastcache_b200.compress.kvpress_compat import (ExpectedAttentionPressWithTi
                                                     StreamingLLMPressWithTime, TimeTik, TOVAPressWithTime,
                                                     exec_compression_methods, get_underlying_model,
                                                     press_select)
-from fastcache_b200.compress.quant import (ImprovedKVQuantizer, QuantizedCacheWrapper,  # noqa: F401
+from fastcache_b200.compress.quant import (BaseCompressionMethod, ImprovedKVQuantizer, QuantizedCacheWrapper,  # noqa: F401
                                            SimpleKVQuantizer)
