@@ -173,11 +173,19 @@ def build_engine(arch: dict, backend: str, method: Optional[str], variant: Confi
     return LLM(dict(arch), **kw)
 
 
-def run_cell(llm: LLM, reqs: Sequence[Tuple[List[int], int]], batch: int) -> Dict[str, Any]:
+def run_cell(llm: LLM, reqs: Sequence[Tuple[List[int], int]], batch: int, warmup_waves: int = 1
+             ) -> Dict[str, Any]:
     """Feeds the requests in waves of `batch`; throughput counts generated tokens over wall time
-    bracketed by device synchronisation."""
+    bracketed by device synchronisation.  `warmup_waves` untimed waves of the same prompts with four
+    output tokens run first, so every kernel shape of the cell (compression included) has been used."""
     cuda = llm.model_runner.device.type == "cuda"
     sync = (lambda: torch.cuda.synchronize(llm.model_runner.device)) if cuda else (lambda: None)
+    for _ in range(warmup_waves):
+        for ids, _n in reqs[:batch]:
+            llm.add_request(ids, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+        while not llm.is_finished():
+            llm.step()
+    base_stats = (llm.stats.compressions, llm.stats.blocks_freed, llm.stats.preemptions)
     bm = llm.scheduler.block_manager
     gen = prompt = steps = 0
     min_free = bm.num_free_blocks
@@ -210,8 +218,71 @@ def run_cell(llm: LLM, reqs: Sequence[Tuple[List[int], int]], batch: int) -> Dic
     return {"throughput_tok_s": gen / dt, "total_time_s": dt, "generated_tokens": gen, "prompt_tokens": prompt,
             "engine_steps": steps, "ttft_p50_s": ttft[len(ttft) // 2] if ttft else None,
             "ttft_p99_s": ttft[min(len(ttft) - 1, int(0.99 * len(ttft)))] if ttft else None,
-            "compressions": st.compressions, "blocks_freed": st.blocks_freed, "preemptions": st.preemptions,
+            "compressions": st.compressions - base_stats[0], "blocks_freed": st.blocks_freed - base_stats[1],
+            "preemptions": st.preemptions - base_stats[2],
             "min_free_blocks": min_free, "total_blocks": bm.num_blocks}
+
+
+def run_cell_here(args, arch: dict, backend: str, method: Optional[str], variant: ConfigVariant,
+                  reqs: Sequence[Tuple[List[int], int]], batch: int, max_len: int) -> Dict[str, Any]:
+    """Build the engine, run the cell, free the engine.  A failure comes back as {"error": ...}."""
+    llm = None
+    out: Dict[str, Any] = {}
+    try:
+        llm = build_engine(arch, backend, method, variant, args.compression_factor, args.device, max_len,
+                           max(batch, 8), args)
+        out["greenctx_active"] = bool(llm.model_runner.greenctx_enabled)
+        out.update(run_cell(llm, reqs, batch, args.warmup_waves))
+    except Exception as exc:                            # one broken cell must not end the sweep
+        out["error"] = f"{type(exc).__name__}: {exc}"
+    try:
+        if llm is not None:
+            llm.exit()
+    except Exception as exc:                            # a device error is sticky: report it, do not mask the first
+        out.setdefault("error", f"{type(exc).__name__}: {exc}")
+    del llm
+    if torch.cuda.is_available() and "error" not in out:
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_cell_in_child(args, model: str, spec: WorkloadSpec, batch: int, variant: ConfigVariant, max_len: int
+                      ) -> Dict[str, Any]:
+    """The cell in a process of its own: a fresh device context per cell, so a device error (which
+    is sticky for the process that hit it) or memory left behind by one engine cannot reach the next
+    cell.  The child prints its result as one JSON line."""
+    import subprocess
+    cell = {"model": model, "spec": asdict(spec), "batch": batch, "variant": asdict(variant), "max_len": max_len,
+            "args": {k: v for k, v in vars(args).items() if k not in ("cell",)}}
+    try:
+        proc = subprocess.run([sys.executable, os.path.abspath(__file__), "--cell", json.dumps(cell)],
+                              capture_output=True, text=True, timeout=args.cell_timeout)
+    except subprocess.TimeoutExpired:
+        return {"error": f"cell exceeded {args.cell_timeout} s"}
+    for line in reversed(proc.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)
+    tail = (proc.stderr or "").strip().splitlines()[-1:] or [""]
+    return {"error": f"child exited {proc.returncode}: {tail[0][:300]}"}
+
+
+def child_main(cell: Dict[str, Any]) -> None:
+    args = argparse.Namespace(**cell["args"])
+    spec = WorkloadSpec(**{**cell["spec"], "batch_sizes": tuple(cell["spec"]["batch_sizes"])})
+    variant = ConfigVariant(**cell["variant"])
+    arch, backend, method = MODELS[cell["model"]]
+    if args.scale == "tiny":
+        arch = dict(TINY)
+    reqs = requests_for(spec, cell["batch"], arch["vocab_size"], cell["max_len"], cell_seed(cell["model"], spec.name))
+    out = run_cell_here(args, arch, backend, method, variant, reqs, cell["batch"], cell["max_len"])
+    sys.stdout.write(json.dumps(out) + "\n")
+    sys.stdout.flush()
+    if "error" in out:
+        os._exit(1)                  # skip interpreter teardown after a device error
+
+
+def cell_seed(model: str, workload: str) -> int:
+    return zlib.crc32(f"{model}/{workload}".encode()) & 0xffff
 
 
 # ------------------------------------------------------------------------ main
@@ -253,9 +324,18 @@ def main(argv: Optional[Sequence[str]] = None) -> List[Dict[str, Any]]:
     ap.add_argument("--greenctx-compress-ratio", type=float, default=0.25)
     ap.add_argument("--greenctx-main-ratio", type=float, default=None)
     ap.add_argument("--greenctx-main-stream", action="store_true")
+    ap.add_argument("--warmup-waves", type=int, default=1)
+    ap.add_argument("--isolate", default="auto", choices=["auto", "on", "off"],
+                    help="one process per cell (auto: on a CUDA device)")
+    ap.add_argument("--cell-timeout", type=float, default=1800.0)
+    ap.add_argument("--cell", default="", help=argparse.SUPPRESS)
     ap.add_argument("--scale", default="full", choices=["full", "tiny"])
     ap.add_argument("--device", default="cuda:0" if torch.cuda.is_available() else "cpu")
     args = ap.parse_args(argv)
+    if args.cell:
+        child_main(json.loads(args.cell))
+        return []
+    args.isolate = args.isolate == "on" or (args.isolate == "auto" and args.device.startswith("cuda"))
     if args.greenctx_main_ratio is None:
         args.greenctx_main_ratio = max(0.05, 1.0 - args.greenctx_compress_ratio)
     tiny = args.scale == "tiny"
@@ -291,7 +371,7 @@ def main(argv: Optional[Sequence[str]] = None) -> List[Dict[str, Any]]:
                 max_len = 8 * max(spec.trace_min_context, spec.synthetic_context, spec.max_prompt_tokens) \
                     + spec.max_output_tokens + 64
                 max_len = min(max_len, arch["max_position_embeddings"])
-                reqs = requests_for(spec, batch, arch["vocab_size"], max_len, seed=zlib.crc32(f"{name}/{spec.name}".encode()) & 0xffff)
+                reqs = requests_for(spec, batch, arch["vocab_size"], max_len, seed=cell_seed(name, spec.name))
                 base: Optional[float] = next((r["throughput_tok_s"] for r in rows if
                                               (r["model"], r["workload"], r["batch_size"], r["variant"]) ==
                                               (name, spec.name, batch, "baseline")), None)
@@ -305,25 +385,16 @@ def main(argv: Optional[Sequence[str]] = None) -> List[Dict[str, Any]]:
                                            "method": method if variant.compression else None,
                                            "compression_factor": args.compression_factor, "scale": args.scale,
                                            "workload_spec": asdict(spec), "device": args.device}
-                    llm = None
-                    try:
-                        llm = build_engine(arch, backend, method, variant, args.compression_factor, args.device,
-                                           max_len, max(batch, 8), args)
-                        row["greenctx_active"] = bool(llm.model_runner.greenctx_enabled)
-                        row.update(run_cell(llm, reqs, batch))
+                    if args.isolate:
+                        row.update(run_cell_in_child(args, name, spec, batch, variant, max_len))
+                    else:
+                        row.update(run_cell_here(args, arch, backend, method, variant, reqs, batch, max_len))
+                    if "error" not in row:
                         if variant.label == "baseline":
                             base = row["throughput_tok_s"]
                         if base:
                             row["speedup_vs_baseline"] = row["throughput_tok_s"] / base
                         done.add(key)
-                    except Exception as exc:            # one broken cell must not end the sweep
-                        row["error"] = f"{type(exc).__name__}: {exc}"
-                    finally:
-                        if llm is not None:
-                            llm.exit()
-                        del llm
-                        if torch.cuda.is_available():
-                            torch.cuda.empty_cache()
                     rows.append(row)
                     save(args.output, rows)
                     print(json.dumps({k: row.get(k) for k in ("model", "workload", "batch_size", "variant",

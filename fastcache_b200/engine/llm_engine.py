@@ -180,6 +180,10 @@ class LLMEngine:
             self.processor = None
 
     def exit(self) -> None:
+        """Release the device memory of this engine (CUDA graphs, KV pool, weights).  The engine cannot
+        step afterwards.  Also drops the interpreter-exit hook, which would otherwise keep the engine
+        (and its pool) alive for the rest of the process."""
+        atexit.unregister(self.exit)
         r = getattr(self, "model_runner", None)
         if r is not None:
             r.exit()

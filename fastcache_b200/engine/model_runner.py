@@ -232,7 +232,15 @@ class ModelRunner:
             if self.device.type == "cuda":
                 total, used, free = get_gpu_memory(self.device.index)
                 budget = int(total * cfg.gpu_memory_utilization) - used
-                cfg.num_kvcache_blocks = max(1, budget // block_bytes)
+                need = -(-cfg.max_model_len // bs)
+                if budget < need * block_bytes:
+                    raise RuntimeError(
+                        f"not enough device memory for the KV pool: {max(budget, 0) / 2**30:.1f} GiB left under "
+                        f"gpu_memory_utilization={cfg.gpu_memory_utilization} ({used / 2**30:.1f} of "
+                        f"{total / 2**30:.1f} GiB in use), one request of max_model_len={cfg.max_model_len} needs "
+                        f"{need * block_bytes / 2**30:.1f} GiB; free other engines in this process "
+                        f"(`llm.exit()`) or pass num_kvcache_blocks")
+                cfg.num_kvcache_blocks = budget // block_bytes
             else:
                 need = cfg.max_num_seqs * -(-cfg.max_model_len // bs)
                 cfg.num_kvcache_blocks = max(1, min(need, (1 << 30) // block_bytes))
@@ -676,10 +684,23 @@ class ModelRunner:
                 self._compressed_lens.pop(sid, None)
 
     def exit(self) -> None:
-        self.graphs.clear()
-        self.graph_pool = None
+        """Wait for the device, then drop everything that holds device memory: graphs and their
+        static buffers, the KV pool (and the layers' views of it), the weights."""
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+        self.graphs.clear()
+        self.graph_pool = None
+        self.graph_vars = {}
+        self._staging = {}
+        model = getattr(self, "model", None)
+        if model is not None:
+            for module in model.modules():
+                if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
+                    module.k_cache = module.v_cache = None
+        self.kv_cache = None
+        self.model = None
+        self.packed_compressor = None
+        self._window_q.clear()
 
 
 class _Null:

@@ -23,11 +23,11 @@ def test_sweep_rows_resume_and_errors(tmp_path, monkeypatch):
     calls, fail = [], [True]
     real = mb.run_cell
 
-    def flaky(llm, reqs, batch):
+    def flaky(llm, reqs, batch, warmup_waves=1):
         calls.append(batch)
         if fail.pop() if fail else False:
             raise RuntimeError("injected")
-        return real(llm, reqs, batch)
+        return real(llm, reqs, batch, warmup_waves)
 
     monkeypatch.setattr(mb, "run_cell", flaky)
     rows2 = mb.main(base + ["--resume", "--variants", "baseline,compression-only,auto-tune+greenctx,triad"])
@@ -48,3 +48,17 @@ def test_trace_csv_filters(tmp_path):
                            trace_min_output=256, trace_max_output=512)
     reqs = mb.requests_for(spec, 3, 1000, 4096, seed=1)
     assert [len(p) for p, _ in reqs] == [2000, 1500, 2000] and all(n == 64 for _, n in reqs)
+
+
+def test_cell_in_a_child_process(tmp_path):
+    out = str(tmp_path / "iso.json")
+    rows = mb.main(["--scale", "tiny", "--device", "cpu", "--models", "llava-mlp", "--workloads", "synthetic-long",
+                    "--batch-sizes", "2", "--variants", "baseline,compression-only", "--isolate", "on",
+                    "--output", out])
+    assert [r.get("error") for r in rows] == [None, None]
+    assert rows[1]["backend"] == "mlp" and rows[1]["compressions"] == 2 and rows[1]["speedup_vs_baseline"] > 0
+    # a child that dies is an error row, not an exception
+    rows = mb.main(["--scale", "tiny", "--device", "cpu", "--models", "llava-mlp", "--workloads", "synthetic-long",
+                    "--batch-sizes", "2", "--variants", "baseline", "--isolate", "on", "--kv-blocks", "2",
+                    "--output", str(tmp_path / "small.json")])
+    assert "blocks" in rows[0]["error"]
