@@ -329,3 +329,81 @@ def create_zero_overhead_compressor(original: _CCMBase, layers_per_decode_step: 
                                     greenctx_streams: Optional[Tuple[Any, Any]] = None) -> ZeroOverheadCompressEngine:
     batched = BatchedGEMMCompressor().load_from_original_compressor(original)
     return ZeroOverheadCompressEngine(batched, layers_per_decode_step, device, greenctx_streams)
+
+
+# ----------------------------------------------------------------- self-benchmarks
+def _time_ms(fn, like: torch.Tensor, iters: int, warmup: int) -> float:
+    """Mean time of `fn()` in ms: CUDA events on the current stream (CUDA) or the host clock (CPU)."""
+    for _ in range(warmup):
+        fn()
+    if like.is_cuda:
+        torch.cuda.synchronize(like.device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        b.synchronize()
+        return float(a.elapsed_time(b)) / iters
+    import time
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        fn()
+    return (time.perf_counter() - t0) * 1e3 / iters
+
+
+def benchmark_batched_vs_original(num_layers: int = 32, batch_size: int = 1, num_heads: int = 8, seq_len: int = 600,
+                                  head_dim: int = 128, compression_factor: int = 5, image_len: int = 576,
+                                  device: Any = None, dtype: Optional[torch.dtype] = None, iters: int = 10,
+                                  warmup: int = 3, verbose: bool = True) -> Dict[str, float]:
+    """Per-layer module compressor against the stacked-weight compressor on one synthetic cache
+    (the reference's self-check, "kv-cache pipeline"/nanovllm/kernels/batched_compress.py:827-942, with
+    its shapes as defaults).  Returns the two times, their ratio and the largest output difference."""
+    from .ccm import KVCacheLinearDecoupleCompressor
+    device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    torch.manual_seed(0)
+    orig = KVCacheLinearDecoupleCompressor(None, compression_factor, 2, n_layer=num_layers, nhead=num_heads,
+                                           head_dim=head_dim)
+    for p in orig.parameters():
+        nn.init.normal_(p, std=0.05)
+    orig = orig.to(device=device, dtype=dtype).eval()
+    batched = BatchedGEMMCompressor().load_from_original_compressor(orig)
+    kv = [(torch.randn(batch_size, num_heads, seq_len, head_dim, device=device, dtype=dtype),
+           torch.randn(batch_size, num_heads, seq_len, head_dim, device=device, dtype=dtype))
+          for _ in range(num_layers)]
+    it_len = [min(image_len, seq_len), max(0, seq_len - image_len)]
+    a, b = orig(kv, it_len), batched(kv, it_len)
+    err = max(float((x[0].float() - y[0].float()).abs().max()) for x, y in zip(a, b))
+    t_orig = _time_ms(lambda: orig(kv, it_len), kv[0][0], iters, warmup)
+    t_batched = _time_ms(lambda: batched(kv, it_len), kv[0][0], iters, warmup)
+    out = {"original_ms": t_orig, "batched_ms": t_batched, "speedup": t_orig / max(t_batched, 1e-9),
+           "max_abs_diff": err, "compressed_len": int(b[0][0].shape[2])}
+    if verbose:
+        print(f"[{device.type}] layers {num_layers} batch {batch_size} heads {num_heads} seq {seq_len} "
+              f"factor {compression_factor}: module {t_orig:.3f} ms, stacked {t_batched:.3f} ms "
+              f"({out['speedup']:.2f}x), max |diff| {err:.3g}")
+    return out
+
+
+def benchmark_fused_vs_pytorch(m: int = 4096, k: int = 640, n: int = 128, device: Any = None,
+                               dtype: Optional[torch.dtype] = None, iters: int = 20, warmup: int = 3,
+                               verbose: bool = True) -> Dict[str, float]:
+    """`relu(x W^T + b)` through this package's linear op (bias and ReLU in the GEMM epilogue on a
+    GPU) against the three PyTorch calls (reference self-check: fused_compress.py:381-462)."""
+    device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(m, k, generator=g).to(device=device, dtype=dtype)
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).to(device=device, dtype=dtype)
+    b = torch.randn(n, generator=g).to(device=device, dtype=dtype)
+    plain = lambda: torch.relu(torch.nn.functional.linear(x, w, b))   # noqa: E731
+    fused = lambda: fused_linear_relu_dropout(x, w, b)                # noqa: E731
+    err = float((plain().float() - fused().float()).abs().max())
+    out = {"pytorch_ms": _time_ms(plain, x, iters, warmup), "fused_ms": _time_ms(fused, x, iters, warmup),
+           "max_abs_diff": err}
+    out["speedup"] = out["pytorch_ms"] / max(out["fused_ms"], 1e-9)
+    if verbose:
+        print(f"[{device.type}] {m}x{k}x{n}: PyTorch {out['pytorch_ms']:.3f} ms, fused {out['fused_ms']:.3f} ms "
+              f"({out['speedup']:.2f}x), max |diff| {err:.3g}")
+    return out

@@ -69,3 +69,12 @@ def test_presses_and_engine_side_compressor():
     u = KVPressCompressor("snapkv", 0.5)(kv)
     assert u[0][0].shape[2] == 32
     assert press_select("ExpectedAttention", 0.5).method == "expected_attention"
+
+
+def test_self_benchmarks_agree_with_the_modules():
+    from fastcache_b200.compress.batched import benchmark_batched_vs_original, benchmark_fused_vs_pytorch
+    r = benchmark_batched_vs_original(num_layers=2, num_heads=2, seq_len=50, head_dim=16, image_len=20, iters=2,
+                                      warmup=1, device="cpu", verbose=False)
+    assert r["max_abs_diff"] < 1e-4 and r["compressed_len"] == 20 // 5 + 30 // 5 and r["speedup"] > 0
+    r = benchmark_fused_vs_pytorch(64, 32, 16, iters=2, warmup=1, device="cpu", verbose=False)
+    assert r["max_abs_diff"] < 1e-4
