@@ -151,6 +151,10 @@ class ModelRunner:
         self.packed_compressor: Optional[PackedCCMWeights] = None
         self._compressed_lens: Dict[int, int] = {}
         self._window_q: Dict[int, Dict[int, torch.Tensor]] = {}
+        if enable_compression and compression_backend == "kvpress":
+            from ..compress.scorers import SCORERS
+            if kvpress_method not in SCORERS:
+                raise ValueError(f"unknown eviction method {kvpress_method!r}; have {sorted(SCORERS)}")
         if enable_compression:
             self._load_compressor(compressor_path, compressor)
         if not enable_compression or (compression_backend == "mlp" and self.packed_compressor is None):

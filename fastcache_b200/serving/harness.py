@@ -177,16 +177,25 @@ class TimestampManager:
 
     def analyze(self, request_id: int, generated_len: int = 1) -> Dict[str, float]:
         t = self.get(request_id)
-        g = lambda k, d=0.0: t.get(k, d)  # noqa: E731
+
+        def span(end: str, *starts: str) -> float:
+            """end - first recorded start; 0 when either side was never stamped."""
+            if t.get(end) is None:
+                return 0.0
+            for s0 in starts:
+                if t.get(s0) is not None:
+                    return t[end] - t[s0]
+            return 0.0
+
         out = {
-            "prefill_queue": g("prefill_start") - g("prefill_queueing_start", g("arrival")),
-            "prefill_process": g("prefill_finish") - g("prefill_start"),
-            "compress_queue": g("compress_start") - g("compress_queueing_start", g("prefill_finish")),
-            "compress_process": g("compress_finish") - g("compress_start"),
-            "decoding_queue": g("decoding_start") - g("decoding_queueing_start", g("prefill_finish")),
-            "decoding_process": g("decoding_finish") - g("decoding_start"),
-            "ttft": g("prefill_finish") - g("prefill_queueing_start", g("arrival")),
-            "latency": g("decoding_finish") - g("arrival"),
+            "prefill_queue": span("prefill_start", "prefill_queueing_start", "arrival"),
+            "prefill_process": span("prefill_finish", "prefill_start"),
+            "compress_queue": span("compress_start", "compress_queueing_start", "prefill_finish"),
+            "compress_process": span("compress_finish", "compress_start"),
+            "decoding_queue": span("decoding_start", "decoding_queueing_start", "prefill_finish"),
+            "decoding_process": span("decoding_finish", "decoding_start", "prefill_finish"),
+            "ttft": span("prefill_finish", "prefill_queueing_start", "arrival"),
+            "latency": span("decoding_finish", "arrival", "prefill_queueing_start"),
         }
         out["tpot"] = out["decoding_process"] / max(1, generated_len)
         out["normalized_latency"] = out["latency"] / max(1, generated_len)
@@ -679,6 +688,7 @@ class ConcurrentTester:
                 r.metrics.generated = len(toks)
                 r.status = RequestStatus.COMPLETED
                 self.timestamps.record(r.request_id, "prefill_finish", r.metrics.prefill_end)
+                self.timestamps.record(r.request_id, "generated_lens", len(toks))
                 self.timestamps.record(r.request_id, "decoding_finish", t)
             if on_step is not None:
                 on_step(steps)

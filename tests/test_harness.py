@@ -59,3 +59,30 @@ def test_concurrent_tester_poisson_arrivals_with_compression():
     assert res.ttft["p50"] > 0 and res.latency["p99"] >= res.ttft["p99"]
     assert res.compression["compressions"] == 12 and res.compression["blocks_freed"] > 0
     assert llm.stats.prefill_steps >= 4                     # prefill cap 3 -> at least 4 prefill batches
+
+
+def test_testcon_cli_single_run_and_yaml(tmp_path):
+    """The harness command line on a CPU: one merge-compressor run (MiniCPM batching rule), then a YAML batch."""
+    from fastcache_b200.serving import testcon
+    common = ["--device", "cpu", "--num_samples", "4", "--max_new_tokens", "4", "--req_per_sec", "500",
+              "--block_size", "16", "--kv_blocks", "256", "--max_model_len", "512"]
+    out = tmp_path / "single"
+    rows = testcon.main(["--model_mode", "minicpm", "--arch", "tiny-minicpm", "--use_compression", "--comp_mode",
+                         "ccm", "--folder_path", str(out), "--gpu_info_path", str(tmp_path / "gpu.csv")] + common)
+    assert rows[0]["batching"] == [15, 45, 135] and rows[0]["result"]["completed"] == 4
+    assert rows[0]["result"]["compression"]["compressions"] == 4
+    av = rows[0]["stage_averages"]
+    assert 0 <= av["ttft"] <= av["latency"] and av["generated_lens"] == 4.0
+    assert (tmp_path / "gpu.csv").exists() and (out / "summary.json").exists()
+    assert "throughput_tok_s" in open(rows[0]["log"]).read()
+
+    cfg = tmp_path / "experiments.yaml"
+    cfg.write_text("global_settings:\n  num_samples: 3\n  req_per_sec: 500\n  max_new_tokens: 3\n"
+                   "experiments:\n"
+                   "  - {name: base, use_compression: false, comp_mode: orig, batching: [5, 5, 5]}\n"
+                   "  - {name: knorm, use_compression: true, comp_mode: Knorm, batching: [5, 5, 5]}\n"
+                   "  - {name: broken, use_compression: true, comp_mode: nonsense, batching: [5, 5, 5]}\n")
+    rows = testcon.main(["--config", str(cfg), "--model_mode", "llava", "--arch", "tiny-llava", "--no_log"] + common)
+    assert [r["name"] for r in rows] == ["base", "knorm", "broken"]
+    assert rows[0]["result"]["completed"] == 3 and rows[0]["batching"] == [5, 5, 5]
+    assert rows[1]["result"]["compression"]["compressions"] == 3 and "error" in rows[2]
