@@ -209,6 +209,11 @@ def main(argv: Optional[Sequence[str]] = None) -> List[Dict[str, Any]]:
         g, exps = load_experiments(args.config, {"seed": args.seed})
         for e in exps:
             e.extra["from_yaml"] = True
+        defaults = parse_args([])
+        for key in ("model_path", "ckpt_path", "datasets_name", "datasets_js_path", "datasets_img_path",
+                    "torch_dtype"):                  # file settings fill what the command line left at its default
+            if key in g and getattr(args, key) == getattr(defaults, key):
+                setattr(args, key, g[key])
     else:
         g = {"num_samples": args.num_samples, "req_per_sec": args.req_per_sec, "seed": args.seed,
              "max_input_tokens": args.max_input_tokens, "max_new_tokens": args.max_new_tokens}
