@@ -159,7 +159,7 @@ def build_engine(args: argparse.Namespace, exp: Experiment):
             kw["compressor"] = comp.eval()
     if args.kv_blocks > 0:
         kw["num_kvcache_blocks"] = args.kv_blocks
-    dtype = {"bfloat16": "bfloat16", "float16": "float16", "float32": "float32"}[args.torch_dtype]
+    dtype = {"bf16": "bfloat16", "fp16": "float16", "fp32": "float32"}.get(args.torch_dtype, args.torch_dtype)
     cpu = args.device == "cpu"
     return LLM(model, device=args.device, dtype="auto" if cpu else dtype, kvcache_block_size=args.block_size,
                max_model_len=args.max_model_len, max_num_seqs=max(args.decoding_batch_size, 8), seed=args.seed,
