@@ -80,3 +80,22 @@ def test_step_trace_records_every_step_and_exports_chrome_trace(tmp_path):
     blob = json.loads(path.read_text())
     assert sum(e["ph"] == "X" for e in blob["traceEvents"]) == len(kinds)
     assert not tracing.nvtx_enabled() or torch.cuda.is_available()
+
+
+def test_exit_releases_the_engine_and_a_second_one_runs():
+    """`exit()` drops the interpreter-exit hook, the pool and the weights, so the engine object and its
+    tensors can be collected; another engine built afterwards in the same process works."""
+    import gc
+    import weakref
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    llm = _engine(True, True)
+    first = llm.generate(_prompts(2, 40), sp)
+    pool, engine = weakref.ref(llm.model_runner.kv_cache), weakref.ref(llm)
+    llm.exit()
+    llm.exit()                                           # idempotent
+    assert llm.model_runner.kv_cache is None and llm.model_runner.model is None
+    del llm
+    gc.collect()
+    assert pool() is None and engine() is None
+    again = _engine(True, True).generate(_prompts(2, 40), sp)
+    assert [o["token_ids"] for o in again] == [o["token_ids"] for o in first]
