@@ -1,2 +1,2 @@
 """`utils_ccm.utils_kvcachePool` of the reference."""
-from fastcache_b200.serving.harness import KVCachePool  # noqa: F401
+from fastcache_b200.serving.harness import KVCacheItem, KVCachePool  # noqa: F401

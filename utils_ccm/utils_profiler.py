@@ -1,3 +1,4 @@
 """`utils_ccm.utils_profiler` of the reference (analytic FLOP / byte models)."""
-from fastcache_b200.serving.profiler import (LLaVAIntensityAnalyzer, LLMIntensityAnalyzer,  # noqa: F401
-                                             VisionEncoderAnalyzer)
+from fastcache_b200.serving.profiler import (ComputeStats, LLaVAConfigWrapper, LLaVAIntensityAnalyzer,  # noqa: F401
+                                             LLMConfig, LLMConfigWrapper, LLMIntensityAnalyzer, PhaseCost,
+                                             VisionEncoderAnalyzer, format_number)
