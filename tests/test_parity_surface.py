@@ -226,3 +226,31 @@ def test_harness_reference_method_names():
     assert compute_hash([1, 2, 3], 5) == BlockManager.compute_hash([1, 2, 3], 5)
     sp_ = StreamPool(None, [])
     assert sp_.streams == [] and not sp_.greenctx_info.available
+
+
+def test_layer_level_helpers():
+    from fastcache_b200.layers.attention import store_kvcache
+    from fastcache_b200.layers.layernorm import RMSNorm
+    from fastcache_b200.layers.rotary_embedding import apply_rotary_emb, get_rope
+    from fastcache_b200.parallel.tp import get_tp_device
+
+    torch.manual_seed(0)
+    k_cache, v_cache = torch.zeros(3, 2, 4, 8), torch.zeros(3, 2, 4, 8)     # [blocks, Hkv, block, D]
+    k, v = torch.randn(3, 2, 8), torch.randn(3, 2, 8)
+    store_kvcache(k, v, k_cache, v_cache, torch.tensor([5, -1, 9]))
+    assert torch.equal(k_cache[1, :, 1], k[0]) and torch.equal(v_cache[2, :, 1], v[2])
+    assert float(k_cache.abs().sum()) == float(k[0].abs().sum() + k[2].abs().sum())     # slot -1 skipped
+    norm = RMSNorm(8)
+    x, res = torch.randn(4, 8), torch.randn(4, 8)
+    assert torch.equal(norm.rms_forward(x), norm(x))
+    a, b = norm.add_rms_forward(x, res)
+    a2, b2 = norm(x, res)
+    assert torch.equal(a, a2) and torch.equal(b, b2)
+    rope = get_rope(8, 8, 64, 10000.0)
+    pos = torch.tensor([0, 3, 7])
+    q = torch.randn(3, 2, 8)
+    cs = rope.cos_sin_cache[pos]
+    q_rot, _ = rope(pos, q, q)
+    assert torch.allclose(apply_rotary_emb(q, cs[:, None, :4], cs[:, None, 4:]), q_rot)
+    assert torch.allclose(apply_rotary_emb(q[:1], cs[:1, None, :4], cs[:1, None, 4:]), q[:1])     # position 0
+    assert get_tp_device().type in ("cpu", "cuda")
