@@ -14,9 +14,10 @@ Parity with the reference's HuggingFace-based harness:
                                                utils_ccm/utils_kvcachePool.py:22-394
   * ImprovedConcurrentTester, PerformanceMonitor, TestResult (collector + dispatcher threads,
     p50 / p90 / p99, throughput)               scripts/llava_testcon2.6.py:100-222, :385-1695
-The reference drives HuggingFace `generate`; here the tester drives this package's engine, whose
-scheduler already has the prefill / compress / decode queues with their batch caps, so the
-harness supplies the arrival process, the per-stage batching rule for the caps, timing and
+`ConcurrentTester` drives this package's engine (the HuggingFace-model form of the pipeline, with the
+pool and the dynamic scheduler in the loop, is `serving/hf_pipeline.py`).  The engine's
+scheduler already has the prefill / compress / decode queues with their batch caps, so this
+tester supplies the arrival process, the per-stage batching rule for the caps, timing and
 reporting.
 """
 from __future__ import annotations
