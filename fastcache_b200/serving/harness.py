@@ -584,6 +584,77 @@ class PerformanceMonitor:
         pick = lambda q: s[min(len(s) - 1, max(0, int(round(q * (len(s) - 1)))))]  # noqa: E731
         return {"mean": sum(s) / len(s), "p50": pick(0.5), "p90": pick(0.9), "p99": pick(0.99), "max": s[-1]}
 
+    # accumulate-then-report interface of the reference's monitor (scripts/llava_testcon2.6.py:100-222):
+    # results are filed under "orig" or "comp", one entry per finished batch
+    def __init__(self) -> None:
+        self.reset()
+
+    def reset(self) -> None:
+        blank = lambda: {"latencies": [], "throughputs": [], "memory_usage": [], "request_id": [],  # noqa: E731
+                         "request_size": [], "valid_tokens": 0, "success_count": 0, "total_count": 0,
+                         "compression_ratios": [], "compression_times": []}
+        self.results: Dict[str, Dict[str, Any]] = {"orig": blank(), "comp": blank()}
+        self.start_time = time.time()
+
+    def add_result(self, result: Any) -> None:
+        """`result`: an object with `method` ("orig" | "comp"), `latency` = (total, ttft, tpot) seconds,
+        `throughput`, `memory_usage`, `request_id`, `request_size`, `valid_tokens`, `success`, and for
+        "comp" optionally `compression_ratio` / `compression_time`."""
+        d = self.results[getattr(result, "method", "orig")]
+        for key, attr in (("latencies", "latency"), ("throughputs", "throughput"), ("memory_usage", "memory_usage"),
+                          ("request_id", "request_id"), ("request_size", "request_size")):
+            d[key].append(getattr(result, attr, 0))
+        d["valid_tokens"] += int(getattr(result, "valid_tokens", 0))
+        d["success_count"] += int(bool(getattr(result, "success", True)))
+        d["total_count"] += 1
+        for key, attr in (("compression_ratios", "compression_ratio"), ("compression_times", "compression_time")):
+            if getattr(result, attr, None) is not None:
+                d[key].append(getattr(result, attr))
+
+    def proc_latencies(self) -> Tuple[List[float], List[float]]:
+        """Per-request TTFT and TPOT lists (a batch entry counts once per request in it)."""
+        ttft: List[float] = []
+        tpot: List[float] = []
+        for d in self.results.values():
+            for lat, n in zip(d["latencies"], d["request_size"]):
+                ttft += [lat[1]] * int(n)
+                tpot += [lat[2]] * int(n)
+        return ttft, tpot
+
+    def calculate_metrics(self, durations_dict: Optional[Dict[str, List[float]]] = None,
+                          system_completion_times: Optional[float] = None) -> Dict[str, Dict[str, float]]:
+        """`durations_dict`: {"TTFT": [...], "TPOT": [...]} (default: from the filed results);
+        `system_completion_times`: wall seconds of the whole job (default: since `reset`)."""
+        if durations_dict is None:
+            a, b = self.proc_latencies()
+            durations_dict = {"TTFT": a, "TPOT": b}
+        wall = system_completion_times if system_completion_times is not None else time.time() - self.start_time
+        out: Dict[str, Dict[str, float]] = {}
+        for method, d in self.results.items():
+            if not d["latencies"] or not durations_dict["TTFT"]:
+                continue
+            row: Dict[str, float] = {"total_requests": d["total_count"],
+                                     "success_rate": 100.0 * d["success_count"] / max(1, d["total_count"]),
+                                     "requests_per_second": d["total_count"] / wall if wall > 0 else 0.0}
+            for name, xs in (("ttft", durations_dict["TTFT"]), ("tpot", durations_dict["TPOT"])):
+                s_ = sorted(xs)
+                n = len(s_)
+                row.update({f"avg_{name}": sum(s_) / n, f"median_{name}": s_[int(n * 0.5)],
+                            f"p90_{name}": s_[int(n * 0.9)], f"p99_{name}": s_[min(int(n * 0.99), n - 1)],
+                            f"min_{name}": s_[0], f"max_{name}": s_[-1]})
+            mem, thr = d["memory_usage"], d["throughputs"]
+            row["avg_memory_usage"] = sum(mem) / max(1, len(mem))
+            row["avg_throughput"] = d["valid_tokens"] / (wall + 1e-5)
+            mean_thr = sum(thr) / max(1, len(thr))
+            row["throughput_stddev"] = (sum((t - mean_thr) ** 2 for t in thr) / (len(thr) - 1)) ** 0.5 \
+                if len(thr) > 1 else 0.0
+            if method == "comp" and d["compression_ratios"]:
+                row["avg_compression_ratio"] = sum(d["compression_ratios"]) / len(d["compression_ratios"])
+                ct = d["compression_times"]
+                row["avg_compression_time"] = sum(ct) / len(ct) if ct else 0.0
+            out[method] = row
+        return out
+
     def summarise(self, requests: Sequence[Request], wall_s: float, rate: float, stats: Any = None) -> TestResult:
         done = [r for r in requests if r.status is RequestStatus.COMPLETED]
         toks = sum(len(r.output) for r in done)
@@ -713,3 +784,65 @@ class ServiceMiddleware:
     def run_concurrent_test(self, prompts: Sequence[Any], **run_kwargs: Any) -> TestResult:
         self.last = ConcurrentTester(self.llm, **self.kw).run(prompts, **run_kwargs)
         return self.last
+
+
+# ----------------------------------------------------------------------- reporting
+def format_metrics(metrics: Dict[str, Dict[str, float]], output_type: str = "print") -> Optional[str]:
+    """The `calculate_metrics` table as text (printed, returns None) or as a JSON string."""
+    import json
+    if output_type == "json":
+        return json.dumps(metrics, indent=2)
+    lines = ["=== Performance Test Results ==="]
+    for method in ("orig", "comp"):
+        lines.append(f"--- {method.upper()} ---")
+        row = metrics.get(method)
+        if not row:
+            lines.append("no data")
+            continue
+        lines.append(f"requests {row['total_requests']}  success {row['success_rate']:.1f} %  "
+                     f"{row['requests_per_second']:.2f} req/s  {row['avg_throughput']:.1f} tok/s")
+        for name in ("ttft", "tpot"):
+            lines.append(f"{name.upper()} (s): avg {row[f'avg_{name}']:.4f}  p50 {row[f'median_{name}']:.4f}  "
+                         f"p90 {row[f'p90_{name}']:.4f}  p99 {row[f'p99_{name}']:.4f}  "
+                         f"min {row[f'min_{name}']:.4f}  max {row[f'max_{name}']:.4f}")
+        if "avg_compression_ratio" in row:
+            lines.append(f"compression: ratio {row['avg_compression_ratio']:.2f}  "
+                         f"time {row['avg_compression_time']:.4f} s")
+    print("\n".join(lines))
+    return None
+
+
+def print_metrics(metrics: Dict[str, Dict[str, float]]) -> None:
+    format_metrics(metrics, "print")
+
+
+def generate_results_txt(metrics: Dict[str, Dict[str, float]], analyze_times_result: Any,
+                         system_completion_time: float, system_total_generated_lens: int, comp_mode: str,
+                         file_path: str) -> str:
+    """Write the run summary the harness scripts keep per run (scripts/llava_testcon2.6.py:2056-2076)."""
+    import json
+    os_lines = [f"mode: {comp_mode}", format_metrics(metrics, "json") or "",
+                "stage times: " + json.dumps(analyze_times_result, default=str),
+                f"service completed in {system_completion_time:.2f} s",
+                f"service generated {system_total_generated_lens} tokens",
+                f"throughput: {system_total_generated_lens / (system_completion_time + 1e-5):.2f} tokens/s"]
+    with open(file_path, "w") as fh:
+        fh.write("\n".join(os_lines) + "\n")
+    return file_path
+
+
+def print_gpu_memory(step: str) -> float:
+    """MiB allocated by torch on the current device (0 without a GPU); prints it with the label."""
+    mb = torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0
+    print(f"=== {step} ===\nGPU memory allocated: {mb:.2f} MB")
+    return mb
+
+
+def load_checkpoint_only_model(model: Any, filename: str, device: Any = None) -> Any:
+    """Load a compressor `.pth` (any of the three layouts the loaders accept) into `model` in place."""
+    from ..compress.ccm import _extract_state
+    if device is None:
+        device = next(model.parameters()).device
+    blob = torch.load(filename, map_location=device, weights_only=False)
+    model.load_state_dict(_extract_state(blob), strict=False)
+    return model

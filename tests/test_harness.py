@@ -86,3 +86,25 @@ def test_testcon_cli_single_run_and_yaml(tmp_path):
     assert [r["name"] for r in rows] == ["base", "knorm", "broken"]
     assert rows[0]["result"]["completed"] == 3 and rows[0]["batching"] == [5, 5, 5]
     assert rows[1]["result"]["compression"]["compressions"] == 3 and "error" in rows[2]
+
+
+def test_monitor_accumulates_batches_and_reports(tmp_path, capsys):
+    from types import SimpleNamespace as NS
+    import fastcache_b200.serving.harness as h
+    m = h.PerformanceMonitor()
+    m.add_result(NS(method="comp", latency=(1.0, 0.2, 0.01), throughput=100.0, memory_usage=5.0, request_id=[1, 2],
+                    request_size=2, valid_tokens=64, success=True, compression_ratio=4.0, compression_time=0.01))
+    m.add_result(NS(method="comp", latency=(1.5, 0.4, 0.02), throughput=120.0, memory_usage=6.0, request_id=[3],
+                    request_size=1, valid_tokens=32, success=False))
+    assert m.proc_latencies() == ([0.2, 0.2, 0.4], [0.01, 0.01, 0.02])
+    met = m.calculate_metrics(system_completion_times=2.0)
+    row = met["comp"]
+    assert "orig" not in met and row["total_requests"] == 2 and row["success_rate"] == 50.0
+    assert row["median_ttft"] == 0.2 and row["p99_ttft"] == 0.4 and abs(row["avg_throughput"] - 48.0) < 0.01
+    assert row["avg_compression_ratio"] == 4.0 and row["throughput_stddev"] > 0
+    h.print_metrics(met)
+    assert "p90 0.4000" in capsys.readouterr().out
+    path = h.generate_results_txt(met, {"ttft": 0.2}, 2.0, 96, "ccm", str(tmp_path / "r.txt"))
+    assert "throughput: 48.00 tokens/s" in open(path).read()
+    m.reset()
+    assert m.calculate_metrics(system_completion_times=1.0) == {}
