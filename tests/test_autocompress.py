@@ -163,3 +163,18 @@ def test_reference_named_planning_surface(tmp_path):
     assert torch.allclose(gen.generate_dequantize_kernel(8)(q), gen.generate_dequantize_kernel()(q))
     assert gen.generate_sparse_gather_kernel()(torch.arange(6.).reshape(3, 2), torch.tensor([2, 0])).tolist() == \
         [[4.0, 5.0], [0.0, 1.0]]
+
+
+def test_examples_run(capsys):
+    import runpy
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    old = sys.argv
+    try:
+        sys.argv = ["autocompress_demo.py"]
+        runpy.run_path(str(root / "examples" / "autocompress_demo.py"), run_name="__main__")
+    finally:
+        sys.argv = old
+    out = capsys.readouterr().out
+    assert "hardware: NVIDIA B200" in out and "ExecutionPlan for 'mlp'" in out and "best of three" in out
