@@ -444,7 +444,11 @@ def run_serving(args):
                        "image": f"{W}x{H}", "output_len": w["out"], "arrivals": f"Poisson {w['rate']} req/s",
                        "batching": list(w["batching"]), "parallelism": f"tp{world}",
                        "compression": "CCM merge, ratio 4 (" + w["compressor"] + ")" if not args.no_compression else "none",
-                       "greenctx_sms": list(w["greenctx"]) if w["greenctx"] else None, "cuda_graph_decode": True,
+                       "greenctx_sms": list(w["greenctx"]) if w["greenctx"] else None,
+                       "greenctx_active": bool(runner.greenctx_enabled),
+                       "greenctx_sms_actual": [runner._greenctx_info.get("main_sms"),
+                                               runner._greenctx_info.get("compress_sms")]
+                       if runner.greenctx_enabled else None, "cuda_graph_decode": True,
                        "l2": "weights (13-16 GB) stream every step: far larger than the 126 MB L2; no flush needed",
                        "step": "one whole arrival process (all requests, served to completion)",
                        "value_is": "output tokens / device-busy time of the engine steps",

@@ -20,11 +20,14 @@ namespace py = pybind11;
 
 namespace {
 
+// `version`: the CUDA release that introduced the entry point (green contexts: 12.4;
+// cuGreenCtxStreamCreate: 12.5).  Asking for a symbol at an older version than its first
+// one reports "not found" even on a newer driver.
 template <typename Fn>
-Fn resolve(const char* name) {
+Fn resolve(const char* name, unsigned version = 12040) {
   void* ptr = nullptr;
   cudaDriverEntryPointQueryResult q;
-  cudaError_t e = cudaGetDriverEntryPointByVersion(name, &ptr, 12040, cudaEnableDefault, &q);
+  cudaError_t e = cudaGetDriverEntryPointByVersion(name, &ptr, version, cudaEnableDefault, &q);
   if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || ptr == nullptr)
     throw std::runtime_error(std::string("driver entry point not available: ") + name);
   return reinterpret_cast<Fn>(ptr);
@@ -62,7 +65,7 @@ py::dict create_partition(int device, int compress_sms, int main_priority, int c
   auto split = resolve<SplitFn>("cuDevSmResourceSplitByCount");
   auto genDesc = resolve<GenDescFn>("cuDevResourceGenerateDesc");
   auto greenCreate = resolve<GreenCreateFn>("cuGreenCtxCreate");
-  auto greenStream = resolve<GreenStreamFn>("cuGreenCtxStreamCreate");
+  auto greenStream = resolve<GreenStreamFn>("cuGreenCtxStreamCreate", 12050);
 
   CUdevice dev;
   check(deviceGet(&dev, device), "cuDeviceGet");
@@ -103,7 +106,7 @@ py::dict create_partition(int device, int compress_sms, int main_priority, int c
 
 // Extra stream on an existing partition's compression group (round-robin compression streams).
 uint64_t extra_compress_stream(uint64_t compress_stream, int priority) {
-  auto greenStream = resolve<GreenStreamFn>("cuGreenCtxStreamCreate");
+  auto greenStream = resolve<GreenStreamFn>("cuGreenCtxStreamCreate", 12050);
   std::lock_guard<std::mutex> lk(g_mu);
   for (auto& p : g_live) {
     if (reinterpret_cast<uint64_t>(p.stream[1]) == compress_stream) {

@@ -194,9 +194,15 @@ class AutoCompressionController:
     def decide(self, *, batch_size: int, seq_len: int, expected_output_len: int, pending_compressions: int = 0
                ) -> AutoCompressionDecision:
         self._decisions += 1
-        if self._last_decision is not None and self._decisions % self.interval != 0:
+        # the size gate is cheap and is looked at every time: a decision cached for the interval is kept
+        # only while the batch stays on the same side of it (a short warm-up batch must not switch
+        # compression off for the long batches that follow, nor the other way round)
+        too_small = (seq_len < self.min_seq_len or expected_output_len < self.min_output_len) and not self.force
+        if (self._last_decision is not None and self._decisions % self.interval != 0
+                and too_small == getattr(self, "_last_too_small", too_small)):
             return self._last_decision
-        if (seq_len < self.min_seq_len or expected_output_len < self.min_output_len) and not self.force:
+        self._last_too_small = too_small
+        if too_small:
             d = AutoCompressionDecision("none", False, self.streams, self.layers_per_step, False, 0.0, 1.0)
             self.pipeline = "none"
             self._last_decision = d

@@ -178,3 +178,16 @@ def test_examples_run(capsys):
         sys.argv = old
     out = capsys.readouterr().out
     assert "hardware: NVIDIA B200" in out and "ExecutionPlan for 'mlp'" in out and "best of three" in out
+
+
+def test_cached_decision_does_not_outlive_a_change_of_the_size_gate():
+    from fastcache_b200.engine.auto_compress_controller import AutoCompressionController
+    c = AutoCompressionController(compression_backend="kvpress", kvpress_method="knorm", compression_factor=2,
+                                  num_layers=36, num_kv_heads=8, head_dim=128, greenctx_enabled=False,
+                                  decision_interval=4, min_seq_len=256, min_output_len=64, min_speedup=1.05,
+                                  force_compress=False, dual_batch_enabled=False, dual_batch_interval=4)
+    assert c.decide(batch_size=8, seq_len=3072, expected_output_len=4).pipeline == "none"      # warm-up: 4 tokens
+    first = c.decide(batch_size=10, seq_len=3072, expected_output_len=512)                      # inside the interval
+    assert first.pipeline == "prefill"
+    assert c.decide(batch_size=10, seq_len=3072, expected_output_len=512) is first              # cached now
+    assert c.decide(batch_size=10, seq_len=64, expected_output_len=512).pipeline == "none"      # gate flips back
