@@ -49,6 +49,12 @@ class StreamPool:
         return GreenCtxInfo(False, str(self.info.get("fallback", "not requested")))
 
 
+# (device index, compression SMs asked for) -> partition.  A controller that moves the split up and down
+# asks for the same few splits again and again; each is created once and lives until the process ends
+# (green contexts are not freed while their streams may still be referenced by captured graphs).
+_PARTITIONS: Dict[Any, Dict[str, Any]] = {}
+
+
 def try_create_greenctx_streams(device: torch.device, compress_ratio: float, n_compress: int = 1
                                 ) -> Optional[Dict[str, Any]]:
     """Returns {"main", "compress": [...], "main_sms", "compress_sms"} or None."""
@@ -59,6 +65,14 @@ def try_create_greenctx_streams(device: torch.device, compress_ratio: float, n_c
     try:
         total = ext().sm_count(index)
         want = max(1, int(round(total * compress_ratio)))
+        cached = _PARTITIONS.get((index, want))
+        if cached is not None:
+            while len(cached["compress"]) < n_compress:
+                extra = torch.cuda.ExternalStream(
+                    ext().greenctx_extra_stream(cached["compress"][0].cuda_stream, 0), device=device)
+                ext().register_stream_sms(extra.cuda_stream, cached["compress_sms"])
+                cached["compress"].append(extra)
+            return dict(cached, compress=cached["compress"][:n_compress])
         got = ext().greenctx_create(index, want, 0, 0)
         main = torch.cuda.ExternalStream(got["main_stream"], device=device)
         comp = [torch.cuda.ExternalStream(got["compress_stream"], device=device)]
@@ -68,8 +82,10 @@ def try_create_greenctx_streams(device: torch.device, compress_ratio: float, n_c
         ext().register_stream_sms(got["main_stream"], got["main_sms"])
         for s in comp:
             ext().register_stream_sms(s.cuda_stream, got["compress_sms"])
-        return {"main": main, "compress": comp, "main_sms": got["main_sms"],
+        part = {"main": main, "compress": comp, "main_sms": got["main_sms"],
                 "compress_sms": got["compress_sms"], "total_sms": got["total_sms"]}
+        _PARTITIONS[(index, want)] = part
+        return dict(part, compress=list(comp))
     except Exception as exc:                      # driver too old, MIG, resources exhausted ...
         print(f"[fastcache_b200] green contexts unavailable ({exc}); using stream priorities")
         return None

@@ -254,3 +254,49 @@ def test_layer_level_helpers():
     assert torch.allclose(apply_rotary_emb(q, cs[:, None, :4], cs[:, None, 4:]), q_rot)
     assert torch.allclose(apply_rotary_emb(q[:1], cs[:1, None, :4], cs[:1, None, 4:]), q[:1])     # position 0
     assert get_tp_device().type in ("cpu", "cuda")
+
+
+def test_green_context_partitions_are_created_once_per_split(monkeypatch):
+    """Against a fake extension: the same SM split asked for twice reuses its partition; more compression
+    streams are added to it on demand; another split is another partition."""
+    import fastcache_b200.ops.loader as loader
+    import fastcache_b200.utils.streams as streams
+
+    class FakeExt:
+        def __init__(self):
+            self.created, self.extra, self.registered = [], 0, {}
+
+        def sm_count(self, index):
+            return 148
+
+        def greenctx_create(self, index, want, a, b):
+            self.created.append(want)
+            base = 1000 * len(self.created)
+            return {"main_stream": base + 1, "compress_stream": base + 2, "main_sms": 148 - want,
+                    "compress_sms": want, "total_sms": 148}
+
+        def greenctx_extra_stream(self, compress_stream, prio):
+            self.extra += 1
+            return compress_stream + 10 * self.extra
+
+        def register_stream_sms(self, ptr, sms):
+            self.registered[ptr] = sms
+
+    class FakeStream:
+        def __init__(self, ptr, device=None):
+            self.cuda_stream = ptr
+
+    fake = FakeExt()
+    monkeypatch.setattr(loader, "ext", lambda: fake)
+    monkeypatch.setattr(loader, "ext_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "ExternalStream", FakeStream)
+    monkeypatch.setattr(streams, "_PARTITIONS", {})
+    dev = torch.device("cuda", 0)
+    a = streams.try_create_greenctx_streams(dev, 36 / 148, 1)
+    b = streams.try_create_greenctx_streams(dev, 36 / 148, 2)
+    c = streams.try_create_greenctx_streams(dev, 36 / 148, 1)
+    assert fake.created == [36] and a["main"] is b["main"] is c["main"]
+    assert len(a["compress"]) == 1 and len(b["compress"]) == 2 and len(c["compress"]) == 1 and fake.extra == 1
+    assert b["compress"][0] is a["compress"][0] and fake.registered[b["compress"][1].cuda_stream] == 36
+    d = streams.try_create_greenctx_streams(dev, 0.40, 1)
+    assert fake.created == [36, 59] and d["compress_sms"] == 59 and d["main"] is not a["main"]
