@@ -386,6 +386,90 @@ def finetune_com_minicpm(model: Any, samples: Sequence[Any], model_config: Any =
                    compression_ratio, train_ratio, is_continue, strategy)
 
 
+# ------------------------------------------------------------- script-level helpers
+# Helper names of the reference's fine-tuning scripts (scripts/finetune_llava.py:29-81, :237-250, :948-951;
+# scripts/finetune_minicpm.py:118-123, :254-265, :785-860).
+def set_seed(seed: int) -> None:
+    import random
+    random.seed(seed)
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed)
+
+
+def save_checkpoint(epoch: int, model: _CCMBase, optimizer: Any, scheduler: Any, loss: float, is_best: bool,
+                    filefoldname: str = "ckpt_store", filename: str = "checkpoint.pth") -> str:
+    """`last_<filename>` always, `best_<filename>` when `is_best`; the layout of `save_compressor`."""
+    os.makedirs(filefoldname, exist_ok=True)
+    last = os.path.join(filefoldname, f"last_{filename}")
+    save_compressor(model, last, epoch, optimizer, scheduler, loss)
+    if is_best:
+        save_compressor(model, os.path.join(filefoldname, f"best_{filename}"), epoch, optimizer, scheduler, loss)
+    return last
+
+
+def load_checkpoint(model: _CCMBase, optimizer: Any = None, scheduler: Any = None,
+                    filename: str = "checkpoint.pth") -> Tuple[int, float]:
+    """Restore compressor, optimizer and scheduler; returns (epoch, loss), or (0, inf) without a file."""
+    if not os.path.isfile(filename):
+        return 0, float("inf")
+    blob = torch.load(filename, map_location="cpu", weights_only=False)
+    state = blob["model_state_dict"]
+    model.load_state_dict(state.get("compressor", state))
+    if optimizer is not None and blob.get("optimizer_state_dict"):
+        optimizer.load_state_dict(blob["optimizer_state_dict"])
+    if scheduler is not None and blob.get("scheduler_state_dict"):
+        scheduler.load_state_dict(blob["scheduler_state_dict"])
+    return int(blob.get("epoch", 0)), float(blob.get("loss", float("inf")))
+
+
+def load_finetune_compressor(compressor_path: str, src_config: Any = None, device: Any = None) -> _CCMBase:
+    """The compressor class that matches the file, with its weights, in eval mode on `device`."""
+    m = load_compressor(compressor_path, src_config=src_config)
+    return (m.to(device) if device is not None else m).eval()
+
+
+def parse_string_with_image(text: str, special_token: str = "<image>") -> Tuple[str, int]:
+    """(text without the image marker, 1 if the marker was there else 0)."""
+    if special_token in text:
+        return text.replace(special_token, "").strip(), 1
+    return text, 0
+
+
+def load_text_data(json_path: str, num_samples: int, seed: Optional[int] = None) -> List[str]:
+    """First human turn of every conversation of a ShareGPT / LLaVA-style JSON, whitespace-normalised,
+    shuffled; `num_samples` < 0 keeps all."""
+    import json
+    import random
+    with open(json_path, "r", encoding="utf-8") as fh:
+        data = json.load(fh)
+    texts = [" ".join(d["conversations"][0]["value"].split()) for d in data
+             if d.get("conversations") and d["conversations"][0].get("from") == "human"]
+    random.Random(seed).shuffle(texts)
+    return texts if num_samples < 0 else texts[:num_samples]
+
+
+@torch.no_grad()
+def validate(compressor: _CCMBase, forward_with_kv: Callable, val_batches: Iterable[Any],
+             it_len_of: Callable[[Any], Sequence[int]] = lambda b: (0, 0),
+             loss_fn: Optional[KVCacheCompressionLoss] = None) -> Tuple[float, float]:
+    """(mean loss, mean agreement with the original-KV predictions) over `val_batches`."""
+    loss_fn = loss_fn or KVCacheCompressionLoss("logit")
+    compressor.eval()
+    tot = acc = n = 0.0
+    for batch in val_batches:
+        _, _, kv = forward_with_kv(batch, None)
+        t_logits, t_hidden, _ = forward_with_kv(batch, kv)
+        s_logits, s_hidden, _ = forward_with_kv(batch, compressor(kv, it_len_of(batch)))
+        loss, _ = loss_fn(s_logits, t_logits, None, s_hidden, t_hidden)
+        tot, acc, n = tot + float(loss), acc + loss_fn.accuracy(s_logits, t_logits), n + 1
+    return tot / max(1.0, n), acc / max(1.0, n)
+
+
+validate_llava = validate_minicpm = validate
+finetune_com = finetune_llava
+
+
 def main(argv: Optional[Sequence[str]] = None) -> Dict[str, Any]:
     """`python -m fastcache_b200.compress.train --model-path DIR --data FILE.json ...` fine-tunes a
     compressor for a HuggingFace checkpoint.  Samples come from the dataset loaders of

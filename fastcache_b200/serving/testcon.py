@@ -184,6 +184,9 @@ def run_one(args: argparse.Namespace, g: Dict[str, Any], exp: Experiment) -> Dic
         llm.exit()
 
 
+exec_testit = run_one          # the reference's name for "run one configuration"
+
+
 def write_result(folder: str, row: Dict[str, Any]) -> str:
     """One text file per run, named for the run (the reference writes `.txt` summaries, :2056-2076)."""
     os.makedirs(folder, exist_ok=True)

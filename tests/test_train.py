@@ -147,3 +147,34 @@ def test_training_datasets_encode_turns():
     items = CustomImageTextDataset(conv, Proc(), max_length=8)[0]
     assert len(items) == 2 and items[0]["input_ids"].shape == (8,) and items[0]["pixel_values"].shape == (3, 4, 4)
     assert CustomImageTextDataset(conv, Proc(), 8, launch_padding_flag=False)[0][0]["input_ids"].shape == (3,)
+
+
+def test_script_level_helpers(tmp_path):
+    import json
+    from fastcache_b200.compress import train as T
+    comp = KVCacheLinearDecoupleCompressor(None, 2, 1, n_layer=2, nhead=2, head_dim=8)
+    opt = torch.optim.Adam(comp.parameters(), lr=1e-3)
+    sched = torch.optim.lr_scheduler.ReduceLROnPlateau(opt)
+    last = T.save_checkpoint(3, comp, opt, sched, 0.25, True, str(tmp_path), "c.pth")
+    assert os.path.exists(last) and os.path.exists(tmp_path / "best_c.pth")
+    other = KVCacheLinearDecoupleCompressor(None, 2, 1, n_layer=2, nhead=2, head_dim=8)
+    assert T.load_checkpoint(other, torch.optim.Adam(other.parameters()), None, last) == (3, 0.25)
+    assert all(torch.equal(a, b) for a, b in zip(comp.state_dict().values(), other.state_dict().values()))
+    assert T.load_checkpoint(other, None, None, str(tmp_path / "none.pth")) == (0, float("inf"))
+    assert T.load_finetune_compressor(last).compression_factor == 2
+    assert T.parse_string_with_image("<image>\nWhat is this?") == ("What is this?", 1)
+    assert T.parse_string_with_image("plain") == ("plain", 0)
+    data = [{"conversations": [{"from": "human", "value": "a   b\nc"}, {"from": "gpt", "value": "x"}]},
+            {"conversations": [{"from": "gpt", "value": "skip"}]}, {"conversations": []}]
+    path = tmp_path / "t.json"
+    path.write_text(json.dumps(data))
+    assert T.load_text_data(str(path), -1) == ["a b c"]
+    fwd = _toy()
+    mk = lambda s: [(torch.randn(2, 2, 12, 8, generator=torch.Generator().manual_seed(s + l)),
+                     torch.randn(2, 2, 12, 8, generator=torch.Generator().manual_seed(9 + s + l))) for l in range(2)]
+    loss, acc = T.validate_llava(comp, fwd, [mk(0), mk(1)], it_len_of=lambda b: (4, 8))
+    assert loss > 0 and 0.0 <= acc <= 1.0
+    T.set_seed(3)
+    a = torch.rand(1)
+    T.set_seed(3)
+    assert torch.equal(a, torch.rand(1)) and T.finetune_com is T.finetune_llava
