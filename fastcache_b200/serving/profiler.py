@@ -77,6 +77,31 @@ class LLMIntensityAnalyzer:
         """Bytes of one all-reduce payload ([tokens, hidden])."""
         return float(tokens) * self.h * self.b
 
+    # ---- tensor-driven interface (utils_ccm/utils_profiler.py:294-428): built from a config, fed the step's tensors
+    peak_tflops = 1590.0
+
+    @classmethod
+    def from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
+        """Build the analyzer from a HuggingFace config, a model directory or a config wrapper."""
+        w = _as_wrapper(config)
+        a = cls(w.hidden_size, w.num_hidden_layers, w.num_attention_heads, w.num_key_value_heads, w.head_dim,
+                w.intermediate_size, w.vocab_size, w.dtype_size, tp)
+        a.config = w
+        a.peak_tflops = peak_tflops
+        return a
+
+    def analyze_prefill(self, input_ids, position_ids=None, attention_mask=None) -> Dict:
+        B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
+        c = self.prefill(B, S)
+        out = B * S * (self.kv_bytes_per_token() + self.h * self.b) + B * self.vocab * self.b
+        return _stats(c, B, S, out).report("prefill", self.peak_tflops)
+
+    def analyze_decode(self, input_ids, past_key_values, position_ids=None, attention_mask=None, **_) -> Dict:
+        B = 1 if input_ids.dim() == 1 else input_ids.shape[0]
+        ctx = int(past_key_values[0][0].shape[2]) if past_key_values else 0
+        c = self.decode(B, ctx)
+        return _stats(c, B, ctx + 1, B * (self.kv_bytes_per_token() + self.vocab * self.b)).report("decode", self.peak_tflops)
+
 
 class VisionEncoderAnalyzer:
     def __init__(self, hidden: int = 1024, layers: int = 24, heads: int = 16, mlp: int = 4096, patches: int = 577,
@@ -89,6 +114,10 @@ class VisionEncoderAnalyzer:
         attn = 4.0 * images * self.n * self.n * self.h * self.L
         byts = self.L * (4 * self.h * self.h + 2 * self.h * self.mlp) * self.b + 10.0 * T * self.h * self.b * self.L
         return PhaseCost(gemm + attn, byts)
+
+    def analyze_vision_encoding(self, batch_size: int = 1) -> ComputeStats:
+        c = self.encode(batch_size)
+        return _stats(c, batch_size, self.n, batch_size * self.n * self.h * self.b)
 
 
 class LLaVAIntensityAnalyzer:
@@ -113,12 +142,61 @@ class LLaVAIntensityAnalyzer:
         out["decode_per_token"] = self.llm.decode(1, ctx + out_tokens // 2)
         return out
 
+    # ---- tensor-driven interface (utils_ccm/utils_profiler.py:622-908): built from a config, fed the step's tensors
+    @classmethod
+    def from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
+        w = _as_wrapper(config, LLaVAConfigWrapper)
+        v = w.vision_config
+        n = (v["image_size"] // v["patch_size"]) ** 2 + 1
+        a = cls(LLMIntensityAnalyzer.from_config(w, peak_tflops, tp),
+                VisionEncoderAnalyzer(v["hidden_size"], v["num_hidden_layers"], v["num_attention_heads"],
+                                      v["intermediate_size"], n, v["patch_size"], w.dtype_size), w.hidden_size)
+        a.config = w
+        return a
 
-# ----------------------------------------------------------- tensor-driven interface
+    def analyze_multimodal_prefill(self, input_ids, pixel_values=None, **_) -> Dict:
+        B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
+        total, rows = ComputeStats(batch_size=B), S
+        if pixel_values is not None:
+            n_img = len(pixel_values)
+            total = total + self.vision.analyze_vision_encoding(n_img)
+            p = self.projection(n_img)
+            total = total + _stats(p, n_img, self.vision.n - 1, n_img * (self.vision.n - 1) * self.proj * 2.0)
+            rows = S + self.vision.n - 2           # the placeholder token becomes n - 1 feature rows
+        c = self.llm.prefill(B, rows)
+        total = total + _stats(c, B, rows, B * rows * self.llm.kv_bytes_per_token())
+        return total.report("multimodal_prefill", self.llm.peak_tflops)
+
+    def analyze_decode(self, input_ids, past_key_values, **kw) -> Dict:
+        return self.llm.analyze_decode(input_ids, past_key_values, **kw)
+
+    def analyze_kv_cache_compression(self, kv_cache, image_len: int, text_len: int,
+                                            compression_factor: int = 2) -> Dict:
+        """Cost of the merge MLPs over a cache given as per-layer (K, V) of shape [B, H, S, D]: each
+        segment of at least `compression_factor` rows is merged, K and V each through a
+        (D f -> D -> D -> D) MLP shared by all heads."""
+        B, H, _, D = kv_cache[0][0].shape
+        b = kv_cache[0][0].element_size()
+        f = compression_factor
+        weights = (D * f * D + 2 * D * D + 3 * D) * b
+        total = ComputeStats(batch_size=B, seq_length=image_len + text_len)
+        for _layer in kv_cache:
+            for seg in (image_len, text_len):
+                if seg < f:
+                    continue
+                rows = B * H * (seg // f)
+                one = ComputeStats(2.0 * rows * (D * f * D + 2 * D * D), rows * D * f * b + weights, rows * D * b, B,
+                                   image_len + text_len)
+                total = total + one + one           # K and V
+        return total.report("kv_cache_compression", self.llm.peak_tflops)
+
+
+# ------------------------------------------------- types of the tensor-driven interface
 # The reference's analyzers are built from a HuggingFace config and take the step's tensors
-# (utils_ccm/utils_profiler.py:8-160, :294-428, :520-908).  The classes below give that interface on top
-# of the shape-driven cost model above; "theoretical_time" uses the peak passed in (the reference
-# hard-codes the A100's 312 TFLOP/s).
+# (utils_ccm/utils_profiler.py:8-160, :294-428, :520-908).  `from_config` / `analyze_*` of the classes
+# above give that interface on top of the shape-driven cost model; these are the types they return and
+# the config views they read.  "theoretical_time" uses the peak passed in (the reference hard-codes the
+# A100's 312 TFLOP/s).
 @dataclass
 class ComputeStats:
     flops: float = 0
@@ -226,95 +304,3 @@ def _stats(cost: PhaseCost, batch: int, seq: int, write_bytes: float) -> Compute
     return ComputeStats(cost.flops, cost.bytes - w, w, batch, seq)
 
 
-def _llm_analyze_prefill(self, input_ids, position_ids=None, attention_mask=None) -> Dict:
-    B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
-    c = self.prefill(B, S)
-    out = B * S * (self.kv_bytes_per_token() + self.h * self.b) + B * self.vocab * self.b
-    return _stats(c, B, S, out).report("prefill", self.peak_tflops)
-
-
-def _llm_analyze_decode(self, input_ids, past_key_values, position_ids=None, attention_mask=None, **_) -> Dict:
-    B = 1 if input_ids.dim() == 1 else input_ids.shape[0]
-    ctx = int(past_key_values[0][0].shape[2]) if past_key_values else 0
-    c = self.decode(B, ctx)
-    return _stats(c, B, ctx + 1, B * (self.kv_bytes_per_token() + self.vocab * self.b)).report("decode", self.peak_tflops)
-
-
-def _llm_from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
-    """Build the analyzer from a HuggingFace config, a model directory or a config wrapper."""
-    w = _as_wrapper(config)
-    a = cls(w.hidden_size, w.num_hidden_layers, w.num_attention_heads, w.num_key_value_heads, w.head_dim,
-            w.intermediate_size, w.vocab_size, w.dtype_size, tp)
-    a.config = w
-    a.peak_tflops = peak_tflops
-    return a
-
-
-LLMIntensityAnalyzer.peak_tflops = 1590.0
-LLMIntensityAnalyzer.from_config = classmethod(_llm_from_config)
-LLMIntensityAnalyzer.analyze_prefill = _llm_analyze_prefill
-LLMIntensityAnalyzer.analyze_decode = _llm_analyze_decode
-
-
-def _vision_analyze(self, batch_size: int = 1) -> ComputeStats:
-    c = self.encode(batch_size)
-    return _stats(c, batch_size, self.n, batch_size * self.n * self.h * self.b)
-
-
-VisionEncoderAnalyzer.analyze_vision_encoding = _vision_analyze
-
-
-def _llava_from_config(cls, config, peak_tflops: float = 1590.0, tp: int = 1):
-    w = _as_wrapper(config, LLaVAConfigWrapper)
-    v = w.vision_config
-    n = (v["image_size"] // v["patch_size"]) ** 2 + 1
-    a = cls(LLMIntensityAnalyzer.from_config(w, peak_tflops, tp),
-            VisionEncoderAnalyzer(v["hidden_size"], v["num_hidden_layers"], v["num_attention_heads"],
-                                  v["intermediate_size"], n, v["patch_size"], w.dtype_size), w.hidden_size)
-    a.config = w
-    return a
-
-
-def _llava_analyze_multimodal_prefill(self, input_ids, pixel_values=None, **_) -> Dict:
-    B, S = (1, input_ids.shape[0]) if input_ids.dim() == 1 else input_ids.shape
-    total, rows = ComputeStats(batch_size=B), S
-    if pixel_values is not None:
-        n_img = len(pixel_values)
-        total = total + self.vision.analyze_vision_encoding(n_img)
-        p = self.projection(n_img)
-        total = total + _stats(p, n_img, self.vision.n - 1, n_img * (self.vision.n - 1) * self.proj * 2.0)
-        rows = S + self.vision.n - 2           # the placeholder token becomes n - 1 feature rows
-    c = self.llm.prefill(B, rows)
-    total = total + _stats(c, B, rows, B * rows * self.llm.kv_bytes_per_token())
-    return total.report("multimodal_prefill", self.llm.peak_tflops)
-
-
-def _llava_analyze_decode(self, input_ids, past_key_values, **kw) -> Dict:
-    return self.llm.analyze_decode(input_ids, past_key_values, **kw)
-
-
-def _llava_analyze_kv_cache_compression(self, kv_cache, image_len: int, text_len: int,
-                                        compression_factor: int = 2) -> Dict:
-    """Cost of the merge MLPs over a cache given as per-layer (K, V) of shape [B, H, S, D]: each
-    segment of at least `compression_factor` rows is merged, K and V each through a
-    (D f -> D -> D -> D) MLP shared by all heads."""
-    B, H, _, D = kv_cache[0][0].shape
-    b = kv_cache[0][0].element_size()
-    f = compression_factor
-    weights = (D * f * D + 2 * D * D + 3 * D) * b
-    total = ComputeStats(batch_size=B, seq_length=image_len + text_len)
-    for _layer in kv_cache:
-        for seg in (image_len, text_len):
-            if seg < f:
-                continue
-            rows = B * H * (seg // f)
-            one = ComputeStats(2.0 * rows * (D * f * D + 2 * D * D), rows * D * f * b + weights, rows * D * b, B,
-                               image_len + text_len)
-            total = total + one + one           # K and V
-    return total.report("kv_cache_compression", self.llm.peak_tflops)
-
-
-LLaVAIntensityAnalyzer.from_config = classmethod(_llava_from_config)
-LLaVAIntensityAnalyzer.analyze_multimodal_prefill = _llava_analyze_multimodal_prefill
-LLaVAIntensityAnalyzer.analyze_decode = _llava_analyze_decode
-LLaVAIntensityAnalyzer.analyze_kv_cache_compression = _llava_analyze_kv_cache_compression
