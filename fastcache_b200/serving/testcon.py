@@ -90,6 +90,9 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
     p.add_argument("--fixed_spacing", action="store_true", help="arrivals every 1 / rate s instead of Poisson")
     p.add_argument("--no_log", action="store_true")
     p.add_argument("--gpu_info_path", default=None, help="CSV of sampled GPU utilisation / memory")
+    p.add_argument("--engine", default="fastcache", choices=["fastcache", "hf"],
+                   help="fastcache: this package's engine; hf: the three-stage pipeline over a HuggingFace causal LM "
+                   "(text prompts of the dataset; without --model_path a tiny random Llama)")
     p.add_argument("--device", default="cuda:0" if torch.cuda.is_available() else "cpu")
     p.add_argument("--kv_blocks", type=int, default=0)
     p.add_argument("--block_size", type=int, default=256)
@@ -166,7 +169,58 @@ def build_engine(args: argparse.Namespace, exp: Experiment):
                enforce_eager=cpu, prefix_caching=False, compression_pipeline="prefill", **kw)
 
 
+def run_one_hf(args: argparse.Namespace, g: Dict[str, Any], exp: Experiment) -> Dict[str, Any]:
+    """The same run through `serving/hf_pipeline.py`: HuggingFace model, KV pool, dynamic scheduler."""
+    import transformers
+    from ..compress.ccm import KVCacheLinearDecoupleCompressor, load_compressor
+    from ..compress.kvpress_compat import create_kvpress_compressor
+    from .hf_pipeline import HFPipelineTester, TransformersBackend
+    if args.model_path:
+        model = transformers.AutoModelForCausalLM.from_pretrained(args.model_path, trust_remote_code=True)
+        tok = transformers.AutoTokenizer.from_pretrained(args.model_path, trust_remote_code=True)
+    else:
+        cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                       num_attention_heads=4, num_key_value_heads=2, vocab_size=600,
+                                       max_position_embeddings=2048)
+        torch.manual_seed(args.seed)
+        model, tok = transformers.LlamaForCausalLM(cfg), None
+    model = model.eval().to(args.device)
+    c = model.config
+    kw = exp.engine_kwargs()
+    comp = None
+    if kw.get("compression_backend") == "mlp":
+        if args.ckpt_path:
+            comp = load_compressor(args.ckpt_path, compression_factor=kw["compression_factor"], min_seq_len=2)
+        else:
+            torch.manual_seed(0)
+            hd = getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads
+            comp = KVCacheLinearDecoupleCompressor(None, kw["compression_factor"], 2, n_layer=c.num_hidden_layers,
+                                                   nhead=2, head_dim=hd)
+        comp = comp.to(args.device).eval()
+    elif kw.get("compression_backend") == "kvpress":
+        comp = create_kvpress_compressor(kw["kvpress_method"], kw["compression_factor"])
+    rng = torch.Generator().manual_seed(int(g["seed"]))
+    n, length = int(g["num_samples"]), min(int(g["max_input_tokens"]), 64)
+    if tok is None or args.datasets_name == "synthetic":
+        prompts = [torch.randint(3, c.vocab_size, (length,), generator=rng).tolist() for _ in range(n)]
+    else:
+        got = load_image_data(args.datasets_js_path, args.datasets_img_path, n, seed=int(g["seed"]))
+        prompts = [tok.encode(s_.prompt)[: int(g["max_input_tokens"])] for s_ in got]
+    tester = HFPipelineTester(TransformersBackend(model), comp, batching_for(args, exp), float(g["req_per_sec"]),
+                              pad_token_id=getattr(c, "pad_token_id", None) or 0, seed=int(g["seed"]),
+                              monitor_gpu=bool(args.gpu_info_path))
+    res = tester.run_concurrent_test(prompts, int(g["max_new_tokens"]), poisson=not args.fixed_spacing)
+    if args.gpu_info_path and tester.monitor is not None:
+        tester.monitor.save_stats(args.gpu_info_path)
+    summary, _ = tester.timestamps.analyze_timestamps()
+    return {"name": exp.name, "comp_mode": exp.comp_mode, "use_compression": exp.use_compression,
+            "compression_ratio": exp.compression_ratio, "batching": batching_for(args, exp), "engine": "hf",
+            "result": res.to_dict(), "stage_averages": summary["average_times"]}
+
+
 def run_one(args: argparse.Namespace, g: Dict[str, Any], exp: Experiment) -> Dict[str, Any]:
+    if getattr(args, "engine", "fastcache") == "hf":
+        return run_one_hf(args, g, exp)
     llm = build_engine(args, exp)
     try:
         prompts, images = samples_for(args, g, llm.model_runner.model, llm.tokenizer)

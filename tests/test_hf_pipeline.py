@@ -89,3 +89,13 @@ def test_a_failing_batch_is_reported_not_raised():
                               max_wait_time=0.02)
     res = tester.run_concurrent_test(_prompts()[:3], max_new_tokens=3)
     assert res.failed == 3 and res.completed == 0 and "compressor down" in res.compression["errors"][0]
+
+
+def test_cli_runs_the_hf_pipeline():
+    from fastcache_b200.serving import testcon
+    rows = testcon.main(["--engine", "hf", "--device", "cpu", "--use_compression", "--comp_mode", "ccm",
+                         "--num_samples", "4", "--max_new_tokens", "4", "--req_per_sec", "300", "--no_log",
+                         "--prefill_batch_size", "2", "--compress_batch_size", "2", "--decoding_batch_size", "4"])
+    r = rows[0]
+    assert r["engine"] == "hf" and r["result"]["completed"] == 4 and r["result"]["output_tokens"] == 16
+    assert r["result"]["compression"]["calls"] == 4 and r["stage_averages"]["generated_lens"] == 4.0
