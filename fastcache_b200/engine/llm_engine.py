@@ -440,6 +440,8 @@ class LLMEngine:
     # ----------------------------------------------------------------------- step
     def step(self, apply_compression: Optional[bool] = None) -> Tuple[List[Tuple[int, List[int]]], int]:
         sch, r = self.scheduler, self.model_runner
+        if r.model is None:
+            raise RuntimeError("this engine was shut down with exit(); build a new one")
         compress = self.enable_compression if apply_compression is None else \
             (apply_compression and self.enable_compression)
         mode = self.compression_mode
