@@ -39,6 +39,9 @@ class Config:
     # compression policy
     compression_mode: str = "none"   # none | eager | async | lazy
     lazy_occupancy_threshold: float = 0.9
+    # > 0: a prompt that does not fit the rest of a prefill step's token budget is prefetched in pieces of at
+    # least this many rows over several steps (text requests only); 0: a prompt is never split
+    chunked_prefill_tokens: int = 0
     # position id of a token decoded after compression:
     #   "compressed": kv length after compression (reference engine behaviour)
     #   "original":   number of tokens the request has really seen

@@ -475,7 +475,8 @@ class LLMEngine:
         if self.trace is not None:
             bm = sch.block_manager
             rec = self.trace.begin(self.stats.steps, "prefill" if is_prefill else "decode", len(seqs),
-                                   sum(s.logical_len - s.num_cached_tokens for s in seqs) if is_prefill else len(seqs),
+                                   sum((s.logical_len if s.prefill_end is None else s.prefill_end) - s.prefill_start
+                                       for s in seqs) if is_prefill else len(seqs),
                                    len(bm.free_block_ids), len(bm.blocks), self.stats.compressions, r.main_stream)
         with nvtx_range("prefill" if is_prefill else "decode"):
             tokens = r.run(seqs, is_prefill)
@@ -484,17 +485,18 @@ class LLMEngine:
         self._end_timing(ctl, timing, is_prefill, seqs)
         now = time.perf_counter()
         if is_prefill:
-            n_tok = sum(s.logical_len - s.num_cached_tokens for s in seqs)
-            for s in seqs:
+            n_tok = sum((s.logical_len if s.prefill_end is None else s.prefill_end) - s.prefill_start for s in seqs)
+            whole = [s for s in seqs if s.prefill_end is None]          # not a piece of a split prompt
+            for s in whole:
                 if s.first_token_time is None:
                     s.first_token_time = now
             if compress and mode in ("eager", "async") and pipeline != "none":
                 if pipeline == "decode":
-                    self._start_chunked(list(seqs))
+                    self._start_chunked(whole)
                 elif use_async or mode == "async":
-                    self._launch_async(list(seqs))
+                    self._launch_async(whole)
                 else:
-                    self._compress_now(list(seqs))
+                    self._compress_now(whole)
         else:
             n_tok = -len(seqs)
         finished = sch.postprocess(seqs, tokens)

@@ -289,12 +289,12 @@ class ModelRunner:
                 p = s.image_token_pos
                 toks = np.concatenate([toks[:p], np.full(s.num_image_tokens, toks[p], dtype=np.int64),
                                        toks[p + 1:]])
-            n = toks.shape[0]
-            start = s.num_cached_tokens
+            start = s.prefill_start
+            n = toks.shape[0] if s.prefill_end is None else int(s.prefill_end)     # a piece of a split prompt
             rows = np.arange(start, n, dtype=np.int64)
             if s.has_image:
                 image_rows.append((si, cu_q[-1] + s.image_token_pos - start, s.num_image_tokens))
-            ids.append(toks[start:])
+            ids.append(toks[start:n])
             pos.append(rows)
             table = np.asarray(s.block_table, dtype=np.int64)
             slots.append(table[rows // bs] * bs + rows % bs)

@@ -38,6 +38,9 @@ class Scheduler:
         self.compress_cap = config.compress_batch_size or config.max_num_seqs
         self.decode_cap = config.decode_batch_size or config.max_num_seqs
         self.lazy_threshold = config.lazy_occupancy_threshold
+        self.chunk_min = int(getattr(config, "chunked_prefill_tokens", 0) or 0)
+        # rows kept for the last piece of a split prompt (the scorers' observation window reads them)
+        self.chunk_tail = 64
         self.one_image_per_prefill = bool(config.extra.get("one_image_per_prefill", False))
         self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size,
                                           prefix_caching=config.prefix_caching)
@@ -58,6 +61,11 @@ class Scheduler:
 
     # ----------------------------------------------------------------- prefill
     def _schedule_prefill(self) -> List[Sequence]:
+        """Requests from the head of `waiting` while they fit the step's token budget.  With
+        `chunked_prefill_tokens` set, a text prompt that does not fit the rest of the budget is split: the
+        piece that fits runs now, the request keeps its blocks and its place at the head of `waiting`, and
+        later steps continue where it stopped (`Sequence.num_computed_tokens`); only the last piece samples
+        a token and moves the request to `running`."""
         picked: List[Sequence] = []
         tokens = 0
         while self.waiting and len(picked) < self.prefill_cap \
@@ -65,13 +73,25 @@ class Scheduler:
             seq = self.waiting[0]
             if self.one_image_per_prefill and seq.has_image and picked:
                 break
-            cost = seq.prompt_rows + seq.num_completion_tokens - seq.num_cached_tokens
-            if tokens + cost > self.max_num_batched_tokens and picked:
+            room = self.max_num_batched_tokens - tokens
+            rows = seq.prompt_rows + seq.num_completion_tokens
+            cost = rows - seq.prefill_start
+            if cost > room and self._piece(seq, cost, room) <= 0:
                 break
-            if tokens + cost > self.max_num_batched_tokens or not self.block_manager.can_allocate(seq):
-                break
-            self.block_manager.allocate(seq)
-            tokens += seq.logical_len - seq.num_cached_tokens
+            if not seq.block_table:             # first time: a request whose earlier pieces ran keeps its blocks
+                if not self.block_manager.can_allocate(seq):
+                    break
+                self.block_manager.allocate(seq)
+                cost = rows - seq.prefill_start             # prefix-cache hits shorten it
+            piece = self._piece(seq, cost, room) if cost > room else 0
+            if cost > room and piece <= 0:
+                break                            # the blocks stay with the request; it is tried again next step
+            if piece > 0:
+                seq.prefill_end = seq.prefill_start + piece
+                self.running.extend(picked)
+                return picked + [seq]
+            seq.prefill_end = None
+            tokens += cost
             seq.status = SequenceStatus.RUNNING
             self.waiting.popleft()
             picked.append(seq)
@@ -79,6 +99,20 @@ class Scheduler:
                 break
         self.running.extend(picked)
         return picked
+
+    def _piece(self, seq: Sequence, cost: int, room: int) -> int:
+        """Rows of `seq` to prefetch now when its `cost` rows exceed the `room` left in the step (0: do not
+        split).  The last `chunk_tail` rows are kept for the final piece where possible.  A piece shorter
+        than `chunked_prefill_tokens` is only cut when the step would otherwise be empty (the request has
+        the whole budget to itself and still cannot finish)."""
+        if self.chunk_min <= 0 or seq.has_image:
+            return 0
+        take = min(room, cost - self.chunk_tail)
+        if take >= self.chunk_min:
+            return take
+        if room < self.max_num_batched_tokens:       # other requests share the step: wait for an emptier one
+            return 0
+        return take if take > 0 else min(room, cost - 1)
 
     # ------------------------------------------------------------------ decode
     def _schedule_decode(self) -> List[Sequence]:
@@ -148,6 +182,10 @@ class Scheduler:
             self.finish(seq)
         else:
             seq.status = SequenceStatus.FINISHED
+            if seq.block_table:                      # a split prompt whose first pieces are in the pool
+                self.block_manager.deallocate(seq)
+                if self.on_release is not None:
+                    self.on_release(seq)
             try:
                 self.compress_queue.remove(seq)
             except ValueError:
@@ -157,6 +195,10 @@ class Scheduler:
     def requeue_running(self) -> int:
         """Recovery after an aborted step: every running request gives its blocks back and is
         prefilled again from its tokens so far (arrival order kept).  Returns how many moved."""
+        for seq in self.waiting:                 # split prompts whose first pieces are in the pool start over
+            if seq.block_table:
+                self.block_manager.deallocate(seq)
+                seq.reset_for_recompute()
         moved = sorted(self.running, key=lambda s: s.seq_id, reverse=True)
         self.running.clear()
         for seq in moved:
@@ -196,6 +238,10 @@ class Scheduler:
         """Append sampled tokens; retire finished requests.  Returns the finished ones."""
         done: List[Sequence] = []
         for seq, token_id in zip(seqs, token_ids):
+            if seq.prefill_end is not None:          # a piece of a split prompt: nothing was sampled for it
+                seq.num_computed_tokens, seq.prefill_end = seq.prefill_end, None
+                continue
+            seq.num_computed_tokens = 0
             seq.append_token(int(token_id))
             hit_eos = (not seq.ignore_eos) and token_id == self.eos
             if hit_eos or seq.num_completion_tokens >= seq.max_tokens:

@@ -49,6 +49,10 @@ class Sequence:
         self.num_tokens = len(self.token_ids)
         self.num_prompt_tokens = self.num_tokens
         self.num_cached_tokens = 0
+        # chunked prefill: rows already in the pool from earlier pieces, and where this step's piece ends
+        # (None: at the end of the request)
+        self.num_computed_tokens = 0
+        self.prefill_end: Optional[int] = None
         self.block_table: List[int] = []
         self.temperature = sp.temperature
         self.max_tokens = sp.max_tokens
@@ -85,6 +89,11 @@ class Sequence:
     def logical_len(self) -> int:
         """Number of KV rows the request would occupy without compression."""
         return self.num_tokens + self.extra_image_rows
+
+    @property
+    def prefill_start(self) -> int:
+        """First row the next prefill step has to compute (after prefix-cache hits and earlier pieces)."""
+        return max(self.num_cached_tokens, self.num_computed_tokens)
 
     @property
     def prompt_rows(self) -> int:
@@ -190,6 +199,8 @@ class Sequence:
         self.hold = False
         self._pending_row = False
         self.num_cached_tokens = 0
+        self.num_computed_tokens = 0
+        self.prefill_end = None
         self.block_table = []
 
     # pickling for the optional driver->worker plan broadcast keeps messages small

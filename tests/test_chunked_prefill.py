@@ -1,0 +1,81 @@
+"""Chunked prefill: prompts split over several prefill steps give the tokens of unsplit prefill."""
+import pytest
+import torch
+
+from fastcache_b200 import LLM, SamplingParams
+from fastcache_b200.compress import KVCacheLinearDecoupleCompressor
+from helpers import random_compressor, tiny_llama_config
+
+
+def _prompts(lengths, seed=4):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(3, 1000, (n,), generator=g).tolist() for n in lengths]
+
+
+def _engine(budget, chunk, **kw):
+    return LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=256, max_model_len=1024, device="cpu",
+               enforce_eager=True, max_num_batched_tokens=budget, chunked_prefill_tokens=chunk, prefix_caching=False,
+               **kw)
+
+
+@pytest.mark.parametrize("kind", ["none", "ccm", "snapkv"])
+def test_split_prompts_generate_the_same_tokens(kind):
+    kw = {}
+    if kind == "ccm":
+        kw = dict(enable_compression=True, compression_backend="mlp", compression_pipeline="prefill",
+                  compressor=random_compressor(KVCacheLinearDecoupleCompressor, 2, 64, 4))
+    elif kind == "snapkv":
+        kw = dict(enable_compression=True, compression_backend="kvpress", kvpress_method="snapkv",
+                  compression_factor=2, compression_pipeline="prefill",
+                  kvpress_params={"window": 16, "kernel_size": 5})
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = _prompts([300, 40, 150, 90, 260])
+    whole = _engine(4096, 0, **kw)
+    ref = [o["token_ids"] for o in whole.generate(prompts, sp)]
+    assert whole.stats.prefill_steps == 1
+
+    llm = _engine(128, 32, **kw)
+    seqs = [llm.add_request(p, sp) for p in prompts]
+    pieces = 0
+    while not llm.is_finished():
+        head = llm.scheduler.waiting[0] if llm.scheduler.waiting else None
+        llm.step()
+        if head is not None and head.num_computed_tokens > 0 and head.status.name == "WAITING":
+            pieces += 1
+            assert head.block_table and head.num_completion_tokens == 0      # keeps its blocks, sampled nothing
+        llm.scheduler.block_manager.check_invariants(list(llm.scheduler.running) +
+                                                     [s for s in llm.scheduler.waiting if s.block_table])
+    assert pieces >= 4 and llm.stats.prefill_steps > 5
+    assert [s.completion_token_ids for s in seqs] == ref
+    assert llm.stats.prefill_tokens == sum(len(p) for p in prompts)
+    if kind != "none":
+        assert llm.stats.compressions == len(prompts)
+    bm = llm.scheduler.block_manager
+    assert bm.num_free_blocks == bm.num_blocks
+
+
+def test_unsplittable_cases_and_abort():
+    sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+    # splitting off: a prompt over the step budget is refused, as before
+    llm = _engine(64, 0)
+    llm.add_request(_prompts([100])[0], sp)
+    with pytest.raises(RuntimeError):
+        llm.step()
+    # a request cancelled between its pieces returns its blocks
+    llm = _engine(64, 16)
+    seq = llm.add_request(_prompts([200])[0], sp)
+    llm.step()
+    assert seq.num_computed_tokens == 64 and seq.block_table
+    bm = llm.scheduler.block_manager
+    assert bm.num_free_blocks < bm.num_blocks
+    assert llm.abort_request(seq.seq_id) and bm.num_free_blocks == bm.num_blocks
+    assert llm.is_finished()
+    # recovery restarts a half-prefetched request from its first row
+    seq = llm.add_request(_prompts([200])[0], sp)
+    llm.step()
+    llm.recover()
+    assert seq.num_computed_tokens == 0 and not seq.block_table and bm.num_free_blocks == bm.num_blocks
+    out = []
+    while not llm.is_finished():
+        out += llm.step()[0]
+    assert len(out[0][1]) == 2
