@@ -189,6 +189,19 @@ class BlockManager:
         block.hash = -1
         block.token_ids = []
 
+    def unpublish_unwritten(self, seq: Sequence, rows_written: int) -> int:
+        """Take the blocks of `seq` that are not completely written yet (block index >= rows_written //
+        block_size) out of the prefix cache, unless another request shares them (then their first owner
+        wrote them).  Used for prompts that are prefetched in pieces: a block must not be found by its
+        content hash before its rows exist.  Returns how many blocks were unpublished."""
+        n = 0
+        for block_id in seq.block_table[rows_written // self.block_size:]:
+            block = self.blocks[block_id]
+            if block.ref_count == 1 and block.hash != -1:
+                self._unpublish(block_id)
+                n += 1
+        return n
+
     def private_copy_needed(self, seq: Sequence) -> List[int]:
         """Indices into the block table whose block is shared with another request.
 

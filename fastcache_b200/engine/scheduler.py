@@ -88,6 +88,8 @@ class Scheduler:
                 break                            # the blocks stay with the request; it is tried again next step
             if piece > 0:
                 seq.prefill_end = seq.prefill_start + piece
+                # rows beyond this piece do not exist yet: their blocks must not be found through the prefix cache
+                self.block_manager.unpublish_unwritten(seq, seq.prefill_end)
                 self.running.extend(picked)
                 return picked + [seq]
             seq.prefill_end = None
@@ -197,6 +199,7 @@ class Scheduler:
         prefilled again from its tokens so far (arrival order kept).  Returns how many moved."""
         for seq in self.waiting:                 # split prompts whose first pieces are in the pool start over
             if seq.block_table:
+                self.block_manager.unpublish_unwritten(seq, seq.num_computed_tokens)
                 self.block_manager.deallocate(seq)
                 seq.reset_for_recompute()
         moved = sorted(self.running, key=lambda s: s.seq_id, reverse=True)

@@ -109,3 +109,55 @@ def test_scheduler_serves_every_request_under_pressure(seed, num_blocks, max_seq
     assert all(s.is_finished and s.num_completion_tokens == s.max_tokens for s in seqs)
     bm = sch.block_manager
     assert bm.num_free_blocks == bm.num_blocks
+
+
+@settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(0, 10 ** 6), st.integers(24, 60), st.integers(1, 6), st.integers(4, 24))
+def test_scheduler_with_split_prompts_serves_every_request(seed, num_blocks, max_seqs, chunk):
+    """The same trace with chunked prefill and prompts longer than a step's budget: a step never exceeds the
+    budget, every piece starts where the last one ended, every request finishes, no block leaks."""
+    rng = random.Random(seed)
+    Sequence.block_size = BS
+    budget = 48
+    cfg = Config.from_kwargs("", kvcache_block_size=BS, num_kvcache_blocks=num_blocks, max_num_seqs=max_seqs,
+                             max_num_batched_tokens=budget, max_model_len=200, eos=-1, chunked_prefill_tokens=chunk)
+    sch = Scheduler(cfg)
+    sch.chunk_tail = 8
+    seqs = []
+    for _ in range(rng.randrange(3, 10)):
+        n = rng.randrange(1, min(150, (num_blocks - 4) * BS))
+        s = Sequence([rng.randrange(3, 50) for _ in range(n)],
+                     SamplingParams(max_tokens=rng.randrange(1, 12), ignore_eos=True))
+        sch.add(s)
+        seqs.append(s)
+    computed = {s.seq_id: 0 for s in seqs}
+    steps = 0
+    while not sch.is_finished():
+        batch, is_prefill = sch.schedule()
+        assert batch and len({s.seq_id for s in batch}) == len(batch)
+        if is_prefill:
+            rows = 0
+            for s in batch:
+                end = s.logical_len if s.prefill_end is None else s.prefill_end
+                # a request that comes back after preemption may find its first blocks in the prefix cache
+                assert s.prefill_start == max(computed[s.seq_id], s.num_cached_tokens) and end > s.prefill_start
+                assert len(s.block_table) * BS >= end
+                rows += end - s.prefill_start
+                computed[s.seq_id] = end if s.prefill_end is not None else 0
+            assert rows <= budget
+            assert sum(s.prefill_end is not None for s in batch) <= 1
+        before = {s.seq_id: s.num_completion_tokens for s in batch}
+        partial = {s.seq_id for s in batch if s.prefill_end is not None}
+        sch.postprocess(batch, [rng.randrange(3, 50) for _ in batch])
+        for s in batch:
+            grew = s.num_completion_tokens - before[s.seq_id]
+            assert grew == (0 if s.seq_id in partial else 1)
+        for s in seqs:                               # a preempted request starts over
+            if not s.block_table and not s.is_finished:
+                computed[s.seq_id] = 0
+        sch.block_manager.check_invariants(list(sch.running) + [s for s in sch.waiting if s.block_table])
+        steps += 1
+        assert steps < 8000
+    assert all(s.is_finished and s.num_completion_tokens == s.max_tokens for s in seqs)
+    bm = sch.block_manager
+    assert bm.num_free_blocks == bm.num_blocks

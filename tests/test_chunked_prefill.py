@@ -79,3 +79,26 @@ def test_unsplittable_cases_and_abort():
     while not llm.is_finished():
         out += llm.step()[0]
     assert len(out[0][1]) == 2
+
+
+def test_unwritten_blocks_of_a_split_prompt_are_not_in_the_prefix_cache():
+    """With prefix caching on, a second request with the same prompt must not hit blocks of a request that is
+    still between its pieces; after the first has finished, the written blocks (up to the first piece's end)
+    may be shared, and both requests generate the same tokens as an engine without prefix caching."""
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    prompt = _prompts([200])[0]
+    plain = LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=256, max_model_len=1024, device="cpu",
+                enforce_eager=True, max_num_batched_tokens=4096, prefix_caching=False)
+    want = plain.generate([prompt], sp)[0]["token_ids"]
+    llm = LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=256, max_model_len=1024, device="cpu",
+              enforce_eager=True, max_num_batched_tokens=64, chunked_prefill_tokens=16, prefix_caching=True)
+    a = llm.add_request(prompt, sp)
+    llm.step()                                           # first piece: rows [0, 64)
+    bm = llm.scheduler.block_manager
+    published = [i for i, b in enumerate(a.block_table) if bm.blocks[b].hash != -1]
+    assert published == [0, 1, 2, 3]                     # only the four blocks the piece fills
+    b = llm.add_request(prompt, sp)
+    while not llm.is_finished():
+        llm.step()
+    assert a.completion_token_ids == want and b.completion_token_ids == want
+    assert bm.num_free_blocks == bm.num_blocks
