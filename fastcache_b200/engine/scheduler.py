@@ -206,6 +206,9 @@ class Scheduler:
         self.running.clear()
         for seq in moved:
             seq.hold = False
+            # the failed step may have been this request's prefill or a compression of its rows: what its
+            # own blocks hold is not to be trusted, so they leave the prefix cache before they are freed
+            self.block_manager.unpublish_unwritten(seq, 0)
             self.preempt(seq)
         return len(moved)
 
