@@ -1,6 +1,9 @@
 """Import-compatibility package: `from nanovllm import LLM, SamplingParams` and the sub-module
 paths used by scripts written against the reference resolve to fastcache_b200."""
 import importlib
+import importlib.abc
+import importlib.machinery
+import importlib.util
 import sys
 
 from fastcache_b200 import LLM, SamplingParams  # noqa: F401
@@ -38,18 +41,46 @@ _ALIASES = {
 }
 
 
-class _Finder:
+def _resolve(name: str):
+    """Real module for an alias name: an exact entry, or the longest aliased package prefix plus the
+    rest of the path (`nanovllm.layers.linear` -> `fastcache_b200.layers.linear`)."""
+    if name in _ALIASES:
+        return _ALIASES[name]
+    parts = name.split(".")
+    for cut in range(len(parts) - 1, 0, -1):
+        head = ".".join(parts[:cut])
+        if head in _ALIASES:
+            return _ALIASES[head] + "." + ".".join(parts[cut:])
+    return None
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    """Imports below `nanovllm.` hand back the module of this package itself (the same object, so its
+    relative imports and its state are those of `fastcache_b200`), not a second copy under another name."""
+
     def find_spec(self, name, path=None, target=None):
-        real = _ALIASES.get(name)
+        if not name.startswith("nanovllm."):
+            return None
+        real = _resolve(name)
         if real is None:
             return None
-        mod = importlib.import_module(real)
-        sys.modules[name] = mod
-        return importlib.util.spec_from_loader(name, loader=None)
+        try:
+            if importlib.util.find_spec(real) is None:
+                return None
+        except (ImportError, ValueError):
+            return None
+        return importlib.machinery.ModuleSpec(name, self)
+
+    def create_module(self, spec):
+        return importlib.import_module(_resolve(spec.name))
+
+    def exec_module(self, module):
+        pass
 
 
-import importlib.util  # noqa: E402
 
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
 for _name, _real in _ALIASES.items():
     try:
         sys.modules.setdefault(_name, importlib.import_module(_real))

@@ -300,3 +300,20 @@ def test_green_context_partitions_are_created_once_per_split(monkeypatch):
     assert b["compress"][0] is a["compress"][0] and fake.registered[b["compress"][1].cuda_stream] == 36
     d = streams.try_create_greenctx_streams(dev, 0.40, 1)
     assert fake.created == [36, 59] and d["compress_sms"] == 59 and d["main"] is not a["main"]
+
+
+def test_alias_submodules_are_the_same_module_objects():
+    """`nanovllm.<pkg>.<module>` must be the module of this package itself (not a second copy whose classes
+    differ and whose relative imports point into the alias package)."""
+    import importlib
+    import fastcache_b200.autocompress.cost_model as cm
+    import fastcache_b200.layers.linear as lin
+    assert importlib.import_module("nanovllm.layers.linear") is lin
+    assert importlib.import_module("nanovllm.autocompress.cost_model") is cm
+    from nanovllm.layers.layernorm import RMSNorm as A
+    from fastcache_b200.layers.layernorm import RMSNorm as B
+    from nanovllm.models.qwen3 import Qwen3ForCausalLM  # noqa: F401
+    from nanovllm.utils.streams import GreenCtxInfo  # noqa: F401
+    assert A is B
+    with pytest.raises(ImportError):
+        importlib.import_module("nanovllm.no_such_module")
