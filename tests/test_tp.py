@@ -30,6 +30,14 @@ def test_tp_cpu_gloo_matches_single_rank(tmp_path, world, kv_heads):
     assert one["tokens"] == many["tokens"]
 
 
+def test_tp_cpu_gloo_split_prompts_match_unsplit(tmp_path):
+    """Two gloo ranks with chunked prefill (replicated schedulers must cut the same pieces) against one rank
+    without it."""
+    one = _run(1, "cpu", str(tmp_path / "a.json"), 29641, ["--kv-heads", "2"])
+    two = _run(2, "cpu", str(tmp_path / "b.json"), 29642, ["--kv-heads", "2", "--chunk", "16"])
+    assert one["tokens"] == two["tokens"]
+
+
 @pytest.mark.gpu
 def test_tp2_gpu_fused_comm(tmp_path):
     if torch.cuda.device_count() < 2:

@@ -21,6 +21,7 @@ def main():
     ap.add_argument("--out", required=True)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--one-shot-tokens", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=0, help="chunked_prefill_tokens (with a 64-token step budget)")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
@@ -89,7 +90,8 @@ def main():
                             intermediate_size=1024, vocab_size=2000)
     llm = LLM(cfg, device=device, dtype="bf16" if a.device == "cuda" else "fp32", tensor_parallel_size=world,
               kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=256, max_num_seqs=8,
-              enforce_eager=False, init_device="cpu", fused_comm_tokens=a.one_shot_tokens)
+              enforce_eager=False, init_device="cpu", fused_comm_tokens=a.one_shot_tokens,
+              **({"chunked_prefill_tokens": a.chunk, "max_num_batched_tokens": 64} if a.chunk else {}))
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (9, 40, 77, 120)]
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
