@@ -401,11 +401,25 @@ def main(argv: Optional[List[str]] = None) -> None:
     ap.add_argument("--max-model-len", type=int, default=8192)
     ap.add_argument("--host", default="0.0.0.0")
     ap.add_argument("--port", type=int, default=8000)
+    # engine settings beyond the reference's command line
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--chunked-prefill-tokens", type=int, default=0,
+                    help="> 0: prompts that do not fit a prefill step's token budget run in pieces of at least this size")
+    ap.add_argument("--greenctx-compress-ratio", type=float, default=0.0,
+                    help="> 0: compression streams get this share of the SMs (green context)")
     a = ap.parse_args(argv)
     import uvicorn
+    extra = {}
+    if a.tensor_parallel_size > 1:
+        extra["tensor_parallel_size"] = a.tensor_parallel_size
+    if a.chunked_prefill_tokens > 0:
+        extra["chunked_prefill_tokens"] = a.chunked_prefill_tokens
+    if a.greenctx_compress_ratio > 0:
+        extra.update(greenctx_enabled=True, greenctx_compress_ratio=a.greenctx_compress_ratio,
+                     greenctx_main_ratio=1.0 - a.greenctx_compress_ratio)
     server = FastCacheServer(a.model, a.compressor if a.compression_backend == "mlp" else None,
                              a.compression_mode, a.compression_backend, a.kvpress_method, a.compression_factor,
-                             a.compression_threshold, a.max_model_len)
+                             a.compression_threshold, a.max_model_len, **extra)
     uvicorn.run(create_app(server), host=a.host, port=a.port)
 
 
