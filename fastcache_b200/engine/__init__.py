@@ -1,0 +1,1 @@
+"""Engine core: sequences, block manager, scheduler, model runner, step loop, compression control."""

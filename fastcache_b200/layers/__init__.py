@@ -1,0 +1,1 @@
+"""Model building blocks (linear family, attention, embeddings, norms, rotary, activation, sampler)."""

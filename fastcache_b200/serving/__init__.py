@@ -1,0 +1,1 @@
+"""Serving layer: HTTP server, load-test harness, command lines, datasets, analytic profiler."""

@@ -1,0 +1,1 @@
+"""Process-wide helpers: step context, weight loading, memory queries, streams, tracing, watchdogs."""
