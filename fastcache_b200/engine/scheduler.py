@@ -41,6 +41,7 @@ class Scheduler:
         self.chunk_min = int(getattr(config, "chunked_prefill_tokens", 0) or 0)
         # rows kept for the last piece of a split prompt (the scorers' observation window reads them)
         self.chunk_tail = 64
+        self._piece_last = False         # the previous step ran a piece of a split prompt
         self.one_image_per_prefill = bool(config.extra.get("one_image_per_prefill", False))
         self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size,
                                           prefix_caching=config.prefix_caching)
@@ -141,12 +142,18 @@ class Scheduler:
 
     def schedule(self, prefer_decode: bool = False) -> Tuple[List[Sequence], bool]:
         """Pick the next batch.  Returns (sequences, is_prefill)."""
+        # between two pieces of a split prompt the running requests get a decode step, so a long prompt
+        # costs them one piece of latency per token instead of its whole prefill
+        if self._piece_last and self.running and self.waiting and self.waiting[0].block_table:
+            prefer_decode = True
+        self._piece_last = False
         if prefer_decode and self.running:
             seqs = self._schedule_decode()
             if seqs:
                 return seqs, False
         seqs = self._schedule_prefill()
         if seqs:
+            self._piece_last = seqs[-1].prefill_end is not None
             return seqs, True
         seqs = self._schedule_decode()
         if not seqs and (self.waiting or self.running) and not any(s.hold for s in self.running):

@@ -102,3 +102,21 @@ def test_unwritten_blocks_of_a_split_prompt_are_not_in_the_prefix_cache():
         llm.step()
     assert a.completion_token_ids == want and b.completion_token_ids == want
     assert bm.num_free_blocks == bm.num_blocks
+
+
+def test_decode_steps_run_between_the_pieces_of_a_long_prompt():
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    short, long_ = _prompts([20, 400], seed=9)
+    want = [o["token_ids"] for o in _engine(4096, 0).generate([short, long_], sp)]
+    llm = _engine(64, 16)
+    a = llm.add_request(short, sp)
+    llm.step()                                           # the short request is running before the long one arrives
+    b = llm.add_request(long_, sp)
+    kinds = []
+    while not llm.is_finished():
+        _, n = llm.step()
+        kinds.append("P" if n > 0 else "D")
+    trace = "".join(kinds)
+    assert "PP" not in trace[: trace.rindex("P")]        # while the short request decodes, no two pieces in a row
+    assert trace.count("P") >= 6
+    assert [a.completion_token_ids, b.completion_token_ids] == want
