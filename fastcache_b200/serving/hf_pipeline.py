@@ -172,7 +172,7 @@ class HFPipelineTester:
             for kv, r in zip(entries[i:i + self.compress_batch], requests[i:i + self.compress_batch]):
                 self.timestamps.record(r.request_id, "compress_start")
                 t0 = self._now(sync=True)
-                ckv = self.compressor(kv, list(self.get_comp_len(r)))
+                ckv = self._apply(kv, list(self.get_comp_len(r)))
                 dt = self._now(sync=True) - t0
                 self.timestamps.record(r.request_id, "compress_finish")
                 self.compress_stats["calls"] += 1
@@ -181,6 +181,18 @@ class HFPipelineTester:
                 self.compress_stats["seconds"] += dt
                 out.append([(k.contiguous(), v.contiguous()) for k, v in ckv])
         return out
+
+    def _apply(self, kv: KV, it_len: List[int]) -> KV:
+        """Compressors take (kv, it_len); quantisers and other one-argument callables take the cache only."""
+        if getattr(self, "_one_arg", None) is None:
+            import inspect
+            try:
+                params = [p for p in inspect.signature(self.compressor).parameters.values()
+                          if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD, p.VAR_POSITIONAL)]
+                self._one_arg = len(params) == 1 and params[0].kind is not params[0].VAR_POSITIONAL
+            except (TypeError, ValueError):
+                self._one_arg = False
+        return self.compressor(kv) if self._one_arg else self.compressor(kv, it_len)
 
     def _now(self, sync: bool = False) -> float:
         if sync and torch.cuda.is_available() and str(getattr(self.backend, "device", "cpu")).startswith("cuda"):

@@ -99,3 +99,14 @@ def test_cli_runs_the_hf_pipeline():
     r = rows[0]
     assert r["engine"] == "hf" and r["result"]["completed"] == 4 and r["result"]["output_tokens"] == 16
     assert r["result"]["compression"]["calls"] == 4 and r["stage_averages"]["generated_lens"] == 4.0
+
+
+def test_quantiser_as_the_compression_stage():
+    from fastcache_b200.compress.quant import SimpleKVQuantizer
+    model = _model()
+    q = SimpleKVQuantizer(8)
+    tester = HFPipelineTester(TransformersBackend(model), q, batching=[4, 4, 8], req_per_sec=400.0, max_wait_time=0.02)
+    res = tester.run_concurrent_test(_prompts()[:4], max_new_tokens=4)
+    assert res.completed == 4 and res.compression["calls"] == 4
+    assert res.compression["rows_in"] == res.compression["rows_out"]          # precision, not length
+    assert q.totalTime > 0
