@@ -120,9 +120,26 @@ def evict_reference(kv_pool: torch.Tensor, block_table: Sequence[int], kv_len: i
     return n_kept
 
 
+def _window_slice(wq: Optional[Dict[int, torch.Tensor]], first: int, last: int) -> Optional[Dict[int, torch.Tensor]]:
+    """Observation-window queries of layers [first, last), keyed from 0 like the pool slice they go with."""
+    if wq is None:
+        return None
+    return {l - first: q for l, q in wq.items() if first <= l < last}
+
+
 def evict_in_pool(kv_pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: Sequence[int],
                   method: str, n_kepts: Sequence[int], window_q: Optional[List[Optional[Dict[int, torch.Tensor]]]] = None,
-                  params: Optional[dict] = None) -> List[int]:
+                  params: Optional[dict] = None, layer_start: int = 0, layer_end: Optional[int] = None) -> List[int]:
+    """Evict in place in layers [layer_start, layer_end) only (all layers by default).  `kv_lens` are the row
+    counts before eviction; a caller that works through the layers in chunks passes the same original counts
+    for every chunk, because the other layers' rows are untouched by a chunk."""
+    L = kv_pool.shape[0]
+    layer_end = L if layer_end is None else min(layer_end, L)
+    if layer_start > 0 or layer_end < L:
+        # the layer index is the outermost dimension of the pool, so a range of layers is a contiguous pool
+        kv_pool = kv_pool[layer_start:layer_end]
+        if window_q is not None:
+            window_q = [_window_slice(wq, layer_start, layer_end) for wq in window_q]
     if kv_pool.is_cuda:
         from ..ops.compress_cuda import evict_cuda
         return evict_cuda(kv_pool, block_tables, kv_lens, method, n_kepts, window_q, params or {})

@@ -91,10 +91,12 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const int c0 = kk * 16 + 2 * t;
-      qa[kk][0] = (g < G) ? *reinterpret_cast<const uint32_t*>(q0 + g * D + c0) : 0u;
-      qa[kk][1] = (g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q0 + (g + 8) * D + c0) : 0u;
-      qa[kk][2] = (g < G) ? *reinterpret_cast<const uint32_t*>(q0 + g * D + c0 + 8) : 0u;
-      qa[kk][3] = (g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q0 + (g + 8) * D + c0 + 8) : 0u;
+      // q was written by the kernel before this one while this grid may already have been resident
+      // (programmatic dependent launch): read it through L2, never through the read-only path
+      qa[kk][0] = (g < G) ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + g * D + c0)) : 0u;
+      qa[kk][1] = (g + 8 < G) ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + (g + 8) * D + c0)) : 0u;
+      qa[kk][2] = (g < G) ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + g * D + c0 + 8)) : 0u;
+      qa[kk][3] = (g + 8 < G) ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + (g + 8) * D + c0 + 8)) : 0u;
     }
   }
 
@@ -240,7 +242,21 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     __syncthreads();                       // every warp is done with this stage
     if (threadIdx.x == 0 && it + DEC_STAGES < n_tiles) load_tile(tile0 + it + DEC_STAGES, stage);
   }
-  if (__syncthreads_or(!alive)) return;    // a TMA never landed: status is set, nothing is written
+  if (__syncthreads_or(!alive)) {
+    // a TMA never landed: the status word is set.  The split's cells are still written (weight zero), so the
+    // merge kernel never mixes in what an earlier call left in the scratch
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_THREADS) {
+      const int r = idx / D, c = idx - r * D;
+      const int hq = hk * G + r;
+      if (splits == 1) {
+        out[((long long)b * Hq + hq) * D + c] = __float2bfloat16(0.f);
+      } else {
+        part_o[(((long long)b * Hq + hq) * splits + split) * D + c] = 0.f;
+        if (c == 0) part_lse[((long long)b * Hq + hq) * splits + split] = -INFINITY;
+      }
+    }
+    return;
+  }
 
   // ---- merge the four warps (each saw a different quarter of every tile)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -300,16 +316,21 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   pdl_wait();
   const long long bh = blockIdx.x;
   const float* lse = part_lse + bh * splits;
+  // the partials come from the kernel right before this one: L2 loads, not the read-only path (see above)
   float mx = -INFINITY;
-  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, lse[s]);
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, __ldcg(lse + s));
   float den = 0.f;
-  for (int s = 0; s < splits; ++s) den += (lse[s] == -INFINITY) ? 0.f : exp2f(lse[s] - mx);
+  for (int s = 0; s < splits; ++s) {
+    const float l = __ldcg(lse + s);
+    den += (l == -INFINITY) ? 0.f : exp2f(l - mx);
+  }
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float acc = 0.f;
     if (mx != -INFINITY) {
       for (int s = 0; s < splits; ++s) {
-        const float w = (lse[s] == -INFINITY) ? 0.f : exp2f(lse[s] - mx);
-        acc += w * part_o[(bh * splits + s) * D + c];
+        const float l = __ldcg(lse + s);
+        const float w = (l == -INFINITY) ? 0.f : exp2f(l - mx);
+        acc += w * __ldcg(part_o + (bh * splits + s) * D + c);
       }
       acc /= den;
     }

@@ -28,6 +28,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 #include <stdexcept>
@@ -480,11 +481,15 @@ static void launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
                        cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, TRANS, SWIGLU>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (function, device) pair: remember it per device, not per process
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_relaxed) & bit)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-    configured = true;
+    configured.fetch_or(bit, std::memory_order_relaxed);
   }
   kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();

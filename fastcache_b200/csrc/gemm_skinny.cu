@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <stdexcept>
 #include <string>
 
@@ -289,11 +290,15 @@ static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Sk
                           cudaStream_t stream) {
   using L = SkinnySmem<BN, STAGES, ROWS>;
   auto kern = gemm_skinny_kernel<BN, STAGES, ROWS>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (function, device) pair: remember it per device, not per process
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_relaxed) & bit)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-    configured = true;
+    configured.fetch_or(bit, std::memory_order_relaxed);
   }
   cudaError_t e = launch_pdl(PDL_SKINNY_GEMM, kern, dim3(tiles, p.splits), dim3(SK_THREADS), L::TOTAL, stream, tw, tx, p);
   if (e == cudaSuccess) e = cudaGetLastError();

@@ -65,8 +65,11 @@ extern "C" int fc_decode_attention_noalloc(const void* q, const void* k_cache, c
     return FC_NOALLOC_BAD_ARGUMENT;
   }
   if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16 || (D != 64 && D != 128) || splits < 1 ||
-      splits > fc::DECODE_MAX_SPLITS || block_size < 8 || max_blocks <= 0 || num_blocks <= 0) {
-    set_err(err, err_len, "unsupported shape: need Hq % Hkv == 0, Hq / Hkv <= 16, D in {64, 128}, 1 <= splits <= 32");
+      splits > fc::DECODE_MAX_SPLITS || block_size < 8 || block_size % 8 != 0 || max_blocks <= 0 ||
+      num_blocks <= 0) {
+    set_err(err, err_len,
+            "unsupported shape: need Hq % Hkv == 0, Hq / Hkv <= 16, D in {64, 128}, 1 <= splits <= 32, "
+            "block_size a multiple of 8");
     return FC_NOALLOC_BAD_ARGUMENT;
   }
   const unsigned long long part = (unsigned long long)B * Hq * splits * D;

@@ -31,8 +31,10 @@
 //    first call before any stream capture begins.
 //  * All calls share the two arrays, and the arrays keep whatever the previous call left.
 //    Nothing in them has to start at zero: every cell that the merge reads is written
-//    by the attention kernel of the same call first.  Two calls whose kernels overlap
-//    on the GPU (different streams, no ordering between them) race on the arrays.
+//    by the attention kernel of the same call first, also when one of its bounded waits
+//    runs out (that split is then written with weight zero and `status` receives the code;
+//    pass a status word if such a call must not go unnoticed).  Two calls whose kernels
+//    overlap on the GPU (different streams, no ordering between them) race on the arrays.
 //  * No cudaMalloc, cudaFree or allocating library routine is called.
 #pragma once
 #include <stddef.h>
@@ -46,7 +48,7 @@ extern "C" {
 
 enum {
   FC_NOALLOC_OK = 0,
-  FC_NOALLOC_BAD_ARGUMENT = 1,   // null pointer, unsupported head_dim / group size, splits < 1
+  FC_NOALLOC_BAD_ARGUMENT = 1,   // null pointer, unsupported head_dim / group size / block size, splits < 1
   FC_NOALLOC_TOO_LARGE = 2,      // the request needs more scratch than the static arrays hold
   FC_NOALLOC_CUDA_ERROR = 3,     // a CUDA call failed (message says which)
 };

@@ -47,6 +47,7 @@ class PendingCompression:
     rows: int = 0                 # rows that were compressed
     new_len: int = 0
     reported: bool = False
+    stream: Any = None            # decode pipeline: the one stream all layer chunks of this request run on
 
 
 @dataclass
@@ -373,7 +374,9 @@ class LLMEngine:
             self._privatize(s)
             s.compression_state = CompressionState.IN_PROGRESS
             s.hold = True
-            self._pending[s.seq_id] = PendingCompression(s, None, None, s.rows_in_pool, 0, s.rows_in_pool, 0)
+            # every chunk of one request runs on the same stream, so chunk k + 1 is ordered after chunk k
+            self._pending[s.seq_id] = PendingCompression(s, None, None, s.rows_in_pool, 0, s.rows_in_pool, 0,
+                                                         stream=self.model_runner.next_compress_stream())
 
     def _advance_chunked(self) -> None:
         r = self.model_runner
@@ -382,15 +385,22 @@ class LLMEngine:
             return
         L = r.num_hidden_layers
         step = max(1, r.decode_layers_per_step)
-        stream = r.next_compress_stream()
-        if stream is not None:
-            ready = torch.cuda.Event()
-            ready.record(r.main_stream)
-            stream.wait_event(ready)
-        groups: Dict[int, List[PendingCompression]] = {}
+        groups: Dict[Tuple[int, int], List[PendingCompression]] = {}
         for p in todo:
-            groups.setdefault(p.next_layer, []).append(p)
-        for first, ps in groups.items():
+            if p.stream is not None and not any(p.stream is c for c in r.compress_streams):
+                # the streams were rebuilt for a new SM split (which synchronises the device first)
+                p.stream = r.next_compress_stream()
+            groups.setdefault((id(p.stream), p.next_layer), []).append(p)
+        ready = None
+        waited = set()
+        for (_, first), ps in groups.items():
+            stream = ps[0].stream
+            if stream is not None and id(stream) not in waited:
+                if ready is None:
+                    ready = torch.cuda.Event()
+                    ready.record(r.main_stream)
+                stream.wait_event(ready)
+                waited.add(id(stream))
             last = min(L, first + step)
             seqs = [p.seq for p in ps]
             saved = [s._kv_cache_len for s in seqs]
@@ -398,16 +408,18 @@ class LLMEngine:
                 p.seq._kv_cache_len = p.rows
             with nvtx_range("compress_chunk"):
                 new = r.compress_kv_cache_batch(seqs, first, last, stream=stream)
+            # an event after every chunk: whoever takes the request's blocks away (preemption, abort, finish)
+            # or reads its rows (decode) orders the main stream after the newest chunk launched so far
+            ev = None
+            if stream is not None:
+                ev = torch.cuda.Event()
+                ev.record(stream)
             for p, s, v, n in zip(ps, seqs, saved, new):
                 s._kv_cache_len = v
                 p.next_layer = last
                 p.new_len = n
+                p.event = ev
                 if last >= L:
-                    ev = None
-                    if stream is not None:
-                        ev = torch.cuda.Event()
-                        ev.record(stream)
-                    p.event = ev
                     s.hold = False
                     s.kv_cache_len = n + int(s._pending_row)
                     self.stats.compressions += 1

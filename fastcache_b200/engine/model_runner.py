@@ -528,7 +528,7 @@ class ModelRunner:
                 if self.kvpress_method in NEEDS_QUERIES:
                     wq = [self._window_q.get(s.seq_id) for s in seqs]
                 new = evict_in_pool(self.kv_cache, tables, lens, self.kvpress_method, kept, wq,
-                                    self.kvpress_params)
+                                    self.kvpress_params, layer_start, layer_end)
         if timed:
             self.timer.stop(stream)
         full = (layer_start == 0 and (layer_end is None or layer_end >= self.num_hidden_layers))

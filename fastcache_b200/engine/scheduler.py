@@ -167,15 +167,23 @@ class Scheduler:
         """Take a running request's blocks away; it is prefetched again later."""
         self.num_preemptions += 1
         seq.status = SequenceStatus.WAITING
-        self.block_manager.deallocate(seq)
-        if self.on_release is not None:
+        if self.on_release is not None:          # orders work in flight on the request's rows before the blocks go
             self.on_release(seq)
+        self.block_manager.deallocate(seq)
         seq.reset_for_recompute()
         try:
             self.compress_queue.remove(seq)
         except ValueError:
             pass
-        self.waiting.appendleft(seq)
+        if self.waiting and self.waiting[0].block_table:
+            # a split prompt whose first pieces are in the pool keeps the head of the queue: it owns all the
+            # blocks it needs, so it always finishes, whereas a preempted request put in front of it could
+            # wait forever for the blocks that it holds
+            head = self.waiting.popleft()
+            self.waiting.appendleft(seq)
+            self.waiting.appendleft(head)
+        else:
+            self.waiting.appendleft(seq)
 
     def abort(self, seq: Sequence) -> bool:
         """Cancel a request wherever it is queued; its blocks return to the pool.  False if it had
@@ -192,9 +200,9 @@ class Scheduler:
         else:
             seq.status = SequenceStatus.FINISHED
             if seq.block_table:                      # a split prompt whose first pieces are in the pool
-                self.block_manager.deallocate(seq)
                 if self.on_release is not None:
                     self.on_release(seq)
+                self.block_manager.deallocate(seq)
             try:
                 self.compress_queue.remove(seq)
             except ValueError:
@@ -264,9 +272,9 @@ class Scheduler:
 
     def finish(self, seq: Sequence) -> None:
         seq.status = SequenceStatus.FINISHED
-        self.block_manager.deallocate(seq)
         if self.on_release is not None:
             self.on_release(seq)
+        self.block_manager.deallocate(seq)
         try:
             self.running.remove(seq)
         except ValueError:

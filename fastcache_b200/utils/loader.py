@@ -40,6 +40,7 @@ def load_weights(model: nn.Module, named_tensors: Iterable[Tuple[str, torch.Tens
     params = dict(model.named_parameters())
     buffers = dict(model.named_buffers())
     stats = {"loaded": 0, "skipped": 0, "unknown": 0}
+    seen = set()                      # (parameter name, shard id) pairs that received data
     for name, tensor in named_tensors:
         if strip_prefix:
             if not name.startswith(strip_prefix):
@@ -70,7 +71,42 @@ def load_weights(model: nn.Module, named_tensors: Iterable[Tuple[str, torch.Tens
         with torch.no_grad():
             loader(param, tensor.to(param.device) if tensor.device != param.device else tensor, shard_id)
         stats["loaded"] += 1
+        seen.add((target, shard_id))
+    stats["missing"] = missing_parameters(model, seen)
     return stats
+
+
+def missing_parameters(model: nn.Module, seen) -> list:
+    """Parameters of `model` that no checkpoint tensor reached: a plain parameter needs its own tensor, a packed
+    one (qkv_proj, gate_up_proj) every shard of its group.  Tied parameters (the LM head sharing the embedding
+    table) count once.  Modules listed in `model.optional_weight_substrings` may stay at their initial values."""
+    packed = getattr(model, "packed_modules_mapping", {})
+    optional = tuple(getattr(model, "optional_weight_substrings", ()))
+    groups: Dict[str, set] = {}
+    for _key, (packed_name, sid) in packed.items():
+        groups.setdefault(packed_name, set()).add(sid)
+    got: Dict[str, set] = {}
+    for target, sid in seen:
+        got.setdefault(target, set()).add(sid)
+    by_id: Dict[int, list] = {}
+    for name, prm in model.named_parameters(remove_duplicate=False):
+        by_id.setdefault(id(prm), []).append(name)
+    missing = []
+    for names in by_id.values():
+        if any(o in n for n in names for o in optional):
+            continue
+        ok = False
+        for n in names:
+            sids = got.get(n)
+            if not sids:
+                continue
+            need = next((g for pk, g in groups.items() if f".{pk}." in n or n.startswith(pk + ".")), None)
+            if need is None or None in sids or need <= sids:
+                ok = True
+                break
+        if not ok:
+            missing.append(names[0])
+    return sorted(missing)
 
 
 def iter_safetensors(path: str) -> Iterable[Tuple[str, torch.Tensor]]:
@@ -81,8 +117,21 @@ def iter_safetensors(path: str) -> Iterable[Tuple[str, torch.Tensor]]:
                 yield name, f.get_tensor(name)
 
 
-def load_model(model: nn.Module, path: str, strip_prefix: str = "", verbose: bool = False) -> Dict[str, int]:
+def load_model(model: nn.Module, path: str, strip_prefix: str = "", verbose: bool = False,
+               strict: bool = True) -> Dict[str, int]:
+    """Load every `*.safetensors` file of `path`.  With `strict` (default) a parameter that no checkpoint tensor
+    reached is an error: a checkpoint with another naming prefix or a missing shard file would otherwise leave
+    part of the model at its initial values without a word."""
+    if not glob(os.path.join(path, "*.safetensors")):
+        raise FileNotFoundError(f"no *.safetensors files in {path!r}")
     stats = load_weights(model, iter_safetensors(path), strip_prefix, verbose)
+    if stats["missing"]:
+        head = ", ".join(stats["missing"][:8]) + (" ..." if len(stats["missing"]) > 8 else "")
+        msg = (f"{len(stats['missing'])} parameters were not found in {path!r} ({stats['unknown']} checkpoint "
+               f"tensors matched no parameter): {head}")
+        if strict:
+            raise RuntimeError(msg)
+        print(f"[fastcache_b200] warning: {msg}")
     if hasattr(model, "finalize_weights"):
         model.finalize_weights()
     return stats

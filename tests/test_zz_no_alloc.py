@@ -75,6 +75,11 @@ def test_noalloc_entry_matches_regular_entry_twice():
         want = ext().decode_attention(q, kc, vc, bt, cl, float(D) ** -0.5, splits, 0)
         torch.cuda.synchronize()
         assert (out.float() - want.float()).abs().max().item() < 2e-2
+        # and against the plain fp32 PyTorch statement of the op
+        from fastcache_b200.ops import reference as ref
+        oracle = ref.decode_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), bt.cpu(), cl.cpu(),
+                                      float(D) ** -0.5)
+        assert (out.float().cpu() - oracle.float()).abs().max().item() < 2e-2
 
 
 def test_noalloc_entry_rejects_oversized_requests():
@@ -88,3 +93,6 @@ def test_noalloc_entry_rejects_oversized_requests():
     assert rc == 2 and "static scratch" in msg
     rc, _, msg = _call(fn, q, kc, vc, bt, cl, 0)
     assert rc == 1
+    odd = torch.zeros(4, 4, 12, 64, dtype=torch.bfloat16, device="cuda")         # block size 12: not a multiple of 8
+    rc, _, msg = _call(fn, q, odd, odd, bt, cl, 2)
+    assert rc == 1 and "multiple of 8" in msg
