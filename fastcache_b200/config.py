@@ -84,6 +84,15 @@ class ModelConfig:
             if isinstance(v, dict) and k.endswith("_config"):
                 v = ModelConfig(**v)
             setattr(self, k, v)
+        # transformers >= 5 writes the rotary settings as one dict, `rope_parameters` = {rope_theta, rope_type,
+        # ...}; the models read the 4.x field names, so give both views of the same facts
+        rp = kw.get("rope_parameters")
+        if isinstance(rp, dict):
+            if "rope_theta" not in kw and rp.get("rope_theta") is not None:
+                self.rope_theta = float(rp["rope_theta"])
+            if "rope_scaling" not in kw:
+                kind = rp.get("rope_type", rp.get("type", "default"))
+                self.rope_scaling = None if kind in (None, "default") else dict(rp)
 
     def get(self, name: str, default: Any = None) -> Any:
         return getattr(self, name, default)

@@ -432,24 +432,41 @@ Tensor dense_attention(const Tensor& q, const Tensor& k, const Tensor& v, double
   return out;
 }
 
-Tensor sample(const Tensor& logits, const Tensor& temps, int64_t seed) {
+// Tokens [B] (with_status false) or [B + 1]: the tokens followed by the device status code, which the host then
+// gets with the tokens it reads back anyway.  Column j of the logits is vocabulary entry vocab_offset + j;
+// entries >= v_limit (-1: none) are padding.
+Tensor sample(const Tensor& logits, const Tensor& temps, int64_t seed, bool with_status, int64_t vocab_offset,
+              int64_t v_limit) {
   check_bf16(logits, "logits");
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [B, V] with unit inner stride");
   TORCH_CHECK(temps.is_cuda() && temps.scalar_type() == torch::kFloat32 && temps.numel() == logits.size(0),
               "temperatures must be fp32 [B] on the device");
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor out = torch::empty({logits.size(0)}, logits.options().dtype(torch::kInt64));
-  fc::launch_sample(logits.data_ptr(), temps.data_ptr(), out.data_ptr(), int(logits.size(0)), int(logits.size(1)),
-                    logits.stride(0), uint32_t(seed), at::cuda::getCurrentCUDAStream());
+  const int64_t B = logits.size(0);
+  Tensor out = torch::empty({B + (with_status ? 1 : 0)}, logits.options().dtype(torch::kInt64));
+  if (B == 0 && with_status) out.zero_();
+  fc::launch_sample(logits.data_ptr(), temps.data_ptr(), out.data_ptr(), int(B), int(logits.size(1)),
+                    logits.stride(0), uint32_t(seed), at::cuda::getCurrentCUDAStream(), int(vocab_offset),
+                    int(v_limit), with_status ? status_ptr(logits.get_device()) : nullptr);
   return out;
 }
 
-// Reads and clears the device status word (synchronises the current stream).
+// Reads the code bits of the device status word and clears them (synchronises the current stream); the wait
+// limit kept in the upper bits stays.
 int64_t read_status(int64_t device) {
   auto& ws = workspace(int(device));
-  int64_t v = ws.status[0].item<int>();
-  if (v != 0) ws.status.zero_();
-  return v;
+  const int64_t v = ws.status[0].item<int>();
+  if ((v & 0xFF) != 0) ws.status[0].bitwise_and_(~0xFF);
+  return v & 0xFF;
+}
+
+// Limit of every bounded device wait (mbarriers and flags of other GPUs) in microseconds for kernels that get this
+// device's status word; 0 restores the built-in limits.  For tests and for deployments that prefer to fail fast.
+void set_wait_limit_us(int64_t device, int64_t us) {
+  TORCH_CHECK(us >= 0 && us < (1 << 24), "limit must be in [0, 2^24) microseconds");
+  auto& ws = workspace(int(device));
+  const int64_t v = ws.status[0].item<int>();
+  ws.status[0].fill_(int64_t(int32_t((uint32_t(v) & 0xFFu) | (uint32_t(us) << 8))));
 }
 
 void register_stream_sms(int64_t stream_ptr, int64_t sms) {
@@ -482,9 +499,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,
         py::arg("max_ctx") = 0);
-  m.def("sample", &sample);
+  m.def("sample", &sample, py::arg("logits"), py::arg("temperatures"), py::arg("seed"), py::arg("with_status") = false,
+        py::arg("vocab_offset") = 0, py::arg("v_limit") = -1);
   m.def("dense_attention", &dense_attention);
   m.def("read_status", &read_status);
+  m.def("set_wait_limit_us", &set_wait_limit_us);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
   m.def("status_tensor", [](int64_t device) { return workspace(int(device)).status; });

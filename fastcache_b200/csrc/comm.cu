@@ -24,6 +24,7 @@
 #include "comm.h"
 #include "launch.h"
 #include "ptx.cuh"
+#include "sample.cuh"
 
 namespace fc {
 
@@ -88,6 +89,7 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, u
     const uint32_t* mine = peers.flags[peers.rank] + (size_t)slot * COMM_MAX_WORLD + tid;
     bool got = false;
     const uint64_t t0 = global_timer_ns();
+    uint64_t limit = FC_PEER_WAIT_LIMIT_NS;
     for (uint32_t i = 0; i < FC_PEER_SPIN_LIMIT; ++i) {
       // epochs only grow; a peer that is already one exchange ahead is fine
       if (int32_t(ld_acquire_sys(mine) - epoch) >= 0) {
@@ -95,8 +97,10 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, u
         break;
       }
       __nanosleep(20);
-      // ranks are launched by different host processes: allow seconds of skew, not more
-      if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
+      if ((i & 255u) == 255u) {
+        if (i == 255u) limit = peer_wait_limit_ns(status);
+        if (global_timer_ns() - t0 > limit) break;
+      }
     }
     if (!got) {
       report(status, ST_TIMEOUT_PEER);
@@ -242,6 +246,107 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
   if (e != cudaSuccess) throw std::runtime_error(std::string("allreduce launch: ") + cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------- sampling over vocabulary shards
+// Every rank holds the logits of its vocabulary shard.  One CTA per request finds the shard's best candidate
+// (see sample.cuh), stores it as one 8-byte cell into every rank's candidate table, exchanges flags exactly like
+// the all-reduce above and picks the winner of the `world` candidates.  All ranks see the same candidates, so
+// they all return the same token: no gather of the logits, no broadcast of the tokens.  The table has two
+// halves used by even and odd epochs, so a rank that is one exchange ahead never overwrites a cell a peer
+// still has to read.
+__device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_exchange_kernel(CommPeers peers, SamplePeers cand, const bf16* __restrict__ logits,
+                       const float* __restrict__ temps, long long* __restrict__ out, int V, long long ld,
+                       uint32_t seed, int vocab_offset, int v_limit, uint32_t* __restrict__ epochs,
+                       uint32_t* status) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ uint64_t s_cand[COMM_MAX_WORLD];
+  __shared__ uint64_t s_mine;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;                       // also the flag slot
+  float best;
+  int best_i;
+  sample_row_best(logits + (long long)b * ld, V, vocab_offset, v_limit, temps[b], sample_row_seed(seed, b), s_val,
+                  s_idx, best, best_i);
+  if (threadIdx.x == 0) {
+    s_mine = (uint64_t(__float_as_uint(best)) << 32) | uint64_t(uint32_t(best_i));
+    s_epoch = epochs[b] + 1;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int tid = threadIdx.x;
+  if (tid < peers.world) {
+    const size_t half = size_t(epoch & 1u) * COMM_MAX_SLOTS;
+    // candidate first, then the flag, both by this thread: the release orders them for the peer
+    st_relaxed_sys_u64(cand.cells[tid] + (half + b) * COMM_MAX_WORLD + peers.rank, s_mine);
+    st_release_sys(peers.flags[tid] + (size_t)b * COMM_MAX_WORLD + peers.rank, epoch);
+    const uint32_t* mine = peers.flags[peers.rank] + (size_t)b * COMM_MAX_WORLD + tid;
+    bool got = false;
+    const uint64_t t0 = global_timer_ns();
+    uint64_t limit = FC_PEER_WAIT_LIMIT_NS;
+    for (uint32_t i = 0; i < FC_PEER_SPIN_LIMIT; ++i) {
+      if (int32_t(ld_acquire_sys(mine) - epoch) >= 0) {
+        got = true;
+        break;
+      }
+      __nanosleep(20);
+      if ((i & 255u) == 255u) {
+        if (i == 255u) limit = peer_wait_limit_ns(status);
+        if (global_timer_ns() - t0 > limit) break;
+      }
+    }
+    if (got) {
+      s_cand[tid] = ld_relaxed_sys_u64(cand.cells[peers.rank] + (half + b) * COMM_MAX_WORLD + tid);
+    } else {
+      report(status, ST_TIMEOUT_PEER);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    epochs[b] = epoch;
+    if (s_ok) {
+      best = -INFINITY;
+      best_i = 0x7fffffff;
+      for (int p = 0; p < peers.world; ++p) {
+        const float v = __uint_as_float(uint32_t(s_cand[p] >> 32));
+        const int i = int(uint32_t(s_cand[p]));
+        if (sample_better(v, i, best, best_i)) {
+          best = v;
+          best_i = i;
+        }
+      }
+    }
+    out[b] = best_i;                 // after a timeout: this shard's own candidate; the host raises on the status
+    if (b == 0) out[gridDim.x] = (long long)(*reinterpret_cast<const volatile uint32_t*>(status) & ST_CODE_MASK);
+  }
+}
+
+void launch_sample_exchange(const CommPeers& peers, const SamplePeers& cand, const void* logits, const void* temps,
+                            void* out, int B, int V, long long ld, uint32_t seed, int vocab_offset, int v_limit,
+                            uint32_t* epochs, uint32_t* status, cudaStream_t stream) {
+  if (B == 0) return;
+  if (B > COMM_MAX_SLOTS) throw std::runtime_error("sample exchange: more requests than flag slots");
+  cudaError_t e = launch_pdl(PDL_SAMPLE, sample_exchange_kernel, dim3(B), dim3(1024), 0, stream, peers, cand,
+                             (const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed, vocab_offset,
+                             v_limit, epochs, status);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sample exchange launch: ") + cudaGetErrorString(e));
+}
+
 }  // namespace fc
 
 namespace fc {
@@ -249,14 +354,15 @@ namespace fc {
 __global__ void wait_gathered_kernel(const uint32_t* flags, int world, uint32_t epoch, uint32_t* status) {
   if (threadIdx.x < world) {
     const uint64_t t0 = global_timer_ns();
+    const uint64_t limit = peer_wait_limit_ns(status);
     bool got = false;
-    for (uint32_t i = 0;; ++i) {
+    for (uint32_t i = 0; i < FC_PEER_SPIN_LIMIT; ++i) {
       if (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) >= 0) {
         got = true;
         break;
       }
       __nanosleep(40);
-      if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
+      if ((i & 255u) == 255u && global_timer_ns() - t0 > limit) break;
     }
     if (!got) report(status, ST_TIMEOUT_PEER);
   }

@@ -17,6 +17,19 @@ struct CommPeers {
   uint32_t* flags[COMM_MAX_WORLD];          // [COMM_MAX_SLOTS][COMM_MAX_WORLD] words per rank
 };
 
+// Candidate tables of the sampler over vocabulary shards: per rank [2][COMM_MAX_SLOTS][COMM_MAX_WORLD] 8-byte
+// cells (value bits << 32 | global token index) in symmetric memory.
+struct SamplePeers {
+  uint64_t* cells[COMM_MAX_WORLD];
+};
+constexpr size_t SAMPLE_CELLS_PER_RANK = size_t(2) * COMM_MAX_SLOTS * COMM_MAX_WORLD;
+
+// logits [B, V] are this rank's shard (vocabulary entries vocab_offset ... vocab_offset + V - 1, entries >= v_limit
+// are padding); out int64 [B + 1]: the tokens, identical on every rank, then the device status code.
+void launch_sample_exchange(const CommPeers& peers, const SamplePeers& cand, const void* logits, const void* temps,
+                            void* out, int B, int V, long long ld, uint32_t seed, int vocab_offset, int v_limit,
+                            uint32_t* epochs, uint32_t* status, cudaStream_t stream);
+
 void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* mc_in, void* residual,
                                   const void* weight, void* out, int T, int H, float eps, uint32_t* epochs,
                                   uint32_t* status, bool use_multimem, cudaStream_t stream,

@@ -15,6 +15,8 @@ struct CommState {
   fc::CommPeers peers{};
   uint64_t mc[2] = {0, 0};
   Tensor epochs;
+  bool sample_ready = false;
+  fc::SamplePeers cand{};
 };
 CommState g_comm;
 
@@ -39,7 +41,36 @@ void comm_init(int64_t rank, int64_t world, const std::vector<int64_t>& data0, c
 
 void comm_shutdown() {
   g_comm.ready = false;
+  g_comm.sample_ready = false;
   g_comm.epochs = Tensor();
+}
+
+// Candidate tables (one symmetric allocation of fc::SAMPLE_CELLS_PER_RANK int64 cells per rank, zeroed).
+void sample_exchange_init(const std::vector<int64_t>& cells) {
+  TORCH_CHECK(g_comm.ready, "comm_init was not called");
+  TORCH_CHECK((int64_t)cells.size() == g_comm.peers.world, "need one pointer per rank");
+  for (int i = 0; i < g_comm.peers.world; ++i) g_comm.cand.cells[i] = reinterpret_cast<uint64_t*>(cells[i]);
+  g_comm.sample_ready = true;
+}
+
+// Tokens drawn from vocabulary-sharded logits; every rank returns the same [B] tokens followed by its device
+// status code ([B + 1] int64).
+Tensor sample_exchange(const Tensor& logits, const Tensor& temps, int64_t seed, int64_t vocab_offset, int64_t v_limit,
+                       Tensor status) {
+  TORCH_CHECK(g_comm.ready && g_comm.sample_ready, "sample_exchange_init was not called");
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == torch::kBFloat16 && logits.dim() == 2 &&
+                  logits.stride(1) == 1, "logits must be bf16 [B, V] with unit inner stride");
+  TORCH_CHECK(temps.is_cuda() && temps.scalar_type() == torch::kFloat32 && temps.numel() == logits.size(0),
+              "temperatures must be fp32 [B] on the device");
+  TORCH_CHECK(logits.size(0) <= fc::COMM_MAX_SLOTS, "at most ", fc::COMM_MAX_SLOTS, " requests per call");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty({logits.size(0) + 1}, logits.options().dtype(torch::kInt64));
+  fc::launch_sample_exchange(g_comm.peers, g_comm.cand, logits.data_ptr(), temps.data_ptr(), out.data_ptr(),
+                             int(logits.size(0)), int(logits.size(1)), logits.stride(0), uint32_t(seed),
+                             int(vocab_offset), int(v_limit),
+                             reinterpret_cast<uint32_t*>(g_comm.epochs.data_ptr<int>()),
+                             reinterpret_cast<uint32_t*>(status.data_ptr<int>()), at::cuda::getCurrentCUDAStream());
+  return out;
 }
 
 // The partial sums of this rank are rows [0, T) of staging buffer `buf`.  Returns the normalised
@@ -166,6 +197,9 @@ void wait_gathered(int64_t epoch, Tensor status) {
 void register_comm(pybind11::module_& m) {
   m.def("comm_init", &comm_init);
   m.def("comm_shutdown", &comm_shutdown);
+  m.def("sample_exchange_init", &sample_exchange_init);
+  m.def("sample_exchange", &sample_exchange);
+  m.def("sample_cells_per_rank", []() { return int64_t(fc::SAMPLE_CELLS_PER_RANK); });
   m.def("allreduce_add_rmsnorm", &allreduce_add_rmsnorm, pybind11::arg("buf"), pybind11::arg("residual"),
         pybind11::arg("weight"), pybind11::arg("eps"), pybind11::arg("use_multimem"), pybind11::arg("status"),
         pybind11::arg("partial") = pybind11::none(), pybind11::arg("splits") = 0,

@@ -11,6 +11,7 @@
 #include "kernels.h"
 #include "launch.h"
 #include "ptx.cuh"
+#include "sample.cuh"
 
 namespace fc {
 
@@ -389,82 +390,26 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
 }
 
 // ------------------------------------------------------------------- sampler
-__device__ __forceinline__ uint32_t mix32(uint32_t x) {
-  x ^= x >> 16;
-  x *= 0x7feb352dU;
-  x ^= x >> 15;
-  x *= 0x846ca68bU;
-  x ^= x >> 16;
-  return x;
-}
-
 // token[b] = argmax_j logits[b, j] / T_b + Gumbel_j   (plain argmax when T_b == 0).
 // argmax(softmax(l / T) / E) with E ~ Exp(1) is the same draw: log p_j - log E_j.
+// out has B + 1 entries: the last one receives the device status word, so the host learns about a wait that
+// ran out (or a bad index) with the tokens it reads back every step anyway.
 __global__ void __launch_bounds__(1024)
 sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, long long* __restrict__ out,
-              int V, long long ld, uint32_t seed) {
+              int V, long long ld, uint32_t seed, int vocab_offset, int v_limit, const uint32_t* status) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x;
-  const float T = temps[b];
-  const bf16* row = logits + (long long)b * ld;
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  const uint32_t row_seed = mix32(seed ^ (uint32_t(b) * 0x9E3779B9u));
-  auto consider = [&](float v, int j) {
-    if (T > 0.f) {
-      const uint32_t r = mix32(row_seed + uint32_t(j));
-      const float u = (float(r >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
-      v = v / T - __logf(-__logf(u));
-    }
-    if (v > best || (v == best && j < best_i)) {
-      best = v;
-      best_i = j;
-    }
-  };
-  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
-  const int v8 = vec ? (V >> 3) : 0;
-  for (int c = threadIdx.x; c < v8; c += blockDim.x) {           // 16-byte loads: 8 logits at a time
-    const uint4 u = reinterpret_cast<const uint4*>(row)[c];
-    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __bfloat1622float2(h2[i]);
-      consider(f.x, c * 8 + 2 * i);
-      consider(f.y, c * 8 + 2 * i + 1);
-    }
-  }
-  for (int j = v8 * 8 + threadIdx.x; j < V; j += blockDim.x) consider(__bfloat162float(row[j]), j);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) {
-      best = ov;
-      best_i = oi;
-    }
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    s_val[warp] = best;
-    s_idx[warp] = best_i;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    best = (lane < (blockDim.x >> 5)) ? s_val[lane] : -INFINITY;
-    best_i = (lane < (blockDim.x >> 5)) ? s_idx[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (ov > best || (ov == best && oi < best_i)) {
-        best = ov;
-        best_i = oi;
-      }
-    }
-    if (lane == 0) out[b] = best_i;
+  float best;
+  int best_i;
+  sample_row_best(logits + (long long)b * ld, V, vocab_offset, v_limit, temps[b], sample_row_seed(seed, b), s_val,
+                  s_idx, best, best_i);
+  if (threadIdx.x == 0) {
+    out[b] = best_i;
+    if (b == 0 && status != nullptr)
+      out[gridDim.x] = (long long)(*reinterpret_cast<const volatile uint32_t*>(status) & ST_CODE_MASK);
   }
 }
 
@@ -524,10 +469,10 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
 }
 
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
-                   cudaStream_t s) {
+                   cudaStream_t s, int vocab_offset, int v_limit, const uint32_t* status) {
   if (B == 0) return;
   launch_pdl(PDL_SAMPLE, sample_kernel, dim3(B), dim3(1024), 0, s, (const bf16*)logits, (const float*)temps, (long long*)out, V,
-             ld, seed);
+             ld, seed, vocab_offset, v_limit < 0 ? vocab_offset + V : v_limit, status);
 }
 
 }  // namespace fc

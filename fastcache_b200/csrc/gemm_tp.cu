@@ -81,10 +81,14 @@ __device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
 // bounded wait for a flag to reach `epoch` (epochs only grow)
 __device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status) {
   const uint64_t t0 = global_timer_ns();
-  for (uint32_t i = 0;; ++i) {
+  uint64_t limit = FC_PEER_WAIT_LIMIT_NS;
+  for (uint32_t i = 0; i < (1u << 28); ++i) {
     if (int32_t(tp_ld_acquire(flag) - epoch) >= 0) return true;
     __nanosleep(40);
-    if ((i & 255u) == 255u && global_timer_ns() - t0 > 10000000000ull) break;
+    if ((i & 255u) == 255u) {
+      if (i == 255u) limit = peer_wait_limit_ns(status);
+      if (global_timer_ns() - t0 > limit) break;
+    }
   }
   report(status, ST_TIMEOUT_PEER);
   return false;

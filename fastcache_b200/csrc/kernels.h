@@ -20,8 +20,10 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
                               uint32_t* status, cudaStream_t s, const float* partial = nullptr, int splits = 0,
                               long long split_stride = 0);   // partial != nullptr (head_dim 128 only): qkv is still
                                                              // fp32 split-K partial sums [splits, T, heads * D]
+// out: int64 [B + 1] when `status` is given (the last entry receives the status code), else [B].  Column j of
+// the logits is vocabulary entry vocab_offset + j; entries >= v_limit (-1: none) are padding.
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
-                   cudaStream_t s);
+                   cudaStream_t s, int vocab_offset = 0, int v_limit = -1, const uint32_t* status = nullptr);
 
 int decode_attn_pick_splits(int B, int Hkv, int max_ctx, int num_sms);
 void launch_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,

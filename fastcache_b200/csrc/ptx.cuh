@@ -26,12 +26,35 @@ enum : uint32_t {
 #define FC_SPIN_LIMIT (1u << 22)   // a few seconds of polling at most, then the kernel unwinds
 #endif
 
+// The status word (one 32-bit word per device, or a word of the caller's):
+//   bits 0-7   first error code reported since the host last cleared them (ST_*)
+//   bits 8-31  wait limit in microseconds for this device's kernels, 0 = the built-in limits
+//              (FC_WAIT_LIMIT_NS for mbarriers, FC_PEER_WAIT_LIMIT_NS for flags of other GPUs)
+// The limit is read on the slow path of a wait only (after tens of failed polls), so it costs nothing in a
+// healthy run; a test sets a few milliseconds and lets a wait run out on a flag that nothing posts.
+constexpr uint32_t ST_CODE_MASK = 0xFFu;
+constexpr int ST_LIMIT_SHIFT = 8;
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// first writer wins; the limit bits stay as they are
 __device__ __forceinline__ void report(uint32_t* status, uint32_t code) {
-  if (status != nullptr) atomicCAS(status, 0u, code);
+  if (status == nullptr) return;
+  uint32_t old = *reinterpret_cast<volatile uint32_t*>(status);
+  while ((old & ST_CODE_MASK) == 0u) {
+    const uint32_t prev = atomicCAS(status, old, old | (code & ST_CODE_MASK));
+    if (prev == old) break;
+    old = prev;
+  }
+}
+__device__ __forceinline__ uint64_t status_wait_limit_ns(const uint32_t* status, uint64_t builtin_ns) {
+  if (status != nullptr) {
+    const uint32_t us = *reinterpret_cast<const volatile uint32_t*>(status) >> ST_LIMIT_SHIFT;
+    if (us != 0u) return uint64_t(us) * 1000ull;
+  }
+  return builtin_ns;
 }
 
 // ------------------------------------------------------------------ mbarrier
@@ -77,12 +100,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
+  uint64_t limit = FC_WAIT_LIMIT_NS;
   for (uint32_t i = 0; i < FC_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && global_timer_ns() - t0 > FC_WAIT_LIMIT_NS) break;
+    if ((i & 63u) == 63u) {
+      if (i == 63u) limit = status_wait_limit_ns(status, FC_WAIT_LIMIT_NS);
+      if (global_timer_ns() - t0 > limit) break;
+    }
   }
   report(status, code);
   return false;
+}
+
+// Limit of a wait on another GPU's flag.  Ranks are launched by different host processes: seconds of skew
+// are normal at start-up, more is a failure.
+#ifndef FC_PEER_WAIT_LIMIT_NS
+#define FC_PEER_WAIT_LIMIT_NS 10000000000ull
+#endif
+__device__ __forceinline__ uint64_t peer_wait_limit_ns(const uint32_t* status) {
+  return status_wait_limit_ns(status, FC_PEER_WAIT_LIMIT_NS);
 }
 
 // ----------------------------------------------------------------------- TMA

@@ -57,6 +57,10 @@ def load_weights(model: nn.Module, named_tensors: Iterable[Tuple[str, torch.Tens
                 target = name.replace(key, packed_name)
                 shard_id = sid
                 break
+        if target not in params and name in params:
+            # the name only looks packed: the vision towers keep separate q / k / v projections under the same
+            # leaf names that the language model packs
+            target, shard_id = name, None
         param = params.get(target)
         if param is None:
             if target in buffers:
