@@ -101,6 +101,7 @@ def _transformers_4x_config_view():
 
 def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
     import torch
+    from bench import COMPRESSION_LABEL, SAMPLING_TEMPERATURE, job_config
     hf, n_req, p_len, o_len = workload
     n_req = args.requests or n_req
     sys.path.insert(0, os.path.join(HERE, "shims"))
@@ -119,8 +120,8 @@ def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
                    compression_factor=2, async_compression=False, max_model_len=p_len + o_len + 256,
                    max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768, kvcache_block_size=256,
                    gpu_memory_utilization=args.mem_util, enforce_eager=False)
-    sp = SamplingParams(temperature=0.6, max_tokens=o_len, ignore_eos=True)
-    wsp = SamplingParams(temperature=0.6, max_tokens=4, ignore_eos=True)
+    sp = SamplingParams(temperature=SAMPLING_TEMPERATURE, max_tokens=o_len, ignore_eos=True)
+    wsp = SamplingParams(temperature=SAMPLING_TEMPERATURE, max_tokens=4, ignore_eos=True)
     for w in range(args.warmup):                    # the same reduced waves as the other arm
         for p in prompts_for(min(8, n_req), p_len, hf["vocab_size"], 1000 + w):
             llm.add_request(p, wsp)
@@ -160,13 +161,9 @@ def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights",
-        "config": {"model": model_label, "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
-                   "parallelism": "tp1", "compression": f"{method} keep 50% (reference engine-native variant)"
-                   if compress else "none", "cuda_graph_decode": True, "kv_block": 256,
-                   "l2": "working set per step far exceeds L2; no flush needed",
-                   "step": "one whole job (all requests submitted at once, served to completion)",
-                   "warmup_step": "wave of 8 prompts of the same length, 4 output tokens",
-                   "engine_steps": engine_steps},
+        "config": job_config(model_label, n_req, p_len, o_len, 1,
+                             COMPRESSION_LABEL["knorm_ref"] if (compress and method == "knorm") else
+                             (f"{method} keep 50%" if compress else "none"), engine_steps),
         "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
         "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
         "output_tokens": out_tokens,

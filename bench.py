@@ -6,9 +6,11 @@
 
 Config (the reference's text benchmark shape): Qwen3-8B architecture, bf16,
 random-init weights, synthetic token ids; 128 concurrent requests of 4096
-prompt tokens and 512 output tokens each; KV eviction by key norm (default) or
-SnapKV (--method snapkv, window 64, pooling kernel 5) keeping 50 % of the prompt
-rows; CUDA-graph decode; tensor parallel over the N GPUs.
+prompt tokens and 512 output tokens each, sampled at temperature 0.6; KV eviction
+by key norm (default: the variant of the reference's engine, so both arms do the
+same work; --method knorm scores per head) or SnapKV (--method snapkv, window 64,
+pooling kernel 5) keeping 50 % of the prompt rows; CUDA-graph decode; tensor
+parallel over the N GPUs.
 
 A "step" is one complete serving job: all requests of the workload submitted at
 once and served to their last output token (the unit the reference's benchmark
@@ -76,6 +78,26 @@ MODEL_LABEL = {
     "qwen3-32b-small": "Qwen3-32B shape cut to 4 layers (functional check only)",
     "llama2-7b-small": "Llama-2-7B shape cut to 4 layers (functional check only)",
 }
+
+
+SAMPLING_TEMPERATURE = 0.6          # the reference's benchmarks sample at 0.6 (bench_llava.py:54-117)
+COMPRESSION_LABEL = {
+    "knorm_ref": "knorm keep 50% (reference engine-native variant)",
+    "knorm": "knorm keep 50% (per-head scores, smallest norms kept)",
+    "snapkv": "snapkv keep 50% (window 64, kernel 5)",
+    "streaming_llm": "streaming_llm keep 50%",
+}
+
+
+def job_config(model_label, n_req, p_len, o_len, world, compression, engine_steps):
+    """The part of the `config` entry that both arms (this build and the reference) fill identically."""
+    return {"model": model_label, "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
+            "parallelism": f"tp{world}", "compression": compression, "temperature": SAMPLING_TEMPERATURE,
+            "cuda_graph_decode": True, "kv_block": 256,
+            "l2": "working set per step (weights 16 GB + KV) far exceeds the 126 MB L2; no flush needed",
+            "step": "one whole job (all requests submitted at once, served to completion)",
+            "warmup_step": "wave of 8 prompts of the same length, 4 output tokens",
+            "engine_steps": engine_steps}
 
 
 class ClockSampler(threading.Thread):
@@ -200,7 +222,7 @@ def run_ours(args):
         comp_kw = dict(enable_compression=not args.no_compression, compression_backend="kvpress",
                        kvpress_method=method, compression_factor=2, compression_pipeline="prefill",
                        kvpress_params=kv_params)
-        comp_label = f"{method} keep 50%"
+        comp_label = COMPRESSION_LABEL.get(method, f"{method} keep 50%")
     else:
         from fastcache_b200 import compress as compress_mod
         head_dim = hf.get("head_dim") or hf["hidden_size"] // hf["num_attention_heads"]
@@ -221,11 +243,11 @@ def run_ours(args):
               gpu_memory_utilization=args.mem_util, seed=0, prefix_caching=False,
               **({"num_kvcache_blocks": args.kv_blocks} if args.kv_blocks > 0 else {}), **comp_kw)
     runner = llm.model_runner
-    sp = SamplingParams(temperature=0.0, max_tokens=o_len, ignore_eos=True)
+    sp = SamplingParams(temperature=SAMPLING_TEMPERATURE, max_tokens=o_len, ignore_eos=True)
 
     # ---- warm-up (untimed): W reduced waves that run every kernel of the job at its full
     # prefill batch shape (8 prompts of the job's length), compression and graph decode included
-    wsp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    wsp = SamplingParams(temperature=SAMPLING_TEMPERATURE, max_tokens=4, ignore_eos=True)
     for w in range(args.warmup):
         for p in prompts_for(min(8, n_req), p_len, hf["vocab_size"], 1000 + w):
             llm.add_request(p, wsp)
@@ -276,16 +298,11 @@ def run_ours(args):
             "steps": steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / max(1, steps), 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": base, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights",
-            "config": {"model": MODEL_LABEL[args.config],
-                       "global_batch": n_req, "seq_len": p_len, "output_len": o_len,
-                       "parallelism": f"tp{world}", "compression": comp_label if not args.no_compression else "none",
-                       "compressions": llm.stats.compressions, "lazy_triggers": llm.stats.lazy_triggers,
-                       "preemptions": llm.stats.preemptions, "blocks_freed": llm.stats.blocks_freed,
-                       "cuda_graph_decode": True, "kv_block": 256,
-                       "l2": "working set per step (weights 16 GB + KV) far exceeds the 126 MB L2; no flush needed",
-                       "step": "one whole job (all requests submitted at once, served to completion)",
-                       "warmup_step": "wave of 8 prompts of the same length, 4 output tokens",
-                       "engine_steps": engine_steps, "prefill_steps": llm.stats.prefill_steps, "decode_steps": llm.stats.decode_steps},
+            "config": dict(job_config(MODEL_LABEL[args.config], n_req, p_len, o_len, world,
+                                      comp_label if not args.no_compression else "none", engine_steps),
+                           compressions=llm.stats.compressions, lazy_triggers=llm.stats.lazy_triggers,
+                           preemptions=llm.stats.preemptions, blocks_freed=llm.stats.blocks_freed,
+                           prefill_steps=llm.stats.prefill_steps, decode_steps=llm.stats.decode_steps),
             "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
             "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
             "output_tokens": out_tokens,
@@ -512,7 +529,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3, help="reduced warm-up waves (at least 3)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3-8b", choices=sorted(WORKLOADS) + sorted(SERVING))
-    ap.add_argument("--method", default="knorm", choices=["knorm", "snapkv", "knorm_ref", "streaming_llm"])
+    ap.add_argument("--method", default="knorm_ref", choices=["knorm", "snapkv", "knorm_ref", "streaming_llm"],
+                    help="knorm_ref: the key-norm variant of the reference's engine (head-mean norms, one index set for "
+                         "all heads, largest kept), the one both arms run; knorm: per-head scores, smallest norms kept")
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--no-compression", action="store_true")
     ap.add_argument("--mem-util", type=float, default=0.85)

@@ -4,42 +4,71 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <string>
 #include <unordered_map>
 
 #include "gemm.h"
 #include "kernels.h"
+#include "workspace.h"
 
 namespace {
 
 using torch::Tensor;
 
 struct DeviceWorkspace {
-  Tensor gemm_scratch, gemm_counters, status, attn_o, attn_lse;
+  Tensor gemm_scratch, gemm_counters, grid_sync, attn_o, attn_lse;
+  fc::StreamWorkspace raw;
 };
-std::unordered_map<int, DeviceWorkspace> g_ws;
+struct DeviceState {
+  Tensor status;
+};
+std::unordered_map<uint64_t, DeviceWorkspace> g_ws;      // (device, stream) -> scratch
+std::unordered_map<int, DeviceState> g_dev;
 std::unordered_map<uint64_t, int> g_stream_sms;
 std::mutex g_mu;
 
-constexpr int64_t ATTN_WS_FLOATS = 4 << 20;   // 16 MiB of split-KV partial outputs
-constexpr int64_t ATTN_LSE_FLOATS = 1 << 18;
+using fc::ATTN_LSE_FLOATS;
+using fc::ATTN_WS_FLOATS;
 
-DeviceWorkspace& workspace(int dev) {
+Tensor& device_status(int dev) {
   std::lock_guard<std::mutex> lk(g_mu);
-  auto it = g_ws.find(dev);
+  auto it = g_dev.find(dev);
+  if (it != g_dev.end()) return it->second.status;
+  DeviceState d;
+  d.status = torch::zeros({4}, torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, dev));
+  return g_dev.emplace(dev, std::move(d)).first->second.status;
+}
+
+DeviceWorkspace& workspace(int dev, cudaStream_t stream) {
+  Tensor& status = device_status(dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  // stream handles are pointers: fold the device into the bits an aligned pointer leaves free
+  const uint64_t key = (reinterpret_cast<uint64_t>(stream) << 8) ^ uint64_t(dev & 0xFF);
+  auto it = g_ws.find(key);
   if (it != g_ws.end()) return it->second;
   auto f32 = torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, dev);
   auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, dev);
   DeviceWorkspace w;
   w.gemm_scratch = torch::empty({int64_t(fc::gemm_scratch_bytes() / 4)}, f32);
   w.gemm_counters = torch::zeros({int64_t(fc::gemm_counter_bytes() / 4)}, i32);
-  w.status = torch::zeros({4}, i32);
-  w.attn_o = torch::empty({ATTN_WS_FLOATS}, f32);
-  w.attn_lse = torch::empty({ATTN_LSE_FLOATS}, f32);
-  return g_ws.emplace(dev, std::move(w)).first->second;
+  w.grid_sync = torch::zeros({4}, i32);
+  w.attn_o = torch::empty({int64_t(ATTN_WS_FLOATS)}, f32);
+  w.attn_lse = torch::empty({int64_t(ATTN_LSE_FLOATS)}, f32);
+  w.raw.gemm_scratch = w.gemm_scratch.data_ptr<float>();
+  w.raw.gemm_counters = w.gemm_counters.data_ptr<int>();
+  w.raw.grid_sync = reinterpret_cast<uint32_t*>(w.grid_sync.data_ptr<int>());
+  w.raw.attn_o = w.attn_o.data_ptr<float>();
+  w.raw.attn_lse = w.attn_lse.data_ptr<float>();
+  w.raw.status = reinterpret_cast<uint32_t*>(status.data_ptr<int>());
+  return g_ws.emplace(key, std::move(w)).first->second;
 }
 
-uint32_t* status_ptr(int dev) { return reinterpret_cast<uint32_t*>(workspace(dev).status.data_ptr<int>()); }
+// the workspace of the current stream of `dev`
+DeviceWorkspace& workspace(int dev) { return workspace(dev, at::cuda::getCurrentCUDAStream(dev)); }
+
+uint32_t* status_ptr(int dev) { return reinterpret_cast<uint32_t*>(device_status(dev).data_ptr<int>()); }
 
 void check_bf16(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
@@ -80,7 +109,8 @@ Tensor gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias,
   fc::GemmWorkspace gw;
   gw.scratch = ws.gemm_scratch.data_ptr<float>();
   gw.counters = ws.gemm_counters.data_ptr<int>();
-  gw.status = reinterpret_cast<uint32_t*>(ws.status.data_ptr<int>());
+  gw.status = ws.raw.status;
+  gw.grid_sync = ws.raw.grid_sync;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   fc::gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, int(M), int(N), int(K), x.stride(0), w.stride(0),
                 out.stride(0), int(act), gw, sm_limit_for(stream), stream);
@@ -95,7 +125,8 @@ static int gemm_maybe_partial(const Tensor& x, const Tensor& w, Tensor& out, Dev
   fc::GemmWorkspace gw;
   gw.scratch = ws.gemm_scratch.data_ptr<float>();
   gw.counters = ws.gemm_counters.data_ptr<int>();
-  gw.status = reinterpret_cast<uint32_t*>(ws.status.data_ptr<int>());
+  gw.status = ws.raw.status;
+  gw.grid_sync = ws.raw.grid_sync;
   if (M <= 256) {
     return fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, int(M), int(N), int(K),
                                 x.stride(0), w.stride(0), out.stride(0), 0, gw, sm_limit_for(stream), 0, false,
@@ -151,6 +182,23 @@ Tensor linear_add_rms_norm(const Tensor& x, const Tensor& w, const c10::optional
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   Tensor y = torch::empty({M, N}, x.options());
   if (M == 0) return y;
+  if (M <= 256 && fc::fused_epilogues_enabled()) {
+    // one kernel: GEMM, grid barrier, then split-K sum + residual add + RMSNorm by the GEMM's own CTAs
+    fc::GemmWorkspace gw;
+    gw.scratch = ws.raw.gemm_scratch;
+    gw.counters = ws.raw.gemm_counters;
+    gw.status = ws.raw.status;
+    gw.grid_sync = ws.raw.grid_sync;
+    fc::SkinnyFused f;
+    f.epi = fc::EPI_ADD_NORM;
+    f.residual = residual.data_ptr();
+    f.norm_w = norm_w.data_ptr();
+    f.y = y.data_ptr();
+    f.eps = float(eps);
+    if (fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), nullptr, bptr, int(M), int(N), int(x.size(1)), x.stride(0),
+                             w.stride(0), N, 0, gw, sm_limit_for(stream), 0, false, stream, &f) > 0)
+      return y;
+  }
   Tensor tmp = torch::empty({M, N}, x.options());
   const int splits = gemm_maybe_partial(x, w, tmp, ws, stream);
   if (splits > 1) {
@@ -454,9 +502,9 @@ Tensor sample(const Tensor& logits, const Tensor& temps, int64_t seed, bool with
 // Reads the code bits of the device status word and clears them (synchronises the current stream); the wait
 // limit kept in the upper bits stays.
 int64_t read_status(int64_t device) {
-  auto& ws = workspace(int(device));
-  const int64_t v = ws.status[0].item<int>();
-  if ((v & 0xFF) != 0) ws.status[0].bitwise_and_(~0xFF);
+  Tensor& st = device_status(int(device));
+  const int64_t v = st[0].item<int>();
+  if ((v & 0xFF) != 0) st[0].bitwise_and_(~0xFF);
   return v & 0xFF;
 }
 
@@ -464,9 +512,21 @@ int64_t read_status(int64_t device) {
 // device's status word; 0 restores the built-in limits.  For tests and for deployments that prefer to fail fast.
 void set_wait_limit_us(int64_t device, int64_t us) {
   TORCH_CHECK(us >= 0 && us < (1 << 24), "limit must be in [0, 2^24) microseconds");
-  auto& ws = workspace(int(device));
-  const int64_t v = ws.status[0].item<int>();
-  ws.status[0].fill_(int64_t(int32_t((uint32_t(v) & 0xFFu) | (uint32_t(us) << 8))));
+  Tensor& st = device_status(int(device));
+  const int64_t v = st[0].item<int>();
+  st[0].fill_(int64_t(int32_t((uint32_t(v) & 0xFFu) | (uint32_t(us) << 8))));
+}
+
+// After a kernel reported a wait that ran out, the arrival counters it was using may be left mid-count: zero the
+// grid-barrier words and the split-K tile counters of every stream of the device (the host calls this once the
+// device is idle, e.g. from LLMEngine.recover()).
+void reset_sync_state(int64_t device) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (auto& kv : g_ws) {
+    if (int(kv.first & 0xFF) != int(device & 0xFF)) continue;
+    kv.second.grid_sync.zero_();
+    kv.second.gemm_counters.zero_();
+  }
 }
 
 void register_stream_sms(int64_t stream_ptr, int64_t sms) {
@@ -481,6 +541,18 @@ void register_greenctx(pybind11::module_& m);
 void register_compress(pybind11::module_& m);
 void register_comm(pybind11::module_& m);
 
+namespace fc {
+const StreamWorkspace& stream_workspace(int device, cudaStream_t stream) { return workspace(device, stream).raw; }
+int stream_sm_limit(cudaStream_t stream) { return sm_limit_for(stream); }
+bool fused_epilogues_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("FC_FUSED_EPILOGUE");
+    return e == nullptr || std::string(e) != "0";
+  }();
+  return on;
+}
+}  // namespace fc
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "y = act(x @ w.T + bias) on tcgen05", py::arg("x"), py::arg("w"), py::arg("bias") = py::none(),
         py::arg("act") = 0, py::arg("out") = py::none());
@@ -494,7 +566,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_qknorm_store", &rope_qknorm_store);
   m.def("linear_rope_qknorm_store", &linear_rope_qknorm_store);
   m.def("gemm_partial", &gemm_partial);
-  m.def("gemm_scratch", [](int64_t device) { return workspace(int(device)).gemm_scratch; });
+  m.def("gemm_scratch", [](int64_t device) { return workspace(int(device)).gemm_scratch; },
+        "split-K scratch of the CURRENT stream of the device");
   m.def("prefill_attention", &prefill_attention);
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,
@@ -504,9 +577,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dense_attention", &dense_attention);
   m.def("read_status", &read_status);
   m.def("set_wait_limit_us", &set_wait_limit_us);
+  m.def("reset_sync_state", &reset_sync_state);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
-  m.def("status_tensor", [](int64_t device) { return workspace(int(device)).status; });
+  m.def("status_tensor", [](int64_t device) { return device_status(int(device)); });
   register_greenctx(m);
   register_compress(m);
   register_comm(m);

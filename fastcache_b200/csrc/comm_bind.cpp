@@ -6,6 +6,8 @@
 #include <vector>
 
 #include "comm.h"
+#include "gemm.h"
+#include "workspace.h"
 
 namespace {
 using torch::Tensor;
@@ -106,6 +108,72 @@ Tensor allreduce_add_rmsnorm(int64_t buf, Tensor residual, const Tensor& weight,
                                    at::cuda::getCurrentCUDAStream(), part, int(splits), residual.numel(), bptr);
   return out;
 }
+// Decode-size row-parallel projection with everything that follows it: residual += sum over ranks of (x @ w.T
+// (+ bias)); returns RMSNorm(residual) * norm_w.  One kernel when the shape allows (the GEMM's CTAs meet at a grid
+// barrier, finish their token rows into staging buffer `buf`, exchange flags with the peers and reduce), else the
+// GEMM and the one-shot all-reduce kernel.
+Tensor linear_allreduce_add_rmsnorm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t buf,
+                                    Tensor residual, const Tensor& norm_w, double eps, bool use_multimem,
+                                    Tensor status) {
+  TORCH_CHECK(g_comm.ready, "comm_init was not called");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 &&
+                  x.stride(0) % 8 == 0 && x.size(1) % 8 == 0, "x must be a row-major bf16 matrix with K % 8 == 0");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.dim() == 2 && w.stride(1) == 1 &&
+                  w.stride(0) % 8 == 0 && w.size(1) == x.size(1), "weight must be row-major bf16 [N, K]");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(M <= 256, "decode-size inputs only (at most 256 rows)");
+  TORCH_CHECK(residual.is_cuda() && residual.scalar_type() == torch::kBFloat16 && residual.is_contiguous() &&
+                  residual.dim() == 2 && residual.size(0) == M && residual.size(1) == N,
+              "residual must be contiguous bf16 [M, N]");
+  TORCH_CHECK(norm_w.scalar_type() == torch::kBFloat16 && norm_w.is_contiguous() && norm_w.numel() == N,
+              "bad norm weight");
+  TORCH_CHECK(buf == 0 || buf == 1, "buf must be 0 or 1");
+  const void* bptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 && bias->is_contiguous() && bias->numel() == N,
+                "bias must be a contiguous bf16 [N] vector");
+    bptr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(residual);
+  if (M == 0) return out;
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const fc::StreamWorkspace& sw = fc::stream_workspace(x.get_device(), stream);
+  fc::GemmWorkspace gw;
+  gw.scratch = sw.gemm_scratch;
+  gw.counters = sw.gemm_counters;
+  gw.status = reinterpret_cast<uint32_t*>(status.data_ptr<int>());
+  gw.grid_sync = sw.grid_sync;
+  const void* mc = (use_multimem && g_comm.mc[buf] != 0) ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(g_comm.epochs.data_ptr<int>());
+  const int sm_limit = fc::stream_sm_limit(stream);
+  if (fc::fused_epilogues_enabled()) {
+    fc::SkinnyFused f;
+    f.epi = fc::EPI_AR_ADD_NORM;
+    f.residual = residual.data_ptr();
+    f.norm_w = norm_w.data_ptr();
+    f.y = out.data_ptr();
+    f.eps = float(eps);
+    f.peers = &g_comm.peers;
+    f.buf = int(buf);
+    f.mc_in = mc;
+    f.epochs = epochs;
+    if (fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), nullptr, bptr, int(M), int(N), int(K), x.stride(0),
+                             w.stride(0), N, 0, gw, sm_limit, 0, false, stream, &f) > 0)
+      return out;
+  }
+  // two kernels: the GEMM leaves bf16 rows in the staging buffer or fp32 split-K partial sums in scratch, the
+  // all-reduce kernel finishes them
+  void* staging = g_comm.peers.data[buf][g_comm.peers.rank];
+  const int splits = fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), staging, bptr, int(M), int(N), int(K),
+                                          x.stride(0), w.stride(0), N, 0, gw, sm_limit, 0, false, stream);
+  fc::launch_allreduce_add_rmsnorm(g_comm.peers, int(buf), mc, residual.data_ptr(), norm_w.data_ptr(),
+                                   out.data_ptr(), int(M), int(N), float(eps), epochs, gw.status, mc != nullptr,
+                                   stream, splits > 1 ? sw.gemm_scratch : nullptr, splits, M * N,
+                                   splits > 1 ? bptr : nullptr);
+  return out;
+}
+
 // ------------------------------------------------------------ prefill-size fused GEMM + collective
 struct TpState {
   bool ready = false;
@@ -204,6 +272,7 @@ void register_comm(pybind11::module_& m) {
         pybind11::arg("weight"), pybind11::arg("eps"), pybind11::arg("use_multimem"), pybind11::arg("status"),
         pybind11::arg("partial") = pybind11::none(), pybind11::arg("splits") = 0,
         pybind11::arg("bias") = pybind11::none());
+  m.def("linear_allreduce_add_rmsnorm", &linear_allreduce_add_rmsnorm);
   m.def("tp_init", &tp_init);
   m.def("gemm_rs_add_norm", &gemm_rs_add_norm);
   m.def("gemm_after_gather", &gemm_after_gather, pybind11::arg("xg"), pybind11::arg("weight"),

@@ -18,6 +18,24 @@ struct GemmWorkspace {
   float* scratch = nullptr;
   int* counters = nullptr;
   uint32_t* status = nullptr;
+  uint32_t* grid_sync = nullptr;   // [2] words of the in-kernel grid barrier (zero before the first launch)
+};
+
+// Epilogues fused into the decode-size GEMM (gemm_skinny.cu).
+enum SkinnyEpilogue : int { EPI_NONE = 0, EPI_ADD_NORM = 1, EPI_AR_ADD_NORM = 2 };
+
+struct CommPeers;
+struct SkinnyFused {
+  int epi = EPI_NONE;
+  void* residual = nullptr;        // [M, N] bf16, updated in place
+  const void* norm_w = nullptr;    // [N] bf16
+  void* y = nullptr;               // [M, N] bf16: RMSNorm(residual) * norm_w
+  float eps = 1e-6f;
+  // EPI_AR_ADD_NORM: sum over the tensor-parallel ranks between the GEMM and the residual add
+  const CommPeers* peers = nullptr;
+  int buf = 0;                     // staging buffer of this call (the two are used in alternation)
+  const void* mc_in = nullptr;     // multicast address of that buffer: multimem.ld_reduce instead of peer loads
+  uint32_t* epochs = nullptr;
 };
 
 size_t gemm_scratch_bytes();
@@ -35,8 +53,11 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
 
 // Decode-size batches (M <= 256).  Returns the number of K splits used; when that is > 1 and
 // `finalize` is false, ws.scratch holds fp32 partial sums [splits, M, N] for the caller to reduce.
+// `fused` != nullptr: the epilogue named there runs inside the kernel (`c` and `act` are unused).  Returns 0 without
+// launching anything when the shape cannot take the fused form (more row tiles than SMs, hidden size above 8192 or
+// not a multiple of 8): the caller then runs the unfused pair of kernels.
 int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                      long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
-                     int splits_request, bool finalize, cudaStream_t stream);
+                     int splits_request, bool finalize, cudaStream_t stream, const SkinnyFused* fused = nullptr);
 
 }  // namespace fc

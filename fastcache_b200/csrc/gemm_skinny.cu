@@ -17,6 +17,15 @@
 // summed by the kernel that consumes the result (add + RMSNorm and SwiGLU in
 // partials.cu, rope + KV store in elementwise.cu, the one-shot all-reduce in comm.cu)
 // or by the small finalize kernel below.  No inter-CTA synchronisation is needed.
+//
+// Fused epilogues (row-parallel projections o_proj / down_proj of a decode step): with `epi` set the kernel
+// goes on after its partial sums are written.  All CTAs meet at a grid barrier (the grid never exceeds the SM
+// count, one CTA per SM, so all of them are resident), then every CTA takes token rows c, c + grid, ...:
+//   EPI_ADD_NORM     sum of the split-K partials (+ bias) + residual -> residual, RMSNorm -> y
+//   EPI_AR_ADD_NORM  the same with the sum over tensor-parallel ranks in between: the CTA finishes its rows into
+//                    this rank's symmetric staging buffer, exchanges flags with the same CTA of every peer and
+//                    reads the peers' rows (plain peer loads in rank order, or multimem.ld_reduce)
+// which replaces the GEMM -> (all-reduce +) add + RMSNorm pair of launches by one.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -26,6 +35,8 @@
 #include <stdexcept>
 #include <string>
 
+#include "comm.h"
+#include "comm_dev.cuh"
 #include "gemm.h"
 #include "launch.h"
 #include "ptx.cuh"
@@ -48,7 +59,174 @@ struct SkinnyParams {
   int splits;
   int kb_per_split;
   uint32_t* status;
+  // fused epilogue (see the header comment); epi == EPI_NONE: everything below is unused
+  int epi;
+  uint32_t* grid_sync;            // [0] arrivals, [1] generation
+  __nv_bfloat16* residual;        // [Mtok, Nw], updated in place
+  const __nv_bfloat16* norm_w;    // [Nw]
+  __nv_bfloat16* y;               // [Mtok, Nw]
+  float eps;
+  CommPeers peers;                // EPI_AR_ADD_NORM
+  int buf;
+  const __nv_bfloat16* mc_in;     // multicast address of staging buffer `buf`, or nullptr for peer loads
+  uint32_t* epochs;
 };
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the 4 epilogue warps
+
+// Grid barrier for the 128 epilogue threads of every CTA (tid = 0..127).  Sense reversal: the generation word is
+// read before arriving (it cannot move until this CTA has arrived too), the last arriver resets the count and
+// bumps the generation, so the two words are ready for the next launch (also a replay from a CUDA graph).
+// Returns false when the bounded wait ran out.
+__device__ __forceinline__ bool skinny_grid_barrier(const SkinnyParams& p, int tid, int nctas, volatile int* s_flag) {
+  __threadfence();                         // this thread's partial sums, before the arrival
+  epi_bar();
+  if (tid == 0) {
+    volatile uint32_t* gen_p = p.grid_sync + 1;
+    const uint32_t gen = *gen_p;
+    __threadfence();
+    bool ok = true;
+    if (atomicAdd(p.grid_sync, 1u) == uint32_t(nctas - 1)) {
+      *reinterpret_cast<volatile uint32_t*>(p.grid_sync) = 0u;
+      __threadfence();
+      atomicAdd(p.grid_sync + 1, 1u);
+    } else {
+      const uint64_t t0 = global_timer_ns();
+      uint64_t limit = FC_WAIT_LIMIT_NS;
+      ok = false;
+      for (uint32_t i = 0; i < (1u << 28); ++i) {
+        if (*gen_p != gen) {
+          ok = true;
+          break;
+        }
+        if ((i & 255u) == 255u) {
+          if (i == 255u) limit = status_wait_limit_ns(p.status, FC_WAIT_LIMIT_NS);
+          if (global_timer_ns() - t0 > limit) break;
+        }
+      }
+      if (!ok) report(p.status, ST_TIMEOUT_GRID);
+    }
+    __threadfence();
+    *s_flag = ok ? 1 : 0;
+  }
+  epi_bar();
+  return *s_flag != 0;
+}
+
+constexpr int EPI_MAX_CHUNKS = 8;          // 16-byte pieces per thread and row: hidden <= 128 * 8 * 8 = 8192
+
+// sum over the K splits of 8 consecutive outputs of one token row (+ bias)
+__device__ __forceinline__ void skinny_sum_splits(const SkinnyParams& p, long long off, int col, float (&acc)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const long long stride = (long long)p.Mtok * p.Nw;
+#pragma unroll 4
+  for (int s = 0; s < p.splits; ++s) {
+    const float4* ps = reinterpret_cast<const float4*>(p.partial + s * stride + off);
+    const float4 a = __ldcg(ps), b = __ldcg(ps + 1);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  if (p.bias != nullptr) {
+    float bb[8];
+    unpack8f(*reinterpret_cast<const uint4*>(p.bias + col), bb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += bb[i];
+  }
+}
+
+// The row phase of the fused epilogues, run by the 128 epilogue threads of CTA `cta` of `nctas`.
+__device__ __noinline__ void skinny_row_phase(const SkinnyParams& p, int cta, int nctas, int tid, float* s_red,
+                                              volatile int* s_flag, uint32_t* s_epoch) {
+  const int H = p.Nw;
+  const int chunks = H >> 3;
+  if (p.epi == EPI_AR_ADD_NORM) {
+    // this rank's contribution of my rows -> staging buffer (bf16, the rounding point of a GEMM output)
+    __nv_bfloat16* mine = p.peers.data[p.buf][p.peers.rank];
+    for (int row = cta; row < p.Mtok; row += nctas) {
+      for (int idx = tid; idx < chunks; idx += 128) {
+        const long long off = (long long)row * H + (long long)idx * 8;
+        float acc[8];
+        skinny_sum_splits(p, off, idx * 8, acc);
+        *reinterpret_cast<uint4*>(mine + off) = pack8f(acc);
+      }
+    }
+    if (tid == 0) {
+      *s_epoch = p.epochs[cta] + 1;
+      *s_flag = 1;
+    }
+    epi_bar();                             // all rows of this CTA are written before any flag goes out
+    const uint32_t epoch = *s_epoch;
+    if (tid < p.peers.world && !peer_flag_exchange(p.peers, cta, epoch, tid, p.status)) *s_flag = 0;
+    epi_bar();
+    if (tid == 0) p.epochs[cta] = epoch;
+    if (*s_flag == 0) return;              // the host reads the status word and raises
+  }
+  for (int row = cta; row < p.Mtok; row += nctas) {
+    const long long base = (long long)row * H;
+    float v[EPI_MAX_CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < EPI_MAX_CHUNKS; ++c) {
+      const int idx = tid + c * 128;
+      if (idx < chunks) {
+        const long long off = base + (long long)idx * 8;
+        float acc[8];
+        if (p.epi == EPI_AR_ADD_NORM) {
+          if (p.mc_in != nullptr) {
+            unpack8f(multimem_ld_reduce_bf16x8(p.mc_in + off), acc);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+            uint4 raw[COMM_MAX_WORLD];     // every peer's piece is requested before the first is used
+#pragma unroll
+            for (int q = 0; q < COMM_MAX_WORLD; ++q)
+              if (q < p.peers.world) raw[q] = ld_peer_16(p.peers.data[p.buf][q] + off);
+#pragma unroll
+            for (int q = 0; q < COMM_MAX_WORLD; ++q) {
+              if (q < p.peers.world) {
+                float f[8];
+                unpack8f(raw[q], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += f[i];
+              }
+            }
+          }
+        } else {
+          skinny_sum_splits(p, off, idx * 8, acc);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __bfloat162float(__float2bfloat16(acc[i]));   // GEMM output rounding
+        }
+        float r[8];
+        unpack8f(*reinterpret_cast<const uint4*>(p.residual + off), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += r[i];
+        const uint4 sres = pack8f(acc);
+        *reinterpret_cast<uint4*>(p.residual + off) = sres;
+        unpack8f(sres, v[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+      }
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+    epi_bar();
+    const float tot = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    epi_bar();
+    const float inv = rsqrtf(tot / float(H) + p.eps);
+#pragma unroll
+    for (int c = 0; c < EPI_MAX_CHUNKS; ++c) {
+      const int idx = tid + c * 128;
+      if (idx < chunks) {
+        float g[8], o[8];
+        unpack8f(*reinterpret_cast<const uint4*>(p.norm_w + (size_t)idx * 8), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __bfloat162float(__float2bfloat16(v[c][i] * inv)) * g[i];
+        *reinterpret_cast<uint4*>(p.y + base + (long long)idx * 8) = pack8f(o);
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ float sk_act(float v, int act) {
   switch (act) {
@@ -88,6 +266,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint64_t* acc_full = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_flag = s_abort + 1;                                   // fused epilogues
+  uint32_t* s_epoch = reinterpret_cast<uint32_t*>(const_cast<int*>(s_abort + 2));
+  float* s_red = reinterpret_cast<float*>(const_cast<int*>(s_abort + 4));   // 4 floats
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,20 +392,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   } else {
     const int lane_group = warp & 3;
     const int row = lane_group * 32 + lane;
+    const bool direct = p.splits == 1 && p.epi == EPI_NONE;     // bf16 result straight from the accumulator
     if (!*s_abort && mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) {
       tc_fence_after();
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int n = tile * ROWS + mt * 128 + row;           // output feature of this thread
         const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(mt * BN);
-        const float bi = (p.bias != nullptr && n < p.Nw && p.splits == 1) ? __bfloat162float(p.bias[n]) : 0.f;
+        const float bi = (p.bias != nullptr && n < p.Nw && direct) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_addr + uint32_t(c * 32), r);
           tmem_ld_wait();
           if (n < p.Nw) {
-            if (p.splits == 1) {
+            if (direct) {
 #pragma unroll
               for (int t = 0; t < 32; ++t) {
                 const int tok = c * 32 + t;
@@ -242,6 +424,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           }
         }
       }
+    }
+    if (p.epi != EPI_NONE) {
+      // every CTA joins the barrier, also one whose pipeline gave up (its partial sums are then missing and the
+      // status word says so): the others must not wait for it until their own limit
+      const int nctas = gridDim.x * gridDim.y;
+      const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+      const int etid = (warp - 2) * 32 + lane;
+      if (skinny_grid_barrier(p, etid, nctas, s_flag))
+        skinny_row_phase(p, cta, nctas, etid, s_red, s_flag, s_epoch);
     }
   }
   tc_fence_before();
@@ -307,12 +498,14 @@ static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Sk
 
 // Number of K splits for `tiles` row tiles on `sms` SMs: fill the machine to a whole
 // number of waves while keeping at least 4 K blocks per CTA.
-int skinny_pick_splits(int tiles, int tile_rows, int num_kb, int sms, int M, int N, size_t scratch_floats) {
+int skinny_pick_splits(int tiles, int tile_rows, int num_kb, int sms, int M, int N, size_t scratch_floats,
+                       int max_ctas = 1 << 30) {
   int best = 1;
   double best_cost = 1e30;
   const int max_s = std::max(1, std::min(num_kb / 4, 32));
   for (int s = 1; s <= max_s; ++s) {
     if (s > 1 && (size_t)s * M * N > scratch_floats) break;
+    if (s > 1 && tiles * s > max_ctas) break;      // fused epilogues: the whole grid is resident at once
     const int ctas = tiles * s;
     const int waves = (ctas + sms - 1) / sms;
     const int kb = (num_kb + s - 1) / s;
@@ -338,7 +531,7 @@ int skinny_pick_splits(int tiles, int tile_rows, int num_kb, int sms, int M, int
 // `finalize` is false the caller consumes ws.scratch as fp32 [splits, M, N] itself.
 int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                      long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
-                     int splits_request, bool finalize, cudaStream_t stream) {
+                     int splits_request, bool finalize, cudaStream_t stream, const SkinnyFused* fused) {
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
   const int num_kb = (K + SK_BK - 1) / SK_BK;
   // 128-row tiles when 256-row tiles would cover less than half of the SMs: the same SM count is then reached
@@ -347,9 +540,19 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   const int rows = small_rows ? 128 : SK_BM;
   const int tiles = (N + rows - 1) / rows;
   const size_t scratch_floats = ws.scratch != nullptr ? gemm_scratch_bytes() / 4 : 0;
-  int splits = splits_request > 0 ? splits_request : skinny_pick_splits(tiles, rows, num_kb, sms, M, N, scratch_floats);
+  const bool fuse = fused != nullptr && fused->epi != EPI_NONE;
+  if (fuse) {
+    // the fused epilogues need the whole grid resident (one CTA per SM), partial sums for every split, and rows
+    // of 16-byte pieces that 128 threads cover in EPI_MAX_CHUNKS steps
+    if (tiles > sms || N % 8 != 0 || N > 128 * EPI_MAX_CHUNKS * 8 || ws.grid_sync == nullptr ||
+        (size_t)M * N > scratch_floats)
+      return 0;
+  }
+  int splits = splits_request > 0 ? splits_request
+                                  : skinny_pick_splits(tiles, rows, num_kb, sms, M, N, scratch_floats, fuse ? sms : 1 << 30);
   if (N % 4 != 0) splits = 1;
   if (splits > 1 && (size_t)splits * M * N > scratch_floats) splits = 1;
+  if (fuse && tiles * splits > sms) splits = std::max(1, sms / tiles);
   int kb_per = (num_kb + splits - 1) / splits;
   splits = (num_kb + kb_per - 1) / kb_per;
   SkinnyParams p{};
@@ -364,6 +567,22 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   p.splits = splits;
   p.kb_per_split = kb_per;
   p.status = ws.status;
+  if (fuse) {
+    p.epi = fused->epi;
+    p.grid_sync = ws.grid_sync;
+    p.residual = reinterpret_cast<__nv_bfloat16*>(fused->residual);
+    p.norm_w = reinterpret_cast<const __nv_bfloat16*>(fused->norm_w);
+    p.y = reinterpret_cast<__nv_bfloat16*>(fused->y);
+    p.eps = fused->eps;
+    if (fused->epi == EPI_AR_ADD_NORM) {
+      if (fused->peers == nullptr || fused->epochs == nullptr || tiles * splits > COMM_MAX_SLOTS)
+        throw std::runtime_error("fused all-reduce epilogue: communication state is missing");
+      p.peers = *fused->peers;
+      p.buf = fused->buf;
+      p.mc_in = reinterpret_cast<const __nv_bfloat16*>(fused->mc_in);
+      p.epochs = fused->epochs;
+    }
+  }
   CUtensorMap tw = make_tmap_bf16_2d(w, N, K, ldw, 128, SK_BK);
   if (M <= 32) {
     CUtensorMap tx = make_tmap_bf16_2d(x, M, K, ldx, 32, SK_BK);
@@ -382,7 +601,7 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
     if (small_rows) launch_skinny<256, 4, 128>(tw, tx, p, tiles, stream);
     else launch_skinny<256, 3, 256>(tw, tx, p, tiles, stream);
   }
-  if (splits > 1 && finalize) {
+  if (splits > 1 && finalize && !fuse) {
     const long long total = (long long)M * (N / 4);
     const int blocks = (int)std::min<long long>((total + 255) / 256, 2048);
     launch_pdl(PDL_FINALIZE, skinny_finalize_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)ws.scratch, p.bias, p.out, M,

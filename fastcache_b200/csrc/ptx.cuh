@@ -20,6 +20,7 @@ enum : uint32_t {
   ST_TIMEOUT_ACC_EMPTY = 4, // MMA warp waited for the epilogue
   ST_TIMEOUT_PEER = 5,      // wait on a flag written by another GPU
   ST_BAD_INDEX = 6,         // a block-table / slot index was out of range (access skipped)
+  ST_TIMEOUT_GRID = 7,      // a CTA waited at a grid barrier for the other CTAs of its own kernel
 };
 
 #ifndef FC_SPIN_LIMIT

@@ -251,6 +251,7 @@ class LLMEngine:
                 if p.event is not None:
                     r.main_stream.wait_event(p.event)
         self._pending.clear()
+        r.reset_sync_state()                 # arrival counters a kernel that gave up may have left mid-count
         n = self.scheduler.requeue_running()
         self.stats.recoveries += 1
         self.scheduler.block_manager.check_invariants()
@@ -492,6 +493,14 @@ class LLMEngine:
                                    len(bm.free_block_ids), len(bm.blocks), self.stats.compressions, r.main_stream)
         with nvtx_range("prefill" if is_prefill else "decode"):
             tokens = r.run(seqs, is_prefill)
+        if r.last_status:
+            # a bounded wait in a kernel ran out (or an index was out of range) during this step or a compression
+            # before it: the tokens cannot be trusted.  The scheduler state is as before the step's postprocess;
+            # `recover()` requeues the running requests.
+            code, r.last_status = r.last_status, 0
+            r.read_device_status()                   # clears the word on the device
+            from ..utils.watchdog import DeviceWaitTimeout
+            raise DeviceWaitTimeout(code)
         if rec is not None:
             self.trace.end(rec, r.main_stream)
         self._end_timing(ctl, timing, is_prefill, seqs)
@@ -543,15 +552,37 @@ class LLMEngine:
         b.record(self.model_runner.main_stream)
         b.synchronize()
         ms = a.elapsed_time(b)
+        # compressions whose end event has been reached feed an EWMA.  `event.query()` and the measured times
+        # are rank-local; the controller's decisions (batch type, pipeline, SM split) must be the same on every
+        # tensor-parallel rank, so the ranks agree on one set of numbers first
+        cands = [p for p in self._pending.values()
+                 if not p.reported and p.start_event is not None and p.event is not None]
+        done = [bool(p.event.query()) for p in cands]
+        c_ms = [p.start_event.elapsed_time(p.event) if d else 0.0 for p, d in zip(cands, done)]
+        ms, done, c_ms = self._agree_on_timings(ms, done, c_ms)
         if is_prefill:
             ctl.update_prefill(ms, sum(s.prompt_rows for s in seqs))
         else:
             ctl.update_decode(ms, len(seqs))
-        for p in self._pending.values():
-            if not p.reported and p.start_event is not None and p.event is not None and p.event.query():
-                # feeds an EWMA only; scheduling never branches on it
-                ctl.update_compress(p.start_event.elapsed_time(p.event), p.tokens)
+        for p, d, t in zip(cands, done, c_ms):
+            if d:
+                ctl.update_compress(t, p.tokens)
                 p.reported = True
+
+    def _agree_on_timings(self, ms: float, done: List[bool], c_ms: List[float]):
+        """One number per measurement for all tensor-parallel ranks: the slowest rank's step time, a
+        compression counts as finished only when it has finished everywhere, and then with its longest time.
+        (One small all-reduce every `auto_tune_interval` steps, only with `auto_tune` on.)"""
+        if tpmod.get_tp_size() <= 1:
+            return ms, done, c_ms
+        import torch.distributed as dist
+        vals = [ms] + [-float(d) for d in done] + list(c_ms)
+        dev = self.model_runner.device if self.model_runner.device.type == "cuda" else "cpu"
+        t = torch.tensor(vals, dtype=torch.float32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=tpmod.get_tp_group())
+        out = t.tolist()
+        n = len(done)
+        return out[0], [v <= -1.0 for v in out[1:1 + n]], out[1 + n:]
 
     # ------------------------------------------------------------------- generate
     def generate(self, prompts: List[Union[str, List[int]]],

@@ -133,9 +133,14 @@ class ModelRunner:
             self.fused_comm = symm.enable(int(config.extra.get("fused_comm_tokens", 512)), tc.hidden_size,
                                           self.device, max_tokens=big)
         self.sampler = Sampler(config.seed)
+        # under tensor parallelism with the fused communication kernels the LM head keeps its vocabulary shard
+        # and the sampler exchanges one candidate per rank: no gather of logits inside or outside the graphs
+        self.local_logits = self.fused_comm is not None
+        self.head = next((m for m in self.model.modules() if m.__class__.__name__ == "ParallelLMHead"), None)
         self.io = {"h2d_bytes": 0, "d2h_bytes": 0}      # host<->device traffic of the step loop
         self.timer: Optional[DeviceTimer] = None        # set by benchmarks to time device work only
         self.graph_launches: Dict[int, int] = {}
+        self.last_status = 0
         self.allocate_kv_cache()
 
         # ------------------------------------------------------ compression
@@ -339,7 +344,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ forward
     def _forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
-                 seqs: Optional[Seq[Sequence]] = None, image_rows=None) -> torch.Tensor:
+                 seqs: Optional[Seq[Sequence]] = None, image_rows=None, local_logits: bool = False) -> torch.Tensor:
         if self.fused_comm is not None:
             self.fused_comm.begin_forward()
         if self.is_multimodal:
@@ -349,16 +354,27 @@ class ModelRunner:
             hidden = self.model(input_ids, positions, images=pixel)
         else:
             hidden = self.model(input_ids, positions)
-        return self.model.compute_logits(hidden)
+        return self._logits(hidden, local_logits)
+
+    def _logits(self, hidden: torch.Tensor, local: bool) -> torch.Tensor:
+        """Logits over the whole vocabulary, or (local) over this rank's vocabulary shard."""
+        if not local:
+            return self.model.compute_logits(hidden)
+        from ..layers import embed_head
+        prev = embed_head.set_local_logits(True)
+        try:
+            return self.model.compute_logits(hidden)
+        finally:
+            embed_head.set_local_logits(prev)
 
     @torch.inference_mode()
-    def run_prefill(self, seqs: Seq[Sequence]) -> torch.Tensor:
+    def run_prefill(self, seqs: Seq[Sequence], local_logits: bool = False) -> torch.Tensor:
         input_ids, positions, image_rows = self.prepare_prefill(seqs)
         from ..utils.context import get_context
         ctx = get_context()
         if self.timer is not None:
             self.timer.start(self.main_stream)
-        logits = self._forward(input_ids, positions, seqs, image_rows)
+        logits = self._forward(input_ids, positions, seqs, image_rows, local_logits=local_logits)
         if ctx.window_q is not None:
             counts = ctx.window_q["counts"]
             offs = np.concatenate([[0], np.cumsum(counts)])
@@ -373,7 +389,9 @@ class ModelRunner:
         return None
 
     @torch.inference_mode()
-    def run_decode(self, seqs: Seq[Sequence]) -> torch.Tensor:
+    def run_decode(self, seqs: Seq[Sequence], local_logits: bool = False) -> torch.Tensor:
+        """Logits of one decode step.  `local_logits` (tensor parallelism with the fused kernels): this rank's
+        vocabulary shard; the CUDA graphs are captured in that form."""
         ids, pos, slots, lens, bt = self.prepare_decode(seqs)
         n = len(seqs)
         bucket = None if self.enforce_eager else self._graph_bucket(n)
@@ -385,7 +403,7 @@ class ModelRunner:
             ids_d, pos_d = self._to_dev(ids, torch.int64), self._to_dev(pos, torch.int64)
             if self.timer is not None:
                 self.timer.start(self.main_stream)
-            return self._forward(ids_d, pos_d)
+            return self._forward(ids_d, pos_d, local_logits=local_logits)
         gv = self.graph_vars
         h = self._staging
         h["input_ids"][:n] = torch.from_numpy(ids)
@@ -405,7 +423,10 @@ class ModelRunner:
         if self.timer is not None:
             self.timer.start(self.main_stream)
         self._replay(bucket)
-        return gv["logits"][:n]
+        logits = gv["logits"][:n]
+        if self.local_logits and not local_logits:          # the graphs hold shards: gather for a caller who asked
+            logits = tpmod.tp_all_gather(logits, dim=-1)[:, : self.text_config.vocab_size]
+        return logits
 
     def _replay(self, bucket: int) -> None:
         g = self.graphs[bucket]
@@ -421,7 +442,8 @@ class ModelRunner:
         set_context(False, slot_mapping=gv["slot_mapping"][:bucket], context_lens=gv["context_lens"][:bucket],
                     block_tables=gv["block_tables"][:bucket],
                     attn_workspace=getattr(self, "attn_workspace", None))
-        gv["logits"][:bucket] = self._forward(gv["input_ids"][:bucket], gv["positions"][:bucket])
+        gv["logits"][:bucket] = self._forward(gv["input_ids"][:bucket], gv["positions"][:bucket],
+                                              local_logits=self.local_logits)
 
     @torch.inference_mode()
     def capture_cudagraph(self) -> None:
@@ -429,7 +451,7 @@ class ModelRunner:
         max_bs = min(cfg.max_num_seqs, cfg.decode_batch_size or cfg.max_num_seqs, 512)
         max_blocks = -(-cfg.max_model_len // self.block_size) + 1
         dev = self.device
-        vocab = self.text_config.vocab_size
+        vocab = self.head.per_rank if (self.local_logits and self.head is not None) else self.text_config.vocab_size
         self.graph_vars = {
             "input_ids": torch.zeros(max_bs, dtype=torch.int64, device=dev),
             "positions": torch.zeros(max_bs, dtype=torch.int64, device=dev),
@@ -473,14 +495,22 @@ class ModelRunner:
         """One model step for a batch; returns the sampled token per request."""
         cm = torch.cuda.stream(self.main_stream) if self.main_stream is not None else _Null()
         with cm:
-            logits = self.run_prefill(seqs) if is_prefill else self.run_decode(seqs)
+            local = self.local_logits and self.head is not None
+            logits = self.run_prefill(seqs, local) if is_prefill else self.run_decode(seqs, local)
             temps = self._temperatures(seqs)
-            tokens = self.sampler(logits, temps)
+            if local:
+                tokens = self.sampler.forward_sharded(logits, temps, self.fused_comm, self.head.vocab_start,
+                                                      self.head.num_embeddings)
+            else:
+                tokens = self.sampler(logits, temps, with_status=True)
             if self.timer is not None:
                 self.timer.stop(self.main_stream)
             out = tokens.tolist()
             self.io["d2h_bytes"] += 8 * len(out)
         reset_context()
+        # the last entry is the device status word: a kernel wait that ran out, or an index that was out of
+        # range, since the status was last cleared (0 on the CPU and in a clean step)
+        self.last_status = int(out.pop())
         return out
 
     # ------------------------------------------------------------- compression
@@ -553,6 +583,16 @@ class ModelRunner:
             return 0
         from .. import ops
         return int(ops.ext().read_status(dev.index if dev.index is not None else torch.cuda.current_device()))
+
+    def reset_sync_state(self) -> None:
+        """After a device wait ran out: wait for the device, then zero the in-kernel barrier words and split-K
+        counters of this device's streams (a kernel that gave up may have left them mid-count)."""
+        dev = torch.device(self.device)
+        if dev.type != "cuda":
+            return
+        from .. import ops
+        torch.cuda.synchronize(dev)
+        ops.ext().reset_sync_state(dev.index if dev.index is not None else torch.cuda.current_device())
 
     def release(self, seq: Sequence) -> None:
         self._compressed_lens.pop(seq.seq_id, None)

@@ -148,7 +148,14 @@ class DecoderForCausalLM(nn.Module):
         self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size)
         self.tie = bool(getattr(cfg, "tie_word_embeddings", False))
         if self.tie:
-            self.lm_head.weight = self.model.embed_tokens.weight
+            emb = self.model.embed_tokens
+            if emb.replicated:
+                # the table is whole on every rank: the head multiplies with this rank's rows of it (a view of
+                # the same storage, so loading the table loads the head)
+                self.lm_head.weight = nn.Parameter(emb.shard_rows(), requires_grad=False)
+                self.optional_weight_substrings = ("lm_head.",)
+            else:
+                self.lm_head.weight = emb.weight
 
     def get_input_embeddings(self, input_ids: torch.Tensor) -> torch.Tensor:
         return self.model.embed_tokens(input_ids)

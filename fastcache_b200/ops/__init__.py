@@ -150,8 +150,15 @@ def embedding(ids, weight, vocab_start: int = 0):
     return ref.embedding(ids, weight, vocab_start)
 
 
-def sample(logits, temperatures, noise=None, seed: int = 0):
+def sample(logits, temperatures, noise=None, seed: int = 0, with_status: bool = False, vocab_offset: int = 0,
+           v_limit: int = -1):
+    """Tokens [B].  `with_status` (CUDA): [B + 1], the last entry is the device status code (0 = clean), so the
+    host learns about a kernel wait that ran out with the tokens it reads back anyway."""
     if logits.is_cuda and noise is None:
         _n()
-        return ext().sample(logits, temperatures, int(seed) & 0x7FFFFFFF)
-    return ref.sample(logits, temperatures, noise)
+        return ext().sample(logits, temperatures, int(seed) & 0x7FFFFFFF, bool(with_status), int(vocab_offset),
+                            int(v_limit))
+    out = ref.sample(logits, temperatures, noise)
+    if with_status:
+        out = torch.cat([out, out.new_zeros(1)])
+    return out

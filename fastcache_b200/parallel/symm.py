@@ -64,8 +64,12 @@ class FusedComm:
                         [int(p) for p in self.handles[1].buffer_ptrs],
                         [int(p) for p in self.flag_handle.buffer_ptrs], mc[0], mc[1], index)
         self.status = ext().status_tensor(index)
-        self._scratch = ext().gemm_scratch(index)
         self.cur = 0
+        # candidate tables of the sampler over vocabulary shards
+        self.cells = symm_mem.empty((ext().sample_cells_per_rank(),), dtype=torch.int64, device=device)
+        self.cells.zero_()
+        self.cell_handle = symm_mem.rendezvous(self.cells, name)
+        ext().sample_exchange_init([int(p) for p in self.cell_handle.buffer_ptrs])
 
         # ---- GEMM + reduce-scatter + add + norm / all-gather + GEMM (prefill)
         self.max_tokens = 0
@@ -112,16 +116,12 @@ class FusedComm:
         if T <= self.one_shot_max_tokens:
             buf = self.cur
             self.cur ^= 1
-            staging = self.bufs[buf][:T]
             x2 = x if x.stride(-1) == 1 else x.contiguous()
-            ops._n(2)
-            # split-K partial sums of the GEMM are finished into the staging buffer by the reduce kernel itself
-            splits = ext().gemm_partial(x2, weight, staging)
-            if splits == 1 and bias is not None:
-                staging.add_(bias)
-            y = ext().allreduce_add_rmsnorm(buf, residual, norm_weight, float(eps), self.use_multimem, self.status,
-                                            self._scratch if splits > 1 else None, splits,
-                                            bias if splits > 1 else None)
+            ops._n()
+            # one kernel where the shape allows: GEMM, then the GEMM's CTAs finish their token rows into the
+            # staging buffer, exchange flags with the peers, reduce, add the residual and normalise
+            y = ext().linear_allreduce_add_rmsnorm(x2, weight, bias, buf, residual, norm_weight, float(eps),
+                                                   self.use_multimem, self.status)
             return y, residual
         if bias is not None or T > self.max_tokens or weight.shape[0] != self.hidden:
             return self._library(x, weight, bias, residual, norm_weight, eps)
@@ -155,6 +155,13 @@ class FusedComm:
             self._gather = None
             return None
         return ext().gemm_after_gather(x, weight, g[1], g[0], self.status, 0, swiglu)
+
+    def sample(self, local_logits: torch.Tensor, temperatures: torch.Tensor, seed: int, vocab_offset: int,
+               vocab_size: int) -> torch.Tensor:
+        """[B + 1] int64: the tokens (the same on every rank) and this rank's device status code."""
+        ops._n()
+        return ext().sample_exchange(local_logits, temperatures, int(seed) & 0x7FFFFFFF, int(vocab_offset),
+                                     int(vocab_size), self.status)
 
     def _library(self, x, weight, bias, residual, norm_weight, eps):
         y = ops.linear(x, weight, bias)

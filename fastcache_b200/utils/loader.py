@@ -85,7 +85,7 @@ def missing_parameters(model: nn.Module, seen) -> list:
     one (qkv_proj, gate_up_proj) every shard of its group.  Tied parameters (the LM head sharing the embedding
     table) count once.  Modules listed in `model.optional_weight_substrings` may stay at their initial values."""
     packed = getattr(model, "packed_modules_mapping", {})
-    optional = tuple(getattr(model, "optional_weight_substrings", ()))
+    optional = tuple(o for m in model.modules() for o in getattr(m, "optional_weight_substrings", ()))
     groups: Dict[str, set] = {}
     for _key, (packed_name, sid) in packed.items():
         groups.setdefault(packed_name, set()).add(sid)

@@ -29,6 +29,7 @@ STATUS_NAMES = {
     4: "timeout waiting for the epilogue",
     5: "timeout waiting for a flag written by another GPU",
     6: "block-table or slot index out of range (access skipped)",
+    7: "timeout at a grid barrier inside a kernel",
 }
 
 

@@ -255,3 +255,92 @@ def test_dead_rank_is_detected_by_gloo_survivor():
     assert left[2] and surv[2]                          # the collective before the failure was correct
     assert surv[1] == [1]                               # learnt on the host, before any launch
     assert surv[3] is not None and surv[4] < 15.0       # the orphaned collective errored, it did not hang
+
+
+# ------------------------------------------------------- device waits that run out (one GPU, nothing faults)
+def test_step_raises_when_the_runner_reports_a_status_code():
+    """The status word comes back with the sampled tokens; `step()` turns a non-zero code into an exception and
+    `recover()` then serves every request."""
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    llm = _engine(compress=False)
+    seqs = [llm.add_request(p, sp) for p in _prompts(2)]
+    llm.step()
+    r = llm.model_runner
+    real = r.run
+
+    def run_with_timeout(batch, is_prefill, **kw):
+        out = real(batch, is_prefill, **kw)
+        r.last_status = 5
+        return out
+
+    r.run = run_with_timeout
+    with pytest.raises(DeviceWaitTimeout) as e:
+        llm.step()
+    assert e.value.code == 5 and r.last_status == 0
+    r.run = real
+    assert llm.recover() == 2
+    while not llm.is_finished():
+        llm.step()
+    assert all(s.num_completion_tokens == 4 for s in seqs)
+
+
+def test_controller_timings_agree_across_ranks(monkeypatch):
+    """Under tensor parallelism the controller is fed the slowest rank's step time, and a compression only
+    counts as finished when it has finished on every rank."""
+    import torch.distributed as dist
+    from fastcache_b200.parallel import tp as tpmod
+    llm = _engine(compress=False)
+    other = [7.0, -0.0, -1.0, 0.0, 2.5]           # the peer: slower step, first compression still running
+
+    def fake_all_reduce(t, op=None, group=None):
+        assert op == dist.ReduceOp.MAX
+        t.copy_(torch.maximum(t, torch.tensor(other, dtype=t.dtype)))
+
+    monkeypatch.setattr(tpmod, "get_tp_size", lambda: 2)
+    monkeypatch.setattr(dist, "all_reduce", fake_all_reduce)
+    ms, done, c_ms = llm._agree_on_timings(5.0, [True, True], [1.0, 2.0])
+    assert ms == 7.0 and done == [False, True] and c_ms[1] == 2.5
+
+
+@pytest.mark.gpu
+def test_peer_wait_runs_out_on_a_flag_that_nothing_posts():
+    """One GPU plays rank 0 of two: the second rank's flag words are local memory that nobody writes.  With the
+    wait limit set to 5 ms the fused all-reduce returns, the status word reads `timeout waiting for a flag
+    written by another GPU`, and the engine's next step raises `DeviceWaitTimeout`.  Nothing traps or hangs:
+    the wait is bounded and the context stays usable."""
+    from fastcache_b200 import ops
+    e = ops.ext()
+    dev = torch.device("cuda", 0)
+    H, T = 1024, 4
+    bufs = [torch.zeros(2, 64, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]      # [rank][rows][H]
+    flags = torch.zeros(2, 512 * 8, dtype=torch.int32, device=dev)
+    status = e.status_tensor(0)
+    e.read_status(0)
+    try:
+        e.comm_init(0, 2, [bufs[0][0].data_ptr(), bufs[0][1].data_ptr()],
+                    [bufs[1][0].data_ptr(), bufs[1][1].data_ptr()],
+                    [flags[0].data_ptr(), flags[1].data_ptr()], 0, 0, 0)
+        e.set_wait_limit_us(0, 5000)
+        resid = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        w = torch.ones(H, dtype=torch.bfloat16, device=dev)
+        t0 = time.perf_counter()
+        e.allreduce_add_rmsnorm(0, resid, w, 1e-6, False, status)
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 2.0                  # the built-in limit would be 10 s
+        assert int(flags[1].view(512, 8)[:T, 0].min()) == 1    # rank 0 posted its arrival to "rank 1"
+        # the engine learns of it with the next tokens it reads back
+        llm = LLM(tiny_llama_config(head_dim=128, hidden_size=512), device="cuda:0", kvcache_block_size=16,
+                  num_kvcache_blocks=32, max_model_len=256, enforce_eager=True)
+        llm.add_request(_prompts(1, length=20)[0], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+        with pytest.raises(DeviceWaitTimeout) as err:
+            llm.step()
+        assert err.value.code == 5
+        assert e.read_status(0) == 0                           # cleared by the engine
+        assert llm.recover() == 1
+        while not llm.is_finished():
+            llm.step()
+        llm.exit()
+    finally:
+        e.set_wait_limit_us(0, 0)
+        e.read_status(0)
+        e.comm_shutdown()

@@ -69,3 +69,99 @@ def test_linear_rope_qknorm_store_matches_unfused(T, Hq, Hkv, qk):
     torch.cuda.synchronize()
     assert ops.ext().read_status(0) == 0
     assert torch.equal(q, q2) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
+
+
+def _norm_ref(x, w, b, res, nw):
+    y = ref.linear(x.float(), w.float(), None if b is None else b.float()).to(torch.bfloat16)
+    return ref.add_rms_norm(y, res.clone(), nw, 1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 4096, 512), (200, 5120, 3200), (1, 4096, 1536), (33, 8192, 1024)])
+def test_fused_gemm_add_norm_in_a_cuda_graph(M, N, K):
+    """GEMM + grid barrier + split-K sum + residual add + RMSNorm as one kernel: tensor-parallel shard shapes,
+    replayed from a CUDA graph (the barrier words reset themselves) with new inputs every time."""
+    x, w = _rand(M, K, seed=21), _rand(N, K, scale=0.03, seed=22)
+    nw = _rand(N, seed=23)
+    res = _rand(M, N, seed=24)
+    xs, rs = x.clone(), res.clone()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(2):                               # warm-up: workspace of this stream, lazy init
+            ops.linear_add_rms_norm(xs, w, None, rs.clone(), nw, 1e-6)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            y, r = ops.linear_add_rms_norm(xs, w, None, rs, nw, 1e-6)
+        for it in range(3):
+            xi, ri = _rand(M, K, seed=30 + it), _rand(M, N, seed=40 + it)
+            xs.copy_(xi)
+            rs.copy_(ri)
+            g.replay()
+            stream.synchronize()
+            want_y, want_r = _norm_ref(xi, w, None, ri, nw)
+            assert (rs.float() - want_r.float()).abs().max().item() < 0.07
+            assert (y.float() - want_y.float()).abs().max().item() < 0.07
+    assert ops.ext().read_status(0) == 0
+
+
+def test_two_streams_run_decode_size_gemms_at_once():
+    """Every stream has its own split-K scratch and barrier words: the same fused op on two streams at the same
+    time, many times, gives each stream its own right answer."""
+    M, N, K = 128, 4096, 4096
+    w, nw = _rand(N, K, scale=0.03, seed=52), _rand(N, seed=53)
+    xa, xb = _rand(M, K, seed=54), _rand(M, K, seed=55)
+    ra, rb = _rand(M, N, seed=56), _rand(M, N, seed=57)
+    want_a, _ = _norm_ref(xa, w, None, ra, nw)
+    want_b, _ = _norm_ref(xb, w, None, rb, nw)
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    outs_a, outs_b = [], []
+    for _ in range(20):
+        with torch.cuda.stream(sa):
+            outs_a.append(ops.linear_add_rms_norm(xa, w, None, ra.clone(), nw, 1e-6)[0])
+        with torch.cuda.stream(sb):
+            outs_b.append(ops.linear_add_rms_norm(xb, w, None, rb.clone(), nw, 1e-6)[0])
+    torch.cuda.synchronize()
+    assert ops.ext().read_status(0) == 0
+    for ya, yb in zip(outs_a, outs_b):
+        assert (ya.float() - want_a.float()).abs().max().item() < 0.07
+        assert (yb.float() - want_b.float()).abs().max().item() < 0.07
+        assert torch.equal(ya, outs_a[0]) and torch.equal(yb, outs_b[0])
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(128, 4096, 512, False), (40, 1024, 1536, True)])
+def test_fused_gemm_allreduce_add_norm_on_one_gpu(M, N, K, bias):
+    """The tensor-parallel epilogue (GEMM, staging, flag exchange, sum over ranks, add, norm) with this GPU as
+    rank 0 of 2 and the second rank played by local memory: its contribution is written beforehand and its flag
+    words are preset to an epoch far ahead, so nothing waits for anything.  Checks both the one-kernel path and
+    the two-kernel path against fp32."""
+    import os
+    e = ops.ext()
+    dev = torch.device("cuda", 0)
+    bufs = [torch.zeros(2, 256, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]      # [buf][rank][rows][N]
+    flags = torch.zeros(2, 512 * 8, dtype=torch.int32, device=dev)
+    flags[0].view(512, 8)[:, 1] = 1 << 20                                 # "rank 1 has arrived" for a long time
+    status = e.status_tensor(0)
+    e.read_status(0)
+    x, w = _rand(M, K, seed=61), _rand(N, K, scale=0.03, seed=62)
+    b = _rand(N, seed=63) if bias else None
+    nw, res = _rand(N, seed=64), _rand(M, N, seed=65)
+    other = _rand(M, N, scale=0.5, seed=66)                               # what rank 1 would have contributed
+    mine = ref.linear(x.float(), w.float(), None if b is None else b.float()).to(torch.bfloat16)
+    want_y, want_r = ref.add_rms_norm((mine.float() + other.float()).to(torch.bfloat16), res.clone(), nw, 1e-6)
+    try:
+        e.comm_init(0, 2, [bufs[0][0].data_ptr(), bufs[0][1].data_ptr()],
+                    [bufs[1][0].data_ptr(), bufs[1][1].data_ptr()],
+                    [flags[0].data_ptr(), flags[1].data_ptr()], 0, 0, 0)
+        for buf in (0, 1, 0):
+            bufs[buf][1][:M].copy_(other)
+            r = res.clone()
+            y = e.linear_allreduce_add_rmsnorm(x, w, b, buf, r, nw, 1e-6, False, status)
+            torch.cuda.synchronize()
+            assert e.read_status(0) == 0
+            assert (r.float() - want_r.float()).abs().max().item() < 0.07
+            # one bf16 step at the magnitude of the normalised, weighted values
+            assert ((y.float() - want_y.float()).abs() / (want_y.float().abs() + 1.0)).max().item() < 2e-2
+            assert (bufs[buf][0][:M].float() - mine.float()).abs().max().item() < 0.03   # rank 0's staged rows
+    finally:
+        e.comm_shutdown()
