@@ -544,13 +544,19 @@ void register_comm(pybind11::module_& m);
 namespace fc {
 const StreamWorkspace& stream_workspace(int device, cudaStream_t stream) { return workspace(device, stream).raw; }
 int stream_sm_limit(cudaStream_t stream) { return sm_limit_for(stream); }
+static int g_fused_epilogues = -1;     // -1: take the environment variable
 bool fused_epilogues_enabled() {
-  static const bool on = [] {
+  if (g_fused_epilogues < 0) {
+    // off unless asked for: measured on B200, the pair of kernels chained by programmatic dependent launch is
+    // faster (the second kernel of the pair needs no shared memory, so the GEMM after it is already resident and
+    // has its first weight tiles in flight while the reduction runs; the one-kernel form keeps the SM's shared
+    // memory until the reduction is done)
     const char* e = std::getenv("FC_FUSED_EPILOGUE");
-    return e == nullptr || std::string(e) != "0";
-  }();
-  return on;
+    g_fused_epilogues = (e != nullptr && std::string(e) == "1") ? 1 : 0;
+  }
+  return g_fused_epilogues == 1;
 }
+void set_fused_epilogues(bool on) { g_fused_epilogues = on ? 1 : 0; }
 }  // namespace fc
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -578,6 +584,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &read_status);
   m.def("set_wait_limit_us", &set_wait_limit_us);
   m.def("reset_sync_state", &reset_sync_state);
+  m.def("set_fused_epilogues", &fc::set_fused_epilogues, "one-kernel GEMM + (all-reduce +) add + RMSNorm for decode sizes");
+  m.def("fused_epilogues_enabled", &fc::fused_epilogues_enabled);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
   m.def("status_tensor", [](int64_t device) { return device_status(int(device)); });

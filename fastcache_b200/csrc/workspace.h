@@ -28,8 +28,10 @@ constexpr long long ATTN_LSE_FLOATS = 1ll << 18;
 const StreamWorkspace& stream_workspace(int device, cudaStream_t stream);
 // SM count of the green context a stream belongs to (0: the whole device).
 int stream_sm_limit(cudaStream_t stream);
-// false when the environment variable FC_FUSED_EPILOGUE is 0: the decode-size row-parallel GEMMs then run as
-// separate GEMM and (all-reduce +) add + RMSNorm kernels (for A/B measurements).
+// true after set_fused_epilogues(true), or initially when the environment variable FC_FUSED_EPILOGUE is 1: the decode-size row-parallel GEMMs then run their
+// (all-reduce +) add + RMSNorm inside the GEMM kernel instead of as a second kernel (see bindings.cpp for why
+// the default is the pair).
 bool fused_epilogues_enabled();
+void set_fused_epilogues(bool on);
 
 }  // namespace fc

@@ -158,6 +158,11 @@ def sample(logits, temperatures, noise=None, seed: int = 0, with_status: bool = 
         _n()
         return ext().sample(logits, temperatures, int(seed) & 0x7FFFFFFF, bool(with_status), int(vocab_offset),
                             int(v_limit))
+    if noise is None:
+        # drawn from the step's seed, not from the process-wide generator: tensor-parallel ranks on the CPU then
+        # make the same draw from their (identical) gathered logits
+        g = torch.Generator(device=logits.device).manual_seed(int(seed) & 0x7FFFFFFF)
+        noise = torch.empty(logits.shape, dtype=torch.float32, device=logits.device).exponential_(1, generator=g)
     out = ref.sample(logits, temperatures, noise)
     if with_status:
         out = torch.cat([out, out.new_zeros(1)])

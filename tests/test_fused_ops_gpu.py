@@ -8,6 +8,18 @@ from fastcache_b200.ops import reference as ref
 pytestmark = pytest.mark.gpu
 
 
+
+@pytest.fixture(autouse=True)
+def _one_kernel_epilogues():
+    """The one-kernel form of GEMM + (all-reduce +) add + RMSNorm is opt-in (the pair of kernels is the faster
+    default); the tests of this module switch it on so that both forms stay covered."""
+    e = ops.ext()
+    before = e.fused_epilogues_enabled()
+    e.set_fused_epilogues(True)
+    yield
+    e.set_fused_epilogues(before)
+
+
 def _rand(*shape, scale=1.0, seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()

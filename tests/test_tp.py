@@ -38,19 +38,32 @@ def test_tp_cpu_gloo_split_prompts_match_unsplit(tmp_path):
     assert one["tokens"] == two["tokens"]
 
 
+def test_tp_cpu_gloo_sharded_embedding_matches_single_rank(tmp_path):
+    """The vocabulary-parallel table (masked lookup + all-reduce), which large vocabularies fall back to."""
+    one = _run(1, "cpu", str(tmp_path / "a.json"), 29651, ["--kv-heads", "2"])
+    two = _run(2, "cpu", str(tmp_path / "b.json"), 29652, ["--kv-heads", "2", "--shard-embedding"])
+    assert one["tokens"] == two["tokens"] and two["ranks_agree"]
+
+
 @pytest.mark.gpu
-def test_tp2_gpu_fused_comm(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    one = _run(1, "cuda", str(tmp_path / "a.json"), 29631)
-    two = _run(2, "cuda", str(tmp_path / "b.json"), 29632)
-    assert two["status"] == 0
-    assert two["allreduce_max_err"] < 6e-2
-    assert two["fused_prefill_max_err"] < 8e-2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_gpu_fused_comm(tmp_path, world):
+    """NCCL ranks with the fused communication kernels at 2, 4 and 8 GPUs (as many as are visible): the fused
+    decode and prefill paths against a library all-reduce, token agreement with one GPU, and the same tokens on
+    every rank, greedy and sampled."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = 29630 + 10 * world
+    one = _run(1, "cuda", str(tmp_path / "a.json"), port)
+    many = _run(world, "cuda", str(tmp_path / "b.json"), port + 1)
+    assert many["status"] == 0 and many["engine_status"] == 0
+    assert many["allreduce_max_err"] < 6e-2
+    assert many["fused_prefill_max_err"] < 8e-2
+    assert many["ranks_agree"] and many["local_logits"] and many["embedding_replicated"]
     # same engine with the one-shot limit lowered so that prefill takes the GEMM + reduce-scatter path
-    big = _run(2, "cuda", str(tmp_path / "c.json"), 29633, ["--one-shot-tokens", "64"])
-    assert big["status"] == 0
+    big = _run(world, "cuda", str(tmp_path / "c.json"), port + 2, ["--one-shot-tokens", "64"])
+    assert big["status"] == 0 and big["engine_status"] == 0 and big["ranks_agree"]
     assert sum(a[0] == b[0] for a, b in zip(one["tokens"], big["tokens"])) >= len(one["tokens"]) - 1, (one, big)
-    # bf16 summation order differs between 1 and 2 ranks: the first tokens (pure prefill) agree
-    same = sum(a[0] == b[0] for a, b in zip(one["tokens"], two["tokens"]))
-    assert same >= len(one["tokens"]) - 1, (one, two)
+    # bf16 summation order differs between 1 and N ranks: the first tokens (pure prefill) agree
+    same = sum(a[0] == b[0] for a, b in zip(one["tokens"], many["tokens"]))
+    assert same >= len(one["tokens"]) - 1, (one, many)

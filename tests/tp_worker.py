@@ -22,7 +22,11 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--one-shot-tokens", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=0, help="chunked_prefill_tokens (with a 64-token step budget)")
+    ap.add_argument("--shard-embedding", action="store_true", help="vocabulary-parallel embedding table + all-reduce")
     a = ap.parse_args()
+    if a.shard_embedding:
+        from fastcache_b200.layers import embed_head
+        embed_head.REPLICATE_EMBEDDING_BYTES = 0
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -96,6 +100,19 @@ def main():
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (9, 40, 77, 120)]
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     res["tokens"] = [o["token_ids"] for o in out]
+    # sampled (not greedy) tokens: every rank must draw the same ones, from its own vocabulary shard
+    warm = llm.generate(prompts, SamplingParams(temperature=0.8, max_tokens=6, ignore_eos=True))
+    res["sampled"] = [o["token_ids"] for o in warm]
+    if world > 1:
+        mine = {"tokens": res["tokens"], "sampled": res["sampled"]}
+        everyone = [None] * world
+        torch.distributed.all_gather_object(everyone, mine)
+        res["ranks_agree"] = all(e == everyone[0] for e in everyone)
+    if a.device == "cuda":
+        from fastcache_b200 import ops as _ops
+        res["engine_status"] = int(_ops.ext().read_status(local))
+        res["local_logits"] = bool(llm.model_runner.local_logits)
+        res["embedding_replicated"] = bool(llm.model_runner.model.model.embed_tokens.replicated)
     llm.exit()
     if rank == 0:
         with open(a.out, "w") as fh:
