@@ -114,11 +114,11 @@ def main():
 
     def decode_layers(kind):
         res, x = res_d.clone(), attn_d
-        if comm is not None and kind == "fused":
+        if comm is not None and kind.startswith("fused"):
             comm.begin_forward()
         for wo, wgu, wd, wq in layer_w:
             for w_row in (wo, wd):
-                if kind == "fused":
+                if kind.startswith("fused"):
                     normed, res = row_linear_reduce_add_norm(x, w_row, None, res, norm_w, 1e-6)
                 else:
                     y = ops.linear(x, w_row)
@@ -131,6 +131,13 @@ def main():
         return x
 
     def graph_ms(kind):
+        # variants of the fused path: the reduction inside the GEMM kernel instead of a second kernel, and
+        # multimem.ld_reduce through the switch instead of one peer load per rank
+        ops.ext().set_fused_epilogues(kind == "fused_one_kernel")
+        if comm is not None:
+            comm.use_multimem = kind == "fused_multimem" and comm.has_multicast
+            if kind == "fused_multimem" and not comm.has_multicast:
+                raise RuntimeError("no multicast address for the staging buffers on this system")
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
             for _ in range(3):
@@ -162,12 +169,15 @@ def main():
     drow = {"phase": "decode (CUDA graph)", "tokens": Td, "world": world, "layers_in_graph": L,
             "op": "layer total (4 GEMMs, SwiGLU, 2 x reduce + add + norm)", "peaks": src,
             "roofline_ms": round(w_bytes / (hbm * 1e9) * 1e3, 4)}
-    for kind in ("fused", "gemm_only", "nccl"):
+    for kind in ("fused", "fused_one_kernel", "fused_multimem", "gemm_only", "nccl"):
         try:
             drow[kind + "_ms"] = round(graph_ms(kind), 4)
         except Exception as exc:               # e.g. a collective that refuses stream capture
             drow[kind + "_ms"] = None
             drow[kind + "_error"] = f"{type(exc).__name__}: {str(exc)[:120]}"
+    ops.ext().set_fused_epilogues(False)
+    if comm is not None:
+        comm.use_multimem = False
     if drow.get("fused_ms"):
         drow["frac_of_roofline"] = round(drow["roofline_ms"] / drow["fused_ms"], 3)
     rows.append(drow)

@@ -74,8 +74,10 @@ class DecoderMLP(nn.Module):
         self.act_fn = SiluAndMul()
 
     def forward(self, normed: torch.Tensor) -> torch.Tensor:
-        if normed.is_cuda and normed.shape[0] <= 256 and self.gate_up_proj.bias is None:
-            # decode sizes: the SwiGLU kernel also reduces the GEMM's split-K partial sums
+        if (normed.is_cuda and normed.shape[0] <= 256 and self.gate_up_proj.bias is None
+                and getattr(get_fused_comm(), "_gather", None) is None):
+            # decode sizes: the SwiGLU kernel also reduces the GEMM's split-K partial sums.  (Not while `normed`
+            # is the gathered buffer that is still filling over NVLink: `ops.linear` below knows how to wait.)
             return ops.linear_silu_mul(normed, self.gate_up_proj.weight)
         if normed.is_cuda and self.gate_up_proj.bias is None:
             # prefill sizes: SwiGLU runs in the GEMM epilogue (gate and up rows share a tile), also in the

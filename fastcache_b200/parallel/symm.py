@@ -59,7 +59,8 @@ class FusedComm:
         mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.handles]
         if use_multimem is None:
             use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
-        self.use_multimem = bool(use_multimem and all(mc))
+        self.has_multicast = all(mc)
+        self.use_multimem = bool(use_multimem and self.has_multicast)
         ext().comm_init(self.rank, self.world, [int(p) for p in self.handles[0].buffer_ptrs],
                         [int(p) for p in self.handles[1].buffer_ptrs],
                         [int(p) for p in self.flag_handle.buffer_ptrs], mc[0], mc[1], index)
