@@ -99,16 +99,29 @@ def _transformers_4x_config_view():
     transformers.AutoConfig.from_pretrained = staticmethod(from_pretrained)
 
 
-def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
+def run(args, workload, model_label, ClockSampler, prompts_for, percentile, rank=0, local_rank=0, world=1):
+    """One rank of the reference arm.  world == 1: the copy installed under baseline/_ref.  world > 1: the
+    reference's newer "kv-cache pipeline" copy (baseline/_ref_p, an unmodified copy of that directory), whose
+    linear layers shard full checkpoint tensors, driven the way the reference's own tp_inference.py:34-123 drives
+    it: every torchrun rank calls `init_tensor_parallel` and then builds and steps an identical `LlavaLLM`.
+    Only the Llama family reads the tensor-parallel degree there (nanovllm/models/llama.py:39-44)."""
     import torch
     from bench import COMPRESSION_LABEL, SAMPLING_TEMPERATURE, job_config
-    hf, n_req, p_len, o_len = workload
+    hf, n_req, p_len, o_len = workload[:4]
     n_req = args.requests or n_req
     sys.path.insert(0, os.path.join(HERE, "shims"))
-    sys.path.insert(0, os.path.join(HERE, "_ref"))
-    torch.cuda.set_device(0)
+    sys.path.insert(0, os.path.join(HERE, "_ref_p" if world > 1 else "_ref"))
+    torch.cuda.set_device(local_rank)
     ckpt = os.path.join(os.environ.get("FC_REF_CKPT_DIR", "/tmp"), f"fc_ref_{args.config}")
-    _write_checkpoint(ckpt, dict(hf))
+    if world > 1:
+        from nanovllm.utils.tp import init_tensor_parallel, tp_barrier
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        init_tensor_parallel(tp_size=world, rank=local_rank)
+        if rank == 0:
+            _write_checkpoint(ckpt, dict(hf))
+        tp_barrier()
+    else:
+        _write_checkpoint(ckpt, dict(hf))
     _transformers_4x_config_view()
 
     from nanovllm.engine.llava_engine import LlavaLLM          # the reference's engine
@@ -128,8 +141,10 @@ def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
         while not llm.is_finished():
             llm.step(apply_compression=compress)
 
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(local_rank)
     torch.cuda.synchronize()
+    if world > 1:
+        tp_barrier()
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -152,16 +167,24 @@ def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
                 out_tokens += -n
     ev1.record()
     torch.cuda.synchronize()
+    if world > 1:
+        tp_barrier()
+        torch.cuda.synchronize()
     t1 = time.perf_counter()
     clocks = sampler.stop()
     ms = max(ev0.elapsed_time(ev1), (t1 - t0) * 1e3)
+    if world > 1:                                   # the slowest rank's time
+        import torch.distributed as dist
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     value = out_tokens / (ms / 1e3)
     return {
-        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1,
+        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights",
-        "config": job_config(model_label, n_req, p_len, o_len, 1,
+        "config": job_config(model_label, n_req, p_len, o_len, world,
                              COMPRESSION_LABEL["knorm_ref"] if (compress and method == "knorm") else
                              (f"{method} keep 50%" if compress else "none"), engine_steps),
         "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
@@ -171,4 +194,5 @@ def run(args, workload, model_label, ClockSampler, prompts_for, percentile):
                 "note": "the reference exposes no device-only timer; its single number is end to end"},
         "clocks": clocks, "impl": "reference",
         "shims": ["xxhash", "kvpress", "transformers 4.x view of the config's rope fields"],
+        "reference_copy": "kv-cache pipeline/nanovllm" if world > 1 else "nanovllm",
     }

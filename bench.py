@@ -505,21 +505,31 @@ def run_reference(args):
                         "HuggingFace harness needs real checkpoints: no reference run of the image configs")
         sys.exit(0)
     if world > 1:
-        if rank == 0:
-            unavailable("the reference's LlavaLLM engine runs one process on one GPU (its Qwen3 attention "
-                        "hard-codes tp_size = 1, nanovllm/models/qwen3.py:36): no tensor-parallel run of this job")
-        sys.exit(0)
+        family = WORKLOADS[args.config][0].get("model_type")
+        if family != "llama":
+            if rank == 0:
+                unavailable("the reference cannot run this model tensor-parallel: its Qwen3 attention hard-codes "
+                            "tp_size = 1 (nanovllm/models/qwen3.py:36); only its Llama family reads the degree "
+                            "(--config llama2-7b has a reference arm at every N)")
+            sys.exit(0)
+        if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref_p", "nanovllm", "engine")):
+            if rank == 0:
+                unavailable("the reference's tensor-parallel copy is not present under baseline/_ref_p")
+            sys.exit(0)
     from baseline.reference_arm import run as ref_run
     try:
         line = ref_run(args, WORKLOADS[args.config], MODEL_LABEL[args.config], ClockSampler, prompts_for,
-                       percentile)
+                       percentile, rank, local_rank, world)
     except SystemExit:
         raise
     except Exception as exc:                       # import/runtime failure of the reference itself
         import traceback
         traceback.print_exc()
-        unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
-    emit(line)
+        if rank == 0:
+            unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
+        sys.exit(0)
+    if rank == 0:
+        emit(line)
 
 
 def main():

@@ -54,11 +54,14 @@ def _ccm_segment(x: torch.Tensor, w: PackedCCMWeights, layer: int, bank: int) ->
 
 def ccm_compress_reference(kv_pool: torch.Tensor, block_table: Sequence[int], kv_len: int, image_len: int,
                            w: PackedCCMWeights, layer_start: int = 0, layer_end: Optional[int] = None,
-                           weight_layer_offset: int = 0) -> int:
-    """PyTorch statement of the fused kernel for one request.  Returns the new row count."""
+                           weight_layer_offset: int = 0, dst_block_table: Optional[Sequence[int]] = None) -> int:
+    """PyTorch statement of the fused kernel for one request.  Returns the new row count.  With
+    `dst_block_table` the result goes to those blocks and the request's own rows stay as they are."""
     L = kv_pool.shape[0]
     layer_end = L if layer_end is None else layer_end
     blocks = torch.as_tensor(block_table, dtype=torch.long, device=kv_pool.device)
+    out_blocks = blocks if dst_block_table is None else \
+        torch.as_tensor(dst_block_table, dtype=torch.long, device=kv_pool.device)
     if w.single_segment:
         image_len = 0
     image_len = max(0, min(image_len, kv_len))
@@ -71,14 +74,16 @@ def ccm_compress_reference(kv_pool: torch.Tensor, block_table: Sequence[int], kv
             txt = _ccm_segment(rows[image_len:], w, wl, kv)
             out = torch.cat([img, txt], dim=0)
             new_len = out.shape[0]
-            _write_rows(kv_pool[layer, kv], blocks, out)
+            _write_rows(kv_pool[layer, kv], out_blocks, out)
     return new_len
 
 
 def ccm_compress_in_pool(kv_pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: Sequence[int],
                          image_lens: Sequence[int], w: PackedCCMWeights, layer_start: int = 0,
-                         layer_end: Optional[int] = None) -> List[int]:
-    """Compress a batch of requests in place.  Returns the new row count per request."""
+                         layer_end: Optional[int] = None,
+                         dst_block_tables: Optional[List[Sequence[int]]] = None) -> List[int]:
+    """Compress a batch of requests in place (or, with `dst_block_tables`, into a second set of blocks per
+    request, leaving the source rows untouched).  Returns the new row count per request."""
     if w.single_segment:
         image_lens = [0] * len(kv_lens)
     new_lens = [ccm_segment_len(min(i, n), w.factor, w.min_seq_len) +
@@ -86,10 +91,11 @@ def ccm_compress_in_pool(kv_pool: torch.Tensor, block_tables: List[Sequence[int]
                 for n, i in zip(kv_lens, image_lens)]
     if kv_pool.is_cuda:
         from ..ops.compress_cuda import ccm_compress_cuda
-        ccm_compress_cuda(kv_pool, block_tables, kv_lens, image_lens, w, layer_start, layer_end)
+        ccm_compress_cuda(kv_pool, block_tables, kv_lens, image_lens, w, layer_start, layer_end, dst_block_tables)
         return new_lens
-    for bt, n, i in zip(block_tables, kv_lens, image_lens):
-        ccm_compress_reference(kv_pool, bt, n, i, w, layer_start, layer_end)
+    for k, (bt, n, i) in enumerate(zip(block_tables, kv_lens, image_lens)):
+        ccm_compress_reference(kv_pool, bt, n, i, w, layer_start, layer_end,
+                               dst_block_table=None if dst_block_tables is None else dst_block_tables[k])
     return new_lens
 
 

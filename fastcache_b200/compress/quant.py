@@ -3,6 +3,9 @@ byte), FP8 casts and NF4 (nearest entry of the 16-value NormalFloat table).
 
 Parity: nanovllm/autocompress/methods.py:636-757, nanovllm/autocompress/kernels.py:388-422,
 utils_ccm/utils_compress.py:51-70, :144-154 (SimpleKVQuantizer / ImprovedKVQuantizer fake-quant).
+
+bf16 tensors on a CUDA device go through the kernels of csrc/quant.cu (one warp per group, one pass, codes and
+scales bit-identical to the statements below); everything else runs the PyTorch statements.
 """
 from __future__ import annotations
 
@@ -21,7 +24,36 @@ def _groups(x: torch.Tensor, g: int):
     return x.reshape(*x.shape[:-1], n // g, g), g
 
 
+_CUDA_MODES = {"int8": 0, "int8_asym": 1, "int4": 2, "nf4": 3, "fp8_e4m3": 4, "fp8_e5m2": 5}
+
+
+def _cuda_group(x: torch.Tensor, mode: str, group_size: int) -> int:
+    """Group size for the CUDA kernels (csrc/quant.cu), or 0 when `x` is not theirs to take: they work on
+    contiguous bf16 rows whose groups are multiples of 8 values and at most 1024 long."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() >= 1 and x.numel() > 0):
+        return 0
+    n = x.shape[-1]
+    g = n
+    if mode in ("int4", "nf4"):
+        g = group_size if n % group_size == 0 else n
+    return g if (g % 8 == 0 and g <= 1024 and n % 2 == 0) else 0
+
+
 def quantize(x: torch.Tensor, mode: str = "int8", group_size: int = 128) -> Dict[str, Any]:
+    g = _cuda_group(x, mode, group_size) if mode in _CUDA_MODES else 0
+    if g:
+        from ..ops.loader import ext
+        q, scale, zero = ext().quantize_rows(x.contiguous(), _CUDA_MODES[mode], g)
+        meta = {"mode": mode, "shape": tuple(x.shape), "dtype": x.dtype, "scale": scale}
+        if mode in ("int4", "nf4"):
+            meta.update(q=q, group=g)
+        else:
+            meta["scale"] = scale.reshape(*x.shape[:-1], 1)
+            meta["q"] = q.view({"int8": torch.int8, "int8_asym": torch.uint8, "fp8_e4m3": torch.float8_e4m3fn,
+                                "fp8_e5m2": torch.float8_e5m2}[mode])
+            if mode == "int8_asym":
+                meta["zero"] = zero.reshape(*x.shape[:-1], 1)
+        return meta
     xf = x.float()
     meta: Dict[str, Any] = {"mode": mode, "shape": tuple(x.shape), "dtype": x.dtype}
     if mode == "int8":
@@ -55,6 +87,16 @@ def quantize(x: torch.Tensor, mode: str = "int8", group_size: int = 128) -> Dict
 
 def dequantize(p: Dict[str, Any]) -> torch.Tensor:
     mode = p["mode"]
+    q = p["q"]
+    if q.is_cuda and p["dtype"] == torch.bfloat16 and mode in _CUDA_MODES and q.is_contiguous():
+        n = p["shape"][-1]
+        g = p.get("group", n)
+        if g % 8 == 0 and n % 2 == 0 and p["scale"].dtype == torch.float32:
+            from ..ops.loader import ext
+            y = ext().dequantize_rows(q.view(torch.uint8), p["scale"].contiguous(),
+                                      p["zero"].contiguous() if mode == "int8_asym" else None,
+                                      _CUDA_MODES[mode], g)
+            return y.reshape(p["shape"])
     if mode == "int8":
         y = p["q"].float() * p["scale"]
     elif mode == "int8_asym":
@@ -84,6 +126,10 @@ def fake_quantize(x: torch.Tensor, nbits: int = 4, group_size: int = 128) -> tor
     mode = {8: "int8", 4: "int4"}.get(nbits)
     if mode is None:
         raise ValueError("nbits must be 4 or 8")
+    g = _cuda_group(x, mode, group_size)
+    if g:                                # one pass on the device: no codes are written
+        from ..ops.loader import ext
+        return ext().fake_quantize_rows(x.contiguous(), _CUDA_MODES[mode], g)
     return dequantize(quantize(x, mode, group_size))
 
 

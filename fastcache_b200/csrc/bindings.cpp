@@ -222,6 +222,18 @@ Tensor linear_silu_mul(const Tensor& x, const Tensor& w) {
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   Tensor out = torch::empty({M, I}, x.options());
   if (M == 0) return out;
+  if (M <= 256 && N % 256 == 0 && fc::cluster_splitk_enabled()) {
+    // one kernel: gate and up rows share a tile, the K splits reduce inside a cluster, SwiGLU in the epilogue
+    fc::GemmWorkspace gw;
+    gw.scratch = ws.raw.gemm_scratch;
+    gw.counters = ws.raw.gemm_counters;
+    gw.status = ws.raw.status;
+    gw.grid_sync = ws.raw.grid_sync;
+    if (fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, int(M), int(N), int(x.size(1)),
+                             x.stride(0), w.stride(0), I, 0, gw, sm_limit_for(stream), 0, false, stream, nullptr,
+                             fc::SK_SWIGLU) > 0)
+      return out;
+  }
   Tensor tmp = torch::empty({M, N}, x.options());
   const int splits = gemm_maybe_partial(x, w, tmp, ws, stream);
   if (splits > 1)
@@ -586,6 +598,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reset_sync_state", &reset_sync_state);
   m.def("set_fused_epilogues", &fc::set_fused_epilogues, "one-kernel GEMM + (all-reduce +) add + RMSNorm for decode sizes");
   m.def("fused_epilogues_enabled", &fc::fused_epilogues_enabled);
+  m.def("set_cluster_splitk", &fc::set_cluster_splitk, "split-K of decode-size GEMMs inside thread-block clusters");
+  m.def("cluster_splitk_enabled", &fc::cluster_splitk_enabled);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
   m.def("status_tensor", [](int64_t device) { return device_status(int(device)); });

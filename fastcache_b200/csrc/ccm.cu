@@ -49,6 +49,7 @@ constexpr int CCM_KB_BYTES = CCM_TILE * 64 * 2;   // one [128 x 64] bf16 sub-til
 struct CcmParams {
   bf16* pool;                 // [L, 2, num_blocks, Hkv, block_size, D]
   const int* block_tables;    // [n_seq, max_blocks]
+  const int* dst_tables;      // [n_seq, max_blocks] blocks the result is written to, or nullptr: in place
   const int* kv_lens;         // [n_seq]
   const int* image_lens;      // [n_seq]
   const bf16 *b1, *b2, *b3;   // [Lw, 4, D]
@@ -134,6 +135,18 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
   const long long plane = (((long long)layer * 2 + kv) * p.num_blocks);
   auto row_ptr = [&](int hh, int tok) -> bf16* {
     int blk = bt[tok / p.block_size];
+    if (blk < 0 || blk >= p.num_blocks) {
+      report(p.status, ST_BAD_INDEX);
+      return nullptr;
+    }
+    return p.pool + (((plane + blk) * p.Hkv + hh) * p.block_size + tok % p.block_size) * CCM_D;
+  };
+  // destination rows: the request's own blocks (in place), or a second set of blocks, in which case the
+  // source rows stay intact and the request can keep decoding over them while its layers are compressed
+  const bool out_of_place = p.dst_tables != nullptr;
+  const int* dbt = out_of_place ? p.dst_tables + (long long)seq * p.max_blocks : bt;
+  auto dst_ptr = [&](int hh, int tok) -> bf16* {
+    int blk = dbt[tok / p.block_size];
     if (blk < 0 || blk >= p.num_blocks) {
       report(p.status, ST_BAD_INDEX);
       return nullptr;
@@ -231,7 +244,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
       const int in0 = seg_in[seg], out0 = seg_out[seg];
       if (seg_tiles[seg] == 0) {
         // too short to compress: move the rows unchanged (at most a few rows; out0 <= in0)
-        if (out0 != in0) {
+        if (out0 != in0 || out_of_place) {
           for (int hl = 0; hl < G; ++hl) {
             for (int base = 0; base < n; base += 8) {
               const int r = base + wt / 16, piece = wt % 16;
@@ -243,7 +256,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
               }
               asm volatile("bar.sync 1, 128;" ::: "memory");
               if (live) {
-                bf16* dst = row_ptr(h0 + hl, out0 + r);
+                bf16* dst = dst_ptr(h0 + hl, out0 + r);
                 if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
               }
               asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -347,7 +360,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
         tc_fence_after();
         {
           const int j = j0 + (row & (RJ - 1));
-          bf16* dst = (j < sp) ? row_ptr(h0 + (row >> rj_shift), out0 + j) : nullptr;
+          bf16* dst = (j < sp) ? dst_ptr(h0 + (row >> rj_shift), out0 + j) : nullptr;
           const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16);
 #pragma unroll 1
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -388,7 +401,7 @@ ccm_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constan
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (live) {
-            bf16* dst = row_ptr(h0 + hl, out0 + sp + r);
+            bf16* dst = dst_ptr(h0 + hl, out0 + sp + r);
             if (dst != nullptr) reinterpret_cast<uint4*>(dst)[piece] = v;
           }
         }
@@ -412,7 +425,7 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
                       const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
                       int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
                       int factor, int min_seq_len, int single_segment, int heads_per_cta, uint32_t* status,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const int* dst_block_tables) {
   if (n_seq == 0 || layer_end <= layer_start) return;
   int G = heads_per_cta <= 0 ? 1 : heads_per_cta;
   if ((G != 1 && G != 2 && G != 4 && G != 8) || Hkv % G != 0)
@@ -425,6 +438,7 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
   CcmParams p{};
   p.pool = (bf16*)pool;
   p.block_tables = block_tables;
+  p.dst_tables = dst_block_tables;
   p.kv_lens = kv_lens;
   p.image_lens = image_lens;
   p.b1 = (const bf16*)b1;

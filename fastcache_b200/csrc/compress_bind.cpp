@@ -3,6 +3,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <vector>
+
 #include "kernels.h"
 
 namespace {
@@ -116,7 +118,8 @@ void select_compact(Tensor pool, const Tensor& scores, const Tensor& block_table
 void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens, const Tensor& image_lens,
                   const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, const Tensor& w3,
                   const Tensor& b3, int64_t layer_start, int64_t layer_end, int64_t weight_layer_start,
-                  int64_t factor, int64_t min_seq_len, bool single_segment, Tensor status, int64_t heads_per_cta) {
+                  int64_t factor, int64_t min_seq_len, bool single_segment, Tensor status, int64_t heads_per_cta,
+                  const c10::optional<Tensor>& dst_block_tables) {
   check_pool(pool);
   check_i32(block_tables, "block_tables");
   check_i32(kv_lens, "kv_lens");
@@ -130,6 +133,12 @@ void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens
   TORCH_CHECK(w2.sizes() == w3.sizes() && w2.size(2) == D && w2.size(3) == D, "w2 / w3 must be [L, 4, D, D]");
   TORCH_CHECK(layer_start >= 0 && layer_end <= pool.size(0) && weight_layer_start >= 0 &&
                   weight_layer_start + (layer_end - layer_start) <= w1.size(0), "layer range out of bounds");
+  const int* dst = nullptr;
+  if (dst_block_tables.has_value() && dst_block_tables->defined()) {
+    check_i32(*dst_block_tables, "dst_block_tables");
+    TORCH_CHECK(dst_block_tables->sizes() == block_tables.sizes(), "dst_block_tables must have the shape of block_tables");
+    dst = dst_block_tables->data_ptr<int>();
+  }
   c10::cuda::CUDAGuard guard(pool.device());
   fc::launch_ccm_fused(pool.data_ptr(), block_tables.data_ptr<int>(), kv_lens.data_ptr<int>(),
                        image_lens.data_ptr<int>(), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), b1.data_ptr(),
@@ -137,11 +146,74 @@ void ccm_compress(Tensor pool, const Tensor& block_tables, const Tensor& kv_lens
                        int(layer_end), int(weight_layer_start), int(pool.size(2)), int(pool.size(3)),
                        int(pool.size(4)), int(D), int(block_tables.size(1)), int(factor), int(min_seq_len),
                        single_segment ? 1 : 0, int(heads_per_cta), reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
-                       at::cuda::getCurrentCUDAStream());
+                       at::cuda::getCurrentCUDAStream(), dst);
+}
+// ---------------------------------------------------------------------------------------- quantisers
+// x: contiguous bf16 [..., D]; group size g divides D.  Returns (codes uint8, scale fp32 [..., D / g, 1], zero or
+// an empty tensor).  Codes: [..., D] bytes (INT8 two's complement, FP8 bit patterns) or [..., D / 2] for the 4-bit modes.
+std::vector<Tensor> quantize_rows(const Tensor& x, int64_t mode, int64_t g) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() >= 1,
+              "x must be a contiguous bf16 CUDA tensor");
+  const int64_t D = x.size(-1);
+  TORCH_CHECK(g > 0 && D % g == 0 && g % 8 == 0 && g <= 1024, "group size must divide the last dim, be a multiple of 8 and <= 1024");
+  const int64_t groups = x.numel() / g;
+  const bool four = mode == fc::QUANT_INT4 || mode == fc::QUANT_NF4;
+  c10::cuda::CUDAGuard guard(x.device());
+  auto qshape = x.sizes().vec();
+  if (four) qshape.back() = D / 2;
+  auto sshape = x.sizes().vec();
+  sshape.back() = D / g;
+  sshape.push_back(1);
+  Tensor q = torch::empty(qshape, x.options().dtype(torch::kUInt8));
+  Tensor scale = torch::empty(sshape, x.options().dtype(torch::kFloat32));
+  Tensor zero = mode == fc::QUANT_INT8_ASYM ? torch::empty(sshape, x.options().dtype(torch::kFloat32))
+                                            : torch::empty({0}, x.options().dtype(torch::kFloat32));
+  fc::launch_quantize(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(),
+                      zero.numel() ? zero.data_ptr<float>() : nullptr, nullptr, groups, int(g), int(mode),
+                      at::cuda::getCurrentCUDAStream());
+  return {q, scale, zero};
+}
+
+Tensor dequantize_rows(const Tensor& q, const Tensor& scale, const c10::optional<Tensor>& zero, int64_t mode, int64_t g) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == torch::kUInt8 && q.is_contiguous(), "codes must be contiguous uint8");
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == torch::kFloat32 && scale.is_contiguous(), "scale must be fp32");
+  const bool four = mode == fc::QUANT_INT4 || mode == fc::QUANT_NF4;
+  auto shape = q.sizes().vec();
+  if (four) shape.back() *= 2;
+  const int64_t D = shape.back();
+  TORCH_CHECK(g > 0 && D % g == 0 && g % 8 == 0, "bad group size");
+  const int64_t groups = q.numel() * (four ? 2 : 1) / g;
+  TORCH_CHECK(scale.numel() == groups, "one scale per group");
+  const float* zp = nullptr;
+  if (mode == fc::QUANT_INT8_ASYM) {
+    TORCH_CHECK(zero.has_value() && zero->numel() == groups && zero->scalar_type() == torch::kFloat32, "zero points missing");
+    zp = zero->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor y = torch::empty(shape, q.options().dtype(torch::kBFloat16));
+  fc::launch_dequantize(q.data_ptr(), scale.data_ptr<float>(), zp, y.data_ptr(), groups, int(g), int(mode),
+                        at::cuda::getCurrentCUDAStream());
+  return y;
+}
+
+// decode(encode(x)) in one pass, no codes written
+Tensor fake_quantize_rows(const Tensor& x, int64_t mode, int64_t g) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "x must be a contiguous bf16 CUDA tensor");
+  const int64_t D = x.size(-1);
+  TORCH_CHECK(g > 0 && D % g == 0 && g % 8 == 0 && g <= 1024, "group size must divide the last dim, be a multiple of 8 and <= 1024");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  fc::launch_quantize(x.data_ptr(), nullptr, nullptr, nullptr, y.data_ptr(), x.numel() / g, int(g), int(mode),
+                      at::cuda::getCurrentCUDAStream());
+  return y;
 }
 }  // namespace
 
 void register_compress(pybind11::module_& m) {
+  m.def("quantize_rows", &quantize_rows);
+  m.def("dequantize_rows", &dequantize_rows, pybind11::arg("q"), pybind11::arg("scale"), pybind11::arg("zero") = pybind11::none(),
+        pybind11::arg("mode") = 0, pybind11::arg("g") = 128);
+  m.def("fake_quantize_rows", &fake_quantize_rows);
   m.def("knorm_scores", &knorm_scores);
   m.def("select_compact", &select_compact);
   m.def("snapkv_scores", &snapkv_scores);
@@ -152,5 +224,5 @@ void register_compress(pybind11::module_& m) {
         py::arg("image_lens"), py::arg("w1"), py::arg("b1"), py::arg("w2"), py::arg("b2"), py::arg("w3"),
         py::arg("b3"), py::arg("layer_start"), py::arg("layer_end"), py::arg("weight_layer_start"),
         py::arg("factor"), py::arg("min_seq_len"), py::arg("single_segment"), py::arg("status"),
-        py::arg("heads_per_cta") = 1);
+        py::arg("heads_per_cta") = 1, py::arg("dst_block_tables") = py::none());
 }

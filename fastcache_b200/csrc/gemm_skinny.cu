@@ -18,6 +18,15 @@
 // partials.cu, rope + KV store in elementwise.cu, the one-shot all-reduce in comm.cu)
 // or by the small finalize kernel below.  No inter-CTA synchronisation is needed.
 //
+// Split-K inside a thread-block cluster (`cluster` > 0, the default where the shape allows): the K splits of one row
+// tile are the CTAs of one cluster (cluster dims (1, splits, 1)).  When the mainloops are done the CTAs exchange
+// their fp32 accumulators through distributed shared memory, reduce-scatter fashion: the token columns are dealt
+// out in chunks of 32, every CTA sends each chunk to the CTA that owns it (st.shared::cluster into the owner's idle
+// operand stages) and sums the chunks it owns, then applies bias / activation and writes bf16.  No partial sums go
+// to global memory and no second kernel reads them back.  With `swiglu` the two 128-row halves of a tile are the
+// gate rows and the matching up rows of a [gate; up] weight, and the epilogue writes silu(gate) * up.
+// Every CTA loads its own operand tiles (no multicast); the cluster is only used for the exchange.
+//
 // Fused epilogues (row-parallel projections o_proj / down_proj of a decode step): with `epi` set the kernel
 // goes on after its partial sums are written.  All CTAs meet at a grid barrier (the grid never exceeds the SM
 // count, one CTA per SM, so all of them are resident), then every CTA takes token rows c, c + grid, ...:
@@ -32,6 +41,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -59,6 +69,8 @@ struct SkinnyParams {
   int splits;
   int kb_per_split;
   uint32_t* status;
+  int cluster;            // > 0: the splits are the CTAs of a cluster and reduce through shared memory
+  int swiglu;             // cluster mode only: tile = 128 gate rows + the matching 128 up rows, out [Mtok, Nw / 2]
   // fused epilogue (see the header comment); epi == EPI_NONE: everything below is unused
   int epi;
   uint32_t* grid_sync;            // [0] arrivals, [1] generation
@@ -275,6 +287,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   constexpr uint32_t TMEM_COLS = (MT * BN <= 32) ? 32 : (MT * BN <= 64) ? 64 : (MT * BN <= 128) ? 128
                                  : (MT * BN <= 256) ? 256 : 512;
   const int tile = blockIdx.x, split = blockIdx.y;
+  // first W row of the two 128-row halves of this CTA's tile
+  const int w_row0 = p.swiglu ? tile * 128 : tile * ROWS;
+  const int w_row1 = p.swiglu ? p.Nw / 2 + tile * 128 : tile * ROWS + 128;
   const int num_kb = (p.K + SK_BK - 1) / SK_BK;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(num_kb, kb0 + p.kb_per_split);
@@ -315,9 +330,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       for (int s = 0; s < npre; ++s) {
         uint8_t* sa = smem + s * L::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-        tma_load_2d(sa, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * ROWS);
+        tma_load_2d(sa, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, w_row0);
         if constexpr (MT == 2)
-          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, tile * ROWS + 128);
+          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[s], (kb0 + s) * SK_BK, w_row1);
       }
       pdl_wait();
       asm volatile("fence.proxy.async.global;" ::: "memory");   // x: ordinary stores before, TMA reads now
@@ -335,9 +350,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         uint8_t* sa = smem + stage * L::STAGE_BYTES;
         uint8_t* sb = sa + L::A_BYTES;
         mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-        tma_load_2d(sa, &tma_w, &full_bar[stage], kb * SK_BK, tile * ROWS);
+        tma_load_2d(sa, &tma_w, &full_bar[stage], kb * SK_BK, w_row0);
         if constexpr (MT == 2)
-          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[stage], kb * SK_BK, tile * ROWS + 128);
+          tma_load_2d(sa + L::A_BYTES / 2, &tma_w, &full_bar[stage], kb * SK_BK, w_row1);
         tma_load_2d(sb, &tma_x, &full_bar[stage], kb * SK_BK, 0);
         ++issued;
         if (++stage == STAGES) {
@@ -393,7 +408,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const int lane_group = warp & 3;
     const int row = lane_group * 32 + lane;
     const bool direct = p.splits == 1 && p.epi == EPI_NONE;     // bf16 result straight from the accumulator
-    if (!*s_abort && mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) {
+    if (p.cluster > 0) {
+      // the accumulators are exchanged and reduced after the role branches, by all CTAs of the cluster together
+      if (*s_abort || !mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) *s_abort = 1;
+      tc_fence_after();
+    } else if (!*s_abort && mbar_wait(acc_full, 0, p.status, ST_TIMEOUT_ACC_FULL)) {
       tc_fence_after();
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
@@ -433,6 +452,102 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       const int etid = (warp - 2) * 32 + lane;
       if (skinny_grid_barrier(p, etid, nctas, s_flag))
         skinny_row_phase(p, cta, nctas, etid, s_red, s_flag, s_epoch);
+    }
+  }
+  if (p.cluster > 0) {
+    // ------------------------------------------------- split-K reduction through distributed shared memory
+    // Every thread of every CTA of the cluster comes through here, whatever happened in its role branch (the two
+    // cluster barriers below count all of them).  Chunk c (tokens 32 c ... 32 c + 31) belongs to CTA c % S.
+    const int S = int(cluster_nctarank()), me = int(cluster_ctarank());
+    constexpr int CHUNKS = BN / 32;
+    const int cl_max = (CHUNKS + S - 1) / S;                 // chunks a CTA can own
+    constexpr uint32_t SLOT_BYTES = 8 * 128 * 16;            // one chunk of one 128-row half: [8 x float4][128 rows]
+    const uint32_t recv0 = smem_u32(smem);                   // the operand stages are idle once the MMAs are done
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;
+    const uint32_t t_row = tmem_base + (uint32_t(lane_group * 32) << 16);
+    __syncwarp();
+    if (S > 1) cluster_sync();                               // 1: every CTA's mainloop is over, its stages are free
+    if (warp >= 2 && S > 1 && !*s_abort) {
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int owner = c % S;
+        if (owner == me) continue;
+        const int src = me < owner ? me : me - 1;            // my index among the owner's S - 1 senders
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + uint32_t(mt * BN + c * 32), r);
+          tmem_ld_wait();
+          const uint32_t slot = uint32_t((src * MT + mt) * cl_max + c / S);
+          const uint32_t dst = cluster_map_shared(recv0 + slot * SLOT_BYTES, uint32_t(owner)) + uint32_t(row) * 16u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_cluster_f32x4(dst + uint32_t(j) * 128u * 16u, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+      }
+    }
+    __syncwarp();
+    if (S > 1) cluster_sync();                               // 2: all chunks have landed at their owners
+    if (warp >= 2 && !*s_abort) {
+      const int width = p.swiglu ? p.Nw / 2 : p.Nw;          // output columns
+#pragma unroll 1
+      for (int c = me; c < CHUNKS; c += S) {
+        if (c * 32 >= p.Mtok) break;
+        float acc[MT][32];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + uint32_t(mt * BN + c * 32), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 32; ++t) acc[mt][t] = __uint_as_float(r[t]);
+#pragma unroll 1
+          for (int src = 0; src < S - 1; ++src) {
+            const uint8_t* slot = smem + size_t((src * MT + mt) * cl_max + c / S) * SLOT_BYTES + size_t(row) * 16;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(slot + size_t(j) * 128 * 16);
+              acc[mt][4 * j] += v.x;
+              acc[mt][4 * j + 1] += v.y;
+              acc[mt][4 * j + 2] += v.z;
+              acc[mt][4 * j + 3] += v.w;
+            }
+          }
+        }
+        if (p.swiglu) {
+          if constexpr (MT == 2) {
+            const int n = tile * 128 + row;
+            if (n < width) {
+#pragma unroll
+              for (int t = 0; t < 32; ++t) {
+                const int tok = c * 32 + t;
+                if (tok < p.Mtok) {
+                  // gate and up rounded to bf16 first: the values a separate SwiGLU kernel would read
+                  const float g = __bfloat162float(__float2bfloat16(acc[0][t]));
+                  const float u = __bfloat162float(__float2bfloat16(acc[1][t]));
+                  p.out[(long long)tok * p.ldc + n] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+                }
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const int n = tile * ROWS + mt * 128 + row;
+            if (n < width) {
+              const float bi = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+              for (int t = 0; t < 32; ++t) {
+                const int tok = c * 32 + t;
+                if (tok < p.Mtok)
+                  p.out[(long long)tok * p.ldc + n] = __float2bfloat16(sk_act(acc[mt][t] + bi, p.act));
+              }
+            }
+          }
+        }
+      }
     }
   }
   tc_fence_before();
@@ -476,6 +591,54 @@ __global__ void skinny_finalize_kernel(const float* __restrict__ partial, const 
   }
 }
 
+static int g_cluster_splitk = -1;
+bool cluster_splitk_enabled() {
+  if (g_cluster_splitk < 0) {
+    const char* e = std::getenv("FC_CLUSTER_SPLITK");
+    g_cluster_splitk = (e != nullptr && std::string(e) == "0") ? 0 : 1;
+  }
+  return g_cluster_splitk == 1;
+}
+void set_cluster_splitk(bool on) { g_cluster_splitk = on ? 1 : 0; }
+
+// How many clusters of `cluster_y` CTAs of this kernel the device holds at once (0: such clusters cannot be placed).
+template <int BN, int STAGES, int ROWS>
+static int skinny_max_clusters(int cluster_y) {
+  using L = SkinnySmem<BN, STAGES, ROWS>;
+  static int cache[64][9];
+  static bool init = false;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!init) {
+    for (auto& row : cache)
+      for (int& v : row) v = -1;
+    init = true;
+  }
+  if (cluster_y < 1 || cluster_y > 8) return 0;
+  if (cache[dev][cluster_y] >= 0) return cache[dev][cluster_y];
+  auto kern = gemm_skinny_kernel<BN, STAGES, ROWS>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1, cluster_y, 1);
+  cfg.blockDim = dim3(SK_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cluster_y;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cache[dev][cluster_y] = n;
+  return n;
+}
+
 template <int BN, int STAGES, int ROWS>
 static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, int tiles,
                           cudaStream_t stream) {
@@ -491,7 +654,10 @@ static void launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Sk
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     configured.fetch_or(bit, std::memory_order_relaxed);
   }
-  cudaError_t e = launch_pdl(PDL_SKINNY_GEMM, kern, dim3(tiles, p.splits), dim3(SK_THREADS), L::TOTAL, stream, tw, tx, p);
+  cudaError_t e = p.cluster > 0
+      ? launch_pdl_cluster(PDL_SKINNY_GEMM, kern, dim3(tiles, p.splits), dim3(SK_THREADS), L::TOTAL, stream,
+                           unsigned(p.splits), tw, tx, p)
+      : launch_pdl(PDL_SKINNY_GEMM, kern, dim3(tiles, p.splits), dim3(SK_THREADS), L::TOTAL, stream, tw, tx, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("skinny gemm launch: ") + cudaGetErrorString(e));
 }
@@ -527,16 +693,46 @@ int skinny_pick_splits(int tiles, int tile_rows, int num_kb, int sms, int M, int
   return best;
 }
 
+// Cluster form: K splits = CTAs of a cluster.  S must leave room for the exchange in the operand stages
+// ((S - 1) x halves x owned chunks x 16 KiB) and clusters of S must be placeable; cost as above with waves counted in
+// clusters.  Returns 0 when no S (not even 1) fits.
+template <int BN, int STAGES, int ROWS>
+static int skinny_pick_cluster(int tiles, int num_kb, int sms_cap) {
+  using L = SkinnySmem<BN, STAGES, ROWS>;
+  constexpr int MT = ROWS / 128, CHUNKS = BN / 32;
+  int best = 0;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 8 && s <= CHUNKS; ++s) {
+    if (s > 1 && num_kb / s < 2) break;
+    if ((num_kb + (num_kb + s - 1) / s - 1) / ((num_kb + s - 1) / s) != s) continue;   // every CTA must get K blocks
+    const int cl_max = (CHUNKS + s - 1) / s;
+    if ((s - 1) * MT * cl_max * (8 * 128 * 16) > L::BAR_OFF) continue;
+    int active = skinny_max_clusters<BN, STAGES, ROWS>(s);
+    if (sms_cap > 0) active = std::min(active, sms_cap / s);
+    if (active <= 0) continue;
+    const int waves = (tiles + active - 1) / active;
+    const int kb = (num_kb + s - 1) / s;
+    const double cost = waves * (kb + 6.0) + 0.7 * (s - 1);      // the exchange grows a little with the cluster
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
 // Returns the number of splits used.  splits_request: 0 = choose; when the result is > 1 and
 // `finalize` is false the caller consumes ws.scratch as fp32 [splits, M, N] itself.
 int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                      long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
-                     int splits_request, bool finalize, cudaStream_t stream, const SkinnyFused* fused) {
+                     int splits_request, bool finalize, cudaStream_t stream, const SkinnyFused* fused, int flags) {
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
   const int num_kb = (K + SK_BK - 1) / SK_BK;
+  const bool swiglu = (flags & SK_SWIGLU) != 0;
+  if (swiglu && (N % 256 != 0 || fused != nullptr || bias != nullptr)) return 0;
   // 128-row tiles when 256-row tiles would cover less than half of the SMs: the same SM count is then reached
-  // with half the K splits, i.e. half the partial-sum traffic
-  const bool small_rows = (N + SK_BM - 1) / SK_BM <= sms / 2;
+  // with half the K splits, i.e. half the partial-sum traffic.  (SwiGLU tiles are 128 gate + 128 up rows.)
+  const bool small_rows = !swiglu && (N + SK_BM - 1) / SK_BM <= sms / 2;
   const int rows = small_rows ? 128 : SK_BM;
   const int tiles = (N + rows - 1) / rows;
   const size_t scratch_floats = ws.scratch != nullptr ? gemm_scratch_bytes() / 4 : 0;
@@ -553,8 +749,25 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   if (N % 4 != 0) splits = 1;
   if (splits > 1 && (size_t)splits * M * N > scratch_floats) splits = 1;
   if (fuse && tiles * splits > sms) splits = std::max(1, sms / tiles);
+  // ---- the cluster form, where allowed: the splits become the CTAs of a cluster and nothing is left for a consumer
+  int cluster = 0;
+  const bool want_cluster = !fuse && splits_request <= 0 && (flags & SK_NO_CLUSTER) == 0 && cluster_splitk_enabled();
+  if (want_cluster || swiglu) {
+    const int cap = sm_limit > 0 ? sm_limit : 0;
+    int s_c = 0;
+    if (M <= 32) s_c = small_rows ? skinny_pick_cluster<32, 8, 128>(tiles, num_kb, cap) : skinny_pick_cluster<32, 6, 256>(tiles, num_kb, cap);
+    else if (M <= 64) s_c = small_rows ? skinny_pick_cluster<64, 7, 128>(tiles, num_kb, cap) : skinny_pick_cluster<64, 5, 256>(tiles, num_kb, cap);
+    else if (M <= 128) s_c = small_rows ? skinny_pick_cluster<128, 6, 128>(tiles, num_kb, cap) : skinny_pick_cluster<128, 4, 256>(tiles, num_kb, cap);
+    else s_c = small_rows ? skinny_pick_cluster<256, 4, 128>(tiles, num_kb, cap) : skinny_pick_cluster<256, 3, 256>(tiles, num_kb, cap);
+    if (s_c > 0) {
+      cluster = 1;
+      splits = s_c;
+    } else if (swiglu) {
+      return 0;
+    }
+  }
   int kb_per = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kb_per - 1) / kb_per;
+  if (!cluster) splits = (num_kb + kb_per - 1) / kb_per;      // (the cluster sizes were chosen so that this holds)
   SkinnyParams p{};
   p.Nw = N;
   p.Mtok = M;
@@ -567,6 +780,8 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
   p.splits = splits;
   p.kb_per_split = kb_per;
   p.status = ws.status;
+  p.cluster = cluster;
+  p.swiglu = swiglu ? 1 : 0;
   if (fuse) {
     p.epi = fused->epi;
     p.grid_sync = ws.grid_sync;
@@ -601,6 +816,7 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
     if (small_rows) launch_skinny<256, 4, 128>(tw, tx, p, tiles, stream);
     else launch_skinny<256, 3, 256>(tw, tx, p, tiles, stream);
   }
+  if (cluster) return 1;               // finished bf16 result in `c`
   if (splits > 1 && finalize && !fuse) {
     const long long total = (long long)M * (N / 4);
     const int blocks = (int)std::min<long long>((total + 255) / 256, 2048);

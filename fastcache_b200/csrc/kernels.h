@@ -79,7 +79,9 @@ void launch_ccm_fused(void* pool, const int* block_tables, const int* kv_lens, c
                       const void* b3, int n_seq, int n_weight_layers, int layer_start, int layer_end,
                       int weight_layer_start, int num_blocks, int Hkv, int block_size, int D, int max_blocks,
                       int factor, int min_seq_len, int single_segment, int heads_per_cta, uint32_t* status,
-                      cudaStream_t stream);
+                      cudaStream_t stream, const int* dst_block_tables = nullptr);
+// dst_block_tables [n_seq, max_blocks]: write the compressed rows into these blocks instead of the leading rows
+// of the request's own blocks (which then stay as they are).
 
 // consumers of split-K partial sums [splits, T, N] fp32 (partials.cu)
 void launch_add_rms_norm_partials(const float* partial, int splits, long long split_stride, const void* bias,
@@ -87,4 +89,16 @@ void launch_add_rms_norm_partials(const float* partial, int splits, long long sp
                                   cudaStream_t s);
 void launch_silu_mul_partials(const float* partial, int splits, long long split_stride, void* out, long long T,
                               int I, cudaStream_t s);
+}  // namespace fc
+
+namespace fc {
+// KV quantisers (quant.cu).  x: bf16 [groups, g]; codes: one byte per value (INT8, FP8) or per two values (INT4,
+// NF4: even index in the low nibble); scale [groups] fp32 (the absmax for the 4-bit modes); zero [groups] for
+// the asymmetric mode.  y_fake != nullptr: write decode(encode(x)) there instead of codes and scales.
+enum QuantMode : int { QUANT_INT8 = 0, QUANT_INT8_ASYM = 1, QUANT_INT4 = 2, QUANT_NF4 = 3, QUANT_FP8_E4M3 = 4,
+                       QUANT_FP8_E5M2 = 5 };
+void launch_quantize(const void* x, void* q, float* scale, float* zero, void* y_fake, long long groups, int g,
+                     int mode, cudaStream_t s);
+void launch_dequantize(const void* q, const float* scale, const float* zero, void* y, long long groups, int g,
+                       int mode, cudaStream_t s);
 }  // namespace fc

@@ -244,6 +244,35 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// ------------------------------------------------------------ thread-block clusters
+// Distributed shared memory between the CTAs of a cluster (no multicast loads anywhere: every CTA fetches its own
+// tiles; the cluster is used to exchange results).  `cluster_sync` is a barrier over ALL threads of ALL CTAs of the
+// cluster with release / acquire semantics for shared-memory writes, so every thread of every CTA must reach each
+// call, on every path.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local_smem_addr` (a shared::cta address of this CTA) in the shared memory of CTA `rank`
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
 // ------------------------------------------- programmatic dependent launch
 // A kernel launched with `launch_pdl` (launch.h) may start while its predecessor in the stream is
 // still running.  `pdl_launch_dependents()` at the top lets the successor's CTAs be scheduled early;

@@ -236,6 +236,22 @@ class BlockManager:
         seq.num_cached_tokens = 0
         return len(tail)
 
+    # ------------------------------------------------- blocks outside a block table
+    def take_blocks(self, n: int) -> List[int]:
+        """`n` fresh private blocks that belong to no block table yet (the destination of an out-of-place
+        compression; the caller keeps them in `Sequence.shadow_table`).  Raises if the pool cannot give them."""
+        if n > len(self.free_block_ids):
+            raise RuntimeError(f"asked for {n} blocks, {len(self.free_block_ids)} are free")
+        return [self._pop_free().block_id for _ in range(n)]
+
+    def release_blocks(self, block_ids: Iterable[int]) -> int:
+        """Give back blocks obtained with `take_blocks` or a block table that a request no longer uses."""
+        n = 0
+        for block_id in reversed(list(block_ids)):
+            self._release(block_id)
+            n += 1
+        return n
+
     def free_specific_blocks(self, block_ids: Iterable[int]) -> int:
         n = 0
         for block_id in block_ids:
@@ -262,7 +278,7 @@ class BlockManager:
         if live is not None:
             refs: Dict[int, int] = {}
             for s in live:
-                for b in s.block_table:
+                for b in list(s.block_table) + list(getattr(s, "shadow_table", ())):
                     refs[b] = refs.get(b, 0) + 1
             for b, n in refs.items():
                 if self.blocks[b].ref_count != n:

@@ -48,6 +48,7 @@ class PendingCompression:
     new_len: int = 0
     reported: bool = False
     stream: Any = None            # decode pipeline: the one stream all layer chunks of this request run on
+    shadow: bool = False          # the result goes to `seq.shadow_table`; the request keeps decoding meanwhile
 
 
 @dataclass
@@ -80,7 +81,7 @@ class LLMEngine:
                  auto_tune: bool = False, auto_tune_interval: int = 4, auto_dual_batch: bool = True,
                  auto_dual_interval: int = 4, auto_min_seq_len: int = 256, auto_min_output_len: int = 64,
                  auto_min_speedup: float = 1.05, auto_force_compress: bool = False,
-                 compressor: Any = None, tokenizer: Any = None, **kwargs):
+                 compressor: Any = None, tokenizer: Any = None, decode_overlap: str = "shadow", **kwargs):
         hf_config = kwargs.pop("hf_config", None)
         if not isinstance(model, str):          # a config object / dict instead of a path: random init
             hf_config, model = model, ""
@@ -158,6 +159,15 @@ class LLMEngine:
                 min_seq_len=auto_min_seq_len, min_output_len=auto_min_output_len,
                 min_speedup=auto_min_speedup, force_compress=auto_force_compress,
                 dual_batch_enabled=auto_dual_batch, dual_batch_interval=self.auto_dual_interval)
+        # decode pipeline: "shadow" = the layers are compressed into a second set of blocks while the request keeps
+        # decoding over its original rows (the reference's decode-overlap engine, "kv-cache pipeline"/nanovllm/
+        # engine/llava_model_runner.py:1271-1338: snapshot, a few layers per decode step, the tokens decoded
+        # meanwhile appended at the end); "hold" = in place, the request sits out of the decode batches until
+        # its last layer is done (no extra blocks).  Shadow needs merge compression and free blocks for the
+        # compressed copy, and falls back to hold per request when it has neither.
+        if decode_overlap not in ("shadow", "hold"):
+            raise ValueError("decode_overlap must be 'shadow' or 'hold'")
+        self.decode_overlap = decode_overlap
         self._pending: Dict[int, PendingCompression] = {}
         self._pending_compression_events = self._pending     # name used by the reference's benches
         self.async_manager = AsyncCompressionManager(self)
@@ -278,6 +288,9 @@ class LLMEngine:
         p = self._pending.pop(seq.seq_id, None)
         if p is not None and p.event is not None and self.model_runner.main_stream is not None:
             self.model_runner.main_stream.wait_event(p.event)
+        if seq.shadow_table:                     # the half-written compressed copy goes back to the pool
+            self.scheduler.block_manager.release_blocks(seq.shadow_table)
+            seq.shadow_table = []
         self.model_runner.release(seq)
 
     def _privatize(self, seq: Sequence) -> None:
@@ -367,34 +380,56 @@ class LLMEngine:
             self.stats.compressed_rows_in += n_in
             self.stats.compressed_rows_out += n_out
 
+    def _shadow_blocks_for(self, seq: Sequence, rows: int) -> Optional[List[int]]:
+        """Destination blocks for an out-of-place compression of `rows` rows, or None when this request has to be
+        compressed in place: eviction backend, or not enough free blocks (every running request keeps one block
+        in reserve for its next rows)."""
+        r, bm = self.model_runner, self.scheduler.block_manager
+        if self.decode_overlap != "shadow" or self.compression_backend != "mlp" or r.packed_compressor is None:
+            return None
+        from ..compress.ccm import ccm_output_len
+        img = 0 if r.packed_compressor.single_segment else r._image_rows_of(seq)
+        n_out = ccm_output_len(rows, img, self.compression_factor, r.min_seq_len)
+        steps = -(-r.num_hidden_layers // max(1, r.decode_layers_per_step))
+        need = -(-(n_out + steps + 2) // bm.block_size)            # the rows decoded meanwhile follow the copy
+        if bm.num_free_blocks - need < len(self.scheduler.running) + 1:
+            return None
+        return bm.take_blocks(need)
+
     def _start_chunked(self, seqs: List[Sequence]) -> None:
         """Decode pipeline: compress a few layers per engine step beside decode."""
         for s in seqs:
             if not self._eligible(s):
                 continue
-            self._privatize(s)
+            rows = s.rows_in_pool
+            shadow = self._shadow_blocks_for(s, rows)
             s.compression_state = CompressionState.IN_PROGRESS
-            s.hold = True
+            if shadow is None:
+                self._privatize(s)
+                s.hold = True
+            else:
+                s.shadow_table = shadow              # the source rows are only read: shared prefix blocks stay shared
             # every chunk of one request runs on the same stream, so chunk k + 1 is ordered after chunk k
-            self._pending[s.seq_id] = PendingCompression(s, None, None, s.rows_in_pool, 0, s.rows_in_pool, 0,
-                                                         stream=self.model_runner.next_compress_stream())
+            self._pending[s.seq_id] = PendingCompression(s, None, None, rows, 0, rows, 0,
+                                                         stream=self.model_runner.next_compress_stream(),
+                                                         shadow=shadow is not None)
 
     def _advance_chunked(self) -> None:
         r = self.model_runner
-        todo = [p for p in self._pending.values() if p.seq.hold]
+        L = r.num_hidden_layers
+        todo = [p for p in self._pending.values() if p.seq.hold or (p.shadow and p.next_layer < L)]
         if not todo:
             return
-        L = r.num_hidden_layers
         step = max(1, r.decode_layers_per_step)
         groups: Dict[Tuple[int, int], List[PendingCompression]] = {}
         for p in todo:
             if p.stream is not None and not any(p.stream is c for c in r.compress_streams):
                 # the streams were rebuilt for a new SM split (which synchronises the device first)
                 p.stream = r.next_compress_stream()
-            groups.setdefault((id(p.stream), p.next_layer), []).append(p)
+            groups.setdefault((id(p.stream), p.next_layer, p.shadow), []).append(p)
         ready = None
         waited = set()
-        for (_, first), ps in groups.items():
+        for (_, first, shadow), ps in groups.items():
             stream = ps[0].stream
             if stream is not None and id(stream) not in waited:
                 if ready is None:
@@ -408,7 +443,8 @@ class LLMEngine:
             for p in ps:
                 p.seq._kv_cache_len = p.rows
             with nvtx_range("compress_chunk"):
-                new = r.compress_kv_cache_batch(seqs, first, last, stream=stream)
+                new = r.compress_kv_cache_batch(seqs, first, last, stream=stream,
+                                                dst_tables=[q.shadow_table for q in seqs] if shadow else None)
             # an event after every chunk: whoever takes the request's blocks away (preemption, abort, finish)
             # or reads its rows (decode) orders the main stream after the newest chunk launched so far
             ev = None
@@ -420,7 +456,9 @@ class LLMEngine:
                 p.next_layer = last
                 p.new_len = n
                 p.event = ev
-                if last >= L:
+                if last >= L and shadow:
+                    pass                         # switched in by `_finalize_pending` before the request's next decode
+                elif last >= L:
                     s.hold = False
                     s.kv_cache_len = n + int(s._pending_row)
                     self.stats.compressions += 1
@@ -434,11 +472,48 @@ class LLMEngine:
             p = self._pending.get(s.seq_id)
             if p is None or s.hold:
                 continue
+            if p.shadow:
+                if p.next_layer >= r.num_hidden_layers:
+                    self._switch_to_shadow(s, p)
+                continue                             # chunks still to go: the request decodes over its full rows
             if p.event is not None and r.main_stream is not None:
                 r.main_stream.wait_event(p.event)
             del self._pending[s.seq_id]
             s.compression_state = CompressionState.COMPLETED
             self._free_compressed_blocks(s)
+
+    def _switch_to_shadow(self, s: Sequence, p: PendingCompression) -> None:
+        """All layers of `s` are compressed into its shadow blocks: move the rows decoded meanwhile behind them,
+        make the shadow blocks the request's block table and return the original blocks.  Called right before
+        the request's next decode step (whose row the scheduler has already made room for in the old table)."""
+        r, bm = self.model_runner, self.scheduler.block_manager
+        tail = s.rows_in_pool - p.rows                    # rows decoded while the chunks ran
+        total = p.new_len + tail + int(s._pending_row)
+        need = -(-total // bm.block_size)
+        extra = need - len(s.shadow_table)
+        if extra > bm.num_free_blocks:
+            return                                   # no room right now: keep decoding over the full rows
+        if extra > 0:
+            s.shadow_table.extend(bm.take_blocks(extra))
+        if p.event is not None and r.main_stream is not None:
+            r.main_stream.wait_event(p.event)
+        cm = torch.cuda.stream(r.main_stream) if r.main_stream is not None else None
+        if cm is not None:
+            with cm:
+                r.copy_rows(s.block_table, p.rows, s.shadow_table, p.new_len, tail)
+        else:
+            r.copy_rows(s.block_table, p.rows, s.shadow_table, p.new_len, tail)
+        old, s.block_table, s.shadow_table = s.block_table, s.shadow_table, []
+        freed = bm.release_blocks(old) - len(s.block_table)
+        s.num_cached_tokens = 0
+        s.kv_cache_len = total
+        s.compression_state = CompressionState.COMPLETED
+        r._compressed_lens[s.seq_id] = p.new_len
+        del self._pending[s.seq_id]
+        self.stats.blocks_freed += max(0, freed)
+        self.stats.compressions += 1
+        self.stats.compressed_rows_in += p.rows
+        self.stats.compressed_rows_out += p.new_len
 
     def _lazy_check(self) -> None:
         sch = self.scheduler

@@ -530,8 +530,10 @@ class ModelRunner:
 
     @torch.inference_mode()
     def compress_kv_cache_batch(self, seqs: Seq[Sequence], layer_start: int = 0,
-                                layer_end: Optional[int] = None, stream: Any = None) -> List[int]:
-        """Compress the pool rows of `seqs` in place; returns the new row counts.
+                                layer_end: Optional[int] = None, stream: Any = None,
+                                dst_tables: Optional[List[List[int]]] = None) -> List[int]:
+        """Compress the pool rows of `seqs` in place; returns the new row counts.  With `dst_tables` (merge
+        compression only) the result goes to those blocks and the requests' own rows stay as they are.
 
         Does not touch scheduler state: the engine updates `seq.kv_cache_len`
         and frees the tail blocks once the work is ordered before their reuse.
@@ -550,8 +552,10 @@ class ModelRunner:
                     raise RuntimeError("no compressor loaded")
                 imgs = [self._image_rows_of(s) for s in seqs]
                 new = ccm_compress_in_pool(self.kv_cache, tables, lens, imgs, self.packed_compressor,
-                                           layer_start, layer_end)
+                                           layer_start, layer_end, dst_tables)
             else:
+                if dst_tables is not None:
+                    raise ValueError("eviction compacts in place: no destination blocks")
                 ratio = ratio_from_factor(self.compression_factor)
                 kept = [n_kept_for(n, ratio) for n in lens]
                 wq = None
@@ -574,6 +578,21 @@ class ModelRunner:
 
     def copy_block(self, src: int, dst: int) -> None:
         self.kv_cache[:, :, dst].copy_(self.kv_cache[:, :, src])
+
+    def copy_rows(self, src_table: Seq[int], src_row: int, dst_table: Seq[int], dst_row: int, count: int) -> None:
+        """Rows [src_row, src_row + count) of one request (all layers, K and V) to rows [dst_row, ...) of another
+        block table.  Used once per request when an out-of-place compression is switched in: the few rows decoded
+        meanwhile move behind the compressed ones."""
+        if count <= 0:
+            return
+        bs = self.block_size
+        dev = self.kv_cache.device
+        r = torch.arange(count)
+        src, dst = r + src_row, r + dst_row
+        sb = torch.as_tensor(src_table, dtype=torch.long)[src // bs].to(dev)
+        db = torch.as_tensor(dst_table, dtype=torch.long)[dst // bs].to(dev)
+        so, do = (src % bs).to(dev), (dst % bs).to(dev)
+        self.kv_cache[:, :, db, :, do] = self.kv_cache[:, :, sb, :, so]
 
     def read_device_status(self) -> int:
         """Status word the kernels write when a bounded wait runs out or an index is out of range
@@ -694,7 +713,8 @@ class ModelRunner:
         if layers_per_step == self.decode_layers_per_step:
             return True
         mgr = getattr(self, "_async_manager", None)
-        if mgr is not None and any(p.seq.hold for p in mgr.engine._pending.values()):
+        if mgr is not None and any(p.seq.hold or (p.shadow and p.next_layer < self.num_hidden_layers)
+                                   for p in mgr.engine._pending.values()):
             return False
         if self.compression_backend == "mlp" and self.packed_compressor is None:
             return False
@@ -711,9 +731,15 @@ class ModelRunner:
         """Launch the next layer chunk of every held request; returns those of `seqs` whose last
         chunk has now been launched (their blocks are freed when they next decode)."""
         eng = self._owner()
-        held = {s.seq_id for s in seqs if s.hold}
+        L = self.num_hidden_layers
+
+        def running(s):
+            p = eng._pending.get(s.seq_id)
+            return s.hold or (p is not None and p.shadow and p.next_layer < L)
+
+        before = {s.seq_id for s in seqs if running(s)}
         eng._advance_chunked()
-        return [s for s in seqs if s.seq_id in held and not s.hold]
+        return [s for s in seqs if s.seq_id in before and not running(s)]
 
     @staticmethod
     def wait_compression(event: Any) -> None:

@@ -67,6 +67,8 @@ class Sequence:
         self.compression_state = CompressionState.NONE
         self.compression_event: Any = None
         self.hold = False             # kept out of decode batches (chunked compression running)
+        # blocks that receive this request's compressed rows while it keeps decoding over the original ones
+        self.shadow_table: List[int] = []
         self._pending_row = False     # the newest token's K/V row is not in the pool yet
         # timestamps (host seconds, monotonic) for TTFT / TPOT
         self.arrival_time = time.perf_counter()
@@ -202,6 +204,7 @@ class Sequence:
         self.num_computed_tokens = 0
         self.prefill_end = None
         self.block_table = []
+        self.shadow_table = []
 
     # pickling for the optional driver->worker plan broadcast keeps messages small
     def __getstate__(self):

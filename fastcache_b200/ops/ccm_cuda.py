@@ -38,15 +38,18 @@ def heads_per_tile(num_kv_heads: int, kv_lens: Sequence[int], image_lens: Sequen
 
 
 def ccm_compress(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: Sequence[int],
-                 image_lens: Sequence[int], w, layer_start: int = 0, layer_end: Optional[int] = None) -> None:
+                 image_lens: Sequence[int], w, layer_start: int = 0, layer_end: Optional[int] = None,
+                 dst_block_tables: Optional[List[Sequence[int]]] = None) -> None:
+    """`dst_block_tables`: blocks that receive the compressed rows (the source rows then stay as they are)."""
     L = pool.shape[0]
     layer_end = L if layer_end is None else min(layer_end, L)
     D = pool.shape[5]
     if D != 128 or w.w1.dtype != torch.bfloat16 or w.factor > 8:
         # shapes the tcgen05 kernel is not built for: the PyTorch statement on the device
         from ..compress.inpool import ccm_compress_reference
-        for bt, n, i in zip(block_tables, kv_lens, image_lens):
-            ccm_compress_reference(pool, bt, n, i, w, layer_start, layer_end)
+        for k, (bt, n, i) in enumerate(zip(block_tables, kv_lens, image_lens)):
+            ccm_compress_reference(pool, bt, n, i, w, layer_start, layer_end,
+                                   dst_block_table=None if dst_block_tables is None else dst_block_tables[k])
         return
     e = ext()
     dev = pool.device
@@ -54,5 +57,13 @@ def ccm_compress(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens:
     img_d = torch.tensor(list(image_lens), dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
     status = e.status_tensor(dev.index if dev.index is not None else torch.cuda.current_device())
     g = heads_per_tile(pool.shape[3], kv_lens, image_lens, int(w.factor), int(w.min_seq_len), bool(w.single_segment))
+    dst_d = None
+    if dst_block_tables is not None:
+        import numpy as np
+        dst = np.zeros(tuple(bt_d.shape), dtype=np.int32)
+        for k, t in enumerate(dst_block_tables):
+            t = list(t)[: dst.shape[1]]
+            dst[k, : len(t)] = t
+        dst_d = torch.from_numpy(dst).pin_memory().to(dev, non_blocking=True)
     e.ccm_compress(pool, bt_d, lens_d, img_d, w.w1, w.b1, w.w2, w.b2, w.w3, w.b3, int(layer_start), int(layer_end),
-                   int(layer_start), int(w.factor), int(w.min_seq_len), bool(w.single_segment), status, g)
+                   int(layer_start), int(w.factor), int(w.min_seq_len), bool(w.single_segment), status, g, dst_d)

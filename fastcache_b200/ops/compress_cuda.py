@@ -84,6 +84,7 @@ def evict_cuda(pool: torch.Tensor, block_tables: List[Sequence[int]], kv_lens: S
     return kept
 
 
-def ccm_compress_cuda(pool, block_tables, kv_lens, image_lens, w, layer_start=0, layer_end=None) -> None:
+def ccm_compress_cuda(pool, block_tables, kv_lens, image_lens, w, layer_start=0, layer_end=None,
+                      dst_block_tables=None) -> None:
     from .ccm_cuda import ccm_compress
-    ccm_compress(pool, block_tables, kv_lens, image_lens, w, layer_start, layer_end)
+    ccm_compress(pool, block_tables, kv_lens, image_lens, w, layer_start, layer_end, dst_block_tables)

@@ -37,8 +37,83 @@ def test_eviction_in_layer_chunks_matches_one_call(method, layers_per_step):
 def test_merge_in_layer_chunks_matches_one_call(layers_per_step):
     sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
     want = _engine("prefill", 4, backend="mlp").generate(_prompts(), sp)
-    got = _engine("decode", layers_per_step, backend="mlp").generate(_prompts(), sp)
+    got = _engine("decode", layers_per_step, backend="mlp", decode_overlap="hold").generate(_prompts(), sp)
     assert [o["token_ids"] for o in got] == [o["token_ids"] for o in want]
+
+
+def test_shadow_compression_with_all_layers_in_one_chunk_matches_the_prefill_pipeline():
+    """Out-of-place compression whose only chunk runs before the request's first decode step switches in with no
+    rows decoded meanwhile: the same tokens as compressing right after prefill."""
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    want = _engine("prefill", 4, backend="mlp").generate(_prompts(), sp)
+    llm = _engine("decode", 4, backend="mlp", decode_overlap="shadow")
+    got = llm.generate(_prompts(), sp)
+    assert [o["token_ids"] for o in got] == [o["token_ids"] for o in want]
+    bm = llm.scheduler.block_manager
+    bm.check_invariants([])
+    assert bm.num_free_blocks == bm.num_blocks and llm.stats.compressions == 3
+
+
+def test_shadow_compression_keeps_the_request_decoding():
+    """One layer per engine step: the request gets a token at every step while its layers are compressed into a
+    second set of blocks, then continues over [compressed rows | rows decoded meanwhile]."""
+    from fastcache_b200.compress.inpool import _rows, ccm_compress_reference
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    llm = _engine("decode", 1, backend="mlp", decode_overlap="shadow")
+    r, bm = llm.model_runner, llm.scheduler.block_manager
+    seq = llm.add_request(_prompts(1)[0], sp)
+    llm.step()                                             # prefill: 96 rows in 6 blocks
+    assert not seq.hold and len(seq.shadow_table) >= 4 and seq.seq_id in llm._pending
+    pool0 = r.kv_cache.clone()
+    old_table = list(seq.block_table)
+    produced = []
+    while seq.seq_id in llm._pending:
+        before = seq.num_completion_tokens
+        llm.step()
+        produced.append(seq.num_completion_tokens - before)
+        bm.check_invariants([seq])
+    assert produced and all(n == 1 for n in produced)      # never held out of a decode batch
+    assert len(produced) == 4                              # a chunk per step; the switch comes in the step of the last
+    tail = len(produced) - 1                               # rows decoded over the full KV before the switch
+    n_out = 96 // 2
+    assert seq.is_compressed and seq.kv_cache_len == n_out + tail + 1 + 1 and not seq.shadow_table
+    # the compressed rows are what compressing the prefill rows gives; the rows decoded meanwhile follow them
+    want_pool = pool0.clone()
+    ccm_compress_reference(want_pool, old_table, 96, 0, r.packed_compressor)
+    new_blocks = torch.tensor(seq.block_table)
+    for layer in range(4):
+        for kv in (0, 1):
+            got = _rows(r.kv_cache[layer, kv], new_blocks, n_out)
+            want = _rows(want_pool[layer, kv], torch.tensor(old_table), n_out)
+            torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+    while not llm.is_finished():
+        llm.step()
+    bm.check_invariants([])
+    assert bm.num_free_blocks == bm.num_blocks and seq.num_completion_tokens == 10
+
+
+def test_shadow_falls_back_to_hold_without_free_blocks_and_survives_preemption():
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = _engine("decode", 1, backend="mlp", decode_overlap="shadow", blocks=8)   # 96 rows = 6 of 8 blocks
+    seq = llm.add_request(_prompts(1)[0], sp)
+    llm.step()
+    assert seq.hold and not seq.shadow_table               # no room for a second copy: in place
+    while not llm.is_finished():
+        llm.step()
+    # a request that loses its blocks between chunks gives its shadow blocks back too
+    llm2 = _engine("decode", 1, backend="mlp", decode_overlap="shadow")
+    s2 = llm2.add_request(_prompts(1)[0], sp)
+    llm2.step()
+    llm2.step()
+    assert s2.shadow_table
+    llm2.scheduler.running.remove(s2)
+    llm2.scheduler.preempt(s2)
+    bm = llm2.scheduler.block_manager
+    assert not s2.shadow_table and bm.num_free_blocks == bm.num_blocks
+    bm.check_invariants([])
+    while not llm2.is_finished():
+        llm2.step()
+    assert s2.num_completion_tokens == 6
 
 
 def test_chunks_of_one_request_stay_on_one_stream_and_leave_an_event_each():
@@ -70,9 +145,9 @@ def test_chunks_of_one_request_stay_on_one_stream_and_leave_an_event_each():
     used = []
     real = r.compress_kv_cache_batch
 
-    def spy(seqs, first=0, last=None, stream=None):
+    def spy(seqs, first=0, last=None, stream=None, dst_tables=None):
         used.append((tuple(s.seq_id for s in seqs), first, stream.name))
-        return real(seqs, first, last, stream=None)
+        return real(seqs, first, last, stream=None, dst_tables=dst_tables)
 
     r.compress_kv_cache_batch = spy
     orig_event = eng_mod.torch.cuda.Event
@@ -121,7 +196,8 @@ def test_preempting_a_request_between_chunks_orders_the_main_stream_first():
     r.compress_streams = [side]
     r.main_stream = FakeStream()
     real = r.compress_kv_cache_batch
-    r.compress_kv_cache_batch = lambda seqs, first=0, last=None, stream=None: real(seqs, first, last, stream=None)
+    r.compress_kv_cache_batch = lambda seqs, first=0, last=None, stream=None, dst_tables=None: \
+        real(seqs, first, last, stream=None, dst_tables=dst_tables)
     orig_event = eng_mod.torch.cuda.Event
     eng_mod.torch.cuda.Event = FakeEvent
     try:

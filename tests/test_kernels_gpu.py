@@ -170,3 +170,27 @@ def test_dense_attention(B, Sq, Sk, H, D, masked):
     o = ops.dense_attention(q, k, v, D ** -0.5, mask)
     want = ref.dense_attention(q.float(), k.float(), v.float(), D ** -0.5, mask)
     assert (o.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("mode", ["int8", "int8_asym", "int4", "nf4", "fp8_e4m3", "fp8_e5m2"])
+@pytest.mark.parametrize("shape", [(2, 8, 333, 128), (5, 77, 256), (3, 64)])
+def test_quantiser_kernels_match_the_pytorch_statements(mode, shape):
+    """Codes, scales and restored values of the CUDA quantisers against the same op stated in PyTorch on fp32
+    copies of the data (bit-identical codes; restored values equal after the bf16 rounding of the output)."""
+    from fastcache_b200.compress import quant
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(*shape, generator=g) * 3).to(torch.bfloat16)
+    x[..., 0] = 0                                                   # exact zeros and ties
+    dev = quant.quantize(x.cuda(), mode, 64)
+    cpu = quant.quantize(x, mode, 64)                               # the PyTorch statement
+    assert dev["q"].dtype == cpu["q"].dtype and tuple(dev["q"].shape) == tuple(cpu["q"].shape)
+    torch.testing.assert_close(dev["scale"].cpu(), cpu["scale"], rtol=0, atol=0)
+    if mode == "int8_asym":
+        torch.testing.assert_close(dev["zero"].cpu(), cpu["zero"], rtol=0, atol=0)
+    assert torch.equal(dev["q"].cpu().view(torch.uint8), cpu["q"].view(torch.uint8))
+    back_dev, back_cpu = quant.dequantize(dev), quant.dequantize(cpu)
+    assert back_dev.dtype == torch.bfloat16 and back_dev.shape == x.shape
+    torch.testing.assert_close(back_dev.cpu().float(), back_cpu.float(), rtol=0, atol=0)
+    if mode in ("int8", "int4"):
+        fake = quant.fake_quantize(x.cuda(), 8 if mode == "int8" else 4, 64)
+        torch.testing.assert_close(fake.cpu().float(), back_cpu.float(), rtol=0, atol=0)

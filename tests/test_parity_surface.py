@@ -145,7 +145,7 @@ def test_runner_surface_drives_chunked_compression():
     comp = random_compressor(KVCacheLinearDecoupleCompressor, 2, 64, 4)
     llm = LLM(tiny_llama_config(), kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=512, device="cpu",
               enforce_eager=True, enable_compression=True, compressor=comp, compression_backend="mlp",
-              compression_pipeline="decode", decode_layers_per_step=1)
+              compression_pipeline="decode", decode_layers_per_step=1, decode_overlap="hold")
     r = llm.model_runner
     sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
     g = torch.Generator().manual_seed(3)
