@@ -534,10 +534,13 @@ void set_wait_limit_us(int64_t device, int64_t us) {
 // device is idle, e.g. from LLMEngine.recover()).
 void reset_sync_state(int64_t device) {
   std::lock_guard<std::mutex> lk(g_mu);
+  c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, int(device)));
+  cudaDeviceSynchronize();
   for (auto& kv : g_ws) {
     if (int(kv.first & 0xFF) != int(device & 0xFF)) continue;
-    kv.second.grid_sync.zero_();
-    kv.second.gemm_counters.zero_();
+    // plain memsets on the raw pointers: the tensors may have been created under inference mode
+    cudaMemset(kv.second.raw.grid_sync, 0, 4 * sizeof(int));
+    cudaMemset(kv.second.raw.gemm_counters, 0, fc::gemm_counter_bytes());
   }
 }
 

@@ -58,14 +58,15 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
 // not a multiple of 8): the caller then runs the unfused pair of kernels.
 // `flags`: SK_SWIGLU: w = [gate; up] ([N, K], N = 2 x width) and c [M, N / 2] = silu(x gate^T) * (x up^T); needs
 // width % 128 == 0 and the cluster form (returns 0 without launching when it cannot be taken).  SK_NO_CLUSTER: never
-// reduce the K splits inside a thread-block cluster (the default is to do so where the shape allows: the result is
-// then always finished bf16 in `c` and the return value is 1).
+// reduce the K splits inside a thread-block cluster (done where the shape allows when cluster_splitk_enabled(): the
+// result is then always finished bf16 in `c` and the return value is 1).
 enum SkinnyFlags : int { SK_SWIGLU = 1, SK_NO_CLUSTER = 2 };
 int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                      long long ldw, long long ldc, int act, const GemmWorkspace& ws, int sm_limit,
                      int splits_request, bool finalize, cudaStream_t stream, const SkinnyFused* fused = nullptr,
                      int flags = 0);
-// Split-K inside clusters on / off for the whole process (initially on unless FC_CLUSTER_SPLITK=0).
+// Split-K inside clusters on / off for the whole process (initially off unless FC_CLUSTER_SPLITK=1: it measured
+// slower than partial sums through L2, see gemm_skinny.cu).
 void set_cluster_splitk(bool on);
 bool cluster_splitk_enabled();
 

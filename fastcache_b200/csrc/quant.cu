@@ -82,7 +82,7 @@ __device__ __forceinline__ int encode(float x, float a, float z) {
 template <int MODE>
 __device__ __forceinline__ float decode(int q, float a, float z) {
   if (MODE == QUANT_INT8) return float(q) * a;
-  if (MODE == QUANT_INT8_ASYM) return float(q) * a + z;
+  if (MODE == QUANT_INT8_ASYM) return __fadd_rn(__fmul_rn(float(q), a), z);   // two roundings, like the tensor ops
   if (MODE == QUANT_INT4) return __fdiv_rn(float(q) - 8.0f, 7.0f) * a;
   if (MODE == QUANT_NF4) return c_nf4[q] * a;
   const __nv_fp8_interpretation_t kind = (MODE == QUANT_FP8_E4M3) ? __NV_E4M3 : __NV_E5M2;

@@ -1,5 +1,6 @@
 """Decode-size GEMMs whose K splits reduce inside a thread-block cluster (distributed shared memory), against
-fp32 PyTorch, and against the form that leaves fp32 partial sums for a consumer kernel."""
+fp32 PyTorch, and against the form that leaves fp32 partial sums for a consumer kernel.  The cluster form is
+opt-in (it measured slower); these tests keep it covered."""
 import pytest
 import torch
 
