@@ -390,16 +390,24 @@ def run_serving(args):
     for p in comp.parameters():
         torch.nn.init.normal_(p, std=0.02)
     green = {}
-    if w["greenctx"] is not None:
-        main_sms, comp_sms = w["greenctx"]
+    split = w["greenctx"] if args.greenctx == "config" else \
+        ((112, 36) if args.greenctx == "on" else None)
+    if split is not None:
+        main_sms, comp_sms = split
         green = dict(greenctx_enabled=True, greenctx_main_ratio=main_sms / 148.0,
-                     greenctx_compress_ratio=comp_sms / 148.0)
+                     greenctx_compress_ratio=comp_sms / 148.0, greenctx_main_stream=args.greenctx_main)
+    rate = 1e9 if args.closed_loop else w["rate"]          # closed loop: every request is there at the start
+    if args.pipeline == "auto":
+        args.pipeline = "async" if split is not None else "prefill"
+    pipeline_kw = dict(compression_pipeline=args.pipeline)
+    if args.pipeline == "async":
+        pipeline_kw = dict(compression_pipeline="prefill", async_compression=True)
     n_req = args.requests or w["requests"]
     llm = LLM(dict(hf), tensor_parallel_size=world, device=f"cuda:{local_rank}", kvcache_block_size=64,
               max_model_len=2048, max_num_seqs=max(n_req, 8), max_num_batched_tokens=16384,
               gpu_memory_utilization=min(args.mem_util, 0.6), enable_compression=not args.no_compression,
               compression_backend="mlp", compressor=comp.eval(), compression_factor=4,
-              compression_pipeline="prefill", seed=0, prefix_caching=False, **green)
+              seed=0, prefix_caching=False, **pipeline_kw, **green)
     runner = llm.model_runner
     vocab = text_cfg["vocab_size"]
     g = torch.Generator().manual_seed(3)
@@ -438,7 +446,7 @@ def run_serving(args):
     results = []
     for job in range(args.steps):
         prompts, images = make_job(n_req, 1 + job)
-        tester = ConcurrentTester(llm, batching=w["batching"], req_per_sec=w["rate"], poisson=True, seed=job)
+        tester = ConcurrentTester(llm, batching=w["batching"], req_per_sec=rate, poisson=not args.closed_loop, seed=job)
         results.append(tester.run(prompts, max_tokens=w["out"], images=images, agree=agree))
     barrier(world)
     wall_ms = (time.perf_counter() - t0) * 1e3
@@ -458,10 +466,12 @@ def run_serving(args):
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random images and token ids, random-init weights and compressor",
             "config": {"model": w["label"], "global_batch": n_req, "seq_len": None, "text_tokens": w["text"],
-                       "image": f"{W}x{H}", "output_len": w["out"], "arrivals": f"Poisson {w['rate']} req/s",
+                       "image": f"{W}x{H}", "output_len": w["out"],
+                       "arrivals": "closed loop (all at once)" if args.closed_loop else f"Poisson {w['rate']} req/s",
+                       "pipeline": args.pipeline,
                        "batching": list(w["batching"]), "parallelism": f"tp{world}",
                        "compression": "CCM merge, ratio 4 (" + w["compressor"] + ")" if not args.no_compression else "none",
-                       "greenctx_sms": list(w["greenctx"]) if w["greenctx"] else None,
+                       "greenctx_sms": list(split) if split else None,
                        "greenctx_active": bool(runner.greenctx_enabled),
                        "greenctx_sms_actual": [runner._greenctx_info.get("main_sms"),
                                                runner._greenctx_info.get("compress_sms")]
@@ -546,6 +556,15 @@ def main():
     ap.add_argument("--no-compression", action="store_true")
     ap.add_argument("--mem-util", type=float, default=0.85)
     ap.add_argument("--kv-blocks", type=int, default=0, help="size of the paged pool in blocks (0 = from free memory)")
+    # serving configs only
+    ap.add_argument("--greenctx", default="config", choices=["config", "on", "off"],
+                    help="SM split between decode and compression: as the config says, 112 / 36, or none (priority streams)")
+    ap.add_argument("--greenctx-main", action="store_true", help="run the main stream on its green context too")
+    ap.add_argument("--closed-loop", action="store_true", help="all requests at once instead of Poisson arrivals")
+    ap.add_argument("--pipeline", default="auto", choices=["auto", "prefill", "async", "decode"],
+                    help="compression right after prefill on the main stream, on a compression stream, or a few "
+                         "layers per decode step beside decode; auto: a compression stream when the SMs are split "
+                         "(measured best: the split only pays when compression runs beside the main stream), else prefill")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.steps = max(1, args.steps)
