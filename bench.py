@@ -509,11 +509,26 @@ def run_reference(args):
             unavailable("reference is not installed under baseline/_ref")
         sys.exit(0)
     if args.config in SERVING:
-        if rank == 0:
-            unavailable("the reference's multimodal engines fail at model construction under the installed "
-                        "transformers (LLaVA and MiniCPM classes pass the rope dict into an lru_cache) and its "
-                        "HuggingFace harness needs real checkpoints: no reference run of the image configs")
-        sys.exit(0)
+        if not args.config.startswith("llava") or world > 1:
+            if rank == 0:
+                unavailable("no reference run of this image config: the reference's MiniCPM engine borrows its "
+                            "vision modules from a HuggingFace remote-code checkpoint (nanovllm/models/minicpm.py:"
+                            "329-340), which random weights cannot stand in for, and its LLaVA attention hard-codes "
+                            "tp_size = 1 (nanovllm/models/llava.py:220), so only --config llava-1.5-7b on one GPU has one")
+            sys.exit(0)
+        if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref_p", "nanovllm", "engine")):
+            unavailable("the reference's pipeline copy is not present under baseline/_ref_p")
+        from baseline.reference_arm import run_llava
+        try:
+            line = run_llava(args, SERVING[args.config], ClockSampler, percentile)
+        except SystemExit:
+            raise
+        except Exception as exc:
+            import traceback
+            traceback.print_exc()
+            unavailable(f"reference failed: {type(exc).__name__}: {str(exc)[:200]}")
+        emit(line)
+        return
     if world > 1:
         family = WORKLOADS[args.config][0].get("model_type")
         if family != "llama":

@@ -310,7 +310,8 @@ class LLMEngine:
         return freed
 
     def _eligible(self, seq: Sequence) -> bool:
-        return (seq.compression_state is CompressionState.NONE and not seq.is_finished
+        # NONE: never considered; PENDING: waiting in the scheduler's compress queue for its turn
+        return (seq.compression_state in (CompressionState.NONE, CompressionState.PENDING) and not seq.is_finished
                 and seq.rows_in_pool >= max(2 * self.compression_factor, 4))
 
     def _compress_now(self, seqs: List[Sequence]) -> None:
@@ -587,14 +588,26 @@ class LLMEngine:
                 if s.first_token_time is None:
                     s.first_token_time = now
             if compress and mode in ("eager", "async") and pipeline != "none":
-                if pipeline == "decode":
-                    self._start_chunked(whole)
-                elif use_async or mode == "async":
-                    self._launch_async(whole)
-                else:
-                    self._compress_now(whole)
+                # the third queue: requests that finished prefill wait here for a compression batch
+                sch.enqueue_compress([s for s in whole if self._eligible(s)])
         else:
             n_tok = -len(seqs)
+        if compress and mode in ("eager", "async") and pipeline != "none" and sch.compress_queue:
+            # one compression batch per engine step, at most `compress_batch_size` requests (the middle number of
+            # the harness' [prefill, compress, decode] caps); the rest keep their place in the queue and may
+            # decode uncompressed meanwhile
+            batch = [s for s in sch.schedule_compress() if self._eligible(s)]
+            try:
+                if pipeline == "decode":
+                    self._start_chunked(batch)
+                elif use_async or mode == "async":
+                    self._launch_async(batch)
+                else:
+                    self._compress_now(batch)
+            finally:
+                for s in batch:                          # not taken after all, or the compressor raised
+                    if s.compression_state is CompressionState.PENDING:
+                        s.compression_state = CompressionState.NONE
         finished = sch.postprocess(seqs, tokens)
         for s in finished:
             s.finish_time = now

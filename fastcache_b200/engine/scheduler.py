@@ -14,10 +14,12 @@ Parity
     nearly full" (nanovllm_fastapi_server.py:98-145)
 
 The compress queue is explicit here: a request that finished prefill and is
-eligible for compression is parked in `compress_queue` until the engine asks
-for a compression batch (`schedule_compress`).  It can decode meanwhile — the
-runner orders the pool accesses — so the queue is a work list, not a state
-that blocks the request.
+eligible for compression is parked in `compress_queue` (`enqueue_compress`,
+called by the engine after every prefill step) until the engine takes a
+compression batch of at most `compress_batch_size` requests
+(`schedule_compress`, once per engine step).  A queued request can decode
+meanwhile — the runner orders the pool accesses — so the queue is a work
+list, not a state that blocks the request.
 """
 from __future__ import annotations
 

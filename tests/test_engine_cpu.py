@@ -99,3 +99,25 @@ def test_exit_releases_the_engine_and_a_second_one_runs():
     assert pool() is None and engine() is None
     again = _engine(True, True).generate(_prompts(2, 40), sp)
     assert [o["token_ids"] for o in again] == [o["token_ids"] for o in first]
+
+
+def test_compress_queue_meters_compression_by_the_compress_cap():
+    """The three-queue batching of the harness ([prefill, compress, decode] caps): requests that finished prefill
+    wait in the scheduler's compress queue and at most `compress_batch_size` of them are compressed per engine
+    step; the others decode uncompressed until their turn."""
+    from fastcache_b200.engine.sequence import CompressionState
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = _engine(True, True, compress_batch_size=1)
+    seqs = [llm.add_request(p, sp) for p in _prompts(3)]
+    llm.step()                                             # one prefill step for all three, one compression
+    assert [s.is_compressed for s in seqs] == [True, False, False]
+    assert list(llm.scheduler.compress_queue) == seqs[1:]
+    assert all(s.compression_state is CompressionState.PENDING for s in seqs[1:])
+    llm.step()                                             # a decode step for all three, the second compression
+    assert [s.is_compressed for s in seqs] == [True, True, False]
+    llm.step()
+    assert all(s.is_compressed for s in seqs) and not llm.scheduler.compress_queue
+    while not llm.is_finished():
+        llm.step()
+    assert llm.stats.compressions == 3
+    llm.scheduler.block_manager.check_invariants([])
