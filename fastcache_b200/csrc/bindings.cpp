@@ -555,6 +555,7 @@ void register_stream_sms(int64_t stream_ptr, int64_t sms) {
 void register_greenctx(pybind11::module_& m);
 void register_compress(pybind11::module_& m);
 void register_comm(pybind11::module_& m);
+void register_symm(pybind11::module_& m);
 
 namespace fc {
 const StreamWorkspace& stream_workspace(int device, cudaStream_t stream) { return workspace(device, stream).raw; }
@@ -609,4 +610,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_greenctx(m);
   register_compress(m);
   register_comm(m);
+  register_symm(m);
 }

@@ -1,8 +1,8 @@
 """Symmetric-memory staging buffers and the fused communication paths.
 
-Each rank allocates its buffers in symmetric memory (`torch.distributed._symmetric_memory`:
-CUDA VMM allocations whose peer mappings and NVSwitch multicast address are exchanged over the
-process group once).  The kernels in csrc/comm.cu and csrc/gemm_tp.cu then read and write the
+Each rank allocates its buffers in symmetric memory: CUDA virtual-memory allocations whose peer
+mappings and NVSwitch multicast address are exchanged once at start-up, by this package's own
+runtime (`symm_native.py` + csrc/symm.cpp) or, as a fallback, `torch.distributed._symmetric_memory`.  The kernels in csrc/comm.cu and csrc/gemm_tp.cu then read and write the
 peers' buffers directly over NVLink; NCCL is left with bootstrap, small control messages and the
 library baseline.
 
@@ -31,13 +31,13 @@ from . import fused as fused_mod
 from . import tp as tpmod
 
 MAX_SLOTS = 512
+DEFAULT_RUNTIME = "torch"       # "native": this package's own allocator and handle exchange (FC_SYMM overrides)
 MAX_WORLD = 8
 
 
 class FusedComm:
     def __init__(self, one_shot_tokens: int, hidden: int, device: torch.device, max_tokens: int = 0,
                  use_multimem: Optional[bool] = None):
-        import torch.distributed._symmetric_memory as symm_mem
         if not tpmod.is_tp_initialized():
             raise RuntimeError("tensor parallelism is not initialised")
         self.world, self.rank = tpmod.get_tp_size(), tpmod.get_tp_rank()
@@ -50,46 +50,65 @@ class FusedComm:
         index = device.index if device.index is not None else torch.cuda.current_device()
         bf16 = torch.bfloat16
 
-        # ---- one-shot all-reduce + add + norm (decode)
-        self.bufs = [symm_mem.empty((one_shot_tokens, hidden), dtype=bf16, device=device) for _ in range(2)]
-        self.flags = symm_mem.empty((MAX_SLOTS * MAX_WORLD,), dtype=torch.int32, device=device)
-        self.flags.zero_()
-        self.handles = [symm_mem.rendezvous(b, name) for b in self.bufs]
-        self.flag_handle = symm_mem.rendezvous(self.flags, name)
-        mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.handles]
-        if use_multimem is None:
-            use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
-        self.has_multicast = all(mc)
-        self.use_multimem = bool(use_multimem and self.has_multicast)
-        ext().comm_init(self.rank, self.world, [int(p) for p in self.handles[0].buffer_ptrs],
-                        [int(p) for p in self.handles[1].buffer_ptrs],
-                        [int(p) for p in self.flag_handle.buffer_ptrs], mc[0], mc[1], index)
-        self.status = ext().status_tensor(index)
-        self.cur = 0
-        # candidate tables of the sampler over vocabulary shards
-        self.cells = symm_mem.empty((ext().sample_cells_per_rank(),), dtype=torch.int64, device=device)
-        self.cells.zero_()
-        self.cell_handle = symm_mem.rendezvous(self.cells, name)
-        ext().sample_exchange_init([int(p) for p in self.cell_handle.buffer_ptrs])
-
-        # ---- GEMM + reduce-scatter + add + norm / all-gather + GEMM (prefill)
+        # ---- the symmetric buffers: one-shot all-reduce staging (two, used in alternation) and flags, the sampler's
+        # candidate tables, and for prefill sizes the reduce-scatter staging, the gathered activations and their flags
         self.max_tokens = 0
         self.epoch = 0
         self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
+        shapes = [((one_shot_tokens, hidden), bf16), ((one_shot_tokens, hidden), bf16),
+                  ((MAX_SLOTS * MAX_WORLD,), torch.int32), ((ext().sample_cells_per_rank(),), torch.int64)]
         if max_tokens > one_shot_tokens:
             per_rank = -(-max_tokens // self.world)
             self.chunk_max = -(-per_rank // 128) * 128
             self.max_tokens = max_tokens
-            self.stage = symm_mem.empty((self.world * self.chunk_max, hidden), dtype=bf16, device=device)
-            self.xg = symm_mem.empty((self.chunk_max * self.world, hidden), dtype=bf16, device=device)
-            self.tp_flags = symm_mem.empty((2 * MAX_WORLD,), dtype=torch.int32, device=device)
-            self.tp_flags.zero_()
-            hs, hx, hf = (symm_mem.rendezvous(t, name) for t in (self.stage, self.xg, self.tp_flags))
-            self._tp_handles = (hs, hx, hf)
-            ext().tp_init(self.rank, self.world, [int(p) for p in hs.buffer_ptrs], [int(p) for p in hx.buffer_ptrs],
-                          [int(p) for p in hf.buffer_ptrs], self.chunk_max, self.chunk_max * self.world, hidden, index)
+            shapes += [((self.world * self.chunk_max, hidden), bf16), ((self.chunk_max * self.world, hidden), bf16),
+                       ((2 * MAX_WORLD,), torch.int32)]
+        tensors, ptrs, mc = self._symmetric(shapes, device, group, name)
+        self.bufs, self.flags, self.cells = tensors[:2], tensors[2], tensors[3]
+        if use_multimem is None:
+            use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
+        self.has_multicast = bool(mc[0] and mc[1])
+        self.use_multimem = bool(use_multimem and self.has_multicast)
+        ext().comm_init(self.rank, self.world, ptrs[0], ptrs[1], ptrs[2], mc[0], mc[1], index)
+        ext().sample_exchange_init(ptrs[3])
+        self.status = ext().status_tensor(index)
+        self.cur = 0
+        if self.max_tokens:
+            self.stage, self.xg, self.tp_flags = tensors[4], tensors[5], tensors[6]
+            ext().tp_init(self.rank, self.world, ptrs[4], ptrs[5], ptrs[6], self.chunk_max,
+                          self.chunk_max * self.world, hidden, index)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
+
+    def _symmetric(self, shapes, device, group, group_name):
+        """Zeroed symmetric buffers: (this rank's tensors, per buffer the address on every rank, per buffer the
+        multicast address or 0).  This package's own runtime (CUDA virtual memory + file descriptors over Unix
+        sockets, `parallel/symm_native.py`) unless FC_SYMM=torch or it cannot be brought up; then
+        `torch.distributed._symmetric_memory`."""
+        self.runtime = "native"
+        self._segment = None
+        if os.environ.get("FC_SYMM", DEFAULT_RUNTIME) != "torch":
+            try:
+                from . import symm_native
+                seg = symm_native.rendezvous_buffers(shapes, device, group)
+                self._segment = seg
+                return ([b.tensor for b in seg.buffers], [list(b.buffer_ptrs) for b in seg.buffers],
+                        [int(b.multicast_ptr) for b in seg.buffers])
+            except RuntimeError as exc:          # raised on every rank together
+                print(f"[fastcache_b200] own symmetric-memory runtime unavailable ({exc}); using torch's")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.runtime = "torch"
+        tensors, ptrs, mc = [], [], []
+        for shape, dtype in shapes:
+            t = symm_mem.empty(tuple(shape), dtype=dtype, device=device)
+            t.zero_()
+            tensors.append(t)
+        torch.cuda.synchronize(device)
+        self._handles = [symm_mem.rendezvous(t, group_name) for t in tensors]
+        for h in self._handles:
+            ptrs.append([int(p) for p in h.buffer_ptrs])
+            mc.append(int(getattr(h, "multicast_ptr", 0) or 0))
+        return tensors, ptrs, mc
 
     # ------------------------------------------------------------------ forward hooks
     def begin_forward(self) -> None:
@@ -171,6 +190,12 @@ class FusedComm:
 
     def close(self) -> None:
         ext().comm_shutdown()
+        seg, self._segment = getattr(self, "_segment", None), None
+        if seg is not None:
+            torch.cuda.synchronize(self.device)
+            self.bufs, self.flags, self.cells = [], None, None
+            self.stage = self.xg = self.tp_flags = None
+            seg.close()
 
 
 def enable(one_shot_tokens: int, hidden: int, device: torch.device, **kw) -> FusedComm:
