@@ -74,36 +74,46 @@ def _tensor_at(address: int, shape: Sequence[int], dtype: torch.dtype, device: t
     return flat.view(dtype).view(*shape)
 
 
+_SOCKET_TIMEOUT_S = 60.0
+
+
 def _exchange_fds(my_fd: int, rank: int, world: int, group) -> List[int]:
-    """Every rank receives every rank's descriptor (its own is returned as given)."""
+    """Every rank receives every rank's descriptor (its own is returned as given).  Each rank listens on a
+    Unix socket, sends its descriptor to every peer (a connect succeeds as soon as the peer listens, the message
+    fits the socket buffer) and then accepts world - 1 connections; the first byte of a message names its sender.
+    All socket calls have a time limit, so a peer that never shows up is an error, not a hang."""
     tmp = tempfile.mkdtemp(prefix=f"fc_symm_{os.getpid()}_")
     path = os.path.join(tmp, "fd.sock")
     srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.settimeout(_SOCKET_TIMEOUT_S)
     srv.bind(path)
     srv.listen(world)
     paths: List[Optional[str]] = [None] * world
     dist.all_gather_object(paths, path, group=group)
     fds = [-1] * world
     fds[rank] = my_fd
-    # round r: rank i sends to (i + r) % world and receives from (i - r) % world; a connect finds the listener up
-    for r in range(1, world):
-        dst, src = (rank + r) % world, (rank - r) % world
-        out = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
-        out.connect(paths[dst])
-        socket.send_fds(out, [bytes([rank])], [my_fd])
-        conn, _ = srv.accept()
-        msg, got, _, _ = socket.recv_fds(conn, 16, 1)
-        sender = msg[0] if msg else src
-        fds[sender] = got[0]
-        conn.close()
-        out.close()
-        dist.barrier(group=group)
-    srv.close()
     try:
-        os.unlink(path)
-        os.rmdir(tmp)
-    except OSError:
-        pass
+        for r in range(1, world):
+            out = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            out.settimeout(_SOCKET_TIMEOUT_S)
+            out.connect(paths[(rank + r) % world])
+            socket.send_fds(out, [bytes([rank])], [my_fd])
+            out.close()
+        for _ in range(world - 1):
+            conn, _ = srv.accept()
+            conn.settimeout(_SOCKET_TIMEOUT_S)
+            msg, got, _, _ = socket.recv_fds(conn, 16, 1)
+            conn.close()
+            if not msg or not got:
+                raise RuntimeError("a peer closed its socket without sending a descriptor")
+            fds[msg[0]] = got[0]
+    finally:
+        srv.close()
+        try:
+            os.unlink(path)
+            os.rmdir(tmp)
+        except OSError:
+            pass
     return fds
 
 
@@ -135,11 +145,21 @@ def rendezvous_buffers(shapes: Sequence[Tuple[Sequence[int], torch.dtype]], devi
     dist.all_gather_object(errs, err, group=group)
     if any(errs):
         raise RuntimeError("symmetric-memory runtime unavailable: " + "; ".join(x for x in errs if x))
-    all_fds = _exchange_fds(fd, rank, world, group)
-    peer_vas = [local_va if r == rank else int(e.symm_import(all_fds[r], size, index)) for r in range(world)]
-    for r, f in enumerate(all_fds):
-        if r != rank:
-            e.symm_close_fd(f)
+    peer_vas: List[int] = []
+    try:
+        all_fds = _exchange_fds(fd, rank, world, group)
+        peer_vas = [local_va if r == rank else int(e.symm_import(all_fds[r], size, index)) for r in range(world)]
+        for r, f in enumerate(all_fds):
+            if r != rank:
+                e.symm_close_fd(f)
+    except Exception as exc:                                  # noqa: BLE001 - reported to every rank below
+        err = f"rank {rank}: {type(exc).__name__}: {exc}"
+    dist.all_gather_object(errs, err, group=group)
+    if any(errs):
+        for va in set(peer_vas) | {int(local_va)}:
+            e.symm_free(va)
+        e.symm_close_fd(fd)
+        raise RuntimeError("symmetric-memory runtime unavailable: " + "; ".join(x for x in errs if x))
     seg = SymmSegment(size=size, local_va=int(local_va), peer_vas=peer_vas)
     # ---- multicast (NVLS): rank 0 creates the object, every rank adds its device, then binds its memory.  After
     # every step the ranks agree on whether all of them succeeded, so that none waits at a barrier for a rank that
@@ -159,6 +179,8 @@ def rendezvous_buffers(shapes: Sequence[Tuple[Sequence[int], torch.dtype]], devi
         if all_ok(problem):
             got_fd = _exchange_fds_from_root(mc_fd, rank, world, group)
             try:
+                if got_fd < 0:
+                    raise RuntimeError("the multicast descriptor did not arrive")
                 if rank != 0:
                     mc_handle = int(e.multicast_import(got_fd))
                 e.multicast_add_device(mc_handle, index)
@@ -183,36 +205,44 @@ def rendezvous_buffers(shapes: Sequence[Tuple[Sequence[int], torch.dtype]], devi
 
 
 def _exchange_fds_from_root(fd: int, rank: int, world: int, group) -> int:
-    """Rank 0's descriptor to every other rank; returns the received descriptor (rank 0: its own)."""
+    """Rank 0's descriptor to every other rank; returns the received descriptor (rank 0: its own), -1 when the
+    exchange failed on this rank (the caller's next agreement step tells the others)."""
     tmp = tempfile.mkdtemp(prefix=f"fc_symm_mc_{os.getpid()}_")
     path = os.path.join(tmp, "fd.sock")
     srv = None
     if rank != 0:
         srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        srv.settimeout(_SOCKET_TIMEOUT_S)
         srv.bind(path)
         srv.listen(1)
     paths: List[Optional[str]] = [None] * world
     dist.all_gather_object(paths, path, group=group)
     got = fd
-    if rank == 0:
-        for r in range(1, world):
-            out = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
-            out.connect(paths[r])
-            socket.send_fds(out, [b"m"], [fd])
-            out.close()
-    else:
-        conn, _ = srv.accept()
-        _, fds, _, _ = socket.recv_fds(conn, 16, 1)
-        got = fds[0]
-        conn.close()
-        srv.close()
+    try:
+        if rank == 0:
+            for r in range(1, world):
+                out = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+                out.settimeout(_SOCKET_TIMEOUT_S)
+                out.connect(paths[r])
+                socket.send_fds(out, [b"m"], [fd])
+                out.close()
+        else:
+            conn, _ = srv.accept()
+            conn.settimeout(_SOCKET_TIMEOUT_S)
+            _, fds, _, _ = socket.recv_fds(conn, 16, 1)
+            conn.close()
+            got = fds[0] if fds else -1
+    except OSError:
+        got = -1
+    finally:
+        if srv is not None:
+            srv.close()
+            try:
+                os.unlink(path)
+            except OSError:
+                pass
         try:
-            os.unlink(path)
+            os.rmdir(tmp)
         except OSError:
             pass
-    try:
-        os.rmdir(tmp)
-    except OSError:
-        pass
-    dist.barrier(group=group)
     return got
