@@ -31,10 +31,17 @@ KV = List[Tuple[torch.Tensor, torch.Tensor]]
 
 def batched_linear_relu(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], relu: bool = True
                         ) -> torch.Tensor:
-    """Y[l] = act(X[l] @ W[l].T + B[l]) for stacked layers: x [L, M, K], w [L, N, K], b [L, N]."""
-    outs = [ops.linear(x[l], w[l], None if b is None else b[l], "relu" if relu else "none")
-            for l in range(x.shape[0])]
-    return torch.stack(outs)
+    """Y[l] = act(X[l] @ W[l].T + B[l]) for stacked layers: x [L, M, K], w [L, N, K], b [L, N].
+
+    One batched matrix product for all layers (the reference's own fallback form of this op,
+    "kv-cache pipeline"/nanovllm/kernels/batched_compress.py:347-358: `torch.bmm` over the stacked layers, one
+    launch instead of L).  The engine does not come through here: its merge compression is the fused in-pool kernel
+    (csrc/ccm.cu), which also does the gather and the scatter; this front end serves callers that hold
+    HuggingFace-format tensors."""
+    y = torch.bmm(x, w.transpose(1, 2))
+    if b is not None:
+        y = y + b[:, None, :].to(y.dtype)
+    return torch.relu(y) if relu else y
 
 
 def fused_linear_relu_dropout(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], p: float = 0.0,

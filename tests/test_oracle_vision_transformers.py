@@ -71,3 +71,60 @@ def test_siglip_tower_matches_transformers_on_a_full_grid():
         got, mask = tower(pixels, torch.tensor([[4, 4], [4, 4]]))
     assert bool(mask.all())
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+
+
+def test_minicpm_resampler_matches_its_published_statement():
+    """The perceiver resampler of MiniCPM-V-2.6 stated with torch's own modules the way the model's published
+    code does it (the reference borrows that code at load time, nanovllm/models/minicpm.py:329-340; it is not
+    shipped with `transformers`): kv_proj -> LayerNorm, learned queries -> LayerNorm, nn.MultiheadAttention with the
+    2-D sin-cos position table (w coordinate in the first half of the channels) added to the keys only and a key
+    padding mask for ragged grids, LayerNorm, then `x @ proj`."""
+    import numpy as np
+    from torch import nn
+    from fastcache_b200.models.vision import Resampler, sincos_2d
+    torch.manual_seed(2)
+    E, KV, Q, H = 64, 48, 8, 4
+    ours = Resampler(Q, E, KV, num_heads=H, max_size=(10, 10)).float()
+    for p in ours.parameters():
+        torch.nn.init.normal_(p, std=0.2)
+
+    # ---- the published statement
+    def pos_1d(dim, pos):                                     # MAE-style table
+        omega = 1.0 / 10000 ** (np.arange(dim // 2, dtype=np.float32) / (dim / 2))
+        out = np.einsum("hw,d->hwd", pos, omega)
+        return np.concatenate([np.sin(out), np.cos(out)], axis=-1)
+
+    def pos_2d(dim, h, w):
+        grid = np.meshgrid(np.arange(w, dtype=np.float32), np.arange(h, dtype=np.float32))   # w goes first
+        return np.concatenate([pos_1d(dim // 2, grid[0]), pos_1d(dim // 2, grid[1])], axis=-1)
+
+    table = torch.from_numpy(pos_2d(E, 10, 10)).float()
+    torch.testing.assert_close(sincos_2d(E, 10, 10), table, rtol=1e-5, atol=1e-5)
+    attn = nn.MultiheadAttention(E, H)
+    kv_proj = nn.Linear(KV, E, bias=False)
+    ln_q, ln_kv, ln_post = (nn.LayerNorm(E, eps=1e-6) for _ in range(3))
+    with torch.no_grad():
+        attn.in_proj_weight.copy_(ours.attn.in_proj_weight)
+        attn.in_proj_bias.copy_(ours.attn.in_proj_bias)
+        attn.out_proj.weight.copy_(ours.attn.out_proj.weight)
+        attn.out_proj.bias.copy_(ours.attn.out_proj.bias)
+        kv_proj.weight.copy_(ours.kv_proj.weight)
+        for theirs, mine in ((ln_q, ours.ln_q), (ln_kv, ours.ln_kv), (ln_post, ours.ln_post)):
+            theirs.weight.copy_(mine.weight)
+            theirs.bias.copy_(mine.bias)
+    tgt = torch.tensor([[3, 4], [2, 5], [4, 4]])
+    counts = (tgt[:, 0] * tgt[:, 1]).tolist()
+    L = max(counts)
+    x = torch.randn(3, L, KV)
+    pos = torch.zeros(3, L, E)
+    pad = torch.zeros(3, L, dtype=torch.bool)
+    for b, (h, w) in enumerate(tgt.tolist()):
+        pos[b, : h * w] = table[:h, :w].reshape(h * w, E)
+        pad[b, h * w:] = True
+    with torch.no_grad():
+        kv = ln_kv(kv_proj(x)).permute(1, 0, 2)                                    # L B E
+        q = ln_q(ours.query)[:, None, :].expand(-1, 3, -1)
+        out = attn(q, kv + pos.permute(1, 0, 2), kv, key_padding_mask=pad)[0].permute(1, 0, 2)
+        want = ln_post(out) @ ours.proj
+        got = ours(x, tgt, key_mask=~pad)
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
