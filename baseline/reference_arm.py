@@ -315,9 +315,12 @@ def run_llava(args, w, ClockSampler, percentile):
         del comp
     n_req = args.requests or w["requests"]
     compress = not args.no_compression
+    # the reference captures decode graphs for batch sizes 1, 2, 4, 8, 16, 32, ... up to max_num_seqs in steps of 16
+    # and has no bucket for a batch above the last multiple of 16 (llava_model_runner.py:1353-1415, :782): give it a
+    # multiple of 16
     llm = LlavaLLM(ckpt, compressor_path=pth, compression_factor=4, enable_compression=compress,
                    async_compression=False, compression_backend="mlp", max_model_len=2048,
-                   max_num_seqs=max(n_req, 8), max_num_batched_tokens=16384, kvcache_block_size=256,
+                   max_num_seqs=-(-max(n_req, 8) // 16) * 16, max_num_batched_tokens=16384, kvcache_block_size=256,
                    gpu_memory_utilization=min(args.mem_util, 0.6), enforce_eager=False)
     sp = SamplingParams(temperature=0.6, max_tokens=w["out"], ignore_eos=True)
     vocab = 30000

@@ -1,7 +1,7 @@
 """Device-timed micro-benchmarks of the hot kernels against the measured roofline.
 
 Usage:  python benchmarks/kernel_bench.py [--what gemm,decode_gemm,decode_attn,prefill_attn,norm,elementwise,
-                                            dense_attn,vit_gemm,ccm,evict] [--small] [--json out.json]
+                                            dense_attn,vit_gemm,ccm,evict,quant] [--small] [--json out.json]
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, an L2 flush
 (write of a 256 MB buffer) before every timed iteration, median of the samples.
 Peaks come from MEASURED_PEAKS.json at the repository root when present
@@ -159,6 +159,27 @@ def bench_elementwise(rows):
     _bw_row(rows, "sample", ms, 2.0 * logits.numel(), {"B": 128, "V": 151936})
 
 
+def bench_quant(rows, small=False):
+    """KV quantisers on the K rows of one layer of the headline decode batch (128 requests x 2304 rows x 8 heads x
+    128): codes + scales out, restore, and the one-pass round trip, beside the PyTorch statement on the device."""
+    from fastcache_b200.compress import quant
+    n = (16 if small else 128) * 2304 * 8
+    x = torch.randn(n, 128, device="cuda", dtype=torch.bfloat16)
+    for mode, out_bytes in (("int8", 1.0), ("int4", 0.5), ("nf4", 0.5), ("fp8_e4m3", 1.0)):
+        ms = timeit(lambda: quant.quantize(x, mode, 128))
+        _bw_row(rows, f"quantize_{mode}", ms, x.numel() * (2.0 + out_bytes) + 4.0 * n, {"rows": n, "D": 128})
+        packed = quant.quantize(x, mode, 128)
+        ms = timeit(lambda: quant.dequantize(packed))
+        _bw_row(rows, f"dequantize_{mode}", ms, x.numel() * (2.0 + out_bytes) + 4.0 * n, {"rows": n, "D": 128})
+    ms = timeit(lambda: quant.fake_quantize(x, 4, 128))
+    _bw_row(rows, "fake_quantize_int4", ms, x.numel() * 4.0, {"rows": n, "D": 128})
+    xf = x.float()
+    ms = timeit(lambda: (torch.round(xf / (xf.abs().amax(-1, keepdim=True).clamp_min(1e-8) / 127.0))
+                         .clamp(-127, 127).to(torch.int8)), iters=5)
+    rows.append({"kernel": "quantize_int8 (PyTorch statement on the device, fp32 input)", "ms": round(ms, 4)})
+    print(rows[-1], flush=True)
+
+
 def bench_dense_attn(rows):
     """Vision-tower attention (CLIP 577 x 16 x 64, SigLIP 1024 x 16 x 72) beside torch's fused attention."""
     _, tf, src = peaks()
@@ -272,6 +293,8 @@ def main():
         bench_norm(rows)
     if "elementwise" in what:
         bench_elementwise(rows)
+    if "quant" in what:
+        bench_quant(rows, a.small)
     if "dense_attn" in what:
         bench_dense_attn(rows)
     if "vit_gemm" in what:
