@@ -400,7 +400,7 @@ def run_serving(args):
     rate = 1e9 if args.closed_loop else w["rate"]          # closed loop: every request is there at the start
     if args.pipeline == "auto":
         args.pipeline = "async" if split is not None else "prefill"
-    pipeline_kw = dict(compression_pipeline=args.pipeline)
+    pipeline_kw = dict(compression_pipeline=args.pipeline, decode_overlap=args.decode_overlap)
     if args.pipeline == "async":
         pipeline_kw = dict(compression_pipeline="prefill", async_compression=True)
     n_req = args.requests or w["requests"]
@@ -577,6 +577,9 @@ def main():
                     help="SM split between decode and compression: as the config says, 112 / 36, or none (priority streams)")
     ap.add_argument("--greenctx-main", action="store_true", help="run the main stream on its green context too")
     ap.add_argument("--closed-loop", action="store_true", help="all requests at once instead of Poisson arrivals")
+    ap.add_argument("--decode-overlap", default="shadow", choices=["shadow", "hold"],
+                    help="decode pipeline: compress into shadow blocks while the request keeps decoding, or in place "
+                         "with the request held out of the decode batches")
     ap.add_argument("--pipeline", default="auto", choices=["auto", "prefill", "async", "decode"],
                     help="compression right after prefill on the main stream, on a compression stream, or a few "
                          "layers per decode step beside decode; auto: a compression stream when the SMs are split "
