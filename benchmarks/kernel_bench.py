@@ -1,7 +1,7 @@
 """Device-timed micro-benchmarks of the hot kernels against the measured roofline.
 
 Usage:  python benchmarks/kernel_bench.py [--what gemm,decode_gemm,decode_attn,prefill_attn,norm,elementwise,
-                                            dense_attn,vit_gemm,ccm,evict,quant] [--small] [--json out.json]
+                                            dense_attn,vit_gemm,ccm,evict,quant,swiglu_gemm] [--small] [--json out.json]
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, an L2 flush
 (write of a 256 MB buffer) before every timed iteration, median of the samples.
 Peaks come from MEASURED_PEAKS.json at the repository root when present
@@ -65,6 +65,47 @@ def bench_gemm(rows, shapes, tag):
                      "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
                      "frac_of_roofline": round(t_roof / ms, 3), "peaks": src})
         print(rows[-1], flush=True)
+
+
+def bench_swiglu_gemm(rows):
+    """Decode-size gate/up projection + SwiGLU: the persistent stream-K kernel (one launch), the split-K GEMM with
+    the consumer kernel that sums its partial sums (two launches), and cuBLAS + an elementwise kernel; then the
+    LM head with and without stream-K."""
+    hbm, tf, src = peaks()
+    e = ops.ext()
+    before = e.streamk_mode()
+    for M, I, K in [(128, 12288, 4096), (128, 3072, 4096), (128, 1536, 4096), (90, 11008, 4096), (16, 12288, 4096)]:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(2 * I, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        t = {}
+        for on in (True, False):
+            e.set_streamk(2 if on else 0)
+            t[on] = timeit(lambda: ops.linear_silu_mul(x, w))
+        def lib():
+            y = torch.nn.functional.linear(x, w)
+            return torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+        ms_lib = timeit(lib)
+        byts = 2.0 * (M * K + 2 * I * K + M * I)
+        rows.append({"kernel": "gate_up_swiglu_decode", "M": M, "I": I, "K": K, "stream_k_ms": round(t[True], 4),
+                     "splitk_plus_consumer_ms": round(t[False], 4), "cublas_plus_elementwise_ms": round(ms_lib, 4),
+                     "gbs": round(byts / t[True] / 1e6, 1), "frac_of_copy_bw": round(byts / t[True] / 1e6 / hbm, 3),
+                     "peaks": src})
+        print(rows[-1], flush=True)
+    for M, N, K in [(128, 151936, 4096), (128, 37984, 4096)]:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        t = {}
+        for on in (True, False):
+            e.set_streamk(2 if on else 0)
+            t[on] = timeit(lambda: ops.linear(x, w))
+        ms_lib = timeit(lambda: torch.nn.functional.linear(x, w))
+        byts = 2.0 * (M * K + N * K + M * N)
+        rows.append({"kernel": "lm_head_decode", "M": M, "N": N, "K": K, "stream_k_ms": round(t[True], 4),
+                     "one_tile_per_cta_ms": round(t[False], 4), "cublas_ms": round(ms_lib, 4),
+                     "gbs": round(byts / t[True] / 1e6, 1), "frac_of_copy_bw": round(byts / t[True] / 1e6 / hbm, 3),
+                     "peaks": src})
+        print(rows[-1], flush=True)
+    e.set_streamk(before)
 
 
 def bench_decode_attn(rows):
@@ -187,11 +228,12 @@ def bench_dense_attn(rows):
         qkv = torch.randn(B, S, 3, H, D, device="cuda", dtype=torch.bfloat16)
         q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
         ms = timeit(lambda: ops.dense_attention(q, k, v, D ** -0.5, None))
+        ms_mma = timeit(lambda: ops.dense_attention(q, k, v, D ** -0.5, None, impl=1))
         qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))
         ms_lib = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt))
         flops = 4.0 * B * H * S * S * D
         rows.append({"kernel": "dense_attn", "B": B, "S": S, "H": H, "D": D, "ms": round(ms, 4),
-                     "torch_sdpa_ms": round(ms_lib, 4), "tflops": round(flops / ms / 1e9, 1),
+                     "mma_sync_kernel_ms": round(ms_mma, 4), "torch_sdpa_ms": round(ms_lib, 4), "tflops": round(flops / ms / 1e9, 1),
                      "frac_of_bf16_peak": round(flops / ms / 1e9 / tf, 3), "peaks": src})
         print(rows[-1], flush=True)
 
@@ -285,6 +327,8 @@ def main():
     if "decode_gemm" in what:
         bench_gemm(rows, [(128, 6144, 4096), (128, 4096, 4096), (128, 24576, 4096), (128, 4096, 12288),
                           (128, 151936, 4096), (16, 4096, 4096), (256, 4096, 12288)], "gemm_decode")
+    if "swiglu_gemm" in what:
+        bench_swiglu_gemm(rows)
     if "decode_attn" in what:
         bench_decode_attn(rows)
     if "prefill_attn" in what:

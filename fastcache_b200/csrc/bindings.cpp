@@ -222,6 +222,18 @@ Tensor linear_silu_mul(const Tensor& x, const Tensor& w) {
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   Tensor out = torch::empty({M, I}, x.options());
   if (M == 0) return out;
+  if (M <= 128 && N % 256 == 0 && fc::streamk_enabled()) {
+    // one persistent kernel: equal spans of (tile, K block) units per SM, gate and up rows share a tile, the owner
+    // of a tile adds the other spans' partial sums and applies SwiGLU
+    fc::GemmWorkspace gw;
+    gw.scratch = ws.raw.gemm_scratch;
+    gw.counters = ws.raw.gemm_counters;
+    gw.status = ws.raw.status;
+    gw.grid_sync = ws.raw.grid_sync;
+    if (fc::gemm_streamk_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, int(M), int(N), int(x.size(1)),
+                              x.stride(0), w.stride(0), I, 0, true, gw, sm_limit_for(stream), stream))
+      return out;
+  }
   if (M <= 256 && N % 256 == 0 && fc::cluster_splitk_enabled()) {
     // one kernel: gate and up rows share a tile, the K splits reduce inside a cluster, SwiGLU in the epilogue
     fc::GemmWorkspace gw;
@@ -459,9 +471,11 @@ Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, con
   return out;
 }
 
-// q [B, Sq, H, D], k / v [B, Sk, H, D]; any strides with a contiguous last dim; key_mask [B, Sk] bool
+// q [B, Sq, H, D], k / v [B, Sk, H, D]; any strides with a contiguous last dim; key_mask [B, Sk] bool.
+// impl: 0 = the tcgen05 kernel where the strides can be described to TMA, else the mma.sync kernel; 1 = mma.sync;
+// 2 = tcgen05 (raises when it cannot run).
 Tensor dense_attention(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
-                       const c10::optional<Tensor>& key_mask) {
+                       const c10::optional<Tensor>& key_mask, int64_t impl) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(v, "v");
@@ -474,21 +488,41 @@ Tensor dense_attention(const Tensor& q, const Tensor& k, const Tensor& v, double
     TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0 && t->stride(0) % 8 == 0 &&
                     t->stride(1) % 8 == 0 && t->stride(2) % 8 == 0, "operands must be 16-byte aligned per row");
   }
-  const uint8_t* mask = nullptr;
-  Tensor mask_c;
-  if (key_mask.has_value() && key_mask->defined()) {
+  const bool has_mask = key_mask.has_value() && key_mask->defined();
+  if (has_mask)
     TORCH_CHECK(key_mask->scalar_type() == torch::kBool && key_mask->dim() == 2 && key_mask->size(0) == B &&
                     key_mask->size(1) == Sk && key_mask->is_cuda(), "key_mask must be bool [B, Sk] on the device");
-    mask_c = key_mask->contiguous();
-    mask = reinterpret_cast<const uint8_t*>(mask_c.data_ptr());
-  }
   c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({B, Sq, H, D}, q.options());
   const long long qs[3] = {q.stride(0), q.stride(1), q.stride(2)};
   const long long ks[3] = {k.stride(0), k.stride(1), k.stride(2)};
   const long long vs[3] = {v.stride(0), v.stride(1), v.stride(2)};
+  const bool tc_ok = B > 0 && Sq > 0 &&
+                     fc::dense_attention_tc_supported(int(B), int(Sq), int(Sk), int(H), int(D), qs, ks, vs);
+  TORCH_CHECK(impl != 2 || tc_ok || B == 0 || Sq == 0, "dense attention: the tcgen05 kernel cannot take these strides");
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (impl != 1 && tc_ok) {
+    const uint8_t* mask = nullptr;
+    Tensor mask_p;
+    const int64_t ld = (Sk + 127) / 128 * 128;
+    if (has_mask) {
+      mask_p = torch::zeros({B, ld}, key_mask->options().dtype(torch::kUInt8));
+      mask_p.narrow(1, 0, Sk).copy_(*key_mask);
+      mask = reinterpret_cast<const uint8_t*>(mask_p.data_ptr());
+    }
+    fc::launch_dense_attention_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), mask, int(ld), int(B),
+                                  int(Sq), int(Sk), int(H), int(D), qs, ks, vs, float(scale),
+                                  status_ptr(q.get_device()), stream);
+    return out;
+  }
+  const uint8_t* mask = nullptr;
+  Tensor mask_c;
+  if (has_mask) {
+    mask_c = key_mask->contiguous();
+    mask = reinterpret_cast<const uint8_t*>(mask_c.data_ptr());
+  }
   fc::launch_dense_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), mask, int(B), int(Sq),
-                             int(Sk), int(H), int(D), qs, ks, vs, float(scale), at::cuda::getCurrentCUDAStream());
+                             int(Sk), int(H), int(D), qs, ks, vs, float(scale), stream);
   return out;
 }
 
@@ -596,7 +630,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("max_ctx") = 0);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperatures"), py::arg("seed"), py::arg("with_status") = false,
         py::arg("vocab_offset") = 0, py::arg("v_limit") = -1);
-  m.def("dense_attention", &dense_attention);
+  m.def("dense_attention", &dense_attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
+        py::arg("key_mask") = py::none(), py::arg("impl") = 0);
   m.def("read_status", &read_status);
   m.def("set_wait_limit_us", &set_wait_limit_us);
   m.def("reset_sync_state", &reset_sync_state);
@@ -604,6 +639,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_epilogues_enabled", &fc::fused_epilogues_enabled);
   m.def("set_cluster_splitk", &fc::set_cluster_splitk, "split-K of decode-size GEMMs inside thread-block clusters");
   m.def("cluster_splitk_enabled", &fc::cluster_splitk_enabled);
+  m.def("set_streamk", &fc::set_streamk, "persistent stream-K form of the decode-size GEMMs with finished outputs");
+  m.def("streamk_enabled", &fc::streamk_enabled);
+  m.def("streamk_mode", &fc::streamk_mode);
   m.def("register_stream_sms", &register_stream_sms);
   m.def("num_sms", []() { return fc::gemm_num_sms(); });
   m.def("status_tensor", [](int64_t device) { return device_status(int(device)); });

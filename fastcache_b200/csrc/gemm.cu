@@ -570,6 +570,10 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
     return;
   }
   if (act == ACT_SWIGLU) throw std::runtime_error("fused SwiGLU GEMM is for M > 256; use linear_silu_mul below that");
+  // decode-size batch with more 256-row tiles than SMs (the LM head): equal spans of (tile, K block) units per SM
+  if (M <= 128 && streamk_enabled() && (N + 255) / 256 >= sms &&
+      gemm_streamk_bf16(x, w, c, bias, M, N, K, ldx, ldw, ldc, act, false, ws, sm_limit, stream))
+    return;
   // decode-size batch: weight-streaming kernel (gemm_skinny.cu)
   gemm_skinny_bf16(x, w, c, bias, M, N, K, ldx, ldw, ldc, act, ws, sm_limit, 0, true, stream);
 }

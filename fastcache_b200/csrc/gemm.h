@@ -70,4 +70,15 @@ int gemm_skinny_bf16(const void* x, const void* w, void* c, const void* bias, in
 void set_cluster_splitk(bool on);
 bool cluster_splitk_enabled();
 
+// Persistent stream-K form for finished outputs (gemm_streamk.cu), M <= 128: c = act(x w^T + bias), or with `swiglu`
+// w = [gate; up] ([N, K]) and c [M, N / 2] = silu(x gate^T) * (x up^T) (N % 256 == 0, no bias).  Returns false
+// without launching when the shape cannot take it.  Mode (FC_STREAMK / set_streamk): 0 never, 1 (initial) where a row
+// tile is cut into about three spans at most, 2 wherever the shape allows.
+bool gemm_streamk_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
+                       long long ldw, long long ldc, int act, bool swiglu, const GemmWorkspace& ws, int sm_limit,
+                       cudaStream_t stream);
+bool streamk_enabled();
+void set_streamk(int mode);
+int streamk_mode();
+
 }  // namespace fc

@@ -71,6 +71,13 @@ void launch_dense_attention(const void* q, const void* k, const void* v, void* o
                             int B, int Sq, int Sk, int H, int D, const long long* q_strides,
                             const long long* k_strides, const long long* v_strides, float scale,
                             cudaStream_t stream);
+// The same on tcgen05 (attn_dense_tc.cu).  key_mask rows are padded with zeros to mask_ld bytes, a multiple of 128.
+bool dense_attention_tc_supported(int B, int Sq, int Sk, int H, int D, const long long* q_strides,
+                                  const long long* k_strides, const long long* v_strides);
+void launch_dense_attention_tc(const void* q, const void* k, const void* v, void* out, const uint8_t* key_mask,
+                               int mask_ld, int B, int Sq, int Sk, int H, int D, const long long* q_strides,
+                               const long long* k_strides, const long long* v_strides, float scale,
+                               uint32_t* status, cudaStream_t stream);
 }  // namespace fc
 
 namespace fc {

@@ -20,6 +20,7 @@ device (`main_stream.wait_event`) before the blocks return to the free list.
 from __future__ import annotations
 
 import atexit
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence as Seq, Tuple, Union
@@ -81,7 +82,8 @@ class LLMEngine:
                  auto_tune: bool = False, auto_tune_interval: int = 4, auto_dual_batch: bool = True,
                  auto_dual_interval: int = 4, auto_min_seq_len: int = 256, auto_min_output_len: int = 64,
                  auto_min_speedup: float = 1.05, auto_force_compress: bool = False,
-                 compressor: Any = None, tokenizer: Any = None, decode_overlap: str = "shadow", **kwargs):
+                 compressor: Any = None, tokenizer: Any = None, decode_overlap: str = "shadow",
+                 check_streams: Optional[bool] = None, **kwargs):
         hf_config = kwargs.pop("hf_config", None)
         if not isinstance(model, str):          # a config object / dict instead of a path: random init
             hf_config, model = model, ""
@@ -175,6 +177,15 @@ class LLMEngine:
         self.stats = StepStats()
         self.trace: Optional[StepTrace] = None
         self._timing: Optional[dict] = None
+        # host-side race detector for the pool (utils/stream_check.py): every launch that touches blocks is checked
+        # against the stream order that the events below establish
+        if check_streams is None:
+            check_streams = os.environ.get("FC_CHECK_STREAMS", "0") == "1"
+        self.stream_check = None
+        if check_streams:
+            from ..utils.stream_check import StreamOrderChecker
+            self.stream_check = StreamOrderChecker()
+            self.stream_check.name_stream(r.main_stream, "main")
         atexit.register(self.exit)
 
     # ------------------------------------------------------------------ set-up
@@ -259,7 +270,7 @@ class LLMEngine:
         if r.main_stream is not None:
             for p in self._pending.values():
                 if p.event is not None:
-                    r.main_stream.wait_event(p.event)
+                    self._wait(r.main_stream, p.event)
         self._pending.clear()
         r.reset_sync_state()                 # arrival counters a kernel that gave up may have left mid-count
         n = self.scheduler.requeue_running()
@@ -282,12 +293,56 @@ class LLMEngine:
             from ..utils.watchdog import DeviceWaitTimeout
             raise DeviceWaitTimeout(code)
 
+
+    # ------------------------------------------------------ stream order (checked when `stream_check` is set)
+    def _record(self, event, stream) -> None:
+        event.record(stream)
+        if self.stream_check is not None:
+            self.stream_check.record(event, stream)
+
+    def _wait(self, stream, event) -> None:
+        stream.wait_event(event)
+        if self.stream_check is not None:
+            self.stream_check.wait(stream, event)
+
+    def _rows(self, table: Seq[int], lo: int, hi: int):
+        """(block, first row, end row) of rows [lo, hi) of a request with block table `table`."""
+        bs = self.scheduler.block_manager.block_size
+        return [(table[i], max(lo - i * bs, 0), min(hi - i * bs, bs))
+                for i in range(max(lo, 0) // bs, min(-(-hi // bs), len(table)))] if hi > lo else []
+
+    def _note_step(self, seqs: Seq[Sequence], is_prefill: bool) -> None:
+        reads, writes = [], []
+        for s in seqs:
+            if is_prefill:
+                end = s.logical_len if s.prefill_end is None else int(s.prefill_end)
+                first = s.prefill_start
+            else:
+                end = s.kv_cache_len
+                first = end - 1
+            reads += self._rows(s.block_table, 0, first)
+            writes += self._rows(s.block_table, first, end)
+        self.stream_check.launch(self.model_runner.main_stream, reads, writes,
+                                 "prefill step" if is_prefill else "decode step")
+
+    def _note_compress(self, stream, seqs: Seq[Sequence], rows: Seq[int], shadow: bool, what: str) -> None:
+        reads, writes = [], []
+        bs = self.scheduler.block_manager.block_size
+        for s, n in zip(seqs, rows):
+            src = self._rows(s.block_table, 0, n)
+            if shadow:
+                reads += src
+                writes += self._rows(s.shadow_table, 0, len(s.shadow_table) * bs)
+            else:
+                writes += src                        # compaction in place reads and rewrites the rows
+        self.stream_check.launch(stream, reads, writes, what)
+
     # -------------------------------------------------------------- compression
     def _on_release(self, seq: Sequence) -> None:
         """A request is about to lose its blocks: order any running compression first."""
         p = self._pending.pop(seq.seq_id, None)
         if p is not None and p.event is not None and self.model_runner.main_stream is not None:
-            self.model_runner.main_stream.wait_event(p.event)
+            self._wait(self.model_runner.main_stream, p.event)
         if seq.shadow_table:                     # the half-written compressed copy goes back to the pool
             self.scheduler.block_manager.release_blocks(seq.shadow_table)
             seq.shadow_table = []
@@ -299,6 +354,8 @@ class LLMEngine:
             if i >= seq.kv_num_blocks:
                 continue
             old, new = bm.make_private(seq, i)
+            if self.stream_check is not None:
+                self.stream_check.launch(self.model_runner.main_stream, [old], [new], "private copy of a shared block")
             self.model_runner.copy_block(old, new)
 
     def _free_compressed_blocks(self, seq: Sequence, new_len: Optional[int] = None) -> int:
@@ -327,6 +384,8 @@ class LLMEngine:
             saved = [s._kv_cache_len for s in chunk]
             for s, n in zip(chunk, rows):
                 s._kv_cache_len = n
+            if self.stream_check is not None:
+                self._note_compress(r.main_stream, chunk, rows, False, "compression (main stream)")
             try:
                 with nvtx_range("compress"):
                     new = r.compress_kv_cache_batch(chunk, stream=r.main_stream)
@@ -362,17 +421,19 @@ class LLMEngine:
             self._privatize(s)
         stream = r.next_compress_stream()
         ready = torch.cuda.Event()
-        ready.record(r.main_stream)
-        stream.wait_event(ready)
+        self._record(ready, r.main_stream)
+        self._wait(stream, ready)
         rows = [s.rows_in_pool for s in seqs]
         for s, n in zip(seqs, rows):
             s._kv_cache_len = n
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
         start.record(stream)
+        if self.stream_check is not None:
+            self._note_compress(stream, seqs, rows, False, "asynchronous compression")
         with nvtx_range("compress"):
             new = r.compress_kv_cache_batch(seqs, stream=stream)
-        end.record(stream)
+        self._record(end, stream)
         for s, n_in, n_out in zip(seqs, rows, new):
             s.compression_state = CompressionState.IN_PROGRESS
             s.kv_cache_len = n_out + int(s._pending_row)
@@ -435,14 +496,17 @@ class LLMEngine:
             if stream is not None and id(stream) not in waited:
                 if ready is None:
                     ready = torch.cuda.Event()
-                    ready.record(r.main_stream)
-                stream.wait_event(ready)
+                    self._record(ready, r.main_stream)
+                self._wait(stream, ready)
                 waited.add(id(stream))
             last = min(L, first + step)
             seqs = [p.seq for p in ps]
             saved = [s._kv_cache_len for s in seqs]
             for p in ps:
                 p.seq._kv_cache_len = p.rows
+            if self.stream_check is not None:
+                self._note_compress(stream if stream is not None else r.main_stream, seqs, [p.rows for p in ps],
+                                    shadow, f"compression of layers {first}-{last - 1}")
             with nvtx_range("compress_chunk"):
                 new = r.compress_kv_cache_batch(seqs, first, last, stream=stream,
                                                 dst_tables=[q.shadow_table for q in seqs] if shadow else None)
@@ -451,7 +515,7 @@ class LLMEngine:
             ev = None
             if stream is not None:
                 ev = torch.cuda.Event()
-                ev.record(stream)
+                self._record(ev, stream)
             for p, s, v, n in zip(ps, seqs, saved, new):
                 s._kv_cache_len = v
                 p.next_layer = last
@@ -478,7 +542,7 @@ class LLMEngine:
                     self._switch_to_shadow(s, p)
                 continue                             # chunks still to go: the request decodes over its full rows
             if p.event is not None and r.main_stream is not None:
-                r.main_stream.wait_event(p.event)
+                self._wait(r.main_stream, p.event)
             del self._pending[s.seq_id]
             s.compression_state = CompressionState.COMPLETED
             self._free_compressed_blocks(s)
@@ -497,7 +561,11 @@ class LLMEngine:
         if extra > 0:
             s.shadow_table.extend(bm.take_blocks(extra))
         if p.event is not None and r.main_stream is not None:
-            r.main_stream.wait_event(p.event)
+            self._wait(r.main_stream, p.event)
+        if self.stream_check is not None:
+            self.stream_check.launch(r.main_stream, self._rows(s.block_table, p.rows, p.rows + tail),
+                                     self._rows(s.shadow_table, p.new_len, p.new_len + tail),
+                                     "copy of the rows decoded during compression")
         cm = torch.cuda.stream(r.main_stream) if r.main_stream is not None else None
         if cm is not None:
             with cm:
@@ -555,7 +623,10 @@ class LLMEngine:
                            expected_output_len=max(1, sum(s.max_tokens for s in seqs) // len(seqs)),
                            pending_compressions=len(self._pending))
             pipeline, use_async = d.pipeline, d.async_compress
+            streams_before = r.compress_streams
             r.update_streams(d.greenctx_enabled, d.sm_compress_ratio, d.sm_main_ratio, d.compression_streams)
+            if self.stream_check is not None and r.compress_streams is not streams_before:
+                self.stream_check.synchronize()      # new streams are built after a device synchronisation
             r.decode_layers_per_step = d.decode_layers_per_step
         if not is_prefill:
             self._finalize_pending(seqs)
@@ -567,8 +638,12 @@ class LLMEngine:
                                    sum((s.logical_len if s.prefill_end is None else s.prefill_end) - s.prefill_start
                                        for s in seqs) if is_prefill else len(seqs),
                                    len(bm.free_block_ids), len(bm.blocks), self.stats.compressions, r.main_stream)
+        if self.stream_check is not None:
+            self._note_step(seqs, is_prefill)
         with nvtx_range("prefill" if is_prefill else "decode"):
             tokens = r.run(seqs, is_prefill)
+        if self.stream_check is not None:
+            self.stream_check.synchronize(r.main_stream)     # the sampled tokens were read back on the host
         if r.last_status:
             # a bounded wait in a kernel ran out (or an index was out of range) during this step or a compression
             # before it: the tokens cannot be trusted.  The scheduler state is as before the step's postprocess;

@@ -136,10 +136,11 @@ def decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale, wor
     return ref.decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
 
 
-def dense_attention(q, k, v, scale, key_mask=None):
+def dense_attention(q, k, v, scale, key_mask=None, impl: int = 0):
+    """impl (CUDA only): 0 = tcgen05 kernel where the strides allow it, 1 = the mma.sync kernel, 2 = tcgen05 or raise."""
     if q.is_cuda:
         _n()
-        return ext().dense_attention(q, k, v, float(scale), key_mask)
+        return ext().dense_attention(q, k, v, float(scale), key_mask, int(impl))
     return ref.dense_attention(q, k, v, scale, key_mask)
 
 

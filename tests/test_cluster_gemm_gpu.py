@@ -18,9 +18,11 @@ def _rand(*shape, scale=1.0, seed=0):
 @pytest.fixture
 def both_forms():
     e = ops.ext()
-    before = e.cluster_splitk_enabled()
+    before, streamk = e.cluster_splitk_enabled(), e.streamk_mode()
+    e.set_streamk(0)                     # the persistent stream-K form would take these shapes first
     yield e
     e.set_cluster_splitk(before)
+    e.set_streamk(streamk)
 
 
 SHAPES = [(128, 6144, 4096), (128, 4096, 4096), (128, 4096, 12288), (7, 1024, 512), (33, 768, 4096),

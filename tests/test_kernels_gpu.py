@@ -159,17 +159,39 @@ def test_prefill_attention(D, Hq, Hkv, bs, qlens, kvlens, impl):
 
 
 @pytest.mark.parametrize("B,Sq,Sk,H,D,masked", [(2, 577, 577, 16, 64, False), (3, 1024, 1024, 16, 72, True),
-                                                (2, 64, 700, 28, 128, True), (1, 10, 10, 4, 64, False)])
-def test_dense_attention(B, Sq, Sk, H, D, masked):
+                                                (2, 64, 700, 28, 128, True), (1, 10, 10, 4, 64, False),
+                                                (1, 300, 129, 1, 32, False), (2, 257, 256, 3, 96, True)])
+@pytest.mark.parametrize("impl", [1, 2])
+def test_dense_attention(B, Sq, Sk, H, D, masked, impl):
+    """impl 1: the mma.sync kernel; impl 2: the tcgen05 kernel (head_dim padded to 64 / 128 by the TMA copies)."""
     qkv = _rand(B, max(Sq, Sk), 3, H, D, seed=21)
     q, k, v = qkv[:, :Sq, 0], qkv[:, :Sk, 1], qkv[:, :Sk, 2]          # strided views, as the towers pass them
     mask = None
     if masked:
         lens = torch.randint(Sk // 2, Sk + 1, (B,))
-        mask = (torch.arange(Sk)[None, :] < lens[:, None]).to(DEV)
-    o = ops.dense_attention(q, k, v, D ** -0.5, mask)
+        mask = (torch.arange(Sk)[None, :] < lens[:, None])
+        mask[:, 3] = False                                             # a hole, not only a length
+        mask = mask.to(DEV)
+    o = ops.dense_attention(q, k, v, D ** -0.5, mask, impl=impl)
     want = ref.dense_attention(q.float(), k.float(), v.float(), D ** -0.5, mask)
+    _check_status()
     assert (o.float() - want).abs().max().item() < 2e-2
+
+
+def test_dense_attention_contiguous_and_expanded_operands():
+    """Separate contiguous q / k / v (the resampler's form) take the tcgen05 kernel; a query expanded over the
+    batch (stride 0) cannot be described to TMA and takes the other kernel under impl 0."""
+    B, Sq, Sk, H, D = 3, 64, 1024, 28, 128
+    q1 = _rand(1, Sq, H, D, seed=5)
+    k, v = _rand(B, Sk, H, D, seed=6), _rand(B, Sk, H, D, seed=7)
+    q = q1.expand(B, -1, -1, -1)
+    want = ref.dense_attention(q.float(), k.float(), v.float(), D ** -0.5, None)
+    for qq, impl in ((q.contiguous(), 2), (q, 0)):
+        o = ops.dense_attention(qq, k, v, D ** -0.5, None, impl=impl)
+        _check_status()
+        assert (o.float() - want).abs().max().item() < 2e-2
+    with pytest.raises(RuntimeError):
+        ops.dense_attention(q, k, v, D ** -0.5, None, impl=2)
 
 
 @pytest.mark.parametrize("mode", ["int8", "int8_asym", "int4", "nf4", "fp8_e4m3", "fp8_e5m2"])
