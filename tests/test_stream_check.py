@@ -137,6 +137,6 @@ def test_gpu_engine_side_stream_compression_is_ordered(mode):
     sps = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for m in (10, 3, 14, 6, 9, 12, 4, 8)]
     out = llm.generate(prompts, sps)
     assert len(out) == 8 and llm.stats.compressions >= 6
-    assert not llm.stream_check.violations and llm.stream_check.launches > 30
+    assert not llm.stream_check.violations and llm.stream_check.launches > 15
     llm.scheduler.block_manager.check_invariants([])
     llm.exit()
