@@ -320,6 +320,73 @@ def run_ours(args):
         tpmod.cleanup_tensor_parallel()
 
 
+
+# ------------------------------------------------------- correctness check of the tensor-parallel path
+def compare_first_tokens(got, want):
+    """(agreeing, total) over the requests' first sampled tokens."""
+    n = min(len(got), len(want))
+    return sum(int(a == b) for a, b in zip(got[:n], want[:n])), max(len(got), len(want))
+
+
+def run_check(args):
+    """`--check`: greedy first tokens of every request of a shrunken job under tensor parallelism against the same
+    prompts on one GPU.  Rank 0 first runs the one-GPU job as a child process (before it touches the device
+    itself), then all ranks run the N-GPU job; one JSON line says how many first tokens agree.  Random-init
+    weights give nearly flat logits, so a few near-ties may flip between reduction orders: "ok" means at least
+    90 % agree, a broken collective gives about 0 %."""
+    import json
+    import subprocess
+    import tempfile
+    rank, local_rank, world = dist_env()
+    cfg = args.config if args.config.endswith("-small") else "qwen3-8b-small"
+    want = None
+    if world > 1 and rank == 0:
+        out = os.path.join(tempfile.gettempdir(), f"fc_check_{os.getpid()}.json")
+        env = {k: v for k, v in os.environ.items()
+               if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "GROUP_RANK",
+                            "LOCAL_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE") and not k.startswith("TORCHELASTIC")}
+        subprocess.run([sys.executable, os.path.abspath(__file__), "--check", "--gpus", "1", "--config", cfg,
+                        "--check-out", out], env=env, check=True, timeout=1200, stdout=subprocess.DEVNULL)
+        with open(out) as f:
+            want = json.load(f)["first_tokens"]
+        os.unlink(out)
+    import torch
+    torch.cuda.set_device(local_rank)
+    from fastcache_b200 import LLM, SamplingParams, ops
+    from fastcache_b200.parallel import tp as tpmod
+    if world > 1:
+        tpmod.init_tensor_parallel(world, rank)
+    hf, n_req, p_len, o_len = WORKLOADS[cfg][:4]
+    llm = LLM(dict(hf), tensor_parallel_size=world, device=f"cuda:{local_rank}", kvcache_block_size=256,
+              max_model_len=p_len + o_len + 256, max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768,
+              gpu_memory_utilization=args.mem_util, seed=0, prefix_caching=False, enable_compression=True,
+              compression_backend="kvpress", kvpress_method=args.method, compression_factor=2,
+              compression_pipeline="prefill")
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    seqs = [llm.add_request(p, sp) for p in prompts_for(n_req, p_len, hf["vocab_size"], 1)]
+    while not llm.is_finished():
+        llm.step()
+    got = [int(s.completion_token_ids[0]) for s in seqs]
+    status = ops.ext().read_status(local_rank)
+    if rank == 0:
+        if args.check_out:
+            with open(args.check_out, "w") as f:
+                json.dump({"first_tokens": got}, f)
+        line = {"check": "first sampled token of every request", "config": MODEL_LABEL[cfg], "n_gpus": world,
+                "requests": n_req, "device_status": int(status)}
+        if want is not None:
+            agree, total = compare_first_tokens(got, want)
+            line.update(agree=agree, of=total, result="ok" if agree >= 0.9 * total and status == 0 else "MISMATCH")
+        else:
+            line.update(result="reference tokens written" if args.check_out else "one GPU: nothing to compare with")
+        emit(line)
+    llm.exit()
+    if world > 1:
+        tpmod.cleanup_tensor_parallel()
+    if rank == 0 and want is not None and line["result"] != "ok":
+        raise SystemExit(1)
+
+
 # ------------------------------------------------------- multimodal serving jobs
 LLAVA_15_7B = dict(
     model_type="llava", architectures=["LlavaForConditionalGeneration"], image_token_index=32000,
@@ -584,10 +651,17 @@ def main():
                     help="compression right after prefill on the main stream, on a compression stream, or a few "
                          "layers per decode step beside decode; auto: a compression stream when the SMs are split "
                          "(measured best: the split only pays when compression runs beside the main stream), else prefill")
+    ap.add_argument("--check", action="store_true",
+                    help="instead of timing: first tokens under --gpus N against the same prompts on one GPU "
+                         "(shrunken config, greedy)")
+    ap.add_argument("--check-out", default="", help=argparse.SUPPRESS)
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.steps = max(1, args.steps)
     claim_stdout()
+    if args.check:
+        run_check(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     elif args.config in SERVING:

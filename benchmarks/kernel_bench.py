@@ -61,7 +61,14 @@ def bench_gemm(rows, shapes, tag):
         flops = 2.0 * M * N * K
         byts = 2.0 * (M * K + N * K + M * N)
         t_roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
-        rows.append({"kernel": tag, "M": M, "N": N, "K": K, "ms": round(ms, 4), "cublas_ms": round(ms_lib, 4),
+        other = {}
+        if M > 256:                          # the other of the two prefill kernels (one CTA per tile / CTA pairs)
+            e = ops.ext()
+            mode = e.gemm_pairs_mode()
+            e.set_gemm_pairs(0 if mode else 1)
+            other = {("one_cta_per_tile_ms" if mode else "cta_pairs_ms"): round(timeit(lambda: ops.linear(x, w)), 4)}
+            e.set_gemm_pairs(mode)
+        rows.append({"kernel": tag, "M": M, "N": N, "K": K, "ms": round(ms, 4), **other, "cublas_ms": round(ms_lib, 4),
                      "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
                      "frac_of_roofline": round(t_roof / ms, 3), "peaks": src})
         print(rows[-1], flush=True)

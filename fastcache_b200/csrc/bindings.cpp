@@ -640,6 +640,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_cluster_splitk", &fc::set_cluster_splitk, "split-K of decode-size GEMMs inside thread-block clusters");
   m.def("cluster_splitk_enabled", &fc::cluster_splitk_enabled);
   m.def("set_streamk", &fc::set_streamk, "persistent stream-K form of the decode-size GEMMs with finished outputs");
+  m.def("set_gemm_pairs", &fc::set_gemm_pairs, "prefill-size GEMMs as tcgen05.mma.cta_group::2 on CTA pairs");
+  m.def("gemm_pairs_mode", &fc::gemm_pairs_mode);
   m.def("streamk_enabled", &fc::streamk_enabled);
   m.def("streamk_mode", &fc::streamk_mode);
   m.def("register_stream_sms", &register_stream_sms);

@@ -73,12 +73,14 @@ Tensor expected_attention_scores(const Tensor& pool, const Tensor& block_tables,
   auto f32 = pool.options().dtype(torch::kFloat32);
   Tensor stats = torch::empty({n, L, Hkv, D + D * D}, f32);
   Tensor scores = torch::empty({n, L, Hkv, stride}, f32);
+  Tensor sig16;                                      // Sigma as hi + lo bf16 for the tensor-core kernel
+  if (D == 128 && fc::ea_tensor_cores()) sig16 = torch::empty({n, L, Hkv, 2, D, D}, pool.options());
   fc::launch_expected_attention_scores(pool.data_ptr(), qw.data_ptr(), block_tables.data_ptr<int>(),
                                        kv_lens.data_ptr<int>(), stats.data_ptr<float>(), scores.data_ptr<float>(),
                                        int(n), int(L), int(pool.size(2)), int(Hkv), int(qw.size(3)), int(pool.size(4)),
                                        int(D), int(block_tables.size(1)), int(stride), int(qw.size(2)), int(n_sink),
                                        reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
-                                       at::cuda::getCurrentCUDAStream());
+                                       at::cuda::getCurrentCUDAStream(), sig16.defined() ? sig16.data_ptr() : nullptr);
   return scores;
 }
 
@@ -219,6 +221,8 @@ void register_compress(pybind11::module_& m) {
   m.def("snapkv_scores", &snapkv_scores);
   m.def("expected_attention_scores", &expected_attention_scores);
   m.def("position_scores", &position_scores);
+  m.def("set_ea_tensor_cores", &fc::set_ea_tensor_cores, "ExpectedAttention scores on tcgen05 (head_dim 128)");
+  m.def("ea_tensor_cores", &fc::ea_tensor_cores);
   namespace py = pybind11;
   m.def("ccm_compress", &ccm_compress, py::arg("pool"), py::arg("block_tables"), py::arg("kv_lens"),
         py::arg("image_lens"), py::arg("w1"), py::arg("b1"), py::arg("w2"), py::arg("b2"), py::arg("w3"),

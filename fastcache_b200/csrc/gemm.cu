@@ -527,6 +527,9 @@ void gemm_bf16(const void* x, const void* w, void* c, const void* bias, int M, i
   p.counters = ws.counters;
   const int num_kb = (K + BK - 1) / BK;
   const bool swapped = (M <= 256);
+  if (!swapped && gemm_pairs_mode() &&
+      gemm_bf16_2cta(x, w, c, bias, M, N, K, ldx, ldw, ldc, act, sm_limit, ws.status, stream))
+    return;
   if (!swapped) {
     // tokens are the 128-row operand
     p.M = M;

@@ -77,6 +77,12 @@ bool cluster_splitk_enabled();
 bool gemm_streamk_bf16(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
                        long long ldw, long long ldc, int act, bool swiglu, const GemmWorkspace& ws, int sm_limit,
                        cudaStream_t stream);
+// Prefill sizes on CTA pairs (gemm_2cta.cu): one tcgen05.mma.cta_group::2 of 256 x 256 per pair of SMs.  M > 256,
+// N >= 256, bias along N, any activation incl. ACT_SWIGLU.  Returns false without launching when it cannot run.
+bool gemm_bf16_2cta(const void* x, const void* w, void* c, const void* bias, int M, int N, int K, long long ldx,
+                    long long ldw, long long ldc, int act, int sm_limit, uint32_t* status, cudaStream_t stream);
+int gemm_pairs_mode();            // FC_GEMM_PAIRS=1 / set_gemm_pairs(1): gemm_bf16 takes the pair form where it can
+void set_gemm_pairs(int mode);
 bool streamk_enabled();
 void set_streamk(int mode);
 int streamk_mode();

@@ -58,7 +58,10 @@ void launch_snapkv_scores(const void* pool, const void* qw, const int* block_tab
 void launch_expected_attention_scores(const void* pool, const void* qw, const int* block_tables, const int* kv_lens,
                                       float* stats, float* scores, int n_seq, int L, int num_blocks, int Hkv, int Hq,
                                       int block_size, int D, int max_blocks, int stride, int w, int n_sink,
-                                      uint32_t* status, cudaStream_t stream);
+                                      uint32_t* status, cudaStream_t stream, void* sig16 = nullptr);
+// tcgen05 form of the ExpectedAttention scores (head_dim 128, needs the `sig16` scratch): on unless FC_EA_TC=0
+bool ea_tensor_cores();
+void set_ea_tensor_cores(bool on);
 void launch_position_scores(float* scores, const int* kv_lens, int n_seq, int units_per_seq, int stride, int n_sink,
                             cudaStream_t stream);
 void launch_select_compact(void* pool, const float* scores, const int* block_tables, const int* kv_lens,

@@ -23,3 +23,11 @@ def test_reference_arm_reports_unavailable_for_tensor_parallel_runs():
     assert p.returncode == 0
     line = json.loads(p.stdout)
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_check_mode_comparison_rule():
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.compare_first_tokens([5, 6, 7, 8], [5, 6, 7, 8]) == (4, 4)
+    assert bench.compare_first_tokens([5, 6, 7, 8], [5, 0, 7, 0]) == (2, 4)
+    assert bench.compare_first_tokens([5, 6], [5, 6, 7]) == (2, 3)          # a missing request counts as a miss

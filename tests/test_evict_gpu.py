@@ -78,8 +78,51 @@ def test_snapkv_eviction_in_pool_keeps_window_and_top_votes():
     assert torch.equal(flat(pool)[:, :, 36:100], flat(before)[:, :, 136:200])
 
 
-@pytest.mark.parametrize("D,Hq,H,w", [(128, 8, 2, 64), (64, 4, 4, 32)])
-def test_expected_attention_scores_kernel_matches_torch_statement(D, Hq, H, w):
+@pytest.mark.parametrize("D,Hq,H,w,tc", [(128, 8, 2, 64, True), (128, 8, 2, 64, False), (64, 4, 4, 32, False)])
+def test_expected_attention_scores_kernel_matches_torch_statement(D, Hq, H, w, tc):
+    """tc: the tcgen05 kernel (K Sigma as a tensor-core product, Sigma as hi + lo bf16); else the FP32-pipe kernel."""
+    from fastcache_b200.ops import ext as _ext
+    before = _ext().ea_tensor_cores()
+    _ext().set_ea_tensor_cores(tc)
+    try:
+        _expected_attention_case(D, Hq, H, w)
+    finally:
+        _ext().set_ea_tensor_cores(before)
+
+
+def test_expected_attention_tensor_core_kernel_long_rows_block_256():
+    """Several 128-key tiles per CTA and several CTAs per (layer, head, request); block size 256 (one TMA box per
+    tile) and lengths that end inside a tile."""
+    from fastcache_b200.compress.inpool import _rows
+    from fastcache_b200.compress.scorers import expected_attention
+    from fastcache_b200.ops import ext
+    from fastcache_b200.ops.compress_cuda import _batch_meta
+    from fastcache_b200.ops.snapkv import stack_window_queries
+    L, H, Hq, D, w = 2, 2, 8, 128, 64
+    pool = (_pool(L=L, nb=24, bs=256, H=H, D=D, seed=9).float() * 0.5).to(torch.bfloat16)
+    tables = [[3, 7, 1, 9, 12, 20, 21, 22, 23], [5, 6, 2, 4, 0]]
+    lens = [2100, 1153]
+    g = torch.Generator().manual_seed(5)
+    window_q = [{l: (torch.randn(w, Hq, D, generator=g) * 0.5).to(torch.bfloat16).cuda() for l in range(L)}
+                for _ in lens]
+    bt_d, lens_d = _batch_meta(pool, tables, lens)
+    status = ext().status_tensor(0)
+    assert ext().ea_tensor_cores()
+    got = ext().expected_attention_scores(pool, bt_d, lens_d, max(lens), stack_window_queries(window_q, L), 4, status)
+    torch.cuda.synchronize()
+    assert ext().read_status(0) == 0
+    for i, (bt, n) in enumerate(zip(tables, lens)):
+        blocks = torch.as_tensor(bt, dtype=torch.long, device="cuda")
+        for l in range(L):
+            k = _rows(pool[l, 0], blocks, n).permute(1, 0, 2)
+            v = _rows(pool[l, 1], blocks, n).permute(1, 0, 2)
+            want = expected_attention(k, v, window_q[i][l].permute(1, 0, 2), n_sink=4)
+            diff = got[i, l, :, 4:n] - torch.log(want[:, 4:n])
+            assert (diff - diff.mean(dim=1, keepdim=True)).abs().max().item() < 2e-2
+            assert torch.all(got[i, l, :, :4] > 1e37) and torch.all(torch.isinf(got[i, l, :, n:]))
+
+
+def _expected_attention_case(D, Hq, H, w):
     from fastcache_b200.compress.inpool import _rows
     from fastcache_b200.compress.scorers import expected_attention
     from fastcache_b200.ops import ext
