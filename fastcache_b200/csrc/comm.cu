@@ -45,7 +45,19 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int slot, u
 constexpr int AR_THREADS = 256;
 constexpr int AR_MAX_CHUNKS = 4;      // H <= 256 * 4 * 8 = 8192
 
-template <bool MULTIMEM>
+// MODE 0: peer loads after the flag exchange; 1: multimem.ld_reduce after it; 2: peer STORES before it ("push":
+// one row per CTA; the CTA finishes its row, stores it into its slot of every peer's staging buffer, then the
+// flag exchange publishes those stores, then every rank sums the `world` slots of its OWN buffer in rank order,
+// its own contribution from registers).  The push form takes the NVLink round trip of the loads out of the
+// critical path: the stores are posted and travel while the CTA is already waiting for the flags.
+constexpr int AR_PULL = 0, AR_MULTIMEM = 1, AR_PUSH = 2;
+
+__device__ __forceinline__ void st_peer_16(void* p, const uint4& v) {
+  asm volatile("st.global.relaxed.sys.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(AR_THREADS)
 allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ mc_in, bf16* __restrict__ residual,
                              const bf16* __restrict__ weight, bf16* __restrict__ out, int T, int H, float eps,
@@ -55,7 +67,46 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
   __shared__ uint32_t s_epoch;
   pdl_launch_dependents();
   pdl_wait();                            // the GEMM that filled the staging buffer, the previous epoch counters
-  if (partial != nullptr) {
+  uint4 mine[AR_MAX_CHUNKS];             // AR_PUSH: this rank's finished row, 16 bytes per chunk and thread
+  if (MODE == AR_PUSH) {
+    // grid == T: CTA b owns token row b.  Slot `rank` of every staging buffer receives this rank's row.
+    const int row = blockIdx.x;
+    const size_t slot_off = ((size_t)peers.rank * peers.slot_rows + row) * H;
+    const int chunks0 = H >> 3;
+#pragma unroll
+    for (int c = 0; c < AR_MAX_CHUNKS; ++c) {
+      const int idx = threadIdx.x + c * AR_THREADS;
+      if (idx < chunks0) {
+        if (partial != nullptr) {
+          const size_t off = (size_t)row * H + (size_t)idx * 8;
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+          for (int s = 0; s < splits; ++s) {
+            const float4* ps = reinterpret_cast<const float4*>(partial + (size_t)s * split_stride + off);
+            const float4 a = __ldcg(ps), b = __ldcg(ps + 1);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+            acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+          }
+          if (bias != nullptr) {
+            float bb[8];
+            unpack8f(*reinterpret_cast<const uint4*>(bias + (size_t)idx * 8), bb);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += bb[i];
+          }
+          mine[c] = pack8f(acc);
+        } else {
+          // the GEMM wrote finished bf16 rows into this rank's own slot of its own buffer
+          mine[c] = *reinterpret_cast<const uint4*>(peers.data[buf][peers.rank] + slot_off + (size_t)idx * 8);
+        }
+#pragma unroll
+        for (int d = 0; d < COMM_MAX_WORLD; ++d)
+          if (d < peers.world && d != peers.rank) st_peer_16(peers.data[buf][d] + slot_off + (size_t)idx * 8, mine[c]);
+      }
+    }
+    __syncthreads();
+  } else if (partial != nullptr) {
     // the GEMM left split-K partial sums [splits, T, H] in local scratch: finish this CTA's rows into this
     // rank's staging buffer first (what the GEMM's finalize kernel would have done), then join the exchange
     bf16* mine = peers.data[buf][peers.rank];
@@ -103,8 +154,28 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
       if (idx < chunks) {
         const size_t off = base + (size_t)idx * 8;
         float acc[8];
-        if (MULTIMEM) {
+        if (MODE == AR_MULTIMEM) {
           unpack8f(multimem_ld_reduce_bf16x8(mc_in + off), acc);
+        } else if (MODE == AR_PUSH) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          // the peers' rows are in this rank's own buffer now (the flag exchange made their stores visible)
+          uint4 raw[COMM_MAX_WORLD];
+          const bf16* here = peers.data[buf][peers.rank];
+#pragma unroll
+          for (int p = 0; p < COMM_MAX_WORLD; ++p)
+            if (p < peers.world)
+              raw[p] = p == peers.rank ? mine[c]
+                                       : ld_peer_16(here + ((size_t)p * peers.slot_rows + row) * H + (size_t)idx * 8);
+#pragma unroll
+          for (int p = 0; p < COMM_MAX_WORLD; ++p) {
+            if (p < peers.world) {
+              float f[8];
+              unpack8f(raw[p], f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] += f[i];
+            }
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -165,12 +236,18 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
   // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
   const int grid = T < COMM_MAX_SLOTS ? T : COMM_MAX_SLOTS;
   cudaError_t e;
-  if (use_multimem && mc_in != nullptr)
-    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<true>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
+  if (peers.slot_rows > 0) {
+    if (T > peers.slot_rows || T > COMM_MAX_SLOTS)
+      throw std::runtime_error("allreduce (push form): more token rows than a staging slot holds");
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<AR_PUSH>, dim3(T), dim3(AR_THREADS), 0, stream, peers, buf,
+                   (const bf16*)nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
+                   partial, splits, split_stride, (const bf16*)bias);
+  } else if (use_multimem && mc_in != nullptr)
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<AR_MULTIMEM>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
                    (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
                    partial, splits, split_stride, (const bf16*)bias);
   else
-    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<false>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<AR_PULL>, dim3(grid), dim3(AR_THREADS), 0, stream, peers, buf,
                    (const bf16*)nullptr, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
                    partial, splits, split_stride, (const bf16*)bias);
   if (e == cudaSuccess) e = cudaGetLastError();

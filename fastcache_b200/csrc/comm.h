@@ -15,6 +15,11 @@ struct CommPeers {
   int rank;
   __nv_bfloat16* data[2][COMM_MAX_WORLD];   // two staging buffers per rank, used in alternation
   uint32_t* flags[COMM_MAX_WORLD];          // [COMM_MAX_SLOTS][COMM_MAX_WORLD] words per rank
+  // > 0: "push" form of the one-shot all-reduce.  Every staging buffer then holds `world` slots of `slot_rows`
+  // token rows, slot s for the rows that rank s sends: a rank stores its finished row into slot `rank` of EVERY
+  // peer before the flag exchange and afterwards sums the slots of its own buffer, instead of fetching the
+  // peers' rows with loads over NVLink after the exchange.
+  int slot_rows;
 };
 
 // Candidate tables of the sampler over vocabulary shards: per rank [2][COMM_MAX_SLOTS][COMM_MAX_WORLD] 8-byte

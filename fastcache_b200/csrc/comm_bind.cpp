@@ -22,13 +22,16 @@ struct CommState {
 };
 CommState g_comm;
 
+// slot_rows > 0: the staging buffers hold `world` slots of `slot_rows` rows and the one-shot all-reduce runs in
+// its push form (comm.cu)
 void comm_init(int64_t rank, int64_t world, const std::vector<int64_t>& data0, const std::vector<int64_t>& data1,
-               const std::vector<int64_t>& flags, int64_t mc0, int64_t mc1, int64_t device) {
+               const std::vector<int64_t>& flags, int64_t mc0, int64_t mc1, int64_t device, int64_t slot_rows) {
   TORCH_CHECK(world >= 2 && world <= fc::COMM_MAX_WORLD, "world size must be in [2, ", fc::COMM_MAX_WORLD, "]");
   TORCH_CHECK((int64_t)data0.size() == world && (int64_t)data1.size() == world && (int64_t)flags.size() == world,
               "need one pointer per rank");
   g_comm.peers.world = int(world);
   g_comm.peers.rank = int(rank);
+  g_comm.peers.slot_rows = int(slot_rows);
   for (int i = 0; i < world; ++i) {
     g_comm.peers.data[0][i] = reinterpret_cast<__nv_bfloat16*>(data0[i]);
     g_comm.peers.data[1][i] = reinterpret_cast<__nv_bfloat16*>(data1[i]);
@@ -147,7 +150,7 @@ Tensor linear_allreduce_add_rmsnorm(const Tensor& x, const Tensor& w, const c10:
   const void* mc = (use_multimem && g_comm.mc[buf] != 0) ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
   uint32_t* epochs = reinterpret_cast<uint32_t*>(g_comm.epochs.data_ptr<int>());
   const int sm_limit = fc::stream_sm_limit(stream);
-  if (fc::fused_epilogues_enabled()) {
+  if (fc::fused_epilogues_enabled() && g_comm.peers.slot_rows == 0) {
     fc::SkinnyFused f;
     f.epi = fc::EPI_AR_ADD_NORM;
     f.residual = residual.data_ptr();
@@ -164,7 +167,9 @@ Tensor linear_allreduce_add_rmsnorm(const Tensor& x, const Tensor& w, const c10:
   }
   // two kernels: the GEMM leaves bf16 rows in the staging buffer or fp32 split-K partial sums in scratch, the
   // all-reduce kernel finishes them
-  void* staging = g_comm.peers.data[buf][g_comm.peers.rank];
+  // (push form: the rank's own slot of its own buffer)
+  void* staging = g_comm.peers.data[buf][g_comm.peers.rank] +
+                  (size_t)g_comm.peers.rank * g_comm.peers.slot_rows * size_t(N);
   const int splits = fc::gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), staging, bptr, int(M), int(N), int(K),
                                           x.stride(0), w.stride(0), N, 0, gw, sm_limit, 0, false, stream);
   fc::launch_allreduce_add_rmsnorm(g_comm.peers, int(buf), mc, residual.data_ptr(), norm_w.data_ptr(),
@@ -263,7 +268,9 @@ void wait_gathered(int64_t epoch, Tensor status) {
 }  // namespace
 
 void register_comm(pybind11::module_& m) {
-  m.def("comm_init", &comm_init);
+  m.def("comm_init", &comm_init, pybind11::arg("rank"), pybind11::arg("world"), pybind11::arg("data0"),
+        pybind11::arg("data1"), pybind11::arg("flags"), pybind11::arg("mc0"), pybind11::arg("mc1"),
+        pybind11::arg("device"), pybind11::arg("slot_rows") = 0);
   m.def("comm_shutdown", &comm_shutdown);
   m.def("sample_exchange_init", &sample_exchange_init);
   m.def("sample_exchange", &sample_exchange);

@@ -31,6 +31,7 @@ from . import fused as fused_mod
 from . import tp as tpmod
 
 MAX_SLOTS = 512
+DEFAULT_AR_PUSH = "1"           # peers' rows are pushed before the flag exchange (FC_AR_PUSH=0: fetched after it)
 DEFAULT_RUNTIME = "torch"       # "native": this package's own allocator and handle exchange (FC_SYMM overrides)
 MAX_WORLD = 8
 
@@ -55,7 +56,10 @@ class FusedComm:
         self.max_tokens = 0
         self.epoch = 0
         self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
-        shapes = [((one_shot_tokens, hidden), bf16), ((one_shot_tokens, hidden), bf16),
+        # push form of the one-shot all-reduce (FC_AR_PUSH=1): every staging buffer holds one slot per source rank
+        self.push = os.environ.get("FC_AR_PUSH", DEFAULT_AR_PUSH) == "1"
+        slots = self.world if self.push else 1
+        shapes = [((one_shot_tokens * slots, hidden), bf16), ((one_shot_tokens * slots, hidden), bf16),
                   ((MAX_SLOTS * MAX_WORLD,), torch.int32), ((ext().sample_cells_per_rank(),), torch.int64)]
         if max_tokens > one_shot_tokens:
             per_rank = -(-max_tokens // self.world)
@@ -68,8 +72,9 @@ class FusedComm:
         if use_multimem is None:
             use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
         self.has_multicast = bool(mc[0] and mc[1])
-        self.use_multimem = bool(use_multimem and self.has_multicast)
-        ext().comm_init(self.rank, self.world, ptrs[0], ptrs[1], ptrs[2], mc[0], mc[1], index)
+        self.use_multimem = bool(use_multimem and self.has_multicast and not self.push)
+        ext().comm_init(self.rank, self.world, ptrs[0], ptrs[1], ptrs[2], mc[0], mc[1], index,
+                        one_shot_tokens if self.push else 0)
         ext().sample_exchange_init(ptrs[3])
         self.status = ext().status_tensor(index)
         self.cur = 0
@@ -124,6 +129,12 @@ class FusedComm:
             ops._n()
             self._gather = None
         return hidden
+
+    def own_rows(self, buf: int, T: int) -> torch.Tensor:
+        """Where this rank's partial rows [T, hidden] of staging buffer `buf` go before `allreduce_add_rmsnorm`
+        (the push form keeps one slot per source rank in every buffer)."""
+        first = self.rank * self.one_shot_max_tokens if self.push else 0
+        return self.bufs[buf][first:first + T]
 
     def chunk_rows_for(self, T: int) -> int:
         return -(-(-(-T // self.world)) // 128) * 128

@@ -177,3 +177,43 @@ def test_fused_gemm_allreduce_add_norm_on_one_gpu(M, N, K, bias):
             assert (bufs[buf][0][:M].float() - mine.float()).abs().max().item() < 0.03   # rank 0's staged rows
     finally:
         e.comm_shutdown()
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(128, 4096, 512, False), (40, 1024, 1536, True), (3, 2048, 4096, False)])
+def test_push_form_of_the_allreduce_on_one_gpu(M, N, K, bias):
+    """The push form (every rank stores its finished row into its slot of every peer's buffer before the flag
+    exchange, then sums the slots of its own buffer) with this GPU as rank 0 of 2 and the second rank played by
+    local memory: what rank 1 would have pushed is written into slot 1 of rank 0's buffer beforehand, its flags
+    are preset, and afterwards slot 0 of "rank 1's" buffer must hold rank 0's row."""
+    e = ops.ext()
+    e.set_fused_epilogues(False)
+    dev = torch.device("cuda", 0)
+    R = 256                                                               # rows per slot
+    bufs = [torch.zeros(2, 2 * R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]    # [buf][rank][slot rows][N]
+    flags = torch.zeros(2, 512 * 8, dtype=torch.int32, device=dev)
+    flags[0].view(512, 8)[:, 1] = 1 << 20
+    status = e.status_tensor(0)
+    e.read_status(0)
+    x, w = _rand(M, K, seed=61), _rand(N, K, scale=0.03, seed=62)
+    b = _rand(N, seed=63) if bias else None
+    nw, res = _rand(N, seed=64), _rand(M, N, seed=65)
+    other = _rand(M, N, scale=0.5, seed=66)
+    mine = ref.linear(x.float(), w.float(), None if b is None else b.float()).to(torch.bfloat16)
+    want_y, want_r = ref.add_rms_norm((mine.float() + other.float()).to(torch.bfloat16), res.clone(), nw, 1e-6)
+    try:
+        e.comm_init(0, 2, [bufs[0][0].data_ptr(), bufs[0][1].data_ptr()],
+                    [bufs[1][0].data_ptr(), bufs[1][1].data_ptr()],
+                    [flags[0].data_ptr(), flags[1].data_ptr()], 0, 0, 0, R)
+        for buf in (0, 1, 0):
+            bufs[buf][0][R:R + M].copy_(other)                            # slot 1 of rank 0's buffer
+            bufs[buf][1].zero_()
+            r = res.clone()
+            y = e.linear_allreduce_add_rmsnorm(x, w, b, buf, r, nw, 1e-6, False, status)
+            torch.cuda.synchronize()
+            assert e.read_status(0) == 0
+            assert (r.float() - want_r.float()).abs().max().item() < 0.07
+            assert ((y.float() - want_y.float()).abs() / (want_y.float().abs() + 1.0)).max().item() < 2e-2
+            assert (bufs[buf][1][:M].float() - mine.float()).abs().max().item() < 0.03    # pushed to "rank 1", slot 0
+            assert int(bufs[buf][1][R:].abs().max()) == 0                                 # and nowhere else
+    finally:
+        e.comm_shutdown()

@@ -80,7 +80,7 @@ def main():
             want_n, want_r = ref.add_rms_norm(total.to(torch.bfloat16), resid.clone(), w, 1e-6)
             for mm in ([False, True] if comm.use_multimem or os.environ.get("FC_MULTIMEM") == "1" else [False]):
                 buf = it % 2
-                comm.bufs[buf][:T].copy_(part)
+                comm.own_rows(buf, T).copy_(part)
                 r2 = resid.clone()
                 y = ops.ext().allreduce_add_rmsnorm(buf, r2, w, 1e-6, mm, comm.status)
                 torch.cuda.synchronize()
