@@ -57,7 +57,8 @@ class FusedComm:
         self.epoch = 0
         self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
         # push form of the one-shot all-reduce (FC_AR_PUSH=1): every staging buffer holds one slot per source rank
-        self.push = os.environ.get("FC_AR_PUSH", DEFAULT_AR_PUSH) == "1"
+        # (one CTA per token row, so at most MAX_SLOTS rows; larger one-shot limits keep the fetching form)
+        self.push = os.environ.get("FC_AR_PUSH", DEFAULT_AR_PUSH) == "1" and one_shot_tokens <= MAX_SLOTS
         slots = self.world if self.push else 1
         shapes = [((one_shot_tokens * slots, hidden), bf16), ((one_shot_tokens * slots, hidden), bf16),
                   ((MAX_SLOTS * MAX_WORLD,), torch.int32), ((ext().sample_cells_per_rank(),), torch.int64)]
