@@ -267,6 +267,11 @@ def main():
         for name in t_f:
             row = {"phase": label, "tokens": tokens, "world": world, "op": name, "fused_ms": round(t_f[name], 4),
                    "nccl_ms": round(t_l[name], 4), "gemm_only_ms": round(t_c.get(name, 0.0), 4), "peaks": src}
+            if "reduce" in name and comm is not None:
+                from fastcache_b200.ops import ext as _ext
+                row["reduce_form"] = ("pipelined, in-switch sums" if _ext().tp_pipeline_enabled() and comm.tp_multicast
+                                      and _ext().tp_nvls_enabled() else
+                                      "pipelined" if _ext().tp_pipeline_enabled() else "one phase after the GEMM")
             if name in flops:
                 # the row-parallel kernel sends both the reduce-scatter partials and the all-gather rows
                 # (link_ms); the gathered GEMM that follows only waits for them

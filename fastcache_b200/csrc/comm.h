@@ -56,7 +56,23 @@ struct TpBuffers {
   uint32_t* rs_flags[COMM_MAX_WORLD] = {};          // per rank: [world] "source s delivered its partials"
   uint32_t* gathered_flags[COMM_MAX_WORLD] = {};    // per rank: [world] "owner o's rows have landed here"
   int* owner_done = nullptr;                        // local [world + 1] counters, zero between calls
+  // pipelined reduce-scatter: per 128-row group of a chunk
+  uint32_t* group_flags[COMM_MAX_WORLD] = {};       // per rank: [max_groups][COMM_MAX_WORLD] "source s delivered group g"
+  int* group_done = nullptr;                        // local [world][max_groups] counters, zero between calls
+  int max_groups = 0;
+  // NVSwitch multicast addresses of the staging / gathered buffers (nullptr: none)
+  const __nv_bfloat16* stage_mc = nullptr;
+  __nv_bfloat16* xg_mc = nullptr;
 };
+
+// The row-parallel GEMM reduces each 128-row group as soon as all ranks have delivered it (on unless
+// FC_TP_PIPELINE=0); off: one reduction phase after the GEMM.
+bool tp_pipeline_enabled();
+void set_tp_pipeline(bool on);
+// The pipelined form sums through the switch (multimem.ld_reduce / multimem.st) when the buffers have multicast
+// addresses (on unless FC_TP_NVLS=0).
+bool tp_nvls_enabled();
+void set_tp_nvls(bool on);
 
 // Row-parallel GEMM + reduce-scatter + residual add + RMSNorm + send half of the all-gather.
 // x [M, K] and w [N, K] are this rank's shards; `residual` holds the rows owned by this rank

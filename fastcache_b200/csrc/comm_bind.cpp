@@ -183,14 +183,16 @@ Tensor linear_allreduce_add_rmsnorm(const Tensor& x, const Tensor& w, const c10:
 struct TpState {
   bool ready = false;
   fc::TpBuffers b;
-  Tensor owner_done;
+  Tensor owner_done, group_done;
   int64_t stage_rows = 0, xg_rows = 0, hidden = 0;
 };
 TpState g_tp;
 
+// `flags`: per rank 2 * COMM_MAX_WORLD words (chunk flags) followed by max_groups * COMM_MAX_WORLD words (row-group
+// flags of the pipelined reduce-scatter; max_groups = 0: none)
 void tp_init(int64_t rank, int64_t world, const std::vector<int64_t>& stage, const std::vector<int64_t>& xg,
              const std::vector<int64_t>& flags, int64_t stage_rows, int64_t xg_rows, int64_t hidden,
-             int64_t device) {
+             int64_t device, int64_t max_groups, int64_t stage_mc, int64_t xg_mc) {
   TORCH_CHECK(world >= 2 && world <= fc::COMM_MAX_WORLD, "world size must be in [2, ", fc::COMM_MAX_WORLD, "]");
   TORCH_CHECK((int64_t)stage.size() == world && (int64_t)xg.size() == world && (int64_t)flags.size() == world,
               "need one pointer per rank");
@@ -201,6 +203,16 @@ void tp_init(int64_t rank, int64_t world, const std::vector<int64_t>& stage, con
     g_tp.b.xg[i] = reinterpret_cast<__nv_bfloat16*>(xg[i]);
     g_tp.b.rs_flags[i] = reinterpret_cast<uint32_t*>(flags[i]);
     g_tp.b.gathered_flags[i] = reinterpret_cast<uint32_t*>(flags[i]) + fc::COMM_MAX_WORLD;
+    g_tp.b.group_flags[i] = max_groups > 0 ? reinterpret_cast<uint32_t*>(flags[i]) + 2 * fc::COMM_MAX_WORLD : nullptr;
+  }
+  g_tp.b.max_groups = int(max_groups);
+  g_tp.b.stage_mc = reinterpret_cast<const __nv_bfloat16*>(stage_mc);
+  g_tp.b.xg_mc = reinterpret_cast<__nv_bfloat16*>(xg_mc);
+  g_tp.b.group_done = nullptr;
+  if (max_groups > 0) {
+    g_tp.group_done = torch::zeros({fc::COMM_MAX_WORLD * max_groups},
+                                   torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, int(device)));
+    g_tp.b.group_done = g_tp.group_done.data_ptr<int>();
   }
   g_tp.owner_done = torch::zeros({fc::COMM_MAX_WORLD + 1},
                                  torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, int(device)));
@@ -280,7 +292,14 @@ void register_comm(pybind11::module_& m) {
         pybind11::arg("partial") = pybind11::none(), pybind11::arg("splits") = 0,
         pybind11::arg("bias") = pybind11::none());
   m.def("linear_allreduce_add_rmsnorm", &linear_allreduce_add_rmsnorm);
-  m.def("tp_init", &tp_init);
+  m.def("tp_init", &tp_init, pybind11::arg("rank"), pybind11::arg("world"), pybind11::arg("stage"), pybind11::arg("xg"),
+        pybind11::arg("flags"), pybind11::arg("stage_rows"), pybind11::arg("xg_rows"), pybind11::arg("hidden"),
+        pybind11::arg("device"), pybind11::arg("max_groups") = 0, pybind11::arg("stage_mc") = 0,
+        pybind11::arg("xg_mc") = 0);
+  m.def("set_tp_nvls", &fc::set_tp_nvls, "pipelined row-parallel GEMM: sums and broadcasts through NVSwitch multicast");
+  m.def("tp_nvls_enabled", &fc::tp_nvls_enabled);
+  m.def("set_tp_pipeline", &fc::set_tp_pipeline, "row-parallel prefill GEMM: reduce row groups while the GEMM runs");
+  m.def("tp_pipeline_enabled", &fc::tp_pipeline_enabled);
   m.def("gemm_rs_add_norm", &gemm_rs_add_norm);
   m.def("gemm_after_gather", &gemm_after_gather, pybind11::arg("xg"), pybind11::arg("weight"),
         pybind11::arg("chunk_rows"), pybind11::arg("epoch"), pybind11::arg("status"), pybind11::arg("sm_limit"),

@@ -20,6 +20,18 @@
 //   "gathered" flag of a chunk's owner before it loads the first tile of that chunk and starts with
 //   its own chunk, so the GEMM runs while later chunks are still arriving.
 //
+// MODE_RS, pipelined form (default): the tiles are walked row group by row group across the owners (group g of
+// owner rank + 1, of rank + 2, ..., of this rank, then group g + 1, ...), every rank counts the tiles it has
+// delivered per (owner, 128-row group) and raises a flag per group, and six extra warps per CTA ("reducers")
+// wait for the flags of the groups this rank owns and reduce + normalise + send them while the main loop is still
+// working on later groups.  Only the last groups' reduction is left after the GEMM instead of the whole chunk's.
+//
+// With NVSwitch multicast addresses for the staging and gathered buffers (NVLS; FC_TP_NVLS=0 turns it off) the
+// pipelined form moves fewer bytes: the epilogue writes its partial tiles into this rank's OWN staging buffer
+// ([M][N], plain local stores), the owner of a row sums the `tp` copies inside the switch (multimem.ld_reduce:
+// one row crosses the owner's link once instead of tp - 1 times) and publishes the normalised row with one
+// multimem.st (one row leaves the owner once instead of tp - 1 times).
+//
 // No TMA touches peer memory and no load is multicast; remote data always lands in the consumer's own
 // memory through ordinary stores first.  Every wait is bounded and reports through the status word.
 #include <cuda.h>
@@ -27,6 +39,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -68,6 +81,18 @@ struct TpGemmParams {
   float eps;
   __nv_bfloat16* xg_peer[COMM_MAX_WORLD];     // gathered activation buffer of every rank: [>= M, N]
   uint32_t* gathered_flag_peer[COMM_MAX_WORLD];
+  // MODE_RS, pipelined form (see the header): per 128-row group instead of per chunk
+  int pipelined;
+  int max_groups;                             // row groups per chunk that the flag / counter arrays hold
+  int* group_done;                            // local [tp][max_groups]: tiles of (owner, group) delivered by this rank
+  uint32_t* group_flag_peer[COMM_MAX_WORLD];  // [max_groups][COMM_MAX_WORLD] words on every rank: "source s delivered group g"
+  const uint32_t* group_flags_local;
+  // NVLS form of the pipelined kernel: the partial sums stay in this rank's own staging buffer, laid out [M][N];
+  // the owner of a row sums all ranks' copies with multimem.ld_reduce through the multicast address of the
+  // staging buffers and publishes the normalised row with one multimem.st to every rank's gathered buffer
+  const __nv_bfloat16* stage_mc;              // nullptr: peer stores and local sums
+  __nv_bfloat16* xg_mc;
+  __nv_bfloat16* stage_rw;                    // this rank's staging buffer, writable
 };
 
 __device__ __forceinline__ void tp_st_release(uint32_t* p, uint32_t v) {
@@ -94,15 +119,106 @@ __device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoc
   return false;
 }
 
+__device__ __forceinline__ uint4 tp_multimem_ld_reduce(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void tp_multimem_st(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// The NVLS form of the row reduction below: one multimem.ld_reduce per 16 bytes instead of `tp` loads, one
+// multimem.st instead of `tp` stores.  U pieces per lane in flight.
+template <int U>
+__device__ __forceinline__ void tp_reduce_rows_nvls(const TpGemmParams& p, int row0, int r_begin, int r_end, int r_step,
+                                                    int lane) {
+  const int chunks = p.N >> 3;
+  for (int r = r_begin; r < r_end; r += r_step) {
+    __nv_bfloat16* res_row = p.residual + (long long)r * p.N;
+    const long long off_row = (long long)(row0 + r) * p.N;
+    float ss = 0.f;
+    for (int i0 = lane; i0 < chunks; i0 += 32 * U) {
+      uint4 sum[U], ru[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          sum[u] = tp_multimem_ld_reduce(p.stage_mc + off_row + idx * 8);
+          ru[u] = *reinterpret_cast<const uint4*>(res_row + idx * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&sum[u]);
+          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&ru[u]);
+          uint4 su;
+          uint32_t* sw = reinterpret_cast<uint32_t*>(&su);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 a = __bfloat1622float2(ah[i]), f = __bfloat1622float2(rh[i]);
+            sw[i] = pack_bf16(a.x + f.x, a.y + f.y);
+          }
+          *reinterpret_cast<uint4*>(res_row + idx * 8) = su;
+          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(sh[i]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+    }
+    const float inv = rsqrtf(warp_sum(ss) / float(p.N) + p.eps);
+    for (int i0 = lane; i0 < chunks; i0 += 32 * U) {
+      uint4 su[U], gu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          su[u] = *reinterpret_cast<const uint4*>(res_row + idx * 8);
+          gu[u] = *reinterpret_cast<const uint4*>(p.norm_w + idx * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = i0 + 32 * u;
+        if (idx < chunks) {
+          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&su[u]);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu[u]);
+          uint4 ou;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&ou);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(sh[i]);
+            const float2 g2 = __bfloat1622float2(gh[i]);
+            const float a = __bfloat162float(__float2bfloat16(f.x * inv)) * g2.x;
+            const float b = __bfloat162float(__float2bfloat16(f.y * inv)) * g2.y;
+            ow[i] = pack_bf16(a, b);
+          }
+          tp_multimem_st(p.xg_mc + off_row + idx * 8, ou);
+        }
+      }
+    }
+  }
+}
+
 // Phase 2 of MODE_RS for the rows this rank owns.  One warp per row, U 16-byte pieces per lane in
 // flight: pass 1 sums the tp partial rows and the residual (written back), pass 2 re-reads the new
 // residual (the lane's own lines), scales it and stores the row into every rank's gathered buffer as
 // full 512-byte warp stores.
 template <int TPMAX, int U>
-__device__ __forceinline__ void tp_reduce_rows(const TpGemmParams& p, int row0, int my_rows, int warp, int lane) {
+__device__ __forceinline__ void tp_reduce_rows(const TpGemmParams& p, int row0, int r_begin, int r_end, int r_step,
+                                               int lane) {
   const int chunks = p.N >> 3;                         // 16-byte pieces per row
-  constexpr int WARPS = TP_THREADS / 32;
-  for (int r = blockIdx.x * WARPS + warp; r < my_rows; r += gridDim.x * WARPS) {
+  for (int r = r_begin; r < r_end; r += r_step) {
     __nv_bfloat16* res_row = p.residual + (long long)r * p.N;
     float ss = 0.f;
     for (int i0 = lane; i0 < chunks; i0 += 32 * U) {
@@ -194,8 +310,13 @@ __device__ __forceinline__ void tp_reduce_rows(const TpGemmParams& p, int row0, 
   }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(TP_THREADS, 1)
+constexpr int TP_REDUCERS = 6;                      // reducer warps per CTA (pipelined MODE_RS)
+constexpr int TP_THREADS_RS = TP_THREADS + 32 * TP_REDUCERS;
+
+// PIPE (MODE_RS only): the pipelined form with reducer warps; both forms are built so that they can be compared
+// NVLS (with PIPE): sums and broadcasts through the NVSwitch multicast addresses
+template <int MODE, bool PIPE = false, bool NVLS = false>
+__global__ void __launch_bounds__(PIPE ? TP_THREADS_RS : TP_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                const TpGemmParams p) {
   constexpr int A_BYTES = TP_BM * TP_BK * 2, B_BYTES = TP_BN * TP_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -240,6 +361,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // tile -> (m_blk, n_blk): grouped raster, then the m-block order is rotated by `rot` blocks so that
   // MODE_RS starts with the chunk of rank + 1 (own chunk last) and MODE_AG with its own chunk
   auto decode_tile = [&](int tile, int& m_blk, int& n_blk) {
+    if (PIPE) {
+      // row group by row group across the owners, own chunk last within a group
+      n_blk = tile % p.num_n;
+      const int q = tile / p.num_n;
+      const int owner = (p.rank + 1 + q % p.tp) % p.tp;
+      m_blk = owner * p.blocks_per_chunk + q / p.tp;
+      return;
+    }
     const int padded = p.tp * p.blocks_per_chunk;            // >= num_m; blocks >= num_m are skipped
     const int per_group = p.group_m * p.num_n;
     const int g = tile / per_group;
@@ -336,7 +465,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (acc == 0) acc_phase ^= 1;
       }
     }
-  } else {
+  } else if (warp < 6) {
     const int lane_group = warp & 3;
     const int ep_tid = (warp - 2) * 32 + lane;
     int acc = 0;
@@ -358,7 +487,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       long long ld;
       if (MODE == MODE_RS) {
         ld = p.N;
-        dst0 = p.stage_peer[owner] + ((long long)p.rank * p.chunk_rows + (gi0 - owner * p.chunk_rows)) * p.N;
+        if (NVLS)
+          dst0 = p.stage_rw + (long long)gi0 * p.N;          // NVLS form: this rank's own buffer, [M][N]
+        else
+          dst0 = p.stage_peer[owner] + ((long long)p.rank * p.chunk_rows + (gi0 - owner * p.chunk_rows)) * p.N;
       } else {
         ld = p.ldc;
         dst0 = p.C + (long long)gi0 * p.ldc;
@@ -415,17 +547,59 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ep_tid == 0) {
           __threadfence_system();
-          const int first = owner * p.blocks_per_chunk;
-          const int nblk = max(0, min(p.num_m - first, p.blocks_per_chunk));
-          const int old = atomicAdd(&p.owner_done[owner], 1);
-          if (old + 1 == nblk * p.num_n) {
-            __threadfence_system();
-            tp_st_release(p.rs_flag_peer[owner] + p.rank, p.epoch);
+          if (PIPE) {
+            const int g = m_blk - owner * p.blocks_per_chunk;
+            const int old = atomicAdd(&p.group_done[owner * p.max_groups + g], 1);
+            if (old + 1 == p.num_n) {
+              __threadfence_system();
+              tp_st_release(p.group_flag_peer[owner] + (size_t)g * COMM_MAX_WORLD + p.rank, p.epoch);
+            }
+          } else {
+            const int first = owner * p.blocks_per_chunk;
+            const int nblk = max(0, min(p.num_m - first, p.blocks_per_chunk));
+            const int old = atomicAdd(&p.owner_done[owner], 1);
+            if (old + 1 == nblk * p.num_n) {
+              __threadfence_system();
+              tp_st_release(p.rs_flag_peer[owner] + p.rank, p.epoch);
+            }
           }
         }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+  } else if (PIPE) {
+    // ------------------------------------------------ reducers (warps 6-11): the rows this rank owns
+    // The rows are dealt out one by one over all reducer warps of the grid, so the 128 rows of a group go to 128
+    // different warps: what is left when the main loop ends (the last group of every owner completes only then) is
+    // one row per warp, not a group per CTA.  A warp takes its rows in rising order and waits for the flags of a
+    // row's group when it enters a new group.
+    const int rw = warp - 6;
+    const int row0r = p.rank * p.chunk_rows;
+    const int my_rows_r = max(0, min(p.M - row0r, p.chunk_rows));
+    const int stride = int(gridDim.x) * TP_REDUCERS;
+    int seen_group = -1;
+    for (int r = rw * int(gridDim.x) + int(blockIdx.x); r < my_rows_r; r += stride) {
+      const int g = r / TP_BM;
+      if (g != seen_group) {
+        bool ok = true;
+        if (lane < p.tp)
+          ok = !s_flag[0] && tp_wait_flag(p.group_flags_local + (size_t)g * COMM_MAX_WORLD + lane, p.epoch, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          s_flag[0] = 1;
+          break;
+        }
+        seen_group = g;
+      }
+      if (NVLS) {
+        tp_reduce_rows_nvls<4>(p, row0r, r, r + 1, 1, lane);
+        continue;
+      }
+      // (fewer pieces in flight than the one-phase form: this kernel has the main loop's state live as well)
+      if (p.tp <= 2) tp_reduce_rows<2, 2>(p, row0r, r, r + 1, 1, lane);
+      else if (p.tp <= 4) tp_reduce_rows<4, 1>(p, row0r, r, r + 1, 1, lane);
+      else tp_reduce_rows<8, 1>(p, row0r, r, r + 1, 1, lane);
     }
   }
 
@@ -440,15 +614,19 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // ------------------------------------------------------------------ phase 2: rows owned by this rank
   const int row0 = p.rank * p.chunk_rows;
   const int my_rows = max(0, min(p.M - row0, p.chunk_rows));
-  if (my_rows > 0 && !s_flag[0]) {
+  if (!PIPE && my_rows > 0 && !s_flag[0]) {
     if (threadIdx.x < p.tp) {
       if (!tp_wait_flag(p.rs_flags_local + threadIdx.x, p.epoch, p.status)) s_flag[0] = 1;
     }
     __syncthreads();
     if (!s_flag[0]) {
-      if (p.tp <= 2) tp_reduce_rows<2, 8>(p, row0, my_rows, warp, lane);
-      else if (p.tp <= 4) tp_reduce_rows<4, 4>(p, row0, my_rows, warp, lane);
-      else tp_reduce_rows<8, 2>(p, row0, my_rows, warp, lane);
+      constexpr int WARPS = TP_THREADS / 32;             // (the reducer warps of the pipelined form are not here)
+      const int rb = blockIdx.x * WARPS + warp, rs = gridDim.x * WARPS;
+      if (warp < WARPS) {
+        if (p.tp <= 2) tp_reduce_rows<2, 8>(p, row0, rb, my_rows, rs, lane);
+        else if (p.tp <= 4) tp_reduce_rows<4, 4>(p, row0, rb, my_rows, rs, lane);
+        else tp_reduce_rows<8, 2>(p, row0, rb, my_rows, rs, lane);
+      }
     }
   }
   // the last CTA to get here publishes "rows of this rank are gathered" everywhere and resets the counters
@@ -456,7 +634,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __syncthreads();
   if (threadIdx.x == 0) {
     const int old = atomicAdd(&p.owner_done[p.tp], 1);
-    if (old == int(gridDim.x) - 1) {
+    s_flag[1] = old == int(gridDim.x) - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_flag[1]) {
+    if (PIPE)
+      for (int i = threadIdx.x; i < p.tp * p.max_groups; i += blockDim.x) p.group_done[i] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
       for (int o = 0; o <= p.tp; ++o) p.owner_done[o] = 0;
       __threadfence_system();
       for (int d = 0; d < p.tp; ++d) tp_st_release(p.gathered_flag_peer[d] + p.rank, p.epoch);
@@ -468,6 +653,26 @@ static int tp_smem_bytes() {
   // operand ring + barriers + output staging (4 epilogue warps x 32 rows x 144 bytes) + alignment slack
   return TP_STAGES * (TP_BM * TP_BK * 2 + TP_BN * TP_BK * 2) + 256 + 4 * 32 * 144 + 1024;
 }
+
+static int g_tp_pipeline = -1;
+bool tp_pipeline_enabled() {
+  if (g_tp_pipeline < 0) {
+    const char* e = std::getenv("FC_TP_PIPELINE");
+    g_tp_pipeline = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return g_tp_pipeline == 1;
+}
+void set_tp_pipeline(bool on) { g_tp_pipeline = on ? 1 : 0; }
+
+static int g_tp_nvls = -1;
+bool tp_nvls_enabled() {
+  if (g_tp_nvls < 0) {
+    const char* e = std::getenv("FC_TP_NVLS");
+    g_tp_nvls = (e == nullptr || e[0] != '0') ? 1 : 0;
+  }
+  return g_tp_nvls == 1;
+}
+void set_tp_nvls(bool on) { g_tp_nvls = on ? 1 : 0; }
 
 static void fill_common(TpGemmParams& p, int M, int N, int K, int tp, int rank, int chunk_rows, uint32_t epoch,
                         uint32_t* status, bool own_first) {
@@ -508,6 +713,15 @@ void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long lo
   p.stage_local = b.stage[b.rank];
   p.rs_flags_local = b.rs_flags[b.rank];
   p.owner_done = b.owner_done;
+  p.pipelined = (tp_pipeline_enabled() && b.group_done != nullptr && p.blocks_per_chunk <= b.max_groups) ? 1 : 0;
+  p.max_groups = b.max_groups;
+  p.group_done = b.group_done;
+  for (int i = 0; i < b.world; ++i) p.group_flag_peer[i] = b.group_flags[i];
+  p.group_flags_local = b.group_flags[b.rank];
+  const bool nvls = p.pipelined && tp_nvls_enabled() && b.stage_mc != nullptr && b.xg_mc != nullptr;
+  p.stage_mc = nvls ? b.stage_mc : nullptr;
+  p.xg_mc = nvls ? b.xg_mc : nullptr;
+  p.stage_rw = b.stage[b.rank];
   p.residual = reinterpret_cast<__nv_bfloat16*>(residual);
   p.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
   p.eps = eps;
@@ -516,10 +730,20 @@ void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long lo
   const CUtensorMap ta = make_tmap_bf16_2d(x, M, K, ldx, TP_BM, TP_BK);
   const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
-  auto kern = gemm_tp_kernel<MODE_RS>;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
   // every CTA takes part in the flag exchange of phase 2: the grid must be fully resident
-  kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  if (p.pipelined && p.stage_mc != nullptr) {
+    auto kern = gemm_tp_kernel<MODE_RS, true, true>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+    kern<<<std::min(p.total_tiles, sms), TP_THREADS_RS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  } else if (p.pipelined) {
+    auto kern = gemm_tp_kernel<MODE_RS, true, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+    kern<<<std::min(p.total_tiles, sms), TP_THREADS_RS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  } else {
+    auto kern = gemm_tp_kernel<MODE_RS, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
+    kern<<<std::min(p.total_tiles, sms), TP_THREADS, tp_smem_bytes(), stream>>>(ta, tb, p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm_rs_add_norm launch: ") + cudaGetErrorString(e));
 }

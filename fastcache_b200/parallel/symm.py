@@ -54,6 +54,7 @@ class FusedComm:
         # ---- the symmetric buffers: one-shot all-reduce staging (two, used in alternation) and flags, the sampler's
         # candidate tables, and for prefill sizes the reduce-scatter staging, the gathered activations and their flags
         self.max_tokens = 0
+        self.tp_multicast = False
         self.epoch = 0
         self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
         # push form of the one-shot all-reduce (FC_AR_PUSH=1): every staging buffer holds one slot per source rank
@@ -67,7 +68,7 @@ class FusedComm:
             self.chunk_max = -(-per_rank // 128) * 128
             self.max_tokens = max_tokens
             shapes += [((self.world * self.chunk_max, hidden), bf16), ((self.chunk_max * self.world, hidden), bf16),
-                       ((2 * MAX_WORLD,), torch.int32)]
+                       ((2 * MAX_WORLD + (self.chunk_max // 128) * MAX_WORLD,), torch.int32)]
         tensors, ptrs, mc = self._symmetric(shapes, device, group, name)
         self.bufs, self.flags, self.cells = tensors[:2], tensors[2], tensors[3]
         if use_multimem is None:
@@ -81,8 +82,11 @@ class FusedComm:
         self.cur = 0
         if self.max_tokens:
             self.stage, self.xg, self.tp_flags = tensors[4], tensors[5], tensors[6]
+            # the row-parallel prefill GEMM sums through the switch when both buffers have multicast addresses
+            self.tp_multicast = bool(mc[4] and mc[5])
             ext().tp_init(self.rank, self.world, ptrs[4], ptrs[5], ptrs[6], self.chunk_max,
-                          self.chunk_max * self.world, hidden, index)
+                          self.chunk_max * self.world, hidden, index, self.chunk_max // 128,
+                          int(mc[4] or 0), int(mc[5] or 0))
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 

@@ -217,3 +217,54 @@ def test_push_form_of_the_allreduce_on_one_gpu(M, N, K, bias):
             assert int(bufs[buf][1][R:].abs().max()) == 0                                 # and nowhere else
     finally:
         e.comm_shutdown()
+
+
+@pytest.mark.parametrize("pipelined", [False, True])
+@pytest.mark.parametrize("T,K", [(1000, 256), (4096, 512), (300, 1024)])
+def test_row_parallel_gemm_reduce_scatter_on_one_gpu(pipelined, T, K):
+    """The prefill-size fused GEMM + reduce-scatter + add + RMSNorm + all-gather send with this GPU as rank 0 of 2
+    and the second rank played by local memory: what rank 1 would have delivered for rank 0's rows is written into
+    the staging buffer beforehand and its flags are preset.  Both forms: one reduction phase after the GEMM, and
+    row groups reduced by the extra warps while the GEMM runs.  Checks rank 0's residual rows, the normalised rows
+    it sends to both ranks, and the partial sums it delivers for rank 1's rows."""
+    e = ops.ext()
+    dev = torch.device("cuda", 0)
+    H, W = 1024, 8                                                        # hidden, flag words per group
+    chunk = -(-(-(-T // 2)) // 128) * 128
+    groups = chunk // 128
+    stage = [torch.zeros(2 * chunk, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]   # [rank][source slot rows][H]
+    xg = [torch.zeros(2 * chunk, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    flags = [torch.zeros(2 * W + groups * W, dtype=torch.int32, device=dev) for _ in range(2)]
+    flags[0][1] = 1 << 20                                                 # chunk flag: source 1 delivered
+    flags[0][2 * W:].view(groups, W)[:, 1] = 1 << 20                      # group flags: source 1 delivered
+    status = e.status_tensor(0)
+    e.read_status(0)
+    before = e.tp_pipeline_enabled()
+    x, w = _rand(T, K, scale=0.5, seed=71), _rand(H, K, scale=0.05, seed=72)
+    nw = _rand(H, seed=73)
+    own = min(T, chunk)
+    res = _rand(own, H, seed=74)
+    other = _rand(own, H, scale=0.5, seed=75)                             # rank 1's partial sums for rank 0's rows
+    mine = ref.linear(x.float(), w.float()).to(torch.bfloat16)            # [T, H]: rank 0's partial sums
+    want_y, want_r = ref.add_rms_norm((mine[:own].float() + other.float()).to(torch.bfloat16), res.clone(), nw, 1e-6)
+    try:
+        e.set_tp_pipeline(pipelined)
+        e.tp_init(0, 2, [t.data_ptr() for t in stage], [t.data_ptr() for t in xg], [t.data_ptr() for t in flags],
+                  chunk, 2 * chunk, H, 0, groups)
+        for epoch in (1, 2):
+            stage[0][chunk:chunk + own].copy_(other)                      # slot of source 1 in rank 0's buffer
+            r = res.clone()
+            e.gemm_rs_add_norm(x, w, r, nw, 1e-6, chunk, epoch, status, 0)
+            torch.cuda.synchronize()
+            assert e.read_status(0) == 0
+            assert (r.float() - want_r.float()).abs().max().item() < 0.07
+            for d in (0, 1):                                              # the all-gather send reached both ranks
+                got = xg[d][:own].float()
+                assert ((got - want_y.float()).abs() / (want_y.float().abs() + 1.0)).max().item() < 2e-2
+            if T > chunk:                                                 # rank 0's partial sums for rank 1's rows
+                assert (stage[1][:T - chunk].float() - mine[chunk:].float()).abs().max().item() < 0.03
+            delivered = flags[1][2 * W] if pipelined else flags[1][0]        # first row group / whole chunk
+            assert int(delivered) == epoch and int(flags[1][W]) == epoch       # delivered to / gathered at rank 1
+            assert int(flags[0][W]) == epoch                                   # gathered flag on itself
+    finally:
+        e.set_tp_pipeline(before)
