@@ -221,6 +221,8 @@ void register_compress(pybind11::module_& m) {
   m.def("snapkv_scores", &snapkv_scores);
   m.def("expected_attention_scores", &expected_attention_scores);
   m.def("position_scores", &position_scores);
+  m.def("set_snapkv_tensor_cores", &fc::set_snapkv_tensor_cores, "SnapKV votes on tcgen05 (head_dim 128)");
+  m.def("snapkv_tensor_cores", &fc::snapkv_tensor_cores);
   m.def("set_ea_tensor_cores", &fc::set_ea_tensor_cores, "ExpectedAttention scores on tcgen05 (head_dim 128)");
   m.def("ea_tensor_cores", &fc::ea_tensor_cores);
   namespace py = pybind11;

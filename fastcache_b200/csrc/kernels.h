@@ -59,6 +59,9 @@ void launch_expected_attention_scores(const void* pool, const void* qw, const in
                                       float* stats, float* scores, int n_seq, int L, int num_blocks, int Hkv, int Hq,
                                       int block_size, int D, int max_blocks, int stride, int w, int n_sink,
                                       uint32_t* status, cudaStream_t stream, void* sig16 = nullptr);
+// tcgen05 form of the SnapKV votes (head_dim 128, (Hq / Hkv) * window a multiple of 64): on unless FC_SNAPKV_TC=0
+bool snapkv_tensor_cores();
+void set_snapkv_tensor_cores(bool on);
 // tcgen05 form of the ExpectedAttention scores (head_dim 128, needs the `sig16` scratch): on unless FC_EA_TC=0
 bool ea_tensor_cores();
 void set_ea_tensor_cores(bool on);

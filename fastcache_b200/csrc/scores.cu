@@ -28,6 +28,9 @@ constexpr float SC_POS = 3.0e38f;
 
 // ------------------------------------------------------------------ query statistics
 // grid (Hkv, L, n_seq), 256 threads.  stats[unit] = mu[D] followed by Sigma[D][D].
+// The G * w window rows of the KV head stay in shared memory as bf16 (64 KB for 256 x 128: three CTAs share an
+// SM).  Sigma = (Q^T Q - rows mu mu^T) / (rows - 1) with fp32 sums; each thread owns 4 x 4 tiles of Q^T Q, so two
+// 64-bit shared-memory reads feed 16 multiply-adds per query row.
 template <int D>
 __global__ void __launch_bounds__(256)
 ea_stats_kernel(const bf16* __restrict__ qw, float* __restrict__ stats, bf16* __restrict__ sig16, int L, int Hkv,
@@ -35,49 +38,73 @@ ea_stats_kernel(const bf16* __restrict__ qw, float* __restrict__ stats, bf16* __
   extern __shared__ __align__(16) uint8_t smem[];
   const int hk = blockIdx.x, layer = blockIdx.y, seq = blockIdx.z;
   const int G = Hq / Hkv, rows = G * w;
-  float* s_q = reinterpret_cast<float*>(smem);               // [rows][D], centred
-  float* s_mu = s_q + rows * D;                              // [D]
+  bf16* s_q = reinterpret_cast<bf16*>(smem);                 // [rows][D]
+  float* s_mu = reinterpret_cast<float*>(s_q + rows * D);    // [D]
+  float* s_half = s_mu + D;                                  // [256 / D][D] partial column sums
   const bf16* src = qw + (((long long)seq * L + layer) * w) * Hq * D;
-  for (int i = threadIdx.x; i < rows * D; i += blockDim.x) {
-    const int r = i / D, d = i % D;
+  constexpr int CH = D / 8;                                  // 16-byte pieces per row
+  for (int i = threadIdx.x; i < rows * CH; i += blockDim.x) {
+    const int r = i / CH, ch = i % CH;
     const int hg = r / w, wr = r % w;
-    s_q[i] = __bfloat162float(src[((long long)wr * Hq + hk * G + hg) * D + d]);
+    *reinterpret_cast<uint4*>(s_q + r * D + ch * 8) =
+        *reinterpret_cast<const uint4*>(src + ((long long)wr * Hq + hk * G + hg) * D + ch * 8);
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  {
+    // column sums: thread (part, d) adds every (256 / D)-th row
+    const int d = threadIdx.x % D, part = threadIdx.x / D, parts = blockDim.x / D;
     float acc = 0.f;
-    for (int r = 0; r < rows; ++r) acc += s_q[r * D + d];
-    s_mu[d] = acc / float(rows);
+    for (int r = part; r < rows; r += parts) acc += __bfloat162float(s_q[r * D + d]);
+    s_half[part * D + d] = acc;
+    __syncthreads();
+    if (threadIdx.x < D) {
+      float tot = 0.f;
+      for (int q = 0; q < parts; ++q) tot += s_half[q * D + threadIdx.x];
+      s_mu[threadIdx.x] = tot / float(rows);
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < rows * D; i += blockDim.x) s_q[i] -= s_mu[i % D];
-  __syncthreads();
   float* out = stats + (((long long)seq * L + layer) * Hkv + hk) * (D + D * D);
   for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = s_mu[d];
-  const float norm = 1.f / float(max(1, rows - 1));
-  // each thread owns strips of four columns of one row of Sigma
-  for (int e = threadIdx.x; e < D * D / 4; e += blockDim.x) {
-    const int i = e / (D / 4), j0 = (e % (D / 4)) * 4;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    for (int r = 0; r < rows; ++r) {
-      const float qi = s_q[r * D + i];
-      const float4 qj = *reinterpret_cast<const float4*>(&s_q[r * D + j0]);
-      a0 += qi * qj.x;
-      a1 += qi * qj.y;
-      a2 += qi * qj.z;
-      a3 += qi * qj.w;
-    }
-    *reinterpret_cast<float4*>(&out[D + i * D + j0]) = make_float4(a0 * norm, a1 * norm, a2 * norm, a3 * norm);
-    if (sig16 != nullptr) {
-      // Sigma as the sum of two bf16 matrices (hi + lo), for the tensor-core scoring kernel: [unit][2][D][D]
-      bf16* hi = sig16 + (((long long)seq * L + layer) * Hkv + hk) * (2 * D * D) + i * D + j0;
-      bf16* lo = hi + D * D;
-      const float v4[4] = {a0 * norm, a1 * norm, a2 * norm, a3 * norm};
+  const float norm = 1.f / float(max(1, rows - 1)), frows = float(rows);
+  for (int e = threadIdx.x; e < (D / 4) * (D / 4); e += blockDim.x) {
+    const int i0 = (e / (D / 4)) * 4, j0 = (e % (D / 4)) * 4;
+    float a[4][4];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const bf16 h = __float2bfloat16(v4[t]);
-        hi[t] = h;
-        lo[t] = __float2bfloat16(v4[t] - __bfloat162float(h));
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) a[x][y] = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < rows; ++r) {
+      const uint2 ri = *reinterpret_cast<const uint2*>(s_q + r * D + i0);
+      const uint2 rj = *reinterpret_cast<const uint2*>(s_q + r * D + j0);
+      // a bf16 is the upper half of the fp32 with the same value
+      const float vi[4] = {__uint_as_float(ri.x << 16), __uint_as_float(ri.x & 0xffff0000u),
+                           __uint_as_float(ri.y << 16), __uint_as_float(ri.y & 0xffff0000u)};
+      const float vj[4] = {__uint_as_float(rj.x << 16), __uint_as_float(rj.x & 0xffff0000u),
+                           __uint_as_float(rj.y << 16), __uint_as_float(rj.y & 0xffff0000u)};
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) a[x][y] = fmaf(vi[x], vj[y], a[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int i = i0 + x;
+      float v4[4];
+#pragma unroll
+      for (int y = 0; y < 4; ++y) v4[y] = (a[x][y] - frows * s_mu[i] * s_mu[j0 + y]) * norm;
+      *reinterpret_cast<float4*>(&out[D + i * D + j0]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
+      if (sig16 != nullptr) {
+        // Sigma as the sum of two bf16 matrices (hi + lo), for the tensor-core scoring kernel: [unit][2][D][D]
+        bf16* hi = sig16 + (((long long)seq * L + layer) * Hkv + hk) * (2 * D * D) + i * D + j0;
+        bf16* lo = hi + D * D;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const bf16 h = __float2bfloat16(v4[t]);
+          hi[t] = h;
+          lo[t] = __float2bfloat16(v4[t] - __bfloat162float(h));
+        }
       }
     }
   }
@@ -431,7 +458,7 @@ void launch_expected_attention_scores(const void* pool, const void* qw, const in
   if (n_seq == 0) return;
   const int rows = (Hq / Hkv) * w;
   if (Hq % Hkv != 0 || rows < 2) throw std::runtime_error("expected attention: bad head grouping or window");
-  const int smem1 = (rows * D + D) * 4;
+  const int smem1 = rows * D * 2 + D * 4 + 256 * 4;
   const int smem2 = (D * (D + 4) + D + 8 * EA_KB * D) * 4;
   if (smem1 > 220 * 1024) throw std::runtime_error("expected attention: (Hq / Hkv) * window * head_dim is too large");
   dim3 g1(Hkv, L, n_seq);

@@ -35,17 +35,37 @@ def test_evict_matches_reference(method, D):
         assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("D,Hq,H,w", [(128, 8, 2, 64), (64, 4, 4, 32), (128, 4, 1, 64)])
-def test_snapkv_scores_kernel_matches_torch_statement(D, Hq, H, w):
+@pytest.mark.parametrize("D,Hq,H,w,tc", [(128, 8, 2, 64, True), (128, 8, 2, 64, False), (64, 4, 4, 32, False),
+                                         (128, 4, 1, 64, True), (128, 4, 2, 32, True), (128, 2, 2, 64, True)])
+def test_snapkv_scores_kernel_matches_torch_statement(D, Hq, H, w, tc):
+    """tc: the tcgen05 kernel (Q K^T by query row for the row statistics, K Q^T by key for the votes); else mma.sync."""
+    from fastcache_b200.ops import ext as _ext
+    before = _ext().snapkv_tensor_cores()
+    _ext().set_snapkv_tensor_cores(tc)
+    try:
+        _snapkv_case(D, Hq, H, w)
+    finally:
+        _ext().set_snapkv_tensor_cores(before)
+
+
+def test_snapkv_tensor_core_kernel_long_rows_block_256():
+    """Many key tiles (the three-stage ring and both accumulators wrap several times), block size 256, requests
+    that end inside a tile and one whose evictable part is a single tile."""
+    _snapkv_case(128, 8, 2, 64, nb=24, bs=256, tables=[[3, 7, 1, 9, 12, 20, 21, 22, 23], [5, 6, 2], [4]],
+                 lens=[2100, 641, 130])
+
+
+def _snapkv_case(D, Hq, H, w, nb=40, bs=16, tables=None, lens=None):
     from fastcache_b200.compress.inpool import _rows
     from fastcache_b200.compress.scorers import snapkv
     from fastcache_b200.ops import ext
     from fastcache_b200.ops.compress_cuda import _batch_meta
     from fastcache_b200.ops.snapkv import snapkv_scores_cuda
     L = 2
-    pool = _pool(L=L, nb=40, bs=16, H=H, D=D, seed=3)
-    tables = [[3, 7, 1, 9, 12, 30, 31, 33, 34, 35, 36, 37, 38], [5, 6, 20, 21, 22, 23, 24, 25, 26, 2, 4]]
-    lens = [200, 170]
+    pool = _pool(L=L, nb=nb, bs=bs, H=H, D=D, seed=3)
+    if tables is None:
+        tables = [[3, 7, 1, 9, 12, 30, 31, 33, 34, 35, 36, 37, 38], [5, 6, 20, 21, 22, 23, 24, 25, 26, 2, 4]]
+        lens = [200, 170]
     g = torch.Generator().manual_seed(9)
     window_q = [{l: torch.randn(w, Hq, D, generator=g).to(torch.bfloat16).cuda() for l in range(L)} for _ in lens]
     bt_d, lens_d = _batch_meta(pool, tables, lens)
