@@ -113,8 +113,7 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
   uint32_t* keys = sm;                       // [S]
   uint32_t* hist = sm + s_stride;            // [256]
   int* s_misc = reinterpret_cast<int*>(hist + 256);   // [8]: bin, above, ...
-  int* dstpos = s_misc + 8;                  // [SC_CHUNK]
-  int* wsum = dstpos + SC_CHUNK;             // [2][8] warp partials
+  int* wsum = s_misc + 8;                    // [SC_THREADS / 32] warp partials
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   const float* sc = scores + (((long long)seq * L + layer) * Hkv + h) * s_stride;
@@ -127,19 +126,48 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
   for (int shift = 24; shift >= 0; shift -= 8) {
     hist[tid] = 0;
     __syncthreads();
-    for (int i = tid; i < S; i += SC_THREADS) {
-      const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1u);
+    // scores of one request share their leading bits, so most keys of a warp fall into the same bin: the lanes
+    // with equal bins elect one that adds their count (one shared-memory atomic per distinct bin and warp)
+    for (int i0 = 0; i0 < S; i0 += SC_THREADS) {
+      const int i = i0 + tid;
+      int bin = -1;
+      if (i < S) {
+        const uint32_t key = keys[i];
+        if ((key & mask) == prefix) bin = int((key >> shift) & 0xFF);
+      }
+      const unsigned peers = __match_any_sync(0xffffffffu, bin);
+      if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], unsigned(__popc(peers)));
     }
     __syncthreads();
-    if (tid == 0) {
-      int acc = 0, bin = 255;
-      for (; bin > 0; --bin) {
-        if (acc + int(hist[bin]) >= remaining) break;
-        acc += int(hist[bin]);
+    if (warp == 0) {
+      // lane l owns bins 255 - 8 l ... 248 - 8 l (from the top); the lane whose bins contain rank `remaining`
+      // walks its eight bins
+      int mine = 0;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) mine += int(hist[255 - 8 * lane - b]);
+      int x = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
       }
-      s_misc[0] = bin;
-      s_misc[1] = acc;
+      const int above = x - mine;                       // keys in higher bins than this lane's
+      const bool here = above < remaining && remaining <= x;
+      const unsigned found = __ballot_sync(0xffffffffu, here);
+      if (found == 0) {
+        if (lane == 31) {                               // fewer keys than `remaining` in this class: lowest bin
+          s_misc[0] = 0;
+          s_misc[1] = x - int(hist[0]);
+        }
+      } else if (here) {
+        int acc = above, bin = 255 - 8 * lane;
+        for (int b = 0; b < 7; ++b, --bin) {
+          if (acc + int(hist[bin]) >= remaining) break;
+          acc += int(hist[bin]);
+        }
+        s_misc[0] = bin;
+        s_misc[1] = acc;
+      }
     }
     __syncthreads();
     prefix |= uint32_t(s_misc[0]) << shift;
@@ -172,21 +200,13 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
     return pool + (((base + blk) * Hkv + h) * block_size + tok % block_size) * D;
   };
 
-  int out_base = 0;        // rows already written
-  int eq_seen = 0;         // ties already passed
-  constexpr int PIECES = D / 8;              // 16-byte pieces per row (K or V)
-  constexpr int PER_THREAD = (SC_CHUNK * 2 * PIECES) / SC_THREADS;
-  for (int c0 = 0; c0 < S; c0 += SC_CHUNK) {
-    // flags and positions for this chunk (threads 0..127 own one row each)
-    int keep = 0, iseq = 0;
-    const int tok = c0 + tid;
-    if (tid < SC_CHUNK && tok < S) {
-      const uint32_t key = keys[tok];
-      iseq = (key == thr);
-      keep = (key > thr);
-    }
-    // exclusive scans of `iseq` and (later) `keep` over the first 128 threads
-    int x = iseq;
+  // ---- destination of every row, once for the whole request: thread t owns rows [t * RPT, (t + 1) * RPT).
+  // Two block-wide exclusive scans (ties, then kept rows); afterwards the copy loop needs one barrier per chunk.
+  int* dstpos = reinterpret_cast<int*>(keys);            // the keys are no longer needed once a row's flags are known
+  const int RPT = (S + SC_THREADS - 1) / SC_THREADS;
+  const int r_lo = min(S, tid * RPT), r_hi = min(S, r_lo + RPT);
+  auto block_exclusive = [&](int local) -> int {         // exclusive prefix of `local` over the threads of the CTA
+    int x = local;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int y = __shfl_up_sync(0xffffffffu, x, o);
@@ -194,37 +214,53 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
     }
     if (lane == 31) wsum[warp] = x;
     __syncthreads();
-    int eq_before = eq_seen + x - iseq;
-    for (int w = 0; w < warp; ++w) eq_before += wsum[w];
-    int eq_chunk = 0;
-    for (int w = 0; w < SC_THREADS / 32; ++w) eq_chunk += wsum[w];
+    int before = x - local;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
     __syncthreads();
-    // a tie is kept when it is among the last `need_eq` ties of the request
-    if (iseq && (eq_total - eq_before) <= need_eq) keep = 1;
-    x = keep;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+    return before;
+  };
+  int eq_mine = 0;
+  for (int r = r_lo; r < r_hi; ++r) eq_mine += (keys[r] == thr);
+  int eq_before = block_exclusive(eq_mine);
+  // a tie is kept when it is among the last `need_eq` ties of the request
+  int kept_mine = 0;
+  {
+    int e = eq_before;
+    for (int r = r_lo; r < r_hi; ++r) {
+      const uint32_t key = keys[r];
+      const bool tie = key == thr;
+      kept_mine += (key > thr) || (tie && (eq_total - e) <= need_eq);
+      e += tie;
     }
-    if (lane == 31) wsum[8 + warp] = x;
-    __syncthreads();
-    int pos = out_base + x - keep;
-    for (int w = 0; w < warp; ++w) pos += wsum[8 + w];
-    int kept_chunk = 0;
-    for (int w = 0; w < SC_THREADS / 32; ++w) kept_chunk += wsum[8 + w];
-    if (tid < SC_CHUNK) dstpos[tid] = keep ? pos : -1;
-    __syncthreads();
+  }
+  int pos = block_exclusive(kept_mine);
+  {
+    int e = eq_before;
+    for (int r = r_lo; r < r_hi; ++r) {
+      const uint32_t key = keys[r];
+      const bool tie = key == thr;
+      const bool keep = (key > thr) || (tie && (eq_total - e) <= need_eq);
+      e += tie;
+      dstpos[r] = keep ? pos : -1;                        // (row r's key is not read again)
+      pos += keep;
+    }
+  }
+  __syncthreads();
 
-    // move rows: read the whole chunk, then write it
+  // ---- move rows, 128 at a time: read the whole chunk, barrier, write it.  A row only ever moves towards the
+  // front, so the rows a chunk writes lie before the rows any LATER chunk reads: no barrier is needed between the
+  // writes of one chunk and the reads of the next.
+  constexpr int PIECES = D / 8;              // 16-byte pieces per row (K or V)
+  constexpr int PER_THREAD = (SC_CHUNK * 2 * PIECES) / SC_THREADS;
+  for (int c0 = 0; c0 < S; c0 += SC_CHUNK) {
     uint4 regs[PER_THREAD];
 #pragma unroll
     for (int j = 0; j < PER_THREAD; ++j) {
       const int piece = tid + j * SC_THREADS;
-      const int r = piece / (2 * PIECES), part = piece % (2 * PIECES);
+      const int r = c0 + piece / (2 * PIECES), part = piece % (2 * PIECES);
       regs[j] = make_uint4(0, 0, 0, 0);
-      if (dstpos[r] >= 0 && dstpos[r] != c0 + r) {
-        const bf16* src = row_ptr(part < PIECES ? kbase : vbase, c0 + r);
+      if (r < S && dstpos[r] >= 0 && dstpos[r] != r) {
+        const bf16* src = row_ptr(part < PIECES ? kbase : vbase, r);
         if (src != nullptr) regs[j] = reinterpret_cast<const uint4*>(src)[part % PIECES];
       }
     }
@@ -232,15 +268,12 @@ select_compact_kernel(bf16* __restrict__ pool, const float* __restrict__ scores,
 #pragma unroll
     for (int j = 0; j < PER_THREAD; ++j) {
       const int piece = tid + j * SC_THREADS;
-      const int r = piece / (2 * PIECES), part = piece % (2 * PIECES);
-      if (dstpos[r] >= 0 && dstpos[r] != c0 + r) {
+      const int r = c0 + piece / (2 * PIECES), part = piece % (2 * PIECES);
+      if (r < S && dstpos[r] >= 0 && dstpos[r] != r) {
         bf16* dst = row_ptr(part < PIECES ? kbase : vbase, dstpos[r]);
         if (dst != nullptr) reinterpret_cast<uint4*>(dst)[part % PIECES] = regs[j];
       }
     }
-    out_base += kept_chunk;
-    eq_seen += eq_chunk;
-    __syncthreads();
   }
 }
 
