@@ -45,13 +45,52 @@ __device__ __forceinline__ uint32_t tswz(int row, int chunk) {
   return uint32_t((chunk >> 3) * (DEC_TILE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
+// Split-KV without a second kernel: every CTA of a (request, KV head) counts itself in after its partial results are
+// written; the last one to arrive merges all splits of the group's query heads
+//     out[b, h, :] = sum_s w_s * part_o[b, h, s, :],  w_s = 2^(lse_s - max) / sum
+// and puts the counter back to zero for the next launch (also a replay from a CUDA graph).
+template <int D>
+__device__ __forceinline__ void decode_merge_last(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                  bf16* __restrict__ out, int* __restrict__ counters, int b, int hk,
+                                                  int G, int Hq, int Hkv, int splits) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(counters + b * Hkv + hk, 1);
+    s_last = old == splits - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += DEC_THREADS) {
+    const int r = idx / D, c = idx - r * D;
+    const long long bh = (long long)b * Hq + hk * G + r;
+    const float* lse = part_lse + bh * splits;
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, __ldcg(lse + s));
+    float acc = 0.f, den = 0.f;
+    if (mx != -INFINITY) {
+      for (int s = 0; s < splits; ++s) {
+        const float l = __ldcg(lse + s);
+        const float w = (l == -INFINITY) ? 0.f : exp2f(l - mx);
+        den += w;
+        acc += w * __ldcg(part_o + (bh * splits + s) * D + c);
+      }
+      acc /= den;
+    }
+    out[bh * D + c] = __float2bfloat16(acc);
+  }
+  if (threadIdx.x == 0) counters[b * Hkv + hk] = 0;
+}
+
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const bf16* __restrict__ q, int box_rows, const int* __restrict__ block_tables, const int* __restrict__ context_lens,
                    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_lse, int Hq,
                    int Hkv, int block_size, int max_blocks, int num_blocks, int splits, float scale_log2,
-                   uint32_t* status) {
+                   uint32_t* status, int* __restrict__ merge_counters) {
   constexpr int CH = D / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
   extern __shared__ uint8_t smem_raw[];
@@ -255,6 +294,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         if (c == 0) part_lse[((long long)b * Hq + hq) * splits + split] = -INFINITY;
       }
     }
+    if (splits > 1 && merge_counters != nullptr) decode_merge_last<D>(part_o, part_lse, out, merge_counters, b, hk, G, Hq, Hkv, splits);
     return;
   }
 
@@ -307,6 +347,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         part_lse[((long long)b * Hq + hq) * splits + split] = (ll > 0.f) ? (mm + log2f(ll)) : -INFINITY;
     }
   }
+  if (splits > 1 && merge_counters != nullptr) decode_merge_last<D>(part_o, part_lse, out, merge_counters, b, hk, G, Hq, Hkv, splits);
 }
 
 // out[b, h, :] = sum_s w_s * part_o[b, h, s, :],  w_s = 2^(lse_s - max) / sum
@@ -349,7 +390,7 @@ int decode_attn_pick_splits(int B, int Hkv, int max_ctx, int num_sms) {
 void launch_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                              const int* context_lens, void* out, float* part_o, float* part_lse, int B, int Hq,
                              int Hkv, int D, int block_size, int max_blocks, int num_blocks, int splits,
-                             float scale, uint32_t* status, cudaStream_t stream) {
+                             float scale, uint32_t* status, cudaStream_t stream, int* merge_counters) {
   if (B == 0) return;
   if (Hq % Hkv != 0 || Hq / Hkv > 16) throw std::runtime_error("decode attention: group size must divide and be <= 16");
   if (splits > 1 && (part_o == nullptr || part_lse == nullptr))
@@ -368,12 +409,14 @@ void launch_decode_attention(const void* q, const void* k_cache, const void* v_c
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     launch_pdl(PDL_DECODE_ATTN, kern, grid, dim3(DEC_THREADS), smem, stream, tk, tv, (const bf16*)q, box_rows, block_tables,
                context_lens, (bf16*)out, part_o, part_lse, Hq, Hkv, block_size, max_blocks, num_blocks, splits,
-               scale_log2, status);
+               scale_log2, status, merge_counters);
   };
   if (D == 128) launch(decode_attn_kernel<128>);
   else if (D == 64) launch(decode_attn_kernel<64>);
   else throw std::runtime_error("decode attention: head_dim must be 64 or 128");
-  if (splits > 1)
+  // `merge_counters` (zero between launches, B * Hkv words): the last split of a (request, KV head) merges in the
+  // attention kernel itself; without them a second kernel does
+  if (splits > 1 && merge_counters == nullptr)
     launch_pdl(PDL_DECODE_MERGE, decode_merge_kernel, dim3(B * Hq), dim3(128), 0, stream, (const float*)part_o, (const float*)part_lse,
                (bf16*)out, splits, D);
   cudaError_t e = cudaGetLastError();

@@ -18,7 +18,7 @@ namespace {
 using torch::Tensor;
 
 struct DeviceWorkspace {
-  Tensor gemm_scratch, gemm_counters, grid_sync, attn_o, attn_lse;
+  Tensor gemm_scratch, gemm_counters, grid_sync, attn_o, attn_lse, attn_counters;
   fc::StreamWorkspace raw;
 };
 struct DeviceState {
@@ -29,6 +29,7 @@ std::unordered_map<int, DeviceState> g_dev;
 std::unordered_map<uint64_t, int> g_stream_sms;
 std::mutex g_mu;
 
+using fc::ATTN_COUNTERS;
 using fc::ATTN_LSE_FLOATS;
 using fc::ATTN_WS_FLOATS;
 
@@ -61,6 +62,8 @@ DeviceWorkspace& workspace(int dev, cudaStream_t stream) {
   w.raw.grid_sync = reinterpret_cast<uint32_t*>(w.grid_sync.data_ptr<int>());
   w.raw.attn_o = w.attn_o.data_ptr<float>();
   w.raw.attn_lse = w.attn_lse.data_ptr<float>();
+  w.attn_counters = torch::zeros({int64_t(ATTN_COUNTERS)}, i32);
+  w.raw.attn_counters = w.attn_counters.data_ptr<int>();
   w.raw.status = reinterpret_cast<uint32_t*>(status.data_ptr<int>());
   return g_ws.emplace(key, std::move(w)).first->second;
 }
@@ -446,6 +449,18 @@ Tensor prefill_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, co
   return out;
 }
 
+// Split-KV decode attention merges its splits in the attention kernel itself (the last split of a (request, KV
+// head) to arrive does it) when FC_DECODE_MERGE_KERNEL=0; else the separate merge kernel runs.
+static int g_merge_in_kernel = -1;
+bool decode_merge_in_kernel() {
+  if (g_merge_in_kernel < 0) {
+    const char* e = std::getenv("FC_DECODE_MERGE_KERNEL");
+    g_merge_in_kernel = (e != nullptr && e[0] == '0') ? 1 : 0;
+  }
+  return g_merge_in_kernel == 1;
+}
+void set_decode_merge_in_kernel(bool on) { g_merge_in_kernel = on ? 1 : 0; }
+
 // splits <= 0: choose from the batch shape and `max_ctx`
 Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_tables,
                         const Tensor& context_lens, double scale, int64_t splits, int64_t max_ctx) {
@@ -467,7 +482,8 @@ Tensor decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, con
                               context_lens.data_ptr<int>(), out.data_ptr(), ws.attn_o.data_ptr<float>(),
                               ws.attn_lse.data_ptr<float>(), int(B), int(Hq), int(Hkv), int(D), int(kc.size(2)),
                               int(block_tables.size(1)), int(kc.size(0)), int(splits), float(scale),
-                              status_ptr(q.get_device()), at::cuda::getCurrentCUDAStream());
+                              status_ptr(q.get_device()), at::cuda::getCurrentCUDAStream(),
+                              (decode_merge_in_kernel() && B * Hkv <= ATTN_COUNTERS) ? ws.raw.attn_counters : nullptr);
   return out;
 }
 
@@ -575,6 +591,7 @@ void reset_sync_state(int64_t device) {
     // plain memsets on the raw pointers: the tensors may have been created under inference mode
     cudaMemset(kv.second.raw.grid_sync, 0, 4 * sizeof(int));
     cudaMemset(kv.second.raw.gemm_counters, 0, fc::gemm_counter_bytes());
+    cudaMemset(kv.second.raw.attn_counters, 0, size_t(ATTN_COUNTERS) * sizeof(int));
   }
 }
 
@@ -625,6 +642,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_scratch", [](int64_t device) { return workspace(int(device)).gemm_scratch; },
         "split-K scratch of the CURRENT stream of the device");
   m.def("prefill_attention", &prefill_attention);
+  m.def("set_decode_merge_in_kernel", &set_decode_merge_in_kernel);
+  m.def("decode_merge_in_kernel", &decode_merge_in_kernel);
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("context_lens"), py::arg("scale"), py::arg("splits") = 0,
         py::arg("max_ctx") = 0);

@@ -29,7 +29,7 @@ int decode_attn_pick_splits(int B, int Hkv, int max_ctx, int num_sms);
 void launch_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                              const int* context_lens, void* out, float* part_o, float* part_lse, int B, int Hq,
                              int Hkv, int D, int block_size, int max_blocks, int num_blocks, int splits,
-                             float scale, uint32_t* status, cudaStream_t stream);
+                             float scale, uint32_t* status, cudaStream_t stream, int* merge_counters = nullptr);
 void launch_prefill_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                               const int* cu_seqlens_q, const int* kv_lens, void* out, int num_seqs, int max_q_len,
                               int Hq, int Hkv, int D, int block_size, int max_blocks, int num_blocks, float scale,

@@ -18,11 +18,13 @@ struct StreamWorkspace {
   uint32_t* grid_sync = nullptr;     // [2] arrival count and generation of the in-kernel grid barrier
   float* attn_o = nullptr;           // ATTN_WS_FLOATS
   float* attn_lse = nullptr;         // ATTN_LSE_FLOATS
+  int* attn_counters = nullptr;      // ATTN_COUNTERS arrival counters of the split-KV merge, zero between launches
   uint32_t* status = nullptr;        // the device's status word
 };
 
 constexpr long long ATTN_WS_FLOATS = 4ll << 20;   // 16 MiB of split-KV partial outputs
 constexpr long long ATTN_LSE_FLOATS = 1ll << 18;
+constexpr long long ATTN_COUNTERS = 1ll << 16;    // (requests x KV heads) of one decode batch
 
 // Implemented in bindings.cpp (the memory is owned by torch tensors).
 const StreamWorkspace& stream_workspace(int device, cudaStream_t stream);

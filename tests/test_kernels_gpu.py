@@ -136,6 +136,43 @@ def test_decode_attention(D, Hq, Hkv, bs, lens, splits):
     assert (o.float() - want).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,bs,lens", [
+    (128, 32, 8, 16, [1, 17, 64, 65, 300]), (128, 8, 8, 256, [1000, 5]), (64, 4, 2, 16, [33, 129]),
+    (128, 8, 1, 32, [4000, 77, 640])])
+@pytest.mark.parametrize("splits", [0, 3, 5])
+def test_decode_attention_merge_in_the_attention_kernel(D, Hq, Hkv, bs, lens, splits):
+    """Split-KV where the last split of a (request, KV head) to arrive merges (no merge kernel): same results as
+    the fp32 statement, again on a second call (the arrival counters are back at zero) and from a CUDA graph."""
+    e = ops.ext()
+    before = e.decode_merge_in_kernel()
+    e.set_decode_merge_in_kernel(True)
+    try:
+        B = len(lens)
+        kc, vc, bt = _paged(B, lens, Hkv, D, bs)
+        q = _rand(B, Hq, D, seed=9)
+        cl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+        scale = D ** -0.5
+        want = ref.decode_attention(q.float(), kc.float(), vc.float(), bt, cl, scale)
+        o1 = ops.decode_attention(q, kc, vc, bt, cl, scale, {"splits": splits})
+        o2 = ops.decode_attention(q, kc, vc, bt, cl, scale, {"splits": splits})
+        _check_status()
+        assert (o1.float() - want).abs().max().item() < 2e-2 and torch.equal(o1, o2)
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            ops.decode_attention(q, kc, vc, bt, cl, scale, {"splits": splits})
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                og = ops.decode_attention(q, kc, vc, bt, cl, scale, {"splits": splits})
+            for _ in range(3):
+                g.replay()
+                stream.synchronize()
+                assert torch.equal(og, o1)
+        _check_status()
+    finally:
+        e.set_decode_merge_in_kernel(before)
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,bs,qlens,kvlens", [
     (128, 8, 2, 16, [5, 64, 130], [5, 64, 130]), (128, 4, 4, 256, [300], [300]),
     (64, 4, 2, 16, [128, 128], [128, 128]), (128, 8, 2, 32, [10, 100], [74, 228]),
