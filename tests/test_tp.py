@@ -57,8 +57,10 @@ def test_tp_gpu_fused_comm(tmp_path, world):
     one = _run(1, "cuda", str(tmp_path / "a.json"), port)
     many = _run(world, "cuda", str(tmp_path / "b.json"), port + 1)
     assert many["status"] == 0 and many["engine_status"] == 0
-    assert many["allreduce_max_err"] < 6e-2
-    assert many["fused_prefill_max_err"] < 8e-2
+    # absolute errors of bf16 results: sums over 8 ranks reach magnitudes where one bf16 step is 0.0625
+    step = max(1, world // 4)
+    assert many["allreduce_max_err"] < 6e-2 * step
+    assert many["fused_prefill_max_err"] < 8e-2 * step
     assert many["ranks_agree"] and many["local_logits"] and many["embedding_replicated"]
     # same engine with the one-shot limit lowered so that prefill takes the GEMM + reduce-scatter path
     big = _run(world, "cuda", str(tmp_path / "c.json"), port + 2, ["--one-shot-tokens", "64"])
