@@ -303,7 +303,8 @@ def run_ours(args):
                            compressions=llm.stats.compressions, lazy_triggers=llm.stats.lazy_triggers,
                            preemptions=llm.stats.preemptions, blocks_freed=llm.stats.blocks_freed,
                            prefill_steps=llm.stats.prefill_steps, decode_steps=llm.stats.decode_steps,
-                           **({"symmetric_memory": runner.fused_comm.runtime} if runner.fused_comm is not None else {})),
+                           **({"symmetric_memory": runner.fused_comm.runtime, "allreduce_form": runner.fused_comm.ar_form}
+                              if runner.fused_comm is not None else {})),
             "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
             "p99_ttft_s": round(percentile(ttft, 0.99), 4) if ttft else None,
             "output_tokens": out_tokens,

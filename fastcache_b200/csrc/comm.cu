@@ -50,8 +50,13 @@ constexpr int AR_MAX_CHUNKS = 4;      // H <= 256 * 4 * 8 = 8192
 // flag exchange publishes those stores, then every rank sums the `world` slots of its OWN buffer in rank order,
 // its own contribution from registers).  The push form takes the NVLink round trip of the loads out of the
 // critical path: the stores are posted and travel while the CTA is already waiting for the flags.
-constexpr int AR_PULL = 0, AR_MULTIMEM = 1, AR_PUSH = 2;
+constexpr int AR_PULL = 0, AR_MULTIMEM = 1, AR_PUSH = 2, AR_TWOSHOT = 3;
 
+__device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ void st_peer_16(void* p, const uint4& v) {
   asm volatile("st.global.relaxed.sys.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
@@ -139,8 +144,27 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
   if (threadIdx.x == 0) s_epoch = epochs[slot] + 1;
   __syncthreads();
   const uint32_t epoch = s_epoch;
-  const bool ok = peer_barrier(peers, slot, epoch, status);
-  if (threadIdx.x == 0) epochs[slot] = epoch;
+  bool ok = peer_barrier(peers, slot, epoch, status);
+  if (MODE == AR_TWOSHOT) {
+    // grid == T: CTA b owns token row b; rank (b % world) reduces it inside the switch and publishes the sum.
+    // Every rank joins the second exchange, also after a first one that ran out (the peers must not wait for it).
+    const int row = blockIdx.x;
+    if (ok && row % peers.world == peers.rank) {
+      const int chunks0 = H >> 3;
+      for (int idx = threadIdx.x; idx < chunks0; idx += AR_THREADS) {
+        const size_t off = (size_t)row * H + (size_t)idx * 8;
+        const uint4 sum = multimem_ld_reduce_bf16x8(mc_in + off);
+        multimem_st_16(const_cast<bf16*>(mc_in) + (size_t)peers.reduced_row0 * H + off, sum);
+      }
+      __threadfence_system();
+    }
+    __syncthreads();
+    const bool ok2 = peer_barrier(peers, slot, epoch + 1, status);
+    ok = ok && ok2;
+    if (threadIdx.x == 0) epochs[slot] = epoch + 1;
+  } else {
+    if (threadIdx.x == 0) epochs[slot] = epoch;
+  }
   if (!ok) return;                       // the host reads the status word and raises
 
   const int chunks = H >> 3;
@@ -156,6 +180,9 @@ allreduce_add_rmsnorm_kernel(CommPeers peers, int buf, const bf16* __restrict__ 
         float acc[8];
         if (MODE == AR_MULTIMEM) {
           unpack8f(multimem_ld_reduce_bf16x8(mc_in + off), acc);
+        } else if (MODE == AR_TWOSHOT) {
+          // the row's sum over all ranks, published by its owner into this rank's own buffer
+          unpack8f(ld_peer_16(peers.data[buf][peers.rank] + (size_t)peers.reduced_row0 * H + off), acc);
         } else if (MODE == AR_PUSH) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -236,7 +263,13 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
   // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
   const int grid = T < COMM_MAX_SLOTS ? T : COMM_MAX_SLOTS;
   cudaError_t e;
-  if (peers.slot_rows > 0) {
+  if (peers.reduced_row0 > 0 && mc_in != nullptr) {
+    if (T > peers.reduced_row0 || T > COMM_MAX_SLOTS)
+      throw std::runtime_error("allreduce (two-shot form): more token rows than the staging buffer holds");
+    e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<AR_TWOSHOT>, dim3(T), dim3(AR_THREADS), 0, stream, peers, buf,
+                   (const bf16*)mc_in, (bf16*)residual, (const bf16*)weight, (bf16*)out, T, H, eps, epochs, status,
+                   partial, splits, split_stride, (const bf16*)bias);
+  } else if (peers.slot_rows > 0) {
     if (T > peers.slot_rows || T > COMM_MAX_SLOTS)
       throw std::runtime_error("allreduce (push form): more token rows than a staging slot holds");
     e = launch_pdl(PDL_ALLREDUCE, allreduce_add_rmsnorm_kernel<AR_PUSH>, dim3(T), dim3(AR_THREADS), 0, stream, peers, buf,

@@ -20,6 +20,11 @@ struct CommPeers {
   // peer before the flag exchange and afterwards sums the slots of its own buffer, instead of fetching the
   // peers' rows with loads over NVLink after the exchange.
   int slot_rows;
+  // > 0: "two-shot" form through NVSwitch multicast.  Rows [reduced_row0, ...) of every staging buffer receive the
+  // reduced rows: the owner of a token row (row % world) sums all ranks' copies of it inside the switch
+  // (multimem.ld_reduce) and publishes the sum to every rank with one multimem.st; a second flag exchange tells
+  // the others that it is there.  Each rank then receives one row's worth of bytes per row instead of world - 1.
+  int reduced_row0;
 };
 
 // Candidate tables of the sampler over vocabulary shards: per rank [2][COMM_MAX_SLOTS][COMM_MAX_WORLD] 8-byte

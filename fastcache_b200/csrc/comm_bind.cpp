@@ -25,13 +25,17 @@ CommState g_comm;
 // slot_rows > 0: the staging buffers hold `world` slots of `slot_rows` rows and the one-shot all-reduce runs in
 // its push form (comm.cu)
 void comm_init(int64_t rank, int64_t world, const std::vector<int64_t>& data0, const std::vector<int64_t>& data1,
-               const std::vector<int64_t>& flags, int64_t mc0, int64_t mc1, int64_t device, int64_t slot_rows) {
+               const std::vector<int64_t>& flags, int64_t mc0, int64_t mc1, int64_t device, int64_t slot_rows,
+               int64_t reduced_row0) {
   TORCH_CHECK(world >= 2 && world <= fc::COMM_MAX_WORLD, "world size must be in [2, ", fc::COMM_MAX_WORLD, "]");
   TORCH_CHECK((int64_t)data0.size() == world && (int64_t)data1.size() == world && (int64_t)flags.size() == world,
               "need one pointer per rank");
   g_comm.peers.world = int(world);
   g_comm.peers.rank = int(rank);
   g_comm.peers.slot_rows = int(slot_rows);
+  // the two-shot form needs the multicast addresses of both staging buffers
+  g_comm.peers.reduced_row0 = (mc0 != 0 && mc1 != 0) ? int(reduced_row0) : 0;
+  TORCH_CHECK(slot_rows == 0 || reduced_row0 == 0, "choose one form of the one-shot all-reduce");
   for (int i = 0; i < world; ++i) {
     g_comm.peers.data[0][i] = reinterpret_cast<__nv_bfloat16*>(data0[i]);
     g_comm.peers.data[1][i] = reinterpret_cast<__nv_bfloat16*>(data1[i]);
@@ -91,7 +95,8 @@ Tensor allreduce_add_rmsnorm(int64_t buf, Tensor residual, const Tensor& weight,
   TORCH_CHECK(buf == 0 || buf == 1, "buf must be 0 or 1");
   c10::cuda::CUDAGuard guard(residual.device());
   Tensor out = torch::empty_like(residual);
-  const void* mc = (use_multimem && g_comm.mc[buf] != 0) ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
+  const void* mc = ((use_multimem || g_comm.peers.reduced_row0 > 0) && g_comm.mc[buf] != 0)
+                       ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
   const float* part = nullptr;
   const void* bptr = nullptr;
   if (partial.has_value() && partial->defined() && splits > 1) {
@@ -147,10 +152,11 @@ Tensor linear_allreduce_add_rmsnorm(const Tensor& x, const Tensor& w, const c10:
   gw.counters = sw.gemm_counters;
   gw.status = reinterpret_cast<uint32_t*>(status.data_ptr<int>());
   gw.grid_sync = sw.grid_sync;
-  const void* mc = (use_multimem && g_comm.mc[buf] != 0) ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
+  const void* mc = ((use_multimem || g_comm.peers.reduced_row0 > 0) && g_comm.mc[buf] != 0)
+                       ? reinterpret_cast<const void*>(g_comm.mc[buf]) : nullptr;
   uint32_t* epochs = reinterpret_cast<uint32_t*>(g_comm.epochs.data_ptr<int>());
   const int sm_limit = fc::stream_sm_limit(stream);
-  if (fc::fused_epilogues_enabled() && g_comm.peers.slot_rows == 0) {
+  if (fc::fused_epilogues_enabled() && g_comm.peers.slot_rows == 0 && g_comm.peers.reduced_row0 == 0) {
     fc::SkinnyFused f;
     f.epi = fc::EPI_AR_ADD_NORM;
     f.residual = residual.data_ptr();
@@ -282,7 +288,7 @@ void wait_gathered(int64_t epoch, Tensor status) {
 void register_comm(pybind11::module_& m) {
   m.def("comm_init", &comm_init, pybind11::arg("rank"), pybind11::arg("world"), pybind11::arg("data0"),
         pybind11::arg("data1"), pybind11::arg("flags"), pybind11::arg("mc0"), pybind11::arg("mc1"),
-        pybind11::arg("device"), pybind11::arg("slot_rows") = 0);
+        pybind11::arg("device"), pybind11::arg("slot_rows") = 0, pybind11::arg("reduced_row0") = 0);
   m.def("comm_shutdown", &comm_shutdown);
   m.def("sample_exchange_init", &sample_exchange_init);
   m.def("sample_exchange", &sample_exchange);

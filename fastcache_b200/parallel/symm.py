@@ -57,10 +57,17 @@ class FusedComm:
         self.tp_multicast = False
         self.epoch = 0
         self._gather = None                 # (epoch, chunk_rows, T) of the rows now arriving in xg
-        # push form of the one-shot all-reduce (FC_AR_PUSH=1): every staging buffer holds one slot per source rank
-        # (one CTA per token row, so at most MAX_SLOTS rows; larger one-shot limits keep the fetching form)
-        self.push = os.environ.get("FC_AR_PUSH", DEFAULT_AR_PUSH) == "1" and one_shot_tokens <= MAX_SLOTS
-        slots = self.world if self.push else 1
+        # form of the decode-size all-reduce (FC_AR_FORM): "push" (default: every rank stores its row into a slot of
+        # every peer's buffer before the flag exchange), "pull" (rows fetched after it), "twoshot" (the owner of a
+        # row sums it inside the switch and publishes it with one multicast store; needs multicast addresses)
+        form = os.environ.get("FC_AR_FORM", "")
+        if not form:
+            form = "push" if os.environ.get("FC_AR_PUSH", DEFAULT_AR_PUSH) == "1" else "pull"
+        if form not in ("push", "pull", "twoshot"):
+            raise ValueError("FC_AR_FORM must be push, pull or twoshot")
+        if one_shot_tokens > MAX_SLOTS and form != "pull":
+            form = "pull"                  # one CTA per token row: at most MAX_SLOTS rows
+        slots = {"pull": 1, "push": self.world, "twoshot": max(2, self.world)}[form]
         shapes = [((one_shot_tokens * slots, hidden), bf16), ((one_shot_tokens * slots, hidden), bf16),
                   ((MAX_SLOTS * MAX_WORLD,), torch.int32), ((ext().sample_cells_per_rank(),), torch.int64)]
         if max_tokens > one_shot_tokens:
@@ -74,9 +81,13 @@ class FusedComm:
         if use_multimem is None:
             use_multimem = os.environ.get("FC_MULTIMEM", "0") == "1"
         self.has_multicast = bool(mc[0] and mc[1])
-        self.use_multimem = bool(use_multimem and self.has_multicast and not self.push)
+        if form == "twoshot" and not self.has_multicast:
+            form = "push"                  # no NVSwitch multicast on this set of GPUs
+        self.ar_form = form
+        self.push = form == "push"
+        self.use_multimem = bool(use_multimem and self.has_multicast and form == "pull")
         ext().comm_init(self.rank, self.world, ptrs[0], ptrs[1], ptrs[2], mc[0], mc[1], index,
-                        one_shot_tokens if self.push else 0)
+                        one_shot_tokens if form == "push" else 0, one_shot_tokens if form == "twoshot" else 0)
         ext().sample_exchange_init(ptrs[3])
         self.status = ext().status_tensor(index)
         self.cur = 0
