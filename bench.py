@@ -80,6 +80,7 @@ MODEL_LABEL = {
 }
 
 
+DECODE_STEPS_PER_CALL = 1
 SAMPLING_TEMPERATURE = 0.6          # the reference's benchmarks sample at 0.6 (bench_llava.py:54-117)
 COMPRESSION_LABEL = {
     "knorm_ref": "knorm keep 50% (reference engine-native variant)",
@@ -241,6 +242,7 @@ def run_ours(args):
     llm = LLM(dict(hf), tensor_parallel_size=world, device=f"cuda:{local_rank}", kvcache_block_size=256,
               max_model_len=p_len + o_len + 256, max_num_seqs=max(n_req, 8), max_num_batched_tokens=32768,
               gpu_memory_utilization=args.mem_util, seed=0, prefix_caching=False,
+              decode_steps_per_call=args.decode_steps,
               **({"num_kvcache_blocks": args.kv_blocks} if args.kv_blocks > 0 else {}), **comp_kw)
     runner = llm.model_runner
     sp = SamplingParams(temperature=SAMPLING_TEMPERATURE, max_tokens=o_len, ignore_eos=True)
@@ -303,6 +305,7 @@ def run_ours(args):
                            compressions=llm.stats.compressions, lazy_triggers=llm.stats.lazy_triggers,
                            preemptions=llm.stats.preemptions, blocks_freed=llm.stats.blocks_freed,
                            prefill_steps=llm.stats.prefill_steps, decode_steps=llm.stats.decode_steps,
+                           decode_steps_per_call=args.decode_steps,
                            **({"symmetric_memory": runner.fused_comm.runtime, "allreduce_form": runner.fused_comm.ar_form}
                               if runner.fused_comm is not None else {})),
             "p50_ttft_s": round(percentile(ttft, 0.5), 4) if ttft else None,
@@ -652,6 +655,9 @@ def main():
                     help="compression right after prefill on the main stream, on a compression stream, or a few "
                          "layers per decode step beside decode; auto: a compression stream when the SMs are split "
                          "(measured best: the split only pays when compression runs beside the main stream), else prefill")
+    ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS_PER_CALL,
+                    help="decode steps launched back to back per engine step while nothing is waiting (one host "
+                         "synchronisation per launch group); 1 = one step at a time")
     ap.add_argument("--check", action="store_true",
                     help="instead of timing: first tokens under --gpus N against the same prompts on one GPU "
                          "(shrunken config, greedy)")

@@ -70,8 +70,8 @@ struct TpBuffers {
   __nv_bfloat16* xg_mc = nullptr;
 };
 
-// The row-parallel GEMM reduces each 128-row group as soon as all ranks have delivered it (on unless
-// FC_TP_PIPELINE=0); off: one reduction phase after the GEMM.
+// The row-parallel GEMM reduces each 128-row group as soon as all ranks have delivered it (only when
+// FC_TP_PIPELINE=1 or after set_tp_pipeline(true)); otherwise one reduction phase after the GEMM.
 bool tp_pipeline_enabled();
 void set_tp_pipeline(bool on);
 // The pipelined form sums through the switch (multimem.ld_reduce / multimem.st) when the buffers have multicast

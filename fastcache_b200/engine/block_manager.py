@@ -157,6 +157,17 @@ class BlockManager:
         needs_new = (seq.kv_cache_len % self.block_size == 1) or self.block_size == 1
         return len(self.free_block_ids) >= int(needs_new)
 
+    def blocks_short_for(self, seq: Sequence, extra_rows: int) -> int:
+        """Blocks still missing from the table of `seq` if it is to hold `extra_rows` rows beyond the one its next
+        decode step writes (several decode steps launched back to back)."""
+        need = -(-(seq.kv_cache_len + extra_rows) // self.block_size)
+        return max(0, need - len(seq.block_table))
+
+    def reserve_rows(self, seq: Sequence, extra_rows: int) -> None:
+        """Grow the block table for `extra_rows` more rows (the caller has checked that the pool has the blocks)."""
+        for _ in range(self.blocks_short_for(seq, extra_rows)):
+            seq.block_table.append(self._pop_free().block_id)
+
     def may_append(self, seq: Sequence) -> None:
         """Grow the block table for the row that this decode step writes.
 

@@ -167,6 +167,9 @@ class LLMEngine:
         # meanwhile appended at the end); "hold" = in place, the request sits out of the decode batches until
         # its last layer is done (no extra blocks).  Shadow needs merge compression and free blocks for the
         # compressed copy, and falls back to hold per request when it has neither.
+        # several decode steps per engine step, launched back to back with one host synchronisation (only while no
+        # request is waiting, compressing or about to finish; see `step`)
+        self.decode_steps_per_call = max(1, int(config.extra.get("decode_steps_per_call", 1)))
         if decode_overlap not in ("shadow", "hold"):
             raise ValueError("decode_overlap must be 'shadow' or 'hold'")
         self.decode_overlap = decode_overlap
@@ -311,15 +314,15 @@ class LLMEngine:
         return [(table[i], max(lo - i * bs, 0), min(hi - i * bs, bs))
                 for i in range(max(lo, 0) // bs, min(-(-hi // bs), len(table)))] if hi > lo else []
 
-    def _note_step(self, seqs: Seq[Sequence], is_prefill: bool) -> None:
+    def _note_step(self, seqs: Seq[Sequence], is_prefill: bool, decode_steps: int = 1) -> None:
         reads, writes = [], []
         for s in seqs:
             if is_prefill:
                 end = s.logical_len if s.prefill_end is None else int(s.prefill_end)
                 first = s.prefill_start
             else:
-                end = s.kv_cache_len
-                first = end - 1
+                first = s.kv_cache_len - 1
+                end = s.kv_cache_len + decode_steps - 1
             reads += self._rows(s.block_table, 0, first)
             writes += self._rows(s.block_table, first, end)
         self.stream_check.launch(self.model_runner.main_stream, reads, writes,
@@ -638,10 +641,14 @@ class LLMEngine:
                                    sum((s.logical_len if s.prefill_end is None else s.prefill_end) - s.prefill_start
                                        for s in seqs) if is_prefill else len(seqs),
                                    len(bm.free_block_ids), len(bm.blocks), self.stats.compressions, r.main_stream)
+        multi = None
+        k = self._decode_steps_now(seqs, is_prefill, ctl)
         if self.stream_check is not None:
-            self._note_step(seqs, is_prefill)
+            self._note_step(seqs, is_prefill, k)
         with nvtx_range("prefill" if is_prefill else "decode"):
-            tokens = r.run(seqs, is_prefill)
+            if k > 1:
+                multi = r.run_decode_steps(seqs, k)
+            tokens = multi[0] if multi is not None else r.run(seqs, is_prefill)
         if self.stream_check is not None:
             self.stream_check.synchronize(r.main_stream)     # the sampled tokens were read back on the host
         if r.last_status:
@@ -684,6 +691,13 @@ class LLMEngine:
                     if s.compression_state is CompressionState.PENDING:
                         s.compression_state = CompressionState.NONE
         finished = sch.postprocess(seqs, tokens)
+        extra_tokens = 0
+        if multi is not None:
+            # the later steps of the same launch: a request that finished in between takes no more tokens
+            for toks in multi[1:]:
+                live = [(s, t) for s, t in zip(seqs, toks) if not s.is_finished]
+                extra_tokens += len(live)
+                finished += sch.postprocess([s for s, _ in live], [t for _, t in live])
         for s in finished:
             s.finish_time = now
         st = self.stats
@@ -692,11 +706,34 @@ class LLMEngine:
             st.prefill_steps += 1
             st.prefill_tokens += n_tok
         else:
-            st.decode_steps += 1
-            st.decode_tokens += len(seqs)
+            st.decode_steps += len(multi) if multi is not None else 1
+            st.decode_tokens += len(seqs) + extra_tokens
+            n_tok -= extra_tokens
         outputs = [(s.seq_id, s.completion_token_ids) for s in finished]
         self._last_finished = finished
         return outputs, n_tok
+
+    def _decode_steps_now(self, seqs: Seq[Sequence], is_prefill: bool, ctl) -> int:
+        """How many decode steps this engine step launches back to back.  More than one only when nothing else
+        could want the next step: no request waiting for prefill, none compressing or queued for it, no controller,
+        every request of the batch with that many tokens still to produce, and blocks for the extra rows."""
+        k = self.decode_steps_per_call
+        sch = self.scheduler
+        if (k < 2 or is_prefill or ctl is not None or sch.waiting or self._pending or sch.compress_queue
+                or self.compression_mode == "lazy" or len(seqs) < len(sch.running)):
+            return 1
+        if sch.block_manager.prefix_caching and not all(s.is_compressed or s.has_image for s in seqs):
+            return 1                     # filled blocks of these requests are published for prefix reuse step by step
+        k = min(k, min(s.max_tokens - s.num_completion_tokens for s in seqs))
+        k = min(k, min(self.config.max_model_len - s.kv_cache_len for s in seqs) + 1)
+        if k < 2:
+            return 1
+        bm = sch.block_manager
+        if sum(bm.blocks_short_for(s, k - 1) for s in seqs) > bm.num_free_blocks:
+            return 1
+        for s in seqs:
+            bm.reserve_rows(s, k - 1)
+        return k
 
     # ---------------------------------------------------------- controller timing
     def _begin_timing(self, ctl):

@@ -491,6 +491,78 @@ class ModelRunner:
     def _temperatures(self, seqs: Seq[Sequence]) -> torch.Tensor:
         return self._to_dev(np.asarray([s.temperature for s in seqs], dtype=np.float32), torch.float32)
 
+    @torch.inference_mode()
+    def run_decode_steps(self, seqs: Seq[Sequence], k: int) -> Optional[List[List[int]]]:
+        """`k` decode steps launched back to back, one host synchronisation at the end: returns the k lists of
+        sampled tokens, or None when the batch cannot take the static-buffer path (the caller then steps once).
+
+        Positions, context lengths and slots of the later steps do not depend on the sampled tokens, so the host
+        prepares them for all k steps at once; between the steps only device-side copies run (the sampled tokens
+        become the next input ids, the step's metadata rows go into the graph's static buffers).  The block tables
+        must already cover `k - 1` rows beyond the one the first step writes."""
+        if self.enforce_eager or k < 2:
+            return None
+        n = len(seqs)
+        bucket = self._graph_bucket(n)
+        ids, pos, slots, lens, bt = self.prepare_decode(seqs)
+        if bucket is None or bt.shape[1] > self.graph_vars["block_tables"].shape[1]:
+            return None
+        bs = self.block_size
+        steps = np.arange(k, dtype=np.int64)[:, None]
+        pos_k = np.zeros((k, bucket), dtype=np.int64)
+        lens_k = np.zeros((k, bucket), dtype=np.int32)
+        slots_k = np.full((k, bucket), -1, dtype=np.int32)
+        pos_k[:, :n] = pos[None, :] + steps
+        lens_k[:, :n] = lens[None, :].astype(np.int64) + steps
+        rows = lens_k[:, :n].astype(np.int64) - 1
+        slots_k[:, :n] = bt[np.arange(n)[None, :], rows // bs].astype(np.int64) * bs + rows % bs
+        cm = torch.cuda.stream(self.main_stream) if self.main_stream is not None else _Null()
+        with cm:
+            local = self.local_logits and self.head is not None
+            gv, h = self.graph_vars, self._staging
+            h["input_ids"][:n] = torch.from_numpy(ids)
+            h["input_ids"][n:bucket] = 0
+            h["block_tables"][:bucket].fill_(0)
+            h["block_tables"][:n, : bt.shape[1]] = torch.from_numpy(np.maximum(bt, 0))
+            for key in ("input_ids", "block_tables"):
+                gv[key][:bucket].copy_(h[key][:bucket], non_blocking=True)
+                if self.device.type == "cuda":
+                    self.io["h2d_bytes"] += h[key][:bucket].numel() * h[key].element_size()
+            pos_d = self._to_dev(pos_k, torch.int64)
+            lens_d = self._to_dev(lens_k, torch.int32)
+            slots_d = self._to_dev(slots_k, torch.int32)
+            temps = self._temperatures(seqs)
+            if self.timer is not None:
+                self.timer.start(self.main_stream)
+            outs = []
+            for j in range(k):
+                gv["positions"][:bucket].copy_(pos_d[j], non_blocking=True)
+                gv["context_lens"][:bucket].copy_(lens_d[j], non_blocking=True)
+                gv["slot_mapping"][:bucket].copy_(slots_d[j], non_blocking=True)
+                if j > 0:
+                    gv["input_ids"][:n].copy_(outs[-1][:n], non_blocking=True)
+                self._replay(bucket)
+                logits = gv["logits"][:n]
+                if local:
+                    tokens = self.sampler.forward_sharded(logits, temps, self.fused_comm, self.head.vocab_start,
+                                                          self.head.num_embeddings)
+                else:
+                    if self.local_logits:
+                        logits = tpmod.tp_all_gather(logits, dim=-1)[:, : self.text_config.vocab_size]
+                    tokens = self.sampler(logits, temps, with_status=True)
+                outs.append(tokens)
+            if self.timer is not None:
+                self.timer.stop(self.main_stream)
+            table = torch.stack(outs).tolist()
+            self.io["d2h_bytes"] += 8 * k * (n + 1)
+        reset_context()
+        self.last_status = 0
+        for row in table:
+            code = int(row.pop())
+            if code and not self.last_status:
+                self.last_status = code
+        return table
+
     def run(self, seqs: Seq[Sequence], is_prefill: bool, **_ignored) -> List[int]:
         """One model step for a batch; returns the sampled token per request."""
         cm = torch.cuda.stream(self.main_stream) if self.main_stream is not None else _Null()

@@ -81,3 +81,20 @@ def test_multimodal_request_on_gpu_matches_cpu_first_token(make_cfg, img_tok):
         llm.exit()
     assert rows["cuda"] == rows["cpu"] and len(outs["cuda"]) == 6
     assert outs["cuda"][0] == outs["cpu"][0], (outs["cuda"], outs["cpu"])
+
+
+def test_multi_step_decode_matches_single_steps_on_gpu():
+    """Several graph replays per engine step with the sampled tokens fed back on the device: same tokens as one
+    step at a time, greedy and sampled (the sampler's step counter advances once per decode step either way)."""
+    for temperature in (0.0, 0.7):
+        outs = []
+        for k in (1, 4):
+            llm = LLM(_cfg(), device="cuda", kvcache_block_size=32, num_kvcache_blocks=128, max_model_len=512,
+                      max_num_seqs=8, enforce_eager=False, init_device="cpu", prefix_caching=False, seed=5,
+                      decode_steps_per_call=k)
+            sps = [SamplingParams(temperature=temperature, max_tokens=m, ignore_eos=True) for m in (17, 3, 12, 9, 20)]
+            out = llm.generate(_prompts(), sps)
+            outs.append([o["token_ids"] for o in out])
+            assert llm.model_runner.read_device_status() == 0
+            llm.exit()
+        assert outs[0] == outs[1]

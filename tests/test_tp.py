@@ -62,6 +62,10 @@ def test_tp_gpu_fused_comm(tmp_path, world):
     assert many["allreduce_max_err"] < 6e-2 * step
     assert many["fused_prefill_max_err"] < 8e-2 * step
     assert many["ranks_agree"] and many["local_logits"] and many["embedding_replicated"]
+    # several decode steps per launch (sampled tokens fed back on the device, one candidate exchange per step)
+    multi = _run(world, "cuda", str(tmp_path / "d.json"), port + 3, ["--decode-steps", "3"])
+    assert multi["status"] == 0 and multi["engine_status"] == 0 and multi["ranks_agree"]
+    assert multi["tokens"] == many["tokens"] and multi["sampled"] == many["sampled"]
     # same engine with the one-shot limit lowered so that prefill takes the GEMM + reduce-scatter path
     big = _run(world, "cuda", str(tmp_path / "c.json"), port + 2, ["--one-shot-tokens", "64"])
     assert big["status"] == 0 and big["engine_status"] == 0 and big["ranks_agree"]

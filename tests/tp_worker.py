@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--one-shot-tokens", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=0, help="chunked_prefill_tokens (with a 64-token step budget)")
     ap.add_argument("--shard-embedding", action="store_true", help="vocabulary-parallel embedding table + all-reduce")
+    ap.add_argument("--decode-steps", type=int, default=1, help="decode steps launched back to back per engine step")
     a = ap.parse_args()
     if a.shard_embedding:
         from fastcache_b200.layers import embed_head
@@ -95,6 +96,7 @@ def main():
     llm = LLM(cfg, device=device, dtype="bf16" if a.device == "cuda" else "fp32", tensor_parallel_size=world,
               kvcache_block_size=16, num_kvcache_blocks=128, max_model_len=256, max_num_seqs=8,
               enforce_eager=False, init_device="cpu", fused_comm_tokens=a.one_shot_tokens,
+              decode_steps_per_call=a.decode_steps, prefix_caching=a.decode_steps < 2,
               **({"chunked_prefill_tokens": a.chunk, "max_num_batched_tokens": 64} if a.chunk else {}))
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (9, 40, 77, 120)]
