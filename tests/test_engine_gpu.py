@@ -98,3 +98,64 @@ def test_multi_step_decode_matches_single_steps_on_gpu():
             assert llm.model_runner.read_device_status() == 0
             llm.exit()
         assert outs[0] == outs[1]
+
+
+def test_chunked_prefill_on_gpu_matches_unsplit_prefill():
+    """A prompt prefetched in pieces (the prefill kernels' cached-prefix path, queries shorter than the keys) against
+    the same prompt in one piece on the GPU and against the fp32 CPU engine: the first sampled token is a pure
+    prefill result and agrees for all prompts but at most one (bf16 near-ties)."""
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 2048, (n,), generator=g).tolist() for n in (300, 40, 150, 90, 260)]
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+
+    def run(device, budget, chunk, dtype="auto"):
+        llm = LLM(_cfg(), device=device, dtype=dtype, kvcache_block_size=32, num_kvcache_blocks=128,
+                  max_model_len=512, max_num_seqs=8, enforce_eager=True, init_device="cpu", prefix_caching=False,
+                  max_num_batched_tokens=budget, chunked_prefill_tokens=chunk)
+        out = [o["token_ids"] for o in llm.generate(prompts, sp)]
+        steps = llm.stats.prefill_steps
+        bm = llm.scheduler.block_manager
+        assert bm.num_free_blocks == bm.num_blocks
+        if device == "cuda":
+            assert llm.model_runner.read_device_status() == 0
+        llm.exit()
+        return out, steps
+
+    pieces, n_pieces = run("cuda", 128, 32)
+    whole, n_whole = run("cuda", 4096, 0)
+    oracle, _ = run("cpu", 4096, 0, "fp32")
+    assert n_whole == 1 and n_pieces > 5
+    assert sum(a[0] == b[0] for a, b in zip(pieces, whole)) >= len(prompts) - 1, (pieces, whole)
+    assert sum(a[0] == b[0] for a, b in zip(pieces, oracle)) >= len(prompts) - 1, (pieces, oracle)
+
+
+@pytest.mark.parametrize("mode", ["compressed", "original"])
+def test_position_mode_with_graph_decode_on_gpu(mode):
+    """Tokens decoded after an eviction take their rotary position from the KV length or from the true index; the
+    CUDA-graph decode path feeds the same positions as the eager one and samples the same tokens."""
+    outs, fed = [], []
+    for eager in (True, False):
+        llm = LLM(_cfg(), device="cuda", kvcache_block_size=32, num_kvcache_blocks=128, max_model_len=512,
+                  max_num_seqs=8, enforce_eager=eager, init_device="cpu", prefix_caching=False,
+                  enable_compression=True, compression_backend="kvpress", kvpress_method="knorm",
+                  compression_factor=2, compression_pipeline="prefill", position_mode=mode)
+        inner, seen = llm.model_runner.prepare_decode, []
+
+        def spy(seqs, inner=inner, seen=seen):
+            out = inner(seqs)
+            seen.append([(len(s.prompt_token_ids), int(p), int(n)) for s, p, n in zip(seqs, out[1], out[3])])
+            return out
+
+        llm.model_runner.prepare_decode = spy
+        out = llm.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+        assert llm.model_runner.read_device_status() == 0 and llm.stats.compressions == len(out)
+        outs.append([o["token_ids"] for o in out])
+        fed.append(seen)
+        llm.exit()
+    assert outs[0] == outs[1] and fed[0] == fed[1]
+    for step in fed[0]:
+        for prompt_len, pos, kv in step:
+            if mode == "compressed":
+                assert pos == kv - 1
+            else:
+                assert pos >= prompt_len and pos > kv - 1
