@@ -394,19 +394,48 @@ rope_qknorm_store_d128_kernel(const bf16* __restrict__ qkv, const long long* __r
 // argmax(softmax(l / T) / E) with E ~ Exp(1) is the same draw: log p_j - log E_j.
 // out has B + 1 entries: the last one receives the device status word, so the host learns about a wait that
 // ran out (or a bad index) with the tokens it reads back every step anyway.
-__global__ void __launch_bounds__(1024)
+// One row is shared by a cluster of SAMPLE_SPLIT CTAs (a quarter of the vocabulary each, so that 128 rows fill
+// 148 SMs several times over instead of leaving 20 idle and the rest with one CTA); the CTAs hand their
+// candidates to the first one through distributed shared memory.  The draw does not depend on the split: the
+// noise is a function of the global index and ties go to the lower index.
+constexpr int SAMPLE_SPLIT = 4;
+constexpr int SAMPLE_THREADS = 512;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const bf16* __restrict__ logits, const float* __restrict__ temps, long long* __restrict__ out,
               int V, long long ld, uint32_t seed, int vocab_offset, int v_limit, const uint32_t* status) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
+  __shared__ __align__(8) uint2 s_cand[SAMPLE_SPLIT];   // (value bits, global index) by CTA of the cluster; used in CTA 0
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x;
+  const uint32_t part = cluster_ctarank(), parts = cluster_nctarank();
+  // slices start at multiples of 8 entries: the 16-byte loads of a slice stay aligned when the row is
+  const int per = ((V + int(parts) * 8 - 1) / (int(parts) * 8)) * 8;
+  const int j0 = min(V, int(part) * per), j1 = min(V, j0 + per);
   float best;
   int best_i;
-  sample_row_best(logits + (long long)b * ld, V, vocab_offset, v_limit, temps[b], sample_row_seed(seed, b), s_val,
-                  s_idx, best, best_i);
+  sample_row_best(logits + (long long)b * ld + j0, j1 - j0, vocab_offset + j0, v_limit, temps[b],
+                  sample_row_seed(seed, b), s_val, s_idx, best, best_i);
   if (threadIdx.x == 0) {
+    const uint32_t cell = cluster_map_shared(smem_u32(&s_cand[part]), 0);
+    asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(cell), "r"(__float_as_uint(best)), "r"(best_i)
+                 : "memory");
+  }
+  cluster_sync();
+  if (part == 0 && threadIdx.x == 0) {
+    best = -INFINITY;
+    best_i = 0x7fffffff;
+    for (uint32_t r = 0; r < parts; ++r) {
+      const float v = __uint_as_float(s_cand[r].x);
+      const int i = int(s_cand[r].y);
+      if (sample_better(v, i, best, best_i)) {
+        best = v;
+        best_i = i;
+      }
+    }
+    // a row without a single admissible entry (every index >= v_limit) yields index 0x7fffffff
     out[b] = best_i;
     if (b == 0 && status != nullptr)
       out[gridDim.x] = (long long)(*reinterpret_cast<const volatile uint32_t*>(status) & ST_CODE_MASK);
@@ -471,8 +500,9 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
                    cudaStream_t s, int vocab_offset, int v_limit, const uint32_t* status) {
   if (B == 0) return;
-  launch_pdl(PDL_SAMPLE, sample_kernel, dim3(B), dim3(1024), 0, s, (const bf16*)logits, (const float*)temps, (long long*)out, V,
-             ld, seed, vocab_offset, v_limit < 0 ? vocab_offset + V : v_limit, status);
+  launch_pdl_cluster(PDL_SAMPLE, sample_kernel, dim3(B, SAMPLE_SPLIT), dim3(SAMPLE_THREADS), 0, s, SAMPLE_SPLIT,
+                     (const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed, vocab_offset,
+                     v_limit < 0 ? vocab_offset + V : v_limit, status);
 }
 
 }  // namespace fc

@@ -87,6 +87,71 @@ def test_silu_embedding_sample():
     assert torch.all(ops.sample(peaked, t1, seed=9) == 123)
 
 
+def _mix32(x):
+    m = 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & m
+    x = x ^ (x >> 15)
+    x = (x * 0x846CA68B) & m
+    return x ^ (x >> 16)
+
+
+@pytest.mark.parametrize("B,V,ld,offset,limit", [(9, 5000, 5000, 0, -1), (5, 151936, 151936, 0, -1),
+                                                 (7, 4099, 4104, 0, -1), (6, 4096, 4096, 8192, 10000),
+                                                 (3, 24, 24, 0, -1)])
+def test_sampler_draw_matches_its_statement(B, V, ld, offset, limit):
+    """token = argmax_j logit_j / T + Gumbel(seed, row, global index j): the same draw from the PyTorch statement of
+    the hash, whichever CTA of the row's cluster holds the winner (rows that are not a multiple of the slice, a row
+    stride larger than the row, a vocabulary shard with padding at its end, a row shorter than one slice)."""
+    seed = 77
+    logits = (_rand(B, ld, seed=11) * 3)[:, :V]
+    temps = torch.tensor([0.0, 0.6, 1.0, 0.8, 1.3, 0.0, 0.9, 0.7, 1.1][:B], device=DEV)
+    got = ops.sample(logits, temps, seed=seed, vocab_offset=offset, v_limit=limit)
+    torch.cuda.synchronize()
+    gj = torch.arange(V, device=DEV, dtype=torch.int64) + offset
+    for b in range(B):
+        row_seed = _mix32(torch.tensor((seed ^ (b * 0x9E3779B9)) & 0xFFFFFFFF, device=DEV, dtype=torch.int64))
+        r = _mix32((row_seed + gj) & 0xFFFFFFFF)
+        u = ((r >> 9).double() + 0.5) / 8388608.0
+        t = float(temps[b])
+        v = logits[b].double()
+        if t > 0:
+            v = v / t - torch.log(-torch.log(u))
+        if limit >= 0:
+            v = torch.where(gj < limit, v, torch.full_like(v, -float("inf")))
+        tok = int(got[b]) - offset
+        assert 0 <= tok < V and (limit < 0 or int(got[b]) < limit)
+        if t == 0:
+            assert tok == int((v == v.max()).nonzero()[0])          # the lowest index among equal logits
+        else:
+            assert float(v.max() - v[tok]) < 1e-3       # the kernel's fast logarithms may swap a near-tie
+
+
+def test_sampler_noise_is_finite_at_the_ends_of_the_hash_range():
+    """The entries whose hash gives the largest and the smallest uniform number get noise of about +16.6 and -2.8:
+    neither beats (or loses to) a logit that is 40 away.  A uniform number that rounded to 1 would win every time."""
+    seed = 5
+    row_seed = _mix32(torch.tensor(seed & 0xFFFFFFFF, device=DEV, dtype=torch.int64))      # row 0
+    hi = lo = None
+    for start in range(0, 1 << 28, 1 << 24):
+        gj = torch.arange(start, start + (1 << 24), device=DEV, dtype=torch.int64)
+        k = _mix32((row_seed + gj) & 0xFFFFFFFF) >> 9
+        if hi is None and bool((k == 0x7FFFFF).any()):
+            hi = int(gj[(k == 0x7FFFFF).nonzero()[0]])
+        if lo is None and bool((k == 0).any()):
+            lo = int(gj[(k == 0).nonzero()[0]])
+        if hi is not None and lo is not None:
+            break
+    assert hi is not None and lo is not None
+    t = torch.ones(1, device=DEV)
+    for g, other in ((hi, 40.0), (lo, -40.0)):
+        off = max(0, g - 11)
+        logits = torch.full((1, 32), other, device=DEV, dtype=torch.bfloat16)
+        logits[0, g - off] = 0.0
+        tok = int(ops.sample(logits, t, seed=seed, vocab_offset=off)[0])
+        assert (tok != g) if other > 0 else (tok == g)
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,qk", [(128, 8, 2, True), (64, 4, 2, False), (128, 4, 4, False)])
 def test_rope_qknorm_store(D, Hq, Hkv, qk):
     T, nb, bs = 45, 8, 16
