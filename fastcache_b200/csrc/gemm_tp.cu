@@ -20,7 +20,8 @@
 //   "gathered" flag of a chunk's owner before it loads the first tile of that chunk and starts with
 //   its own chunk, so the GEMM runs while later chunks are still arriving.
 //
-// MODE_RS, pipelined form (default): the tiles are walked row group by row group across the owners (group g of
+// MODE_RS, pipelined form (FC_TP_PIPELINE=1; off by default, it measured no faster than the one reduction phase
+// after the GEMM): the tiles are walked row group by row group across the owners (group g of
 // owner rank + 1, of rank + 2, ..., of this rank, then group g + 1, ...), every rank counts the tiles it has
 // delivered per (owner, 128-row group) and raises a flag per group, and six extra warps per CTA ("reducers")
 // wait for the flags of the groups this rank owns and reduce + normalise + send them while the main loop is still
