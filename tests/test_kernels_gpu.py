@@ -127,6 +127,25 @@ def test_sampler_draw_matches_its_statement(B, V, ld, offset, limit):
             assert float(v.max() - v[tok]) < 1e-3       # the kernel's fast logarithms may swap a near-tie
 
 
+def test_sampler_frequencies_follow_the_tempered_softmax():
+    """49152 draws of one 12-entry row (rows of a batch and steps differ only in the noise): every entry is drawn
+    with its softmax(logits / T) probability, within four standard deviations."""
+    B, V, T = 16384, 12, 0.7
+    row = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5, -1.0, 3.0, 2.5, -2.0, 0.25, 1.75]).to(torch.bfloat16)
+    logits = row.repeat(B, 1).to(DEV)
+    temps = torch.full((B,), T, device=DEV)
+    counts = torch.zeros(V, dtype=torch.float64)
+    seeds = (3, 1000003 + 4, 77777)
+    for seed in seeds:
+        tok = ops.sample(logits, temps, seed=seed)
+        counts += torch.bincount(tok.cpu(), minlength=V).double()
+    n = B * len(seeds)
+    p = torch.softmax(row.double() / T, dim=0)
+    sigma = torch.sqrt(p * (1 - p) / n)
+    assert float(counts.sum()) == n
+    assert torch.all((counts / n - p).abs() < 4 * sigma + 1e-4), (counts / n, p)
+
+
 def test_sampler_noise_is_finite_at_the_ends_of_the_hash_range():
     """The entries whose hash gives the largest and the smallest uniform number get noise of about +16.6 and -2.8:
     neither beats (or loses to) a logit that is 40 away.  A uniform number that rounded to 1 would win every time."""
