@@ -38,6 +38,16 @@ def test_tp_cpu_gloo_split_prompts_match_unsplit(tmp_path):
     assert one["tokens"] == two["tokens"]
 
 
+def test_tp_cpu_gloo_several_decode_steps_per_call(tmp_path):
+    """Two gloo ranks that run three decode steps per engine step (replicated engines must take the same
+    decisions about when they may) against one rank stepping one at a time, greedy and sampled."""
+    one = _run(1, "cpu", str(tmp_path / "a.json"), 29661, ["--kv-heads", "2"])
+    two = _run(2, "cpu", str(tmp_path / "b.json"), 29662, ["--kv-heads", "2", "--decode-steps", "3"])
+    assert one["tokens"] == two["tokens"] and one["sampled"] == two["sampled"] and two["ranks_agree"]
+    assert one["decode_steps"] + one["prefill_steps"] == one["engine_steps"]
+    assert two["decode_steps"] + two["prefill_steps"] > two["engine_steps"]       # some steps made several
+
+
 def test_tp_cpu_gloo_sharded_embedding_matches_single_rank(tmp_path):
     """The vocabulary-parallel table (masked lookup + all-reduce), which large vocabularies fall back to."""
     one = _run(1, "cpu", str(tmp_path / "a.json"), 29651, ["--kv-heads", "2"])
@@ -66,6 +76,7 @@ def test_tp_gpu_fused_comm(tmp_path, world):
     multi = _run(world, "cuda", str(tmp_path / "d.json"), port + 3, ["--decode-steps", "3"])
     assert multi["status"] == 0 and multi["engine_status"] == 0 and multi["ranks_agree"]
     assert multi["tokens"] == many["tokens"] and multi["sampled"] == many["sampled"]
+    assert multi["decode_steps"] + multi["prefill_steps"] > multi["engine_steps"]
     # same engine with the one-shot limit lowered so that prefill takes the GEMM + reduce-scatter path
     big = _run(world, "cuda", str(tmp_path / "c.json"), port + 2, ["--one-shot-tokens", "64"])
     assert big["status"] == 0 and big["engine_status"] == 0 and big["ranks_agree"]

@@ -105,6 +105,9 @@ def main():
     # sampled (not greedy) tokens: every rank must draw the same ones, from its own vocabulary shard
     warm = llm.generate(prompts, SamplingParams(temperature=0.8, max_tokens=6, ignore_eos=True))
     res["sampled"] = [o["token_ids"] for o in warm]
+    res["decode_steps"] = int(llm.stats.decode_steps)
+    res["prefill_steps"] = int(llm.stats.prefill_steps)
+    res["engine_steps"] = int(llm.stats.steps)
     if world > 1:
         mine = {"tokens": res["tokens"], "sampled": res["sampled"]}
         everyone = [None] * world
