@@ -260,7 +260,10 @@ void launch_allreduce_add_rmsnorm(const CommPeers& peers, int buf, const void* m
                                   int splits, long long split_stride, const void* bias) {
   if (T == 0) return;
   if (H % 8 != 0 || H > AR_THREADS * AR_MAX_CHUNKS * 8) throw std::runtime_error("allreduce: unsupported hidden size");
-  // every CTA takes part in a cross-GPU flag exchange, so all of them must be resident at once
+  // CTA b exchanges flags only with CTA b of the peers (no CTA waits for another CTA of its own grid), and CTAs
+  // are dispatched in index order on every rank, so the lowest unfinished slot is resident everywhere and the
+  // exchange makes progress even while kernels of other streams hold SMs.  The grid is still kept within what
+  // one GPU holds at once (COMM_MAX_SLOTS CTAs, several per SM) so that no slot waits for a whole wave.
   const int grid = T < COMM_MAX_SLOTS ? T : COMM_MAX_SLOTS;
   cudaError_t e;
   if (peers.reduced_row0 > 0 && mc_in != nullptr) {

@@ -731,7 +731,11 @@ void gemm_rs_add_norm(const void* x, const void* w, int M, int N, int K, long lo
   const CUtensorMap ta = make_tmap_bf16_2d(x, M, K, ldx, TP_BM, TP_BK);
   const CUtensorMap tb = make_tmap_bf16_2d(w, N, K, ldw, TP_BN, TP_BK);
   const int sms = sm_limit > 0 ? sm_limit : gemm_num_sms();
-  // every CTA takes part in the flag exchange of phase 2: the grid must be fully resident
+  // Every CTA takes part in the flag exchange of phase 2, and a flag is raised only when ALL tiles of a rank are
+  // delivered, so every CTA must get an SM without another CTA of this grid having to finish first.  The grid is
+  // therefore at most one CTA per SM of the stream's SM set (the green context's, if any).  Kernels of other
+  // streams can delay a CTA's start (they end without waiting for this kernel) but not prevent it; the waits of
+  // phase 2 are bounded and report through the status word if that delay ever exceeded the limit.
   if (p.pipelined && p.stage_mc != nullptr) {
     auto kern = gemm_tp_kernel<MODE_RS, true, true>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes());
