@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <algorithm>
 #include <stdexcept>
+#include <string>
 
 #include "kernels.h"
 #include "launch.h"
@@ -500,9 +501,12 @@ void launch_rope_qknorm_store(const void* qkv, const void* positions, const void
 void launch_sample(const void* logits, const void* temps, void* out, int B, int V, long long ld, uint32_t seed,
                    cudaStream_t s, int vocab_offset, int v_limit, const uint32_t* status) {
   if (B == 0) return;
-  launch_pdl_cluster(PDL_SAMPLE, sample_kernel, dim3(B, SAMPLE_SPLIT), dim3(SAMPLE_THREADS), 0, s, SAMPLE_SPLIT,
-                     (const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed, vocab_offset,
-                     v_limit < 0 ? vocab_offset + V : v_limit, status);
+  const cudaError_t e =
+      launch_pdl_cluster(PDL_SAMPLE, sample_kernel, dim3(B, SAMPLE_SPLIT), dim3(SAMPLE_THREADS), 0, s, SAMPLE_SPLIT,
+                         (const bf16*)logits, (const float*)temps, (long long*)out, V, ld, seed, vocab_offset,
+                         v_limit < 0 ? vocab_offset + V : v_limit, status);
+  // a cluster that the stream's SM set cannot place is a launch error, not a kernel that ran: say so here
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sampler launch: ") + cudaGetErrorString(e));
 }
 
 }  // namespace fc
