@@ -84,3 +84,35 @@ def test_tp_gpu_fused_comm(tmp_path, world):
     # bf16 summation order differs between 1 and N ranks: the first tokens (pure prefill) agree
     same = sum(a[0] == b[0] for a, b in zip(one["tokens"], many["tokens"]))
     assert same >= len(one["tokens"]) - 1, (one, many)
+
+
+def _tp_inference(world, cfg_path, port, extra=()):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=os.path.dirname(HERE))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "fastcache_b200.serving.tp_inference",
+           "--model", cfg_path, "--tp-size", str(world), "--backend", "gloo", "--num-prompts", "3",
+           "--prompt-len", "40", "--max-tokens", "5", *extra]
+    r = subprocess.run(cmd, env=dict(env, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, r.stdout          # rank 0 alone prints the result
+    return json.loads(lines[0])
+
+
+def test_tp_inference_command_line_two_gloo_ranks(tmp_path):
+    """`python -m fastcache_b200.serving.tp_inference` (the reference's tp_inference.py:34-123) on a random-init
+    model given as an HF config file: two ranks print one result with the tokens of one rank, with and without
+    key-norm eviction."""
+    cfg = dict(model_type="llama", architectures=["LlamaForCausalLM"], hidden_size=128, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, intermediate_size=256, vocab_size=512,
+               rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=512, tie_word_embeddings=False,
+               eos_token_id=2, torch_dtype="float32")
+    path = str(tmp_path / "config.json")
+    json.dump(cfg, open(path, "w"))
+    one = _tp_inference(1, path, 29671)
+    two = _tp_inference(2, path, 29672)
+    assert one["tp"] == 1 and two["tp"] == 2 and one["output_tokens"] == two["output_tokens"] == 15
+    assert one["first"] == two["first"]
+    pressed = _tp_inference(2, path, 29673, ["--enable-compression", "--kvpress-method", "knorm",
+                                             "--compression-factor", "2"])
+    assert pressed["output_tokens"] == 15
