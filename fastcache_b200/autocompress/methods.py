@@ -16,8 +16,8 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..compress import quant as Q
-from ..compress.scorers import NEEDS_QUERIES, SCORERS, n_kept_for, score_keys, select_keep
-from .profiles import CompressMethodProfile, ComputeType, get_profile
+from ..compress.scorers import NEEDS_QUERIES, n_kept_for, score_keys, select_keep
+from .profiles import CompressMethodProfile, get_profile
 
 KV = List[Tuple[torch.Tensor, torch.Tensor]]
 

@@ -24,7 +24,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from .ccm import BANKS, PackedCCMWeights, _CCMBase
+from .ccm import PackedCCMWeights, _CCMBase
 
 KV = List[Tuple[torch.Tensor, torch.Tensor]]
 

@@ -23,7 +23,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .ccm import PackedCCMWeights, ccm_segment_len
-from .scorers import NEEDS_QUERIES, SHARED_INDICES, score_keys, select_keep
+from .scorers import NEEDS_QUERIES, score_keys, select_keep
 
 
 def _rows(pool_lkv: torch.Tensor, block_ids: torch.Tensor, n: int) -> torch.Tensor:

@@ -34,7 +34,7 @@ from ..utils.tracing import StepTrace, nvtx_range
 from .model_runner import ModelRunner
 from .scheduler import Scheduler
 from .async_compression import AsyncCompressionManager
-from .sequence import CompressionState, Sequence, SequenceStatus
+from .sequence import CompressionState, Sequence
 
 
 @dataclass

@@ -19,7 +19,6 @@ static-buffer, padded-batch replay code with eager execution in place of
 """
 from __future__ import annotations
 
-import os
 from typing import Any, Dict, List, Optional, Sequence as Seq, Tuple
 
 import numpy as np
@@ -36,7 +35,7 @@ from ..utils.context import reset_context, set_context
 from ..utils.loader import init_random_weights, load_model
 from ..utils.memory import get_gpu_memory
 from .async_compression import AsyncCompressionManager  # noqa: F401  (the reference exports it from here)
-from .sequence import CompressionState, Sequence
+from .sequence import Sequence
 
 
 def _resolve_device(config: Config) -> torch.device:

@@ -8,7 +8,6 @@ The rotation itself is fused with the q/k RMSNorm and the KV-pool store in
 from __future__ import annotations
 
 import math
-from functools import lru_cache
 from typing import Optional
 
 import torch

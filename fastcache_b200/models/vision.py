@@ -18,8 +18,7 @@ The towers are replicated on every tensor-parallel rank, like the reference's.
 """
 from __future__ import annotations
 
-import math
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 import numpy as np
 import torch

@@ -1,7 +1,6 @@
 """CUDA attention wrappers."""
 from __future__ import annotations
 
-import torch
 
 from .loader import ext
 

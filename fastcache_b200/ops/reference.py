@@ -6,7 +6,6 @@ name here) and the execution path on CPU.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

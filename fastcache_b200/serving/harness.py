@@ -23,7 +23,6 @@ reporting.
 from __future__ import annotations
 
 import heapq
-import math
 import random
 import threading
 import time
