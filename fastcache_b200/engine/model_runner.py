@@ -35,7 +35,7 @@ from ..utils.context import reset_context, set_context
 from ..utils.loader import init_random_weights, load_model
 from ..utils.memory import get_gpu_memory
 from .async_compression import AsyncCompressionManager  # noqa: F401  (the reference exports it from here)
-from .sequence import Sequence
+from .sequence import CompressionState, Sequence  # noqa: F401  (CompressionState: the reference defines it in llava_model_runner.py:43)
 
 
 def _resolve_device(config: Config) -> torch.device:

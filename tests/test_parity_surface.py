@@ -30,7 +30,8 @@ def test_async_manager_views_engine_state():
     mgr = llm.async_manager
     assert isinstance(mgr, AsyncCompressionManager) and llm.model_runner._async_manager is mgr
     from nanovllm.engine.llava_model_runner import AsyncCompressionManager as Aliased
-    assert Aliased is AsyncCompressionManager
+    from nanovllm.engine.llava_model_runner import CompressionState as AliasedState     # llava_model_runner.py:43
+    assert Aliased is AsyncCompressionManager and AliasedState is CompressionState
     sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
     g = torch.Generator().manual_seed(0)
     seqs = [llm.add_request(torch.randint(3, 1000, (64,), generator=g).tolist(), sp) for _ in range(2)]
